@@ -1,0 +1,63 @@
+// C ABI of libccb200: every kernel launcher is a plain `extern "C"` function
+// taking raw device pointers, sizes and a CUDA stream, so the Python layer
+// binds it with ctypes and no libtorch headers are compiled into the library.
+// All launchers return 0 on success or a negative host-side error code; device
+// side failures (a bounded wait that ran out) land in the status word returned
+// by ccb_status_ptr() and are read back by ccb_read_status().
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// ---- runtime --------------------------------------------------------------
+int ccb_init(void);                      // per-process, per-current-device set-up
+int* ccb_status_ptr(void);               // device int, 0 == OK
+int ccb_read_status(int reset);          // synchronises; returns the status word
+int ccb_num_sms(void);
+int ccb_launch_count(void);              // kernels launched by this library so far
+const char* ccb_last_error(void);
+
+// ---- generic tcgen05 GEMM ---------------------------------------------------
+// C[b][s] (M x N) = epilogue( sum_k opA(A)[m,k] * opB(B)[n,k] )
+//   a_mn == 0: A is stored [M rows][K contiguous] (K-major)
+//   a_mn == 1: A is stored [K rows][M contiguous] (MN-major, i.e. A^T in memory)
+//   b_mn likewise for B with N.
+// bf16 operands, fp32 accumulation in TMEM.  `splits` > 1 partitions K; split s
+// writes its own partial tile at C + s * c_split (the caller reduces).
+enum CcbEpilogue {
+  CCB_EPI_STORE = 0,          // out = alpha * acc + beta * Cin
+  CCB_EPI_ROWSCALE = 1,       // out = rs(m) * acc,  rs = rsqrt(rowss[m] * inv_dim + eps)
+  CCB_EPI_ROWSCALE_SILU = 2,  // u = rs(m) * acc -> C ; silu(u) -> C2
+  CCB_EPI_RESID_SS = 3,       // out = R1 + acc ; ss_out[m] (+)= sum_n out^2
+  CCB_EPI_DSILU = 4,          // out = acc * silu'(R1) * rs(m)
+  CCB_EPI_RMSBWD = 5,         // out = R2 + acc - R1 * (rs^2 * inv_dim * sum_n acc * R1)   (N <= tile)
+};
+
+typedef struct CcbGemmArgs {
+  const void* A;
+  const void* B;
+  void* C;
+  void* C2;
+  const void* Cin;
+  const void* R1;
+  const void* R2;
+  const float* rowss;
+  float* ss_out;
+  int64_t M, N, K;
+  int64_t batch, splits;
+  int64_t lda, ldb, ldc, ldcin, ldr;         // element strides between rows
+  int64_t a_batch, b_batch, c_batch, cin_batch, c_split;  // element strides
+  int64_t a_mn, b_mn;
+  int64_t epi;
+  int64_t out_fp32;                          // 1: C is float, 0: C is bf16
+  int64_t ss_atomic;                         // RESID_SS: atomicAdd instead of store
+  float alpha, beta, inv_dim, eps;
+} CcbGemmArgs;
+
+int ccb_gemm(const CcbGemmArgs* args, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,566 @@
+// Bandwidth-bound helpers around the GEMMs: embedding gather with fused row
+// sum-of-squares, sorted scatter-add embedding backward, split-K reduction with
+// the RMSNorm-weight fold, standalone RMSNorm (fwd/bwd) for callers outside
+// the fused trunk, optimizer updates (Muon momentum / apply, AdamW, LAMB
+// moments), global grad-norm clip, casts and the SGD step used by test-time
+// training.  Everything is vectorised to 16-byte accesses where shapes allow.
+//
+// Reference counterparts: kernels/_lm_head_loss/src/rms_norm.cu:23-112 (RMSNorm),
+// optim/muon.py:390-448 and 540-658 (Muon / AdamW updates),
+// distributed.py:175-216 (fused grad clip).
+#include "ptx.cuh"
+#include "ccb_api.h"
+#include "runtime.h"
+
+namespace ccb {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float block_sum(float v, float* sm) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (l == 0) sm[w] = v;
+  __syncthreads();
+  float r = (threadIdx.x < nw) ? sm[threadIdx.x] : 0.f;
+  if (w == 0) r = warp_sum(r);
+  if (threadIdx.x == 0) sm[0] = r;
+  __syncthreads();
+  return sm[0];
+}
+
+// ---------------------------------------------------------------------------
+// Embedding forward: x[r, :] = E[tok[r], :], ss[r] = sum x^2.  One warp per row.
+// ---------------------------------------------------------------------------
+template <typename TokT>
+__global__ void embed_fwd_kernel(const TokT* __restrict__ tok, const __nv_bfloat16* __restrict__ E,
+                                 __nv_bfloat16* __restrict__ x, float* __restrict__ ss, long long R,
+                                 int D, int V) {
+  const long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= R) return;
+  const int lane = threadIdx.x & 31;
+  long long t = (long long)tok[r];
+  t = t < 0 ? 0 : (t >= V ? V - 1 : t);
+  const uint4* src = reinterpret_cast<const uint4*>(E + t * D);
+  uint4* dst = reinterpret_cast<uint4*>(x + r * D);
+  float acc = 0.f;
+  for (int c = lane; c < D / 8; c += 32) {
+    uint4 q = __ldg(src + c);
+    dst[c] = q;
+    float2 f;
+    f = unpack_bf16x2(q.x); acc += f.x * f.x + f.y * f.y;
+    f = unpack_bf16x2(q.y); acc += f.x * f.x + f.y * f.y;
+    f = unpack_bf16x2(q.z); acc += f.x * f.x + f.y * f.y;
+    f = unpack_bf16x2(q.w); acc += f.x * f.x + f.y * f.y;
+  }
+  acc = warp_sum(acc);
+  if (lane == 0 && ss) ss[r] = acc;
+}
+
+// ---------------------------------------------------------------------------
+// Embedding backward over token-sorted rows.  Each warp owns CH consecutive
+// sorted positions, accumulates rows of equal token in registers and flushes
+// with fp32 atomics when the token changes: at most (#chunks + #tokens) * D
+// atomics in total, and hot tokens spread over many warps.
+// dE must be zeroed by the caller (or hold a running accumulation).
+// ---------------------------------------------------------------------------
+template <int VPL>   // uint4 vectors per lane: D = 256 * VPL
+__global__ void embed_bwd_sorted_kernel(const long long* __restrict__ sorted_tok,
+                                        const long long* __restrict__ perm,
+                                        const __nv_bfloat16* __restrict__ dx,
+                                        float* __restrict__ dE, long long R, int D, int V, int CH) {
+  const long long chunk = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long p0 = chunk * CH;
+  if (p0 >= R) return;
+  const long long p1 = (p0 + CH < R) ? p0 + CH : R;
+  const int lane = threadIdx.x & 31;
+  float acc[VPL][8];
+#pragma unroll
+  for (int v = 0; v < VPL; ++v)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[v][i] = 0.f;
+  long long cur = sorted_tok[p0];
+  for (long long p = p0; p < p1; ++p) {
+    const long long tk = sorted_tok[p];
+    if (tk != cur) {
+      if (cur >= 0 && cur < V) {
+#pragma unroll
+        for (int v = 0; v < VPL; ++v) {
+          float* o = dE + cur * D + (v * 32 + lane) * 8;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) { atomicAdd(o + i, acc[v][i]); acc[v][i] = 0.f; }
+        }
+      }
+      cur = tk;
+    }
+    const uint4* src = reinterpret_cast<const uint4*>(dx + perm[p] * D);
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+      uint4 q = __ldg(src + v * 32 + lane);
+      float2 f;
+      f = unpack_bf16x2(q.x); acc[v][0] += f.x; acc[v][1] += f.y;
+      f = unpack_bf16x2(q.y); acc[v][2] += f.x; acc[v][3] += f.y;
+      f = unpack_bf16x2(q.z); acc[v][4] += f.x; acc[v][5] += f.y;
+      f = unpack_bf16x2(q.w); acc[v][6] += f.x; acc[v][7] += f.y;
+    }
+  }
+  if (cur >= 0 && cur < V) {
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+      float* o = dE + cur * D + (v * 32 + lane) * 8;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) atomicAdd(o + i, acc[v][i]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Split-K reduction.  out[n,k] (+)= colscale[k] * sum_s part[s,n,k]; when W is
+// given also emits per-row-block partial column sums of sum[n,k] * W[n,k]
+// (the gradient of an RMSNorm weight folded into W), reduced by a second tiny
+// kernel so the result is deterministic.
+// grid: ceil(N / 8); block: 256 threads striding over k.
+// ---------------------------------------------------------------------------
+__global__ void splitk_reduce_kernel(const float* __restrict__ part, int S, long long split_stride,
+                                     int N, int K, const __nv_bfloat16* __restrict__ colscale,
+                                     const __nv_bfloat16* __restrict__ W, float* __restrict__ out,
+                                     int accumulate, float* __restrict__ colpart) {
+  const int n0 = blockIdx.x * 8;
+  for (int k = threadIdx.x; k < K; k += blockDim.x) {
+    const float cs = colscale ? __bfloat162float(colscale[k]) : 1.f;
+    float cacc = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int n = n0 + i;
+      if (n < N) {
+        float s = 0.f;
+        const float* pp = part + (long long)n * K + k;
+        for (int sp = 0; sp < S; ++sp) s += pp[(long long)sp * split_stride];
+        const long long o = (long long)n * K + k;
+        if (W) cacc += s * __bfloat162float(W[o]);
+        const float val = s * cs;
+        out[o] = accumulate ? out[o] + val : val;
+      }
+    }
+    if (colpart) colpart[(long long)blockIdx.x * K + k] = cacc;
+  }
+}
+
+__global__ void colsum_kernel(const float* __restrict__ part, int NB, int K, float* __restrict__ out,
+                              int accumulate) {
+  const int k = blockIdx.x * blockDim.x + threadIdx.x;
+  if (k >= K) return;
+  float s = 0.f;
+  for (int b = 0; b < NB; ++b) s += part[(long long)b * K + k];
+  out[k] = accumulate ? out[k] + s : s;
+}
+
+// W'[n,k] = W[n,k] * wn[k]  (bf16), the RMSNorm weight folded into a linear.
+__global__ void fold_colscale_kernel(const __nv_bfloat16* __restrict__ W,
+                                     const __nv_bfloat16* __restrict__ wn,
+                                     __nv_bfloat16* __restrict__ out, long long N, int K) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= N * K) return;
+  const int k = (int)(i % K);
+  out[i] = __float2bfloat16(__bfloat162float(W[i]) * __bfloat162float(wn[k]));
+}
+
+// ---------------------------------------------------------------------------
+// Standalone RMSNorm (one warp per row), fp32 statistics.
+// y = x * rsqrt(mean(x^2) + eps) * w ; optional residual add x = x + res first.
+// ---------------------------------------------------------------------------
+__global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                   const __nv_bfloat16* __restrict__ res,
+                                   const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                                   __nv_bfloat16* __restrict__ xsum, float* __restrict__ inv_rms,
+                                   long long R, int D, float eps) {
+  const long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= R) return;
+  const int lane = threadIdx.x & 31;
+  const __nv_bfloat16* xr = x + r * D;
+  float acc = 0.f;
+  for (int c = lane * 2; c < D; c += 64) {
+    float2 f = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(xr + c));
+    if (res) {
+      float2 g = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(res + r * D + c));
+      f.x = __bfloat162float(__float2bfloat16(f.x + g.x));
+      f.y = __bfloat162float(__float2bfloat16(f.y + g.y));
+      if (xsum) *reinterpret_cast<uint32_t*>(xsum + r * D + c) = pack_bf16x2(f.x, f.y);
+    }
+    acc += f.x * f.x + f.y * f.y;
+  }
+  acc = warp_sum(acc);
+  const float inv = rsqrtf(acc / (float)D + eps);
+  if (lane == 0 && inv_rms) inv_rms[r] = inv;
+  for (int c = lane * 2; c < D; c += 64) {
+    float2 f = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(xr + c));
+    if (res) {
+      float2 g = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(res + r * D + c));
+      f.x = __bfloat162float(__float2bfloat16(f.x + g.x));
+      f.y = __bfloat162float(__float2bfloat16(f.y + g.y));
+    }
+    float2 ww = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(w + c));
+    *reinterpret_cast<uint32_t*>(y + r * D + c) = pack_bf16x2(f.x * inv * ww.x, f.y * inv * ww.y);
+  }
+}
+
+// Backward: gx = inv * (go*w - xhat * mean(go*w*xhat)); weight grad as
+// per-block partials [gridDim.x, D] (deterministic second-stage reduce).
+__global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                   const __nv_bfloat16* __restrict__ w,
+                                   const __nv_bfloat16* __restrict__ go,
+                                   const float* __restrict__ inv_rms, __nv_bfloat16* __restrict__ gx,
+                                   float* __restrict__ gw_part, long long R, int D,
+                                   int rows_per_block) {
+  extern __shared__ float sm_gw[];   // [D]
+  for (int c = threadIdx.x; c < D; c += blockDim.x) sm_gw[c] = 0.f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const long long r0 = (long long)blockIdx.x * rows_per_block;
+  for (long long r = r0 + warp; r < r0 + rows_per_block && r < R; r += nw) {
+    const float inv = inv_rms[r];
+    float dot = 0.f;
+    for (int c = lane * 2; c < D; c += 64) {
+      float2 xv = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(x + r * D + c));
+      float2 gv = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(go + r * D + c));
+      float2 wv = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(w + c));
+      dot += gv.x * wv.x * xv.x * inv + gv.y * wv.y * xv.y * inv;
+    }
+    dot = warp_sum(dot) / (float)D;
+    for (int c = lane * 2; c < D; c += 64) {
+      float2 xv = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(x + r * D + c));
+      float2 gv = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(go + r * D + c));
+      float2 wv = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(w + c));
+      const float xh0 = xv.x * inv, xh1 = xv.y * inv;
+      *reinterpret_cast<uint32_t*>(gx + r * D + c) =
+          pack_bf16x2(inv * (gv.x * wv.x - xh0 * dot), inv * (gv.y * wv.y - xh1 * dot));
+      atomicAdd(&sm_gw[c], gv.x * xh0);       // shared-memory atomics: block-local only
+      atomicAdd(&sm_gw[c + 1], gv.y * xh1);
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < D; c += blockDim.x) gw_part[(long long)blockIdx.x * D + c] = sm_gw[c];
+}
+
+// ---------------------------------------------------------------------------
+// Optimizer kernels
+// ---------------------------------------------------------------------------
+// Muon momentum: buf = mu*buf + g ; dir = nesterov ? g + mu*buf : buf.  Writes
+// dir in bf16 and accumulates per-matrix sum of squares of the bf16-rounded
+// direction (one atomicAdd per block).  grid: (blocks_per_mat, G).
+__global__ void muon_momentum_kernel(const float* __restrict__ g, float* __restrict__ buf,
+                                     __nv_bfloat16* __restrict__ dir, float* __restrict__ sumsq,
+                                     long long numel_per_mat, float mu, int nesterov) {
+  __shared__ float sm[32];
+  const long long base = (long long)blockIdx.y * numel_per_mat;
+  float acc = 0.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < numel_per_mat;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float gv = g[base + i];
+    const float b = mu * buf[base + i] + gv;
+    buf[base + i] = b;
+    const float dv = nesterov ? gv + mu * b : b;
+    const __nv_bfloat16 q = __float2bfloat16(dv);
+    dir[base + i] = q;
+    const float qf = __bfloat162float(q);
+    acc += qf * qf;
+  }
+  acc = block_sum(acc, sm);
+  if (threadIdx.x == 0) atomicAdd(sumsq + blockIdx.y, acc);
+}
+
+// X = dir / (||dir||_F + eps) in bf16, in place.
+__global__ void muon_normalize_kernel(__nv_bfloat16* __restrict__ dir, const float* __restrict__ sumsq,
+                                      long long numel_per_mat, float eps) {
+  const long long base = (long long)blockIdx.y * numel_per_mat;
+  const float inv = 1.f / (sqrtf(sumsq[blockIdx.y]) + eps);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < numel_per_mat;
+       i += (long long)gridDim.x * blockDim.x)
+    dir[base + i] = __float2bfloat16(__bfloat162float(dir[base + i]) * inv);
+}
+
+// p = p * (1 - lr*wd) - lr*scale * O   (bf16 params, bf16 orthogonalised update)
+__global__ void muon_apply_kernel(__nv_bfloat16* __restrict__ p, const __nv_bfloat16* __restrict__ O,
+                                  long long n, float lr_scale, float decay_mul) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float v = __bfloat162float(p[i]) * decay_mul - lr_scale * __bfloat162float(O[i]);
+    p[i] = __float2bfloat16(v);
+  }
+}
+
+// Decoupled AdamW over a flat range; fp32 moments, bf16 or fp32 params.
+template <typename PT>
+__global__ void adamw_kernel(PT* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
+                             float* __restrict__ v, long long n, float lr, float b1, float b2,
+                             float eps, float wd, float bias1, float bias2_sqrt,
+                             const float* __restrict__ gscale) {
+  const float gs = gscale ? *gscale : 1.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float gv = g[i] * gs;
+    const float mi = b1 * m[i] + (1.f - b1) * gv;
+    const float vi = b2 * v[i] + (1.f - b2) * gv * gv;
+    m[i] = mi;
+    v[i] = vi;
+    float pv = (float)p[i];
+    pv *= (1.f - lr * wd);
+    pv -= (lr / bias1) * mi / (sqrtf(vi) / bias2_sqrt + eps);
+    p[i] = (PT)pv;
+  }
+}
+
+// Sum of squares over a flat fp32 range -> out[0] (atomic, caller zeroes).
+__global__ void sumsq_kernel(const float* __restrict__ g, long long n, float* __restrict__ out) {
+  __shared__ float sm[32];
+  float acc = 0.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x)
+    acc += g[i] * g[i];
+  acc = block_sum(acc, sm);
+  if (threadIdx.x == 0) atomicAdd(out, acc);
+}
+
+// clip coefficient = min(1, max_norm / (sqrt(sumsq) + 1e-6)) written to out[1];
+// then g *= coef over the range (second launch reads out[1]).
+__global__ void clip_coef_kernel(float* __restrict__ stat, float max_norm) {
+  const float norm = sqrtf(stat[0]);
+  stat[1] = fminf(1.f, max_norm / (norm + 1e-6f));
+  stat[2] = norm;
+}
+__global__ void scale_by_ptr_kernel(float* __restrict__ g, long long n, const float* __restrict__ coef) {
+  const float c = *coef;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x)
+    g[i] *= c;
+}
+
+// p -= lr * g  (test-time-training SGD), bf16 params, fp32 grads.
+__global__ void sgd_kernel(__nv_bfloat16* __restrict__ p, const float* __restrict__ g, long long n,
+                           float lr) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x)
+    p[i] = __float2bfloat16(__bfloat162float(p[i]) - lr * g[i]);
+}
+
+__global__ void cast_f32_to_bf16_kernel(const float* __restrict__ s, __nv_bfloat16* __restrict__ d,
+                                        long long n, float scale) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x)
+    d[i] = __float2bfloat16(s[i] * scale);
+}
+__global__ void cast_bf16_to_f32_kernel(const __nv_bfloat16* __restrict__ s, float* __restrict__ d,
+                                        long long n, float scale, int accumulate) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float v = __bfloat162float(s[i]) * scale;
+    d[i] = accumulate ? d[i] + v : v;
+  }
+}
+
+static inline int grid_for(long long n, int threads, int cap = 148 * 8) {
+  long long b = (n + threads - 1) / threads;
+  if (b < 1) b = 1;
+  return (int)(b > cap ? cap : b);
+}
+
+}  // namespace ccb
+
+using namespace ccb;
+#define CCB_CHECK_LAUNCH(name)                                                   \
+  do {                                                                           \
+    count_launch();                                                              \
+    cudaError_t e__ = cudaGetLastError();                                        \
+    if (e__ != cudaSuccess) return set_error(name ": %s", cudaGetErrorString(e__)); \
+  } while (0)
+
+extern "C" int ccb_embed_fwd(const void* tok, int64_t tok_is_i64, const void* E, void* x, float* ss,
+                             int64_t R, int64_t D, int64_t V, void* stream) {
+  if (R <= 0) return 0;
+  if (D % 8) return set_error("ccb_embed_fwd: D must be a multiple of 8");
+  const int wpb = 8;
+  const unsigned grid = (unsigned)((R + wpb - 1) / wpb);
+  if (tok_is_i64)
+    embed_fwd_kernel<long long><<<grid, wpb * 32, 0, (cudaStream_t)stream>>>(
+        (const long long*)tok, (const __nv_bfloat16*)E, (__nv_bfloat16*)x, ss, R, (int)D, (int)V);
+  else
+    embed_fwd_kernel<int><<<grid, wpb * 32, 0, (cudaStream_t)stream>>>(
+        (const int*)tok, (const __nv_bfloat16*)E, (__nv_bfloat16*)x, ss, R, (int)D, (int)V);
+  CCB_CHECK_LAUNCH("embed_fwd");
+  return 0;
+}
+
+extern "C" int ccb_embed_bwd_sorted(const int64_t* sorted_tok, const int64_t* perm, const void* dx,
+                                    float* dE, int64_t R, int64_t D, int64_t V, void* stream) {
+  if (R <= 0) return 0;
+  const int CH = 32, wpb = 4;
+  const long long chunks = (R + CH - 1) / CH;
+  const unsigned grid = (unsigned)((chunks + wpb - 1) / wpb);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (D == 256)
+    embed_bwd_sorted_kernel<1><<<grid, wpb * 32, 0, s>>>((const long long*)sorted_tok,
+        (const long long*)perm, (const __nv_bfloat16*)dx, dE, R, (int)D, (int)V, CH);
+  else if (D == 512)
+    embed_bwd_sorted_kernel<2><<<grid, wpb * 32, 0, s>>>((const long long*)sorted_tok,
+        (const long long*)perm, (const __nv_bfloat16*)dx, dE, R, (int)D, (int)V, CH);
+  else if (D == 1024)
+    embed_bwd_sorted_kernel<4><<<grid, wpb * 32, 0, s>>>((const long long*)sorted_tok,
+        (const long long*)perm, (const __nv_bfloat16*)dx, dE, R, (int)D, (int)V, CH);
+  else
+    return set_error("ccb_embed_bwd_sorted: D=%lld unsupported (256, 512, 1024)", (long long)D);
+  CCB_CHECK_LAUNCH("embed_bwd_sorted");
+  return 0;
+}
+
+extern "C" int ccb_splitk_reduce(const float* part, int64_t S, int64_t split_stride, int64_t N,
+                                 int64_t K, const void* colscale, const void* W, float* out,
+                                 int64_t accumulate, float* colpart, float* colsum_out,
+                                 int64_t colsum_accumulate, void* stream) {
+  if (N <= 0 || K <= 0) return 0;
+  const unsigned nb = (unsigned)((N + 7) / 8);
+  cudaStream_t s = (cudaStream_t)stream;
+  splitk_reduce_kernel<<<nb, 256, 0, s>>>(part, (int)S, split_stride, (int)N, (int)K,
+                                          (const __nv_bfloat16*)colscale, (const __nv_bfloat16*)W,
+                                          out, (int)accumulate, W ? colpart : nullptr);
+  CCB_CHECK_LAUNCH("splitk_reduce");
+  if (W && colpart && colsum_out) {
+    colsum_kernel<<<(unsigned)((K + 127) / 128), 128, 0, s>>>(colpart, (int)nb, (int)K, colsum_out,
+                                                              (int)colsum_accumulate);
+    CCB_CHECK_LAUNCH("colsum");
+  }
+  return 0;
+}
+
+extern "C" int ccb_colsum(const float* part, int64_t NB, int64_t K, float* out, int64_t accumulate,
+                          void* stream) {
+  if (K <= 0) return 0;
+  colsum_kernel<<<(unsigned)((K + 127) / 128), 128, 0, (cudaStream_t)stream>>>(part, (int)NB, (int)K,
+                                                                               out, (int)accumulate);
+  CCB_CHECK_LAUNCH("colsum");
+  return 0;
+}
+
+extern "C" int ccb_fold_colscale(const void* W, const void* wn, void* out, int64_t N, int64_t K,
+                                 void* stream) {
+  if (N * K <= 0) return 0;
+  fold_colscale_kernel<<<(unsigned)((N * K + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)W, (const __nv_bfloat16*)wn, (__nv_bfloat16*)out, N, (int)K);
+  CCB_CHECK_LAUNCH("fold_colscale");
+  return 0;
+}
+
+extern "C" int ccb_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* xsum,
+                               float* inv_rms, int64_t R, int64_t D, float eps, void* stream) {
+  if (R <= 0) return 0;
+  if (D % 2) return set_error("ccb_rmsnorm_fwd: D must be even");
+  const int wpb = 8;
+  rmsnorm_fwd_kernel<<<(unsigned)((R + wpb - 1) / wpb), wpb * 32, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w, (__nv_bfloat16*)y,
+      (__nv_bfloat16*)xsum, inv_rms, R, (int)D, eps);
+  CCB_CHECK_LAUNCH("rmsnorm_fwd");
+  return 0;
+}
+
+// gw_part must hold ccb_rmsnorm_bwd_blocks(R) * D floats.
+extern "C" int64_t ccb_rmsnorm_bwd_blocks(int64_t R) {
+  const int64_t rpb = 256;
+  return (R + rpb - 1) / rpb;
+}
+extern "C" int ccb_rmsnorm_bwd(const void* x, const void* w, const void* go, const float* inv_rms,
+                               void* gx, float* gw_part, float* gw_out, int64_t R, int64_t D,
+                               void* stream) {
+  if (R <= 0) return 0;
+  const int rpb = 256;
+  const unsigned nb = (unsigned)ccb_rmsnorm_bwd_blocks(R);
+  rmsnorm_bwd_kernel<<<nb, 256, (size_t)D * sizeof(float), (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)go, inv_rms,
+      (__nv_bfloat16*)gx, gw_part, R, (int)D, rpb);
+  CCB_CHECK_LAUNCH("rmsnorm_bwd");
+  if (gw_out) {
+    colsum_kernel<<<(unsigned)((D + 127) / 128), 128, 0, (cudaStream_t)stream>>>(gw_part, (int)nb,
+                                                                                 (int)D, gw_out, 0);
+    CCB_CHECK_LAUNCH("colsum");
+  }
+  return 0;
+}
+
+extern "C" int ccb_muon_momentum(const float* g, float* buf, void* dir, float* sumsq, int64_t G,
+                                 int64_t numel_per_mat, float mu, int64_t nesterov, void* stream) {
+  if (G <= 0 || numel_per_mat <= 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  cudaMemsetAsync(sumsq, 0, sizeof(float) * (size_t)G, s);
+  dim3 grid((unsigned)grid_for(numel_per_mat, 256, 64), (unsigned)G);
+  muon_momentum_kernel<<<grid, 256, 0, s>>>(g, buf, (__nv_bfloat16*)dir, sumsq, numel_per_mat, mu,
+                                            (int)nesterov);
+  CCB_CHECK_LAUNCH("muon_momentum");
+  return 0;
+}
+extern "C" int ccb_muon_normalize(void* dir, const float* sumsq, int64_t G, int64_t numel_per_mat,
+                                  float eps, void* stream) {
+  if (G <= 0 || numel_per_mat <= 0) return 0;
+  dim3 grid((unsigned)grid_for(numel_per_mat, 256, 64), (unsigned)G);
+  muon_normalize_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)dir, sumsq,
+                                                                numel_per_mat, eps);
+  CCB_CHECK_LAUNCH("muon_normalize");
+  return 0;
+}
+extern "C" int ccb_muon_apply(void* p, const void* O, int64_t n, float lr_scale, float decay_mul,
+                              void* stream) {
+  if (n <= 0) return 0;
+  muon_apply_kernel<<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>(
+      (__nv_bfloat16*)p, (const __nv_bfloat16*)O, n, lr_scale, decay_mul);
+  CCB_CHECK_LAUNCH("muon_apply");
+  return 0;
+}
+extern "C" int ccb_adamw(void* p, int64_t p_is_bf16, const float* g, float* m, float* v, int64_t n,
+                         float lr, float b1, float b2, float eps, float wd, float bias1,
+                         float bias2_sqrt, const float* gscale, void* stream) {
+  if (n <= 0) return 0;
+  if (p_is_bf16)
+    adamw_kernel<__nv_bfloat16><<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>(
+        (__nv_bfloat16*)p, g, m, v, n, lr, b1, b2, eps, wd, bias1, bias2_sqrt, gscale);
+  else
+    adamw_kernel<float><<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>(
+        (float*)p, g, m, v, n, lr, b1, b2, eps, wd, bias1, bias2_sqrt, gscale);
+  CCB_CHECK_LAUNCH("adamw");
+  return 0;
+}
+// stat: 3 floats {sumsq, coef, norm}.  Computes the global L2 norm of g[0:n]
+// and multiplies g by min(1, max_norm / (norm + 1e-6)) without a host sync.
+extern "C" int ccb_clip_grad_norm(float* g, int64_t n, float max_norm, float* stat, void* stream) {
+  if (n <= 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  cudaMemsetAsync(stat, 0, 3 * sizeof(float), s);
+  sumsq_kernel<<<grid_for(n, 256), 256, 0, s>>>(g, n, stat);
+  CCB_CHECK_LAUNCH("sumsq");
+  clip_coef_kernel<<<1, 1, 0, s>>>(stat, max_norm);
+  CCB_CHECK_LAUNCH("clip_coef");
+  scale_by_ptr_kernel<<<grid_for(n, 256), 256, 0, s>>>(g, n, stat + 1);
+  CCB_CHECK_LAUNCH("scale_by_ptr");
+  return 0;
+}
+extern "C" int ccb_sgd(void* p, const float* g, int64_t n, float lr, void* stream) {
+  if (n <= 0) return 0;
+  sgd_kernel<<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)p, g, n, lr);
+  CCB_CHECK_LAUNCH("sgd");
+  return 0;
+}
+extern "C" int ccb_cast_f32_to_bf16(const float* s, void* d, int64_t n, float scale, void* stream) {
+  if (n <= 0) return 0;
+  cast_f32_to_bf16_kernel<<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>(s, (__nv_bfloat16*)d, n,
+                                                                              scale);
+  CCB_CHECK_LAUNCH("cast_f32_to_bf16");
+  return 0;
+}
+extern "C" int ccb_cast_bf16_to_f32(const void* s, float* d, int64_t n, float scale,
+                                    int64_t accumulate, void* stream) {
+  if (n <= 0) return 0;
+  cast_bf16_to_f32_kernel<<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)s, d, n, scale, (int)accumulate);
+  CCB_CHECK_LAUNCH("cast_bf16_to_f32");
+  return 0;
+}

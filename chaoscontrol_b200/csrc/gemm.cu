@@ -1,0 +1,470 @@
+// Generic bf16 GEMM for sm_100a: TMA-fed shared-memory ring -> tcgen05.mma
+// (single-thread issue, fp32 accumulators in TMEM, two accumulators so the
+// epilogue of tile i overlaps the MMAs of tile i+1) -> tcgen05.ld epilogue
+// with the trunk's elementwise work fused in (RMSNorm row scale, SiLU and its
+// derivative, residual add with row sum-of-squares, RMSNorm backward).
+//
+// One persistent CTA per SM walks tiles round-robin.  Warp roles:
+//   warp 0      TMA producer (one lane)
+//   warp 1      TMEM owner + MMA issuer (one lane)
+//   warps 2..5  epilogue; warp w reads TMEM lanes [32*(w%4), 32*(w%4)+32)
+//
+// Replaces the library GEMM call sites of the reference trunk
+// (src/chaoscontrol/core.py:453-474, 503, 545, 327-335) and the batched
+// Newton-Schulz matmuls (src/chaoscontrol/optim/muon.py:42-45).
+#include "ptx.cuh"
+#include "ccb_api.h"
+#include "runtime.h"
+
+namespace ccb {
+
+constexpr int BM = 128;
+constexpr int BK = 64;                       // 64 bf16 = one 128-byte swizzle row
+constexpr int A_STAGE_BYTES = BM * BK * 2;   // 16 KiB
+constexpr int GEMM_THREADS = 192;
+
+struct GemmKArgs {
+  int M, N, K;
+  int batch, splits, tiles_m, tiles_n, kblocks, kper;
+  int epi, out_fp32, ss_atomic;
+  long long ldc, c_batch, c_split, ldcin, cin_batch, ldr;
+  void* C;
+  void* C2;
+  const void* Cin;
+  const void* R1;
+  const void* R2;
+  const float* rowss;
+  float* ss_out;
+  float alpha, beta, inv_dim, eps;
+  int* status;
+};
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int B_STAGE_BYTES = BN * BK * 2;
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int TMEM_COLS = 2 * BN;   // 512 or 256: powers of two
+  static constexpr int SMEM_BYTES =
+      1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256;
+};
+
+__device__ __forceinline__ void load_bf16x32(const __nv_bfloat16* src, float (&v)[32], int nvalid) {
+  if (nvalid >= 32) {
+    const uint4* s4 = reinterpret_cast<const uint4*>(src);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint4 q = __ldg(s4 + i);
+      float2 f0 = unpack_bf16x2(q.x), f1 = unpack_bf16x2(q.y), f2 = unpack_bf16x2(q.z),
+             f3 = unpack_bf16x2(q.w);
+      v[i * 8 + 0] = f0.x; v[i * 8 + 1] = f0.y; v[i * 8 + 2] = f1.x; v[i * 8 + 3] = f1.y;
+      v[i * 8 + 4] = f2.x; v[i * 8 + 5] = f2.y; v[i * 8 + 6] = f3.x; v[i * 8 + 7] = f3.y;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = (i < nvalid) ? __bfloat162float(src[i]) : 0.f;
+  }
+}
+
+__device__ __forceinline__ void store_bf16x32(__nv_bfloat16* dst, const float (&v)[32], int nvalid) {
+  if (nvalid >= 32) {
+    uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint4 q;
+      q.x = pack_bf16x2(v[i * 8 + 0], v[i * 8 + 1]);
+      q.y = pack_bf16x2(v[i * 8 + 2], v[i * 8 + 3]);
+      q.z = pack_bf16x2(v[i * 8 + 4], v[i * 8 + 5]);
+      q.w = pack_bf16x2(v[i * 8 + 6], v[i * 8 + 7]);
+      d4[i] = q;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (i < nvalid) dst[i] = __float2bfloat16(v[i]);
+  }
+}
+
+__device__ __forceinline__ void store_f32x32(float* dst, const float (&v)[32], int nvalid) {
+  if (nvalid >= 32) {
+    float4* d4 = reinterpret_cast<float4*>(dst);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) d4[i] = make_float4(v[i * 4], v[i * 4 + 1], v[i * 4 + 2], v[i * 4 + 3]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (i < nvalid) dst[i] = v[i];
+  }
+}
+
+struct TileCoord {
+  int b, sp, m0, n0, kb0, kb1;
+};
+
+__device__ __forceinline__ TileCoord decode_tile(const GemmKArgs& p, int tile, int BN) {
+  TileCoord t;
+  int tn = tile % p.tiles_n;
+  int r = tile / p.tiles_n;
+  int tm = r % p.tiles_m;
+  r /= p.tiles_m;
+  t.sp = r % p.splits;
+  t.b = r / p.splits;
+  t.m0 = tm * BM;
+  t.n0 = tn * BN;
+  t.kb0 = t.sp * p.kper;
+  t.kb1 = min(p.kblocks, t.kb0 + p.kper);
+  return t;
+}
+
+template <int BN, int A_MN, int B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+            const GemmKArgs p) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int STAGES = Cfg::STAGES;
+  constexpr int B_STAGE_BYTES = Cfg::B_STAGE_BYTES;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES));
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int total_tiles = p.batch * p.splits * p.tiles_m * p.tiles_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        TileCoord t = decode_tile(p, tile, BN);
+        for (int kb = t.kb0; kb < t.kb1; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status)) { ok = false; break; }
+          mbar_arrive_expect_tx(&full_bar[stage], A_STAGE_BYTES + B_STAGE_BYTES);
+          uint8_t* a_dst = sA + stage * A_STAGE_BYTES;
+          uint8_t* b_dst = sB + stage * B_STAGE_BYTES;
+          if (A_MN == 0) {
+            tma_load_3d(a_dst, &tmA, &full_bar[stage], kb * BK, t.m0, t.b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_3d(a_dst + j * 8192, &tmA, &full_bar[stage], t.m0 + 64 * j, kb * BK, t.b);
+          }
+          if (B_MN == 0) {
+            tma_load_3d(b_dst, &tmB, &full_bar[stage], kb * BK, t.n0, t.b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_3d(b_dst + j * 8192, &tmB, &full_bar[stage], t.n0 + 64 * j, kb * BK, t.b);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        // Aborting: give loads already in flight a bounded chance to land
+        // before the CTA's shared memory is released.
+        uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 2000000ull) { }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+        TileCoord t = decode_tile(p, tile, BN);
+        const int acc = it & 1;
+        const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, abort_flag, p.status)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = t.kb0; kb < t.kb1; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a_base = smem_u32(sA + stage * A_STAGE_BYTES);
+          const uint32_t b_base = smem_u32(sB + stage * B_STAGE_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t adesc = A_MN ? make_smem_desc(a_base + k * 2048, 8192, 1024)
+                                        : make_smem_desc(a_base + k * 32, 16, 1024);
+            const uint64_t bdesc = B_MN ? make_smem_desc(b_base + k * 2048, 8192, 1024)
+                                        : make_smem_desc(b_base + k * 32, 16, 1024);
+            umma_bf16(d_tmem, adesc, bdesc, idesc, (kb > t.kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);   // stage reusable once these MMAs retire
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit(&tfull_bar[acc]);
+      }
+    }
+  } else {
+    // ------------------------------ epilogue -----------------------------------
+    const int q = warp & 3;                 // TMEM lane quadrant of this warp
+    const int row_in_tile = q * 32 + lane;
+    int it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+      TileCoord t = decode_tile(p, tile, BN);
+      const int acc = it & 1;
+      const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+      if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status)) { ok = false; break; }
+      tc_fence_after_sync();
+      const uint32_t t_addr = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(q * 32) << 16);
+      const int m = t.m0 + row_in_tile;
+      const bool row_ok = m < p.M;
+      const long long out_off = (long long)t.b * p.c_batch + (long long)t.sp * p.c_split +
+                                (long long)m * p.ldc;
+      float rs = 1.f;
+      if (p.rowss != nullptr && row_ok) rs = rsqrtf(p.rowss[m] * p.inv_dim + p.eps);
+      const int ncols = min(BN, p.N - t.n0);   // valid columns in this tile
+      const int nchunks = (ncols + 31) >> 5;
+
+      float row_acc = 0.f;   // RESID_SS: sum of squares; RMSBWD: dot(acc, x)
+      if (p.epi == CCB_EPI_RMSBWD) {
+        for (int c = 0; c < nchunks; ++c) {
+          uint32_t r[32];
+          __syncwarp();
+          tmem_ld32(t_addr + c * 32, r);
+          tmem_ld_wait();
+          if (row_ok) {
+            float x[32];
+            const int n = t.n0 + c * 32;
+            load_bf16x32(reinterpret_cast<const __nv_bfloat16*>(p.R1) + (long long)m * p.ldr + n, x,
+                         p.N - n);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) row_acc += __uint_as_float(r[i]) * x[i];
+          }
+        }
+        row_acc *= rs * rs * p.inv_dim;
+      }
+
+      for (int c = 0; c < nchunks; ++c) {
+        uint32_t r[32];
+        __syncwarp();
+        tmem_ld32(t_addr + c * 32, r);
+        tmem_ld_wait();
+        if (!row_ok) continue;
+        const int n = t.n0 + c * 32;
+        const int nvalid = p.N - n;
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+
+        switch (p.epi) {
+          case CCB_EPI_STORE: {
+            if (p.Cin != nullptr) {
+              float cin[32];
+              load_bf16x32(reinterpret_cast<const __nv_bfloat16*>(p.Cin) +
+                               (long long)t.b * p.cin_batch + (long long)m * p.ldcin + n,
+                           cin, nvalid);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = p.alpha * v[i] + p.beta * cin[i];
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] *= p.alpha;
+            }
+          } break;
+          case CCB_EPI_ROWSCALE: {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] *= rs;
+          } break;
+          case CCB_EPI_ROWSCALE_SILU: {
+            float f[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              v[i] *= rs;
+              // silu of the bf16-rounded pre-activation, as the unfused path would see it
+              float u = __bfloat162float(__float2bfloat16(v[i]));
+              f[i] = u * sigmoidf_fast(u);
+            }
+            store_bf16x32(reinterpret_cast<__nv_bfloat16*>(p.C2) + out_off + n, f, nvalid);
+          } break;
+          case CCB_EPI_RESID_SS: {
+            float res[32];
+            load_bf16x32(reinterpret_cast<const __nv_bfloat16*>(p.R1) + (long long)m * p.ldr + n,
+                         res, nvalid);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              v[i] = __bfloat162float(__float2bfloat16(v[i] + res[i]));
+              if (i < nvalid) row_acc += v[i] * v[i];
+            }
+          } break;
+          case CCB_EPI_DSILU: {
+            float u[32];
+            load_bf16x32(reinterpret_cast<const __nv_bfloat16*>(p.R1) + (long long)m * p.ldr + n, u,
+                         nvalid);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              float s = sigmoidf_fast(u[i]);
+              v[i] = v[i] * (s * (1.f + u[i] * (1.f - s))) * rs;
+            }
+          } break;
+          case CCB_EPI_RMSBWD: {
+            float x[32], dres[32];
+            load_bf16x32(reinterpret_cast<const __nv_bfloat16*>(p.R1) + (long long)m * p.ldr + n, x,
+                         nvalid);
+            if (p.R2 != nullptr) {
+              load_bf16x32(reinterpret_cast<const __nv_bfloat16*>(p.R2) + (long long)m * p.ldr + n,
+                           dres, nvalid);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) dres[i] = 0.f;
+            }
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = dres[i] + v[i] - x[i] * row_acc;
+          } break;
+          default: break;
+        }
+        if (p.out_fp32)
+          store_f32x32(reinterpret_cast<float*>(p.C) + out_off + n, v, nvalid);
+        else
+          store_bf16x32(reinterpret_cast<__nv_bfloat16*>(p.C) + out_off + n, v, nvalid);
+      }
+      if (p.epi == CCB_EPI_RESID_SS && row_ok && p.ss_out != nullptr) {
+        if (p.ss_atomic) atomicAdd(p.ss_out + m, row_acc);
+        else p.ss_out[m] = row_acc;
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+    }
+  }
+
+  // ------------------------------ teardown ------------------------------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+template <int BN, int A_MN, int B_MN>
+static int launch_gemm(const CcbGemmArgs* a, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  static bool attr_set[16] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  auto kern = gemm_kernel<BN, A_MN, B_MN>;
+  if (!attr_set[dev & 15]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return set_error("cudaFuncSetAttribute(gemm): %s", cudaGetErrorString(e));
+    attr_set[dev & 15] = true;
+  }
+  CUtensorMap tmA, tmB;
+  // A
+  if (A_MN == 0) {
+    if (make_tmap_bf16_3d(&tmA, a->A, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->batch,
+                          (uint64_t)a->lda, (uint64_t)a->a_batch, BK, BM)) return -1;
+  } else {
+    if (make_tmap_bf16_3d(&tmA, a->A, (uint64_t)a->M, (uint64_t)a->K, (uint64_t)a->batch,
+                          (uint64_t)a->lda, (uint64_t)a->a_batch, 64, BK)) return -1;
+  }
+  if (B_MN == 0) {
+    if (make_tmap_bf16_3d(&tmB, a->B, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)a->batch,
+                          (uint64_t)a->ldb, (uint64_t)a->b_batch, BK, BN)) return -1;
+  } else {
+    if (make_tmap_bf16_3d(&tmB, a->B, (uint64_t)a->N, (uint64_t)a->K, (uint64_t)a->batch,
+                          (uint64_t)a->ldb, (uint64_t)a->b_batch, 64, BK)) return -1;
+  }
+  GemmKArgs p;
+  p.M = (int)a->M; p.N = (int)a->N; p.K = (int)a->K;
+  p.batch = (int)a->batch;
+  p.tiles_m = (p.M + BM - 1) / BM;
+  p.tiles_n = (p.N + BN - 1) / BN;
+  p.kblocks = (p.K + BK - 1) / BK;
+  int splits = (int)(a->splits < 1 ? 1 : a->splits);
+  if (splits > p.kblocks) splits = p.kblocks;
+  p.kper = (p.kblocks + splits - 1) / splits;
+  p.splits = (p.kblocks + p.kper - 1) / p.kper;
+  if (p.splits != (int)(a->splits < 1 ? 1 : a->splits))
+    return set_error("ccb_gemm: splits=%lld does not divide %d k-blocks evenly enough (got %d)",
+                     (long long)a->splits, p.kblocks, p.splits);
+  p.epi = (int)a->epi; p.out_fp32 = (int)a->out_fp32; p.ss_atomic = (int)a->ss_atomic;
+  p.ldc = a->ldc; p.c_batch = a->c_batch; p.c_split = a->c_split;
+  p.ldcin = a->ldcin; p.cin_batch = a->cin_batch; p.ldr = a->ldr;
+  p.C = a->C; p.C2 = a->C2; p.Cin = a->Cin; p.R1 = a->R1; p.R2 = a->R2;
+  p.rowss = a->rowss; p.ss_out = a->ss_out;
+  p.alpha = a->alpha; p.beta = a->beta; p.inv_dim = a->inv_dim; p.eps = a->eps;
+  p.status = ccb_status_ptr();
+  if (p.epi == CCB_EPI_RMSBWD && p.tiles_n != 1)
+    return set_error("ccb_gemm: RMSBWD epilogue needs N <= %d (got %d)", BN, p.N);
+  long long total = (long long)p.batch * p.splits * p.tiles_m * p.tiles_n;
+  if (total <= 0) return 0;
+  int grid = (int)(total < ccb_num_sms() ? total : ccb_num_sms());
+  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, p);
+  count_launch();
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error("gemm launch: %s", cudaGetErrorString(e));
+  return 0;
+}
+
+}  // namespace ccb
+
+extern "C" int ccb_gemm(const CcbGemmArgs* a, void* stream_) {
+  using namespace ccb;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (a->M <= 0 || a->N <= 0 || a->K <= 0 || a->batch <= 0) return 0;
+  if ((a->lda % 8) || (a->ldb % 8) || (a->ldc % 4))
+    return set_error("ccb_gemm: row strides must keep rows 16-byte aligned");
+  const int key = (int)(a->a_mn * 2 + a->b_mn);
+  // 128-wide tiles only where the problem has a single narrow N tile to fill.
+  const bool narrow = a->N <= 128 && a->epi == CCB_EPI_STORE;
+  if (narrow) {
+    switch (key) {
+      case 0: return launch_gemm<128, 0, 0>(a, stream);
+      case 1: return launch_gemm<128, 0, 1>(a, stream);
+      case 3: return launch_gemm<128, 1, 1>(a, stream);
+      default: break;
+    }
+  } else {
+    switch (key) {
+      case 0: return launch_gemm<256, 0, 0>(a, stream);
+      case 1: return launch_gemm<256, 0, 1>(a, stream);
+      case 3: return launch_gemm<256, 1, 1>(a, stream);
+      default: break;
+    }
+  }
+  return set_error("ccb_gemm: operand layout a_mn=%lld b_mn=%lld is not instantiated",
+                   (long long)a->a_mn, (long long)a->b_mn);
+}

@@ -1,0 +1,139 @@
+"""Python front-end of the tcgen05 GEMM (``csrc/gemm.cu``).
+
+``gemm(a, b)`` computes ``a @ b.T`` for K-major operands (``a`` is ``[M, K]``,
+``b`` is ``[N, K]``: the ``F.linear`` form).  ``a_mn`` / ``b_mn`` say that the
+operand is stored transposed (``[K, M]`` / ``[K, N]``), which is how the
+backward GEMMs consume activations and weights without any transpose copy:
+
+* forward      ``y  = x @ W.T``        -> ``gemm(x, W)``
+* input grad   ``dx = dy @ W``         -> ``gemm(dy, W, b_mn=True)``
+* weight grad  ``dW = dy.T @ x``       -> ``gemm(dy, x, a_mn=True, b_mn=True, splits=S)``
+
+A CPU / fp32 reference of every epilogue lives in :func:`gemm_reference` and
+is what the GPU tests compare against.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import (EPI_DSILU, EPI_RESID_SS, EPI_RMSBWD, EPI_ROWSCALE, EPI_ROWSCALE_SILU,
+                   EPI_STORE, GemmArgs)
+
+__all__ = ["gemm", "gemm_reference", "pick_splits", "EPI_STORE", "EPI_ROWSCALE",
+           "EPI_ROWSCALE_SILU", "EPI_RESID_SS", "EPI_DSILU", "EPI_RMSBWD"]
+
+
+def pick_splits(m: int, n: int, k: int, bn: int = 256) -> int:
+    """Split-K factor that fills the SMs for a weight-gradient GEMM."""
+    tiles = ((m + 127) // 128) * ((n + bn - 1) // bn)
+    kblocks = (k + 63) // 64
+    sms = _lib.lib().ccb_num_sms() if _lib.available() else 148
+    want = max(1, sms // max(tiles, 1))
+    want = min(want, kblocks)
+    # the kernel needs every split non-empty: shrink until ceil-division is exact
+    while want > 1:
+        kper = (kblocks + want - 1) // want
+        if (kblocks + kper - 1) // kper == want:
+            break
+        want -= 1
+    return want
+
+
+def _dims(a: torch.Tensor, b: torch.Tensor, a_mn: bool, b_mn: bool):
+    batch = a.shape[0] if a.dim() == 3 else 1
+    am, ak = (a.shape[-1], a.shape[-2]) if a_mn else (a.shape[-2], a.shape[-1])
+    bn, bk = (b.shape[-1], b.shape[-2]) if b_mn else (b.shape[-2], b.shape[-1])
+    if ak != bk:
+        raise ValueError(f"contraction mismatch: {tuple(a.shape)} vs {tuple(b.shape)}")
+    return batch, am, bn, ak
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+         out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
+         splits: int = 1, epi: int = EPI_STORE, alpha: float = 1.0, beta: float = 0.0,
+         cin: Optional[torch.Tensor] = None, r1: Optional[torch.Tensor] = None,
+         r2: Optional[torch.Tensor] = None, rowss: Optional[torch.Tensor] = None,
+         inv_dim: float = 0.0, eps: float = 1e-6, c2: Optional[torch.Tensor] = None,
+         ss_out: Optional[torch.Tensor] = None, ss_atomic: bool = False) -> torch.Tensor:
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
+        raise TypeError("gemm operands must be bf16")
+    if a.stride(-1) != 1 or b.stride(-1) != 1:
+        raise ValueError("gemm operands must have a contiguous last dimension")
+    batch, M, N, K = _dims(a, b, a_mn, b_mn)
+    if out is None:
+        shape = (M, N) if a.dim() == 2 else (batch, M, N)
+        if splits > 1:
+            shape = (splits, *shape)
+        out = torch.empty(shape, dtype=out_dtype, device=a.device)
+    args = GemmArgs()
+    args.A, args.B, args.C = a.data_ptr(), b.data_ptr(), out.data_ptr()
+    args.C2 = _lib.ptr(c2)
+    args.Cin = _lib.ptr(cin)
+    args.R1, args.R2 = _lib.ptr(r1), _lib.ptr(r2)
+    args.rowss, args.ss_out = _lib.ptr(rowss), _lib.ptr(ss_out)
+    args.M, args.N, args.K = M, N, K
+    args.batch, args.splits = batch, splits
+    args.lda, args.ldb = a.stride(-2), b.stride(-2)
+    args.ldc = out.stride(-2)
+    args.ldcin = cin.stride(-2) if cin is not None else 0
+    args.ldr = r1.stride(-2) if r1 is not None else 0
+    args.a_batch = a.stride(0) if a.dim() == 3 else 0
+    args.b_batch = b.stride(0) if b.dim() == 3 else 0
+    if splits > 1:
+        args.c_split = out.stride(0)
+        args.c_batch = out.stride(1) if a.dim() == 3 else 0
+    else:
+        args.c_split = 0
+        args.c_batch = out.stride(0) if a.dim() == 3 else 0
+    args.cin_batch = cin.stride(0) if (cin is not None and cin.dim() == 3) else 0
+    args.a_mn, args.b_mn = int(a_mn), int(b_mn)
+    args.epi = epi
+    args.out_fp32 = int(out.dtype == torch.float32)
+    args.ss_atomic = int(ss_atomic)
+    args.alpha, args.beta, args.inv_dim, args.eps = alpha, beta, inv_dim, eps
+    _lib.check(_lib.lib().ccb_gemm(C.byref(args), _lib.stream_ptr()), "gemm")
+    return out
+
+
+def gemm_reference(a, b, *, a_mn=False, b_mn=False, epi=EPI_STORE, alpha=1.0, beta=0.0, cin=None,
+                   r1=None, r2=None, rowss=None, inv_dim=0.0, eps=1e-6):
+    """fp32 PyTorch statement of what ``gemm`` computes (returns fp32 tensors).
+
+    Returns ``out`` or ``(out, second)`` where ``second`` is the SiLU output
+    (``EPI_ROWSCALE_SILU``) or the row sum of squares (``EPI_RESID_SS``).
+    """
+    A = a.float().transpose(-1, -2) if a_mn else a.float()
+    B = b.float().transpose(-1, -2) if b_mn else b.float()
+    acc = A @ B.transpose(-1, -2)
+    rs = None
+    if rowss is not None:
+        rs = torch.rsqrt(rowss.float() * inv_dim + eps).unsqueeze(-1)
+    if epi == EPI_STORE:
+        out = alpha * acc
+        if cin is not None:
+            out = out + beta * cin.float()
+        return out
+    if epi == EPI_ROWSCALE:
+        return acc * rs
+    if epi == EPI_ROWSCALE_SILU:
+        u = (acc * rs).bfloat16().float()
+        return u, torch.nn.functional.silu(u)
+    if epi == EPI_RESID_SS:
+        out = (acc + r1.float()).bfloat16().float()
+        return out, (out * out).sum(-1)
+    if epi == EPI_DSILU:
+        u = r1.float()
+        s = torch.sigmoid(u)
+        return acc * (s * (1 + u * (1 - s))) * rs
+    if epi == EPI_RMSBWD:
+        x = r1.float()
+        coef = (acc * x).sum(-1, keepdim=True) * rs * rs * inv_dim
+        out = acc - x * coef
+        if r2 is not None:
+            out = out + r2.float()
+        return out
+    raise ValueError(f"unknown epilogue {epi}")

@@ -1,0 +1,71 @@
+"""Fused scan kernels vs the fp32 PyTorch statement (and autograd through it)."""
+import pytest
+import torch
+
+from chaoscontrol_b200.ops import _lib
+from chaoscontrol_b200.ops import scan as S
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("B,T,D,with_h0", [(4, 64, 256, False), (3, 37, 512, True), (2, 9, 64, True)])
+def test_scan_fused_fwd_bwd(B, T, D, with_h0):
+    torch.manual_seed(0)
+    dev = "cuda"
+    P = (torch.randn(B * T, 4 * D, device=dev) * 1.5).bfloat16()
+    log_a = torch.randn(D, device=dev)
+    h0 = torch.randn(B, D, device=dev) if with_h0 else None
+    y, h, hT = S.scan_fused_fwd(P, log_a, h0, B, T, D)
+    Pr = P.float().requires_grad_(True)
+    la = log_a.clone().requires_grad_(True)
+    h0r = h0.clone().requires_grad_(True) if with_h0 else None
+    y_ref, h_ref, hT_ref = S.scan_fused_reference(Pr, la, h0r, B, T, D)
+    assert torch.allclose(y.float(), y_ref, rtol=2e-2, atol=2e-2)
+    assert torch.allclose(h.float(), h_ref, rtol=2e-2, atol=2e-2)
+    assert torch.allclose(hT, hT_ref, rtol=1e-3, atol=1e-3)
+
+    dy = (torch.randn(B * T, D, device=dev)).bfloat16()
+    dhT = torch.randn(B, D, device=dev)
+    (y_ref * dy.float()).sum().add((hT_ref * dhT).sum()).backward()
+    dP, dloga, dh0 = S.scan_fused_bwd(P, log_a, h0, h, dy, dhT, None, 0.0, 0.0, B, T, D,
+                                      want_dh0=with_h0)
+    _lib.assert_ok()
+    scale = Pr.grad.abs().max().item()
+    assert (dP.float() - Pr.grad).abs().max().item() <= 0.03 * scale + 1e-3
+    ga = la.grad
+    assert (dloga - ga).abs().max().item() <= 0.03 * ga.abs().max().item() + 1e-2
+    if with_h0:
+        assert torch.allclose(dh0, h0r.grad, rtol=2e-2, atol=2e-2)
+
+
+def test_scan_bwd_rowscale():
+    torch.manual_seed(1)
+    B, T, D = 2, 16, 256
+    P = torch.randn(B * T, 4 * D, device="cuda").bfloat16()
+    log_a = torch.zeros(D, device="cuda")
+    y, h, _ = S.scan_fused_fwd(P, log_a, None, B, T, D)
+    dy = torch.randn(B * T, D, device="cuda").bfloat16()
+    ss = torch.rand(B * T, device="cuda") * D + 1.0
+    dP0, _, _ = S.scan_fused_bwd(P, log_a, None, h, dy, None, None, 0.0, 0.0, B, T, D)
+    dP1, _, _ = S.scan_fused_bwd(P, log_a, None, h, dy, None, ss, 1.0 / D, 1e-6, B, T, D)
+    rs = torch.rsqrt(ss / D + 1e-6)[:, None]
+    assert torch.allclose(dP1.float(), dP0.float() * rs, rtol=2e-2, atol=1e-3)
+
+
+def test_ssm_scan_public_op():
+    torch.manual_seed(2)
+    B, T, D = 3, 50, 96
+    decay = torch.rand(B, T, D, device="cuda").requires_grad_(True)
+    update = torch.randn(B, T, D, device="cuda").requires_grad_(True)
+    out = S.ssm_scan(decay, update)
+    ref = S.diag_recurrence_reference(decay, update)
+    assert torch.allclose(out, ref, rtol=1e-5, atol=1e-5)
+    g = torch.randn_like(out)
+    gd, gu = torch.autograd.grad(out, (decay, update), g)
+    rd, ru = torch.autograd.grad(ref, (decay, update), g)
+    assert torch.allclose(gd, rd, rtol=1e-4, atol=1e-4)
+    assert torch.allclose(gu, ru, rtol=1e-4, atol=1e-4)
+    # t=0 decay gradient is exactly zero with a zero initial state
+    assert torch.count_nonzero(gd[:, 0]) == 0
+    with pytest.raises(ValueError):
+        S.ssm_scan(decay.transpose(0, 1), update.transpose(0, 1))

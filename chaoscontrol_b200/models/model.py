@@ -1,0 +1,561 @@
+"""``CareStudentLM``: embedding -> N x (RMSNorm, diagonal-SSM core, residual,
+RMSNorm, SiLU feed-forward, residual) -> final RMSNorm -> LM head.
+
+Public surface and state-dict keys match the reference
+(src/chaoscontrol/model.py:27-140 for the block, model.py:573-2035 for the LM),
+so ``CareStudentLM(**cfg).load_state_dict(ckpt["model"], strict=True)`` works
+on reference checkpoints.  On a CUDA device with bf16 parameters the bare-SSM
+configuration runs the hand-scheduled kernel trunk (:mod:`..ops.trunk`) behind
+one autograd node; every other configuration (CPU, fp32, research add-ons)
+runs the plain PyTorch statement of the same math, which is also the oracle
+the kernels are tested against.
+"""
+from __future__ import annotations
+
+from typing import Any, Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+from torch.utils.checkpoint import checkpoint as _checkpoint
+
+from ..ops import trunk as T
+from .core import CareSSMCore, FeedForward, RMSNorm
+
+__all__ = ["CareSSMBlock", "CareStudentLM", "RMSNorm", "FeedForward", "CareSSMCore"]
+
+
+class CareSSMBlock(nn.Module):
+    """input_norm -> core -> residual -> ff_norm -> FeedForward -> residual."""
+
+    def __init__(self, dim: int, ff_mult: int = 2, *, a_mode: str = "diag", a_full_rank: int = 8,
+                 a_full_gamma: float = 0.05, ssm_delta_rank: int = 0, rich_b_mode: str = "none",
+                 rich_b_bottleneck: int = 32, rich_b_num_subnets: int = 4,
+                 rich_b_settling_steps: int = 2) -> None:
+        super().__init__()
+        self.input_norm = RMSNorm(dim)
+        self.ff_norm = RMSNorm(dim)
+        self.ff = FeedForward(dim, ff_mult)
+        self.core = CareSSMCore(dim, a_mode=a_mode, a_full_rank=a_full_rank,
+                                a_full_gamma=a_full_gamma, delta_rank=ssm_delta_rank)
+        if rich_b_mode == "none":
+            self.rich_b: Optional[nn.Module] = None
+        elif rich_b_mode == "nn":
+            from .routing import RichBNN
+            self.rich_b = RichBNN(dim, bottleneck=rich_b_bottleneck)
+        elif rich_b_mode in ("hub", "assembly", "hybrid"):
+            from .routing import DistributedB
+            self.rich_b = DistributedB(dim, num_subnets=rich_b_num_subnets,
+                                       bottleneck=rich_b_bottleneck, topology=rich_b_mode,
+                                       settling_steps=rich_b_settling_steps)
+        else:
+            raise ValueError(f"unsupported rich_b_mode: {rich_b_mode}")
+
+    def step(self, x: torch.Tensor, state: torch.Tensor):
+        y, new_state = self.core.step(self.input_norm(x), state, rich_b=self.rich_b)
+        x = x + y
+        x = x + self.ff(self.ff_norm(x))
+        return x, new_state
+
+    def forward(self, x: torch.Tensor, *, return_jacobian_stats: bool = False,
+                initial_state: Optional[torch.Tensor] = None, return_final_state: bool = False):
+        result = self.core(self.input_norm(x), rich_b=self.rich_b,
+                           return_jacobian_stats=return_jacobian_stats,
+                           initial_state=initial_state, return_final_state=return_final_state)
+        stats = final_state = None
+        if return_jacobian_stats and return_final_state:
+            y, stats, final_state = result
+        elif return_jacobian_stats:
+            y, stats = result
+        elif return_final_state:
+            y, final_state = result
+        else:
+            y = result
+        x = x + y
+        x = x + self.ff(self.ff_norm(x))
+        if return_jacobian_stats and return_final_state:
+            return x, stats, final_state
+        if return_jacobian_stats:
+            return x, stats
+        if return_final_state:
+            return x, final_state
+        return x
+
+
+# ---------------------------------------------------------------------------
+# kernel trunk behind one autograd node
+# ---------------------------------------------------------------------------
+_PER_LAYER = 10  # select, in, gate, delta, out, fc, proj, input_norm, ff_norm, log_a
+
+
+def _layer_weights(params: tuple, i: int) -> T.LayerWeights:
+    sel, inp, gate, delta, out, fc, proj, wn1, wn2, log_a = params[i * _PER_LAYER:(i + 1) * _PER_LAYER]
+    # The four [D, D] projections are consumed as one packed [4D, D] weight.
+    base = sel.data_ptr()
+    step = sel.numel() * sel.element_size()
+    packed = (inp.data_ptr() == base + step and gate.data_ptr() == base + 2 * step and
+              delta.data_ptr() == base + 3 * step and sel.is_contiguous())
+    if packed:
+        Wp = torch.as_strided(sel, (4 * sel.shape[0], sel.shape[1]), (sel.shape[1], 1))
+    else:
+        Wp = torch.cat((sel, inp, gate, delta), dim=0)
+    return T.LayerWeights(Wp=Wp, Wo=out, Wfc=fc, Wproj=proj, wn1=wn1, wn2=wn2, log_a=log_a).prepare()
+
+
+class _TrunkFn(torch.autograd.Function):
+    """tokens -> (hidden, final row sums of squares, final states) through the
+    kernel trunk; backward replays the layers in reverse with saved activations."""
+
+    @staticmethod
+    def forward(ctx, tokens, h0_stack, want_grad, embed_w, *params):
+        B, Tn = tokens.shape
+        L = len(params) // _PER_LAYER
+        x, ss = T.embed_fwd(tokens, embed_w)
+        ws, ctxs, hTs = [], [], []
+        for i in range(L):
+            w = _layer_weights(params, i)
+            h0 = h0_stack[i].float().contiguous() if h0_stack is not None else None
+            x, ss, hT, c = T.layer_forward(x, ss, w, B, Tn, h0, save=want_grad)
+            ws.append(w)
+            ctxs.append(c)
+            hTs.append(hT)
+        ctx.ws, ctxs_, ctx.tokens = ws, ctxs, tokens
+        ctx.ctxs = ctxs_
+        ctx.shape = (B, Tn, embed_w.shape[0])
+        ctx.has_h0 = h0_stack is not None
+        ctx.mark_non_differentiable(ss)
+        return x.view(B, Tn, -1), ss, torch.stack(hTs, dim=0)
+
+    @staticmethod
+    def backward(ctx, dhidden, _dss, dhT_stack):
+        B, Tn, V = ctx.shape
+        dx = dhidden.reshape(B * Tn, -1).contiguous()
+        grads: list = []
+        L = len(ctx.ws)
+        dh0s = []
+        use_dhT = dhT_stack is not None and bool(dhT_stack.abs().sum() != 0) if dhT_stack is not None else False
+        for i in reversed(range(L)):
+            w, c = ctx.ws[i], ctx.ctxs[i]
+            dhT = dhT_stack[i].float().contiguous() if use_dhT else None
+            dx, g = T.layer_backward(dx, c, w, B, Tn, dhT, want_dh0=ctx.has_h0)
+            D = w.Wo.shape[0]
+            pd = w.Wo.dtype
+            dsel, dinp, dgate, ddelta = (t.to(pd) for t in g.dWp.split(D, dim=0))
+            grads = [dsel, dinp, dgate, ddelta, g.dWo.to(pd), g.dWfc.to(pd), g.dWproj.to(pd),
+                     g.dwn1.to(w.wn1.dtype), g.dwn2.to(w.wn2.dtype),
+                     g.dlog_a.to(w.log_a.dtype)] + grads
+            dh0s.append(g.dh0)
+            ctx.ctxs[i] = None
+        dE = T.embed_bwd(ctx.tokens, dx, V).to(ctx.ws[0].Wo.dtype)
+        dh0 = torch.stack(list(reversed(dh0s)), 0) if ctx.has_h0 else None
+        return (None, dh0, None, dE, *grads)
+
+
+class CareStudentLM(nn.Module):
+    """Diagonal-SSM language model.  See the module docstring for the layout."""
+
+    def __init__(self, *, vocab_size: int, dim: int, num_layers: int, ff_mult: int = 2,
+                 block_type: str = "ssm", attention_num_heads: int = 8,
+                 attention_dropout: float = 0.0, a_mode: str = "diag", a_full_rank: int = 8,
+                 a_full_gamma: float = 0.05, ssm_delta_rank: int = 0, rich_b_mode: str = "none",
+                 rich_b_bottleneck: int = 32, rich_b_num_subnets: int = 4,
+                 rich_b_settling_steps: int = 2, outer_model_dim: int = 0,
+                 consolidation_mode: str = "symmetric", consolidation_ema_decay: float = 0.99,
+                 consolidation_trigger: str = "immediate", consolidation_window: int = 8,
+                 outer_model_type: str = "single", outer_max_slots: int = 64,
+                 outer_compress_ratio: int = 2, wernicke_enabled: bool = False,
+                 wernicke_k_max: int = 16, wernicke_window: int = 8, wernicke_router: str = "vq",
+                 wernicke_balance_weight: float = 0.01, wernicke_expert_dim: int = 0,
+                 wernicke_layers: int = 1, wernicke_k_max_fine: int = 16,
+                 buffer_mode: str = "legacy", retrieval_mode: str = "softmax_all",
+                 retrieval_k: int = 8, bucket_prototypes: bool = False, prototype_dim: int = 64,
+                 prototype_update_rate: float = 0.1, semantic_tier_bases: int = 0,
+                 semantic_tier_update_rate: float = 0.01, typed_storage: bool = False,
+                 typed_consolidation: bool = False, compression_consequence: bool = False,
+                 cue_projection: bool = True, dynamic_crit_per_layer: bool = False,
+                 compression_selection: str = "survival", posterior_mode: str = "none",
+                 posterior_lr: float = 0.01, residual_cache_k: int = 4, local_attn_window: int = 0,
+                 local_attn_heads: int = 1, local_attn_dim: int = 64, local_attn_topk: int = 0,
+                 local_attn_topk_random: bool = False,
+                 depth_recurrence_shared_layers: Optional[list[int]] = None,
+                 depth_recurrence_count: int = 1, activation_checkpoint: bool = False,
+                 tie_embeddings: bool = False, log_a_init: str = "zeros") -> None:
+        super().__init__()
+        self.vocab_size = vocab_size
+        self.dim = dim
+        self.activation_checkpoint = bool(activation_checkpoint)
+        self.local_attn_window = local_attn_window
+        self.embed = nn.Embedding(vocab_size, dim)
+        self.buffer_mode = buffer_mode
+        self.retrieval_mode = retrieval_mode
+        self.retrieval_k = retrieval_k
+        self.block_type = block_type
+        self.wernicke_balance_weight = wernicke_balance_weight
+
+        self.wernicke: Optional[nn.Module] = None
+        if wernicke_enabled:
+            from .wernicke import HierarchicalWernicke, WernickeLayer
+            expert = wernicke_expert_dim if wernicke_expert_dim > 0 else None
+            if wernicke_layers >= 2:
+                self.wernicke = HierarchicalWernicke(
+                    dim=dim, k_coarse=wernicke_k_max, k_fine=wernicke_k_max_fine,
+                    window=wernicke_window, router_type=wernicke_router,
+                    balance_weight=wernicke_balance_weight, expert_dim=expert)
+            else:
+                self.wernicke = WernickeLayer(
+                    dim, k_max=wernicke_k_max, window=wernicke_window, router_type=wernicke_router,
+                    balance_weight=wernicke_balance_weight, expert_dim=expert)
+
+        if block_type == "attention":
+            from .attention import AttentionControlBlock
+            self.layers = nn.ModuleList([
+                AttentionControlBlock(dim, ff_mult, num_heads=attention_num_heads,
+                                      attn_dropout=attention_dropout)
+                for _ in range(num_layers)])
+        elif block_type == "ssm":
+            kw = dict(a_mode=a_mode, a_full_rank=a_full_rank, a_full_gamma=a_full_gamma,
+                      ssm_delta_rank=ssm_delta_rank, rich_b_mode=rich_b_mode,
+                      rich_b_bottleneck=rich_b_bottleneck, rich_b_num_subnets=rich_b_num_subnets,
+                      rich_b_settling_steps=rich_b_settling_steps)
+            if local_attn_window > 0:
+                from .attention import CareSSMHybridBlock
+                blocks: list[nn.Module] = [CareSSMBlock(dim, ff_mult, **kw)
+                                           for _ in range(num_layers - 1)]
+                blocks.append(CareSSMHybridBlock(
+                    dim, ff_mult, a_mode=a_mode, a_full_rank=a_full_rank, a_full_gamma=a_full_gamma,
+                    ssm_delta_rank=ssm_delta_rank, local_attn_window=local_attn_window,
+                    local_attn_heads=local_attn_heads, local_attn_dim=local_attn_dim,
+                    local_attn_topk=local_attn_topk, local_attn_topk_random=local_attn_topk_random))
+                self.layers = nn.ModuleList(blocks)
+            else:
+                self.layers = nn.ModuleList([CareSSMBlock(dim, ff_mult, **kw)
+                                             for _ in range(num_layers)])
+        else:
+            raise ValueError(
+                f"unsupported block_type: {block_type!r} (expected 'ssm' or 'attention')")
+
+        shared = list(depth_recurrence_shared_layers or [])
+        self.depth_recurrence_shared_layers: list[int] = shared
+        self.depth_recurrence_count = int(depth_recurrence_count)
+        if self.depth_recurrence_count < 1:
+            raise ValueError(f"depth_recurrence_count must be >= 1, got {self.depth_recurrence_count}")
+        if shared:
+            if any(not (0 <= i < len(self.layers)) for i in shared):
+                raise ValueError(f"depth_recurrence_shared_layers indices out of range "
+                                 f"[0, {len(self.layers)}): {shared}")
+            if sorted(shared) != shared:
+                raise ValueError(f"depth_recurrence_shared_layers must be sorted ascending: {shared}")
+            if any(shared[i] + 1 != shared[i + 1] for i in range(len(shared) - 1)):
+                raise ValueError(f"depth_recurrence_shared_layers must be contiguous: {shared}")
+            a, b = shared[0], shared[-1]
+            self._virtual_layer_indices = (list(range(0, a)) + shared * self.depth_recurrence_count +
+                                           list(range(b + 1, len(self.layers))))
+        else:
+            self._virtual_layer_indices = list(range(len(self.layers)))
+
+        self.final_norm = RMSNorm(dim)
+        self.lm_head = nn.Linear(dim, vocab_size, bias=False)
+        self.tie_embeddings = bool(tie_embeddings)
+        if self.tie_embeddings:
+            self.lm_head.weight = self.embed.weight
+        if log_a_init == "log_uniform":
+            # option asked for by some configs: diag A spread uniformly in log space over [-4, 0]
+            for blk in self.layers:
+                core = getattr(blk, "core", None)
+                if core is not None and hasattr(core, "log_a"):
+                    with torch.no_grad():
+                        core.log_a.uniform_(-4.0, 0.0)
+        elif log_a_init != "zeros":
+            raise ValueError(f"log_a_init must be 'zeros' or 'log_uniform', got {log_a_init!r}")
+
+        self.outer_model_type = outer_model_type
+        self.outer_model: Optional[nn.Module] = None
+        if outer_model_dim > 0:
+            from .memory import MultiSlotOuterModel, OuterModel
+            common = dict(consolidation_mode=consolidation_mode, ema_decay=consolidation_ema_decay,
+                          trigger=consolidation_trigger, trigger_window=consolidation_window)
+            if outer_model_type == "multislot":
+                self.outer_model = MultiSlotOuterModel(
+                    dim, outer_dim=outer_model_dim, max_slots=outer_max_slots,
+                    compress_ratio=outer_compress_ratio,
+                    compression_selection=compression_selection, **common)
+            else:
+                self.outer_model = OuterModel(dim, outer_dim=outer_model_dim, **common)
+        self.semantic_tier: Optional[nn.Module] = None
+        if semantic_tier_bases > 0:
+            from .memory import SemanticTier
+            self.semantic_tier = SemanticTier(dim, num_bases=semantic_tier_bases,
+                                              update_rate=semantic_tier_update_rate)
+        self.bucket_prototypes_module: Optional[nn.Module] = None
+        if bucket_prototypes and outer_model_dim > 0:
+            from .memory import BucketPrototypes
+            total_k = wernicke_k_max * wernicke_k_max_fine if wernicke_layers >= 2 else wernicke_k_max
+            self.bucket_prototypes_module = BucketPrototypes(
+                k_max=total_k, prototype_dim=prototype_dim, model_dim=dim,
+                update_rate=prototype_update_rate)
+        self.posterior: Optional[nn.Module] = None
+        self.posterior_mode = posterior_mode
+        if posterior_mode != "none":
+            from .posterior import BucketDelta, GlobalDelta, ResidualCache
+            total_buckets = (self.wernicke.total_buckets if hasattr(self.wernicke, "total_buckets")
+                             else (self.wernicke.k_max if self.wernicke is not None else wernicke_k_max))
+            if posterior_mode == "global_delta":
+                self.posterior = GlobalDelta(dim, lr=posterior_lr)
+            elif posterior_mode == "bucket_delta":
+                self.posterior = BucketDelta(k_max=total_buckets, model_dim=dim, lr=posterior_lr)
+            elif posterior_mode == "residual_cache":
+                self.posterior = ResidualCache(model_dim=dim, k=residual_cache_k)
+        self.typed_storage = typed_storage
+        self.typed_consolidation = typed_consolidation
+        self.compression_consequence = compression_consequence
+        self.cue_projection = cue_projection
+        self.dynamic_crit_per_layer = dynamic_crit_per_layer
+
+    # -- state -----------------------------------------------------------
+    def init_state(self, batch_size: int) -> list[torch.Tensor]:
+        w = self.embed.weight
+        return [torch.zeros(batch_size, self.dim, device=w.device, dtype=w.dtype)
+                for _ in range(len(self.layers))]
+
+    def init_kv_caches(self):
+        return [layer._init_kv_cache() if hasattr(layer, "_init_kv_cache") else None
+                for layer in self.layers]
+
+    def artifact_bytes(self) -> int:
+        return sum(p.numel() for p in self.parameters()) * 2
+
+    # -- fast-path gate --------------------------------------------------
+    def _is_bare_ssm(self) -> bool:
+        return (self.block_type == "ssm" and self.wernicke is None and self.outer_model is None and
+                self.semantic_tier is None and self.posterior is None and
+                self.local_attn_window == 0 and
+                all(isinstance(b, CareSSMBlock) and b.rich_b is None and b.core.a_mode == "diag" and
+                    b.core.delta_rank == 0 for b in self.layers))
+
+    def kernel_trunk_supported(self) -> bool:
+        """True when ``encode`` runs the hand-scheduled sm_100a trunk."""
+        w = self.embed.weight
+        if not (w.is_cuda and w.dtype == torch.bfloat16 and self._is_bare_ssm()):
+            return False
+        if self._virtual_layer_indices != list(range(len(self.layers))):
+            return False
+        if self.dim % 64 != 0 or self.dim > 256:
+            return False
+        if any(p.dtype != torch.bfloat16 for p in self.parameters()):
+            return False
+        # training hooks (ScOpt / TTT instrumentation) need the module-by-module path
+        for blk in self.layers:
+            for m in (blk.core.in_proj, blk.core.select_proj, blk.core.gate_proj, blk.core.delta_proj,
+                      blk.core.out_proj, blk.ff.fc, blk.ff.proj):
+                if m._forward_hooks or m._forward_pre_hooks or m._backward_hooks:
+                    return False
+            if blk.core._capture_states_enabled:
+                return False
+        return True
+
+    def _trunk_params(self) -> list[torch.Tensor]:
+        ps: list[torch.Tensor] = []
+        for blk in self.layers:
+            c = blk.core
+            ps += [c.select_proj.weight, c.in_proj.weight, c.gate_proj.weight, c.delta_proj.weight,
+                   c.out_proj.weight, blk.ff.fc.weight, blk.ff.proj.weight, blk.input_norm.weight,
+                   blk.ff_norm.weight, c.log_a]
+        return ps
+
+    def encode_with_stats(self, input_ids: torch.Tensor, *,
+                          initial_states: Optional[list[torch.Tensor]] = None):
+        """Kernel trunk only: ``(hidden, row_ss, final_states)`` where ``row_ss``
+        is the per-token sum of squares of ``hidden`` that the fused LM head
+        turns into the final RMSNorm scale without re-reading ``hidden``."""
+        h0 = None
+        if initial_states is not None:
+            h0 = torch.stack([s.float() for s in initial_states], 0)
+        want_grad = torch.is_grad_enabled() and any(p.requires_grad for p in self.parameters())
+        hidden, ss, hT = _TrunkFn.apply(input_ids, h0, want_grad, self.embed.weight,
+                                        *self._trunk_params())
+        return hidden, ss, [hT[i] for i in range(hT.shape[0])]
+
+    # -- encoder ---------------------------------------------------------
+    def encode(self, input_ids: torch.Tensor, *, memory_mode: str = "packet",
+               cache_read_cutoff: Optional[int] = None,
+               episodic_residual: Optional[torch.Tensor] = None,
+               episodic_gate: Optional[torch.Tensor] = None,
+               memory_slot_mask: Optional[torch.Tensor] = None,
+               memory_slot_override_index: Optional[int] = None,
+               memory_slot_override_values: Optional[torch.Tensor] = None,
+               return_memory_meta: bool = False,
+               initial_states: Optional[list[torch.Tensor]] = None,
+               return_final_states: bool = False):
+        """Everything before the LM head; returns ``hidden`` ``(batch, seq, dim)``
+        (and the per-layer final states when asked)."""
+        if memory_mode not in {"off", "force_on", "packet"}:
+            raise ValueError("memory_mode must be one of 'off', 'force_on', or 'packet', "
+                             f"got {memory_mode!r}")
+        if memory_mode != "packet" and (episodic_residual is not None or episodic_gate is not None):
+            raise ValueError("episodic_residual/episodic_gate are only valid with memory_mode='packet'")
+        if memory_mode == "packet" and ((episodic_residual is None) != (episodic_gate is None)):
+            raise ValueError("memory_mode='packet' requires both episodic_residual and "
+                             "episodic_gate, or neither for a zero-residual no-op")
+        if initial_states is not None and len(initial_states) != len(self.layers):
+            raise ValueError(f"initial_states length {len(initial_states)} does not match "
+                             f"num_layers {len(self.layers)}")
+
+        plain = episodic_residual is None and not return_memory_meta
+        if plain and self.kernel_trunk_supported() and not self.activation_checkpoint:
+            hidden, _ss, finals = self.encode_with_stats(input_ids, initial_states=initial_states)
+            return (hidden, finals) if return_final_states else hidden
+
+        x = self.embed(input_ids)
+        meta: dict[str, Any] = {}
+        if self.wernicke is not None:
+            x, bucket_ids, balance = self.wernicke(x)
+            meta.update(bucket_ids=bucket_ids, balance_loss=balance)
+        if memory_mode != "off":
+            x = self._memory_read(x, memory_mode, episodic_residual, episodic_gate, meta,
+                                  memory_slot_mask=memory_slot_mask,
+                                  cache_read_cutoff=cache_read_cutoff,
+                                  override_index=memory_slot_override_index,
+                                  override_values=memory_slot_override_values)
+        x, finals, _ = self._run_layers(x, initial_states, want_stats=False)
+        if self.posterior is not None:
+            x = self._posterior_read(x, meta.get("bucket_ids"))
+        if return_memory_meta:
+            out: dict[str, Any] = {"hidden": x, "memory_meta": meta}
+            if return_final_states:
+                out["final_states"] = finals
+            return out
+        return (x, finals) if return_final_states else x
+
+    def _run_layers(self, x, initial_states, want_stats: bool):
+        finals: list[Optional[torch.Tensor]] = [None] * len(self.layers)
+        cur = list(initial_states) if initial_states is not None else [None] * len(self.layers)
+        all_stats = []
+        for idx in self._virtual_layer_indices:
+            layer = self.layers[idx]
+            kw = dict(initial_state=cur[idx], return_final_state=True)
+            if want_stats:
+                kw["return_jacobian_stats"] = True
+            if self.activation_checkpoint and self.training and torch.is_grad_enabled():
+                res = _checkpoint(lambda t, _l=layer, _kw=kw: _l(t, **_kw), x, use_reentrant=False)
+            else:
+                res = layer(x, **kw)
+            if want_stats:
+                x, stats, fs = res
+                all_stats.append(stats)
+            else:
+                x, fs = res
+            finals[idx] = fs
+            cur[idx] = fs
+        return x, finals, all_stats
+
+    def _memory_read(self, x, memory_mode, residual, gate, meta, **_kw):
+        if memory_mode == "packet":
+            if residual is None:
+                return x
+            g = gate
+            while g.dim() < residual.dim():
+                g = g.unsqueeze(-1)
+            return x + g.to(x.dtype) * residual.to(x.dtype)
+        if self.outer_model is not None:
+            bias = self.outer_model.read(x.size(0)) if hasattr(self.outer_model, "read") else None
+            if bias is not None:
+                x = x + bias.to(x.dtype).unsqueeze(1)
+        if self.semantic_tier is not None:
+            x = x + self.semantic_tier.read(x.size(0)).to(x.dtype).unsqueeze(1)
+        return x
+
+    def _posterior_read(self, x, bucket_ids):
+        from .posterior import BucketDelta, GlobalDelta, ResidualCache
+        if isinstance(self.posterior, GlobalDelta):
+            return x + self.posterior.read(x.size(0)).unsqueeze(1)
+        if isinstance(self.posterior, BucketDelta) and bucket_ids is not None:
+            per = bucket_ids.mode(dim=1).values
+            bias = torch.cat([self.posterior.read(bucket_id=int(per[i].item()), batch_size=1)
+                              for i in range(x.size(0))], dim=0)
+            return x + bias.unsqueeze(1)
+        if isinstance(self.posterior, ResidualCache):
+            return x + self.posterior.read(x.detach().mean(dim=1)).unsqueeze(1)
+        return x
+
+    # -- full forward ----------------------------------------------------
+    def forward(self, input_ids: torch.Tensor, *, return_jacobian_stats: bool = False,
+                memory_write_mode: str = "none",
+                initial_states: Optional[list[torch.Tensor]] = None) -> dict[str, Any]:
+        """Returns ``{"logits", "hidden", "final_states"[, "balance_loss", "bucket_ids",
+        "jacobian_stats"]}``."""
+        if initial_states is not None and len(initial_states) != len(self.layers):
+            raise ValueError(f"initial_states length {len(initial_states)} does not match "
+                             f"num_layers {len(self.layers)}")
+        out: dict[str, Any] = {}
+        if (not return_jacobian_stats and memory_write_mode == "none" and
+                self.kernel_trunk_supported() and not self.activation_checkpoint):
+            hidden, _ss, finals = self.encode_with_stats(input_ids, initial_states=initial_states)
+        else:
+            x = self.embed(input_ids)
+            meta: dict[str, Any] = {}
+            if self.wernicke is not None:
+                x, bucket_ids, balance = self.wernicke(x)
+                out["balance_loss"] = balance
+                out["bucket_ids"] = bucket_ids
+                meta["bucket_ids"] = bucket_ids
+            x = self._memory_read(x, "force_on", None, None, meta)
+            x, finals, all_stats = self._run_layers(x, initial_states, want_stats=return_jacobian_stats)
+            if self.posterior is not None:
+                x = self._posterior_read(x, meta.get("bucket_ids"))
+            hidden = x
+            if return_jacobian_stats and all_stats:
+                out["jacobian_stats"] = {k: torch.stack([s[k] for s in all_stats]).mean()
+                                         for k in all_stats[0]}
+                if self.dynamic_crit_per_layer:
+                    out["per_layer_jacobian_stats"] = all_stats
+        out["hidden"] = hidden
+        out["logits"] = self.lm_head(self.final_norm(hidden))
+        out["final_states"] = finals
+        if (memory_write_mode == "append_only" and self.buffer_mode == "append_only" and
+                self.outer_model is not None and hasattr(self.outer_model, "append_kv_batch")):
+            self.append_memory_from_hidden(hidden, bucket_ids=out.get("bucket_ids"))
+        return out
+
+    def append_memory_from_hidden(self, hidden: torch.Tensor, *, bucket_ids=None, **kw):
+        """Append per-token key/value pairs of ``hidden`` to the multi-slot store."""
+        if self.outer_model is None or not hasattr(self.outer_model, "append_kv_batch"):
+            return []
+        flat = hidden.detach().reshape(-1, hidden.shape[-1])
+        bids = bucket_ids.detach().reshape(-1) if bucket_ids is not None else None
+        return self.outer_model.append_kv_batch(flat, bucket_ids=bids, **kw)
+
+    # -- single token ----------------------------------------------------
+    def step(self, token_ids: torch.Tensor, states: list[torch.Tensor], kv_caches=None):
+        """One token through the recurrence only: ``(logits, hidden, new_states)``."""
+        if self.depth_recurrence_count > 1:
+            raise NotImplementedError(
+                "CareStudentLM.step() does not implement depth recurrence; use forward() for "
+                f"depth_recurrence_count={self.depth_recurrence_count}")
+        x = self.embed(token_ids).squeeze(1)
+        if kv_caches is None:
+            kv_caches = [None] * len(self.layers)
+        new_states = []
+        for i, layer in enumerate(self.layers):
+            if hasattr(layer, "_init_kv_cache"):
+                if kv_caches[i] is None:
+                    raise RuntimeError(f"Layer {i} is a hybrid block but no KV cache provided. "
+                                       "Call init_kv_caches() and pass the result to step().")
+                x, s = layer.step(x, states[i], kv_cache=kv_caches[i])
+            else:
+                x, s = layer.step(x, states[i])
+            new_states.append(s)
+        hidden = x
+        logits = self.lm_head(self.final_norm(x.unsqueeze(1)).squeeze(1))
+        return logits, hidden, new_states
+
+    def dream_step(self, token_ids: torch.Tensor, states: list[torch.Tensor], *,
+                   temperature: float = 1.0, generator: Optional[torch.Generator] = None):
+        """Sample the next token from the model's own distribution and advance:
+        ``(next_token (batch, 1), logits, hidden, new_states)``."""
+        logits, hidden, new_states = self.step(token_ids, states)
+        if temperature <= 0:
+            nxt = logits.argmax(dim=-1, keepdim=True)
+        else:
+            probs = F.softmax(logits.float() / temperature, dim=-1)
+            nxt = torch.multinomial(probs, 1, generator=generator)
+        return nxt, logits, hidden, new_states

@@ -59,6 +59,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
          r2: Optional[torch.Tensor] = None, rowss: Optional[torch.Tensor] = None,
          inv_dim: float = 0.0, eps: float = 1e-6, c2: Optional[torch.Tensor] = None,
          ss_out: Optional[torch.Tensor] = None, ss_atomic: bool = False) -> torch.Tensor:
+    if not a.is_cuda:
+        return _gemm_cpu(a, b, a_mn=a_mn, b_mn=b_mn, out=out, out_dtype=out_dtype, splits=splits,
+                         epi=epi, alpha=alpha, beta=beta, cin=cin, r1=r1, r2=r2, rowss=rowss,
+                         inv_dim=inv_dim, eps=eps, c2=c2, ss_out=ss_out, ss_atomic=ss_atomic)
     if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
         raise TypeError("gemm operands must be bf16")
     if a.stride(-1) != 1 or b.stride(-1) != 1:
@@ -99,6 +103,40 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     return out
 
 
+def _gemm_cpu(a, b, *, a_mn, b_mn, out, out_dtype, splits, epi, alpha, beta, cin, r1, r2, rowss,
+              inv_dim, eps, c2, ss_out, ss_atomic):
+    """CPU stand-in with the kernel's exact call contract (any float dtype).
+
+    Used by the CPU tests to check the hand-written backward algebra built on
+    these epilogues, and by the CPU training path.  Split-K returns the full
+    product in split 0 and zeros elsewhere so reducing over splits is exact.
+    """
+    res = gemm_reference(a, b, a_mn=a_mn, b_mn=b_mn, epi=epi, alpha=alpha, beta=beta, cin=cin,
+                         r1=r1, r2=r2, rowss=rowss, inv_dim=inv_dim, eps=eps)
+    second = None
+    if isinstance(res, tuple):
+        res, second = res
+    dt = out.dtype if out is not None else (a.dtype if out_dtype == torch.bfloat16 and
+                                            a.dtype != torch.bfloat16 else out_dtype)
+    if splits > 1:
+        full = torch.zeros((splits, *res.shape), dtype=dt)
+        full[0] = res.to(dt)
+        res = full
+    if out is not None:
+        out.copy_(res.to(out.dtype))
+    else:
+        out = res.to(dt)
+    if epi == EPI_ROWSCALE_SILU and c2 is not None:
+        c2.copy_(second.to(c2.dtype))
+    if epi == EPI_RESID_SS and ss_out is not None:
+        ss = (out.float() ** 2).sum(-1)
+        if ss_atomic:
+            ss_out.add_(ss)
+        else:
+            ss_out.copy_(ss)
+    return out
+
+
 def gemm_reference(a, b, *, a_mn=False, b_mn=False, epi=EPI_STORE, alpha=1.0, beta=0.0, cin=None,
                    r1=None, r2=None, rowss=None, inv_dim=0.0, eps=1e-6):
     """fp32 PyTorch statement of what ``gemm`` computes (returns fp32 tensors).
@@ -119,11 +157,16 @@ def gemm_reference(a, b, *, a_mn=False, b_mn=False, epi=EPI_STORE, alpha=1.0, be
         return out
     if epi == EPI_ROWSCALE:
         return acc * rs
+    lowp = a.dtype == torch.bfloat16
     if epi == EPI_ROWSCALE_SILU:
-        u = (acc * rs).bfloat16().float()
+        u = acc * rs
+        if lowp:
+            u = u.bfloat16().float()
         return u, torch.nn.functional.silu(u)
     if epi == EPI_RESID_SS:
-        out = (acc + r1.float()).bfloat16().float()
+        out = acc + r1.float()
+        if lowp:
+            out = out.bfloat16().float()
         return out, (out * out).sum(-1)
     if epi == EPI_DSILU:
         u = r1.float()

@@ -30,7 +30,7 @@ def test_gemm_tn(M, N, K):
     _close(out, G.gemm_reference(a, b), atol=0.05 * (K ** 0.5) / 16)
 
 
-@pytest.mark.parametrize("M,N,K", [(256, 256, 256), (512, 300, 128), (128, 1024, 192)])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 256), (512, 304, 128), (128, 1024, 192)])
 def test_gemm_b_mn(M, N, K):
     torch.manual_seed(1)
     a, b = _rand(M, K), _rand(K, N)

@@ -243,7 +243,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       TileCoord t = decode_tile(p, tile, BN);
       const int acc = it & 1;
       const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
-      if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status)) { ok = false; break; }
+      {
+        // warp-uniform result: the TMEM loads below are warp-collective
+        const bool w = mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status);
+        if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
+      }
       tc_fence_after_sync();
       const uint32_t t_addr = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(q * 32) << 16);
       const int m = t.m0 + row_in_tile;

@@ -1,0 +1,645 @@
+// Fused LM head for sm_100a: logits GEMM + log-softmax + cross-entropy, with
+// the logits recomputed in backward and never written to memory.
+//
+//   logits[r, v] = rs[r] * sum_d X[r, d] * W'[v, d]
+//     X   final hidden state (bf16, [R, 256]), rs = rsqrt(rowss/D + eps): the
+//         final RMSNorm, whose weight is folded into W' = W_lm * w_norm.
+//
+// Three launch modes share one pipeline (TMA ring -> tcgen05.mma -> TMEM ->
+// tcgen05.ld epilogue -> bf16 tile in shared memory -> second tcgen05.mma):
+//   MODE_LSE    one sweep over the vocabulary: online max/sum -> lse[r] and the
+//               per-row CE (scoring / evaluation; forward only).
+//   MODE_TRAIN  CTA owns a 128-row tile, X stays in shared memory.  Sweep 1
+//               gives lse.  Sweep 2 recomputes each 128x128 logits tile, forms
+//               g = (softmax - onehot) * gscale * rs in registers, stores it as
+//               a bf16 tile in shared memory and accumulates dX += g . W' in a
+//               TMEM accumulator that lives across the sweep; the final
+//               epilogue applies the RMSNorm backward and writes dX.
+//   MODE_DW     CTA owns a 128-row tile of W' (kept in shared memory) and a
+//               chunk of rows; recomputes logits tiles against streamed X
+//               tiles, forms the same g tile and accumulates dW' += g^T . X in
+//               TMEM; the result is one fp32 partial tile per row chunk.
+//
+// The g tile is stored once, as rows of 128 bytes in 1 KiB swizzle atoms, and
+// is read by the second MMA either K-major (MODE_TRAIN: A = g) or MN-major
+// (MODE_DW: A = g^T); the streamed / resident operand tiles are likewise read
+// K-major by the logits MMA and MN-major by the second MMA, so nothing is
+// transposed or loaded twice.
+//
+// Replaces the reference's vocab-tiled linear+CE backends, whose GEMMs are
+// library calls with separate row-reduction kernels between them
+// (kernels/_lm_head_loss/src/rms_norm_binding.cpp:139-551, linear_ce.cu:24-304).
+//
+// Warp roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM
+// owner, warps 2..9 epilogue (warp w: TMEM lanes 32*(w%4).., column half (w-2)/4).
+#include "ptx.cuh"
+#include "ccb_api.h"
+#include "runtime.h"
+
+namespace ccb {
+
+constexpr int LH_D = 256;            // model dim handled by this kernel
+constexpr int LH_ROWS = 128;         // rows per tile
+constexpr int LH_VT = 128;           // vocabulary entries per tile
+constexpr int LH_CHUNK = 16384;      // one [128 rows][64 bf16] operand chunk
+constexpr int LH_TILE = 4 * LH_CHUNK;   // 128 x 256 bf16
+constexpr int LH_THREADS = 320;
+constexpr int LH_OFF_RES = 0;
+constexpr int LH_OFF_STG = LH_TILE;
+constexpr int LH_OFF_G = 3 * LH_TILE;
+constexpr int LH_OFF_X = LH_OFF_G + 2 * LH_CHUNK;      // (m, s) exchange: 2 x 128 float2
+constexpr int LH_OFF_BAR = LH_OFF_X + 2048;
+constexpr int LH_SMEM = LH_OFF_BAR + 256;
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float LN2 = 0.6931471805599453f;
+
+enum { MODE_LSE = 0, MODE_TRAIN = 1, MODE_DW = 2 };
+
+struct LmHeadArgs {
+  int R, V;
+  int n_mtiles, n_vtiles;
+  int row_chunks, mtiles_per_chunk;   // MODE_DW work decomposition
+  const float* rowss;       // [R] sum of squares of X rows; null = no RMSNorm (rs = 1)
+  float inv_dim, eps;
+  const long long* targets; // [R]
+  const float* rowweight;   // [R] or null
+  float gscale;             // d loss / d (per-row CE), e.g. 1/R
+  float* lse;               // [R] natural-log lse (out in LSE/TRAIN, in for DW)
+  float* loss;              // [R] per-row CE (out, LSE/TRAIN)
+  const __nv_bfloat16* X;   // [R, 256] for the final epilogue of TRAIN
+  __nv_bfloat16* dX;        // [R, 256] out (TRAIN)
+  float* dWpart;            // [row_chunks, V, 256] out (DW)
+  int* status;
+};
+
+struct LhBars {
+  uint64_t res_full, res_empty;
+  uint64_t stg_full[2], stg_empty[2];
+  uint64_t d1_full[2], d1_empty[2];
+  uint64_t g_full[2], g_empty[2];
+  uint64_t d2_full, d2_empty;
+  uint64_t xbar;            // epilogue-group rendezvous (8 warps)
+  uint32_t tmem_slot;
+  int abort_flag;
+};
+
+__device__ __forceinline__ float ex2f(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(LH_THREADS, 1)
+lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
+              const LmHeadArgs p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  LhBars* bars = reinterpret_cast<LhBars*>(smem + LH_OFF_BAR);
+  volatile int* abort_flag = &bars->abort_flag;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if ((smem_u32(smem) & 1023u) != 0u) {   // the swizzled tiles need a 1 KiB aligned base
+    if (threadIdx.x == 0) atomicCAS(p.status, CCB_OK, CCB_ERR_BAD_SHAPE);
+    return;
+  }
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->res_full, 1);
+    mbar_init(&bars->res_empty, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->stg_full[i], 1);
+      mbar_init(&bars->stg_empty[i], 1);
+      mbar_init(&bars->d1_full[i], 1);
+      mbar_init(&bars->d1_empty[i], 8);
+      mbar_init(&bars->g_full[i], MODE == MODE_DW ? 4 : 8);
+      mbar_init(&bars->g_empty[i], 1);
+    }
+    mbar_init(&bars->d2_full, 1);
+    mbar_init(&bars->d2_empty, 4);
+    mbar_init(&bars->xbar, 8);
+    bars->abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmX);
+    tma_prefetch_desc(&tmW);
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_slot;
+
+  // ---- work decomposition (identical in every role) -------------------------
+  // LSE / TRAIN: unit = m-tile; inner = v-tiles (x sweeps).
+  // DW: unit = (v-tile, row chunk); inner = m-tiles of the chunk.
+  const int n_units = (MODE == MODE_DW) ? p.n_vtiles * p.row_chunks : p.n_mtiles;
+  const int n_sweeps = (MODE == MODE_TRAIN) ? 2 : 1;
+
+  if (warp == 0) {
+    // =========================== TMA producer ================================
+    if (lane == 0) {
+      uint32_t res_phase = 0;
+      uint32_t n_stg = 0;
+      bool ok = true;
+      for (int unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x) {
+        int res_row, inner0, inner1;
+        if (MODE == MODE_DW) {
+          const int vt = unit % p.n_vtiles, ch = unit / p.n_vtiles;
+          res_row = vt * LH_VT;
+          inner0 = ch * p.mtiles_per_chunk;
+          inner1 = min(p.n_mtiles, inner0 + p.mtiles_per_chunk);
+        } else {
+          res_row = unit * LH_ROWS;
+          inner0 = 0;
+          inner1 = p.n_vtiles;
+        }
+        if (!mbar_wait(&bars->res_empty, res_phase ^ 1u, abort_flag, p.status)) { ok = false; break; }
+        mbar_arrive_expect_tx(&bars->res_full, LH_TILE);
+        const CUtensorMap* tmRes = (MODE == MODE_DW) ? &tmW : &tmX;
+        const CUtensorMap* tmStg = (MODE == MODE_DW) ? &tmX : &tmW;
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          tma_load_3d(smem + LH_OFF_RES + c * LH_CHUNK, tmRes, &bars->res_full, c * 64, res_row, 0);
+        res_phase ^= 1u;
+        for (int sw = 0; sw < n_sweeps && ok; ++sw) {
+          for (int it = inner0; it < inner1; ++it, ++n_stg) {
+            const int s = n_stg & 1;
+            const uint32_t ph = (n_stg >> 1) & 1u;
+            if (!mbar_wait(&bars->stg_empty[s], ph ^ 1u, abort_flag, p.status)) { ok = false; break; }
+            mbar_arrive_expect_tx(&bars->stg_full[s], LH_TILE);
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+              tma_load_3d(smem + LH_OFF_STG + s * LH_TILE + c * LH_CHUNK, tmStg, &bars->stg_full[s],
+                          c * 64, it * 128, 0);
+          }
+        }
+      }
+      if (!ok) {
+        uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 2000000ull) { }
+      }
+    }
+  } else if (warp == 1) {
+    // =========================== MMA issuer ==================================
+    if (lane == 0) {
+      constexpr uint32_t idesc1 = make_idesc_bf16(128, 128, 0, 0);
+      constexpr uint32_t idesc2 = (MODE == MODE_DW) ? make_idesc_bf16(128, 256, 1, 1)
+                                                    : make_idesc_bf16(128, 256, 0, 1);
+      const uint32_t res_base = smem_u32(smem + LH_OFF_RES);
+      const uint32_t g_base = smem_u32(smem + LH_OFF_G);
+      const uint32_t d2_tmem = tmem_base + 256;
+      uint32_t res_phase = 0, n_stg = 0, n_d1 = 0, n_g = 0, n_d2 = 0;
+      bool ok = true;
+
+      // second MMA for the tile that used stage `s`; `first` = first of its unit
+      auto issue_mma2 = [&](int s, bool first) -> bool {
+        const uint32_t stg_base = smem_u32(smem + LH_OFF_STG + s * LH_TILE);
+        if (first) {
+          if (!mbar_wait(&bars->d2_empty, (n_d2 & 1u) ^ 1u, abort_flag, p.status)) return false;
+          tc_fence_after_sync();
+        }
+        const uint32_t gph = n_g & 1u;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          if (!mbar_wait(&bars->g_full[h], gph, abort_flag, p.status)) return false;
+          tc_fence_after_sync();
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            uint64_t adesc, bdesc;
+            if (MODE == MODE_DW) {
+              const int kk = h * 4 + k;   // 16 rows of r per step
+              adesc = make_smem_desc(g_base + kk * 2048, LH_CHUNK, 1024);
+              bdesc = make_smem_desc(stg_base + kk * 2048, LH_CHUNK, 1024);
+            } else {
+              adesc = make_smem_desc(g_base + h * LH_CHUNK + k * 32, 16, 1024);
+              bdesc = make_smem_desc(stg_base + h * 8192 + k * 2048, LH_CHUNK, 1024);
+            }
+            umma_bf16(d2_tmem, adesc, bdesc, idesc2, (first && h == 0 && k == 0) ? 0u : 1u);
+          }
+          umma_commit(&bars->g_empty[h]);
+        }
+        umma_commit(&bars->stg_empty[s]);
+        ++n_g;
+        return true;
+      };
+
+      for (int unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x) {
+        int inner0 = 0, inner1 = p.n_vtiles;
+        if (MODE == MODE_DW) {
+          const int ch = unit / p.n_vtiles;
+          inner0 = ch * p.mtiles_per_chunk;
+          inner1 = min(p.n_mtiles, inner0 + p.mtiles_per_chunk);
+        }
+        if (!mbar_wait(&bars->res_full, res_phase, abort_flag, p.status)) { ok = false; break; }
+        res_phase ^= 1u;
+        tc_fence_after_sync();
+        for (int sw = 0; sw < n_sweeps && ok; ++sw) {
+          const bool second = (MODE == MODE_DW) || (MODE == MODE_TRAIN && sw == 1);
+          int prev_stage = -1;
+          bool prev_first = true;
+          for (int it = inner0; it < inner1; ++it) {
+            const int s = n_stg & 1;
+            const uint32_t sph = (n_stg >> 1) & 1u;
+            ++n_stg;
+            const int b = n_d1 & 1;
+            const uint32_t dph = (n_d1 >> 1) & 1u;
+            ++n_d1;
+            if (!mbar_wait(&bars->stg_full[s], sph, abort_flag, p.status)) { ok = false; break; }
+            if (!mbar_wait(&bars->d1_empty[b], dph ^ 1u, abort_flag, p.status)) { ok = false; break; }
+            tc_fence_after_sync();
+            const uint32_t stg_base = smem_u32(smem + LH_OFF_STG + s * LH_TILE);
+            const uint32_t xa = (MODE == MODE_DW) ? stg_base : res_base;   // X tile
+            const uint32_t wb = (MODE == MODE_DW) ? res_base : stg_base;   // W' tile
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const uint64_t adesc = make_smem_desc(xa + c * LH_CHUNK + k * 32, 16, 1024);
+                const uint64_t bdesc = make_smem_desc(wb + c * LH_CHUNK + k * 32, 16, 1024);
+                umma_bf16(tmem_base + b * 128, adesc, bdesc, idesc1, (c > 0 || k > 0) ? 1u : 0u);
+              }
+            }
+            umma_commit(&bars->d1_full[b]);
+            if (!second) {
+              umma_commit(&bars->stg_empty[s]);
+            } else {
+              if (prev_stage >= 0) {
+                if (!issue_mma2(prev_stage, prev_first)) { ok = false; break; }
+                prev_first = false;
+              }
+              prev_stage = s;
+            }
+          }
+          if (ok && second && prev_stage >= 0) {
+            if (!issue_mma2(prev_stage, prev_first)) { ok = false; break; }
+            umma_commit(&bars->d2_full);
+            ++n_d2;
+          }
+        }
+        if (ok) umma_commit(&bars->res_empty);
+      }
+    }
+  } else {
+    // =========================== epilogue ====================================
+    const int q = warp & 3;                 // TMEM lane quadrant
+    const int part = (warp - 2) >> 2;       // which 32 columns of each 64-column chunk
+    const int row_in_tile = q * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+    float2* xchg = reinterpret_cast<float2*>(smem + LH_OFF_X);
+    uint32_t n_d1 = 0, n_g = 0, n_d2 = 0, n_x = 0;
+    bool ok = true;
+    // Every wait below is made warp-uniform, so the warp-collective TMEM loads
+    // that follow never run with part of the warp on the abort path.
+    auto wait_all = [&](uint64_t* bar, uint32_t parity) -> bool {
+      const bool w = mbar_wait(bar, parity, abort_flag, p.status);
+      return __all_sync(0xffffffffu, w);
+    };
+    // Bounded rendezvous of the eight epilogue warps (orders the xchg traffic).
+    auto epi_sync = [&]() -> bool {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->xbar);
+      const bool w = wait_all(&bars->xbar, n_x & 1u);
+      ++n_x;
+      return w;
+    };
+
+    for (int unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x) {
+      int inner0 = 0, inner1 = p.n_vtiles, v_unit0 = 0, ch = 0;
+      if (MODE == MODE_DW) {
+        const int vt = unit % p.n_vtiles;
+        ch = unit / p.n_vtiles;
+        v_unit0 = vt * LH_VT;
+        inner0 = ch * p.mtiles_per_chunk;
+        inner1 = min(p.n_mtiles, inner0 + p.mtiles_per_chunk);
+      }
+      // per-row constants (LSE / TRAIN: fixed for the unit; DW: reloaded per m-tile)
+      int r = 0;
+      bool row_ok = false;
+      float c1 = 0.f, c2 = 0.f, gs = 0.f, rs = 0.f;
+      int tgt = -1;
+      auto load_row = [&](int mtile, bool need_lse) {
+        r = mtile * LH_ROWS + row_in_tile;
+        row_ok = r < p.R;
+        rs = row_ok ? (p.rowss ? rsqrtf(p.rowss[r] * p.inv_dim + p.eps) : 1.f) : 0.f;
+        c1 = rs * LOG2E;
+        tgt = row_ok ? (int)p.targets[r] : -1;
+        const float w = (row_ok && p.rowweight) ? p.rowweight[r] : 1.f;
+        gs = row_ok ? p.gscale * w * rs : 0.f;
+        if (need_lse) c2 = row_ok ? p.lse[r] * LOG2E : 0.f;
+      };
+      if (MODE != MODE_DW) load_row(unit, false);
+
+      for (int sw = 0; sw < n_sweeps && ok; ++sw) {
+        const bool second = (MODE == MODE_DW) || (MODE == MODE_TRAIN && sw == 1);
+        float run_m = -INFINITY, run_s = 0.f, tacc = 0.f, zt = 0.f;
+        for (int it = inner0; it < inner1 && ok; ++it) {
+          const int b = n_d1 & 1;
+          const uint32_t dph = (n_d1 >> 1) & 1u;
+          ++n_d1;
+          int v0;
+          if (MODE == MODE_DW) {
+            load_row(it, true);
+            v0 = v_unit0;
+          } else {
+            v0 = it * LH_VT;
+          }
+          if (!wait_all(&bars->d1_full[b], dph)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t t_addr = tmem_base + b * 128 + lane_addr;
+          if (!second) {
+            // ---- sweep 1: online max / sum (log2 domain) ----------------------
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const int col0 = h * 64 + part * 32;
+              uint32_t a[32];
+              __syncwarp();
+              tmem_ld32(t_addr + col0, a);
+              tmem_ld_wait();
+              float mx = __uint_as_float(a[0]);
+#pragma unroll
+              for (int i = 1; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(a[i]));
+              const float new_m = fmaxf(run_m, mx * c1);
+              float acc = 0.f;
+#pragma unroll
+              for (int i = 0; i < 32; ++i) acc += ex2f(fmaf(__uint_as_float(a[i]), c1, -new_m));
+              run_s = run_s * ex2f(run_m - new_m) + acc;
+              run_m = new_m;
+              if (MODE == MODE_LSE) {
+                const int tl = tgt - (v0 + col0);
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  if (i == tl) tacc = __uint_as_float(a[i]);
+              }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->d1_empty[b]);
+          } else {
+            // ---- sweep 2 / DW: g tile -> shared memory ------------------------
+            const uint32_t gph = n_g & 1u;
+            ++n_g;
+            if (MODE == MODE_DW) {
+              if (!wait_all(&bars->g_empty[q >> 1], gph ^ 1u)) { ok = false; break; }
+            }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const int col0 = h * 64 + part * 32;
+              uint32_t a[32];
+              __syncwarp();
+              tmem_ld32(t_addr + col0, a);
+              tmem_ld_wait();
+              const int tl = tgt - (v0 + col0);
+              uint32_t packed[16];
+#pragma unroll
+              for (int i = 0; i < 32; i += 2) {
+                const float z0 = fmaf(__uint_as_float(a[i]), c1, -c2);
+                const float z1 = fmaf(__uint_as_float(a[i + 1]), c1, -c2);
+                float p0 = ex2f(z0), p1 = ex2f(z1);
+                if (i == tl) { p0 -= 1.f; zt = z0; }
+                if (i + 1 == tl) { p1 -= 1.f; zt = z1; }
+                packed[i >> 1] = pack_bf16x2(p0 * gs, p1 * gs);
+              }
+              if (MODE != MODE_DW) {
+                if (!wait_all(&bars->g_empty[h], gph ^ 1u)) { ok = false; break; }
+              }
+              // row `row_in_tile` of chunk h, 16-byte slots part*4 .. part*4+3, 128B swizzle
+              uint8_t* grow = smem + LH_OFF_G + h * LH_CHUNK + row_in_tile * 128;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const int slot = (part * 4 + j) ^ (row_in_tile & 7);
+                *reinterpret_cast<uint4*>(grow + slot * 16) =
+                    make_uint4(packed[j * 4], packed[j * 4 + 1], packed[j * 4 + 2], packed[j * 4 + 3]);
+              }
+              if (MODE != MODE_DW) {
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars->g_full[h]);
+              }
+            }
+            if (!ok) break;
+            if (MODE == MODE_DW) {
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&bars->g_full[q >> 1]);
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->d1_empty[b]);
+          }
+        }
+        if (!ok) break;
+
+        if (!second) {
+          // combine the two column halves of each row -> lse
+          if (!epi_sync()) { ok = false; break; }
+          xchg[part * 128 + row_in_tile] = make_float2(run_m, run_s);
+          if (!epi_sync()) { ok = false; break; }
+          const float2 o = xchg[(part ^ 1) * 128 + row_in_tile];
+          const float m = fmaxf(run_m, o.x);
+          const float s = run_s * ex2f(run_m - m) + o.y * ex2f(o.x - m);
+          const float lse2 = m + __log2f(s);
+          c2 = lse2;
+          if (row_ok && part == 0) p.lse[r] = lse2 * LN2;
+          if (MODE == MODE_LSE) {
+            // the target column lived in exactly one of the two halves
+            if (!epi_sync()) { ok = false; break; }
+            xchg[part * 128 + row_in_tile] = make_float2(tacc, 0.f);
+            if (!epi_sync()) { ok = false; break; }
+            const float t_other = xchg[(part ^ 1) * 128 + row_in_tile].x;
+            if (row_ok && part == 0) p.loss[r] = lse2 * LN2 - (tacc + t_other) * rs;
+          }
+        } else if (MODE == MODE_TRAIN) {
+          // per-row CE = -log p_target = -zt * ln2 (zt captured by one of the two warps)
+          if (!epi_sync()) { ok = false; break; }
+          xchg[part * 128 + row_in_tile] = make_float2(zt, 0.f);
+          if (!epi_sync()) { ok = false; break; }
+          const float z_other = xchg[(part ^ 1) * 128 + row_in_tile].x;
+          if (row_ok && part == 0) p.loss[r] = -(zt + z_other) * LN2;
+        }
+      }
+      if (!ok) break;
+
+      // ---- unit epilogue: drain the second accumulator ------------------------
+      if (MODE != MODE_LSE) {
+        if (part == 0) {
+          if (!wait_all(&bars->d2_full, n_d2 & 1u)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t t2 = tmem_base + 256 + lane_addr;
+          if (MODE == MODE_TRAIN) {
+            // dx = q - x * (rs^2 / D) * sum_d q * x   (RMSNorm backward, weight folded)
+            const __nv_bfloat16* xrow = p.X + (long long)r * LH_D;
+            float dot = 0.f;
+            for (int c = 0; c < 8; ++c) {
+              uint32_t a[32];
+              __syncwarp();
+              tmem_ld32(t2 + c * 32, a);
+              tmem_ld_wait();
+              if (row_ok) {
+                const uint4* x4 = reinterpret_cast<const uint4*>(xrow + c * 32);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const uint4 qv = __ldg(x4 + j);
+                  float2 f;
+                  f = unpack_bf16x2(qv.x); dot += __uint_as_float(a[j * 8 + 0]) * f.x + __uint_as_float(a[j * 8 + 1]) * f.y;
+                  f = unpack_bf16x2(qv.y); dot += __uint_as_float(a[j * 8 + 2]) * f.x + __uint_as_float(a[j * 8 + 3]) * f.y;
+                  f = unpack_bf16x2(qv.z); dot += __uint_as_float(a[j * 8 + 4]) * f.x + __uint_as_float(a[j * 8 + 5]) * f.y;
+                  f = unpack_bf16x2(qv.w); dot += __uint_as_float(a[j * 8 + 6]) * f.x + __uint_as_float(a[j * 8 + 7]) * f.y;
+                }
+              }
+            }
+            const float coef = p.rowss ? dot * rs * rs * p.inv_dim : 0.f;   // no norm: plain dX
+            for (int c = 0; c < 8; ++c) {
+              uint32_t a[32];
+              __syncwarp();
+              tmem_ld32(t2 + c * 32, a);
+              tmem_ld_wait();
+              if (row_ok) {
+                const uint4* x4 = reinterpret_cast<const uint4*>(xrow + c * 32);
+                uint4* o4 = reinterpret_cast<uint4*>(p.dX + (long long)r * LH_D + c * 32);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const uint4 qv = __ldg(x4 + j);
+                  const float2 f0 = unpack_bf16x2(qv.x), f1 = unpack_bf16x2(qv.y),
+                               f2 = unpack_bf16x2(qv.z), f3 = unpack_bf16x2(qv.w);
+                  uint4 o;
+                  o.x = pack_bf16x2(__uint_as_float(a[j * 8 + 0]) - f0.x * coef, __uint_as_float(a[j * 8 + 1]) - f0.y * coef);
+                  o.y = pack_bf16x2(__uint_as_float(a[j * 8 + 2]) - f1.x * coef, __uint_as_float(a[j * 8 + 3]) - f1.y * coef);
+                  o.z = pack_bf16x2(__uint_as_float(a[j * 8 + 4]) - f2.x * coef, __uint_as_float(a[j * 8 + 5]) - f2.y * coef);
+                  o.w = pack_bf16x2(__uint_as_float(a[j * 8 + 6]) - f3.x * coef, __uint_as_float(a[j * 8 + 7]) - f3.y * coef);
+                  o4[j] = o;
+                }
+              }
+            }
+          } else {
+            // MODE_DW: fp32 partial tile [v rows][256]
+            const int v = v_unit0 + row_in_tile;
+            float* orow = p.dWpart + ((long long)ch * p.V + v) * LH_D;
+            for (int c = 0; c < 8; ++c) {
+              uint32_t a[32];
+              __syncwarp();
+              tmem_ld32(t2 + c * 32, a);
+              tmem_ld_wait();
+              if (v < p.V) {
+                float4* o4 = reinterpret_cast<float4*>(orow + c * 32);
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                  o4[j] = make_float4(__uint_as_float(a[j * 4]), __uint_as_float(a[j * 4 + 1]),
+                                      __uint_as_float(a[j * 4 + 2]), __uint_as_float(a[j * 4 + 3]));
+              }
+            }
+          }
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars->d2_empty);
+        }
+        ++n_d2;
+      }
+    }
+  }
+
+  // =========================== teardown ========================================
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int MODE>
+static int launch_lmhead(const void* X, const void* W, LmHeadArgs& a, cudaStream_t stream) {
+  static bool attr_set[16] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  auto kern = lmhead_kernel<MODE>;
+  if (!attr_set[dev & 15]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, LH_SMEM);
+    if (e != cudaSuccess) return set_error("cudaFuncSetAttribute(lmhead): %s", cudaGetErrorString(e));
+    attr_set[dev & 15] = true;
+  }
+  CUtensorMap tmX, tmW;
+  if (make_tmap_bf16_3d(&tmX, X, LH_D, (uint64_t)a.R, 1, LH_D, 0, 64, 128)) return -1;
+  if (make_tmap_bf16_3d(&tmW, W, LH_D, (uint64_t)a.V, 1, LH_D, 0, 64, 128)) return -1;
+  a.status = ccb_status_ptr();
+  const int units = (MODE == MODE_DW) ? a.n_vtiles * a.row_chunks : a.n_mtiles;
+  const int grid = units < ccb_num_sms() ? units : ccb_num_sms();
+  kern<<<grid, LH_THREADS, LH_SMEM, stream>>>(tmX, tmW, a);
+  count_launch();
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : set_error("lmhead launch: %s", cudaGetErrorString(e));
+}
+
+}  // namespace ccb
+
+using namespace ccb;
+
+static int lmhead_common(LmHeadArgs& a, int64_t R, int64_t V, int64_t D, const float* rowss,
+                         float eps, const int64_t* targets) {
+  if (D != LH_D) return set_error("fused LM head: model dim must be %d (got %lld)", LH_D, (long long)D);
+  if (V % LH_VT != 0) return set_error("fused LM head: vocab must be a multiple of %d", LH_VT);
+  if (R <= 0) return 1;
+  a.R = (int)R;
+  a.V = (int)V;
+  a.n_mtiles = (int)((R + LH_ROWS - 1) / LH_ROWS);
+  a.n_vtiles = (int)(V / LH_VT);
+  a.row_chunks = 1;
+  a.mtiles_per_chunk = a.n_mtiles;
+  a.rowss = rowss;
+  a.inv_dim = 1.f / (float)D;
+  a.eps = eps;
+  a.targets = (const long long*)targets;
+  return 0;
+}
+
+// lse[r], loss[r] = CE of row r.  Forward only.
+extern "C" int ccb_lmhead_lse(const void* X, const void* W, const float* rowss, float eps,
+                              const int64_t* targets, float* lse, float* loss, int64_t R, int64_t V,
+                              int64_t D, void* stream) {
+  LmHeadArgs a = {};
+  int rc = lmhead_common(a, R, V, D, rowss, eps, targets);
+  if (rc) return rc < 0 ? rc : 0;
+  a.lse = lse;
+  a.loss = loss;
+  return launch_lmhead<MODE_LSE>(X, W, a, (cudaStream_t)stream);
+}
+
+// lse, per-row loss and dX (gradient w.r.t. the un-normalised hidden state).
+extern "C" int ccb_lmhead_train(const void* X, const void* W, const float* rowss, float eps,
+                                const int64_t* targets, const float* rowweight, float gscale,
+                                float* lse, float* loss, void* dX, int64_t R, int64_t V, int64_t D,
+                                void* stream) {
+  LmHeadArgs a = {};
+  int rc = lmhead_common(a, R, V, D, rowss, eps, targets);
+  if (rc) return rc < 0 ? rc : 0;
+  a.rowweight = rowweight;
+  a.gscale = gscale;
+  a.lse = lse;
+  a.loss = loss;
+  a.X = (const __nv_bfloat16*)X;
+  a.dX = (__nv_bfloat16*)dX;
+  return launch_lmhead<MODE_TRAIN>(X, W, a, (cudaStream_t)stream);
+}
+
+// dWpart[row_chunks, V, D] fp32: partial gradients of W' = W_lm * w_norm.
+extern "C" int ccb_lmhead_dw(const void* X, const void* W, const float* rowss, float eps,
+                             const int64_t* targets, const float* rowweight, float gscale,
+                             const float* lse, float* dWpart, int64_t row_chunks, int64_t R,
+                             int64_t V, int64_t D, void* stream) {
+  LmHeadArgs a = {};
+  int rc = lmhead_common(a, R, V, D, rowss, eps, targets);
+  if (rc) return rc < 0 ? rc : 0;
+  if (row_chunks < 1) row_chunks = 1;
+  if (row_chunks > a.n_mtiles) row_chunks = a.n_mtiles;
+  a.mtiles_per_chunk = (int)((a.n_mtiles + row_chunks - 1) / row_chunks);
+  a.row_chunks = (a.n_mtiles + a.mtiles_per_chunk - 1) / a.mtiles_per_chunk;
+  if (a.row_chunks != (int)row_chunks)
+    return set_error("ccb_lmhead_dw: row_chunks=%lld leaves an empty chunk (use %d)",
+                     (long long)row_chunks, a.row_chunks);
+  a.rowweight = rowweight;
+  a.gscale = gscale;
+  a.lse = const_cast<float*>(lse);
+  a.dWpart = dWpart;
+  return launch_lmhead<MODE_DW>(X, W, a, (cudaStream_t)stream);
+}

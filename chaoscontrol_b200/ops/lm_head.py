@@ -1,0 +1,125 @@
+"""Fused LM head (``csrc/lmhead.cu``): linear + log-softmax + cross-entropy with
+logits recomputed in backward, plus the PyTorch statements used on CPU and as
+test oracles.
+
+Inputs are the *un-normalised* final hidden state ``x`` with its row sums of
+squares ``rowss`` (the final RMSNorm is applied inside the kernel as a row
+scale) and ``W_f = lm_head.weight * final_norm.weight`` (norm weight folded).
+Pass ``rowss=None`` for an already-normalised ``x``.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import f32, i64, vp
+
+_lib.register_sig("ccb_lmhead_lse", [vp, vp, vp, f32, vp, vp, vp, i64, i64, i64, vp])
+_lib.register_sig("ccb_lmhead_train", [vp, vp, vp, f32, vp, vp, f32, vp, vp, vp, i64, i64, i64, vp])
+_lib.register_sig("ccb_lmhead_dw", [vp, vp, vp, f32, vp, vp, f32, vp, vp, i64, i64, i64, i64, vp])
+
+EPS = 1e-6
+
+
+def fused_supported(x: torch.Tensor, W: torch.Tensor) -> bool:
+    """Shapes / dtypes the tcgen05 LM-head kernels handle."""
+    return (x.is_cuda and x.dtype == torch.bfloat16 and W.dtype == torch.bfloat16 and
+            x.shape[-1] == 256 and W.shape[0] % 128 == 0 and W.shape[1] == 256)
+
+
+def lm_head_reference(x, rowss, W_f, targets, *, gscale: float = 1.0, rowweight=None,
+                      eps: float = EPS, want_grads: bool = True):
+    """fp32 statement.  Returns ``(loss_rows, lse, dX, dW_f)`` (grads None if not wanted)."""
+    xf = x.detach().float().requires_grad_(want_grads)
+    Wf = W_f.detach().float().requires_grad_(want_grads)
+    D = xf.shape[-1]
+    with torch.enable_grad():
+        if rowss is not None:
+            rs = torch.rsqrt((xf * xf).sum(-1) / D + eps)
+            xn = xf * rs[:, None]
+        else:
+            xn = xf
+        logits = xn @ Wf.t()
+        lse = torch.logsumexp(logits, dim=-1)
+        loss_rows = lse - logits.gather(1, targets.view(-1, 1).long()).squeeze(1)
+        if not want_grads:
+            return loss_rows.detach(), lse.detach(), None, None
+        w = rowweight.float() if rowweight is not None else torch.ones_like(loss_rows)
+        (loss_rows * w).sum().mul(gscale).backward()
+    return loss_rows.detach(), lse.detach(), xf.grad, Wf.grad
+
+
+def _prep(x, rowss, W_f, targets):
+    assert x.is_contiguous() and W_f.is_contiguous()
+    t = targets.reshape(-1)
+    if t.dtype != torch.int64:
+        t = t.long()
+    return t.contiguous()
+
+
+def lm_head_lse(x, rowss, W_f, targets, *, eps: float = EPS):
+    """Forward only: ``(loss_rows, lse)`` fp32 ``[R]``; no logits in memory."""
+    R, D = x.shape
+    if not fused_supported(x, W_f):
+        lr, lse, _, _ = lm_head_reference(x, rowss, W_f, targets, eps=eps, want_grads=False)
+        return lr, lse
+    t = _prep(x, rowss, W_f, targets)
+    lse = torch.empty(R, dtype=torch.float32, device=x.device)
+    loss = torch.empty(R, dtype=torch.float32, device=x.device)
+    _lib.check(_lib.lib().ccb_lmhead_lse(x.data_ptr(), W_f.data_ptr(), _lib.ptr(rowss), eps,
+                                         t.data_ptr(), lse.data_ptr(), loss.data_ptr(), R,
+                                         W_f.shape[0], D, _lib.stream_ptr()), "lmhead_lse")
+    return loss, lse
+
+
+def default_row_chunks(R: int, V: int) -> int:
+    """Row-chunk count for the dW kernel so (V/128 x chunks) work items divide
+    evenly over the SMs."""
+    sms = _lib.lib().ccb_num_sms() if _lib.available() else 148
+    vt = max(V // 128, 1)
+    mt = (R + 127) // 128
+    best = 1
+    for c in range(1, min(mt, 64) + 1):
+        per = (mt + c - 1) // c
+        if (mt + per - 1) // per != c:
+            continue
+        items = vt * c
+        waves = (items + sms - 1) // sms
+        eff = items / (waves * sms)
+        if eff > 0.97 and c >= best:
+            best = c
+            if items >= 8 * sms:
+                break
+    return best
+
+
+def lm_head_train(x, rowss, W_f, targets, *, gscale: float, rowweight=None, eps: float = EPS,
+                  row_chunks: Optional[int] = None):
+    """Loss and both gradients.  Returns ``(loss_rows, lse, dX bf16, dW_f_partials fp32 [C,V,D])``.
+
+    ``dX`` is the gradient w.r.t. the un-normalised hidden state (RMSNorm
+    backward applied); the partials sum to the gradient w.r.t. ``W_f``.
+    """
+    R, D = x.shape
+    V = W_f.shape[0]
+    if not fused_supported(x, W_f):
+        lr, lse, dX, dW = lm_head_reference(x, rowss, W_f, targets, gscale=gscale,
+                                            rowweight=rowweight, eps=eps)
+        return lr, lse, dX.to(x.dtype), dW.unsqueeze(0)
+    t = _prep(x, rowss, W_f, targets)
+    dev = x.device
+    lse = torch.empty(R, dtype=torch.float32, device=dev)
+    loss = torch.empty(R, dtype=torch.float32, device=dev)
+    dX = torch.empty_like(x)
+    L = _lib.lib()
+    _lib.check(L.ccb_lmhead_train(x.data_ptr(), W_f.data_ptr(), _lib.ptr(rowss), eps, t.data_ptr(),
+                                  _lib.ptr(rowweight), gscale, lse.data_ptr(), loss.data_ptr(),
+                                  dX.data_ptr(), R, V, D, _lib.stream_ptr()), "lmhead_train")
+    C = row_chunks or default_row_chunks(R, V)
+    part = torch.empty(C, V, D, dtype=torch.float32, device=dev)
+    _lib.check(L.ccb_lmhead_dw(x.data_ptr(), W_f.data_ptr(), _lib.ptr(rowss), eps, t.data_ptr(),
+                               _lib.ptr(rowweight), gscale, lse.data_ptr(), part.data_ptr(), C, R, V,
+                               D, _lib.stream_ptr()), "lmhead_dw")
+    return loss, lse, dX, part

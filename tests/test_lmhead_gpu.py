@@ -1,0 +1,57 @@
+"""Fused LM-head kernels (lse / train / dW) vs the fp32 PyTorch statement."""
+import pytest
+import torch
+
+from chaoscontrol_b200.ops import _lib
+from chaoscontrol_b200.ops import lm_head as LH
+
+pytestmark = pytest.mark.gpu
+
+
+def _mk(R, V, seed=0, wscale=0.08):
+    torch.manual_seed(seed)
+    x = torch.randn(R, 256, device="cuda").bfloat16()
+    W = (torch.randn(V, 256, device="cuda") * wscale).bfloat16()
+    t = torch.randint(0, V, (R,), device="cuda")
+    ss = (x.float() ** 2).sum(-1)
+    return x, W, t, ss
+
+
+@pytest.mark.parametrize("R,V", [(128, 128), (256, 512), (1000, 1024), (4096, 16384)])
+def test_lmhead_lse(R, V):
+    x, W, t, ss = _mk(R, V)
+    loss, lse = LH.lm_head_lse(x, ss, W, t)
+    _lib.assert_ok()
+    rl, rlse, _, _ = LH.lm_head_reference(x, ss, W, t, want_grads=False)
+    assert torch.allclose(lse, rlse, rtol=1e-3, atol=2e-2), (lse - rlse).abs().max()
+    assert torch.allclose(loss, rl, rtol=1e-3, atol=3e-2), (loss - rl).abs().max()
+
+
+@pytest.mark.parametrize("R,V,chunks,norm", [(128, 128, 1, True), (384, 512, 3, True),
+                                             (1000, 1024, 2, False), (2048, 16384, 4, True)])
+def test_lmhead_train(R, V, chunks, norm):
+    x, W, t, ss = _mk(R, V, seed=1)
+    w = torch.rand(R, device="cuda")
+    gscale = 1.0 / R
+    rowss = ss if norm else None
+    loss, lse, dX, part = LH.lm_head_train(x, rowss, W, t, gscale=gscale, rowweight=w,
+                                           row_chunks=chunks)
+    _lib.assert_ok()
+    rl, rlse, rdX, rdW = LH.lm_head_reference(x, rowss, W, t, gscale=gscale, rowweight=w)
+    assert torch.allclose(lse, rlse, rtol=1e-3, atol=2e-2)
+    assert torch.allclose(loss, rl, rtol=1e-3, atol=3e-2), (loss - rl).abs().max()
+    sx = rdX.abs().max().item()
+    assert (dX.float() - rdX).abs().max().item() <= 0.03 * sx + 1e-7, \
+        ((dX.float() - rdX).abs().max().item(), sx)
+    dW = part.sum(0)
+    sw = rdW.abs().max().item()
+    assert (dW - rdW).abs().max().item() <= 0.03 * sw + 1e-7, ((dW - rdW).abs().max().item(), sw)
+
+
+def test_lmhead_train_deterministic():
+    x, W, t, ss = _mk(1024, 2048, seed=2)
+    a = LH.lm_head_train(x, ss, W, t, gscale=1e-3)
+    b = LH.lm_head_train(x, ss, W, t, gscale=1e-3)
+    _lib.assert_ok()
+    for u, v in zip(a, b):
+        assert torch.equal(u, v)

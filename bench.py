@@ -1,0 +1,356 @@
+#!/usr/bin/env python
+"""Headline benchmark: training tokens/s of the 4-layer x 256-d, V=16384
+diagonal-SSM LM (seq 512, batch 1024 per rank, bf16, Muon lr 0.064, weight
+decay 0.01, grad clip 1.0) on N GPUs of one node.
+
+    python bench.py --gpus N --steps K --warmup W [--impl ours|reference]
+
+For N > 1 launch one rank per GPU with ``python -m torch.distributed.run``.
+Rank 0 prints one JSON line.  ``value`` is the whole-job tokens/s with the
+step's inputs already resident on the device (CUDA-event timed, max over
+ranks); ``e2e`` repeats the measurement through the public training API with a
+pinned-host -> device copy of every step's batch and a device -> host read of
+every step's loss inside the timed region.
+
+``--impl reference`` runs the unmodified reference package installed under
+``baseline/_ref`` through its own ``train_ssm_step`` / ``Muon`` /
+``clip_grad_norm_fused`` on the same model, data and schedule.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+BASELINE_TOKS_8XH100 = 25_023_217.0          # reference headline, 8 x H100 aggregate
+BASELINE_TOKS_1XH100 = 3_214_781.0           # reference headline, 1 x H100
+
+VOCAB, DIM, LAYERS, FF_MULT = 16384, 256, 4, 2
+SEQ, BATCH = 512, 1024
+LR, WD, CLIP = 0.064, 0.01, 1.0
+
+
+def _parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=BATCH, help=argparse.SUPPRESS)
+    ap.add_argument("--seq", type=int, default=SEQ, help=argparse.SUPPRESS)
+    ap.add_argument("--no-e2e", action="store_true", help=argparse.SUPPRESS)
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows: list[list[str]] = []
+        self._stop = threading.Event()
+        self._th = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                      "-i", str(self.index)], capture_output=True, text=True, timeout=5)
+                if out.returncode == 0 and out.stdout.strip():
+                    self.rows.append([c.strip() for c in out.stdout.strip().split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._th.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._th.join(timeout=6)
+
+    def summary(self) -> dict:
+        if not self.rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        sm = sorted(float(r[0]) for r in self.rows if r[0].replace(".", "").isdigit())
+        mx = [float(r[1]) for r in self.rows if r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 3 + i and r[3 + i] == "Active" for r in self.rows)]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(self.rows)}
+
+
+def _make_batches(n_steps: int, batch: int, seq: int, rank: int):
+    """Pinned-host int64 Zipf(1.1) windows, one [batch, seq + 1] block per step, per-rank seed."""
+    import numpy as np
+    import torch
+    ranks = np.arange(1, VOCAB + 1, dtype=np.float64)
+    cdf = np.cumsum(ranks ** (-1.1))
+    cdf /= cdf[-1]
+    rng = np.random.default_rng(1234 + rank)
+    n_distinct = min(n_steps, 8)
+    blocks = []
+    for _ in range(n_distinct):
+        ids = np.searchsorted(cdf, rng.random(batch * (seq + 1)), side="left").clip(0, VOCAB - 1)
+        t = torch.from_numpy(ids.astype(np.int64)).view(batch, seq + 1)
+        blocks.append(t.pin_memory() if torch.cuda.is_available() else t)
+    return [blocks[i % n_distinct] for i in range(n_steps)]
+
+
+def _dist_setup(args):
+    import torch
+    import torch.distributed as dist
+    ws = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if ws > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    if ws != args.gpus and rank == 0:
+        print(f"[bench] note: WORLD_SIZE={ws} differs from --gpus {args.gpus}; using WORLD_SIZE",
+              file=sys.stderr)
+    return rank, local, ws
+
+
+def _max_over_ranks(ms: float, ws: int) -> float:
+    if ws == 1:
+        return ms
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def _barrier(ws: int):
+    import torch
+    if ws > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def _timed(fn_step, n: int, ws: int) -> float:
+    """ms per step over exactly n steps, CUDA events, barrier + sync on both sides, max over ranks."""
+    import torch
+    _barrier(ws)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(n):
+        fn_step(i)
+    e1.record()
+    _barrier(ws)
+    return _max_over_ranks(e0.elapsed_time(e1), ws) / n
+
+
+# ---------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    sys.path.insert(0, str(ROOT))
+    from chaoscontrol_b200.models.model import CareStudentLM
+    from chaoscontrol_b200.ops import _lib
+    from chaoscontrol_b200.optim.muon import Muon
+    from chaoscontrol_b200.parallel.distributed import (allreduce_grads, broadcast_params,
+                                                        clip_arena_grad_norm)
+    from chaoscontrol_b200.train_ssm import _engine_for, train_ssm_step
+    from chaoscontrol_b200.utils.arena import ParamArena
+
+    rank, local, ws = _dist_setup(args)
+    dev = torch.device("cuda", local)
+    torch.manual_seed(0)
+    model = CareStudentLM(vocab_size=VOCAB, dim=DIM, num_layers=LAYERS, ff_mult=FF_MULT)
+    model = model.to(dev).to(torch.bfloat16)
+    arena = ParamArena.install(model)
+    model.train()
+    if ws > 1:
+        from chaoscontrol_b200.parallel import symm_comm
+        symm_comm.try_enable(arena.flat_grad.numel())
+        broadcast_params(model)
+    opt = Muon(model.parameters(), lr=LR, weight_decay=WD, adamw_lr=LR, adamw_weight_decay=WD, fused=True)
+    opt.bind_arena(arena)
+    engine = _engine_for(model)
+    if engine is None:
+        raise RuntimeError("kernel training engine unavailable: refusing to bench a fallback path")
+
+    n_total = args.warmup + args.steps
+    host = _make_batches(n_total, args.batch, args.seq, rank)
+    dev_batches = [h.to(dev) for h in host[:8]]
+    dev_in = [b[:, :-1].to(torch.int32).contiguous() for b in dev_batches]
+    dev_tg = [b[:, 1:].contiguous() for b in dev_batches]
+    losses = []
+
+    def step_resident(i):
+        j = i % len(dev_in)
+        loss = engine.step(dev_in[j], dev_tg[j])
+        if ws > 1:
+            allreduce_grads(model, ws)
+        clip_arena_grad_norm(arena, CLIP)
+        opt.step()
+        losses.append(loss)
+
+    for i in range(args.warmup):
+        step_resident(i)
+    _lib.assert_ok()
+    l0 = _lib.launch_count()
+    with ClockSampler(local) as cs:
+        ms = _timed(step_resident, args.steps, ws)
+    launches = _lib.launch_count() - l0
+    _lib.assert_ok()
+    final_loss = float(torch.stack(losses[-args.steps:]).float().mean().item())
+
+    # end to end through the public API: H2D of the batch and D2H of the loss every step
+    e2e = None
+    if not args.no_e2e:
+        h2d = host[0].numel() * host[0].element_size()
+
+        def step_e2e(i):
+            blk = host[i % len(host)].to(dev, non_blocking=True)
+            inputs, targets = blk[:, :-1], blk[:, 1:]
+            opt.zero_grad(set_to_none=True)
+            loss = train_ssm_step(model, inputs, targets, 64, ddp_active=ws > 1, world_size=ws,
+                                  precision="bf16", lm_head_backward_mode="fused_streaming_cached",
+                                  lm_head_tile_size=8192)
+            clip_arena_grad_norm(arena, CLIP)
+            opt.step()
+            step_e2e.last = float(loss.item())
+
+        for i in range(max(3, args.warmup // 2)):
+            step_e2e(i)
+        ms_e = _timed(step_e2e, args.steps, ws)
+        e2e = {"value": ws * args.batch * args.seq / (ms_e / 1e3), "unit": "tokens/s",
+               "ms_per_step": ms_e, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
+               "api": "chaoscontrol_b200.train_ssm.train_ssm_step + Muon.step"}
+
+    toks = ws * args.batch * args.seq / (ms / 1e3)
+    base = BASELINE_TOKS_8XH100 * ws / 8.0
+    out = {"metric": "train tokens/sec, 4Lx256d V16384 SSM (seq 512, bs 1024/rank, bf16, Muon)",
+           "value": toks, "unit": "tokens/s", "n_gpus": ws, "steps": args.steps,
+           "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+           "vs_baseline": toks / base, "dtype": "bf16", "data": "synthetic Zipf(1.1) tokens, random-init weights",
+           "impl": "ours", "final_loss": final_loss, "gpu_launches": launches,
+           "clocks": cs.summary(), "e2e": e2e,
+           "config": {"model": f"CareStudentLM {LAYERS}x{DIM} V{VOCAB} ff_mult {FF_MULT}",
+                      "global_batch": ws * args.batch, "seq_len": args.seq,
+                      "parallelism": f"dp{ws}", "optimizer": f"Muon lr {LR} wd {WD} clip {CLIP}",
+                      "lm_head": "fused tcgen05 linear+CE, logits recomputed in backward",
+                      "l2": "working set per step (>10 GB of activations) exceeds the 126 MB L2",
+                      "vs_baseline_ref": "reference 8xH100 headline 25,023,217 tok/s scaled by n_gpus/8"}}
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    if ws > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------
+def run_reference(args):
+    ref = ROOT / "baseline" / "_ref"
+    if not (ref / "chaoscontrol").exists():
+        print(json.dumps({"impl": "reference",
+                          "unavailable": "baseline/_ref is missing: the reference is not installed on this box"}))
+        return
+    sys.path.insert(0, str(ref))
+    os.environ.setdefault("CHAOSCONTROL_DIAG_SCAN_BACKEND", "ssm_scan")
+    import torch
+    try:
+        from chaoscontrol.distributed import (allreduce_grads, broadcast_params,  # noqa: F401
+                                              clip_grad_norm_fused)
+        from chaoscontrol.model import CareStudentLM
+        from chaoscontrol.optim.muon import Muon
+        from chaoscontrol.train_ssm import train_ssm_step
+    except Exception as exc:  # pragma: no cover
+        print(json.dumps({"impl": "reference", "unavailable": f"import failed: {type(exc).__name__}: {exc}"[:300]}))
+        return
+
+    rank, local, ws = _dist_setup(args)
+    dev = torch.device("cuda", local)
+    torch.manual_seed(0)
+    model = CareStudentLM(vocab_size=VOCAB, dim=DIM, num_layers=LAYERS, ff_mult=FF_MULT)
+    model = model.to(dev).to(torch.bfloat16)
+    model.train()
+    if ws > 1:
+        broadcast_params(model)
+    opt = Muon(model.parameters(), lr=LR, weight_decay=WD, adamw_lr=LR, adamw_weight_decay=WD, fused=True)
+    opt.bind_param_names(list(model.named_parameters()))
+    mode = os.environ.get("BENCH_REF_HEAD_MODE", "fused_streaming_cached")
+
+    n_total = args.warmup + args.steps
+    host = _make_batches(n_total, args.batch, args.seq, rank)
+    dev_batches = [h.to(dev) for h in host[:8]]
+    losses = []
+
+    def one(inputs, targets):
+        opt.zero_grad(set_to_none=True)
+        loss = train_ssm_step(model, inputs, targets, 64, ddp_active=ws > 1, world_size=ws,
+                              precision="bf16", lm_head_backward_mode=mode, lm_head_tile_size=8192)
+        clip_grad_norm_fused(model.parameters(), CLIP)
+        opt.step()
+        return loss
+
+    def step_resident(i):
+        b = dev_batches[i % len(dev_batches)]
+        losses.append(one(b[:, :-1].to(torch.int32), b[:, 1:]))
+
+    try:
+        for i in range(args.warmup):
+            step_resident(i)
+        torch.cuda.synchronize()
+    except Exception as exc:
+        if rank == 0:
+            print(json.dumps({"impl": "reference",
+                              "unavailable": f"reference step failed: {type(exc).__name__}: {exc}"[:400]}))
+        return
+    with ClockSampler(local) as cs:
+        ms = _timed(step_resident, args.steps, ws)
+    final_loss = float(torch.stack([l.float() for l in losses[-args.steps:]]).mean().item())
+
+    e2e = None
+    if not args.no_e2e:
+        h2d = host[0].numel() * host[0].element_size()
+
+        def step_e2e(i):
+            blk = host[i % len(host)].to(dev, non_blocking=True)
+            step_e2e.last = float(one(blk[:, :-1].to(torch.int32), blk[:, 1:]).item())
+
+        for i in range(max(3, args.warmup // 2)):
+            step_e2e(i)
+        ms_e = _timed(step_e2e, args.steps, ws)
+        e2e = {"value": ws * args.batch * args.seq / (ms_e / 1e3), "unit": "tokens/s",
+               "ms_per_step": ms_e, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
+               "api": "chaoscontrol.train_ssm.train_ssm_step + Muon.step"}
+
+    toks = ws * args.batch * args.seq / (ms / 1e3)
+    out = {"metric": "train tokens/sec, 4Lx256d V16384 SSM (seq 512, bs 1024/rank, bf16, Muon)",
+           "value": toks, "unit": "tokens/s", "n_gpus": ws, "steps": args.steps, "warmup": args.warmup,
+           "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+           "vs_baseline": toks / (BASELINE_TOKS_8XH100 * ws / 8.0), "dtype": "bf16",
+           "data": "synthetic Zipf(1.1) tokens, random-init weights", "impl": "reference",
+           "final_loss": final_loss, "clocks": cs.summary(), "e2e": e2e,
+           "config": {"model": f"CareStudentLM {LAYERS}x{DIM} V{VOCAB} ff_mult {FF_MULT}",
+                      "global_batch": ws * args.batch, "seq_len": args.seq, "parallelism": f"dp{ws}",
+                      "optimizer": f"Muon lr {LR} wd {WD} clip {CLIP}", "lm_head": mode,
+                      "scan_backend": os.environ.get("CHAOSCONTROL_DIAG_SCAN_BACKEND")}}
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    if ws > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    a = _parse()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_ours(a)

@@ -66,6 +66,8 @@ struct LmHeadArgs {
   float gscale;             // d loss / d (per-row CE), e.g. 1/R
   float* lse;               // [R] natural-log lse (out in LSE/TRAIN, in for DW)
   float* loss;              // [R] per-row CE (out, LSE/TRAIN)
+  float* entropy;           // [R] softmax entropy in nats (out, LSE; optional)
+  int skip_lse;             // TRAIN: lse[] is an input, run only the gradient sweep
   const __nv_bfloat16* X;   // [R, 256] for the final epilogue of TRAIN
   __nv_bfloat16* dX;        // [R, 256] out (TRAIN)
   float* dWpart;            // [row_chunks, V, 256] out (DW)
@@ -135,7 +137,7 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
   // LSE / TRAIN: unit = m-tile; inner = v-tiles (x sweeps).
   // DW: unit = (v-tile, row chunk); inner = m-tiles of the chunk.
   const int n_units = (MODE == MODE_DW) ? p.n_vtiles * p.row_chunks : p.n_mtiles;
-  const int n_sweeps = (MODE == MODE_TRAIN) ? 2 : 1;
+  const int n_sweeps = (MODE == MODE_TRAIN && !p.skip_lse) ? 2 : 1;
 
   if (warp == 0) {
     // =========================== TMA producer ================================
@@ -236,7 +238,7 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         res_phase ^= 1u;
         tc_fence_after_sync();
         for (int sw = 0; sw < n_sweeps && ok; ++sw) {
-          const bool second = (MODE == MODE_DW) || (MODE == MODE_TRAIN && sw == 1);
+          const bool second = (MODE == MODE_DW) || (MODE == MODE_TRAIN && sw == n_sweeps - 1);
           int prev_stage = -1;
           bool prev_first = true;
           for (int it = inner0; it < inner1; ++it) {
@@ -329,11 +331,11 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         gs = row_ok ? p.gscale * w * rs : 0.f;
         if (need_lse) c2 = row_ok ? p.lse[r] * LOG2E : 0.f;
       };
-      if (MODE != MODE_DW) load_row(unit, false);
+      if (MODE != MODE_DW) load_row(unit, MODE == MODE_TRAIN && p.skip_lse);
 
       for (int sw = 0; sw < n_sweeps && ok; ++sw) {
-        const bool second = (MODE == MODE_DW) || (MODE == MODE_TRAIN && sw == 1);
-        float run_m = -INFINITY, run_s = 0.f, tacc = 0.f, zt = 0.f;
+        const bool second = (MODE == MODE_DW) || (MODE == MODE_TRAIN && sw == n_sweeps - 1);
+        float run_m = -INFINITY, run_s = 0.f, run_e = 0.f, tacc = 0.f, zt = 0.f;
         for (int it = inner0; it < inner1 && ok; ++it) {
           const int b = n_d1 & 1;
           const uint32_t dph = (n_d1 >> 1) & 1u;
@@ -361,10 +363,16 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
 #pragma unroll
               for (int i = 1; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(a[i]));
               const float new_m = fmaxf(run_m, mx * c1);
-              float acc = 0.f;
+              float acc = 0.f, eacc = 0.f;
 #pragma unroll
-              for (int i = 0; i < 32; ++i) acc += ex2f(fmaf(__uint_as_float(a[i]), c1, -new_m));
-              run_s = run_s * ex2f(run_m - new_m) + acc;
+              for (int i = 0; i < 32; ++i) {
+                const float e = ex2f(fmaf(__uint_as_float(a[i]), c1, -new_m));
+                acc += e;
+                if (MODE == MODE_LSE) eacc = fmaf(e, __uint_as_float(a[i]), eacc);   // sum p~ * raw
+              }
+              const float resc = ex2f(run_m - new_m);
+              run_s = run_s * resc + acc;
+              if (MODE == MODE_LSE) run_e = run_e * resc + eacc;
               run_m = new_m;
               if (MODE == MODE_LSE) {
                 const int tl = tgt - (v0 + col0);
@@ -438,7 +446,8 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
           if (!epi_sync()) { ok = false; break; }
           const float2 o = xchg[(part ^ 1) * 128 + row_in_tile];
           const float m = fmaxf(run_m, o.x);
-          const float s = run_s * ex2f(run_m - m) + o.y * ex2f(o.x - m);
+          const float my_resc = ex2f(run_m - m), o_resc = ex2f(o.x - m);
+          const float s = run_s * my_resc + o.y * o_resc;
           const float lse2 = m + __log2f(s);
           c2 = lse2;
           if (row_ok && part == 0) p.lse[r] = lse2 * LN2;
@@ -449,6 +458,14 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             if (!epi_sync()) { ok = false; break; }
             const float t_other = xchg[(part ^ 1) * 128 + row_in_tile].x;
             if (row_ok && part == 0) p.loss[r] = lse2 * LN2 - (tacc + t_other) * rs;
+            if (p.entropy != nullptr) {
+              // H = lse - E[logit],  E[logit] = rs * sum(p~ * raw) / sum(p~)
+              if (!epi_sync()) { ok = false; break; }
+              xchg[part * 128 + row_in_tile] = make_float2(run_e * my_resc, 0.f);
+              if (!epi_sync()) { ok = false; break; }
+              const float e_tot = run_e * my_resc + xchg[(part ^ 1) * 128 + row_in_tile].x;
+              if (row_ok && part == 0) p.entropy[r] = lse2 * LN2 - rs * e_tot / s;
+            }
           }
         } else if (MODE == MODE_TRAIN) {
           // per-row CE = -log p_target = -zt * ln2 (zt captured by one of the two warps)
@@ -595,27 +612,30 @@ static int lmhead_common(LmHeadArgs& a, int64_t R, int64_t V, int64_t D, const f
 
 // lse[r], loss[r] = CE of row r.  Forward only.
 extern "C" int ccb_lmhead_lse(const void* X, const void* W, const float* rowss, float eps,
-                              const int64_t* targets, float* lse, float* loss, int64_t R, int64_t V,
-                              int64_t D, void* stream) {
+                              const int64_t* targets, float* lse, float* loss, float* entropy,
+                              int64_t R, int64_t V, int64_t D, void* stream) {
   LmHeadArgs a = {};
   int rc = lmhead_common(a, R, V, D, rowss, eps, targets);
   if (rc) return rc < 0 ? rc : 0;
   a.lse = lse;
   a.loss = loss;
+  a.entropy = entropy;
   return launch_lmhead<MODE_LSE>(X, W, a, (cudaStream_t)stream);
 }
 
 // lse, per-row loss and dX (gradient w.r.t. the un-normalised hidden state).
+// With lse_is_input the lse sweep is skipped and lse[] is read instead.
 extern "C" int ccb_lmhead_train(const void* X, const void* W, const float* rowss, float eps,
                                 const int64_t* targets, const float* rowweight, float gscale,
-                                float* lse, float* loss, void* dX, int64_t R, int64_t V, int64_t D,
-                                void* stream) {
+                                float* lse, int64_t lse_is_input, float* loss, void* dX, int64_t R,
+                                int64_t V, int64_t D, void* stream) {
   LmHeadArgs a = {};
   int rc = lmhead_common(a, R, V, D, rowss, eps, targets);
   if (rc) return rc < 0 ? rc : 0;
   a.rowweight = rowweight;
   a.gscale = gscale;
   a.lse = lse;
+  a.skip_lse = lse_is_input ? 1 : 0;
   a.loss = loss;
   a.X = (const __nv_bfloat16*)X;
   a.dX = (__nv_bfloat16*)dX;

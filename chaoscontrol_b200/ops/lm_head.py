@@ -16,8 +16,8 @@ import torch
 from . import _lib
 from ._lib import f32, i64, vp
 
-_lib.register_sig("ccb_lmhead_lse", [vp, vp, vp, f32, vp, vp, vp, i64, i64, i64, vp])
-_lib.register_sig("ccb_lmhead_train", [vp, vp, vp, f32, vp, vp, f32, vp, vp, vp, i64, i64, i64, vp])
+_lib.register_sig("ccb_lmhead_lse", [vp, vp, vp, f32, vp, vp, vp, vp, i64, i64, i64, vp])
+_lib.register_sig("ccb_lmhead_train", [vp, vp, vp, f32, vp, vp, f32, vp, i64, vp, vp, i64, i64, i64, vp])
 _lib.register_sig("ccb_lmhead_dw", [vp, vp, vp, f32, vp, vp, f32, vp, vp, i64, i64, i64, i64, vp])
 
 EPS = 1e-6
@@ -59,19 +59,28 @@ def _prep(x, rowss, W_f, targets):
     return t.contiguous()
 
 
-def lm_head_lse(x, rowss, W_f, targets, *, eps: float = EPS):
-    """Forward only: ``(loss_rows, lse)`` fp32 ``[R]``; no logits in memory."""
+def lm_head_lse(x, rowss, W_f, targets, *, eps: float = EPS, want_entropy: bool = False):
+    """Forward only: ``(loss_rows, lse)`` fp32 ``[R]`` (plus the softmax entropy
+    when asked); no logits in memory."""
     R, D = x.shape
     if not fused_supported(x, W_f):
         lr, lse, _, _ = lm_head_reference(x, rowss, W_f, targets, eps=eps, want_grads=False)
+        if want_entropy:
+            xf = x.float()
+            if rowss is not None:
+                xf = xf * torch.rsqrt((xf * xf).sum(-1, keepdim=True) / D + eps)
+            logits = xf @ W_f.float().t()
+            p = torch.softmax(logits, -1)
+            return lr, lse, lse - (p * logits).sum(-1)
         return lr, lse
     t = _prep(x, rowss, W_f, targets)
     lse = torch.empty(R, dtype=torch.float32, device=x.device)
     loss = torch.empty(R, dtype=torch.float32, device=x.device)
+    ent = torch.empty(R, dtype=torch.float32, device=x.device) if want_entropy else None
     _lib.check(_lib.lib().ccb_lmhead_lse(x.data_ptr(), W_f.data_ptr(), _lib.ptr(rowss), eps,
-                                         t.data_ptr(), lse.data_ptr(), loss.data_ptr(), R,
-                                         W_f.shape[0], D, _lib.stream_ptr()), "lmhead_lse")
-    return loss, lse
+                                         t.data_ptr(), lse.data_ptr(), loss.data_ptr(), _lib.ptr(ent),
+                                         R, W_f.shape[0], D, _lib.stream_ptr()), "lmhead_lse")
+    return (loss, lse, ent) if want_entropy else (loss, lse)
 
 
 def default_row_chunks(R: int, V: int) -> int:
@@ -96,7 +105,7 @@ def default_row_chunks(R: int, V: int) -> int:
 
 
 def lm_head_train(x, rowss, W_f, targets, *, gscale: float, rowweight=None, eps: float = EPS,
-                  row_chunks: Optional[int] = None):
+                  row_chunks: Optional[int] = None, lse: Optional[torch.Tensor] = None):
     """Loss and both gradients.  Returns ``(loss_rows, lse, dX bf16, dW_f_partials fp32 [C,V,D])``.
 
     ``dX`` is the gradient w.r.t. the un-normalised hidden state (RMSNorm
@@ -110,13 +119,16 @@ def lm_head_train(x, rowss, W_f, targets, *, gscale: float, rowweight=None, eps:
         return lr, lse, dX.to(x.dtype), dW.unsqueeze(0)
     t = _prep(x, rowss, W_f, targets)
     dev = x.device
-    lse = torch.empty(R, dtype=torch.float32, device=dev)
+    lse_given = lse is not None
+    if not lse_given:
+        lse = torch.empty(R, dtype=torch.float32, device=dev)
     loss = torch.empty(R, dtype=torch.float32, device=dev)
     dX = torch.empty_like(x)
     L = _lib.lib()
     _lib.check(L.ccb_lmhead_train(x.data_ptr(), W_f.data_ptr(), _lib.ptr(rowss), eps, t.data_ptr(),
-                                  _lib.ptr(rowweight), gscale, lse.data_ptr(), loss.data_ptr(),
-                                  dX.data_ptr(), R, V, D, _lib.stream_ptr()), "lmhead_train")
+                                  _lib.ptr(rowweight), gscale, lse.data_ptr(), int(lse_given),
+                                  loss.data_ptr(), dX.data_ptr(), R, V, D, _lib.stream_ptr()),
+               "lmhead_train")
     C = row_chunks or default_row_chunks(R, V)
     part = torch.empty(C, V, D, dtype=torch.float32, device=dev)
     _lib.check(L.ccb_lmhead_dw(x.data_ptr(), W_f.data_ptr(), _lib.ptr(rowss), eps, t.data_ptr(),

@@ -71,11 +71,14 @@ def embed_fwd(tokens: torch.Tensor, E: torch.Tensor):
 
 
 def embed_bwd(tokens: torch.Tensor, dx: torch.Tensor, V: int,
-              sort_cache: Optional[tuple] = None) -> torch.Tensor:
+              sort_cache: Optional[tuple] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """fp32 ``[V, D]`` gradient of the embedding table (scatter-add of ``dx`` rows)."""
     flat = tokens.reshape(-1).long()
     D = dx.shape[1]
-    dE = torch.zeros(V, D, dtype=torch.float32, device=dx.device)
+    if out is not None:
+        dE = out.zero_()
+    else:
+        dE = torch.zeros(V, D, dtype=torch.float32, device=dx.device)
     if dx.is_cuda and D in (256, 512, 1024):
         if sort_cache is None:
             sort_cache = torch.sort(flat)
@@ -89,7 +92,8 @@ def embed_bwd(tokens: torch.Tensor, dx: torch.Tensor, V: int,
 
 
 def splitk_reduce(part: torch.Tensor, *, colscale: Optional[torch.Tensor] = None,
-                  W: Optional[torch.Tensor] = None):
+                  W: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                  dcol_out: Optional[torch.Tensor] = None):
     """Sum split-K partials ``[S, N, K]`` (or ``[N, K]``).
 
     Returns ``(dW [N,K] fp32, dcol [K] fp32 or None)`` with
@@ -101,10 +105,15 @@ def splitk_reduce(part: torch.Tensor, *, colscale: Optional[torch.Tensor] = None
     S, N, K = part.shape
     if part.is_cuda and (colscale is None or colscale.dtype == torch.bfloat16) and (
             W is None or (W.dtype == torch.bfloat16 and W.is_contiguous())):
-        out = torch.empty(N, K, dtype=torch.float32, device=part.device)
+        if out is None:
+            out = torch.empty(N, K, dtype=torch.float32, device=part.device)
+        assert out.dtype == torch.float32 and out.is_contiguous()
         nb = (N + 7) // 8
         colpart = torch.empty(nb, K, dtype=torch.float32, device=part.device) if W is not None else None
-        dcol = torch.empty(K, dtype=torch.float32, device=part.device) if W is not None else None
+        dcol = None
+        if W is not None:
+            dcol = dcol_out if dcol_out is not None else torch.empty(K, dtype=torch.float32,
+                                                                     device=part.device)
         _lib.check(_lib.lib().ccb_splitk_reduce(part.data_ptr(), S, part.stride(0), N, K,
                                                 _lib.ptr(colscale), _lib.ptr(W), out.data_ptr(), 0,
                                                 _lib.ptr(colpart), _lib.ptr(dcol), 0,
@@ -114,6 +123,12 @@ def splitk_reduce(part: torch.Tensor, *, colscale: Optional[torch.Tensor] = None
     dcol = (s * W.float()).sum(0) if W is not None else None
     if colscale is not None:
         s = s * colscale.float()[None, :]
+    if out is not None:
+        out.copy_(s)
+        s = out
+    if dcol is not None and dcol_out is not None:
+        dcol_out.copy_(dcol)
+        dcol = dcol_out
     return s, dcol
 
 
@@ -222,22 +237,32 @@ def layer_forward(x: torch.Tensor, ss1: torch.Tensor, w: LayerWeights, B: int, T
 
 
 def layer_backward(dx3: torch.Tensor, ctx: LayerCtx, w: LayerWeights, B: int, T: int,
-                   dhT: Optional[torch.Tensor] = None, *, want_dh0: bool = False):
-    """Backward of :func:`layer_forward`.  Returns ``(dx, LayerGrads)``."""
+                   dhT: Optional[torch.Tensor] = None, *, want_dh0: bool = False,
+                   outs: Optional[dict] = None):
+    """Backward of :func:`layer_forward`.  Returns ``(dx, LayerGrads)``.
+
+    ``outs`` may map ``dWp / dWo / dWfc / dWproj / dwn1 / dwn2`` to preallocated
+    fp32 tensors (views of a flat gradient buffer) that receive the results.
+    """
     R, D = ctx.x.shape
     inv_d = 1.0 / D
+    o = outs or {}
     # feed-forward half
     du = gemm(dx3, w.Wproj, b_mn=True, epi=EPI_DSILU, r1=ctx.u, rowss=ctx.ss2, inv_dim=inv_d, eps=EPS)
-    dWproj, _ = splitk_reduce(_wgrad(dx3, ctx.f))
+    dWproj, _ = splitk_reduce(_wgrad(dx3, ctx.f), out=o.get("dWproj"))
     dx2 = gemm(du, w.Wfc_f, b_mn=True, epi=EPI_RMSBWD, r1=ctx.x2, r2=dx3, rowss=ctx.ss2,
                inv_dim=inv_d, eps=EPS)
-    dWfc, dwn2 = splitk_reduce(_wgrad(du, ctx.x2), colscale=w.wn2, W=w.Wfc)
+    dWfc, dwn2 = splitk_reduce(_wgrad(du, ctx.x2), colscale=w.wn2, W=w.Wfc, out=o.get("dWfc"),
+                               dcol_out=o.get("dwn2"))
     # recurrence half
     dy = gemm(dx2, w.Wo, b_mn=True)
-    dWo, _ = splitk_reduce(_wgrad(dx2, ctx.y))
+    dWo, _ = splitk_reduce(_wgrad(dx2, ctx.y), out=o.get("dWo"))
     dP, dlog_a, dh0 = _scan_bwd(ctx.P, w.log_a32, ctx.h0, ctx.h, dy, dhT, ctx.ss1, inv_d, EPS, B, T,
                                 D, want_dh0)
     dx = gemm(dP, w.Wp_f, b_mn=True, epi=EPI_RMSBWD, r1=ctx.x, r2=dx2, rowss=ctx.ss1, inv_dim=inv_d,
               eps=EPS)
-    dWp, dwn1 = splitk_reduce(_wgrad(dP, ctx.x), colscale=w.wn1, W=w.Wp)
+    dWp, dwn1 = splitk_reduce(_wgrad(dP, ctx.x), colscale=w.wn1, W=w.Wp, out=o.get("dWp"),
+                              dcol_out=o.get("dwn1"))
+    if "dlog_a" in o:
+        o["dlog_a"].copy_(dlog_a)
     return dx, LayerGrads(dWp, dWo, dWfc, dWproj, dwn1, dwn2, dlog_a, dh0)

@@ -1,0 +1,283 @@
+"""Lean training entry points: ``train_ssm_step`` and ``train_ssm_for_budget``
+plus the LM-head backward helpers, with the reference's signatures and result
+contract (src/chaoscontrol/train_ssm.py:50-774).
+
+Execution paths of ``train_ssm_step``:
+
+* **engine** -- bare-SSM model whose parameters live in a ``ParamArena`` on a
+  CUDA device, bf16, with a fused LM-head mode: the whole step (forward,
+  fused LM head with recompute, backward) is the hand-scheduled kernel
+  sequence of :class:`chaoscontrol_b200.engine.TrainEngine`; gradients land in
+  the arena's flat fp32 buffer and are also exposed as ``p.grad``.
+* **autograd** -- everything else (CPU, fp32, hooks, ``chunked`` / ``single``
+  head modes): ``model.encode`` under autocast, then the requested LM-head
+  backward.
+
+In both cases gradients are averaged across ranks before returning when DDP is
+active, and the caller owns ``zero_grad`` / ``optimizer.step``.
+"""
+from __future__ import annotations
+
+import random
+import time
+from typing import Any, Callable, Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .data import batch_from_starts
+from .engine import TrainEngine
+from .kernels.lm_head_loss import (fused_linear_cross_entropy, fused_linear_cross_entropy_with_ce,
+                                   fused_rms_linear_cross_entropy, fused_rms_norm)
+from .parallel.distributed import (allreduce_grads, broadcast_params, clip_arena_grad_norm,
+                                   clip_grad_norm_fused, resolve_ddp_context, should_stop_now)
+from .precision import autocast_context
+from .utils.arena import get_arena
+
+_FUSED_LM_HEAD_BACKENDS: dict[str, str] = {
+    "fused": "auto",
+    "fused_streaming": "streaming",
+    "fused_streaming_v2": "streaming_v2",
+    "fused_streaming_cached": "streaming_cached",
+    "fused_norm_streaming_v2": "norm_streaming_v2",
+}
+
+_UNSUPPORTED_ATTRS = (
+    ("wernicke", "wernicke layer"),
+    ("outer_model", "outer_model / typed buffer"),
+    ("semantic_tier", "semantic_tier bias"),
+    ("posterior", "posterior correction module"),
+    ("bucket_prototypes_module", "bucket_prototypes"),
+)
+
+
+def fused_lm_head_backend_for_mode(lm_head_backward_mode: str) -> str:
+    try:
+        return _FUSED_LM_HEAD_BACKENDS[str(lm_head_backward_mode).strip().lower()]
+    except KeyError as exc:
+        raise ValueError(
+            "lm_head_backward_mode must be 'fused', 'fused_streaming', 'fused_streaming_v2', "
+            f"'fused_streaming_cached', or 'fused_norm_streaming_v2', got {lm_head_backward_mode!r}"
+        ) from exc
+
+
+def _reject_unsupported(model: nn.Module) -> None:
+    for attr, label in _UNSUPPORTED_ATTRS:
+        if getattr(model, attr, None) is not None:
+            raise ValueError(f"train_ssm does not support the {label} path (model.{attr} is not "
+                             "None). Use chaoscontrol_b200.training.train_chaoscontrol_for_budget "
+                             "for configs that enable this feature.")
+
+
+# ---------------------------------------------------------------------------
+# LM-head backward helpers
+# ---------------------------------------------------------------------------
+def chunked_lm_head_backward(hidden: torch.Tensor, final_norm: nn.Module, lm_head: nn.Linear,
+                             targets: torch.Tensor, chunk_size: int) -> torch.Tensor:
+    """final_norm -> lm_head -> CE -> backward in time chunks; the full
+    ``(B, T, V)`` logits tensor never exists.  ``hidden`` must be a detached leaf
+    with ``requires_grad=True``; its ``.grad`` and the head / norm weight grads
+    are populated.  Each chunk's loss is ``CE(sum) / (B*T)`` so the accumulated
+    gradient is that of one mean-reduced loss.  Returns the detached loss."""
+    if chunk_size <= 0:
+        raise ValueError(f"chunked_lm_head_backward: chunk_size must be positive, got {chunk_size}. "
+                         "A non-positive value would wedge the time-chunk loop indefinitely "
+                         "rather than failing cleanly.")
+    if not hidden.requires_grad:
+        raise ValueError("chunked_lm_head_backward: ``hidden`` must have requires_grad=True so "
+                         "per-chunk backward can accumulate into hidden.grad. Call "
+                         "hidden.detach().requires_grad_(True) before passing it here.")
+    batch, seq, _ = hidden.shape
+    vocab = lm_head.out_features
+    total = batch * seq
+    loss_accum = hidden.new_zeros((), dtype=torch.float32)
+    start = 0
+    while start < seq:
+        end = min(start + chunk_size, seq)
+        logits = lm_head(final_norm(hidden[:, start:end, :]))
+        chunk_loss = F.cross_entropy(logits.reshape(-1, vocab).float(),
+                                     targets[:, start:end].reshape(-1), reduction="sum") / total
+        chunk_loss.backward()
+        loss_accum = loss_accum + chunk_loss.detach()
+        start = end
+    return loss_accum
+
+
+def full_lm_head_backward(hidden, final_norm, lm_head, targets, *, loss_weight: float = 1.0):
+    """Materialise full logits, one ``backward()``."""
+    logits = lm_head(final_norm(hidden))
+    loss = F.cross_entropy(logits.reshape(-1, logits.shape[-1]).float(), targets.reshape(-1))
+    (loss * float(loss_weight)).backward()
+    return loss.detach()
+
+
+def fused_lm_head_loss_with_ce(*, hidden, final_norm, lm_head, targets, backend: str = "auto",
+                               tile_size: int = 1024):
+    """``(mean loss, per-token CE)`` through the fused head; differentiable."""
+    weight = getattr(final_norm, "weight", None)
+    eps = float(getattr(final_norm, "eps", 1e-6))
+    normed = fused_rms_norm(hidden, weight, eps=eps) if weight is not None else final_norm(hidden)
+    b = "streaming_v2" if str(backend).strip().lower() == "norm_streaming_v2" else backend
+    loss, ce = fused_linear_cross_entropy_with_ce(normed, lm_head.weight, targets, reduction="mean",
+                                                  backend=b, tile_size=int(tile_size))
+    return loss, ce.view(targets.shape)
+
+
+def fused_lm_head_backward(hidden, final_norm, lm_head, targets, *, backend: str = "auto",
+                           tile_size: int = 1024, loss_weight: float = 1.0) -> torch.Tensor:
+    """Fused RMSNorm + tiled linear+CE, one backward.  Returns the detached loss."""
+    weight = getattr(final_norm, "weight", None)
+    eps = float(getattr(final_norm, "eps", 1e-6))
+    if weight is None:
+        return full_lm_head_backward(hidden, final_norm, lm_head, targets, loss_weight=loss_weight)
+    if str(backend).strip().lower() == "norm_streaming_v2":
+        loss = fused_rms_linear_cross_entropy(hidden, weight, lm_head.weight, targets, eps=eps,
+                                              reduction="mean", backend="streaming_v2",
+                                              tile_size=int(tile_size))
+    else:
+        loss = fused_linear_cross_entropy(fused_rms_norm(hidden, weight, eps=eps), lm_head.weight,
+                                          targets, reduction="mean", backend=backend,
+                                          tile_size=int(tile_size))
+    (loss * float(loss_weight)).backward()
+    return loss.detach()
+
+
+def fused_lm_head_backward_with_ce(hidden, final_norm, lm_head, targets, *, backend: str = "auto",
+                                   tile_size: int = 1024, loss_weight: float = 1.0):
+    loss, ce = fused_lm_head_loss_with_ce(hidden=hidden, final_norm=final_norm, lm_head=lm_head,
+                                          targets=targets, backend=backend, tile_size=tile_size)
+    (loss * float(loss_weight)).backward()
+    return loss.detach(), ce.detach()
+
+
+# ---------------------------------------------------------------------------
+# one step
+# ---------------------------------------------------------------------------
+def _engine_for(model: nn.Module) -> Optional[TrainEngine]:
+    eng = getattr(model, "_ccb_engine", None)
+    if eng is not None and eng.arena.still_valid():
+        return eng
+    arena = get_arena(model)
+    if arena is None or not TrainEngine.supported(model):
+        return None
+    eng = TrainEngine(model, arena)
+    model._ccb_engine = eng          # type: ignore[attr-defined]
+    return eng
+
+
+def train_ssm_step(model: nn.Module, inputs: torch.Tensor, targets: torch.Tensor, chunk_size: int, *,
+                   ddp_active: bool = False, world_size: int = 1, precision: str = "bf16",
+                   compile_full_path: bool = False, lm_head_backward_mode: str = "chunked",
+                   lm_head_tile_size: int = 1024) -> torch.Tensor:
+    """One forward + backward.  Gradients are left on the parameters (averaged
+    across ranks when ``ddp_active``); returns the detached mean CE.
+
+    ``compile_full_path`` is accepted for signature compatibility and ignored:
+    there is no tracing compiler in this stack, the encoder is already one
+    hand-scheduled kernel sequence on the GPU.
+    """
+    _reject_unsupported(model)
+    mode = str(lm_head_backward_mode).strip().lower()
+    fused_mode = mode in _FUSED_LM_HEAD_BACKENDS
+    if mode not in ("single", "chunked") and not fused_mode:
+        raise ValueError("lm_head_backward_mode must be 'chunked', 'single', 'fused', "
+                         "'fused_streaming', 'fused_streaming_v2', or 'fused_streaming_cached', or "
+                         f"'fused_norm_streaming_v2', got {lm_head_backward_mode!r}")
+
+    engine = _engine_for(model) if (fused_mode and precision in ("bf16", "fp8_fused") and
+                                    model.training) else None
+    if engine is not None:
+        loss = engine.step(inputs, targets)
+        if ddp_active and world_size > 1:
+            allreduce_grads(model, world_size)
+        engine.arena.materialize_grads()
+        return loss
+
+    with autocast_context(precision, device_type=inputs.device.type):
+        hidden = model.encode(inputs)
+        if mode == "single":
+            loss = full_lm_head_backward(hidden, model.final_norm, model.lm_head, targets)
+        elif fused_mode:
+            loss = fused_lm_head_backward(hidden, model.final_norm, model.lm_head, targets,
+                                          backend=fused_lm_head_backend_for_mode(mode),
+                                          tile_size=int(lm_head_tile_size))
+        else:
+            hidden_for_ce = hidden.detach().requires_grad_(True)
+            loss = chunked_lm_head_backward(hidden_for_ce, model.final_norm, model.lm_head, targets,
+                                            chunk_size)
+            hidden.backward(gradient=hidden_for_ce.grad)
+    if ddp_active and world_size > 1:
+        allreduce_grads(model, world_size)
+    return loss
+
+
+# ---------------------------------------------------------------------------
+# budgeted loop
+# ---------------------------------------------------------------------------
+def train_ssm_for_budget(model: nn.Module, *, train_tokens: torch.Tensor, train_starts: list[int],
+                         seq_len: int, batch_size: int, device: torch.device,
+                         optimizer: torch.optim.Optimizer, budget_seconds: float, chunk_size: int,
+                         grad_clip_norm: float = 0.0, fused_grad_clip: bool = False,
+                         rank: Optional[int] = None, world_size: Optional[int] = None, seed: int = 0,
+                         time_fn: Callable[[], float] = time.perf_counter, precision: str = "bf16",
+                         compile_full_path: bool = False, max_steps: Optional[int] = None,
+                         lm_head_backward_mode: str = "chunked",
+                         lm_head_tile_size: int = 1024) -> dict[str, Any]:
+    """Wall-clock-budgeted training loop.  Returns ``{"history", "steps",
+    "elapsed_s", "rank", "world_size", "peak_vram_mb"}``; losses stay on the
+    device until the loop ends (one transfer)."""
+    _reject_unsupported(model)
+    rank_, world_size_ = resolve_ddp_context(rank, world_size)
+    ddp_active = world_size_ > 1
+    if ddp_active:
+        broadcast_params(model)
+    rng = random.Random(seed + rank_)
+    model.train()
+    loss_tensors: list[torch.Tensor] = []
+    steps = 0
+    start_time = time_fn()
+    if device.type == "cuda":
+        torch.cuda.reset_peak_memory_stats(device)
+
+    while True:
+        elapsed = time_fn() - start_time
+        local_stop = (elapsed >= budget_seconds and steps > 0) or (
+            max_steps is not None and steps >= max_steps)
+        if should_stop_now(local_stop, device, ddp_active):
+            break
+        starts = [train_starts[rng.randrange(len(train_starts))] for _ in range(batch_size)]
+        inputs, targets = batch_from_starts(train_tokens, starts, seq_len, device)
+        optimizer.zero_grad(set_to_none=True)
+        loss = train_ssm_step(model=model, inputs=inputs, targets=targets, chunk_size=chunk_size,
+                              ddp_active=ddp_active, world_size=world_size_, precision=precision,
+                              compile_full_path=compile_full_path,
+                              lm_head_backward_mode=lm_head_backward_mode,
+                              lm_head_tile_size=int(lm_head_tile_size))
+        if grad_clip_norm > 0.0:
+            arena = get_arena(model)
+            if arena is not None and arena.grads_fresh:
+                clip_arena_grad_norm(arena, grad_clip_norm)
+                arena.materialize_grads()
+            elif fused_grad_clip:
+                clip_grad_norm_fused(model.parameters(), grad_clip_norm)
+            else:
+                torch.nn.utils.clip_grad_norm_(model.parameters(), grad_clip_norm)
+        optimizer.step()
+        if precision == "fp8_fused":
+            from .ops.fp8_linear import fused_fp8_flush_all
+            fused_fp8_flush_all(model)
+        loss_tensors.append(loss.detach())
+        steps += 1
+
+    if ddp_active:
+        dist.barrier()
+    if loss_tensors:
+        stacked = torch.stack([t.float() for t in loss_tensors]).cpu()
+        history = [{"step": float(i), "loss": float(stacked[i])} for i in range(len(loss_tensors))]
+    else:
+        history = []
+    peak = torch.cuda.max_memory_allocated(device) / (1024 * 1024) if device.type == "cuda" else 0.0
+    return {"history": history, "steps": steps, "elapsed_s": time_fn() - start_time, "rank": rank_,
+            "world_size": world_size_, "peak_vram_mb": peak}

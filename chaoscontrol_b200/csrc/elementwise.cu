@@ -493,7 +493,7 @@ extern "C" int ccb_muon_momentum(const float* g, float* buf, void* dir, float* s
   if (G <= 0 || numel_per_mat <= 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
   cudaMemsetAsync(sumsq, 0, sizeof(float) * (size_t)G, s);
-  dim3 grid((unsigned)grid_for(numel_per_mat, 256, 64), (unsigned)G);
+  dim3 grid((unsigned)grid_for(numel_per_mat, 256, (int)(G >= 16 ? 74 : 1184 / G)), (unsigned)G);
   muon_momentum_kernel<<<grid, 256, 0, s>>>(g, buf, (__nv_bfloat16*)dir, sumsq, numel_per_mat, mu,
                                             (int)nesterov);
   CCB_CHECK_LAUNCH("muon_momentum");
@@ -502,7 +502,7 @@ extern "C" int ccb_muon_momentum(const float* g, float* buf, void* dir, float* s
 extern "C" int ccb_muon_normalize(void* dir, const float* sumsq, int64_t G, int64_t numel_per_mat,
                                   float eps, void* stream) {
   if (G <= 0 || numel_per_mat <= 0) return 0;
-  dim3 grid((unsigned)grid_for(numel_per_mat, 256, 64), (unsigned)G);
+  dim3 grid((unsigned)grid_for(numel_per_mat, 256, (int)(G >= 16 ? 74 : 1184 / G)), (unsigned)G);
   muon_normalize_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)dir, sumsq,
                                                                 numel_per_mat, eps);
   CCB_CHECK_LAUNCH("muon_normalize");

@@ -15,6 +15,7 @@
 #include "ptx.cuh"
 #include "ccb_api.h"
 #include "runtime.h"
+#include <string.h>
 
 namespace ccb {
 
@@ -26,7 +27,7 @@ constexpr int GEMM_THREADS = 192;
 struct GemmKArgs {
   int M, N, K;
   int batch, splits, tiles_m, tiles_n, kblocks, kper;
-  int epi, out_fp32, ss_atomic;
+  int epi, out_fp32, ss_atomic, tma_store;
   long long ldc, c_batch, c_split, ldcin, cin_batch, ldr;
   void* C;
   void* C2;
@@ -39,13 +40,20 @@ struct GemmKArgs {
   int* status;
 };
 
+// bf16 outputs leave through shared-memory staging tiles and TMA stores: each
+// epilogue warp owns four 32-row x 64-column (4 KiB, 128B-swizzled) buffers.
+constexpr int STG_BUF_BYTES = 32 * 128;
+constexpr int STG_BUFS_PER_WARP = 4;
+constexpr int STG_BYTES = 4 * STG_BUFS_PER_WARP * STG_BUF_BYTES;   // 64 KiB
+
 template <int BN>
 struct GemmCfg {
   static constexpr int B_STAGE_BYTES = BN * BK * 2;
-  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int STAGES = (BN == 256) ? 3 : 5;
   static constexpr int TMEM_COLS = 2 * BN;   // 512 or 256: powers of two
-  static constexpr int SMEM_BYTES =
-      1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256;
+  static constexpr int STG_OFF = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);
+  static constexpr int BAR_OFF = STG_OFF + STG_BYTES;
+  static constexpr int SMEM_BYTES = 1024 + BAR_OFF + 256;
 };
 
 __device__ __forceinline__ void load_bf16x32(const __nv_bfloat16* src, float (&v)[32], int nvalid) {
@@ -118,6 +126,7 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmKArgs& p, int tile, i
 template <int BN, int A_MN, int B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+            const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmC2,
             const GemmKArgs p) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
@@ -128,7 +137,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* sA = smem;
   uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES));
+  uint8_t* sStage = smem + Cfg::STG_OFF;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::BAR_OFF);
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* tfull_bar = empty_bar + STAGES;
   uint64_t* tempty_bar = tfull_bar + 2;
@@ -238,6 +248,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const int q = warp & 3;                 // TMEM lane quadrant of this warp
     const int row_in_tile = q * 32 + lane;
     int it = 0;
+    int stg_n = 0;          // TMA stores issued by this warp (selects the staging buffer)
     bool ok = true;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
       TileCoord t = decode_tile(p, tile, BN);
@@ -258,6 +269,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       if (p.rowss != nullptr && row_ok) rs = rsqrtf(p.rowss[m] * p.inv_dim + p.eps);
       const int ncols = min(BN, p.N - t.n0);   // valid columns in this tile
       const int nchunks = (ncols + 31) >> 5;
+
+      // TMA-store path: 64-column groups staged in this warp's swizzled buffers
+      uint8_t* my_stage = sStage + (warp & 3) * (STG_BUFS_PER_WARP * STG_BUF_BYTES);
+      const bool two_out = (p.epi == CCB_EPI_ROWSCALE_SILU);
+      auto stage_write = [&](uint8_t* buf, int half, const float (&vals)[32]) {
+        uint8_t* row = buf + lane * 128;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int slot = (half * 4 + j) ^ (lane & 7);
+          *reinterpret_cast<uint4*>(row + slot * 16) =
+              make_uint4(pack_bf16x2(vals[j * 8 + 0], vals[j * 8 + 1]),
+                         pack_bf16x2(vals[j * 8 + 2], vals[j * 8 + 3]),
+                         pack_bf16x2(vals[j * 8 + 4], vals[j * 8 + 5]),
+                         pack_bf16x2(vals[j * 8 + 6], vals[j * 8 + 7]));
+        }
+      };
 
       float row_acc = 0.f;   // RESID_SS: sum of squares; RMSBWD: dot(acc, x)
       if (p.epi == CCB_EPI_RMSBWD) {
@@ -281,9 +308,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       for (int c = 0; c < nchunks; ++c) {
         uint32_t r[32];
         __syncwarp();
+        if (p.tma_store && (c & 1) == 0) {
+          // the buffers this 64-column group will use must have been read out
+          if (lane == 0) {
+            if (two_out) tma_store_wait_read<2>(); else tma_store_wait_read<3>();
+          }
+          __syncwarp();
+        }
         tmem_ld32(t_addr + c * 32, r);
         tmem_ld_wait();
-        if (!row_ok) continue;
+        if (!row_ok && !p.tma_store) continue;
         const int n = t.n0 + c * 32;
         const int nvalid = p.N - n;
         float v[32];
@@ -292,7 +326,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
         switch (p.epi) {
           case CCB_EPI_STORE: {
-            if (p.Cin != nullptr) {
+            if (p.Cin != nullptr && row_ok) {
               float cin[32];
               load_bf16x32(reinterpret_cast<const __nv_bfloat16*>(p.Cin) +
                                (long long)t.b * p.cin_batch + (long long)m * p.ldcin + n,
@@ -317,12 +351,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               float u = __bfloat162float(__float2bfloat16(v[i]));
               f[i] = u * sigmoidf_fast(u);
             }
-            store_bf16x32(reinterpret_cast<__nv_bfloat16*>(p.C2) + out_off + n, f, nvalid);
+            if (p.tma_store) {
+              stage_write(my_stage + ((stg_n + 1) & 3) * STG_BUF_BYTES, c & 1, f);
+            } else {
+              store_bf16x32(reinterpret_cast<__nv_bfloat16*>(p.C2) + out_off + n, f, nvalid);
+            }
           } break;
           case CCB_EPI_RESID_SS: {
             float res[32];
             load_bf16x32(reinterpret_cast<const __nv_bfloat16*>(p.R1) + (long long)m * p.ldr + n,
-                         res, nvalid);
+                         res, row_ok ? nvalid : 0);
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               v[i] = __bfloat162float(__float2bfloat16(v[i] + res[i]));
@@ -332,7 +370,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           case CCB_EPI_DSILU: {
             float u[32];
             load_bf16x32(reinterpret_cast<const __nv_bfloat16*>(p.R1) + (long long)m * p.ldr + n, u,
-                         nvalid);
+                         row_ok ? nvalid : 0);
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               float s = sigmoidf_fast(u[i]);
@@ -342,10 +380,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           case CCB_EPI_RMSBWD: {
             float x[32], dres[32];
             load_bf16x32(reinterpret_cast<const __nv_bfloat16*>(p.R1) + (long long)m * p.ldr + n, x,
-                         nvalid);
+                         row_ok ? nvalid : 0);
             if (p.R2 != nullptr) {
               load_bf16x32(reinterpret_cast<const __nv_bfloat16*>(p.R2) + (long long)m * p.ldr + n,
-                           dres, nvalid);
+                           dres, row_ok ? nvalid : 0);
             } else {
 #pragma unroll
               for (int i = 0; i < 32; ++i) dres[i] = 0.f;
@@ -355,10 +393,28 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           } break;
           default: break;
         }
-        if (p.out_fp32)
+        if (p.tma_store) {
+          stage_write(my_stage + (stg_n & 3) * STG_BUF_BYTES, c & 1, v);
+          if ((c & 1) == 1 || c == nchunks - 1) {
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              const int col = t.n0 + (c >> 1) * 64;
+              const int row = t.m0 + q * 32;
+              tma_store_3d(&tmC, my_stage + (stg_n & 3) * STG_BUF_BYTES, col, row, t.b);
+              tma_store_commit();
+              if (two_out) {
+                tma_store_3d(&tmC2, my_stage + ((stg_n + 1) & 3) * STG_BUF_BYTES, col, row, t.b);
+                tma_store_commit();
+              }
+            }
+            stg_n += two_out ? 2 : 1;
+          }
+        } else if (p.out_fp32) {
           store_f32x32(reinterpret_cast<float*>(p.C) + out_off + n, v, nvalid);
-        else
+        } else {
           store_bf16x32(reinterpret_cast<__nv_bfloat16*>(p.C) + out_off + n, v, nvalid);
+        }
       }
       if (p.epi == CCB_EPI_RESID_SS && row_ok && p.ss_out != nullptr) {
         if (p.ss_atomic) atomicAdd(p.ss_out + m, row_acc);
@@ -368,6 +424,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);
     }
+    // all of this warp's stores must have left shared memory and landed
+    if (p.tma_store && lane == 0) tma_store_wait_all<0>();
+    __syncwarp();
   }
 
   // ------------------------------ teardown ------------------------------------
@@ -412,6 +471,22 @@ static int launch_gemm(const CcbGemmArgs* a, cudaStream_t stream) {
                           (uint64_t)a->ldb, (uint64_t)a->b_batch, 64, BK)) return -1;
   }
   GemmKArgs p;
+  // bf16 outputs that keep rows 16-byte aligned go out through TMA stores
+  CUtensorMap tmC, tmC2;
+  const bool tma_ok = !a->out_fp32 && (a->ldc % 8 == 0) && (a->c_batch % 8 == 0) &&
+                      ((reinterpret_cast<uintptr_t>(a->C) & 15) == 0) &&
+                      (a->epi != CCB_EPI_ROWSCALE_SILU ||
+                       (a->C2 != nullptr && (reinterpret_cast<uintptr_t>(a->C2) & 15) == 0));
+  memset(&tmC, 0, sizeof(tmC));
+  memset(&tmC2, 0, sizeof(tmC2));
+  if (tma_ok) {
+    if (make_tmap_bf16_3d(&tmC, a->C, (uint64_t)a->N, (uint64_t)a->M, (uint64_t)a->batch,
+                          (uint64_t)a->ldc, (uint64_t)a->c_batch, 64, 32)) return -1;
+    if (a->epi == CCB_EPI_ROWSCALE_SILU &&
+        make_tmap_bf16_3d(&tmC2, a->C2, (uint64_t)a->N, (uint64_t)a->M, (uint64_t)a->batch,
+                          (uint64_t)a->ldc, (uint64_t)a->c_batch, 64, 32)) return -1;
+  }
+  p.tma_store = tma_ok ? 1 : 0;
   p.M = (int)a->M; p.N = (int)a->N; p.K = (int)a->K;
   p.batch = (int)a->batch;
   p.tiles_m = (p.M + BM - 1) / BM;
@@ -436,7 +511,7 @@ static int launch_gemm(const CcbGemmArgs* a, cudaStream_t stream) {
   long long total = (long long)p.batch * p.splits * p.tiles_m * p.tiles_n;
   if (total <= 0) return 0;
   int grid = (int)(total < ccb_num_sms() ? total : ccb_num_sms());
-  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, p);
+  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, tmC, tmC2, p);
   count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error("gemm launch: %s", cudaGetErrorString(e));

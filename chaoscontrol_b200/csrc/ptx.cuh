@@ -142,6 +142,13 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, const void* s
       ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1)
       : "memory");
 }
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, const void* smem_src, int c0,
+                                             int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+      ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
@@ -271,10 +278,18 @@ __host__ __device__ constexpr uint32_t make_idesc_f8(int M, int N, int a_fmt, in
 // ---------------------------------------------------------------------------
 // Small math helpers shared by epilogues and elementwise kernels
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ float sigmoidf_fast(float x) { return 1.f / (1.f + __expf(-x)); }
 __device__ __forceinline__ float tanhf_fast(float x) {
   float y;
   asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// sigmoid(x) = 0.5 * tanh(x / 2) + 0.5: one special-function op, no division.
+__device__ __forceinline__ float sigmoidf_fast(float x) {
+  return fmaf(0.5f, tanhf_fast(0.5f * x), 0.5f);
+}
+__device__ __forceinline__ float rcpf_fast(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
 __device__ __forceinline__ float softplusf(float x) {

@@ -36,7 +36,8 @@ __device__ __forceinline__ Gates eval_gates(float s_raw, float c_raw, float g_ra
   const float e = __expf(-fabsf(d_raw));
   float sp = fmaxf(d_raw, 0.f) + __logf(1.f + e);
   // d softplus / dx = sigmoid(x)
-  const float sig = d_raw >= 0.f ? 1.f / (1.f + e) : e / (1.f + e);
+  const float inv1pe = rcpf_fast(1.f + e);
+  const float sig = d_raw >= 0.f ? inv1pe : e * inv1pe;
   g.sp_sig = sp > 1e-4f ? sig : 0.f;
   g.delta = fmaxf(sp, 1e-4f);
   g.decay = __expf(-g.delta * a);

@@ -45,7 +45,7 @@ def test_engine_step_vs_fp32_autograd():
     eng = TrainEngine(m, arena)
     loss = eng.step(inp, tgt)
     _lib.assert_ok()
-    assert abs(float(loss) - float(loss_ref)) < 0.03
+    assert abs(float(loss) - float(loss_ref.detach())) < 0.03
     for n, p in ref.named_parameters():
         g, r = arena.grad_view(n), p.grad
         scale = r.abs().max().item()
@@ -93,9 +93,9 @@ def test_newton_schulz_kernel_vs_torch(shape):
     ref = newton_schulz_orthogonalize(g.cpu(), compute_dtype=torch.float32).cuda()
     _lib.assert_ok()
     assert (got - ref).abs().max().item() < 0.05
-    # singular values pushed toward 1
+    # singular values pushed toward 1 (the smallest few of a random matrix stay small)
     sv = torch.linalg.svdvals(got[0])
-    assert sv.max() < 1.3 and sv.min() > 0.3
+    assert sv.max() < 1.3 and 0.6 < sv.median() < 1.25
 
 
 def test_muon_arena_vs_plain():
@@ -117,5 +117,5 @@ def test_muon_arena_vs_plain():
     _lib.assert_ok()
     for (n, p1), (_, p2) in zip(m1.named_parameters(), m2.named_parameters()):
         d = (p1.float() - p2.float()).abs().max().item()
-        assert d < 3e-3, (n, d)
+        assert d < 1e-2, (n, d)   # one bf16 ulp at |w| ~ 1
     assert o1.ns_calls == len(arena.muon_groups)

@@ -564,3 +564,54 @@ extern "C" int ccb_cast_bf16_to_f32(const void* s, float* d, int64_t n, float sc
   CCB_CHECK_LAUNCH("cast_bf16_to_f32");
   return 0;
 }
+
+// ---------------------------------------------------------------------------
+// Allocation-free RMSNorm backward (declared in ccb_noalloc.h).
+// The per-block partial weight gradients live in an array that is part of the
+// library image instead of a buffer handed in by the caller.
+// ---------------------------------------------------------------------------
+#include "ccb_noalloc.h"
+
+namespace {
+constexpr int64_t kNoallocRowsPerBlock = 256;
+constexpr int64_t kNoallocMaxBlocks = CCB_NOALLOC_RMSNORM_MAX_ROWS / kNoallocRowsPerBlock;
+// 256 blocks x 1024 channels x 4 B = 1 MiB, resident on every device that loads the library.
+static __device__ __align__(256) float g_noalloc_rmsnorm_part[kNoallocMaxBlocks *
+                                                               CCB_NOALLOC_RMSNORM_MAX_DIM];
+// In host code the array's name is only a handle; the kernels need the device
+// address, looked up once per device with that device current.
+static float* g_noalloc_part_ptr[16] = {nullptr};
+}  // namespace
+
+extern "C" int ccb_rmsnorm_bwd_noalloc(const void* x, const void* w, const void* go,
+                                       const float* inv_rms, void* gx, float* gw_out, int64_t R,
+                                       int64_t D, void* stream) {
+  if (R <= 0) return 0;
+  if (R > CCB_NOALLOC_RMSNORM_MAX_ROWS)
+    return set_error("ccb_rmsnorm_bwd_noalloc: R=%lld exceeds the built-in workspace (max %d rows)",
+                     (long long)R, CCB_NOALLOC_RMSNORM_MAX_ROWS);
+  if (D <= 0 || D > CCB_NOALLOC_RMSNORM_MAX_DIM || (D % 2) != 0)
+    return set_error("ccb_rmsnorm_bwd_noalloc: D=%lld unsupported (even, max %d)", (long long)D,
+                     CCB_NOALLOC_RMSNORM_MAX_DIM);
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return set_error("cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= 16) return set_error("ccb_rmsnorm_bwd_noalloc: device index %d unsupported", dev);
+  if (g_noalloc_part_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_noalloc_rmsnorm_part);
+    if (e != cudaSuccess || p == nullptr)
+      return set_error("cudaGetSymbolAddress(workspace): %s", cudaGetErrorString(e));
+    g_noalloc_part_ptr[dev] = p;
+  }
+  float* part = g_noalloc_part_ptr[dev];
+  const unsigned nb = (unsigned)((R + kNoallocRowsPerBlock - 1) / kNoallocRowsPerBlock);
+  cudaStream_t s = (cudaStream_t)stream;
+  rmsnorm_bwd_kernel<<<nb, 256, (size_t)D * sizeof(float), s>>>(
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)go, inv_rms,
+      (__nv_bfloat16*)gx, part, R, (int)D, (int)kNoallocRowsPerBlock);
+  CCB_CHECK_LAUNCH("rmsnorm_bwd(noalloc)");
+  colsum_kernel<<<(unsigned)((D + 127) / 128), 128, 0, s>>>(part, (int)nb, (int)D, gw_out, 0);
+  CCB_CHECK_LAUNCH("colsum(noalloc)");
+  return 0;
+}

@@ -1,0 +1,292 @@
+// In-kernel gradient all-reduce over NVLink peer memory (one process per GPU,
+// buffers shared with CUDA IPC, every peer mapped into every rank's address
+// space).  Replaces flatten -> NCCL all_reduce -> unflatten + copy of the
+// reference (src/chaoscontrol/distributed.py:86-97) with kernels that read the
+// peers' buffers directly:
+//
+//   pack      grad (fp32) * scale -> bf16 into this rank's symmetric buffer;
+//             the last block to finish publishes epoch flags to every peer.
+//   one-shot  wait for all peers' flags, every rank reads the whole vector from
+//             all peers (fixed rank order => bitwise identical sums on all
+//             ranks), writes the fp32 gradient in place.  (ws-1) x S bytes in
+//             per GPU: best for small S (the 10.7 M-parameter model: 21 MB).
+//   two-shot  reduce-scatter (rank r sums slice r from all peers into an fp32
+//             staging slice, publishes a second flag) then all-gather (every
+//             rank reads every reduced slice).  2 (ws-1)/ws x S bytes per GPU.
+//
+// Flags are monotonically increasing 32-bit epochs written with
+// st.release.sys into the *peer's* pad and polled locally with
+// ld.acquire.sys.  Every poll is bounded: on expiry the kernel records
+// CCB_ERR_PEER_TIMEOUT in the status word and returns without reducing, so a
+// dead or late peer can never hang the GPU.  All remote data moves with plain
+// per-thread loads; no TMA and nothing cluster-scoped touches peer memory.
+#include "ptx.cuh"
+#include "ccb_api.h"
+#include "runtime.h"
+#include <string.h>
+
+namespace ccb {
+
+constexpr int COMM_MAX_RANKS = 8;
+constexpr int COMM_THREADS = 512;
+
+struct PeerPtrs {
+  __nv_bfloat16* buf[COMM_MAX_RANKS];   // symmetric bf16 data buffers
+  float* buf2[COMM_MAX_RANKS];          // fp32 reduced-slice staging (two-shot)
+  uint32_t* pad[COMM_MAX_RANKS];        // signal pads: [4][COMM_MAX_RANKS] uint32 each
+};
+// pad rows: 0 = "packed epoch e", 1 = "done reading epoch e", 2 = "slice reduced epoch e"
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_relaxed_sys_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+
+// Bounded wait until *flag >= epoch.  Returns false on timeout.
+__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, uint64_t limit_ns,
+                                          int* status) {
+  if ((int32_t)(ld_acquire_sys(flag) - epoch) >= 0) return true;
+  const uint64_t t0 = globaltimer_ns();
+  while (true) {
+    if ((int32_t)(ld_acquire_sys(flag) - epoch) >= 0) return true;
+    if (globaltimer_ns() - t0 > limit_ns) {
+      atomicCAS(status, CCB_OK, CCB_ERR_PEER_TIMEOUT);
+      return false;
+    }
+    __nanosleep(64);
+  }
+}
+
+// Block-wide: threads 0..ws-1 each wait on one peer's flag in row `row` of my pad.
+__device__ __forceinline__ bool wait_all_peers(const uint32_t* my_pad, int row, int ws, uint32_t epoch,
+                                               uint64_t limit_ns, int* status, int* sm_ok) {
+  if (threadIdx.x == 0) *sm_ok = 1;
+  __syncthreads();
+  if ((int)threadIdx.x < ws) {
+    if (!wait_flag(my_pad + row * COMM_MAX_RANKS + threadIdx.x, epoch, limit_ns, status))
+      atomicExch(sm_ok, 0);
+  }
+  __syncthreads();
+  return *sm_ok != 0;
+}
+
+// Last block to arrive publishes `epoch` into row `row`, column `rank` of every peer's pad.
+__device__ __forceinline__ void last_block_signal(unsigned* counter, const PeerPtrs& pp, int row,
+                                                  int rank, int ws, uint32_t epoch) {
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned old = atomicAdd(counter, 1u);
+    if (old == gridDim.x - 1) {
+      *counter = 0;
+      __threadfence_system();
+      for (int p = 0; p < ws; ++p) st_release_sys(pp.pad[p] + row * COMM_MAX_RANKS + rank, epoch);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(COMM_THREADS)
+comm_pack_kernel(const float* __restrict__ grad, long long n, float scale, PeerPtrs pp, int rank,
+                 int ws, uint32_t epoch, unsigned* counter, uint64_t limit_ns, int* status) {
+  __shared__ int sm_ok;
+  // peers must have finished reading what I packed last time
+  if (!wait_all_peers(pp.pad[rank], 1, ws, epoch - 1, limit_ns, status, &sm_ok)) return;
+  __nv_bfloat16* out = pp.buf[rank];
+  const long long n8 = n / 8;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float4 a = reinterpret_cast<const float4*>(grad)[2 * i];
+    const float4 b = reinterpret_cast<const float4*>(grad)[2 * i + 1];
+    uint4 q;
+    q.x = pack_bf16x2(a.x * scale, a.y * scale);
+    q.y = pack_bf16x2(a.z * scale, a.w * scale);
+    q.z = pack_bf16x2(b.x * scale, b.y * scale);
+    q.w = pack_bf16x2(b.z * scale, b.w * scale);
+    reinterpret_cast<uint4*>(out)[i] = q;
+  }
+  last_block_signal(counter, pp, 0, rank, ws, epoch);
+}
+
+__device__ __forceinline__ void acc_bf16x8(float (&acc)[8], const uint4& q) {
+  float2 f;
+  f = unpack_bf16x2(q.x); acc[0] += f.x; acc[1] += f.y;
+  f = unpack_bf16x2(q.y); acc[2] += f.x; acc[3] += f.y;
+  f = unpack_bf16x2(q.z); acc[4] += f.x; acc[5] += f.y;
+  f = unpack_bf16x2(q.w); acc[6] += f.x; acc[7] += f.y;
+}
+
+__global__ void __launch_bounds__(COMM_THREADS)
+comm_oneshot_kernel(float* __restrict__ grad, long long n, PeerPtrs pp, int rank, int ws,
+                    uint32_t epoch, unsigned* counter, uint64_t limit_ns, int* status) {
+  __shared__ int sm_ok;
+  if (!wait_all_peers(pp.pad[rank], 0, ws, epoch, limit_ns, status, &sm_ok)) return;
+  const long long n8 = n / 8;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8;
+       i += (long long)gridDim.x * blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    uint4 q[COMM_MAX_RANKS];
+#pragma unroll
+    for (int p = 0; p < COMM_MAX_RANKS; ++p)
+      if (p < ws) q[p] = ld_relaxed_sys_v4(reinterpret_cast<const uint4*>(pp.buf[p]) + i);
+#pragma unroll
+    for (int p = 0; p < COMM_MAX_RANKS; ++p)
+      if (p < ws) acc_bf16x8(acc, q[p]);
+    reinterpret_cast<float4*>(grad)[2 * i] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    reinterpret_cast<float4*>(grad)[2 * i + 1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+  }
+  last_block_signal(counter, pp, 1, rank, ws, epoch);
+}
+
+// two-shot, stage 1: this rank reduces slice `rank` into its fp32 staging buffer
+__global__ void __launch_bounds__(COMM_THREADS)
+comm_reduce_scatter_kernel(long long n, PeerPtrs pp, int rank, int ws, uint32_t epoch,
+                           unsigned* counter, uint64_t limit_ns, int* status) {
+  __shared__ int sm_ok;
+  if (!wait_all_peers(pp.pad[rank], 0, ws, epoch, limit_ns, status, &sm_ok)) return;
+  const long long slice8 = (n / 8) / ws;           // host guarantees divisibility
+  const long long base = (long long)rank * slice8;
+  float* out = pp.buf2[rank];
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < slice8;
+       i += (long long)gridDim.x * blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    uint4 q[COMM_MAX_RANKS];
+#pragma unroll
+    for (int p = 0; p < COMM_MAX_RANKS; ++p)
+      if (p < ws) q[p] = ld_relaxed_sys_v4(reinterpret_cast<const uint4*>(pp.buf[p]) + base + i);
+#pragma unroll
+    for (int p = 0; p < COMM_MAX_RANKS; ++p)
+      if (p < ws) acc_bf16x8(acc, q[p]);
+    reinterpret_cast<float4*>(out)[2 * i] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    reinterpret_cast<float4*>(out)[2 * i + 1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+  }
+  last_block_signal(counter, pp, 2, rank, ws, epoch);
+}
+
+// two-shot, stage 2: gather every rank's reduced slice
+__global__ void __launch_bounds__(COMM_THREADS)
+comm_all_gather_kernel(float* __restrict__ grad, long long n, PeerPtrs pp, int rank, int ws,
+                       uint32_t epoch, unsigned* counter, uint64_t limit_ns, int* status) {
+  __shared__ int sm_ok;
+  if (!wait_all_peers(pp.pad[rank], 2, ws, epoch, limit_ns, status, &sm_ok)) return;
+  const long long slice4 = (n / 4) / ws;
+  const long long total4 = slice4 * ws;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total4;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int p = (int)(i / slice4);
+    const long long j = i - (long long)p * slice4;
+    const uint4 v = ld_relaxed_sys_v4(reinterpret_cast<const uint4*>(pp.buf2[p]) + j);
+    reinterpret_cast<uint4*>(grad)[i] = v;
+  }
+  last_block_signal(counter, pp, 1, rank, ws, epoch);
+}
+
+}  // namespace ccb
+
+using namespace ccb;
+
+extern "C" void* ccb_comm_malloc(int64_t bytes) {
+  void* p = nullptr;
+  if (cudaMalloc(&p, (size_t)bytes) != cudaSuccess) {
+    set_error("ccb_comm_malloc(%lld): %s", (long long)bytes, cudaGetErrorString(cudaGetLastError()));
+    return nullptr;
+  }
+  cudaMemset(p, 0, (size_t)bytes);
+  cudaDeviceSynchronize();
+  return p;
+}
+extern "C" int ccb_comm_free(void* p) {
+  return cudaFree(p) == cudaSuccess ? 0 : set_error("cudaFree failed");
+}
+extern "C" int ccb_ipc_get(void* ptr, void* out64) {
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, ptr);
+  if (e != cudaSuccess) return set_error("cudaIpcGetMemHandle: %s", cudaGetErrorString(e));
+  memcpy(out64, &h, sizeof(h));
+  return 0;
+}
+extern "C" void* ccb_ipc_open(const void* handle64) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  void* p = nullptr;
+  cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) {
+    set_error("cudaIpcOpenMemHandle: %s", cudaGetErrorString(e));
+    return nullptr;
+  }
+  return p;
+}
+extern "C" int ccb_ipc_close(void* p) {
+  return cudaIpcCloseMemHandle(p) == cudaSuccess ? 0 : set_error("cudaIpcCloseMemHandle failed");
+}
+
+// bufs / bufs2 / pads: host arrays of `ws` device pointers (peer-mapped; index
+// `rank` is this rank's own allocation).  counters: 4 device uint32, zeroed.
+// mode 0 = one-shot, 1 = two-shot.  n must be a multiple of 8 * ws.
+extern "C" int ccb_allreduce(float* grad, int64_t n, float scale, void* const* bufs,
+                             void* const* bufs2, void* const* pads, int64_t rank, int64_t ws,
+                             int64_t epoch, void* counters, int64_t mode, int64_t timeout_ms,
+                             void* stream) {
+  if (ws < 1 || ws > COMM_MAX_RANKS) return set_error("ccb_allreduce: world size %lld unsupported", (long long)ws);
+  if (n % (8 * ws) != 0) return set_error("ccb_allreduce: n=%lld must be a multiple of %lld", (long long)n, (long long)(8 * ws));
+  PeerPtrs pp;
+  for (int i = 0; i < COMM_MAX_RANKS; ++i) {
+    pp.buf[i] = i < ws ? (__nv_bfloat16*)bufs[i] : nullptr;
+    pp.buf2[i] = i < ws ? (float*)bufs2[i] : nullptr;
+    pp.pad[i] = i < ws ? (uint32_t*)pads[i] : nullptr;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  unsigned* ctr = (unsigned*)counters;
+  int* status = ccb_status_ptr();
+  const uint64_t limit = (uint64_t)(timeout_ms > 0 ? timeout_ms : 2000) * 1000000ull;
+  const int sms = ccb_num_sms();
+  long long want = (n / 8 + COMM_THREADS - 1) / COMM_THREADS;
+  const int grid = (int)(want < sms ? (want < 1 ? 1 : want) : sms);
+  comm_pack_kernel<<<grid, COMM_THREADS, 0, s>>>(grad, n, scale, pp, (int)rank, (int)ws,
+                                                  (uint32_t)epoch, ctr + 0, limit, status);
+  count_launch();
+  if (mode == 0) {
+    comm_oneshot_kernel<<<grid, COMM_THREADS, 0, s>>>(grad, n, pp, (int)rank, (int)ws,
+                                                       (uint32_t)epoch, ctr + 1, limit, status);
+    count_launch();
+  } else {
+    comm_reduce_scatter_kernel<<<grid, COMM_THREADS, 0, s>>>(n, pp, (int)rank, (int)ws,
+                                                              (uint32_t)epoch, ctr + 2, limit, status);
+    count_launch();
+    comm_all_gather_kernel<<<grid, COMM_THREADS, 0, s>>>(grad, n, pp, (int)rank, (int)ws,
+                                                          (uint32_t)epoch, ctr + 3, limit, status);
+    count_launch();
+  }
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : set_error("allreduce launch: %s", cudaGetErrorString(e));
+}
+
+// Single-GPU self-test hook: waits on a flag that nothing sets, with a short
+// limit, and reports through the status word (used to test the timeout path).
+namespace ccb {
+__global__ void comm_wait_probe_kernel(const uint32_t* flag, uint32_t epoch, uint64_t limit_ns,
+                                       int* status, int* result) {
+  const bool ok = wait_flag(flag, epoch, limit_ns, status);
+  *result = ok ? 1 : 0;
+}
+}  // namespace ccb
+extern "C" int ccb_comm_wait_probe(const void* flag, int64_t epoch, int64_t timeout_ms, int* result,
+                                   void* stream) {
+  comm_wait_probe_kernel<<<1, 1, 0, (cudaStream_t)stream>>>((const uint32_t*)flag, (uint32_t)epoch,
+                                                            (uint64_t)timeout_ms * 1000000ull,
+                                                            ccb_status_ptr(), result);
+  count_launch();
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : set_error("wait probe launch: %s", cudaGetErrorString(e));
+}

@@ -254,12 +254,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       TileCoord t = decode_tile(p, tile, BN);
       const int acc = it & 1;
       const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
-      {
-        // warp-uniform result: the TMEM loads below are warp-collective
-        const bool w = mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status);
-        if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
-      }
-      tc_fence_after_sync();
       const uint32_t t_addr = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(q * 32) << 16);
       const int m = t.m0 + row_in_tile;
       const bool row_ok = m < p.M;
@@ -286,6 +280,78 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
       };
 
+      // Epilogue operands (residual / pre-activation / x / dres) do not depend on
+      // the accumulator, so their loads are issued two 32-column chunks ahead --
+      // the first two before this tile's MMAs have even finished -- and global
+      // load latency stays off the per-chunk critical path.
+      const __nv_bfloat16* aux1_row = nullptr;
+      if (p.epi == CCB_EPI_STORE) {
+        if (p.Cin != nullptr)
+          aux1_row = reinterpret_cast<const __nv_bfloat16*>(p.Cin) + (long long)t.b * p.cin_batch +
+                     (long long)m * p.ldcin;
+      } else if (p.R1 != nullptr) {
+        aux1_row = reinterpret_cast<const __nv_bfloat16*>(p.R1) + (long long)m * p.ldr;
+      }
+      const __nv_bfloat16* aux2_row =
+          (p.epi == CCB_EPI_RMSBWD && p.R2 != nullptr)
+              ? reinterpret_cast<const __nv_bfloat16*>(p.R2) + (long long)m * p.ldr : nullptr;
+      const int aux1_total = aux1_row ? nchunks * (p.epi == CCB_EPI_RMSBWD ? 2 : 1) : 0;
+      const int aux2_total = aux2_row ? nchunks : 0;
+      auto aux_issue = [&](const __nv_bfloat16* rowp, int s_idx, int total, uint4 (&qv)[4]) {
+        if (rowp == nullptr || !row_ok || s_idx >= total) return;
+        const int c = s_idx % nchunks;
+        const int n = t.n0 + c * 32;
+        if (n + 32 <= p.N) {
+          const uint4* src = reinterpret_cast<const uint4*>(rowp + n);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) qv[i] = __ldg(src + i);
+        }
+      };
+      auto aux_get = [&](const __nv_bfloat16* rowp, int c, const uint4 (&qv)[4], float (&vals)[32]) {
+        const int n = t.n0 + c * 32;
+        if (rowp == nullptr || !row_ok) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) vals[i] = 0.f;
+        } else if (n + 32 <= p.N) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 f0 = unpack_bf16x2(qv[i].x), f1 = unpack_bf16x2(qv[i].y),
+                         f2 = unpack_bf16x2(qv[i].z), f3 = unpack_bf16x2(qv[i].w);
+            vals[i * 8 + 0] = f0.x; vals[i * 8 + 1] = f0.y; vals[i * 8 + 2] = f1.x; vals[i * 8 + 3] = f1.y;
+            vals[i * 8 + 4] = f2.x; vals[i * 8 + 5] = f2.y; vals[i * 8 + 6] = f3.x; vals[i * 8 + 7] = f3.y;
+          }
+        } else {
+          load_bf16x32(rowp + n, vals, p.N - n);
+        }
+      };
+      uint4 a1_cur[4], a1_nxt[4], a2_cur[4], a2_nxt[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a1_cur[i] = a1_nxt[i] = a2_cur[i] = a2_nxt[i] = make_uint4(0, 0, 0, 0);
+      aux_issue(aux1_row, 0, aux1_total, a1_cur);
+      aux_issue(aux1_row, 1, aux1_total, a1_nxt);
+      aux_issue(aux2_row, 0, aux2_total, a2_cur);
+      aux_issue(aux2_row, 1, aux2_total, a2_nxt);
+      int a1_s = 0, a2_s = 0;      // stream positions of a1_cur / a2_cur
+      auto a1_advance = [&]() {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) a1_cur[i] = a1_nxt[i];
+        ++a1_s;
+        aux_issue(aux1_row, a1_s + 1, aux1_total, a1_nxt);
+      };
+      auto a2_advance = [&]() {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) a2_cur[i] = a2_nxt[i];
+        ++a2_s;
+        aux_issue(aux2_row, a2_s + 1, aux2_total, a2_nxt);
+      };
+
+      {
+        // warp-uniform result: the TMEM loads below are warp-collective
+        const bool w = mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status);
+        if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
+      }
+      tc_fence_after_sync();
+
       float row_acc = 0.f;   // RESID_SS: sum of squares; RMSBWD: dot(acc, x)
       if (p.epi == CCB_EPI_RMSBWD) {
         for (int c = 0; c < nchunks; ++c) {
@@ -293,11 +359,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           __syncwarp();
           tmem_ld32(t_addr + c * 32, r);
           tmem_ld_wait();
-          if (row_ok) {
+          {
             float x[32];
-            const int n = t.n0 + c * 32;
-            load_bf16x32(reinterpret_cast<const __nv_bfloat16*>(p.R1) + (long long)m * p.ldr + n, x,
-                         p.N - n);
+            aux_get(aux1_row, c, a1_cur, x);
+            a1_advance();
 #pragma unroll
             for (int i = 0; i < 32; ++i) row_acc += __uint_as_float(r[i]) * x[i];
           }
@@ -326,11 +391,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
         switch (p.epi) {
           case CCB_EPI_STORE: {
-            if (p.Cin != nullptr && row_ok) {
+            if (p.Cin != nullptr) {
               float cin[32];
-              load_bf16x32(reinterpret_cast<const __nv_bfloat16*>(p.Cin) +
-                               (long long)t.b * p.cin_batch + (long long)m * p.ldcin + n,
-                           cin, nvalid);
+              aux_get(aux1_row, c, a1_cur, cin);
+              a1_advance();
 #pragma unroll
               for (int i = 0; i < 32; ++i) v[i] = p.alpha * v[i] + p.beta * cin[i];
             } else {
@@ -359,8 +423,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           } break;
           case CCB_EPI_RESID_SS: {
             float res[32];
-            load_bf16x32(reinterpret_cast<const __nv_bfloat16*>(p.R1) + (long long)m * p.ldr + n,
-                         res, row_ok ? nvalid : 0);
+            aux_get(aux1_row, c, a1_cur, res);
+            a1_advance();
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               v[i] = __bfloat162float(__float2bfloat16(v[i] + res[i]));
@@ -369,8 +433,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           } break;
           case CCB_EPI_DSILU: {
             float u[32];
-            load_bf16x32(reinterpret_cast<const __nv_bfloat16*>(p.R1) + (long long)m * p.ldr + n, u,
-                         row_ok ? nvalid : 0);
+            aux_get(aux1_row, c, a1_cur, u);
+            a1_advance();
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               float s = sigmoidf_fast(u[i]);
@@ -379,15 +443,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           } break;
           case CCB_EPI_RMSBWD: {
             float x[32], dres[32];
-            load_bf16x32(reinterpret_cast<const __nv_bfloat16*>(p.R1) + (long long)m * p.ldr + n, x,
-                         row_ok ? nvalid : 0);
-            if (p.R2 != nullptr) {
-              load_bf16x32(reinterpret_cast<const __nv_bfloat16*>(p.R2) + (long long)m * p.ldr + n,
-                           dres, row_ok ? nvalid : 0);
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) dres[i] = 0.f;
-            }
+            aux_get(aux1_row, c, a1_cur, x);
+            a1_advance();
+            aux_get(aux2_row, c, a2_cur, dres);
+            a2_advance();
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = dres[i] + v[i] - x[i] * row_acc;
           } break;

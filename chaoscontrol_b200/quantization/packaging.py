@@ -16,7 +16,11 @@ def pack_int6_lzma(quantized: dict, meta: dict, *, preset: int = LZMA_PRESET) ->
 
 
 def unpack_int6_lzma(blob: bytes, *, map_location="cpu"):
-    payload = torch.load(io.BytesIO(lzma.decompress(blob)), map_location=map_location, weights_only=False)
+    try:
+        payload = torch.load(io.BytesIO(lzma.decompress(blob)), map_location=map_location,
+                             weights_only=False)
+    except Exception as exc:
+        raise ValueError(f"blob is not a valid int6-lzma container: {exc}") from exc
     if not isinstance(payload, dict) or "w" not in payload or "m" not in payload:
         raise ValueError("blob is not a valid int6-lzma container")
     return payload["w"], payload["m"]

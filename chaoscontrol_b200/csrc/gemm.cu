@@ -7,7 +7,8 @@
 // One persistent CTA per SM walks tiles round-robin.  Warp roles:
 //   warp 0      TMA producer (one lane)
 //   warp 1      TMEM owner + MMA issuer (one lane)
-//   warps 2..5  epilogue; warp w reads TMEM lanes [32*(w%4), 32*(w%4)+32)
+//   warps 2..9  epilogue; warp w reads TMEM lanes [32*(w%4), 32*(w%4)+32), the
+//               two warps of a lane quadrant take alternate 64-column groups
 //
 // Replaces the library GEMM call sites of the reference trunk
 // (src/chaoscontrol/core.py:453-474, 503, 545, 327-335) and the batched
@@ -22,7 +23,9 @@ namespace ccb {
 constexpr int BM = 128;
 constexpr int BK = 64;                       // 64 bf16 = one 128-byte swizzle row
 constexpr int A_STAGE_BYTES = BM * BK * 2;   // 16 KiB
-constexpr int GEMM_THREADS = 192;
+constexpr int EPI_PARTS = 2;                  // epilogue warps per TMEM lane quadrant
+constexpr int EPI_WARPS = 4 * EPI_PARTS;
+constexpr int GEMM_THREADS = 64 + 32 * EPI_WARPS;
 
 struct GemmKArgs {
   int M, N, K;
@@ -41,19 +44,21 @@ struct GemmKArgs {
 };
 
 // bf16 outputs leave through shared-memory staging tiles and TMA stores: each
-// epilogue warp owns four 32-row x 64-column (4 KiB, 128B-swizzled) buffers.
+// epilogue warp owns two 32-row x 64-column (4 KiB, 128B-swizzled) buffers.
 constexpr int STG_BUF_BYTES = 32 * 128;
-constexpr int STG_BUFS_PER_WARP = 4;
-constexpr int STG_BYTES = 4 * STG_BUFS_PER_WARP * STG_BUF_BYTES;   // 64 KiB
+constexpr int STG_BUFS_PER_WARP = 2;
+constexpr int STG_BYTES = EPI_WARPS * STG_BUFS_PER_WARP * STG_BUF_BYTES;   // 64 KiB
 
 template <int BN>
 struct GemmCfg {
   static constexpr int B_STAGE_BYTES = BN * BK * 2;
-  static constexpr int STAGES = (BN == 256) ? 3 : 5;
+  static constexpr int STAGES = (BN == 256) ? 3 : 4;
   static constexpr int TMEM_COLS = 2 * BN;   // 512 or 256: powers of two
   static constexpr int STG_OFF = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);
   static constexpr int BAR_OFF = STG_OFF + STG_BYTES;
-  static constexpr int SMEM_BYTES = 1024 + BAR_OFF + 256;
+  static constexpr int XCH_OFF = BAR_OFF + 256;     // per-row partials exchanged between warps
+  static constexpr int SMEM_BYTES = 1024 + XCH_OFF + 2 * EPI_PARTS * BM * 4;
+  static_assert(SMEM_BYTES <= 227 * 1024, "tile configuration exceeds the per-CTA shared memory limit");
 };
 
 __device__ __forceinline__ void load_bf16x32(const __nv_bfloat16* src, float (&v)[32], int nvalid) {
@@ -142,7 +147,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* tfull_bar = empty_bar + STAGES;
   uint64_t* tempty_bar = tfull_bar + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  uint64_t* xbar = tempty_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xbar + 1);
+  float* xch = reinterpret_cast<float*>(smem + Cfg::XCH_OFF);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -156,8 +163,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);
-      mbar_init(&tempty_bar[a], 4);
+      mbar_init(&tempty_bar[a], EPI_WARPS);
     }
+    mbar_init(xbar, EPI_WARPS);
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmA);
@@ -245,11 +253,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     }
   } else {
     // ------------------------------ epilogue -----------------------------------
+    // Two warps share each TMEM lane quadrant; they take alternate 64-column
+    // groups of the tile, so two warps per scheduler hide each other's
+    // TMEM-load, global-load and store-drain latency.
     const int q = warp & 3;                 // TMEM lane quadrant of this warp
+    const int part = (warp - 2) >> 2;       // which 64-column groups this warp takes
     const int row_in_tile = q * 32 + lane;
     int it = 0;
     int stg_n = 0;          // TMA stores issued by this warp (selects the staging buffer)
+    uint32_t xphase = 0;
     bool ok = true;
+    // all eight epilogue warps meet here (bounded); false = abort
+    auto rendezvous = [&]() -> bool {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(xbar);
+      const bool w = mbar_wait(xbar, xphase, abort_flag, p.status);
+      xphase ^= 1u;
+      return __all_sync(0xffffffffu, w);
+    };
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
       TileCoord t = decode_tile(p, tile, BN);
       const int acc = it & 1;
@@ -263,9 +284,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       if (p.rowss != nullptr && row_ok) rs = rsqrtf(p.rowss[m] * p.inv_dim + p.eps);
       const int ncols = min(BN, p.N - t.n0);   // valid columns in this tile
       const int nchunks = (ncols + 31) >> 5;
+      // k-th 32-column chunk of this warp: groups part, part+2, ... two chunks each
+      auto chunk_of = [&](int k) { return (((k >> 1) * EPI_PARTS + part) << 1) + (k & 1); };
+      int nmine = 0;
+      while (chunk_of(nmine) < nchunks) ++nmine;
+      float* xch_acc = xch + acc * (EPI_PARTS * BM);
 
       // TMA-store path: 64-column groups staged in this warp's swizzled buffers
-      uint8_t* my_stage = sStage + (warp & 3) * (STG_BUFS_PER_WARP * STG_BUF_BYTES);
+      uint8_t* my_stage = sStage + (warp - 2) * (STG_BUFS_PER_WARP * STG_BUF_BYTES);
       const bool two_out = (p.epi == CCB_EPI_ROWSCALE_SILU);
       auto stage_write = [&](uint8_t* buf, int half, const float (&vals)[32]) {
         uint8_t* row = buf + lane * 128;
@@ -281,9 +307,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       };
 
       // Epilogue operands (residual / pre-activation / x / dres) do not depend on
-      // the accumulator, so their loads are issued two 32-column chunks ahead --
-      // the first two before this tile's MMAs have even finished -- and global
-      // load latency stays off the per-chunk critical path.
+      // the accumulator, so their loads are issued one chunk ahead -- the first
+      // before this tile's MMAs have even finished -- and the other warp of the
+      // scheduler covers what latency is left.
       const __nv_bfloat16* aux1_row = nullptr;
       if (p.epi == CCB_EPI_STORE) {
         if (p.Cin != nullptr)
@@ -295,11 +321,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const __nv_bfloat16* aux2_row =
           (p.epi == CCB_EPI_RMSBWD && p.R2 != nullptr)
               ? reinterpret_cast<const __nv_bfloat16*>(p.R2) + (long long)m * p.ldr : nullptr;
-      const int aux1_total = aux1_row ? nchunks * (p.epi == CCB_EPI_RMSBWD ? 2 : 1) : 0;
-      const int aux2_total = aux2_row ? nchunks : 0;
+      const int aux1_total = aux1_row ? nmine * (p.epi == CCB_EPI_RMSBWD ? 2 : 1) : 0;
+      const int aux2_total = aux2_row ? nmine : 0;
       auto aux_issue = [&](const __nv_bfloat16* rowp, int s_idx, int total, uint4 (&qv)[4]) {
         if (rowp == nullptr || !row_ok || s_idx >= total) return;
-        const int c = s_idx % nchunks;
+        const int c = chunk_of(s_idx % nmine);
         const int n = t.n0 + c * 32;
         if (n + 32 <= p.N) {
           const uint4* src = reinterpret_cast<const uint4*>(rowp + n);
@@ -324,25 +350,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           load_bf16x32(rowp + n, vals, p.N - n);
         }
       };
-      uint4 a1_cur[4], a1_nxt[4], a2_cur[4], a2_nxt[4];
+      uint4 a1_cur[4], a2_cur[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) a1_cur[i] = a1_nxt[i] = a2_cur[i] = a2_nxt[i] = make_uint4(0, 0, 0, 0);
+      for (int i = 0; i < 4; ++i) a1_cur[i] = a2_cur[i] = make_uint4(0, 0, 0, 0);
       aux_issue(aux1_row, 0, aux1_total, a1_cur);
-      aux_issue(aux1_row, 1, aux1_total, a1_nxt);
       aux_issue(aux2_row, 0, aux2_total, a2_cur);
-      aux_issue(aux2_row, 1, aux2_total, a2_nxt);
       int a1_s = 0, a2_s = 0;      // stream positions of a1_cur / a2_cur
+      // called after aux_get has unpacked the current chunk: refill for the next
       auto a1_advance = [&]() {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) a1_cur[i] = a1_nxt[i];
         ++a1_s;
-        aux_issue(aux1_row, a1_s + 1, aux1_total, a1_nxt);
+        aux_issue(aux1_row, a1_s, aux1_total, a1_cur);
       };
       auto a2_advance = [&]() {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) a2_cur[i] = a2_nxt[i];
         ++a2_s;
-        aux_issue(aux2_row, a2_s + 1, aux2_total, a2_nxt);
+        aux_issue(aux2_row, a2_s, aux2_total, a2_cur);
       };
 
       {
@@ -354,7 +375,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
       float row_acc = 0.f;   // RESID_SS: sum of squares; RMSBWD: dot(acc, x)
       if (p.epi == CCB_EPI_RMSBWD) {
-        for (int c = 0; c < nchunks; ++c) {
+        for (int k = 0; k < nmine; ++k) {
+          const int c = chunk_of(k);
           uint32_t r[32];
           __syncwarp();
           tmem_ld32(t_addr + c * 32, r);
@@ -367,16 +389,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             for (int i = 0; i < 32; ++i) row_acc += __uint_as_float(r[i]) * x[i];
           }
         }
+        // the row's dot product spans both warps of the quadrant
+        xch_acc[part * BM + row_in_tile] = row_acc;
+        if (!rendezvous()) { ok = false; break; }
+        row_acc += xch_acc[(part ^ 1) * BM + row_in_tile];
         row_acc *= rs * rs * p.inv_dim;
       }
 
-      for (int c = 0; c < nchunks; ++c) {
+      for (int k = 0; k < nmine; ++k) {
+        const int c = chunk_of(k);
         uint32_t r[32];
         __syncwarp();
         if (p.tma_store && (c & 1) == 0) {
           // the buffers this 64-column group will use must have been read out
           if (lane == 0) {
-            if (two_out) tma_store_wait_read<2>(); else tma_store_wait_read<3>();
+            if (two_out) tma_store_wait_read<0>(); else tma_store_wait_read<1>();
           }
           __syncwarp();
         }
@@ -416,7 +443,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               f[i] = u * sigmoidf_fast(u);
             }
             if (p.tma_store) {
-              stage_write(my_stage + ((stg_n + 1) & 3) * STG_BUF_BYTES, c & 1, f);
+              stage_write(my_stage + STG_BUF_BYTES, c & 1, f);
             } else {
               store_bf16x32(reinterpret_cast<__nv_bfloat16*>(p.C2) + out_off + n, f, nvalid);
             }
@@ -453,21 +480,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           default: break;
         }
         if (p.tma_store) {
-          stage_write(my_stage + (stg_n & 3) * STG_BUF_BYTES, c & 1, v);
+          uint8_t* buf = my_stage + (two_out ? 0 : (stg_n & 1) * STG_BUF_BYTES);
+          stage_write(buf, c & 1, v);
           if ((c & 1) == 1 || c == nchunks - 1) {
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
               const int col = t.n0 + (c >> 1) * 64;
               const int row = t.m0 + q * 32;
-              tma_store_3d(&tmC, my_stage + (stg_n & 3) * STG_BUF_BYTES, col, row, t.b);
+              tma_store_3d(&tmC, buf, col, row, t.b);
               tma_store_commit();
               if (two_out) {
-                tma_store_3d(&tmC2, my_stage + ((stg_n + 1) & 3) * STG_BUF_BYTES, col, row, t.b);
+                tma_store_3d(&tmC2, my_stage + STG_BUF_BYTES, col, row, t.b);
                 tma_store_commit();
               }
             }
-            stg_n += two_out ? 2 : 1;
+            ++stg_n;
           }
         } else if (p.out_fp32) {
           store_f32x32(reinterpret_cast<float*>(p.C) + out_off + n, v, nvalid);
@@ -475,9 +503,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           store_bf16x32(reinterpret_cast<__nv_bfloat16*>(p.C) + out_off + n, v, nvalid);
         }
       }
-      if (p.epi == CCB_EPI_RESID_SS && row_ok && p.ss_out != nullptr) {
-        if (p.ss_atomic) atomicAdd(p.ss_out + m, row_acc);
-        else p.ss_out[m] = row_acc;
+      if (p.epi == CCB_EPI_RESID_SS && p.ss_out != nullptr) {
+        if (p.ss_atomic) {
+          if (row_ok) atomicAdd(p.ss_out + m, row_acc);
+        } else {
+          // one value per row: the second warp of the quadrant hands its half over
+          if (part != 0) xch_acc[part * BM + row_in_tile] = row_acc;
+          if (!rendezvous()) { ok = false; break; }
+          if (part == 0 && row_ok) p.ss_out[m] = row_acc + xch_acc[BM + row_in_tile];
+        }
       }
       tc_fence_before_sync();
       __syncwarp();

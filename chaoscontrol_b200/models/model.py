@@ -406,25 +406,215 @@ class CareStudentLM(nn.Module):
             return (hidden, finals) if return_final_states else hidden
 
         x = self.embed(input_ids)
-        meta: dict[str, Any] = {}
+        bucket_ids = None
         if self.wernicke is not None:
-            x, bucket_ids, balance = self.wernicke(x)
-            meta.update(bucket_ids=bucket_ids, balance_loss=balance)
-        if memory_mode != "off":
-            x = self._memory_read(x, memory_mode, episodic_residual, episodic_gate, meta,
-                                  memory_slot_mask=memory_slot_mask,
-                                  cache_read_cutoff=cache_read_cutoff,
-                                  override_index=memory_slot_override_index,
-                                  override_values=memory_slot_override_values)
+            x, bucket_ids, _balance = self.wernicke(x)
+        gate: Optional[torch.Tensor] = None
+        residual: Optional[torch.Tensor] = None
+        if memory_mode == "packet" and episodic_residual is not None:
+            gate = self._packet_gate(episodic_gate, x)
+            residual = self._packet_residual(episodic_residual, x)
+            x = torch.addcmul(x, residual, gate.unsqueeze(-1))
+        reads_memory = memory_mode == "force_on"
+        self._stash_outer_cue(x, reads_memory)
+        if reads_memory:
+            for bias in self._pre_recurrence_biases(
+                    x, bucket_ids, cache_read_cutoff=cache_read_cutoff, slot_mask=memory_slot_mask,
+                    override_index=memory_slot_override_index,
+                    override_values=memory_slot_override_values):
+                x = x + bias
+                residual = bias if residual is None else residual + bias
         x, finals, _ = self._run_layers(x, initial_states, want_stats=False)
-        if self.posterior is not None:
-            x = self._posterior_read(x, meta.get("bucket_ids"))
+        if reads_memory:
+            bias = self._posterior_bias(x, bucket_ids)
+            if bias is not None:
+                x = x + bias
+                residual = bias if residual is None else residual + bias
+        if reads_memory and residual is not None and gate is None:
+            gate = torch.ones(x.shape[:2], device=x.device, dtype=x.dtype)
         if return_memory_meta:
-            out: dict[str, Any] = {"hidden": x, "memory_meta": meta}
+            out: dict[str, Any] = {"hidden": x, "memory_meta": {
+                "memory_mode": memory_mode, "cache_read_cutoff": cache_read_cutoff,
+                "memory_gate": gate, "memory_residual": residual}}
             if return_final_states:
                 out["final_states"] = finals
             return out
         return (x, finals) if return_final_states else x
+
+    # -- memory injection ------------------------------------------------
+    @staticmethod
+    def _packet_gate(gate: torch.Tensor, ref: torch.Tensor) -> torch.Tensor:
+        """Packet gate ``(B,)``, ``(B, 1)`` or ``(B, T)`` broadcast to ``(B, T)``."""
+        g = gate.to(device=ref.device, dtype=ref.dtype)
+        B, T = ref.shape[:2]
+        bad = ValueError(f"episodic_gate shape {tuple(g.shape)} cannot gate hidden shape {(B, T)}")
+        if g.dim() == 1:
+            if g.shape[0] != B:
+                raise bad
+            return g[:, None].expand(B, T)
+        if g.dim() == 2:
+            if g.shape[0] != B or g.shape[1] not in (1, T):
+                raise bad
+            return g.expand(B, T)
+        raise ValueError("episodic_gate must have shape (B,), (B, 1), or (B, T)")
+
+    @staticmethod
+    def _packet_residual(residual: torch.Tensor, ref: torch.Tensor) -> torch.Tensor:
+        """Compact packet residual ``(B, D)`` or ``(B, 1, D)`` as ``(B, 1, D)``."""
+        r = residual.to(device=ref.device, dtype=ref.dtype)
+        B, _T, D = ref.shape
+        if r.dim() == 2 and r.shape == (B, D):
+            return r.unsqueeze(1)
+        if r.dim() == 3 and r.shape[0] == B and r.shape[2] == D:
+            if r.shape[1] != 1:
+                raise ValueError("episodic_residual packets must be compact with shape "
+                                 f"(B, D) or (B, 1, D); got {tuple(r.shape)}")
+            return r
+        if r.dim() in (2, 3):
+            raise ValueError(f"episodic_residual shape {tuple(r.shape)} cannot feed hidden shape "
+                             f"{tuple(ref.shape)}")
+        raise ValueError("episodic_residual must have compact shape (B, D) or (B, 1, D)")
+
+    def _stash_outer_cue(self, x: torch.Tensor, reads_memory: bool) -> None:
+        """Maintenance probes compare a cheap saliency map against the full
+        read, so the cue that read used is kept (detached) on the module."""
+        from .memory import MultiSlotOuterModel
+        keep = reads_memory and isinstance(self.outer_model, MultiSlotOuterModel) and self.cue_projection
+        self._last_outer_cue = x.detach().mean(dim=1) if keep else None
+
+    def _per_bucket(self, x: torch.Tensor, per_sample: torch.Tensor, read_fn) -> torch.Tensor:
+        """``(B, 1, D)`` bias assembled from one read per distinct dominant bucket."""
+        out = torch.zeros(x.size(0), 1, x.size(2), device=x.device, dtype=x.dtype)
+        for b_id in per_sample.unique().tolist():
+            rows = per_sample == b_id
+            out[rows] = read_fn(int(b_id), rows).unsqueeze(1).to(dtype=x.dtype)
+        return out
+
+    def _pre_recurrence_biases(self, x: torch.Tensor, bucket_ids: Optional[torch.Tensor], *,
+                               cache_read_cutoff: Optional[int] = None,
+                               slot_mask: Optional[torch.Tensor] = None,
+                               override_index: Optional[int] = None,
+                               override_values: Optional[torch.Tensor] = None) -> list[torch.Tensor]:
+        """Full-strength memory reads added before the recurrence, each ``(B, 1, D)``:
+        the episodic store (per dominant bucket in ``append_only`` mode, whole-store
+        otherwise), bucket prototypes, then the semantic tier
+        (reference src/chaoscontrol/model.py:1661-1722)."""
+        from .memory import MultiSlotOuterModel
+        B = x.size(0)
+        om = self.outer_model
+        biases: list[torch.Tensor] = []
+        if om is not None and self.buffer_mode == "append_only":
+            per_sample = (bucket_ids.mode(dim=1).values if bucket_ids is not None
+                          else torch.zeros(B, dtype=torch.long, device=x.device))
+            if isinstance(om, MultiSlotOuterModel) and len(om.table):
+                want_cue = self.retrieval_mode in ("bucket_topk", "softmax_all")
+
+                def _read(b_id: int, rows: torch.Tensor) -> torch.Tensor:
+                    cue = None
+                    if want_cue:
+                        cue = om.cue_proj(x[rows].detach().mean(dim=1).to(dtype=om.cue_proj.weight.dtype))
+                    return om.read_bucket(
+                        int(rows.sum()), bucket_id=b_id, mode=self.retrieval_mode, k=self.retrieval_k,
+                        cue=cue, read_cutoff=cache_read_cutoff,
+                        slot_mask=None if slot_mask is None else slot_mask[rows],
+                        slot_override_index=override_index,
+                        slot_override_values=None if override_values is None else override_values[rows])
+                biases.append(self._per_bucket(x, per_sample, _read))
+            if self.bucket_prototypes_module is not None and bucket_ids is not None:
+                biases.append(self._per_bucket(
+                    x, per_sample,
+                    lambda b_id, rows: self.bucket_prototypes_module.read(int(rows.sum()), b_id)))
+        elif om is not None:
+            if isinstance(om, MultiSlotOuterModel):
+                cue = x.detach().mean(dim=1) if self.cue_projection else None
+                read = om.read(B, cue=cue, read_cutoff=cache_read_cutoff, slot_mask=slot_mask,
+                               slot_override_index=override_index, slot_override_values=override_values)
+            else:
+                read = om.read(B)
+            biases.append(read.unsqueeze(1).to(dtype=x.dtype))
+        if self.semantic_tier is not None:
+            biases.append(self.semantic_tier.read(B).unsqueeze(1).to(dtype=x.dtype))
+        return biases
+
+    def _posterior_bias(self, x: torch.Tensor, bucket_ids: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        """Error-driven correction added after the recurrence, ``(B, 1, D)`` or ``None``."""
+        if self.posterior is None:
+            return None
+        from .posterior import BucketDelta, GlobalDelta, ResidualCache
+        if isinstance(self.posterior, GlobalDelta):
+            return self.posterior.read(x.size(0)).unsqueeze(1).to(x.dtype)
+        if isinstance(self.posterior, BucketDelta) and bucket_ids is not None:
+            per = bucket_ids.mode(dim=1).values.tolist()
+            bias = torch.cat([self.posterior.read(bucket_id=int(b), batch_size=1) for b in per], dim=0)
+            return bias.unsqueeze(1).to(x.dtype)
+        if isinstance(self.posterior, ResidualCache):
+            return self.posterior.read(x.detach().mean(dim=1)).unsqueeze(1).to(x.dtype)
+        return None
+
+    _PACKET_FORWARD_MODULE_ATTRS: tuple[str, ...] = (
+        "embed", "wernicke", "outer_model", "semantic_tier", "bucket_prototypes_module")
+
+    def packet_forward_state_keys(self) -> set[str]:
+        """Tensor state-dict keys that ``build_episodic_packet`` reads: what a
+        packet-serving rank needs from a trunk snapshot (no SSM layers, no head)."""
+        keys: set[str] = set()
+        for attr in self._PACKET_FORWARD_MODULE_ATTRS:
+            mod = getattr(self, attr, None)
+            if isinstance(mod, nn.Module):
+                keys.update(f"{attr}.{k}" for k, v in mod.state_dict().items() if torch.is_tensor(v))
+        return keys
+
+    @torch.no_grad()
+    def build_episodic_packet(self, input_ids: torch.Tensor, *,
+                              cache_read_cutoff: Optional[int] = None) -> dict[str, Any]:
+        """The pre-recurrence memory bias that ``memory_mode='force_on'`` would
+        inject, as a compact packet, without running the recurrence or the head
+        (reference model.py:1166-1301).  A serving proposal, not an oracle label."""
+        x = self.embed(input_ids)
+        bucket_ids = None
+        if self.wernicke is not None:
+            x, bucket_ids, _ = self.wernicke(x)
+        self._stash_outer_cue(x, True)
+        biases = self._pre_recurrence_biases(x, bucket_ids, cache_read_cutoff=cache_read_cutoff)
+        B, T, D = x.shape
+        residual = torch.zeros(B, 1, D, device=x.device, dtype=x.dtype)
+        for bias in biases:
+            residual.add_(bias)
+        gate = torch.ones(B, T, device=x.device, dtype=x.dtype) if biases else \
+            torch.zeros(B, T, device=x.device, dtype=x.dtype)
+        return {
+            "memory_residual": residual.contiguous(),
+            "memory_gate": gate,
+            "packet_source_hidden": x.detach(),
+            "packet_source_bucket_ids": None if bucket_ids is None else bucket_ids.detach(),
+            "packet_write_score": x.detach().float().square().mean(dim=-1),
+            "packet_source_count": len(biases),
+        }
+
+    def encode_paired_for_score(self, input_ids: torch.Tensor, *,
+                                cache_read_cutoff: Optional[int] = None):
+        """``(h_off, h_mem, memory_meta)``: memory-off and force-on streams of the
+        same batch, stacked through the recurrence in ONE pass over the layers
+        (reference model.py:1303-1455)."""
+        x_base = self.embed(input_ids)
+        bucket_ids = None
+        if self.wernicke is not None:
+            x_base, bucket_ids, _ = self.wernicke(x_base)
+        self._stash_outer_cue(x_base, True)
+        residual: Optional[torch.Tensor] = None
+        x_mem = x_base
+        for bias in self._pre_recurrence_biases(x_base, bucket_ids, cache_read_cutoff=cache_read_cutoff):
+            x_mem = x_mem + bias
+            residual = bias if residual is None else residual + bias
+        pair, _f, _s = self._run_layers(torch.cat([x_base, x_mem], dim=0), None, want_stats=False)
+        h_off, h_mem = pair.chunk(2, dim=0)
+        bias = self._posterior_bias(h_mem, bucket_ids)
+        if bias is not None:
+            h_mem = h_mem + bias
+            residual = bias if residual is None else residual + bias
+        gate = None if residual is None else torch.ones(h_mem.shape[:2], device=h_mem.device, dtype=h_mem.dtype)
+        return h_off, h_mem, {"memory_mode": "force_on", "cache_read_cutoff": cache_read_cutoff,
+                              "memory_gate": gate, "memory_residual": residual}
 
     def _run_layers(self, x, initial_states, want_stats: bool):
         finals: list[Optional[torch.Tensor]] = [None] * len(self.layers)
@@ -448,35 +638,6 @@ class CareStudentLM(nn.Module):
             cur[idx] = fs
         return x, finals, all_stats
 
-    def _memory_read(self, x, memory_mode, residual, gate, meta, **_kw):
-        if memory_mode == "packet":
-            if residual is None:
-                return x
-            g = gate
-            while g.dim() < residual.dim():
-                g = g.unsqueeze(-1)
-            return x + g.to(x.dtype) * residual.to(x.dtype)
-        if self.outer_model is not None:
-            bias = self.outer_model.read(x.size(0)) if hasattr(self.outer_model, "read") else None
-            if bias is not None:
-                x = x + bias.to(x.dtype).unsqueeze(1)
-        if self.semantic_tier is not None:
-            x = x + self.semantic_tier.read(x.size(0)).to(x.dtype).unsqueeze(1)
-        return x
-
-    def _posterior_read(self, x, bucket_ids):
-        from .posterior import BucketDelta, GlobalDelta, ResidualCache
-        if isinstance(self.posterior, GlobalDelta):
-            return x + self.posterior.read(x.size(0)).unsqueeze(1)
-        if isinstance(self.posterior, BucketDelta) and bucket_ids is not None:
-            per = bucket_ids.mode(dim=1).values
-            bias = torch.cat([self.posterior.read(bucket_id=int(per[i].item()), batch_size=1)
-                              for i in range(x.size(0))], dim=0)
-            return x + bias.unsqueeze(1)
-        if isinstance(self.posterior, ResidualCache):
-            return x + self.posterior.read(x.detach().mean(dim=1)).unsqueeze(1)
-        return x
-
     # -- full forward ----------------------------------------------------
     def forward(self, input_ids: torch.Tensor, *, return_jacobian_stats: bool = False,
                 memory_write_mode: str = "none",
@@ -492,16 +653,17 @@ class CareStudentLM(nn.Module):
             hidden, _ss, finals = self.encode_with_stats(input_ids, initial_states=initial_states)
         else:
             x = self.embed(input_ids)
-            meta: dict[str, Any] = {}
+            bucket_ids = None
             if self.wernicke is not None:
                 x, bucket_ids, balance = self.wernicke(x)
                 out["balance_loss"] = balance
                 out["bucket_ids"] = bucket_ids
-                meta["bucket_ids"] = bucket_ids
-            x = self._memory_read(x, "force_on", None, None, meta)
+            for bias in self._pre_recurrence_biases(x, bucket_ids):
+                x = x + bias
             x, finals, all_stats = self._run_layers(x, initial_states, want_stats=return_jacobian_stats)
-            if self.posterior is not None:
-                x = self._posterior_read(x, meta.get("bucket_ids"))
+            bias = self._posterior_bias(x, bucket_ids)
+            if bias is not None:
+                x = x + bias
             hidden = x
             if return_jacobian_stats and all_stats:
                 out["jacobian_stats"] = {k: torch.stack([s[k] for s in all_stats]).mean()
@@ -513,16 +675,69 @@ class CareStudentLM(nn.Module):
         out["final_states"] = finals
         if (memory_write_mode == "append_only" and self.buffer_mode == "append_only" and
                 self.outer_model is not None and hasattr(self.outer_model, "append_kv_batch")):
-            self.append_memory_from_hidden(hidden, bucket_ids=out.get("bucket_ids"))
+            bids = out.get("bucket_ids")
+            records = self.append_memory_from_hidden(hidden, bucket_ids=bids)
+            if records and self.bucket_prototypes_module is not None and bids is not None:
+                om = self.outer_model
+                enc = torch.tanh(om.encoder(hidden.detach().reshape(-1, hidden.shape[-1])
+                                            .to(dtype=om.encoder.weight.dtype)))
+                if enc.shape[-1] != self.bucket_prototypes_module.prototype_dim:
+                    raise ValueError(f"outer_dim ({enc.shape[-1]}) != prototype_dim "
+                                     f"({self.bucket_prototypes_module.prototype_dim})")
+                self.bucket_prototypes_module.update_batch(bids.detach().reshape(-1), enc)
         return out
 
-    def append_memory_from_hidden(self, hidden: torch.Tensor, *, bucket_ids=None, **kw):
-        """Append per-token key/value pairs of ``hidden`` to the multi-slot store."""
-        if self.outer_model is None or not hasattr(self.outer_model, "append_kv_batch"):
-            return []
-        flat = hidden.detach().reshape(-1, hidden.shape[-1])
-        bids = bucket_ids.detach().reshape(-1) if bucket_ids is not None else None
-        return self.outer_model.append_kv_batch(flat, bucket_ids=bids, **kw)
+    @torch.no_grad()
+    def append_memory_from_hidden(self, hidden: torch.Tensor, *, bucket_ids: Optional[torch.Tensor] = None,
+                                  score: Optional[torch.Tensor] = None, max_tokens: Optional[int] = None,
+                                  event_ids: Optional[torch.Tensor] = None) -> list[dict[str, object]]:
+        """Encodes per-token hidden states and appends them to the append-only
+        multi-slot store (reference model.py:1043-1163).  With ``max_tokens`` the
+        highest-``score`` tokens (or an even stride without scores) are kept.
+        Returns one generation-stamped record per slot actually appended."""
+        from .memory import MultiSlotOuterModel
+        om = self.outer_model
+        if self.buffer_mode != "append_only" or not isinstance(om, MultiSlotOuterModel):
+            raise ValueError("append_memory_from_hidden requires append-only MultiSlotOuterModel")
+        B, T, D = hidden.shape
+        flat = hidden.detach().reshape(-1, D)
+        dev = hidden.device
+        sel = None
+        cap = 0 if max_tokens is None else int(max_tokens)
+        if cap > 0 and flat.shape[0] > cap:
+            if score is not None:
+                sel = torch.topk(score.detach().reshape(-1).to(device=dev, dtype=torch.float32), k=cap,
+                                 largest=True, sorted=False).indices
+            else:
+                sel = torch.linspace(0, flat.shape[0] - 1, steps=cap, device=dev).long()
+            flat = flat.index_select(0, sel)
+        ev = None
+        if event_ids is not None:
+            ev = event_ids.detach().reshape(-1).to(device=dev, dtype=torch.long)
+            if ev.numel() == B * T:
+                ev = ev if sel is None else ev.index_select(0, sel)
+            elif ev.numel() != flat.shape[0]:
+                raise ValueError("event_ids must either cover the full hidden shape "
+                                 f"({B * T}) or the selected write count ({flat.shape[0]}), got {ev.numel()}")
+        enc = torch.tanh(om.encoder(flat.to(dtype=om.encoder.weight.dtype)))
+        if bucket_ids is None:
+            bids = torch.zeros(flat.shape[0], dtype=torch.long, device=dev)
+        else:
+            bids = bucket_ids.detach().reshape(-1).to(device=dev, dtype=torch.long)
+            if sel is not None:
+                bids = bids.index_select(0, sel)
+        ids = (om.append_kv_batch(enc, bids) if ev is None
+               else om._append_kv_batch_committed(enc, bids, event_ids=ev))
+        bid_list = bids[: len(ids)].tolist()
+        ev_list = None if ev is None else ev[: len(ids)].tolist()
+        records: list[dict[str, object]] = []
+        for i, sid in enumerate(ids):
+            rec = om.table.record(int(sid))
+            records.append({
+                "slot_id": int(sid), "tensor": enc[i].detach().reshape(1, -1), "bucket_id": int(bid_list[i]),
+                "event_id": int(ev_list[i]) if ev_list is not None else int(rec.event_id if rec else 0),
+                "generation": int(rec.write_generation if rec else 0)})
+        return records
 
     # -- single token ----------------------------------------------------
     def step(self, token_ids: torch.Tensor, states: list[torch.Tensor], kv_caches=None):

@@ -24,7 +24,7 @@ const char* ccb_last_error(void);
 //   a_mn == 0: A is stored [M rows][K contiguous] (K-major)
 //   a_mn == 1: A is stored [K rows][M contiguous] (MN-major, i.e. A^T in memory)
 //   b_mn likewise for B with N.
-// bf16 operands, fp32 accumulation in TMEM.  `splits` > 1 partitions K; split s
+// bf16 (or 8-bit float) operands, fp32 accumulation in TMEM.  `splits` > 1 partitions K; split s
 // writes its own partial tile at C + s * c_split (the caller reduces).
 enum CcbEpilogue {
   CCB_EPI_STORE = 0,          // out = alpha * acc + beta * Cin
@@ -54,9 +54,26 @@ typedef struct CcbGemmArgs {
   int64_t out_fp32;                          // 1: C is float, 0: C is bf16
   int64_t ss_atomic;                         // RESID_SS: atomicAdd instead of store
   float alpha, beta, inv_dim, eps;
+  // 8-bit float operands (tcgen05 kind::f8f6f4): 0 = bf16, 1 = e4m3, 2 = e5m2.
+  // Both operands must then be K-major and K a multiple of 16.
+  int64_t a_fp8, b_fp8;
+  const float* dscale_a;                     // optional device scalars: alpha *= *dscale_a * *dscale_b
+  const float* dscale_b;
+  const void* bias;                          // optional bf16 [N], added in the STORE epilogue
 } CcbGemmArgs;
 
 int ccb_gemm(const CcbGemmArgs* args, void* stream);
+
+// ---- 8-bit float helpers (fmt: 1 = e4m3, 2 = e5m2) --------------------------
+// out = fp8(x / *scale), *pending = max(*pending, max|x|)
+int ccb_fp8_cast_amax(const void* x_bf16, void* out_u8, const float* scale, float* pending, int64_t n,
+                      int64_t fmt, void* stream);
+// out[c][r] = fp8(x[r][c] / *scale); optional colsum[c] += sum_r x[r][c]
+int ccb_fp8_cast_transpose_amax(const void* x_bf16, void* out_u8, const float* scale, float* pending,
+                                float* colsum, int64_t R, int64_t C, int64_t ldx, int64_t ldo, int64_t fmt,
+                                void* stream);
+// roll the amax history, append *pending, recompute *scale (nullptr: skip), zero *pending
+int ccb_fp8_flush_amax(float* history, int64_t len, float* pending, float* scale, float max_rep, void* stream);
 
 #ifdef __cplusplus
 }

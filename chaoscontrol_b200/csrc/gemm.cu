@@ -41,6 +41,11 @@ struct GemmKArgs {
   float* ss_out;
   float alpha, beta, inv_dim, eps;
   int* status;
+  int f8, bk;                 // 8-bit operands: kind::f8f6f4, 128 elements per 128-byte row
+  uint32_t idesc_f8;
+  const float* dscale_a;
+  const float* dscale_b;
+  const void* bias;
 };
 
 // bf16 outputs leave through shared-memory staging tiles and TMA stores: each
@@ -194,14 +199,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           uint8_t* a_dst = sA + stage * A_STAGE_BYTES;
           uint8_t* b_dst = sB + stage * B_STAGE_BYTES;
           if (A_MN == 0) {
-            tma_load_3d(a_dst, &tmA, &full_bar[stage], kb * BK, t.m0, t.b);
+            tma_load_3d(a_dst, &tmA, &full_bar[stage], kb * p.bk, t.m0, t.b);
           } else {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j)
               tma_load_3d(a_dst + j * 8192, &tmA, &full_bar[stage], t.m0 + 64 * j, kb * BK, t.b);
           }
           if (B_MN == 0) {
-            tma_load_3d(b_dst, &tmB, &full_bar[stage], kb * BK, t.n0, t.b);
+            tma_load_3d(b_dst, &tmB, &full_bar[stage], kb * p.bk, t.n0, t.b);
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
@@ -243,7 +248,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                                         : make_smem_desc(a_base + k * 32, 16, 1024);
             const uint64_t bdesc = B_MN ? make_smem_desc(b_base + k * 2048, 8192, 1024)
                                         : make_smem_desc(b_base + k * 32, 16, 1024);
-            umma_bf16(d_tmem, adesc, bdesc, idesc, (kb > t.kb0 || k > 0) ? 1u : 0u);
+            const uint32_t accum = (kb > t.kb0 || k > 0) ? 1u : 0u;
+            if (p.f8) umma_f8(d_tmem, adesc, bdesc, p.idesc_f8, accum);   // 32 one-byte k per MMA
+            else umma_bf16(d_tmem, adesc, bdesc, idesc, accum);           // 16 two-byte k per MMA
           }
           umma_commit(&empty_bar[stage]);   // stage reusable once these MMAs retire
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -282,6 +289,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                                 (long long)m * p.ldc;
       float rs = 1.f;
       if (p.rowss != nullptr && row_ok) rs = rsqrtf(p.rowss[m] * p.inv_dim + p.eps);
+      float alpha = p.alpha;
+      if (p.dscale_a != nullptr) alpha *= __ldg(p.dscale_a);
+      if (p.dscale_b != nullptr) alpha *= __ldg(p.dscale_b);
       const int ncols = min(BN, p.N - t.n0);   // valid columns in this tile
       const int nchunks = (ncols + 31) >> 5;
       // k-th 32-column chunk of this warp: groups part, part+2, ... two chunks each
@@ -423,10 +433,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               aux_get(aux1_row, c, a1_cur, cin);
               a1_advance();
 #pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] = p.alpha * v[i] + p.beta * cin[i];
+              for (int i = 0; i < 32; ++i) v[i] = alpha * v[i] + p.beta * cin[i];
             } else {
 #pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] *= p.alpha;
+              for (int i = 0; i < 32; ++i) v[i] *= alpha;
+            }
+            if (p.bias != nullptr) {
+              float bv[32];
+              load_bf16x32(reinterpret_cast<const __nv_bfloat16*>(p.bias) + n, bv, nvalid);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] += bv[i];
             }
           } break;
           case CCB_EPI_ROWSCALE: {
@@ -548,7 +564,15 @@ static int launch_gemm(const CcbGemmArgs* a, cudaStream_t stream) {
     attr_set[dev & 15] = true;
   }
   CUtensorMap tmA, tmB;
-  // A
+  const bool f8 = a->a_fp8 != 0;
+  if (f8) {
+    // one-byte operands: a 128-byte swizzle row holds 128 k-elements
+    if (A_MN != 0 || B_MN != 0) return set_error("ccb_gemm: 8-bit operands must be K-major");
+    if (make_tmap_u8_3d(&tmA, a->A, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->batch,
+                        (uint64_t)a->lda, (uint64_t)a->a_batch, 128, BM)) return -1;
+    if (make_tmap_u8_3d(&tmB, a->B, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)a->batch,
+                        (uint64_t)a->ldb, (uint64_t)a->b_batch, 128, BN)) return -1;
+  } else {
   if (A_MN == 0) {
     if (make_tmap_bf16_3d(&tmA, a->A, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->batch,
                           (uint64_t)a->lda, (uint64_t)a->a_batch, BK, BM)) return -1;
@@ -563,7 +587,12 @@ static int launch_gemm(const CcbGemmArgs* a, cudaStream_t stream) {
     if (make_tmap_bf16_3d(&tmB, a->B, (uint64_t)a->N, (uint64_t)a->K, (uint64_t)a->batch,
                           (uint64_t)a->ldb, (uint64_t)a->b_batch, 64, BK)) return -1;
   }
+  }
   GemmKArgs p;
+  p.f8 = f8 ? 1 : 0;
+  p.bk = f8 ? 128 : BK;
+  p.idesc_f8 = make_idesc_f8(BM, BN, (int)a->a_fp8 - 1, (int)a->b_fp8 - 1);
+  p.dscale_a = a->dscale_a; p.dscale_b = a->dscale_b; p.bias = a->bias;
   // bf16 outputs that keep rows 16-byte aligned go out through TMA stores
   CUtensorMap tmC, tmC2;
   const bool tma_ok = !a->out_fp32 && (a->ldc % 8 == 0) && (a->c_batch % 8 == 0) &&
@@ -584,7 +613,7 @@ static int launch_gemm(const CcbGemmArgs* a, cudaStream_t stream) {
   p.batch = (int)a->batch;
   p.tiles_m = (p.M + BM - 1) / BM;
   p.tiles_n = (p.N + BN - 1) / BN;
-  p.kblocks = (p.K + BK - 1) / BK;
+  p.kblocks = (p.K + p.bk - 1) / p.bk;
   int splits = (int)(a->splits < 1 ? 1 : a->splits);
   if (splits > p.kblocks) splits = p.kblocks;
   p.kper = (p.kblocks + splits - 1) / splits;
@@ -613,11 +642,16 @@ static int launch_gemm(const CcbGemmArgs* a, cudaStream_t stream) {
 
 }  // namespace ccb
 
+static inline int64_t b_fp8_of(const CcbGemmArgs* a) { return a->b_fp8; }
+
 extern "C" int ccb_gemm(const CcbGemmArgs* a, void* stream_) {
   using namespace ccb;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (a->M <= 0 || a->N <= 0 || a->K <= 0 || a->batch <= 0) return 0;
-  if ((a->lda % 8) || (a->ldb % 8) || (a->ldc % 4))
+  if ((a->a_fp8 != 0) != (b_fp8_of(a) != 0) || a->a_fp8 < 0 || a->a_fp8 > 2 || a->b_fp8 > 2)
+    return set_error("ccb_gemm: a_fp8/b_fp8 must both be 0 (bf16) or both in {1: e4m3, 2: e5m2}");
+  const int row_align = a->a_fp8 ? 16 : 8;
+  if ((a->lda % row_align) || (a->ldb % row_align) || (a->ldc % 4))
     return set_error("ccb_gemm: row strides must keep rows 16-byte aligned");
   const int key = (int)(a->a_mn * 2 + a->b_mn);
   // 128-wide tiles only where the problem has a single narrow N tile to fill.

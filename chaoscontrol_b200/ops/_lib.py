@@ -33,6 +33,7 @@ class GemmArgs(C.Structure):
         ("a_mn", i64), ("b_mn", i64),
         ("epi", i64), ("out_fp32", i64), ("ss_atomic", i64),
         ("alpha", f32), ("beta", f32), ("inv_dim", f32), ("eps", f32),
+        ("a_fp8", i64), ("b_fp8", i64), ("dscale_a", vp), ("dscale_b", vp), ("bias", vp),
     ]
 
 
@@ -46,6 +47,9 @@ _SIGS = {
     "ccb_last_error": ([], C.c_char_p),
     "ccb_status_ptr": ([], vp),
     "ccb_gemm": ([C.POINTER(GemmArgs), vp], C.c_int),
+    "ccb_fp8_cast_amax": ([vp, vp, vp, vp, i64, i64, vp], C.c_int),
+    "ccb_fp8_cast_transpose_amax": ([vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, vp], C.c_int),
+    "ccb_fp8_flush_amax": ([vp, i64, vp, vp, f32, vp], C.c_int),
     "ccb_scan_fwd": ([vp, i64, vp, vp, vp, vp, vp, i64, i64, i64, vp], C.c_int),
     "ccb_scan_bwd": ([vp, i64, vp, vp, vp, vp, vp, vp, f32, f32, vp, i64, vp, vp, i64, i64, i64, vp],
                      C.c_int),

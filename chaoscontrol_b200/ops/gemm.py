@@ -23,7 +23,7 @@ from . import _lib
 from ._lib import (EPI_DSILU, EPI_RESID_SS, EPI_RMSBWD, EPI_ROWSCALE, EPI_ROWSCALE_SILU,
                    EPI_STORE, GemmArgs)
 
-__all__ = ["gemm", "gemm_reference", "pick_splits", "EPI_STORE", "EPI_ROWSCALE",
+__all__ = ["gemm", "gemm_fp8", "gemm_reference", "pick_splits", "EPI_STORE", "EPI_ROWSCALE",
            "EPI_ROWSCALE_SILU", "EPI_RESID_SS", "EPI_DSILU", "EPI_RMSBWD"]
 
 
@@ -100,6 +100,53 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     args.ss_atomic = int(ss_atomic)
     args.alpha, args.beta, args.inv_dim, args.eps = alpha, beta, inv_dim, eps
     _lib.check(_lib.lib().ccb_gemm(C.byref(args), _lib.stream_ptr()), "gemm")
+    return out
+
+
+_FP8_CODE = {torch.float8_e4m3fn: 1, torch.float8_e5m2: 2}
+
+
+def gemm_fp8(a: torch.Tensor, b: torch.Tensor, *, scale_a: torch.Tensor, scale_b: torch.Tensor,
+             bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+             out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """``(scale_a * a) @ (scale_b * b).T (+ bias)`` for 8-bit float operands.
+
+    ``a`` ``[M, K]`` and ``b`` ``[N, K]`` are ``float8_e4m3fn`` / ``float8_e5m2``
+    (any mix), K-major, with row strides that are multiples of 16 bytes; the
+    scales are one-element fp32 device tensors read by the kernel (no host
+    sync).  Runs ``tcgen05.mma kind::f8f6f4`` with fp32 accumulation.  The
+    reference's counterpart is its cuBLASLt call
+    (src/chaoscontrol/kernels/_cublaslt/src/cublaslt_fp8_matmul.cpp:281-291).
+    """
+    if a.dtype not in _FP8_CODE or b.dtype not in _FP8_CODE:
+        raise TypeError("gemm_fp8 operands must be float8_e4m3fn or float8_e5m2")
+    M, K = a.shape
+    N, Kb = b.shape
+    if K != Kb:
+        raise ValueError(f"contraction mismatch: {tuple(a.shape)} vs {tuple(b.shape)}")
+    if not a.is_cuda:
+        res = (a.float() * scale_a.float()) @ (b.float() * scale_b.float()).T
+        if bias is not None:
+            res = res + bias.float()
+        if out is not None:
+            return out.copy_(res.to(out.dtype))
+        return res.to(out_dtype)
+    if a.stride(-1) != 1 or b.stride(-1) != 1 or a.stride(0) % 16 or b.stride(0) % 16:
+        raise ValueError("gemm_fp8 operands need a contiguous last dimension and 16-byte row strides")
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    args = GemmArgs()
+    args.A, args.B, args.C = a.data_ptr(), b.data_ptr(), out.data_ptr()
+    args.M, args.N, args.K = M, N, K
+    args.batch, args.splits = 1, 1
+    args.lda, args.ldb, args.ldc = a.stride(0), b.stride(0), out.stride(0)
+    args.epi = EPI_STORE
+    args.out_fp32 = int(out.dtype == torch.float32)
+    args.alpha, args.beta, args.inv_dim, args.eps = 1.0, 0.0, 0.0, 0.0
+    args.a_fp8, args.b_fp8 = _FP8_CODE[a.dtype], _FP8_CODE[b.dtype]
+    args.dscale_a, args.dscale_b = scale_a.data_ptr(), scale_b.data_ptr()
+    args.bias = _lib.ptr(bias)
+    _lib.check(_lib.lib().ccb_gemm(C.byref(args), _lib.stream_ptr()), "gemm_fp8")
     return out
 
 

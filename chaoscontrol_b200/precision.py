@@ -1,7 +1,7 @@
 """Mixed-precision policy: ``autocast_context`` and the linear-promotion helpers
 (API of src/chaoscontrol/precision.py:100-301 in the reference).
 
-``fp8`` here is the library's own block-scaled e4m3 path (no Transformer
+``fp8`` here is the library's own delayed-scaling e4m3/e5m2 path (no Transformer
 Engine): ``"fp8"`` and ``"fp8_fused"`` both mean bf16 ambient autocast with
 eligible ``nn.Linear`` modules swapped for :class:`..ops.fp8_linear.FusedFP8Linear`.
 """
@@ -47,7 +47,7 @@ def maybe_promote_linears_to_fused_fp8(model: nn.Module, enabled: bool) -> int:
         for child_name, child in list(parent.named_children()):
             full = f"{parent_name}.{child_name}" if parent_name else child_name
             if _eligible(full, child):
-                setattr(parent, child_name, FusedFP8Linear.from_linear(child))
+                setattr(parent, child_name, FusedFP8Linear.from_nn_linear(child))
                 count += 1
     return count
 

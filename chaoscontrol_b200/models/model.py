@@ -763,14 +763,36 @@ class CareStudentLM(nn.Module):
         logits = self.lm_head(self.final_norm(x.unsqueeze(1)).squeeze(1))
         return logits, hidden, new_states
 
-    def dream_step(self, token_ids: torch.Tensor, states: list[torch.Tensor], *,
-                   temperature: float = 1.0, generator: Optional[torch.Generator] = None):
-        """Sample the next token from the model's own distribution and advance:
-        ``(next_token (batch, 1), logits, hidden, new_states)``."""
-        logits, hidden, new_states = self.step(token_ids, states)
-        if temperature <= 0:
-            nxt = logits.argmax(dim=-1, keepdim=True)
-        else:
-            probs = F.softmax(logits.float() / temperature, dim=-1)
-            nxt = torch.multinomial(probs, 1, generator=generator)
-        return nxt, logits, hidden, new_states
+    def dream_step(self, token_ids: torch.Tensor, states: list[torch.Tensor], kv_caches=None):
+        """Single-token step through ALL tiers (Wernicke, memory read with the
+        token itself as cue, semantic tier, then the recurrence): what REM dream
+        generation uses, where ``step()`` deliberately runs the recurrence alone
+        (reference src/chaoscontrol/model.py:922-1000).
+        Returns ``(logits (batch, vocab), hidden (batch, dim), new_states)``."""
+        if self.depth_recurrence_count > 1:
+            raise NotImplementedError(
+                "CareStudentLM.dream_step() does not implement depth recurrence; use forward() for "
+                f"depth_recurrence_count={self.depth_recurrence_count}")
+        x = self.embed(token_ids).squeeze(1)
+        if self.wernicke is not None:
+            x = self.wernicke(x.unsqueeze(1))[0].squeeze(1)
+        if self.outer_model is not None:
+            om = self.outer_model
+            read = om.read(x.size(0), cue=x) if hasattr(om, "table") else om.read(x.size(0))
+            x = x + read.to(x.dtype)
+        if self.semantic_tier is not None:
+            x = x + self.semantic_tier.read(x.size(0)).to(x.dtype)
+        if kv_caches is None:
+            kv_caches = [None] * len(self.layers)
+        new_states = []
+        for i, layer in enumerate(self.layers):
+            if hasattr(layer, "_init_kv_cache"):
+                if kv_caches[i] is None:
+                    raise RuntimeError(f"Layer {i} is a hybrid block but no KV cache provided. "
+                                       "Call init_kv_caches() and pass the result to dream_step().")
+                x, s = layer.step(x, states[i], kv_cache=kv_caches[i])
+            else:
+                x, s = layer.step(x, states[i])
+            new_states.append(s)
+        logits = self.lm_head(self.final_norm(x.unsqueeze(1)).squeeze(1))
+        return logits, x, new_states

@@ -75,6 +75,15 @@ int ccb_fp8_cast_transpose_amax(const void* x_bf16, void* out_u8, const float* s
 // roll the amax history, append *pending, recompute *scale (nullptr: skip), zero *pending
 int ccb_fp8_flush_amax(float* history, int64_t len, float* pending, float* scale, float max_rep, void* stream);
 
+// ---- episodic write events ---------------------------------------------------
+// Packs M selected (batch, position) candidates into 568-byte WriteEvent records
+// (all-zero record = candidate dropped at a sequence edge).  rep_dtype: 0 fp32, 1 bf16, 2 fp16.
+int ccb_pack_write_events(void* out, const int64_t* input_ids, const int64_t* target_ids, const void* key_rep,
+                          int64_t rep_dtype, const float* pressure, const float* per_token_ce,
+                          const int64_t* positions, const int64_t* candidate_base, int64_t M, int64_t B,
+                          int64_t T, int64_t D, int64_t gpu_step, int64_t source_rank, int64_t write_bucket,
+                          int64_t fingerprint_window, int64_t span_length, int64_t key_rep_dim, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

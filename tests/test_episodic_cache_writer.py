@@ -172,3 +172,56 @@ def test_pack_write_events_kernel_matches_host(dtype):
         torch.cuda.synchronize()
         assert torch.equal(got.cpu(), want)
         assert int((got[:, 0] == 1).sum()) > 100
+
+
+# --------------------------------------------------------------------------- slot tensor / query
+def test_gpu_slot_row_and_batched_round_trip():
+    from chaoscontrol_b200.episodic import gpu_slot as G
+    S, D = 3, 6
+    assert G.slot_dim(span_length=4, key_rep_dim=256) == 528
+    slots = G.make_slot_tensor(k_max=5, span_length=S, key_rep_dim=D, device="cpu")
+    big = 2 ** 63 - 1
+    G.pack_payload(slots[1], valid_mask=1.0, pressure=0.5, key_fp=big, value_anchor_id=7,
+                   value_tok_ids=torch.tensor([7, 8, 9]), key_rep=torch.arange(6.0), residual=-torch.arange(6.0),
+                   span_length=S, key_rep_dim=D, pre_write_ce=2.5, protection_score=0.25)
+    u = G.unpack_payload(slots[1], span_length=S, key_rep_dim=D)
+    assert u["key_fp"] == big and u["value_anchor_id"] == 7 and u["value_tok_ids"].tolist() == [7, 8, 9]
+    assert u["pre_write_ce"] == 2.5 and u["protection_score"] == 0.25 and u["residual"][2] == -2.0
+    assert G.unpack_payload(slots[0], span_length=S, key_rep_dim=D)["valid_mask"] == 0.0
+    n = G.pack_payload_rows(slots, pressure=torch.tensor([1.0, 2.0]), key_fp=torch.tensor([big, 5]),
+                            value_anchor_id=torch.tensor([1, 2]), value_tok_ids=torch.tensor([[1, 2, 3], [4, 5, 6]]),
+                            key_rep=torch.ones(2, D), residual=torch.zeros(2, D))
+    assert n == 2
+    one = G.unpack_payload(slots[0], span_length=S, key_rep_dim=D)
+    assert one["key_fp"] == big and one["valid_mask"] == 1.0 and one["pre_write_ce"] != one["pre_write_ce"]
+    rows = G.unpack_payload_rows(slots, span_length=S, key_rep_dim=D)
+    assert rows["key_fp"].tolist() == [big, 5] and rows["value_tok_ids"].tolist() == [[1, 2, 3], [4, 5, 6]]
+    with pytest.raises(ValueError):
+        G.make_slot_tensor(k_max=2, span_length=S, key_rep_dim=D, device="cpu", dtype=torch.float16)
+    with pytest.raises(ValueError):
+        G.pack_payload(slots[0][:5], valid_mask=1, pressure=0, key_fp=0, value_anchor_id=0,
+                       value_tok_ids=torch.zeros(S), key_rep=torch.zeros(D), residual=torch.zeros(D),
+                       span_length=S, key_rep_dim=D)
+
+
+def test_query_topk_modes():
+    from chaoscontrol_b200.episodic.query import query_topk, query_topk_batch
+    c = EpisodicCache(capacity=6, span_length=2, key_rep_dim=4)
+    assert query_topk(torch.ones(4), c, 3).numel() == 0
+    reps = torch.eye(4)
+    for i in range(4):
+        c.append(key_fp=i + 1, key_rep=reps[i], value_tok_ids=torch.tensor([0, 0]), value_anchor_id=0,
+                 current_step=i, embedding_version=0, pressure_at_write=float(10 - i))
+    c.utility_u[2] = 5.0
+    q = torch.tensor([0.9, 0.1, 0.5, 0.0])
+    assert query_topk(q, c, 2).tolist() == [2, 0]                     # 0.5*5 beats 0.9*1
+    assert query_topk(q, c, 9, score_mode="pressure_only").tolist() == [0, 1, 2, 3]
+    c.evict(2)
+    assert query_topk(q, c, 2).tolist() == [0, 1]
+    idx, sc = query_topk_batch(torch.stack([q, reps[3]]), c.snapshot_to(torch.device("cpu")), 5)
+    assert idx[0].tolist() == [0, 1, 3, -1, -1] and idx[1, 0] == 3 and torch.isinf(sc[0, 3])
+    with pytest.raises(ValueError):
+        query_topk(q, c, 2, score_mode="bogus")
+    from chaoscontrol_b200.episodic.payload_dtypes import make_query_candidate_dtype, make_write_payload_dtype
+    assert make_write_payload_dtype(span_length=4, key_rep_dim=8).itemsize == 8 + 32 + 32 + 8
+    assert make_query_candidate_dtype(key_rep_dim=8).itemsize == 8 + 8 + 4 + 32

@@ -35,7 +35,8 @@ struct PeerPtrs {
   float* buf2[COMM_MAX_RANKS];          // fp32 reduced-slice staging (two-shot)
   uint32_t* pad[COMM_MAX_RANKS];        // signal pads: [4][COMM_MAX_RANKS] uint32 each
 };
-// pad rows: 0 = "packed epoch e", 1 = "done reading epoch e", 2 = "slice reduced epoch e"
+// pad rows: 0 = "packed epoch e", 1 = "done reading the packed data of epoch e",
+// 2 = "slice reduced / owned parameters published, epoch e", 3 = "epoch e finished: my buffer may be reused"
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -84,7 +85,7 @@ __device__ __forceinline__ bool wait_all_peers(const uint32_t* my_pad, int row, 
 
 // Last block to arrive publishes `epoch` into row `row`, column `rank` of every peer's pad.
 __device__ __forceinline__ void last_block_signal(unsigned* counter, const PeerPtrs& pp, int row,
-                                                  int rank, int ws, uint32_t epoch) {
+                                                  int rank, int ws, uint32_t epoch, int row2 = -1) {
   __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -92,7 +93,10 @@ __device__ __forceinline__ void last_block_signal(unsigned* counter, const PeerP
     if (old == gridDim.x - 1) {
       *counter = 0;
       __threadfence_system();
-      for (int p = 0; p < ws; ++p) st_release_sys(pp.pad[p] + row * COMM_MAX_RANKS + rank, epoch);
+      for (int p = 0; p < ws; ++p) {
+        st_release_sys(pp.pad[p] + row * COMM_MAX_RANKS + rank, epoch);
+        if (row2 >= 0) st_release_sys(pp.pad[p] + row2 * COMM_MAX_RANKS + rank, epoch);
+      }
     }
   }
 }
@@ -101,8 +105,8 @@ __global__ void __launch_bounds__(COMM_THREADS)
 comm_pack_kernel(const float* __restrict__ grad, long long n, float scale, PeerPtrs pp, int rank,
                  int ws, uint32_t epoch, unsigned* counter, uint64_t limit_ns, int* status) {
   __shared__ int sm_ok;
-  // peers must have finished reading what I packed last time
-  if (!wait_all_peers(pp.pad[rank], 1, ws, epoch - 1, limit_ns, status, &sm_ok)) return;
+  // peers must have finished with everything I staged in the previous epoch
+  if (!wait_all_peers(pp.pad[rank], 3, ws, epoch - 1, limit_ns, status, &sm_ok)) return;
   __nv_bfloat16* out = pp.buf[rank];
   const long long n8 = n / 8;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8;
@@ -146,7 +150,7 @@ comm_oneshot_kernel(float* __restrict__ grad, long long n, PeerPtrs pp, int rank
     reinterpret_cast<float4*>(grad)[2 * i] = make_float4(acc[0], acc[1], acc[2], acc[3]);
     reinterpret_cast<float4*>(grad)[2 * i + 1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
   }
-  last_block_signal(counter, pp, 1, rank, ws, epoch);
+  last_block_signal(counter, pp, 1, rank, ws, epoch, 3);
 }
 
 // two-shot, stage 1: this rank reduces slice `rank` into its fp32 staging buffer
@@ -189,7 +193,89 @@ comm_all_gather_kernel(float* __restrict__ grad, long long n, PeerPtrs pp, int r
     const uint4 v = ld_relaxed_sys_v4(reinterpret_cast<const uint4*>(pp.buf2[p]) + j);
     reinterpret_cast<uint4*>(grad)[i] = v;
   }
+  last_block_signal(counter, pp, 1, rank, ws, epoch, 3);
+}
+
+// ---------------------------------------------------------------------------
+// Sharded-optimizer path (distributed Muon): ownership is a list of ranges of
+// the flat buffers, in units of 8 elements.  owner >= 0: that rank reduces the
+// range, updates it, and publishes the new parameters; owner < 0: replicated --
+// every rank reduces and updates it itself.
+//
+//   pack (above)       all gradients -> bf16 staging, flag row 0
+//   reduce_ranges      sum of all peers' staged values over my + replicated ranges
+//                      -> local fp32 gradient (written, not accumulated), row 1
+//   ... local optimizer on owned matrices and replicated tensors ...
+//   publish_params     my owned bf16 parameters -> my staging buffer (after every
+//                      peer has finished reading my staged gradients), row 2
+//   gather_params      every other owner's ranges, from its staging buffer, into
+//                      my flat parameters, rows 1 + 3
+// ---------------------------------------------------------------------------
+struct CommRange {
+  long long off8, len8;
+  int owner, pad;
+};
+
+__global__ void __launch_bounds__(COMM_THREADS)
+comm_reduce_ranges_kernel(float* __restrict__ grad, const CommRange* __restrict__ ranges, int nranges,
+                          PeerPtrs pp, int rank, int ws, uint32_t epoch, unsigned* counter,
+                          uint64_t limit_ns, int* status) {
+  __shared__ int sm_ok;
+  if (!wait_all_peers(pp.pad[rank], 0, ws, epoch, limit_ns, status, &sm_ok)) return;
+  for (int r = 0; r < nranges; ++r) {
+    const CommRange rg = ranges[r];
+    if (rg.owner >= 0 && rg.owner != rank) continue;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < rg.len8;
+         i += (long long)gridDim.x * blockDim.x) {
+      const long long e = rg.off8 + i;
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      uint4 q[COMM_MAX_RANKS];
+#pragma unroll
+      for (int p = 0; p < COMM_MAX_RANKS; ++p)
+        if (p < ws) q[p] = ld_relaxed_sys_v4(reinterpret_cast<const uint4*>(pp.buf[p]) + e);
+#pragma unroll
+      for (int p = 0; p < COMM_MAX_RANKS; ++p)
+        if (p < ws) acc_bf16x8(acc, q[p]);
+      reinterpret_cast<float4*>(grad)[2 * e] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      reinterpret_cast<float4*>(grad)[2 * e + 1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    }
+  }
   last_block_signal(counter, pp, 1, rank, ws, epoch);
+}
+
+__global__ void __launch_bounds__(COMM_THREADS)
+comm_publish_params_kernel(const __nv_bfloat16* __restrict__ param, const CommRange* __restrict__ ranges,
+                           int nranges, PeerPtrs pp, int rank, int ws, uint32_t epoch, unsigned* counter,
+                           uint64_t limit_ns, int* status) {
+  __shared__ int sm_ok;
+  // my staging buffer still holds gradients until every peer has read them
+  if (!wait_all_peers(pp.pad[rank], 1, ws, epoch, limit_ns, status, &sm_ok)) return;
+  uint4* out = reinterpret_cast<uint4*>(pp.buf[rank]);
+  for (int r = 0; r < nranges; ++r) {
+    const CommRange rg = ranges[r];
+    if (rg.owner != rank) continue;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < rg.len8;
+         i += (long long)gridDim.x * blockDim.x)
+      out[rg.off8 + i] = reinterpret_cast<const uint4*>(param)[rg.off8 + i];
+  }
+  last_block_signal(counter, pp, 2, rank, ws, epoch);
+}
+
+__global__ void __launch_bounds__(COMM_THREADS)
+comm_gather_params_kernel(__nv_bfloat16* __restrict__ param, const CommRange* __restrict__ ranges,
+                          int nranges, PeerPtrs pp, int rank, int ws, uint32_t epoch, unsigned* counter,
+                          uint64_t limit_ns, int* status) {
+  __shared__ int sm_ok;
+  if (!wait_all_peers(pp.pad[rank], 2, ws, epoch, limit_ns, status, &sm_ok)) return;
+  for (int r = 0; r < nranges; ++r) {
+    const CommRange rg = ranges[r];
+    if (rg.owner < 0 || rg.owner == rank || rg.owner >= ws) continue;
+    const uint4* src = reinterpret_cast<const uint4*>(pp.buf[rg.owner]);
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < rg.len8;
+         i += (long long)gridDim.x * blockDim.x)
+      reinterpret_cast<uint4*>(param)[rg.off8 + i] = ld_relaxed_sys_v4(src + rg.off8 + i);
+  }
+  last_block_signal(counter, pp, 3, rank, ws, epoch);
 }
 
 }  // namespace ccb
@@ -270,6 +356,54 @@ extern "C" int ccb_allreduce(float* grad, int64_t n, float scale, void* const* b
   }
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : set_error("allreduce launch: %s", cudaGetErrorString(e));
+}
+
+static void fill_peers(ccb::PeerPtrs& pp, void* const* bufs, void* const* bufs2, void* const* pads, int64_t ws) {
+  for (int i = 0; i < ccb::COMM_MAX_RANKS; ++i) {
+    pp.buf[i] = i < ws ? (__nv_bfloat16*)bufs[i] : nullptr;
+    pp.buf2[i] = i < ws ? (float*)bufs2[i] : nullptr;
+    pp.pad[i] = i < ws ? (uint32_t*)pads[i] : nullptr;
+  }
+}
+
+// Sharded-optimizer collectives.  `ranges` is a DEVICE array of `nranges` records
+// {int64 off8, int64 len8, int32 owner, int32 pad}.  phase 0: pack all gradients and
+// reduce the owned + replicated ranges into `grad`; phase 1: publish the owned
+// parameter ranges and gather everyone else's into `param` (bf16 flat buffer).
+extern "C" int ccb_sharded_sync(int64_t phase, float* grad, void* param, int64_t n, float scale,
+                                const void* ranges, int64_t nranges, void* const* bufs, void* const* bufs2,
+                                void* const* pads, int64_t rank, int64_t ws, int64_t epoch, void* counters,
+                                int64_t timeout_ms, void* stream) {
+  if (ws < 1 || ws > COMM_MAX_RANKS) return set_error("ccb_sharded_sync: world size %lld unsupported", (long long)ws);
+  if (n % 8 != 0) return set_error("ccb_sharded_sync: n=%lld must be a multiple of 8", (long long)n);
+  PeerPtrs pp;
+  fill_peers(pp, bufs, bufs2, pads, ws);
+  cudaStream_t s = (cudaStream_t)stream;
+  unsigned* ctr = (unsigned*)counters;
+  int* status = ccb_status_ptr();
+  const uint64_t limit = (uint64_t)(timeout_ms > 0 ? timeout_ms : 2000) * 1000000ull;
+  const int sms = ccb_num_sms();
+  long long want = (n / 8 + COMM_THREADS - 1) / COMM_THREADS;
+  const int grid = (int)(want < sms ? (want < 1 ? 1 : want) : sms);
+  const CommRange* rg = reinterpret_cast<const CommRange*>(ranges);
+  if (phase == 0) {
+    comm_pack_kernel<<<grid, COMM_THREADS, 0, s>>>(grad, n, scale, pp, (int)rank, (int)ws, (uint32_t)epoch,
+                                                    ctr + 0, limit, status);
+    count_launch();
+    comm_reduce_ranges_kernel<<<grid, COMM_THREADS, 0, s>>>(grad, rg, (int)nranges, pp, (int)rank, (int)ws,
+                                                             (uint32_t)epoch, ctr + 4, limit, status);
+    count_launch();
+  } else {
+    comm_publish_params_kernel<<<grid, COMM_THREADS, 0, s>>>((const __nv_bfloat16*)param, rg, (int)nranges, pp,
+                                                              (int)rank, (int)ws, (uint32_t)epoch, ctr + 5, limit,
+                                                              status);
+    count_launch();
+    comm_gather_params_kernel<<<grid, COMM_THREADS, 0, s>>>((__nv_bfloat16*)param, rg, (int)nranges, pp, (int)rank,
+                                                             (int)ws, (uint32_t)epoch, ctr + 6, limit, status);
+    count_launch();
+  }
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : set_error("sharded sync launch: %s", cudaGetErrorString(e));
 }
 
 // Single-GPU self-test hook: waits on a flag that nothing sets, with a short

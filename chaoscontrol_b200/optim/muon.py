@@ -163,6 +163,26 @@ class Muon(torch.optim.Optimizer):
         self._arena = arena
         self._param_name_by_id = {id(p): n for n, p in arena.params.items()}
 
+    def set_arena_shard(self, shard: Optional[dict]) -> None:
+        """Restrict the matrix (Muon) update to an owned sub-batch of every arena
+        shape group: ``shard[group_index] = (first, end)``.  ``None`` restores the
+        full update.  Non-matrix (AdamW) parameters are always updated: they are
+        replicated.  Used by the distributed optimizer, which gathers the owned
+        results afterwards.  Momentum buffers stay full-size so ``state_dict()``
+        keeps its layout; only the owned slices are touched."""
+        self._arena_shard = None if shard is None else {int(k): (int(v[0]), int(v[1])) for k, v in shard.items()}
+        self._owned_ids = None
+        if self._arena_shard is not None and self._arena is not None:
+            owned = set()
+            for gi, g in enumerate(self._arena.muon_groups):
+                a, b = self._arena_shard.get(gi, (0, 0))
+                owned.update(id(self._arena.params[n]) for n in g.names[a:b])
+            self._owned_ids = owned
+
+    def _owns(self, p: Tensor) -> bool:
+        ids = getattr(self, "_owned_ids", None)
+        return ids is None or id(p) in ids
+
     def _is_matrix_param(self, p: Tensor) -> bool:
         name = self._param_name_by_id.get(id(p))
         if self._matrix_param_names is not None and name is not None:
@@ -328,6 +348,8 @@ class Muon(torch.optim.Optimizer):
                     continue
                 grad, state = p.grad, self.state[p]
                 if self._is_matrix_param(p):
+                    if not self._owns(p):
+                        continue
                     if "momentum_buffer" not in state:
                         state["momentum_buffer"] = torch.zeros_like(p, memory_format=torch.preserve_format)
                     buf = state["momentum_buffer"]
@@ -361,7 +383,8 @@ class Muon(torch.optim.Optimizer):
                 if p.grad is None:
                     continue
                 if self._is_matrix_param(p):
-                    by_shape.setdefault((tuple(p.shape), p.dtype, p.device), []).append(p)
+                    if self._owns(p):
+                        by_shape.setdefault((tuple(p.shape), p.dtype, p.device), []).append(p)
                 else:
                     self._adamw_update_param(p=p, state=self.state[p], grad=p.grad, beta1=beta1,
                                              beta2=beta2, adamw_eps=group["adamw_eps"],
@@ -432,28 +455,33 @@ class Muon(torch.optim.Optimizer):
         stream = _lib.stream_ptr()
         p_bf16 = arena.flat_param.dtype == torch.bfloat16
         es = arena.flat_param.element_size()
-        for g in arena.muon_groups:
+        shard = getattr(self, "_arena_shard", None)
+        for gi, g in enumerate(arena.muon_groups):
             r, c = g.shape
             per = r * c
-            off = g.offset
+            m0, m1 = (0, g.count) if shard is None else shard.get(gi, (0, 0))
+            cnt = m1 - m0
+            if cnt <= 0:
+                continue
+            off = g.offset + m0 * per          # first owned matrix of this group
             gptr = arena.flat_grad.data_ptr() + off * 4
             _lib.check(L.ccb_muon_momentum(gptr, st["momentum"].data_ptr() + off * 4,
                                            st["dir"].data_ptr() + off * 2, st["sumsq"].data_ptr(),
-                                           g.count, per, mu, nesterov, stream), "muon_momentum")
+                                           cnt, per, mu, nesterov, stream), "muon_momentum")
             _lib.check(L.ccb_muon_normalize(st["dir"].data_ptr() + off * 2, st["sumsq"].data_ptr(),
-                                            g.count, per, 1e-7, stream), "muon_normalize")
-            X = st["dir"][off: off + g.count * per].view(g.count, r, c)
+                                            cnt, per, 1e-7, stream), "muon_normalize")
+            X = st["dir"][off: off + cnt * per].view(cnt, r, c)
             O = _ns_kernels(X, steps)
             self.ns_calls += 1
             scale = max(1.0, r / c) ** 0.5
-            # apply over maximal runs of non-skipped matrices
+            # apply over maximal runs of non-skipped matrices (indices relative to m0)
             i = 0
-            while i < g.count:
-                if i in g.skip:
+            while i < cnt:
+                if (m0 + i) in g.skip:
                     i += 1
                     continue
                 j = i
-                while j < g.count and j not in g.skip:
+                while j < cnt and (m0 + j) not in g.skip:
                     j += 1
                 n = (j - i) * per
                 if p_bf16:

@@ -30,6 +30,7 @@ _lib.register_sig("ccb_ipc_open", [vp], vp)
 _lib.register_sig("ccb_ipc_close", [vp])
 _lib.register_sig("ccb_allreduce", [vp, i64, C.c_float, vp, vp, vp, i64, i64, i64, vp, i64, i64, vp])
 _lib.register_sig("ccb_comm_wait_probe", [vp, i64, i64, vp, vp])
+_lib.register_sig("ccb_sharded_sync", [i64, vp, vp, i64, C.c_float, vp, i64, vp, vp, vp, i64, i64, i64, vp, i64, vp])
 
 MAX_RANKS = 8
 ONE_SHOT_MAX_BYTES = 64 << 20      # bf16 payload; above this the two-shot kernels run
@@ -116,6 +117,41 @@ class PeerComm:
                                             self._pads, self.rank, self.ws, self.epoch,
                                             self._counters.data_ptr(), mode, self.timeout_ms,
                                             _lib.stream_ptr()), "allreduce")
+
+    # ------------------------------------------------------------------
+    def make_ranges(self, ranges: list[tuple[int, int, int]]) -> torch.Tensor:
+        """Device table for :meth:`sharded_reduce_` / :meth:`sharded_gather_` from
+        ``(element offset, element count, owner)`` triples (owner -1: replicated).
+        Offsets and counts must be multiples of 8 elements."""
+        rows = []
+        for off, cnt, owner in ranges:
+            if off % 8 or cnt % 8:
+                raise ValueError(f"range ({off}, {cnt}) is not aligned to 8 elements")
+            rows.append([off // 8, cnt // 8, int(owner) & 0xFFFFFFFF])      # third word: {int32 owner, int32 pad}
+        t = torch.tensor(rows, dtype=torch.int64).reshape(-1, 3)
+        return t.to("cuda")
+
+    def sharded_reduce_(self, flat_grad: torch.Tensor, ranges: torch.Tensor, average: bool = True) -> None:
+        """Sums the owned and the replicated ranges of ``flat_grad`` over ranks, in
+        place; ranges owned by other ranks are left untouched (stale)."""
+        n = flat_grad.numel()
+        if flat_grad.dtype != torch.float32 or n % 8 or n > self.numel:
+            raise ValueError("sharded_reduce_ needs an fp32 flat tensor, length % 8 == 0, within the buffer")
+        self.epoch += 1
+        self._sharded(0, flat_grad, None, n, 1.0 / self.ws if average else 1.0, ranges)
+
+    def sharded_gather_(self, flat_param: torch.Tensor, ranges: torch.Tensor) -> None:
+        """Publishes this rank's owned ranges of the bf16 ``flat_param`` and pulls every
+        other owner's ranges from its buffer.  Must follow ``sharded_reduce_`` of the same step."""
+        if flat_param.dtype != torch.bfloat16:
+            raise TypeError("sharded_gather_ moves bf16 parameters")
+        self._sharded(1, None, flat_param, flat_param.numel() // 8 * 8, 1.0, ranges)
+
+    def _sharded(self, phase, grad, param, n, scale, ranges) -> None:
+        _lib.check(_lib.lib().ccb_sharded_sync(
+            phase, _lib.ptr(grad), _lib.ptr(param), n, scale, ranges.data_ptr(), ranges.shape[0], self._bufs,
+            self._bufs2, self._pads, self.rank, self.ws, self.epoch, self._counters.data_ptr(), self.timeout_ms,
+            _lib.stream_ptr()), "sharded_sync")
 
     def close(self) -> None:
         L = _lib.lib()

@@ -141,9 +141,11 @@ def _gpu_worker(rank, ws, port, outdir):
             torch.cuda.synchronize()
             if abs(float(norm) - float(n_ref)) > 1e-3 * float(n_ref):
                 ok, msg = False, f"step {step}: norm {float(norm)} vs {float(n_ref)}"
-            diff = (arena.flat_param.float() - arena_ref.flat_param.float()).abs().max().item()
-            if diff > 4e-3:
-                ok, msg = False, f"step {step}: param diff {diff}"
+            # summation order differs from NCCL's: allow two bf16 ulps
+            a, b = arena.flat_param.float(), arena_ref.flat_param.float()
+            bad = ((a - b).abs() > 1e-3 + 2.0 ** -6 * b.abs()).sum().item()
+            if bad:
+                ok, msg = False, f"step {step}: {bad} parameters differ, max {(a - b).abs().max().item()}"
         chk = arena.flat_param.float().double().sum().reshape(1)
         gathered = [torch.zeros_like(chk) for _ in range(ws)]
         dist.all_gather(gathered, chk)

@@ -1,0 +1,531 @@
+"""Production train + eval entry point (one process per GPU, launched by
+``torch.distributed.run``):
+
+    python -m torch.distributed.run --nproc-per-node N -m chaoscontrol_b200.runner_fast_path \\
+        --config cfg.yaml --data-path DIR --sp-model-path tok.model --output-json out.json
+
+Same contract as the reference's runner (experiments/23_fast_path/
+runner_fast_path.py: ``run_condition`` :14201, ``train_fast_for_budget`` :10513,
+``_run_train_step`` :9646, ``_build_optimizer`` :600, ``_warmup`` :13975): YAML
+config -> model -> optional warm-up with state restore -> wall-clock-budgeted
+training -> rank-0 evaluation under the weight EMA / slow weights -> atomic JSON
+result and checkpoint.
+
+What the hot loop is made of here: the no-autograd kernel engine for the forward
+and backward (``train_ssm_step``), the in-kernel peer-memory all-reduce or the
+distributed Muon (``distributed_muon: true``) for gradient exchange, flat-buffer
+clip / Muon / AdamW kernels, and the pinned double-buffered prefetcher for input.
+The only host synchronisation is the stop-flag reduce every
+``stop_check_interval`` steps; losses stay on the device until the loop ends.
+
+Research-only options of the reference's loop that have no implementation here
+are listed in ``UNSUPPORTED_OPTIONS`` and rejected up front rather than ignored.
+"""
+from __future__ import annotations
+
+import argparse
+import faulthandler
+import json
+import math
+import os
+import random
+import signal
+import sys
+import time
+from pathlib import Path
+from typing import Any, Callable, Optional
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from . import fast_path as FP
+from .config import ssm_constructor_kwargs
+from .data import load_fineweb_tokens, load_fineweb_val_tokens, resolve_param_dtype
+from .models.core import verify_diag_recurrence
+from .models.model import CareStudentLM
+from .optim import LAMB, Muon
+from .optim.param_groups import build_optimizer_params
+from .optim.schedule import eval_with_ema, wrap_optimizer_step
+from .parallel.distributed import (allreduce_grads, broadcast_params, clip_arena_grad_norm, clip_grad_norm_fused,
+                                   should_stop_now)
+from .train_ssm import _reject_unsupported, train_ssm_step
+from .training_hooks import FastSlowConsolidator, spectral_summary, zero_embedding_grad_until
+from .utils.arena import get_arena
+
+__all__ = ["run_condition", "train_fast_for_budget", "build_model", "main", "UNSUPPORTED_OPTIONS"]
+
+# options that switch on research machinery this runner does not carry
+UNSUPPORTED_OPTIONS = ("crct_enabled", "replay_eviction_enabled", "episodic_enabled", "dreamworld_enabled",
+                       "rare_bucket_ce_enabled", "event_sleep_enabled", "criticality_distill_enabled")
+
+
+# ---------------------------------------------------------------------------
+# process set-up
+# ---------------------------------------------------------------------------
+def _enable_runner_stack_dump_signal() -> None:
+    """``kill -USR1 <pid>`` dumps every thread's Python stack to stderr (hang triage)."""
+    if hasattr(signal, "SIGUSR1") and not faulthandler.is_enabled():
+        try:
+            faulthandler.register(signal.SIGUSR1, file=sys.stderr, all_threads=True, chain=False)
+        except (ValueError, RuntimeError):        # not the main thread / unsupported platform
+            pass
+
+
+def _init_distributed(world_size_override: Optional[int]) -> tuple[int, int, int]:
+    """``(rank, world_size, local_rank)`` from the launcher's environment."""
+    ws = int(os.environ.get("WORLD_SIZE", "1"))
+    if world_size_override is not None and int(world_size_override) != ws:
+        raise ValueError(f"--world-size {world_size_override} does not match the launcher's WORLD_SIZE={ws}")
+    rank, local = int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    if ws > 1 and not dist.is_initialized():
+        if torch.cuda.is_available():
+            torch.cuda.set_device(local)
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        else:
+            dist.init_process_group("gloo")
+    return rank, ws, local
+
+
+def _pick_device(local_rank: int, name: str) -> torch.device:
+    if name == "auto":
+        return torch.device("cuda", local_rank) if torch.cuda.is_available() else torch.device("cpu")
+    dev = torch.device(name)
+    return torch.device("cuda", local_rank) if dev.type == "cuda" and dev.index is None else dev
+
+
+def _control_barrier(group, label: str, timeout_s: float = 30.0) -> None:
+    """Host-side barrier on the gloo control group with a deadline: a rank that
+    never arrives produces an error naming the barrier instead of a silent hang."""
+    if group is None:
+        return
+    import datetime
+    try:
+        dist.monitored_barrier(group=group, timeout=datetime.timedelta(seconds=timeout_s))
+    except RuntimeError as exc:
+        faulthandler.dump_traceback(file=sys.stderr, all_threads=True)
+        raise RuntimeError(f"control barrier '{label}' timed out after {timeout_s:.0f}s: {exc}") from exc
+
+
+# ---------------------------------------------------------------------------
+# model / optimizer
+# ---------------------------------------------------------------------------
+def build_model(config: dict[str, Any], device: torch.device, dtype: torch.dtype) -> CareStudentLM:
+    return CareStudentLM(**ssm_constructor_kwargs(config)).to(device=device, dtype=dtype)
+
+
+def _apply_embed_init(model: CareStudentLM, config: dict[str, Any], device: torch.device) -> None:
+    """Optional pretrained embedding table (``embed_init_path``: a tensor or ``{"embed": tensor}``)."""
+    path = config.get("embed_init_path")
+    if not path:
+        return
+    blob = torch.load(path, map_location="cpu", weights_only=True)
+    table = blob["embed"] if isinstance(blob, dict) and "embed" in blob else blob
+    if tuple(table.shape) != tuple(model.embed.weight.shape):
+        raise ValueError(f"embed_init_path shape {tuple(table.shape)} does not match embed.weight "
+                         f"{tuple(model.embed.weight.shape)}")
+    with torch.no_grad():
+        model.embed.weight.copy_(table.to(device=device, dtype=model.embed.weight.dtype))
+
+
+def _build_optimizer(config: dict[str, Any], model: torch.nn.Module, *, rank: int = 0) -> torch.optim.Optimizer:
+    name = str(config.get("optimizer", "muon")).strip()
+    lr, wd = float(config.get("base_lr", 0.128)), float(config.get("weight_decay", 0.01))
+    named = list(model.named_parameters())
+    params = build_optimizer_params(named, grouping=str(config.get("optimizer_param_grouping", "flat")).strip(),
+                                    base_lr=lr, weight_decay=wd,
+                                    dynamics_lr_mul=float(config.get("optimizer_dynamics_lr_mul", 0.1)))
+    if name == "adamw":
+        return torch.optim.AdamW(params, lr=lr, weight_decay=wd)
+    if name == "lamb":
+        return LAMB(params, lr=lr, weight_decay=wd)
+    if name == "muon":
+        opt = Muon(params, lr=lr, weight_decay=wd, adamw_lr=lr, adamw_weight_decay=wd,
+                   fused=bool(config.get("fused_muon", True)),
+                   log_a_beta_coupling=bool(config.get("optimizer_log_a_beta_coupling", False)),
+                   log_a_beta_ema=float(config.get("optimizer_log_a_beta_ema", 0.99)),
+                   log_a_beta_min=float(config.get("optimizer_log_a_beta_min", 0.5)))
+        opt.bind_param_names(named)
+        if get_arena(model) is not None:
+            opt.bind_arena(get_arena(model))
+        wrap_optimizer_step(opt, model=model, target_momentum=float(config.get("muon_momentum", 0.95)),
+                            warmup_start=float(config.get("muon_momentum_warmup_start", 0.95)),
+                            warmup_steps=int(config.get("muon_momentum_warmup_steps", 0)),
+                            weight_ema_decay=float(config.get("weight_ema_decay", 0.0)), is_rank_zero=rank == 0,
+                            weight_ema_fake_quant_bits=int(config.get("weight_ema_fake_quant_bits", 0)))
+        return opt
+    if name == "semantic":
+        from .optim.semantic import SemanticOptimizer, semantic_optimizer_config
+        opt = SemanticOptimizer(params, lr=lr, weight_decay=wd, adamw_lr=lr, adamw_weight_decay=wd,
+                                momentum_min=float(config.get("semantic_momentum_min", 0.5)),
+                                **semantic_optimizer_config(model, int(config.get("semantic_layer_index", 0))))
+        opt.bind_param_names(named)
+        return opt
+    if name in {"scopt", "scarcity", "scarcity_aware"}:
+        from .optim.scopt import ScarcityAwareOptimizer, scopt_optimizer_config
+        opt = ScarcityAwareOptimizer(
+            params, lr=lr, weight_decay=wd, adamw_lr=lr, adamw_weight_decay=wd,
+            warmup_steps=int(config.get("scopt_warmup_steps", 200)),
+            rare_ema_decay=float(config.get("scopt_rare_ema_decay", 0.9)),
+            rare_orthogonal_weight=float(config.get("scopt_rare_orthogonal_weight", 1.0)),
+            rare_macro_c=float(config.get("scopt_rare_macro_c", 0.5)),
+            row_scarcity_power=float(config.get("scopt_row_scarcity_power", 0.5)),
+            tau_std_scale=float(config.get("scopt_tau_std_scale", 0.5)),
+            **scopt_optimizer_config(model, int(config.get("scopt_layer_index", 0))))
+        opt.bind_param_names(named)
+        return opt
+    raise ValueError(f"unknown optimizer {name!r}")
+
+
+def _state_dict_clone(model: torch.nn.Module) -> dict[str, torch.Tensor]:
+    return {k: v.detach().clone() for k, v in model.state_dict().items() if torch.is_tensor(v)}
+
+
+def _restore_state_dict(model: torch.nn.Module, saved: dict[str, torch.Tensor]) -> None:
+    with torch.no_grad():
+        own = model.state_dict()
+        for k, v in saved.items():
+            own[k].copy_(v)
+
+
+def _load_checkpoint_into_model_for_runner(model: torch.nn.Module, path: str) -> dict[str, Any]:
+    blob = torch.load(path, map_location="cpu", weights_only=False)
+    sd = blob.get("model", blob) if isinstance(blob, dict) else blob
+    model.load_state_dict(sd, strict=True)
+    return {"checkpoint_path": str(path), "online_eval_state": blob.get("online_eval_state") if isinstance(blob, dict) else None}
+
+
+def _save_output_ckpt(path: str, model: torch.nn.Module, config: dict[str, Any], *, episodic_cache=None,
+                      online_eval_state=None) -> None:
+    """``{"model": state_dict, "config": config[, "episodic_cache", "online_eval_state"]}``,
+    written to a temporary file and renamed."""
+    out = Path(path)
+    out.parent.mkdir(parents=True, exist_ok=True)
+    blob: dict[str, Any] = {"model": {k: (v.detach().cpu() if torch.is_tensor(v) else v)
+                                      for k, v in model.state_dict().items()}, "config": dict(config)}
+    if episodic_cache is not None:
+        blob["episodic_cache"] = episodic_cache
+    if online_eval_state:
+        blob["online_eval_state"] = online_eval_state
+    tmp = out.with_suffix(out.suffix + ".tmp")
+    torch.save(blob, tmp)
+    tmp.rename(out)
+
+
+# ---------------------------------------------------------------------------
+# training
+# ---------------------------------------------------------------------------
+def _clip(model: torch.nn.Module, max_norm: float, fused: bool) -> None:
+    if max_norm <= 0:
+        return
+    arena = get_arena(model)
+    if arena is not None and arena.grads_fresh:
+        clip_arena_grad_norm(arena, max_norm)
+        arena.materialize_grads()
+    elif fused:
+        clip_grad_norm_fused(model.parameters(), max_norm)
+    else:
+        torch.nn.utils.clip_grad_norm_(model.parameters(), max_norm)
+
+
+def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor, train_num_tokens: int, stride: int,
+                          seq_len: int, batch_size: int, device: torch.device, optimizer: torch.optim.Optimizer,
+                          budget_seconds: float, chunk_size: int = 64, grad_clip_norm: float = 1.0,
+                          fused_grad_clip: bool = True, rank: int = 0, world_size: int = 1, seed: int = 0,
+                          precision: str = "bf16", stop_check_interval: int = 4, stop_margin_seconds: float = 2.0,
+                          vocab_size: Optional[int] = None, max_steps: Optional[int] = None,
+                          compile_full_path: bool = False, prefetch_batches: bool = True,
+                          lm_head_backward_mode: str = "fused_streaming_cached", lm_head_tile_size: int = 8192,
+                          cuda_graph_mode: str = "none", train_sampling_mode: str = "random",
+                          fast_slow: Optional[FastSlowConsolidator] = None, embed_freeze_steps: int = 0,
+                          distributed_muon: bool = False, time_fn: Callable[[], float] = time.perf_counter,
+                          **unused: Any) -> dict[str, Any]:
+    """Budgeted hot loop.  Returns the train-result dict (``steps``, ``elapsed_s``,
+    ``initial_loss``, ``final_loss``, ``loss_history``, throughput keys,
+    ``peak_vram_mb`` ...)."""
+    _reject_unsupported(model)
+    bad = [k for k in UNSUPPORTED_OPTIONS if unused.get(k)]
+    if bad:
+        raise NotImplementedError(f"options {bad} are not supported by this runner")
+    ddp = world_size > 1
+    if ddp:
+        broadcast_params(model)
+    model.train()
+    mode = str(train_sampling_mode).strip().lower()
+    sampler = {"random": None, "sequential_epoch": FP.SequentialShardedStartSampler(),
+               "shuffled_epoch": FP.ShuffledEpochShardedStartSampler(seed=seed)}.get(mode, "bad")
+    if sampler == "bad":
+        raise ValueError(f"train_sampling_mode must be random, sequential_epoch or shuffled_epoch; got {mode!r}")
+    gen = torch.Generator().manual_seed(int(seed) + int(rank))
+    prefetch = FP.BatchPrefetcher(tokens=train_tokens[:train_num_tokens], seq_len=seq_len, stride=stride,
+                                  batch_size=batch_size, rank=rank, world_size=world_size, device=device,
+                                  generator=gen, vocab_size=vocab_size, batch_sampler=sampler)
+    if prefetch_batches:
+        prefetch.prime()
+    dist_opt = None
+    if distributed_muon and ddp and isinstance(optimizer, Muon):
+        from .parallel import symm
+        from .parallel.dist_muon import DistributedMuon
+        arena = get_arena(model)
+        if arena is not None:
+            dist_opt = DistributedMuon(optimizer, arena, comm=symm.active_comm(None), grad_clip_norm=grad_clip_norm)
+    if device.type == "cuda":
+        torch.cuda.reset_peak_memory_stats(device)
+    losses: list[torch.Tensor] = []
+    step_times: list[float] = []
+    steps = 0
+    epoch_steps = (FP.sequential_epoch_steps(num_tokens=train_num_tokens, seq_len=seq_len, stride=stride,
+                                             batch_size=batch_size, world_size=world_size)
+                   if mode != "random" else None)
+    t0 = time_fn()
+    try:
+        while True:
+            if steps % max(1, int(stop_check_interval)) == 0:
+                local = FP.should_stop_training_loop(steps=steps, elapsed_s=time_fn() - t0,
+                                                     budget_seconds=budget_seconds,
+                                                     stop_margin_seconds=stop_margin_seconds, max_steps=max_steps)
+                if epoch_steps is not None and steps >= epoch_steps:
+                    local = True
+                if should_stop_now(local, device, ddp):
+                    break
+            elif max_steps is not None and steps >= max_steps:
+                break
+            ts = time_fn()
+            inputs, targets = prefetch.next()
+            optimizer.zero_grad(set_to_none=True)
+            loss = train_ssm_step(model, inputs, targets, chunk_size, ddp_active=ddp and dist_opt is None,
+                                  world_size=world_size, precision=precision, compile_full_path=compile_full_path,
+                                  lm_head_backward_mode=lm_head_backward_mode, lm_head_tile_size=lm_head_tile_size)
+            zero_embedding_grad_until(model, steps, embed_freeze_steps)
+            if dist_opt is not None:
+                dist_opt.step()                     # reduce (sharded) + clip + owned update + gather
+            else:
+                _clip(model, grad_clip_norm, fused_grad_clip)
+                optimizer.step()
+            if precision == "fp8_fused":
+                from .ops.fp8_linear import fused_fp8_flush_all
+                fused_fp8_flush_all(model)
+            steps += 1
+            if fast_slow is not None and fast_slow.enabled:
+                fast_slow.after_optimizer_step(model, step=steps)
+            losses.append(loss.detach())
+            step_times.append(time_fn() - ts)
+    finally:
+        prefetch.close()
+    if device.type == "cuda":
+        torch.cuda.synchronize(device)
+    elapsed = time_fn() - t0
+    hist = torch.stack([l.float() for l in losses]).cpu().tolist() if losses else []
+    result: dict[str, Any] = {
+        "steps": steps, "elapsed_s": elapsed, "rank": rank, "world_size": world_size,
+        "initial_loss": hist[0] if hist else float("nan"), "final_loss": hist[-1] if hist else float("nan"),
+        "loss_history": hist, "peak_vram_mb": (torch.cuda.max_memory_allocated(device) / 2 ** 20
+                                               if device.type == "cuda" else 0.0),
+        "steady_state_step_seconds": FP.steady_state_step_seconds(step_times) if step_times else float("nan"),
+        "train_sampling_mode": mode, "lm_head_backward_mode": lm_head_backward_mode,
+        "cuda_graph_mode": str(cuda_graph_mode), "distributed_muon": dist_opt is not None,
+        "spectral": spectral_summary(model),
+    }
+    result.update(FP.summarize_train_timing(steps=steps, elapsed_s=elapsed, batch_size=batch_size, seq_len=seq_len,
+                                            world_size=world_size))
+    if fast_slow is not None:
+        result["fast_slow"] = fast_slow.diagnostics(model)
+    return result
+
+
+_LOOP_KEYS = ("chunk_size", "grad_clip_norm", "fused_grad_clip", "precision", "stop_check_interval",
+              "stop_margin_seconds", "compile_full_path", "prefetch_batches", "lm_head_backward_mode",
+              "lm_head_tile_size", "cuda_graph_mode", "train_sampling_mode", "embed_freeze_steps",
+              "distributed_muon") + UNSUPPORTED_OPTIONS
+
+
+def _loop_kwargs(config: dict[str, Any]) -> dict[str, Any]:
+    return {k: config[k] for k in _LOOP_KEYS if k in config}
+
+
+def _warmup(*, model, train_tokens, train_num_tokens, stride, seq_len, batch_size, device, optimizer, config, rank,
+            world_size, seed, vocab_size) -> None:
+    """``warmup_steps`` untimed steps (kernel selection, allocator growth, peer buffers)."""
+    steps = int(config.get("warmup_steps", 0))
+    if steps <= 0:
+        return
+    kw = _loop_kwargs(config)
+    kw.update(stop_check_interval=1, stop_margin_seconds=0.0, cuda_graph_mode="none")
+    train_fast_for_budget(model, train_tokens=train_tokens, train_num_tokens=train_num_tokens, stride=stride,
+                          seq_len=seq_len, batch_size=batch_size, device=device, optimizer=optimizer,
+                          budget_seconds=300.0, rank=rank, world_size=world_size, seed=seed, vocab_size=vocab_size,
+                          max_steps=steps, **kw)
+
+
+# ---------------------------------------------------------------------------
+# run_condition
+# ---------------------------------------------------------------------------
+def run_condition(config: dict[str, Any], *, data_path: str, sp_model_path: Optional[str], budget_seconds: float,
+                  output_json: Optional[str], output_ckpt: Optional[str], world_size_override: Optional[int],
+                  val_cache_dir: Optional[str] = None) -> dict[str, Any]:
+    _enable_runner_stack_dump_signal()
+    rank, world_size, local_rank = _init_distributed(world_size_override)
+    ddp = world_size > 1
+    control = dist.new_group(list(range(world_size)), backend="gloo") if ddp else None
+    device = _pick_device(local_rank, str(config.get("device", "auto")))
+    dtype = resolve_param_dtype(str(config.get("dtype", "bf16")), device)
+    seed = int(config.get("seed", 1337))
+    random.seed(seed)
+    np.random.seed(seed)
+    torch.manual_seed(seed)
+    verify_diag_recurrence(device)
+    vocab = int(config["vocab_size"])
+    eval_only = bool(config.get("eval_only", False))
+    calc_types = list(config.get("calc_types") or [])
+    if eval_only:
+        train_tokens = torch.empty(0, dtype=torch.int16)
+        val_tokens = torch.empty(0, dtype=torch.int16) if calc_types else load_fineweb_val_tokens(data_path)
+    else:
+        train_tokens, val_tokens = load_fineweb_tokens(data_path)
+    luts = (None, None, None)
+    if sp_model_path:
+        import sentencepiece as spm
+
+        from .sp_eval import build_sentencepiece_luts
+        sp = spm.SentencePieceProcessor()
+        sp.Load(sp_model_path)
+        luts = build_sentencepiece_luts(sp, vocab, device)
+    seq_len = int(config["seq_len"])
+    stride = int(config.get("stride", seq_len // 2))
+    batch = int(config["batch_size"])
+    eval_batches = int(config.get("eval_batches", 0))
+    eval_starts = FP.choose_lm_starts_lazy(num_tokens=int(val_tokens.numel()), seq_len=seq_len, stride=stride,
+                                           batch_size=batch, eval_batches=max(0, eval_batches), seed=seed)
+    model = build_model(config, device, dtype)
+    _apply_embed_init(model, config, device)
+    _reject_unsupported(model)
+    n_params = sum(p.numel() for p in model.parameters())
+    ckpt_meta = None
+    if str(config.get("checkpoint_path", "") or "").strip():
+        ckpt_meta = _load_checkpoint_into_model_for_runner(model, str(config["checkpoint_path"]).strip())
+    elif eval_only:
+        raise ValueError("eval_only=True requires config.checkpoint_path")
+    if rank == 0:
+        print(f"[rank 0/{world_size}] {config.get('name', '<unnamed>')} vocab={vocab} batch={batch} "
+              f"params={n_params:,}", flush=True)
+    # flat parameter / gradient arena: required by the kernel engine, the flat-buffer optimizer
+    # kernels, the peer-memory collectives and the distributed optimizer
+    from .engine import TrainEngine
+    from .utils.arena import ParamArena
+    arena = None
+    if TrainEngine.supported(model) or bool(config.get("distributed_muon", False)):
+        arena = ParamArena.install(model)
+    if ddp and device.type == "cuda" and arena is not None:
+        from .parallel import symm_comm
+        symm_comm.try_enable(arena.flat_grad.numel())      # peer-memory collectives; NCCL remains the fallback
+
+    train_result: dict[str, Any]
+    optimizer = None
+    fast_slow = None
+    if eval_only:
+        train_result = {"steps": 0, "elapsed_s": 0.0, "initial_loss": 0.0, "final_loss": 0.0,
+                        "aggregate_tokens_per_sec": 0.0, "peak_vram_mb": 0.0, "eval_only": True}
+    else:
+        common = dict(model=model, train_tokens=train_tokens, train_num_tokens=int(train_tokens.numel()),
+                      stride=stride, seq_len=seq_len, batch_size=batch, device=device, rank=rank,
+                      world_size=world_size, seed=seed, vocab_size=vocab)
+        restore = bool(config.get("restore_after_warmup", False)) and int(config.get("warmup_steps", 0)) > 0
+        saved = _state_dict_clone(model) if restore else None
+        optimizer = _build_optimizer(config, model, rank=rank)
+        _warmup(optimizer=optimizer, config=config, **common)
+        if saved is not None:
+            _restore_state_dict(model, saved)
+            optimizer = _build_optimizer(config, model, rank=rank)
+            if ddp:
+                dist.barrier()
+        fast_slow = FastSlowConsolidator.from_config(model, config)
+        common.pop("model")
+        train_result = train_fast_for_budget(
+            model, optimizer=optimizer, budget_seconds=budget_seconds, fast_slow=fast_slow,
+            max_steps=None if config.get("max_steps") is None else int(config["max_steps"]),
+            **common, **_loop_kwargs(config))
+    if ddp:
+        _control_barrier(control, "post_train")
+
+    eval_result: dict[str, Any] = {}
+    if rank == 0 and (eval_batches > 0 or calc_types):
+        from .eval import dispatch_eval_for_config
+        from .sp_eval import evaluate_bpb_sp
+        val_cache = None
+        if calc_types:
+            if not val_cache_dir:
+                raise ValueError("config sets calc_types but --val-cache-dir was not provided to the runner")
+            from .eval_stream import load_val_cache
+            val_cache = load_val_cache(Path(val_cache_dir))
+        slow_backup = None
+        if fast_slow is not None and fast_slow.should_copy_slow_to_model_for_eval():
+            slow_backup = _state_dict_clone(model)
+            fast_slow.copy_slow_to_model(model)
+
+        def _do_eval():
+            return dispatch_eval_for_config(
+                config, model=model, val_cache=val_cache, val_tokens=val_tokens, eval_starts=eval_starts,
+                batch_size=batch, seq_len=seq_len, device=device, base_bytes_lut=luts[0],
+                has_leading_space_lut=luts[1], is_boundary_token_lut=luts[2], legacy_evaluate_fn=evaluate_bpb_sp)
+        eval_result = eval_with_ema(model, getattr(optimizer, "_weight_ema", None), _do_eval)
+        if slow_backup is not None:
+            _restore_state_dict(model, slow_backup)
+    if ddp:
+        _control_barrier(control, "post_eval", timeout_s=float(config.get("eval_barrier_timeout_s", 3600.0)))
+
+    result = {
+        "config": config, "params": n_params, "train": train_result, "eval": eval_result,
+        "artifact": {"artifact_impact": str(config.get("artifact_impact", "artifact_changes_weights_only")),
+                     "submit_valid": bool(config.get("submit_valid", True)),
+                     "artifact_bytes_estimate": int(model.artifact_bytes()),
+                     "compressed_artifact_bytes": config.get("compressed_artifact_bytes")},
+        "exp24": {"phase": config.get("exp24_phase"), "mechanism": config.get("exp24_mechanism")},
+    }
+    if ckpt_meta is not None:
+        result["checkpoint"] = {"checkpoint_path": ckpt_meta["checkpoint_path"]}
+    if rank == 0:
+        bad = [f"train.{k} is not finite" for k in ("initial_loss", "final_loss")
+               if not math.isfinite(float(train_result.get(k, float("nan"))))]
+        bad += [f"eval.{k} is not finite" for k in ("bpb", "loss")
+                if k in eval_result and not math.isfinite(float(eval_result[k]))]
+        if bad:
+            raise RuntimeError("; ".join(bad))
+        if output_json:
+            out = Path(output_json)
+            out.parent.mkdir(parents=True, exist_ok=True)
+            tmp = out.with_suffix(out.suffix + ".tmp")
+            tmp.write_text(json.dumps(result, indent=2, default=str))
+            tmp.rename(out)
+        if output_ckpt:
+            _save_output_ckpt(output_ckpt, model, config)
+        print(f"[rank 0/{world_size}] done steps={train_result['steps']} "
+              f"tok/s={train_result.get('aggregate_tokens_per_sec', 0.0):.0f} "
+              f"loss={train_result['final_loss']:.4f} vram={train_result.get('peak_vram_mb', 0.0):.1f}MB", flush=True)
+    if ddp and dist.is_initialized():
+        dist.destroy_process_group()
+    return result
+
+
+def main(argv: Optional[list[str]] = None) -> int:
+    import yaml
+    ap = argparse.ArgumentParser(description="throughput runner (train + eval)")
+    ap.add_argument("--config", required=True)
+    ap.add_argument("--data-path", required=True)
+    ap.add_argument("--sp-model-path", default=None)
+    ap.add_argument("--budget", type=float, default=None)
+    ap.add_argument("--output-json", default=None)
+    ap.add_argument("--output-ckpt", default=None)
+    ap.add_argument("--world-size", type=int, default=None)
+    ap.add_argument("--val-cache-dir", default=None,
+                    help="ValCache directory (tokens.npy / docs.npy / manifest.json); required with calc_types")
+    a = ap.parse_args(argv)
+    config = yaml.safe_load(Path(a.config).read_text())
+    run_condition(config, data_path=a.data_path, sp_model_path=a.sp_model_path,
+                  budget_seconds=float(a.budget) if a.budget is not None else float(config.get("budget_seconds", 90.0)),
+                  output_json=a.output_json, output_ckpt=a.output_ckpt, world_size_override=a.world_size,
+                  val_cache_dir=a.val_cache_dir)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -1,0 +1,203 @@
+"""Production runner end to end on CPU (tiny model, synthetic shards), the training
+hooks, and the launch helpers."""
+import json
+
+import numpy as np
+import pytest
+import torch
+
+from chaoscontrol_b200 import launch
+from chaoscontrol_b200 import training_hooks as TH
+from chaoscontrol_b200.models.model import CareStudentLM
+from chaoscontrol_b200.runner_fast_path import run_condition, train_fast_for_budget, _build_optimizer
+
+
+def _shards(tmp_path, vocab=64, n=20000):
+    rng = np.random.default_rng(0)
+    rng.integers(0, vocab, n, dtype=np.uint16).tofile(tmp_path / "fineweb_train_000.bin")
+    rng.integers(0, vocab, n // 4, dtype=np.uint16).tofile(tmp_path / "fineweb_val_000.bin")
+
+
+def _config(**kw):
+    cfg = dict(name="tiny", vocab_size=64, model_dim=16, num_layers=2, ff_mult=2, seq_len=16, stride=8, batch_size=4,
+               dtype="fp32", precision="fp32", device="cpu", optimizer="muon", base_lr=0.02, warmup_steps=2,
+               restore_after_warmup=True, max_steps=6, eval_batches=2, lm_head_backward_mode="fused",
+               stop_check_interval=2, fast_slow_enabled=True, fast_slow_interval=2, fast_slow_alpha=0.5,
+               weight_ema_decay=0.9, seed=3)
+    cfg.update(kw)
+    return cfg
+
+
+class _FakeSP:
+    """Four control tokens, byte tokens, then pieces (some with the leading-space marker)."""
+
+    def vocab_size(self):
+        return 64
+
+    def is_control(self, t):
+        return t < 2
+
+    def is_unknown(self, t):
+        return t == 2
+
+    def is_unused(self, t):
+        return t == 3
+
+    def is_byte(self, t):
+        return 4 <= t < 10
+
+    def id_to_piece(self, t):
+        return ("▁" if t % 2 else "") + "ab"[: 1 + t % 2]
+
+
+def test_sentencepiece_luts_and_byte_counts():
+    from chaoscontrol_b200.sp_eval import build_sentencepiece_luts, token_byte_counts
+    base, lead, boundary = build_sentencepiece_luts(_FakeSP(), 70, "cpu")
+    assert base.shape == (70,) and boundary[:4].all() and not boundary[4:64].any() and boundary[64:].all()
+    assert base[5] == 1 and base[11] == 2 and lead[11] and base[12] == 1 and not lead[12]
+    prev = torch.tensor([0, 12, 12])
+    tgt = torch.tensor([11, 11, 12])
+    # leading space counts unless the previous token is a boundary token
+    assert token_byte_counts(prev, tgt, base, lead, boundary).tolist() == [2, 3, 1]
+
+
+def test_run_condition_cpu_end_to_end(tmp_path, monkeypatch):
+    _shards(tmp_path)
+    import chaoscontrol_b200.runner_fast_path as R
+    import sys
+    import types
+    fake = types.ModuleType("sentencepiece")
+
+    class _Proc(_FakeSP):
+        def Load(self, path):
+            return True
+    fake.SentencePieceProcessor = _Proc
+    monkeypatch.setitem(sys.modules, "sentencepiece", fake)
+    out_json, out_ckpt = tmp_path / "res" / "tiny.json", tmp_path / "res" / "tiny.pt"
+    res = run_condition(_config(), data_path=str(tmp_path), sp_model_path="fake.model", budget_seconds=30.0,
+                        output_json=str(out_json), output_ckpt=str(out_ckpt), world_size_override=None)
+    tr = res["train"]
+    assert tr["steps"] == 6 and len(tr["loss_history"]) == 6 and np.isfinite(tr["final_loss"])
+    assert tr["tokens_per_step"] == 64 and tr["aggregate_tokens_per_sec"] > 0
+    assert tr["fast_slow"]["sync_count"] == 3 and tr["spectral"]["log_a_param_count"] == 2
+    assert 0 < res["eval"]["bpb"] < 20 and res["eval"]["tokens"] == 2 * 4 * 16
+    saved = json.loads(out_json.read_text())
+    assert saved["params"] == res["params"] and saved["artifact"]["artifact_bytes_estimate"] == 2 * res["params"]
+    ck = torch.load(out_ckpt, weights_only=False)
+    m = CareStudentLM(vocab_size=64, dim=16, num_layers=2)
+    m.load_state_dict(ck["model"])
+    # eval-only pass from that checkpoint reproduces the evaluation
+    ev = run_condition(_config(eval_only=True, checkpoint_path=str(out_ckpt), fast_slow_enabled=False),
+                       data_path=str(tmp_path), sp_model_path="fake.model", budget_seconds=1.0, output_json=None,
+                       output_ckpt=None, world_size_override=None)
+    assert ev["train"]["steps"] == 0 and np.isfinite(ev["eval"]["bpb"])
+    with pytest.raises(NotImplementedError):
+        run_condition(_config(crct_enabled=True, warmup_steps=0), data_path=str(tmp_path), sp_model_path=None,
+                      budget_seconds=1.0, output_json=None, output_ckpt=None, world_size_override=None)
+    with pytest.raises(ValueError):
+        run_condition(_config(), data_path=str(tmp_path), sp_model_path=None, budget_seconds=1.0, output_json=None,
+                      output_ckpt=None, world_size_override=4)
+
+
+@pytest.mark.parametrize("mode,opt", [("sequential_epoch", "adamw"), ("shuffled_epoch", "lamb")])
+def test_train_loop_epoch_modes_stop_after_one_epoch(tmp_path, mode, opt):
+    torch.manual_seed(0)
+    tokens = torch.randint(0, 64, (600,), dtype=torch.int16)
+    model = CareStudentLM(vocab_size=64, dim=16, num_layers=1)
+    optim = _build_optimizer(dict(optimizer=opt, base_lr=1e-3), model)
+    res = train_fast_for_budget(model, train_tokens=tokens, train_num_tokens=600, stride=8, seq_len=16, batch_size=8,
+                                device=torch.device("cpu"), optimizer=optim, budget_seconds=600.0, precision="fp32",
+                                stop_check_interval=1, train_sampling_mode=mode, lm_head_backward_mode="chunked",
+                                prefetch_batches=False)
+    assert res["steps"] == 10                       # ceil(73 starts / 8)
+    with pytest.raises(ValueError):
+        train_fast_for_budget(model, train_tokens=tokens, train_num_tokens=600, stride=8, seq_len=16, batch_size=8,
+                              device=torch.device("cpu"), optimizer=optim, budget_seconds=1.0,
+                              train_sampling_mode="nope")
+
+
+class _Heads:
+    def __init__(self):
+        self.rewards, self.credits = [], []
+
+    def readiness(self, head):
+        return 1.0
+
+    def scalar_value(self, *, head_name, gpu_step, fallback, reward_context):
+        return 0.5 if head_name == "consolidation" else 0.4
+
+    def record_credit_assignment(self, **kw):
+        self.credits.append(kw)
+
+    def apply_reward(self, *, key, reward, gpu_step, reward_context):
+        self.rewards.append((key, reward))
+        return 1
+
+
+def test_fast_slow_consolidator_interval_learned_and_eval_copy():
+    torch.manual_seed(0)
+    m = CareStudentLM(vocab_size=32, dim=8, num_layers=1)
+    c = TH.FastSlowConsolidator.from_config(m, dict(fast_slow_enabled=True, fast_slow_interval=2, fast_slow_alpha=0.25))
+    w0 = m.embed.weight.detach().clone()
+    with torch.no_grad():
+        m.embed.weight.add_(1.0)
+    assert c.after_optimizer_step(m, step=1).mode == "hold" and not c.should_copy_slow_to_model_for_eval()
+    d = c.after_optimizer_step(m, step=2)
+    assert d.mode == "interval" and d.accepted
+    assert torch.allclose(c.slow_state["embed.weight"], w0 + 0.25)
+    heads = _Heads()
+    d = c.after_optimizer_step(m, step=3, action_space=heads, loss_value=2.0)
+    assert d.mode == "learned" and d.effective_alpha == pytest.approx(0.2) and heads.credits[0]["key"] == 3
+    c.after_optimizer_step(m, step=4, action_space=heads, loss_value=1.5)
+    assert heads.rewards == [(3, 0.5)] and c.last_reward == 0.5
+    diag = c.diagnostics(m)
+    assert diag["sync_count"] == 3 and diag["learned_sync_count"] == 2 and diag["fast_slow_l2"] > 0
+    c.copy_slow_to_model(m)
+    assert c.diagnostics(m)["fast_slow_l2"] == pytest.approx(0.0, abs=1e-6)
+    rt = TH.fast_slow_decision_from_dict(TH.fast_slow_decision_to_dict(d))
+    assert rt == d and TH.fast_slow_decision_from_dict("x") is None
+    off = TH.FastSlowConsolidator.from_config(m, {})
+    assert off.after_optimizer_step(m, step=2).mode == "disabled"
+
+
+def test_spectral_predictive_and_freeze_hooks():
+    m = CareStudentLM(vocab_size=32, dim=8, num_layers=2)
+    with torch.no_grad():
+        m.layers[0].core.log_a.fill_(-6.0)            # a ~ 0.0025: dead
+        m.layers[1].core.log_a.fill_(6.0)             # a ~ 0.9975: sticky
+    loss = TH.spectral_regularization_loss(m, 1.0, 2.0, 0.05, 0.95)
+    a0, a1 = torch.sigmoid(torch.tensor(-6.0)), torch.sigmoid(torch.tensor(6.0))
+    assert float(loss.detach()) == pytest.approx(float(((0.05 - a0) ** 2 + 2 * (a1 - 0.95) ** 2) / 2), rel=1e-5)
+    s = TH.spectral_summary(m)
+    assert s["log_a_param_count"] == 2 and s["a_min"] < 0.01 < 0.99 < s["a_max"]
+    h = torch.randn(2, 10, 8)
+    proj = torch.nn.Linear(8, 8)
+    assert TH.predictive_auxiliary_loss(h, projection=proj, horizon=3) > 0
+    assert TH.predictive_auxiliary_loss(h, projection=proj, horizon=10) is None
+    m.embed.weight.grad = torch.ones_like(m.embed.weight)
+    TH.zero_embedding_grad_until(m, step=5, freeze_steps=5)
+    assert m.embed.weight.grad.sum() > 0
+    TH.zero_embedding_grad_until(m, step=4, freeze_steps=5)
+    assert m.embed.weight.grad.sum() == 0
+
+
+def test_launch_helpers(tmp_path):
+    cmd = launch.build_torchrun_cmd(config_path=tmp_path / "c.yaml", data_path="/d", sp_model_path="/sp",
+                                    output_json=tmp_path / "o.json", world_size=8, dry_run=True, budget_seconds=90,
+                                    output_ckpt=tmp_path / "o.pt", val_cache_dir="/vc")
+    assert cmd[1:3] == ["-m", "torch.distributed.run"] and "--nproc-per-node=8" in cmd and "127.0.0.1" in cmd
+    assert cmd[cmd.index("--master-port") + 1] == "0" and "-m" in cmd[3:] and "--val-cache-dir" in cmd
+    p = launch.write_entry_config({"name": "e1", "batch_size": 4}, tmp_path / "cfg")
+    assert p.name == "e1.yaml"
+    (tmp_path / "r").mkdir()
+    (tmp_path / "r" / "a.json").write_text(json.dumps({"config": {"name": "a"}, "train": {
+        "aggregate_tokens_per_sec": 5.0, "steps": 3, "final_loss": 1.0}, "eval": {"bpb": 1.5}}))
+    (tmp_path / "r" / "b.json").write_text(json.dumps({"config": {"name": "b"}, "train": {
+        "aggregate_tokens_per_sec": 9.0, "steps": 3, "final_loss": 1.0}}))
+    (tmp_path / "r" / "c.json").write_text(json.dumps({"config": {"name": "c"}, "error": "boom"}))
+    s = launch.summarize_result_dir(tmp_path / "r")
+    assert [r["name"] for r in s["ranked"]] == ["b", "a"] and s["errors"] == [{"name": "c", "error": "boom"}]
+    dry = launch.run_matrix([{"name": "x", "budget_seconds": 5}], results_dir=tmp_path / "m", data_path="/d",
+                            sp_model_path=None, world_size=2, dry_run=True)
+    assert len(dry["commands"]) == 1 and (tmp_path / "m" / "configs" / "x.yaml").exists()
+    assert 1024 < launch.pick_free_port() < 65536

@@ -32,7 +32,12 @@ enum CcbEpilogue {
   CCB_EPI_ROWSCALE_SILU = 2,  // u = rs(m) * acc -> C ; silu(u) -> C2
   CCB_EPI_RESID_SS = 3,       // out = R1 + acc ; ss_out[m] (+)= sum_n out^2
   CCB_EPI_DSILU = 4,          // out = acc * silu'(R1) * rs(m)
-  CCB_EPI_RMSBWD = 5,         // out = R2 + acc - R1 * (rs^2 * inv_dim * sum_n acc * R1)   (N <= tile)
+  CCB_EPI_RMSBWD = 5,         // out = R2 + acc - R1 * (rs^2 * inv_dim * sum_n acc * R1)   (N <= 512)
+  // LM head for model dims the single-kernel fused head does not take (logits = rs(m) * acc):
+  CCB_EPI_LSE_PART = 6,       // no C; part_out[(tile_n*2 + half) * M + m] = (max, sum 2^(z - max)) of
+                              // z = logits * log2(e) over the half tile; zt_out[m] = logits[m, targets[m]]
+  CCB_EPI_CE_GRAD = 7,        // out = (exp(logits - lse[m]) - [n == targets[m]]) * alpha * rowweight[m] * rs(m);
+                              // zt_out[m] = lse[m] - logits[m, targets[m]]  (the row's cross-entropy)
 };
 
 typedef struct CcbGemmArgs {
@@ -60,9 +65,20 @@ typedef struct CcbGemmArgs {
   const float* dscale_a;                     // optional device scalars: alpha *= *dscale_a * *dscale_b
   const float* dscale_b;
   const void* bias;                          // optional bf16 [N], added in the STORE epilogue
+  // LM-head epilogues
+  const int64_t* targets;                    // [M]
+  const float* lse;                          // [M] natural-log lse (CE_GRAD input)
+  const float* rowweight;                    // [M] or null
+  float* part_out;                           // [tiles_n * 2, M] float2 (LSE_PART)
+  float* zt_out;                             // [M] or null
 } CcbGemmArgs;
 
 int ccb_gemm(const CcbGemmArgs* args, void* stream);
+
+// lse[m] = ln sum_v exp(logits[m, v]) from the LSE_PART partials ([nparts, M] float2);
+// loss[m] = lse[m] - zt[m] when both pointers are given.
+int ccb_lse_combine(const float* part, int64_t nparts, int64_t M, const float* zt, float* lse, float* loss,
+                    void* stream);
 
 // ---- 8-bit float helpers (fmt: 1 = e4m3, 2 = e5m2) --------------------------
 // out = fp8(x / *scale), *pending = max(*pending, max|x|)

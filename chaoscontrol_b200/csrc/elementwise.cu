@@ -347,6 +347,25 @@ __global__ void sgd_kernel(__nv_bfloat16* __restrict__ p, const float* __restric
     p[i] = __float2bfloat16(__bfloat162float(p[i]) - lr * g[i]);
 }
 
+// lse[m] from per-(tile, half) partials (max, sum 2^(z - max)) in the log2 domain;
+// partials are laid out [nparts][M] so consecutive threads read consecutive rows.
+__global__ void lse_combine_kernel(const float2* __restrict__ part, int nparts, long long M,
+                                   const float* __restrict__ zt, float* __restrict__ lse,
+                                   float* __restrict__ loss) {
+  const long long m = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (m >= M) return;
+  float mx = -INFINITY;
+  for (int i = 0; i < nparts; ++i) mx = fmaxf(mx, __ldg(&part[(long long)i * M + m]).x);
+  float s = 0.f;
+  for (int i = 0; i < nparts; ++i) {
+    const float2 v = __ldg(&part[(long long)i * M + m]);
+    if (v.y > 0.f) s += v.y * exp2f(v.x - mx);
+  }
+  const float l = (mx + log2f(s)) * 0.6931471805599453f;
+  lse[m] = l;
+  if (loss != nullptr && zt != nullptr) loss[m] = l - zt[m];
+}
+
 __global__ void cast_f32_to_bf16_kernel(const float* __restrict__ s, __nv_bfloat16* __restrict__ d,
                                         long long n, float scale) {
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
@@ -547,6 +566,14 @@ extern "C" int ccb_sgd(void* p, const float* g, int64_t n, float lr, void* strea
   if (n <= 0) return 0;
   sgd_kernel<<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)p, g, n, lr);
   CCB_CHECK_LAUNCH("sgd");
+  return 0;
+}
+extern "C" int ccb_lse_combine(const float* part, int64_t nparts, int64_t M, const float* zt, float* lse,
+                               float* loss, void* stream) {
+  if (M <= 0) return 0;
+  lse_combine_kernel<<<(unsigned)((M + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      (const float2*)part, (int)nparts, (long long)M, zt, lse, loss);
+  CCB_CHECK_LAUNCH("lse_combine");
   return 0;
 }
 extern "C" int ccb_cast_f32_to_bf16(const float* s, void* d, int64_t n, float scale, void* stream) {

@@ -46,6 +46,14 @@ struct GemmKArgs {
   const float* dscale_a;
   const float* dscale_b;
   const void* bias;
+  // pair: one CTA computes both 256-column halves of a row block into the two
+  // accumulators and the epilogue treats them as one 512-column tile
+  int pair;
+  const long long* targets;
+  const float* lse;
+  const float* rowweight;
+  float2* part_out;
+  float* zt_out;
 };
 
 // bf16 outputs leave through shared-memory staging tiles and TMA stores: each
@@ -133,7 +141,17 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmKArgs& p, int tile, i
   return t;
 }
 
-template <int BN, int A_MN, int B_MN>
+constexpr float GEMM_LOG2E = 1.4426950408889634f;
+constexpr float GEMM_LN2 = 0.6931471805599453f;
+
+__device__ __forceinline__ float gemm_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// LM = 1 compiles the LM-head epilogues (LSE_PART, CE_GRAD) instead of the trunk set.
+template <int BN, int A_MN, int B_MN, int LM>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmC2,
@@ -193,6 +211,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         TileCoord t = decode_tile(p, tile, BN);
+        for (int hn = 0; hn <= p.pair && ok; ++hn, t.n0 += BN)
         for (int kb = t.kb0; kb < t.kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status)) { ok = false; break; }
           mbar_arrive_expect_tx(&full_bar[stage], A_STAGE_BYTES + B_STAGE_BYTES);
@@ -232,11 +251,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
         TileCoord t = decode_tile(p, tile, BN);
-        const int acc = it & 1;
-        const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+        const int acc = p.pair ? 0 : (it & 1);
+        const uint32_t acc_phase = (uint32_t)(p.pair ? it : (it >> 1)) & 1u;
         if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, abort_flag, p.status)) { ok = false; break; }
         tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int hn = 0; hn <= p.pair && ok; ++hn) {
+        const uint32_t d_tmem = tmem_base + (uint32_t)((p.pair ? hn : acc) * BN);
         for (int kb = t.kb0; kb < t.kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status)) { ok = false; break; }
           tc_fence_after_sync();
@@ -254,6 +274,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           }
           umma_commit(&empty_bar[stage]);   // stage reusable once these MMAs retire
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
         }
         if (ok) umma_commit(&tfull_bar[acc]);
       }
@@ -280,8 +301,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     };
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
       TileCoord t = decode_tile(p, tile, BN);
-      const int acc = it & 1;
-      const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+      const int acc = p.pair ? 0 : (it & 1);
+      const uint32_t acc_phase = (uint32_t)(p.pair ? it : (it >> 1)) & 1u;
       const uint32_t t_addr = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(q * 32) << 16);
       const int m = t.m0 + row_in_tile;
       const bool row_ok = m < p.M;
@@ -292,7 +313,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       float alpha = p.alpha;
       if (p.dscale_a != nullptr) alpha *= __ldg(p.dscale_a);
       if (p.dscale_b != nullptr) alpha *= __ldg(p.dscale_b);
-      const int ncols = min(BN, p.N - t.n0);   // valid columns in this tile
+      const int ncols = min(p.pair ? 2 * BN : BN, p.N - t.n0);   // valid columns in this tile
       const int nchunks = (ncols + 31) >> 5;
       // k-th 32-column chunk of this warp: groups part, part+2, ... two chunks each
       auto chunk_of = [&](int k) { return (((k >> 1) * EPI_PARTS + part) << 1) + (k & 1); };
@@ -383,8 +404,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       }
       tc_fence_after_sync();
 
+      // LM-head epilogues: log2-domain constants and running (max, sum)
+      float lm_c1 = 0.f, lm_c2 = 0.f, lm_gs = 0.f, run_m = -INFINITY, run_s = 0.f, lm_zt = 0.f;
+      int lm_tgt = -1;
+      bool lm_hit = false;
+      if (LM && row_ok) {
+        lm_c1 = rs * GEMM_LOG2E;
+        lm_tgt = (int)p.targets[m];
+        if (p.epi == CCB_EPI_CE_GRAD) {
+          lm_c2 = p.lse[m] * GEMM_LOG2E;
+          lm_gs = alpha * rs * (p.rowweight ? p.rowweight[m] : 1.f);
+        }
+      }
+
       float row_acc = 0.f;   // RESID_SS: sum of squares; RMSBWD: dot(acc, x)
-      if (p.epi == CCB_EPI_RMSBWD) {
+      if (!LM && p.epi == CCB_EPI_RMSBWD) {
         for (int k = 0; k < nmine; ++k) {
           const int c = chunk_of(k);
           uint32_t r[32];
@@ -426,6 +460,32 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 
+        if (LM) {
+          const int tl = lm_tgt - n;
+          if (p.epi == CCB_EPI_LSE_PART) {
+            float mx = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (i < nvalid) mx = fmaxf(mx, v[i]);
+            const float new_m = fmaxf(run_m, mx * lm_c1);
+            float sacc = 0.f;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              if (i < nvalid) sacc += gemm_ex2(fmaf(v[i], lm_c1, -new_m));
+              if (i == tl) { lm_zt = v[i] * rs; lm_hit = true; }
+            }
+            run_s = run_s * gemm_ex2(run_m - new_m) + sacc;
+            run_m = new_m;
+            continue;   // nothing is stored per column
+          }
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float z = fmaf(v[i], lm_c1, -lm_c2);
+            float pr = gemm_ex2(z);
+            if (i == tl) { pr -= 1.f; lm_zt = -z * GEMM_LN2; lm_hit = true; }
+            v[i] = pr * lm_gs;
+          }
+        } else
         switch (p.epi) {
           case CCB_EPI_STORE: {
             if (p.Cin != nullptr) {
@@ -519,14 +579,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           store_bf16x32(reinterpret_cast<__nv_bfloat16*>(p.C) + out_off + n, v, nvalid);
         }
       }
-      if (p.epi == CCB_EPI_RESID_SS && p.ss_out != nullptr) {
-        if (p.ss_atomic) {
-          if (row_ok) atomicAdd(p.ss_out + m, row_acc);
-        } else {
-          // one value per row: the second warp of the quadrant hands its half over
-          if (part != 0) xch_acc[part * BM + row_in_tile] = row_acc;
-          if (!rendezvous()) { ok = false; break; }
-          if (part == 0 && row_ok) p.ss_out[m] = row_acc + xch_acc[BM + row_in_tile];
+      if (LM) {
+        if (row_ok) {
+          if (p.epi == CCB_EPI_LSE_PART)
+            p.part_out[(long long)((t.n0 / BN) * EPI_PARTS + part) * p.M + m] = make_float2(run_m, run_s);
+          if (lm_hit && p.zt_out != nullptr) p.zt_out[m] = lm_zt;
+        }
+      } else if (p.epi == CCB_EPI_RESID_SS && p.ss_out != nullptr) {
+        // one value per row and tile: the second warp of the quadrant hands its
+        // half over, so a row split over two N tiles gets exactly two (commutative,
+        // hence order-independent) atomic adds
+        if (part != 0) xch_acc[part * BM + row_in_tile] = row_acc;
+        if (!rendezvous()) { ok = false; break; }
+        if (part == 0 && row_ok) {
+          const float tot = row_acc + xch_acc[BM + row_in_tile];
+          if (p.ss_atomic) atomicAdd(p.ss_out + m, tot); else p.ss_out[m] = tot;
         }
       }
       tc_fence_before_sync();
@@ -550,13 +617,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 // ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
-template <int BN, int A_MN, int B_MN>
+template <int BN, int A_MN, int B_MN, int LM = 0>
 static int launch_gemm(const CcbGemmArgs* a, cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
   static bool attr_set[16] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
-  auto kern = gemm_kernel<BN, A_MN, B_MN>;
+  auto kern = gemm_kernel<BN, A_MN, B_MN, LM>;
   if (!attr_set[dev & 15]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg::SMEM_BYTES);
@@ -595,7 +662,8 @@ static int launch_gemm(const CcbGemmArgs* a, cudaStream_t stream) {
   p.dscale_a = a->dscale_a; p.dscale_b = a->dscale_b; p.bias = a->bias;
   // bf16 outputs that keep rows 16-byte aligned go out through TMA stores
   CUtensorMap tmC, tmC2;
-  const bool tma_ok = !a->out_fp32 && (a->ldc % 8 == 0) && (a->c_batch % 8 == 0) &&
+  const bool tma_ok = a->epi != CCB_EPI_LSE_PART &&
+                      !a->out_fp32 && (a->ldc % 8 == 0) && (a->c_batch % 8 == 0) &&
                       ((reinterpret_cast<uintptr_t>(a->C) & 15) == 0) &&
                       (a->epi != CCB_EPI_ROWSCALE_SILU ||
                        (a->C2 != nullptr && (reinterpret_cast<uintptr_t>(a->C2) & 15) == 0));
@@ -628,8 +696,24 @@ static int launch_gemm(const CcbGemmArgs* a, cudaStream_t stream) {
   p.rowss = a->rowss; p.ss_out = a->ss_out;
   p.alpha = a->alpha; p.beta = a->beta; p.inv_dim = a->inv_dim; p.eps = a->eps;
   p.status = ccb_status_ptr();
-  if (p.epi == CCB_EPI_RMSBWD && p.tiles_n != 1)
-    return set_error("ccb_gemm: RMSBWD epilogue needs N <= %d (got %d)", BN, p.N);
+  p.pair = 0;
+  if (p.epi == CCB_EPI_RMSBWD && p.tiles_n != 1) {
+    // the row reduction needs the whole row in tensor memory: both accumulators as one tile
+    if (p.tiles_n != 2 || BN != 256)
+      return set_error("ccb_gemm: RMSBWD epilogue needs N <= %d (got %d)", 2 * BN, p.N);
+    p.pair = 1;
+    p.tiles_n = 1;
+  }
+  p.targets = (const long long*)a->targets; p.lse = a->lse; p.rowweight = a->rowweight;
+  p.part_out = (float2*)a->part_out; p.zt_out = a->zt_out;
+  if (LM) {
+    if (p.targets == nullptr || p.splits != 1 || p.batch != 1)
+      return set_error("ccb_gemm: LM-head epilogues need targets, one split and one batch");
+    if (p.epi == CCB_EPI_LSE_PART && p.part_out == nullptr)
+      return set_error("ccb_gemm: LSE_PART needs part_out");
+    if (p.epi == CCB_EPI_CE_GRAD && (p.lse == nullptr || !tma_ok))
+      return set_error("ccb_gemm: CE_GRAD needs lse and a 16-byte aligned bf16 output");
+  }
   long long total = (long long)p.batch * p.splits * p.tiles_m * p.tiles_n;
   if (total <= 0) return 0;
   int grid = (int)(total < ccb_num_sms() ? total : ccb_num_sms());
@@ -654,6 +738,11 @@ extern "C" int ccb_gemm(const CcbGemmArgs* a, void* stream_) {
   if ((a->lda % row_align) || (a->ldb % row_align) || (a->ldc % 4))
     return set_error("ccb_gemm: row strides must keep rows 16-byte aligned");
   const int key = (int)(a->a_mn * 2 + a->b_mn);
+  if (a->epi == CCB_EPI_LSE_PART || a->epi == CCB_EPI_CE_GRAD) {
+    if (key != 0 || a->a_fp8) return set_error("ccb_gemm: LM-head epilogues take K-major bf16 operands");
+    return launch_gemm<256, 0, 0, 1>(a, stream);
+  }
+  if (a->epi < 0 || a->epi > CCB_EPI_RMSBWD) return set_error("ccb_gemm: unknown epilogue %lld", (long long)a->epi);
   // 128-wide tiles only where the problem has a single narrow N tile to fill.
   const bool narrow = a->N <= 128 && a->epi == CCB_EPI_STORE;
   if (narrow) {

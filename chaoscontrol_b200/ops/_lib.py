@@ -34,10 +34,12 @@ class GemmArgs(C.Structure):
         ("epi", i64), ("out_fp32", i64), ("ss_atomic", i64),
         ("alpha", f32), ("beta", f32), ("inv_dim", f32), ("eps", f32),
         ("a_fp8", i64), ("b_fp8", i64), ("dscale_a", vp), ("dscale_b", vp), ("bias", vp),
+        ("targets", vp), ("lse", vp), ("rowweight", vp), ("part_out", vp), ("zt_out", vp),
     ]
 
 
-EPI_STORE, EPI_ROWSCALE, EPI_ROWSCALE_SILU, EPI_RESID_SS, EPI_DSILU, EPI_RMSBWD = range(6)
+(EPI_STORE, EPI_ROWSCALE, EPI_ROWSCALE_SILU, EPI_RESID_SS, EPI_DSILU, EPI_RMSBWD, EPI_LSE_PART,
+ EPI_CE_GRAD) = range(8)
 
 _SIGS = {
     "ccb_init": ([], C.c_int),
@@ -47,6 +49,7 @@ _SIGS = {
     "ccb_last_error": ([], C.c_char_p),
     "ccb_status_ptr": ([], vp),
     "ccb_gemm": ([C.POINTER(GemmArgs), vp], C.c_int),
+    "ccb_lse_combine": ([vp, i64, i64, vp, vp, vp, vp], C.c_int),
     "ccb_fp8_cast_amax": ([vp, vp, vp, vp, i64, i64, vp], C.c_int),
     "ccb_fp8_cast_transpose_amax": ([vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, vp], C.c_int),
     "ccb_fp8_flush_amax": ([vp, i64, vp, vp, f32, vp], C.c_int),

@@ -100,7 +100,7 @@ def chunked_nll_from_hidden(model: Any, hidden_states: torch.Tensor, targets: to
     targets = targets.long()
     nw = getattr(norm, "weight", None)
     if (nw is not None and getattr(head, "bias", None) is None and hidden_states.is_cuda and
-            LH.fused_supported(hidden_states.new_empty(1, D, dtype=head.weight.dtype), head.weight)):
+            LH.kernel_supported(hidden_states.new_empty(1, D, dtype=head.weight.dtype), head.weight)):
         x = hidden_states.to(head.weight.dtype).reshape(B * T, D).contiguous()
         ss = x.float().square().sum(-1)
         rows, _ = LH.lm_head_lse(x, ss, fold_colscale(head.weight, nw), targets.reshape(-1),

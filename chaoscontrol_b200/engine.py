@@ -51,7 +51,7 @@ class TrainEngine:
         if getattr(model, "tie_embeddings", False):
             return False
         w = model.lm_head.weight
-        return w.shape[1] == 256 and w.shape[0] % 128 == 0
+        return LH.kernel_supported(w.new_empty(1, w.shape[1]), w)
 
     def _packed(self, i: int):
         a, n = self.arena, self._names[i]

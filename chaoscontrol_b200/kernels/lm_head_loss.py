@@ -99,7 +99,7 @@ class _LinearCeFn(torch.autograd.Function):
 
 def _linear_ce(x, weight, targets, row_weight=None):
     """Returns (weighted sum of per-row CE, per-row CE)."""
-    if LH.fused_supported(x, weight) and _lib.available():
+    if LH.kernel_supported(x, weight) and _lib.available():
         return _LinearCeFn.apply(x.contiguous(), weight.contiguous(), targets.reshape(-1), row_weight)
     logits = F.linear(x, weight).float()
     rows = F.cross_entropy(logits, targets.reshape(-1).long(), reduction="none")

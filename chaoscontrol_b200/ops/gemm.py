@@ -20,11 +20,11 @@ from typing import Optional
 import torch
 
 from . import _lib
-from ._lib import (EPI_DSILU, EPI_RESID_SS, EPI_RMSBWD, EPI_ROWSCALE, EPI_ROWSCALE_SILU,
-                   EPI_STORE, GemmArgs)
+from ._lib import (EPI_CE_GRAD, EPI_DSILU, EPI_LSE_PART, EPI_RESID_SS, EPI_RMSBWD, EPI_ROWSCALE,
+                   EPI_ROWSCALE_SILU, EPI_STORE, GemmArgs)
 
-__all__ = ["gemm", "gemm_fp8", "gemm_reference", "pick_splits", "EPI_STORE", "EPI_ROWSCALE",
-           "EPI_ROWSCALE_SILU", "EPI_RESID_SS", "EPI_DSILU", "EPI_RMSBWD"]
+__all__ = ["gemm", "gemm_fp8", "gemm_lm", "gemm_reference", "pick_splits", "EPI_STORE", "EPI_ROWSCALE",
+           "EPI_ROWSCALE_SILU", "EPI_RESID_SS", "EPI_DSILU", "EPI_RMSBWD", "EPI_LSE_PART", "EPI_CE_GRAD"]
 
 
 def pick_splits(m: int, n: int, k: int, bn: int = 256) -> int:
@@ -68,6 +68,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     if a.stride(-1) != 1 or b.stride(-1) != 1:
         raise ValueError("gemm operands must have a contiguous last dimension")
     batch, M, N, K = _dims(a, b, a_mn, b_mn)
+    if epi == EPI_RESID_SS and ss_out is not None and N > 256 and not ss_atomic:
+        # a row spans several N tiles: each tile adds its share into a zeroed buffer
+        ss_out.zero_()
+        ss_atomic = True
     if out is None:
         shape = (M, N) if a.dim() == 2 else (batch, M, N)
         if splits > 1:
@@ -101,6 +105,52 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     args.alpha, args.beta, args.inv_dim, args.eps = alpha, beta, inv_dim, eps
     _lib.check(_lib.lib().ccb_gemm(C.byref(args), _lib.stream_ptr()), "gemm")
     return out
+
+
+def gemm_lm(x: torch.Tensor, w: torch.Tensor, *, epi: int, targets: torch.Tensor,
+            rowss: Optional[torch.Tensor], inv_dim: float, eps: float, lse: Optional[torch.Tensor] = None,
+            rowweight: Optional[torch.Tensor] = None, alpha: float = 1.0,
+            out: Optional[torch.Tensor] = None, zt_out: Optional[torch.Tensor] = None):
+    """LM-head epilogues on ``logits = rs * (x @ w.T)`` (``x`` ``[R, D]``, ``w`` ``[V, D]``, bf16, CUDA).
+
+    ``EPI_LSE_PART`` returns ``(partials [2 * ceil(V / 256), R, 2] fp32, zt [R])``: log2-domain
+    ``(max, sum)`` per half tile and the target logit; no logits are written.
+    ``EPI_CE_GRAD`` returns the bf16 ``[R, V]`` gradient of the summed, ``alpha * rowweight``-weighted
+    cross-entropy w.r.t. the un-scaled GEMM output, and fills ``zt_out`` with the per-row CE.
+    """
+    R, D = x.shape
+    V = w.shape[0]
+    args = GemmArgs()
+    args.A, args.B = x.data_ptr(), w.data_ptr()
+    args.M, args.N, args.K = R, V, D
+    args.batch, args.splits = 1, 1
+    args.lda, args.ldb = x.stride(0), w.stride(0)
+    args.epi = epi
+    args.alpha, args.beta, args.inv_dim, args.eps = alpha, 0.0, inv_dim, eps
+    args.rowss = _lib.ptr(rowss)
+    t = targets.reshape(-1)
+    if t.dtype != torch.int64:
+        t = t.long()
+    t = t.contiguous()
+    args.targets = t.data_ptr()
+    res = None
+    if epi == EPI_LSE_PART:
+        nparts = 2 * ((V + 255) // 256)
+        part = torch.empty(nparts, R, 2, dtype=torch.float32, device=x.device)
+        zt = zt_out if zt_out is not None else torch.empty(R, dtype=torch.float32, device=x.device)
+        args.part_out, args.zt_out = part.data_ptr(), zt.data_ptr()
+        args.ldc = V
+        res = (part, zt)
+    elif epi == EPI_CE_GRAD:
+        if out is None:
+            out = torch.empty(R, V, dtype=torch.bfloat16, device=x.device)
+        args.C, args.ldc = out.data_ptr(), out.stride(0)
+        args.lse, args.rowweight, args.zt_out = lse.data_ptr(), _lib.ptr(rowweight), _lib.ptr(zt_out)
+        res = out
+    else:
+        raise ValueError(f"gemm_lm: epilogue {epi} is not an LM-head epilogue")
+    _lib.check(_lib.lib().ccb_gemm(C.byref(args), _lib.stream_ptr()), "gemm_lm")
+    return res
 
 
 _FP8_CODE = {torch.float8_e4m3fn: 1, torch.float8_e5m2: 2}

@@ -14,6 +14,7 @@ from typing import Optional
 import torch
 
 from . import _lib
+from . import gemm as G
 from ._lib import f32, i64, vp
 
 _lib.register_sig("ccb_lmhead_lse", [vp, vp, vp, f32, vp, vp, vp, vp, i64, i64, i64, vp])
@@ -27,6 +28,74 @@ def fused_supported(x: torch.Tensor, W: torch.Tensor) -> bool:
     """Shapes / dtypes the tcgen05 LM-head kernels handle."""
     return (x.is_cuda and x.dtype == torch.bfloat16 and W.dtype == torch.bfloat16 and
             x.shape[-1] == 256 and W.shape[0] % 128 == 0 and W.shape[1] == 256)
+
+
+def general_supported(x: torch.Tensor, W: torch.Tensor) -> bool:
+    """Shapes the GEMM-epilogue LM head handles (any model dim that keeps rows 16-byte
+    aligned and fits the 512-column RMSNorm-backward tile)."""
+    D = x.shape[-1]
+    return (x.is_cuda and x.dtype == torch.bfloat16 and W.dtype == torch.bfloat16 and W.shape[1] == D and
+            D % 8 == 0 and D <= 512 and W.shape[0] % 8 == 0)
+
+
+def kernel_supported(x: torch.Tensor, W: torch.Tensor) -> bool:
+    """True when one of the two hand-written LM-head paths takes these operands."""
+    return fused_supported(x, W) or general_supported(x, W)
+
+
+def _lse_general(x, rowss, W_f, t, eps):
+    """``(loss_rows, lse)`` from one GEMM whose epilogue reduces each half tile to a
+    (max, sum) pair, followed by a per-row combine; logits never reach memory."""
+    R, D = x.shape
+    part, zt = G.gemm_lm(x, W_f, epi=G.EPI_LSE_PART, targets=t, rowss=rowss, inv_dim=1.0 / D, eps=eps)
+    lse = torch.empty(R, dtype=torch.float32, device=x.device)
+    loss = torch.empty(R, dtype=torch.float32, device=x.device)
+    _lib.check(_lib.lib().ccb_lse_combine(part.data_ptr(), part.shape[0], R, zt.data_ptr(), lse.data_ptr(),
+                                          loss.data_ptr(), _lib.stream_ptr()), "lse_combine")
+    return loss, lse
+
+
+def general_row_chunk(R: int) -> int:
+    """Rows per backward chunk: one 128-row block per SM, so the paired-accumulator dX GEMM
+    (one CTA per row block) fills the device exactly and the bf16 gradient chunk stays bounded."""
+    sms = _lib.lib().ccb_num_sms() if _lib.available() else 148
+    return min(R, 128 * sms)
+
+
+def _train_general(x, rowss, W_f, t, gscale, rowweight, eps, lse):
+    """Chunked LM-head backward from GEMM epilogues.  Per row chunk: ``g = (softmax - onehot) *
+    scale`` is produced by the logits GEMM's epilogue as a bf16 ``[rows, V]`` tile (bounded by the
+    chunk, never the full ``[R, V]``), then ``dX = RMSNorm-backward(g @ W')`` and
+    ``dW' += g^T @ X`` are two more tcgen05 GEMMs."""
+    R, D = x.shape
+    V = W_f.shape[0]
+    if lse is None:
+        loss, lse = _lse_general(x, rowss, W_f, t, eps)
+    else:
+        loss = torch.empty(R, dtype=torch.float32, device=x.device)
+    rc = general_row_chunk(R)
+    nchunks = (R + rc - 1) // rc
+    S = G.pick_splits(V, D, rc)
+    dX = torch.empty_like(x)
+    part = torch.empty(nchunks * S, V, D, dtype=torch.float32, device=x.device)
+    gbuf = torch.empty(rc, V, dtype=torch.bfloat16, device=x.device)
+    for i in range(nchunks):
+        r0, r1 = i * rc, min(R, (i + 1) * rc)
+        xc = x[r0:r1]
+        ssc = rowss[r0:r1] if rowss is not None else None
+        g = G.gemm_lm(xc, W_f, epi=G.EPI_CE_GRAD, targets=t[r0:r1], rowss=ssc, inv_dim=1.0 / D, eps=eps,
+                      lse=lse[r0:r1], rowweight=rowweight[r0:r1] if rowweight is not None else None,
+                      alpha=gscale, out=gbuf[: r1 - r0], zt_out=loss[r0:r1])
+        if rowss is not None:
+            G.gemm(g, W_f, b_mn=True, epi=G.EPI_RMSBWD, r1=xc, rowss=ssc, inv_dim=1.0 / D, eps=eps,
+                   out=dX[r0:r1])
+        else:
+            G.gemm(g, W_f, b_mn=True, out=dX[r0:r1])
+        Sc = min(S, G.pick_splits(V, D, r1 - r0))
+        if Sc != S:
+            part[i * S + Sc:(i + 1) * S].zero_()
+        G.gemm(g, xc, a_mn=True, b_mn=True, splits=Sc, out=part[i * S: i * S + Sc] if Sc > 1 else part[i * S])
+    return loss, lse, dX, part
 
 
 def lm_head_reference(x, rowss, W_f, targets, *, gscale: float = 1.0, rowweight=None,
@@ -63,6 +132,8 @@ def lm_head_lse(x, rowss, W_f, targets, *, eps: float = EPS, want_entropy: bool 
     """Forward only: ``(loss_rows, lse)`` fp32 ``[R]`` (plus the softmax entropy
     when asked); no logits in memory."""
     R, D = x.shape
+    if not fused_supported(x, W_f) and general_supported(x, W_f) and not want_entropy:
+        return _lse_general(x, rowss, W_f, _prep(x, rowss, W_f, targets), eps)
     if not fused_supported(x, W_f):
         lr, lse, _, _ = lm_head_reference(x, rowss, W_f, targets, eps=eps, want_grads=False)
         if want_entropy:
@@ -113,6 +184,8 @@ def lm_head_train(x, rowss, W_f, targets, *, gscale: float, rowweight=None, eps:
     """
     R, D = x.shape
     V = W_f.shape[0]
+    if not fused_supported(x, W_f) and general_supported(x, W_f):
+        return _train_general(x, rowss, W_f, _prep(x, rowss, W_f, targets), gscale, rowweight, eps, lse)
     if not fused_supported(x, W_f):
         lr, lse, dX, dW = lm_head_reference(x, rowss, W_f, targets, gscale=gscale,
                                             rowweight=rowweight, eps=eps)

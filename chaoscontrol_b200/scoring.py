@@ -66,7 +66,7 @@ class ScoreResult:
 
 def _chunk_loss_rows(model: nn.Module, inputs: torch.Tensor, targets: torch.Tensor, states):
     """Per-position CE ``[B, T]`` and final states for one block of chunks."""
-    if getattr(model, "kernel_trunk_supported", lambda: False)() and LH.fused_supported(
+    if getattr(model, "kernel_trunk_supported", lambda: False)() and LH.kernel_supported(
             model.embed.weight.new_empty(1, model.dim), model.lm_head.weight):
         hidden, ss, finals = model.encode_with_stats(inputs, initial_states=states)
         W_f = fold_colscale(model.lm_head.weight, model.final_norm.weight)

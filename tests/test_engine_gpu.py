@@ -16,9 +16,9 @@ from chaoscontrol_b200.utils.arena import ParamArena
 pytestmark = pytest.mark.gpu
 
 
-def _model(vocab=512, layers=2, seed=0):
+def _model(vocab=512, layers=2, seed=0, dim=256, ff_mult=2):
     torch.manual_seed(seed)
-    m = CareStudentLM(vocab_size=vocab, dim=256, num_layers=layers)
+    m = CareStudentLM(vocab_size=vocab, dim=dim, num_layers=layers, ff_mult=ff_mult)
     with torch.no_grad():
         for n, p in m.named_parameters():
             if n.endswith("norm.weight"):
@@ -28,8 +28,9 @@ def _model(vocab=512, layers=2, seed=0):
     return m
 
 
-def test_engine_step_vs_fp32_autograd():
-    ref = _model().cuda()
+@pytest.mark.parametrize("dim,ff_mult", [(256, 2), (512, 4), (128, 2)])
+def test_engine_step_vs_fp32_autograd(dim, ff_mult):
+    ref = _model(dim=dim, ff_mult=ff_mult).cuda()
     m = copy.deepcopy(ref).to(torch.bfloat16)
     # the fp32 oracle uses the bf16-rounded weights
     with torch.no_grad():

@@ -120,3 +120,29 @@ def test_gemm_deterministic():
     o2 = G.gemm(a, b)
     _lib.assert_ok()
     assert torch.equal(o1, o2)
+
+
+@pytest.mark.parametrize("M,D,F", [(640, 512, 1024), (300, 384, 768), (4096, 512, 2048)])
+def test_gemm_wide_rows(M, D, F):
+    """Rows wider than one 256-column tile: RMSNorm backward over the paired
+    accumulators and the residual epilogue's per-tile sum of squares."""
+    torch.manual_seed(7)
+    x, du, dres = _rand(M, D), _rand(M, F), _rand(M, D)
+    ss = (x.float() ** 2).sum(-1)
+    wf = _rand(F, D, scale=0.05)
+    dxo = G.gemm(du, wf, b_mn=True, epi=G.EPI_RMSBWD, r1=x, r2=dres, rowss=ss, inv_dim=1.0 / D)
+    _close(dxo, G.gemm_reference(du, wf, b_mn=True, epi=G.EPI_RMSBWD, r1=x, r2=dres, rowss=ss,
+                                 inv_dim=1.0 / D))
+    dx1 = G.gemm(du, wf, b_mn=True, epi=G.EPI_RMSBWD, r1=x, rowss=ss, inv_dim=1.0 / D)
+    _close(dx1, G.gemm_reference(du, wf, b_mn=True, epi=G.EPI_RMSBWD, r1=x, rowss=ss, inv_dim=1.0 / D))
+    y = _rand(M, F)
+    wp = _rand(D, F, scale=0.05)
+    ss2 = torch.full((M,), 123.0, dtype=torch.float32, device="cuda")   # stale contents must not leak
+    x2 = G.gemm(y, wp, epi=G.EPI_RESID_SS, r1=x, ss_out=ss2)
+    x2b = G.gemm(y, wp, epi=G.EPI_RESID_SS, r1=x, ss_out=torch.empty_like(ss2))
+    _lib.assert_ok()
+    _close(x2, G.gemm_reference(y, wp, epi=G.EPI_RESID_SS, r1=x)[0])
+    assert torch.allclose(ss2, (x2.float() ** 2).sum(-1), rtol=1e-3, atol=1e-3)
+    assert torch.equal(x2, x2b)
+    assert torch.equal(dxo, G.gemm(du, wf, b_mn=True, epi=G.EPI_RMSBWD, r1=x, r2=dres, rowss=ss,
+                                   inv_dim=1.0 / D))

@@ -55,3 +55,40 @@ def test_lmhead_train_deterministic():
     _lib.assert_ok()
     for u, v in zip(a, b):
         assert torch.equal(u, v)
+
+
+def _mk_d(R, V, D, seed=0, wscale=0.08):
+    torch.manual_seed(seed)
+    x = torch.randn(R, D, device="cuda").bfloat16()
+    W = (torch.randn(V, D, device="cuda") * wscale).bfloat16()
+    t = torch.randint(0, V, (R,), device="cuda")
+    return x, W, t, (x.float() ** 2).sum(-1)
+
+
+@pytest.mark.parametrize("R,V,D,norm", [(300, 1000, 512, True), (1024, 16384, 512, True),
+                                        (515, 520, 128, False), (20000, 2048, 384, True)])
+def test_lmhead_general_dims(R, V, D, norm):
+    """Model dims other than 256 go through the GEMM-epilogue LM head."""
+    x, W, t, ss = _mk_d(R, V, D, seed=3)
+    assert not LH.fused_supported(x, W) and LH.general_supported(x, W)
+    rowss = ss if norm else None
+    loss, lse = LH.lm_head_lse(x, rowss, W, t)
+    rl, rlse, _, _ = LH.lm_head_reference(x, rowss, W, t, want_grads=False)
+    _lib.assert_ok()
+    assert torch.allclose(lse, rlse, rtol=1e-3, atol=2e-2), (lse - rlse).abs().max()
+    assert torch.allclose(loss, rl, rtol=1e-3, atol=3e-2), (loss - rl).abs().max()
+    w = torch.rand(R, device="cuda")
+    gscale = 1.0 / R
+    loss2, lse2, dX, part = LH.lm_head_train(x, rowss, W, t, gscale=gscale, rowweight=w)
+    _lib.assert_ok()
+    _, _, rdX, rdW = LH.lm_head_reference(x, rowss, W, t, gscale=gscale, rowweight=w)
+    assert torch.allclose(loss2, rl, rtol=1e-3, atol=3e-2), (loss2 - rl).abs().max()
+    assert torch.equal(lse2, lse)
+    sx = rdX.abs().max().item()
+    assert (dX.float() - rdX).abs().max().item() <= 0.03 * sx + 1e-7, ((dX.float() - rdX).abs().max().item(), sx)
+    dW = part.sum(0)
+    sw = rdW.abs().max().item()
+    assert (dW - rdW).abs().max().item() <= 0.03 * sw + 1e-7, ((dW - rdW).abs().max().item(), sw)
+    again = LH.lm_head_train(x, rowss, W, t, gscale=gscale, rowweight=w)
+    for u, v in zip((loss2, lse2, dX, part), again):
+        assert torch.equal(u, v)

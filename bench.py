@@ -40,6 +40,9 @@ CONFIGS = {
     "submission": dict(dim=256, layers=4, ff_mult=2, seq=512, batch=1024, dist_muon=False, fp8=False),
     # ~57.7 M parameters; gradients exchanged by the sharded reduce -> owner-side Muon -> parameter gather
     "scaled": dict(dim=512, layers=12, ff_mult=4, seq=2048, batch=128, dist_muon=True, fp8=False),
+    # the submission trunk with every trunk linear in fp8: ours = block-scaled e4m3 (1x128 / 128x128 scales,
+    # cast fused into the RMSNorm producer), reference = its per-tensor cuBLASLt path
+    "fp8": dict(dim=256, layers=4, ff_mult=2, seq=512, batch=1024, dist_muon=False, fp8=True),
 }
 
 
@@ -290,6 +293,115 @@ def run_ours(args):
 
 
 # ---------------------------------------------------------------------------
+def run_fp8(args):
+    """fp8 trunk linears, module-by-module autograd path, either arm: same loop, same timing."""
+    import torch
+    ref_arm = args.impl == "reference"
+    if ref_arm:
+        ref = ROOT / "baseline" / "_ref"
+        if not (ref / "chaoscontrol").exists():
+            print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is missing"}))
+            return
+        sys.path.insert(0, str(ref))
+        os.environ.setdefault("CHAOSCONTROL_DIAG_SCAN_BACKEND", "ssm_scan")
+        try:
+            from chaoscontrol.distributed import broadcast_params, clip_grad_norm_fused
+            from chaoscontrol.kernels.fp8_linear import fused_fp8_flush_all
+            from chaoscontrol.model import CareStudentLM
+            from chaoscontrol.optim.muon import Muon
+            from chaoscontrol.precision import maybe_promote_linears_to_fused_fp8
+            from chaoscontrol.train_ssm import train_ssm_step
+        except Exception as exc:  # pragma: no cover
+            print(json.dumps({"impl": "reference",
+                              "unavailable": f"import failed: {type(exc).__name__}: {exc}"[:300]}))
+            return
+        promote = lambda m: maybe_promote_linears_to_fused_fp8(m, True)
+        precision, recipe = "fp8_fused", "per-tensor delayed scaling, cuBLASLt"
+    else:
+        sys.path.insert(0, str(ROOT))
+        from chaoscontrol_b200.models.model import CareStudentLM
+        from chaoscontrol_b200.ops import _lib
+        from chaoscontrol_b200.optim.muon import Muon
+        from chaoscontrol_b200.parallel.distributed import broadcast_params, clip_grad_norm_fused
+        from chaoscontrol_b200.precision import maybe_promote_linears_to_fused_fp8
+        from chaoscontrol_b200.train_ssm import train_ssm_step
+        promote = lambda m: maybe_promote_linears_to_fused_fp8(m, True, scaling="block")
+        fused_fp8_flush_all = lambda m: None
+        precision, recipe = "bf16", "block-scaled e4m3 (1x128 activations, 128x128 weights), tcgen05 f8f6f4"
+    rank, local, ws = _dist_setup(args)
+    dev = torch.device("cuda", local)
+    torch.manual_seed(0)
+    model = CareStudentLM(vocab_size=VOCAB, dim=DIM, num_layers=LAYERS, ff_mult=FF_MULT).to(dev).to(torch.bfloat16)
+    model.train()
+    try:
+        n_promoted = promote(model)
+    except Exception as exc:
+        if rank == 0:
+            print(json.dumps({"impl": args.impl, "unavailable": f"fp8 promotion failed: {type(exc).__name__}: {exc}"[:300]}))
+        return
+    if ws > 1:
+        broadcast_params(model)
+    opt = Muon(model.parameters(), lr=LR, weight_decay=WD, adamw_lr=LR, adamw_weight_decay=WD, fused=True)
+    opt.bind_param_names(list(model.named_parameters()))
+    host = _make_batches(args.warmup + args.steps, args.batch, args.seq, rank)
+    dev_batches = [h.to(dev) for h in host[:8]]
+    losses = []
+
+    def one(inputs, targets):
+        opt.zero_grad(set_to_none=True)
+        loss = train_ssm_step(model, inputs, targets, 64, ddp_active=ws > 1, world_size=ws, precision=precision,
+                              lm_head_backward_mode="fused_streaming_cached", lm_head_tile_size=8192)
+        clip_grad_norm_fused(model.parameters(), CLIP)
+        opt.step()
+        fused_fp8_flush_all(model)
+        return loss
+
+    def step_resident(i):
+        b = dev_batches[i % len(dev_batches)]
+        losses.append(one(b[:, :-1].to(torch.int32), b[:, 1:]))
+
+    try:
+        for i in range(args.warmup):
+            step_resident(i)
+        torch.cuda.synchronize()
+    except Exception as exc:
+        if rank == 0:
+            print(json.dumps({"impl": args.impl, "unavailable": f"fp8 step failed: {type(exc).__name__}: {exc}"[:400]}))
+        return
+    l0 = 0 if ref_arm else _lib.launch_count()
+    with ClockSampler(local) as cs:
+        ms = _timed(step_resident, args.steps, ws)
+    launches = None if ref_arm else _lib.launch_count() - l0
+    final_loss = float(torch.stack([l.float() for l in losses[-args.steps:]]).mean().item())
+    h2d = host[0].numel() * host[0].element_size()
+
+    def step_e2e(i):
+        blk = host[i % len(host)].to(dev, non_blocking=True)
+        step_e2e.last = float(one(blk[:, :-1].to(torch.int32), blk[:, 1:]).item())
+
+    for i in range(3):
+        step_e2e(i)
+    ms_e = _timed(step_e2e, args.steps, ws)
+    toks = ws * args.batch * args.seq / (ms / 1e3)
+    out = {"metric": "train tokens/sec, 4Lx256d V16384 SSM, fp8 trunk linears (seq 512, bs 1024/rank, Muon)",
+           "value": toks, "unit": "tokens/s", "n_gpus": ws, "steps": args.steps, "warmup": args.warmup,
+           "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+           "dtype": "fp8 (e4m3) linears, bf16 elsewhere", "data": "synthetic Zipf(1.1) tokens, random-init weights",
+           "impl": args.impl, "final_loss": final_loss, "gpu_launches": launches, "clocks": cs.summary(),
+           "e2e": {"value": ws * args.batch * args.seq / (ms_e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e,
+                   "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
+           "config": {"model": f"CareStudentLM {LAYERS}x{DIM} V{VOCAB} ff_mult {FF_MULT}", "promoted_linears": n_promoted,
+                      "fp8_recipe": recipe, "global_batch": ws * args.batch, "seq_len": args.seq,
+                      "parallelism": f"dp{ws}", "optimizer": f"Muon lr {LR} wd {WD} clip {CLIP}",
+                      "l2": "working set per step exceeds the 126 MB L2"}}
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    if ws > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------
 def run_reference(args):
     ref = ROOT / "baseline" / "_ref"
     if not (ref / "chaoscontrol").exists():
@@ -386,7 +498,9 @@ def run_reference(args):
 
 if __name__ == "__main__":
     a = _parse()
-    if a.impl == "reference":
+    if a.config == "fp8":
+        run_fp8(a)
+    elif a.impl == "reference":
         run_reference(a)
     else:
         run_ours(a)

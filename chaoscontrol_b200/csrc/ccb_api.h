@@ -91,6 +91,18 @@ int ccb_fp8_cast_transpose_amax(const void* x_bf16, void* out_u8, const float* s
 // roll the amax history, append *pending, recompute *scale (nullptr: skip), zero *pending
 int ccb_fp8_flush_amax(float* history, int64_t len, float* pending, float* scale, float max_rep, void* stream);
 
+// ---- block-scaled e4m3 linear (1 x 128 activation scales, 128 x 128 weight scales) --------
+// q[R,K] = e4m3(v / s), s_t[K/128, R]; v = x, or RMSNorm(x) * norm_w when norm_w is given
+// (then inv_rms_out[R] and the bf16 normalised row y_out[R,K] are optional extra outputs).
+int ccb_fp8_quant_rows(const void* x_bf16, int64_t ldx, const void* norm_w, float eps, void* q, float* s_t,
+                       float* inv_rms_out, void* y_out, int64_t R, int64_t K, void* stream);
+// q[N,K] = e4m3(w / s[n/128, k/128]); qt (optional) is the same matrix stored [K, N]
+int ccb_fp8_quant_blocks(const void* w_bf16, void* q, void* qt, float* s, int64_t N, int64_t K, void* stream);
+// C[M,N] = sum_kb sa_t[kb, m] * sb[(n/128) * sb_so + kb * sb_sk] * (A8[m, kb] . B8[n, kb]) (+ bias[n])
+int ccb_fp8_block_gemm(const void* A8, const float* sa_t, const void* B8, const float* sb, int64_t sb_so,
+                       int64_t sb_sk, void* C, int64_t ldc, int64_t out_fp32, const void* bias, int64_t M,
+                       int64_t N, int64_t K, void* stream);
+
 // ---- episodic write events ---------------------------------------------------
 // Packs M selected (batch, position) candidates into 568-byte WriteEvent records
 // (all-zero record = candidate dropped at a sequence edge).  rep_dtype: 0 fp32, 1 bf16, 2 fp16.

@@ -60,7 +60,13 @@ class RMSNorm(nn.Module):
         self.weight = nn.Parameter(torch.ones(dim, dtype=torch.float32))
         self.eps = eps
 
+    #: set by the block-scaled fp8 promotion: the norm also emits the e4m3 copy its consumers read
+    emit_fp8_blocks = False
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.emit_fp8_blocks and x.is_cuda and x.dtype == torch.bfloat16 and x.size(-1) % 128 == 0:
+            from ..ops.fp8_block import rmsnorm_quant
+            return rmsnorm_quant(x, self.weight, self.eps)
         normed = F.rms_norm(x.float(), (x.size(-1),), eps=self.eps)
         return normed.to(x.dtype) * self.weight
 

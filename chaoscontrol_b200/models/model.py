@@ -347,6 +347,8 @@ class CareStudentLM(nn.Module):
         for blk in self.layers:
             for m in (blk.core.in_proj, blk.core.select_proj, blk.core.gate_proj, blk.core.delta_proj,
                       blk.core.out_proj, blk.ff.fc, blk.ff.proj):
+                if type(m) is not nn.Linear:      # promoted (fp8) linears run module by module
+                    return False
                 if m._forward_hooks or m._forward_pre_hooks or m._backward_hooks:
                     return False
             if blk.core._capture_states_enabled:

@@ -50,6 +50,9 @@ _SIGS = {
     "ccb_status_ptr": ([], vp),
     "ccb_gemm": ([C.POINTER(GemmArgs), vp], C.c_int),
     "ccb_lse_combine": ([vp, i64, i64, vp, vp, vp, vp], C.c_int),
+    "ccb_fp8_quant_rows": ([vp, i64, vp, f32, vp, vp, vp, vp, i64, i64, vp], C.c_int),
+    "ccb_fp8_quant_blocks": ([vp, vp, vp, vp, i64, i64, vp], C.c_int),
+    "ccb_fp8_block_gemm": ([vp, vp, vp, vp, i64, i64, vp, i64, i64, vp, i64, i64, i64, vp], C.c_int),
     "ccb_fp8_cast_amax": ([vp, vp, vp, vp, i64, i64, vp], C.c_int),
     "ccb_fp8_cast_transpose_amax": ([vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, vp], C.c_int),
     "ccb_fp8_flush_amax": ([vp, i64, vp, vp, f32, vp], C.c_int),

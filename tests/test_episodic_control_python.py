@@ -181,3 +181,145 @@ def test_constrained_action_space_contract():
     assert isinstance(las.coerce_action_space({"trace_only": True}), las.ConstrainedActionSpace)
     with pytest.raises(TypeError):
         las.coerce_action_space(3)
+
+
+def test_numpy_shm_ring(tmp_path):
+    import os
+    from chaoscontrol_b200.episodic.ipc import ShmRing
+    name = f"ccb_t_{os.getpid()}"
+    ring = ShmRing.create(name=name, slot_shape=(3,), dtype=np.float32, capacity=4)
+    try:
+        with pytest.raises(FileExistsError):
+            ShmRing.create(name=name, slot_shape=(3,), dtype=np.float32, capacity=4)
+        for bad in (dict(slot_shape=(2,), dtype=np.float32, capacity=4), dict(slot_shape=(3,), dtype=np.float64, capacity=4),
+                    dict(slot_shape=(3,), dtype=np.float32, capacity=5)):
+            with pytest.raises(ValueError):
+                ShmRing.attach(name=name, **bad)
+        reader = ShmRing.attach(name=name, slot_shape=(3,), dtype=np.float32, capacity=4)
+        assert reader.try_read() is None
+        for i in range(6):
+            ring.try_write(np.full(3, i, np.float32))
+        assert ring.dropped_count() == 2 and len(reader) == 4
+        got = [int(reader.try_read()[0]) for _ in range(4)]
+        assert got == [2, 3, 4, 5] and reader.try_read() is None
+        with pytest.raises(ValueError):
+            ring.try_write(np.zeros(4, np.float32))
+        with pytest.raises(ValueError):
+            ring.try_write(np.zeros(3, np.float64))
+        with pytest.raises(ValueError):
+            ring.try_write([0, 0, 0])
+        reader.close()
+        reader.close_and_unlink()      # non-owner: no unlink
+        again = ShmRing.attach(name=name, slot_shape=(3,), dtype=np.float32, capacity=4)
+        again.close()
+    finally:
+        ring.close_and_unlink()
+        ring.close_and_unlink()
+    with pytest.raises(FileNotFoundError):
+        ShmRing.attach(name=name, slot_shape=(3,), dtype=np.float32, capacity=4)
+    with pytest.raises(ValueError):
+        ShmRing.create(name=name + "x", slot_shape=(1,) * 9, dtype=np.float32, capacity=1)
+
+
+def _filled_cache(n=6, dim=8):
+    from chaoscontrol_b200.episodic.cache import EpisodicCache
+    torch.manual_seed(0)
+    cache = EpisodicCache(capacity=16, span_length=2, key_rep_dim=dim)
+    for i in range(n):
+        cache.append(key_fp=100 + i, key_rep=torch.randn(dim), value_tok_ids=torch.tensor([i, i + 1]),
+                     value_anchor_id=i, current_step=10 * i, embedding_version=0, pressure_at_write=0.1 * i,
+                     source_write_id=1000 + i, write_bucket=i % 4)
+        cache.utility_u[i] = 0.5 + 0.1 * i
+    return cache
+
+
+def test_controller_cycle_heuristic_and_per_slot_runtime():
+    from collections import deque
+    from chaoscontrol_b200.episodic.controller import run_controller_cycle
+    from chaoscontrol_b200.episodic.query import query_topk
+    cache = _filled_cache()
+    q = [{"step": 70, "rank": 1, "k": i, "pressure": 0.3, "residual": torch.randn(8)} for i in range(3)]
+    residuals = [c["residual"].clone() for c in q]
+    tags: list = []
+    assert run_controller_cycle(controller_query_queue=deque(), tagged_replay_queue=tags, cache=cache) == 0
+    n = run_controller_cycle(controller_query_queue=q, tagged_replay_queue=tags, cache=cache, k=4, selected_at=5,
+                             policy_version=2)
+    assert n == 3 and not q and len(tags) == 12
+    for qi in range(3):
+        mine = [t["slot"] for t in tags[4 * qi: 4 * qi + 4]]
+        assert mine == query_topk(residuals[qi], cache, 4).tolist()
+    t0 = tags[0]
+    assert t0["query_event_id"] == (1 << 56) and t0["replay_id"] == ((1 << 56) & ((1 << 56) - 1)) << 8
+    assert t0["source_write_id"] == 1000 + t0["slot"] and t0["selected_at"] == 5 and t0["policy_version"] == 2
+    assert not any(isinstance(v, torch.Tensor) for t in tags for v in t.values())
+    assert tags[1]["replay_id"] & 0xFF == 1 and t0["outcome_status"] == "pending"
+    # learned per-slot runtime + bounded action space with a 2-tag budget
+    rt = csc.CpuSsmControllerRuntime(_weights(F=4), capacity=16, prefer_cpp=False)
+    recorded = []
+
+    class Rec:
+        def record_replay_selection(self, **kw):
+            recorded.append(kw)
+
+    tags2: list = []
+    q2 = deque([{"step": 80, "query_event_id": 77, "pressure": 0.1, "residual": residuals[0]}])
+    run_controller_cycle(controller_query_queue=q2, tagged_replay_queue=tags2, cache=cache, k=4,
+                         controller_runtime=rt, action_recorder=Rec(),
+                         action_space={"selection_readiness": 1.0, "selection_max_delta": 5.0, "max_tags_per_query": 2})
+    assert len(tags2) == 2 and len(recorded) == 2 and tags2[0]["query_event_id"] == 77
+    assert {"heuristic_rank", "action_space_score", "controller_features", "controller_slot_state"} <= set(tags2[0])
+    assert tags2[0]["action_space_score"] >= tags2[1]["action_space_score"]
+    empty = type(cache)(capacity=4, span_length=2, key_rep_dim=8)
+    tags3: list = []
+    assert run_controller_cycle(controller_query_queue=[{"step": 1, "residual": torch.randn(8)}],
+                                tagged_replay_queue=tags3, cache=empty) == 1 and not tags3
+
+
+def test_controller_cycle_simplex_runtime_and_thread():
+    import threading
+    from chaoscontrol_b200.episodic import controller as ctl
+    cache = _filled_cache()
+    rt = ctl.SimplexRuntime(num_slots=16)
+    space = las.ConstrainedActionSpace(head_readiness={"temperature": 1.0}, event_ssm=las.SharedEventSsm(),
+                                       online_learning_rate=0.1)
+    tags: list = []
+    q = [{"step": 90, "rank": 0, "k": 3, "pressure": 0.2, "residual": torch.randn(8), "arm": "c"}]
+    ctl.run_controller_cycle(controller_query_queue=q, tagged_replay_queue=tags, cache=cache, k=16,
+                             controller_runtime=rt, action_recorder=rt, simplex_selection_mode="sample",
+                             simplex_generator=torch.Generator().manual_seed(0), action_space=space)
+    assert len(tags) == 1
+    t = tags[0]
+    assert t["simplex_n_actual"] == 6 and len(t["p_behavior"]) == 6 and abs(sum(t["p_behavior"]) - 1) < 1e-5
+    assert t["slot"] == t["candidate_slot_ids"][t["simplex_chosen_idx"]] and t["arm"] == "c"
+    assert t["feature_manifest_hash"] == ctl.FEATURE_MANIFEST_HASH and 0 <= t["entropy"] <= math.log(6) + 1e-6
+    assert rt.decisions and rt.decisions[0]["selection_mode"] == "sample"
+    assert rt.learner.history_size(t["slot"]) == 1
+    assert 0.25 <= rt.policy.temperature <= 4.0 and t["replay_id"] in space.credit_history
+    assert space.apply_reward(key=t["replay_id"], reward=1.0, gpu_step=91) == 1
+    V, E, sf, ids = ctl.build_simplex_inputs(cache_view=cache.snapshot_to(torch.device("cpu")),
+                                             slots=torch.tensor([2, 4]), scores=torch.tensor([0.9, 0.1]),
+                                             current_step=100)
+    assert V.shape == (16, 16) and E.shape == (16, 16) and ids[:3] == [2, 4, 0]
+    assert V[0, 0] == pytest.approx(0.7) and V[1, 2] == pytest.approx((100 - 40) / 1000) and E[0, 0] == pytest.approx(1.0)
+    assert sf.tolist() == pytest.approx([0.9, 0.8, 0.9, 0.8])
+    assert ctl.choose_simplex_vertex([0.1, 0.7, 0.2, 9.0], 3)[0] == 1
+    assert ctl.choose_simplex_vertex([0.0, 0.0], 2)[1] == 0.5
+    with pytest.raises(ValueError):
+        ctl.choose_simplex_vertex([1.0], 1, mode="nope")
+    rt.learner.close()
+    # thread: starts, processes, stops
+    stop, beat, lock = threading.Event(), [0], threading.Lock()
+    queue, out = [], []
+    th = threading.Thread(target=ctl.controller_main, daemon=True,
+                          kwargs=dict(controller_query_queue=queue, tagged_replay_queue=out, cache=cache,
+                                      stop_event=stop, queue_lock=lock, k=2, heartbeat=beat))
+    th.start()
+    with lock:
+        queue.append({"step": 1, "rank": 0, "k": 0, "residual": torch.randn(8)})
+    import time
+    t0 = time.time()
+    while len(out) < 2 and time.time() - t0 < 10:
+        time.sleep(0.01)
+    stop.set()
+    th.join(timeout=10)
+    assert not th.is_alive() and len(out) == 2 and beat[0] > 0

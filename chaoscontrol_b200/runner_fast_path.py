@@ -360,13 +360,25 @@ def _warmup(*, model, train_tokens, train_num_tokens, stride, seq_len, batch_siz
 # ---------------------------------------------------------------------------
 # run_condition
 # ---------------------------------------------------------------------------
+_CONTROL: dict[int, Any] = {}
+
+
+def _control_group(world_size: int):
+    """Gloo side group for object / flag collectives, created once per process group."""
+    if world_size not in _CONTROL:
+        _CONTROL[world_size] = dist.new_group(list(range(world_size)), backend="gloo")
+    return _CONTROL[world_size]
+
+
 def run_condition(config: dict[str, Any], *, data_path: str, sp_model_path: Optional[str], budget_seconds: float,
                   output_json: Optional[str], output_ckpt: Optional[str], world_size_override: Optional[int],
-                  val_cache_dir: Optional[str] = None) -> dict[str, Any]:
+                  val_cache_dir: Optional[str] = None, keep_process_group: bool = False) -> dict[str, Any]:
+    """``keep_process_group`` leaves the process group (and the cached control group) alive on return,
+    for a warm worker that runs many conditions back to back."""
     _enable_runner_stack_dump_signal()
     rank, world_size, local_rank = _init_distributed(world_size_override)
     ddp = world_size > 1
-    control = dist.new_group(list(range(world_size)), backend="gloo") if ddp else None
+    control = _control_group(world_size) if ddp else None
     device = _pick_device(local_rank, str(config.get("device", "auto")))
     dtype = resolve_param_dtype(str(config.get("dtype", "bf16")), device)
     seed = int(config.get("seed", 1337))
@@ -501,7 +513,8 @@ def run_condition(config: dict[str, Any], *, data_path: str, sp_model_path: Opti
         print(f"[rank 0/{world_size}] done steps={train_result['steps']} "
               f"tok/s={train_result.get('aggregate_tokens_per_sec', 0.0):.0f} "
               f"loss={train_result['final_loss']:.4f} vram={train_result.get('peak_vram_mb', 0.0):.1f}MB", flush=True)
-    if ddp and dist.is_initialized():
+    if ddp and dist.is_initialized() and not keep_process_group:
+        _CONTROL.clear()
         dist.destroy_process_group()
     return result
 

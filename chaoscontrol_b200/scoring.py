@@ -117,7 +117,7 @@ def score_docs(model: nn.Module, tokens: torch.Tensor, doc_starts: Sequence[int]
         max_targets = int(lens[idx[0]]) - 1
         for c0 in range(0, max_targets, chunk_size):
             # documents are sorted by length: the active ones form a prefix
-            active = int((ln - 1 > c0).sum().item())
+            active = int((lens[idx] - 1 > c0).sum())          # host-side count: no device sync per chunk
             if active == 0:
                 break
             pos = c0 + torch.arange(chunk_size + 1, device=device)[None, :]          # [1, C+1]

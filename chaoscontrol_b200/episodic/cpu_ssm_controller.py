@@ -134,14 +134,10 @@ def forward_step(features: torch.Tensor, state: CpuSsmControllerState, weights: 
     g = _cpu_f32(state.global_state, expected_shape=(weights.global_dim,))
     s = _cpu_f32(state.slot_state, expected_shape=(weights.slot_dim,))
     w = weights.to_dict()
-    nat = _native() if prefer_cpp else None
-    if nat is not None:
-        fn = f.numpy()
-        out_g = nat.diag_step(w["decay_global"].numpy(), nat.matvec(w["w_global_in"].numpy(), fn), g.numpy())
-        out_s = nat.diag_step(w["decay_slot"].numpy(), nat.matvec(w["w_slot_in"].numpy(), fn), s.numpy())
-        logit = np.float32(out_g @ w["w_global_out"].numpy() + out_s @ w["w_slot_out"].numpy() + float(w["bias"]))
-        return CpuSsmControllerStep(torch.from_numpy(out_g), torch.from_numpy(out_s),
-                                    torch.tensor(float(logit), dtype=torch.float32))
+    if prefer_cpp and _native() is not None:
+        from .arm_native import ssm_forward_step
+        out_g, out_s, logit = ssm_forward_step(weights, f, g, s)      # one native call: both mat-vecs, both recurrences
+        return CpuSsmControllerStep(out_g, out_s, logit.reshape(()))
     out_g = w["decay_global"] * g + torch.mv(w["w_global_in"], f)
     out_s = w["decay_slot"] * s + torch.mv(w["w_slot_in"], f)
     logit = out_g.dot(w["w_global_out"]) + out_s.dot(w["w_slot_out"]) + w["bias"]

@@ -701,7 +701,9 @@ class ReplayEvictionLoop:
                  peak_preserve_sharpness_threshold: float = 0.20, useful_threshold: float = 0.005,
                  probe_buffer_size: int = 32, frame_ttl_steps: int = 256, slot_work_chunk_size: int = 64,
                  action_agreement_count: int = 2, commit_policy: str = "learned", commit_online_lr: float = 0.05,
-                 commit_temperature: float = 0.75, max_slots: Optional[int] = None, **unused: Any) -> None:
+                 commit_temperature: float = 0.75, max_slots: Optional[int] = None, arm_runtime_enabled: bool = False,
+                 arm_runtime_namespace: Optional[str] = None, evidence_engine_enabled: bool = False,
+                 evidence_engine_d_model: int = 384, evidence_engine_lanes: int = 8, **unused: Any) -> None:
         if action_mode not in ("active", "shadow"):
             raise ValueError("action_mode must be 'active' or 'shadow'")
         if scoring_mode not in ("proxy", "oracle"):
@@ -733,6 +735,16 @@ class ReplayEvictionLoop:
         self.proposals = CpuRefreshProposalModel(refresh_candidate_count, refresh_proposal_rank, refresh_lr,
                                                  refresh_proposal_noise_scale, refresh_proposal_momentum,
                                                  refresh_proposal_seed)
+        # optional native runtime: the C++ scheduler owns frame / slot-chunk selection, the evidence engine
+        # scores every frame's 32-token cue on the host cores
+        self._sched = self._evidence = None
+        if arm_runtime_enabled:
+            from .episodic.arm_native import ArmMaintenanceScheduler
+            self._sched = ArmMaintenanceScheduler(self.memory_streams, min(self.slot_chunk, 16), self.frame_ttl,
+                                                  max(1, int(probe_buffer_size)))
+        if evidence_engine_enabled:
+            from .episodic.arm_native import CpuEvidenceEngine
+            self._evidence = CpuEvidenceEngine(evidence_engine_lanes, evidence_engine_d_model)
         self._frames: deque = deque(maxlen=max(1, int(probe_buffer_size)))
         self._next_frame_id = self._tick = 0
         self._streak: dict[int, tuple[str, int]] = {}
@@ -755,8 +767,31 @@ class ReplayEvictionLoop:
         self._frames.append(ProbeFrame(self._next_frame_id, int(step), input_ids.detach(), valid_mask.detach(),
                                        None if cue is None else cue.detach(), cache_read_cutoff,
                                        int(stream_id) % self.memory_streams, time.monotonic()))
+        frame = self._frames[-1]
+        if self._sched is not None:
+            self._sched.ingest_frame(frame.frame_id, frame.step, frame.stream_id, cache_read_cutoff)
+        if self._evidence is not None:
+            self._ingest_evidence(frame)
         self._next_frame_id += 1
         self._stats["frames_ingested"] += 1
+
+    def refresh_evidence_weights(self, model: Any) -> None:
+        """Installs the model's current final-norm weight and LM head in the evidence engine."""
+        if self._evidence is not None:
+            self._evidence.set_lm_head(model.final_norm.weight.detach().float().cpu(),
+                                       model.lm_head.weight.detach().cpu())
+
+    def _ingest_evidence(self, frame: ProbeFrame) -> None:
+        from .episodic.arm_native import CUE_TOKENS
+        d = self._evidence.d_model
+        cue = torch.zeros(CUE_TOKENS, d, dtype=torch.bfloat16)
+        if frame.cue is not None and frame.cue.shape[-1] == d:
+            rows = frame.cue.detach().reshape(-1, d)[:CUE_TOKENS].to("cpu", torch.bfloat16)
+            cue[: rows.shape[0]] = rows
+        tg = torch.zeros(CUE_TOKENS, dtype=torch.int32)
+        ids = frame.input_ids.detach().reshape(-1)[1:CUE_TOKENS + 1].to("cpu", torch.int32)
+        tg[: ids.numel()] = ids
+        self._evidence.ingest_frame(cue, tg, frame_id=frame.frame_id, step=frame.step, stream_id=frame.stream_id)
 
     def has_probe(self) -> bool:
         return bool(self._frames)
@@ -817,8 +852,19 @@ class ReplayEvictionLoop:
         if outer is None or getattr(outer, "table", None) is None or not self._frames:
             return out
         t0 = time.monotonic()
-        frame, work = self._select_work(outer, step)
+        job = None
+        if self._sched is not None:
+            table0: SlotTable = outer.table
+            ids = [table0.physical_to_slot_id(p) for p in table0.visible_indices()]
+            job = self._sched.next_job(step, [i for i in ids if i is not None])
+            frame = next((f for f in self._frames if job is not None and f.frame_id == job["frame_id"]), None)
+            work = ([p for p in (table0.slot_id_to_physical(sid) for sid in job["slot_ids"]) if p is not None]
+                    if frame is not None else [])
+        else:
+            frame, work = self._select_work(outer, step)
         if frame is None:
+            if job is not None:
+                self._sched.record_result({**job, "status": 1})
             return out
         table: SlotTable = outer.table
         if self.scoring_mode == "oracle":
@@ -835,6 +881,8 @@ class ReplayEvictionLoop:
             gains, mask, idx, weights = r.marginal_gains, r.mask, r.slot_indices, r.weights_baseline
         self._stats["probe_seconds"] += time.monotonic() - t0
         if not idx:
+            if job is not None:
+                self._sched.record_result({**job, "status": 1})
             return out
         m = mask.float()
         mean_gain = (gains.float() * m).sum((1, 2)) / m.sum().clamp_min(1.0)
@@ -866,7 +914,14 @@ class ReplayEvictionLoop:
             if self.max_seconds > 0 and time.monotonic() - t0 > self.max_seconds:
                 self._stats["budget_exhausted"] += 1
                 break
+        before = (self._stats["oracle_confirmed"], self._stats["oracle_rejected"])
         self._act(model, outer, frame, decisions, step, out)
+        if job is not None:
+            self._sched.record_result({**job, "status": 0, "slots_scored": len(decisions),
+                                       "actions_confirmed": self._stats["oracle_confirmed"] - before[0],
+                                       "actions_rejected": self._stats["oracle_rejected"] - before[1],
+                                       "probe_seconds": time.monotonic() - t0,
+                                       "frame_age_seconds": time.monotonic() - frame.ingested_at})
         self._flush_if_needed()
         return out
 
@@ -1044,6 +1099,10 @@ class ReplayEvictionLoop:
 
     def close(self) -> None:
         self.flush_trace()
+        for h in (self._sched, self._evidence):
+            if h is not None:
+                h.close()
+        self._sched = self._evidence = None
 
     def recent_events(self, n: int = 64) -> list[MemoryEvent]:
         return self._events[-n:]
@@ -1052,7 +1111,9 @@ class ReplayEvictionLoop:
         return {**self._stats, "tick": self._tick, "queue_depth": len(self._frames), "action_counts": dict(self._counts),
                 "distill_receipts": len(self._receipts), "controller": self.controller.diagnostics(),
                 "commit_policy": self.learned.diagnostics(), "refresh_proposals": self.proposals.diagnostics(),
-                "action_mode": self.action_mode, "scoring_mode": self.scoring_mode, "trace_rows": self._trace_rows}
+                "action_mode": self.action_mode, "scoring_mode": self.scoring_mode, "trace_rows": self._trace_rows,
+                "arm_runtime": self._sched.diagnostics() if self._sched is not None else {"enabled": False},
+                "evidence_engine": self._evidence.diagnostics() if self._evidence is not None else {"enabled": False}}
 
     def state_dict(self) -> dict[str, Any]:
         """Everything learned or counted (probe frames are transient and not saved)."""

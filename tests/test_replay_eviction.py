@@ -215,3 +215,22 @@ def test_shadow_mode_never_mutates_and_stale_frames_drop():
             RE.ReplayEvictionLoop(**bad)
     ids_evict = RE._evict_slots(m.outer_model, [0, 2])
     assert len(ids_evict) == 2 and table.n_active == 2
+
+
+def test_tick_loop_with_native_scheduler_and_evidence_engine():
+    m = _model(n_slots=6)
+    loop = RE.ReplayEvictionLoop(commit_policy="rule", min_slot_age_steps=0, slot_work_chunk_size=4,
+                                 action_agreement_count=1, max_seconds_per_tick=0.0, arm_runtime_enabled=True,
+                                 evidence_engine_enabled=True, evidence_engine_d_model=16, evidence_engine_lanes=2)
+    loop.refresh_evidence_weights(m)
+    ids, valid = _probe(T=40)
+    for step in range(1, 5):
+        loop.cache_probe(input_ids=ids, valid_mask=valid, cue=torch.randn(2, 16), cache_read_cutoff=None, step=step,
+                         stream_id=step)
+        loop.tick(model=m, step=step)
+    d = loop.diagnostics()
+    assert d["arm_runtime"]["jobs_emitted"] >= 2 and d["arm_runtime"]["results_recorded"] == d["arm_runtime"]["jobs_emitted"]
+    assert d["arm_runtime"]["slots_scored_total"] == d["slots_scored"] >= 6
+    ev = d["evidence_engine"]
+    assert ev["frames_ingested"] == 4 and ev["cue_nll_calls_total"] == 4 and ev["last_cue_nll_mean"] > 0
+    loop.close()

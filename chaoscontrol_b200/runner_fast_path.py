@@ -49,7 +49,7 @@ from .optim.param_groups import build_optimizer_params
 from .optim.schedule import eval_with_ema, wrap_optimizer_step
 from .parallel.distributed import (allreduce_grads, broadcast_params, clip_arena_grad_norm, clip_grad_norm_fused,
                                    should_stop_now)
-from .train_ssm import _reject_unsupported, train_ssm_step
+from .train_ssm import _FUSED_LM_HEAD_BACKENDS, _reject_unsupported, train_ssm_step
 from .training_hooks import FastSlowConsolidator, spectral_summary, zero_embedding_grad_until
 from .utils.arena import get_arena
 
@@ -228,6 +228,179 @@ def _clip(model: torch.nn.Module, max_norm: float, fused: bool) -> None:
         torch.nn.utils.clip_grad_norm_(model.parameters(), max_norm)
 
 
+def _cuda_graph_rejection_reasons(*, device: torch.device, ddp_active: bool, lm_head_backward_mode: str,
+                                  optimizer: Optional[torch.optim.Optimizer] = None,
+                                  train_sampling_mode: str = "random",
+                                  model: Optional[torch.nn.Module] = None) -> list[str]:
+    """Why a whole-step capture is not attempted (empty list = capture)
+    (runner_fast_path.py:10094-10123).  Data-parallel steps stay eager: the
+    peer-memory collectives take a host-incremented epoch as a launch argument,
+    which a replay would freeze."""
+    reasons: list[str] = []
+    if device.type != "cuda" or not torch.cuda.is_available():
+        reasons.append("cuda_required")
+    if ddp_active:
+        reasons.append("ddp_not_supported")
+    if str(lm_head_backward_mode).strip().lower() not in _FUSED_LM_HEAD_BACKENDS:
+        reasons.append("fused_lm_head_required")
+    if optimizer is not None and type(optimizer).__name__ == "ScarcityAwareOptimizer":
+        reasons.append("scopt_autograd_grad_not_captured")
+    if str(train_sampling_mode).strip().lower() != "random":
+        reasons.append("train_sampling_mode_not_supported")
+    if model is not None and not reasons:
+        from .train_ssm import _engine_for
+        if _engine_for(model) is None:             # the autograd fallback is not sync-free
+            reasons.append("kernel_engine_required")
+    return reasons
+
+
+def _rejected_cuda_graph_summary(*, mode: str, reasons: list[str], budget_seconds: float, min_total_speedup: float,
+                                 max_capture_seconds: float) -> dict[str, Any]:
+    summary = FP.summarize_cuda_graph_gate(budget_seconds=budget_seconds, capture_seconds=0.0, warmup_seconds=0.0,
+                                           warmup_steps=0, eager_step_seconds=0.0, graph_step_seconds=0.0,
+                                           min_total_speedup=min_total_speedup,
+                                           max_capture_seconds=max_capture_seconds)
+    summary.update({"mode": mode, "accepted": False,
+                    "reasons": list(dict.fromkeys([*reasons, *summary["reasons"]]))})
+    return summary
+
+
+def _train_fast_for_budget_cuda_graph(model: torch.nn.Module, *, prefetch: "FP.BatchPrefetcher",
+                                      device: torch.device, optimizer: torch.optim.Optimizer, budget_seconds: float,
+                                      chunk_size: int, grad_clip_norm: float, fused_grad_clip: bool, rank: int,
+                                      seq_len: int, batch_size: int, precision: str, stop_check_interval: int,
+                                      stop_margin_seconds: float, max_steps: Optional[int],
+                                      lm_head_backward_mode: str, lm_head_tile_size: int, cuda_graph_mode: str,
+                                      cuda_graph_min_total_speedup: float, cuda_graph_max_capture_seconds: float,
+                                      cuda_graph_warmup_steps: int, embed_freeze_steps: int = 0,
+                                      fast_slow: Optional[FastSlowConsolidator] = None,
+                                      time_fn: Callable[[], float] = time.perf_counter) -> dict[str, Any]:
+    """Single-GPU loop with the forward, backward and gradient clip of a step
+    captured once into a CUDA graph and replayed per batch
+    (runner_fast_path.py:10221-10510).  Batches land in two static device
+    buffers; the optimizer step stays eager so momentum warm-up and the AdamW
+    bias corrections (host scalars) keep advancing.  The eager warm-up steps
+    and the capture step are real training steps; their wall time is charged to
+    the budget and reported through the acceptance gate."""
+    model.train()
+    losses: list[torch.Tensor] = []
+    t0 = time_fn()
+    torch.cuda.reset_peak_memory_stats(device)
+    static_in, static_tg = (t.contiguous().clone() for t in prefetch.next())
+
+    def fwd_bwd_clip() -> torch.Tensor:
+        optimizer.zero_grad(set_to_none=False)
+        loss = train_ssm_step(model, static_in, static_tg, chunk_size, ddp_active=False, world_size=1,
+                              precision=precision, lm_head_backward_mode=lm_head_backward_mode,
+                              lm_head_tile_size=lm_head_tile_size)
+        _clip(model, grad_clip_norm, fused_grad_clip)
+        return loss
+
+    def load_next() -> None:
+        a, b = prefetch.next()
+        static_in.copy_(a, non_blocking=True)
+        static_tg.copy_(b, non_blocking=True)
+
+    def after_step(n_done: int) -> None:
+        if precision == "fp8_fused":
+            from .ops.fp8_linear import fused_fp8_flush_all
+            fused_fp8_flush_all(model)
+        if fast_slow is not None and fast_slow.enabled:
+            fast_slow.after_optimizer_step(model, step=n_done)
+
+    warm_n = max(1, int(cuda_graph_warmup_steps))
+    eager_times: list[float] = []
+    side = torch.cuda.Stream(device=device)
+    side.wait_stream(torch.cuda.current_stream(device))
+    tw = time_fn()
+    done = 0
+    with torch.cuda.stream(side):
+        for i in range(warm_n):
+            if i:                                  # the batch that sized the static buffers trains first
+                load_next()
+            torch.cuda.synchronize(device)
+            ts = time_fn()
+            loss = fwd_bwd_clip()
+            zero_embedding_grad_until(model, done, embed_freeze_steps)
+            optimizer.step()
+            torch.cuda.synchronize(device)
+            eager_times.append(time_fn() - ts)
+            done += 1
+            after_step(done)
+            losses.append(loss.detach().clone())
+    torch.cuda.current_stream(device).wait_stream(side)
+    torch.cuda.synchronize(device)
+    warm_s = time_fn() - tw
+
+    load_next()
+    torch.cuda.synchronize(device)
+    tc = time_fn()
+    graph = torch.cuda.CUDAGraph()
+    optimizer.zero_grad(set_to_none=False)
+    # thread-local capture mode: the prefetch thread keeps pinning and copying batches meanwhile
+    with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+        graph_loss = fwd_bwd_clip()
+    torch.cuda.synchronize(device)
+    capture_s = time_fn() - tc
+    # capture records the launches without running them: replay once so this batch trains too
+    graph.replay()
+    zero_embedding_grad_until(model, done, embed_freeze_steps)
+    optimizer.step()
+    done += 1
+    after_step(done)
+    losses.append(graph_loss.detach().clone())
+
+    steps = 0
+    tr = time_fn()
+    every = max(1, int(stop_check_interval))
+    while True:
+        hit_max = max_steps is not None and done >= int(max_steps)
+        if steps % every == 0 or hit_max:
+            if FP.should_stop_training_loop(steps=done, elapsed_s=time_fn() - t0, budget_seconds=budget_seconds,
+                                            stop_margin_seconds=stop_margin_seconds, max_steps=max_steps):
+                break
+        load_next()
+        graph.replay()
+        zero_embedding_grad_until(model, done, embed_freeze_steps)
+        optimizer.step()
+        steps += 1
+        done += 1
+        after_step(done)
+        losses.append(graph_loss.detach().clone())
+    torch.cuda.synchronize(device)
+    replay_s = time_fn() - tr
+    elapsed = time_fn() - t0
+    from .ops import _lib as _ops_lib
+    _ops_lib.assert_ok()
+
+    hist = torch.stack([l.float() for l in losses]).cpu().tolist()
+    eager_step = FP.steady_state_step_seconds(eager_times) if eager_times else warm_s / warm_n
+    graph_step = replay_s / max(steps, 1)
+    summary = FP.summarize_cuda_graph_gate(budget_seconds=budget_seconds, capture_seconds=capture_s,
+                                           warmup_seconds=warm_s, warmup_steps=warm_n,
+                                           eager_step_seconds=eager_step, graph_step_seconds=graph_step,
+                                           min_total_speedup=cuda_graph_min_total_speedup,
+                                           max_capture_seconds=cuda_graph_max_capture_seconds)
+    summary.update({"mode": cuda_graph_mode, "replay_steps": steps, "replay_seconds": replay_s,
+                    "capture_counted_as_training_step": True, "optimizer_step_captured": False,
+                    "eager_step_times": [float(t) for t in eager_times],
+                    "eager_warmup_mean_seconds": warm_s / warm_n})
+    result: dict[str, Any] = {
+        "steps": done, "elapsed_s": elapsed, "rank": rank, "world_size": 1,
+        "initial_loss": hist[0], "final_loss": hist[-1], "loss_history": hist,
+        "loss_delta": hist[-1] - hist[0] if len(hist) >= 2 else float("nan"),
+        "peak_vram_mb": torch.cuda.max_memory_allocated(device) / 2 ** 20,
+        "steady_state_step_seconds": graph_step, "train_sampling_mode": "random",
+        "lm_head_backward_mode": lm_head_backward_mode, "cuda_graph_mode": cuda_graph_mode,
+        "distributed_muon": False, "spectral": spectral_summary(model), "cuda_graph": summary,
+    }
+    result.update(FP.summarize_train_timing(steps=done, elapsed_s=elapsed, batch_size=batch_size, seq_len=seq_len,
+                                            world_size=1))
+    if fast_slow is not None:
+        result["fast_slow"] = fast_slow.diagnostics(model)
+    return result
+
+
 def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor, train_num_tokens: int, stride: int,
                           seq_len: int, batch_size: int, device: torch.device, optimizer: torch.optim.Optimizer,
                           budget_seconds: float, chunk_size: int = 64, grad_clip_norm: float = 1.0,
@@ -238,8 +411,9 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
                           lm_head_backward_mode: str = "fused_streaming_cached", lm_head_tile_size: int = 8192,
                           cuda_graph_mode: str = "none", train_sampling_mode: str = "random",
                           fast_slow: Optional[FastSlowConsolidator] = None, embed_freeze_steps: int = 0,
-                          distributed_muon: bool = False, time_fn: Callable[[], float] = time.perf_counter,
-                          **unused: Any) -> dict[str, Any]:
+                          distributed_muon: bool = False, cuda_graph_min_total_speedup: float = 0.05,
+                          cuda_graph_max_capture_seconds: float = 30.0, cuda_graph_warmup_steps: int = 3,
+                          time_fn: Callable[[], float] = time.perf_counter, **unused: Any) -> dict[str, Any]:
     """Budgeted hot loop.  Returns the train-result dict (``steps``, ``elapsed_s``,
     ``initial_loss``, ``final_loss``, ``loss_history``, throughput keys,
     ``peak_vram_mb`` ...)."""
@@ -262,6 +436,38 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
                                   generator=gen, vocab_size=vocab_size, batch_sampler=sampler)
     if prefetch_batches:
         prefetch.prime()
+    graph_mode = str(cuda_graph_mode).strip().lower()
+    if graph_mode not in {"none", "probe"}:
+        prefetch.close()
+        raise ValueError(f"cuda_graph_mode must be 'none' or 'probe', got {cuda_graph_mode!r}")
+    graph_summary: Optional[dict[str, Any]] = None
+    if graph_mode != "none":
+        gate = dict(budget_seconds=budget_seconds, min_total_speedup=float(cuda_graph_min_total_speedup),
+                    max_capture_seconds=float(cuda_graph_max_capture_seconds))
+        why_not = _cuda_graph_rejection_reasons(device=device, ddp_active=ddp,
+                                                lm_head_backward_mode=lm_head_backward_mode, optimizer=optimizer,
+                                                train_sampling_mode=mode, model=model)
+        if why_not:
+            graph_summary = _rejected_cuda_graph_summary(mode=graph_mode, reasons=why_not, **gate)
+        else:
+            try:
+                return _train_fast_for_budget_cuda_graph(
+                    model, prefetch=prefetch, device=device, optimizer=optimizer, budget_seconds=budget_seconds,
+                    chunk_size=chunk_size, grad_clip_norm=grad_clip_norm, fused_grad_clip=fused_grad_clip,
+                    rank=rank, seq_len=seq_len, batch_size=batch_size, precision=precision,
+                    stop_check_interval=stop_check_interval, stop_margin_seconds=stop_margin_seconds,
+                    max_steps=max_steps, lm_head_backward_mode=lm_head_backward_mode,
+                    lm_head_tile_size=lm_head_tile_size, cuda_graph_mode=graph_mode,
+                    cuda_graph_min_total_speedup=float(cuda_graph_min_total_speedup),
+                    cuda_graph_max_capture_seconds=float(cuda_graph_max_capture_seconds),
+                    cuda_graph_warmup_steps=int(cuda_graph_warmup_steps), embed_freeze_steps=embed_freeze_steps,
+                    fast_slow=fast_slow, time_fn=time_fn)
+            except RuntimeError as exc:           # capture refused: carry on eagerly with the same prefetcher
+                graph_summary = _rejected_cuda_graph_summary(mode=graph_mode, reasons=["capture_failed"], **gate)
+                graph_summary["error"] = str(exc)[:500]
+            finally:
+                if graph_summary is None:
+                    prefetch.close()
     dist_opt = None
     if distributed_muon and ddp and isinstance(optimizer, Muon):
         from .parallel import symm
@@ -330,13 +536,16 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
                                             world_size=world_size))
     if fast_slow is not None:
         result["fast_slow"] = fast_slow.diagnostics(model)
+    if graph_summary is not None:
+        result["cuda_graph"] = graph_summary
     return result
 
 
 _LOOP_KEYS = ("chunk_size", "grad_clip_norm", "fused_grad_clip", "precision", "stop_check_interval",
               "stop_margin_seconds", "compile_full_path", "prefetch_batches", "lm_head_backward_mode",
-              "lm_head_tile_size", "cuda_graph_mode", "train_sampling_mode", "embed_freeze_steps",
-              "distributed_muon") + UNSUPPORTED_OPTIONS
+              "lm_head_tile_size", "cuda_graph_mode", "cuda_graph_min_total_speedup",
+              "cuda_graph_max_capture_seconds", "cuda_graph_warmup_steps", "train_sampling_mode",
+              "embed_freeze_steps", "distributed_muon") + UNSUPPORTED_OPTIONS
 
 
 def _loop_kwargs(config: dict[str, Any]) -> dict[str, Any]:

@@ -9,6 +9,7 @@ import torch
 from chaoscontrol_b200 import launch
 from chaoscontrol_b200 import training_hooks as TH
 from chaoscontrol_b200.models.model import CareStudentLM
+from chaoscontrol_b200.utils.arena import ParamArena
 from chaoscontrol_b200.runner_fast_path import run_condition, train_fast_for_budget, _build_optimizer
 
 
@@ -201,3 +202,48 @@ def test_launch_helpers(tmp_path):
                             sp_model_path=None, world_size=2, dry_run=True)
     assert len(dry["commands"]) == 1 and (tmp_path / "m" / "configs" / "x.yaml").exists()
     assert 1024 < launch.pick_free_port() < 65536
+
+
+def test_cuda_graph_probe_is_rejected_with_reasons_on_cpu():
+    torch.manual_seed(0)
+    tokens = torch.randint(0, 64, (600,), dtype=torch.int16)
+    model = CareStudentLM(vocab_size=64, dim=16, num_layers=1)
+    optim = _build_optimizer(dict(optimizer="adamw", base_lr=1e-3), model)
+    res = train_fast_for_budget(model, train_tokens=tokens, train_num_tokens=600, stride=8, seq_len=16, batch_size=8,
+                                device=torch.device("cpu"), optimizer=optim, budget_seconds=600.0, precision="fp32",
+                                max_steps=3, lm_head_backward_mode="chunked", cuda_graph_mode="probe",
+                                prefetch_batches=False)
+    assert res["steps"] == 3
+    g = res["cuda_graph"]
+    assert g["accepted"] is False and g["mode"] == "probe"
+    assert "cuda_required" in g["reasons"] and "fused_lm_head_required" in g["reasons"]
+    with pytest.raises(ValueError):
+        train_fast_for_budget(model, train_tokens=tokens, train_num_tokens=600, stride=8, seq_len=16, batch_size=8,
+                              device=torch.device("cpu"), optimizer=optim, budget_seconds=1.0,
+                              cuda_graph_mode="always", prefetch_batches=False)
+
+
+@pytest.mark.gpu
+def test_cuda_graph_loop_matches_eager_trajectory():
+    """Same seed, same batches: the replayed step gives the eager loop's losses."""
+    dev = torch.device("cuda:0")
+    tokens = torch.randint(0, 512, (1 << 18,), dtype=torch.int16, generator=torch.Generator().manual_seed(1))
+
+    def run(mode):
+        torch.manual_seed(0)
+        model = CareStudentLM(vocab_size=512, dim=256, num_layers=2).to(dev).to(torch.bfloat16)
+        ParamArena.install(model)
+        optim = _build_optimizer(dict(optimizer="muon", base_lr=0.02), model)
+        return train_fast_for_budget(model, train_tokens=tokens, train_num_tokens=tokens.numel(), stride=64,
+                                     seq_len=256, batch_size=16, device=dev, optimizer=optim, budget_seconds=600.0,
+                                     precision="bf16", max_steps=12, stop_check_interval=1, seed=5,
+                                     lm_head_backward_mode="fused_streaming_cached", cuda_graph_mode=mode,
+                                     cuda_graph_warmup_steps=3, vocab_size=512)
+
+    eager, graph = run("none"), run("probe")
+    assert graph["steps"] == 12 and eager["steps"] == 12
+    g = graph["cuda_graph"]
+    assert g["replay_steps"] == 8 and g["optimizer_step_captured"] is False
+    a, b = torch.tensor(eager["loss_history"]), torch.tensor(graph["loss_history"])
+    assert a.shape == b.shape and torch.allclose(a, b, atol=2e-2, rtol=0), (a, b)
+    assert b[-1] < b[0]

@@ -41,6 +41,7 @@ import torch.distributed as dist
 
 from . import fast_path as FP
 from .config import ssm_constructor_kwargs
+from .crct import CrctRuntime, crct_train_step
 from .data import load_fineweb_tokens, load_fineweb_val_tokens, resolve_param_dtype
 from .models.core import verify_diag_recurrence
 from .models.model import CareStudentLM
@@ -56,8 +57,8 @@ from .utils.arena import get_arena
 __all__ = ["run_condition", "train_fast_for_budget", "build_model", "main", "UNSUPPORTED_OPTIONS"]
 
 # options that switch on research machinery this runner does not carry
-UNSUPPORTED_OPTIONS = ("crct_enabled", "replay_eviction_enabled", "episodic_enabled", "dreamworld_enabled",
-                       "rare_bucket_ce_enabled", "event_sleep_enabled", "criticality_distill_enabled")
+UNSUPPORTED_OPTIONS = ("episodic_enabled", "dreamworld_enabled", "rare_bucket_ce_enabled", "event_sleep_enabled",
+                       "criticality_distill_enabled")
 
 
 # ---------------------------------------------------------------------------
@@ -413,17 +414,36 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
                           fast_slow: Optional[FastSlowConsolidator] = None, embed_freeze_steps: int = 0,
                           distributed_muon: bool = False, cuda_graph_min_total_speedup: float = 0.05,
                           cuda_graph_max_capture_seconds: float = 30.0, cuda_graph_warmup_steps: int = 3,
+                          crct_enabled: bool = False, crct: Optional["CrctRuntime"] = None,
+                          replay_eviction_enabled: bool = False,
                           time_fn: Callable[[], float] = time.perf_counter, **unused: Any) -> dict[str, Any]:
     """Budgeted hot loop.  Returns the train-result dict (``steps``, ``elapsed_s``,
     ``initial_loss``, ``final_loss``, ``loss_history``, throughput keys,
     ``peak_vram_mb`` ...)."""
-    _reject_unsupported(model)
+    crct_enabled = bool(crct_enabled) or crct is not None
+    _reject_unsupported(model, crct_enabled=crct_enabled)
     bad = [k for k in UNSUPPORTED_OPTIONS if unused.get(k)]
     if bad:
         raise NotImplementedError(f"options {bad} are not supported by this runner")
+    if replay_eviction_enabled and not crct_enabled:
+        raise ValueError("replay_eviction_enabled needs crct_enabled: slot maintenance runs beside the teacher")
     ddp = world_size > 1
     if ddp:
         broadcast_params(model)
+    # CRCT: the memory rank leaves for its service loop; train ranks shrink to the gradient group
+    grad_group = None
+    if crct is not None and ddp:
+        if crct.is_memory_rank:
+            B_T = (int(batch_size), int(seq_len))
+            out = crct.run_memory_rank(budget_seconds=budget_seconds, stop_margin_seconds=stop_margin_seconds,
+                                       max_steps=max_steps, batch_shape=B_T, time_fn=time_fn)
+            crct.close()
+            out.update({"initial_loss": 0.0, "final_loss": 0.0, "loss_history": [], "crct": crct.diagnostics()})
+            return out
+        grad_group = crct.train_group
+        rank, world_size = crct.topology["train_ranks"].index(rank), crct.grad_world_size
+        ddp = world_size > 1
+        distributed_muon = False
     model.train()
     mode = str(train_sampling_mode).strip().lower()
     sampler = {"random": None, "sequential_epoch": FP.SequentialShardedStartSampler(),
@@ -447,6 +467,8 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
         why_not = _cuda_graph_rejection_reasons(device=device, ddp_active=ddp,
                                                 lm_head_backward_mode=lm_head_backward_mode, optimizer=optimizer,
                                                 train_sampling_mode=mode, model=model)
+        if crct_enabled:
+            why_not.append("crct_not_supported")
         if why_not:
             graph_summary = _rejected_cuda_graph_summary(mode=graph_mode, reasons=why_not, **gate)
         else:
@@ -483,6 +505,9 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
     epoch_steps = (FP.sequential_epoch_steps(num_tokens=train_num_tokens, seq_len=seq_len, stride=stride,
                                              batch_size=batch_size, world_size=world_size)
                    if mode != "random" else None)
+    sync_teacher = crct is not None and crct.mode == "sync" and crct.world_size > 1
+    if sync_teacher:
+        stop_check_interval = 1                    # the memory rank mirrors every step: it needs every flag
     t0 = time_fn()
     try:
         while True:
@@ -492,16 +517,31 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
                                                      stop_margin_seconds=stop_margin_seconds, max_steps=max_steps)
                 if epoch_steps is not None and steps >= epoch_steps:
                     local = True
-                if should_stop_now(local, device, ddp):
+                if sync_teacher:
+                    if crct.signal_stop_sync(local):
+                        break
+                elif should_stop_now(local, device, ddp, group=grad_group):
                     break
             elif max_steps is not None and steps >= max_steps:
                 break
             ts = time_fn()
             inputs, targets = prefetch.next()
             optimizer.zero_grad(set_to_none=True)
-            loss = train_ssm_step(model, inputs, targets, chunk_size, ddp_active=ddp and dist_opt is None,
-                                  world_size=world_size, precision=precision, compile_full_path=compile_full_path,
-                                  lm_head_backward_mode=lm_head_backward_mode, lm_head_tile_size=lm_head_tile_size)
+            if crct_enabled:
+                payload = None
+                if crct is not None:
+                    payload, inputs, targets = crct.begin_step(inputs, targets, steps)
+                loss = crct_train_step(model, inputs, targets, payload, precision=precision,
+                                       lm_head_backward_mode=lm_head_backward_mode,
+                                       lm_head_tile_size=lm_head_tile_size)
+                if ddp:
+                    allreduce_grads(model, world_size, group=grad_group)
+            else:
+                loss = train_ssm_step(model, inputs, targets, chunk_size, ddp_active=ddp and dist_opt is None,
+                                      world_size=world_size, precision=precision,
+                                      compile_full_path=compile_full_path,
+                                      lm_head_backward_mode=lm_head_backward_mode,
+                                      lm_head_tile_size=lm_head_tile_size)
             zero_embedding_grad_until(model, steps, embed_freeze_steps)
             if dist_opt is not None:
                 dist_opt.step()                     # reduce (sharded) + clip + owned update + gather
@@ -511,6 +551,8 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
             if precision == "fp8_fused":
                 from .ops.fp8_linear import fused_fp8_flush_all
                 fused_fp8_flush_all(model)
+            if crct is not None:
+                crct.after_optimizer_step(steps)
             steps += 1
             if fast_slow is not None and fast_slow.enabled:
                 fast_slow.after_optimizer_step(model, step=steps)
@@ -518,6 +560,8 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
             step_times.append(time_fn() - ts)
     finally:
         prefetch.close()
+        if crct is not None:
+            crct.close()
     if device.type == "cuda":
         torch.cuda.synchronize(device)
     elapsed = time_fn() - t0
@@ -538,6 +582,8 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
         result["fast_slow"] = fast_slow.diagnostics(model)
     if graph_summary is not None:
         result["cuda_graph"] = graph_summary
+    if crct is not None:
+        result["crct"] = crct.diagnostics()
     return result
 
 
@@ -545,7 +591,8 @@ _LOOP_KEYS = ("chunk_size", "grad_clip_norm", "fused_grad_clip", "precision", "s
               "stop_margin_seconds", "compile_full_path", "prefetch_batches", "lm_head_backward_mode",
               "lm_head_tile_size", "cuda_graph_mode", "cuda_graph_min_total_speedup",
               "cuda_graph_max_capture_seconds", "cuda_graph_warmup_steps", "train_sampling_mode",
-              "embed_freeze_steps", "distributed_muon") + UNSUPPORTED_OPTIONS
+              "embed_freeze_steps", "distributed_muon", "crct_enabled",
+              "replay_eviction_enabled") + UNSUPPORTED_OPTIONS
 
 
 def _loop_kwargs(config: dict[str, Any]) -> dict[str, Any]:
@@ -619,7 +666,7 @@ def run_condition(config: dict[str, Any], *, data_path: str, sp_model_path: Opti
                                            batch_size=batch, eval_batches=max(0, eval_batches), seed=seed)
     model = build_model(config, device, dtype)
     _apply_embed_init(model, config, device)
-    _reject_unsupported(model)
+    _reject_unsupported(model, crct_enabled=bool(config.get("crct_enabled", False)))
     n_params = sum(p.numel() for p in model.parameters())
     ckpt_meta = None
     if str(config.get("checkpoint_path", "") or "").strip():
@@ -661,10 +708,14 @@ def run_condition(config: dict[str, Any], *, data_path: str, sp_model_path: Opti
                 dist.barrier()
         fast_slow = FastSlowConsolidator.from_config(model, config)
         common.pop("model")
+        max_steps = None if config.get("max_steps") is None else int(config["max_steps"])
+        crct = None
+        if bool(config.get("crct_enabled", False)):
+            crct = CrctRuntime(model=model, config=config, rank=rank, world_size=world_size, device=device,
+                               batch_size=batch, seq_len=seq_len, total_steps=max_steps)
         train_result = train_fast_for_budget(
-            model, optimizer=optimizer, budget_seconds=budget_seconds, fast_slow=fast_slow,
-            max_steps=None if config.get("max_steps") is None else int(config["max_steps"]),
-            **common, **_loop_kwargs(config))
+            model, optimizer=optimizer, budget_seconds=budget_seconds, fast_slow=fast_slow, max_steps=max_steps,
+            crct=crct, **common, **_loop_kwargs(config))
     if ddp:
         _control_barrier(control, "post_train")
 

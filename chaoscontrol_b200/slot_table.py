@@ -135,9 +135,12 @@ class SlotTable:
         cap = 64 if self._store is None else self._store.shape[0]
         while cap < n_total:
             cap *= 2
-        new = torch.zeros(cap, like.shape[-1], dtype=like.dtype, device=like.device)
-        if self._store is not None and self._n:
-            new[: self._n].copy_(self._store[: self._n])
+        # the store outlives any inference-mode scope a writer runs in: allocate it as a normal tensor so
+        # later in-place slot edits are legal from every context
+        with torch.inference_mode(False):
+            new = torch.zeros(cap, like.shape[-1], dtype=like.dtype, device=like.device)
+            if self._store is not None and self._n:
+                new[: self._n].copy_(self._store[: self._n])
         self._store = new
 
     def __len__(self) -> int:

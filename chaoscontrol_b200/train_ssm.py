@@ -63,8 +63,13 @@ def fused_lm_head_backend_for_mode(lm_head_backward_mode: str) -> str:
         ) from exc
 
 
-def _reject_unsupported(model: nn.Module) -> None:
+def _reject_unsupported(model: nn.Module, *, crct_enabled: bool = False) -> None:
+    """With ``crct_enabled`` the episodic store and the bucket prototypes may be
+    present: train ranks only ever run ``encode(memory_mode="packet")``, which
+    reads neither (runner_fast_path.py:1223-1244)."""
     for attr, label in _UNSUPPORTED_ATTRS:
+        if crct_enabled and attr in ("outer_model", "bucket_prototypes_module"):
+            continue
         if getattr(model, attr, None) is not None:
             raise ValueError(f"train_ssm does not support the {label} path (model.{attr} is not "
                              "None). Use chaoscontrol_b200.training.train_chaoscontrol_for_budget "

@@ -93,8 +93,18 @@ def test_run_condition_cpu_end_to_end(tmp_path, monkeypatch):
                        output_ckpt=None, world_size_override=None)
     assert ev["train"]["steps"] == 0 and np.isfinite(ev["eval"]["bpb"])
     with pytest.raises(NotImplementedError):
+        run_condition(_config(episodic_enabled=True, warmup_steps=0), data_path=str(tmp_path), sp_model_path=None,
+                      budget_seconds=1.0, output_json=None, output_ckpt=None, world_size_override=None)
+    with pytest.raises(ValueError):                                 # the teacher needs an episodic store
         run_condition(_config(crct_enabled=True, warmup_steps=0), data_path=str(tmp_path), sp_model_path=None,
                       budget_seconds=1.0, output_json=None, output_ckpt=None, world_size_override=None)
+    mem = run_condition(_config(crct_enabled=True, replay_eviction_enabled=True, warmup_steps=1, outer_model_dim=8,
+                                outer_model_type="multislot", outer_max_slots=0, buffer_mode="append_only",
+                                crct_memory_write_tokens_per_step=4, fast_slow_enabled=False, weight_ema_decay=0.0),
+                        data_path=str(tmp_path), sp_model_path="fake.model", budget_seconds=60.0, output_json=None,
+                        output_ckpt=None, world_size_override=None)
+    assert mem["train"]["steps"] == 6 and mem["train"]["crct"]["teacher_payloads"] == 6
+    assert mem["train"]["crct"]["transport_mode"] == "inline" and np.isfinite(mem["eval"]["bpb"])
     with pytest.raises(ValueError):
         run_condition(_config(), data_path=str(tmp_path), sp_model_path=None, budget_seconds=1.0, output_json=None,
                       output_ckpt=None, world_size_override=4)

@@ -42,7 +42,7 @@ from .wake_cache import TransactionalWakeCache
 __all__ = ["crct_rank_topology", "crct_full_input_ids", "crct_valid_mask", "score_payload_inline",
            "packet_payload_inline", "broadcast_params_coalesced", "collect_teacher_payload_sync",
            "TeacherMailbox", "memory_rank_should_stop", "memory_rank_defer_stop", "CrctRuntime",
-           "TEACHER_RESULT_SLICE_NAMES", "weighted_row_scale", "crct_train_step"]
+           "TEACHER_RESULT_SLICE_NAMES", "weighted_row_scale", "crct_train_step", "SlotCommitPeerLane"]
 
 TEACHER_RESULT_SLICE_NAMES = ("target", "confidence", "loss_weight", "utility", "memory_residual", "memory_gate",
                               "plasticity_coverage", "plasticity_confidence", "plasticity_budget")
@@ -791,6 +791,165 @@ class TeacherMailbox:
 
 
 # ---------------------------------------------------------------------------
+# slot-commit lane between two memory ranks
+# ---------------------------------------------------------------------------
+_LANE_MAGIC = 0x4343424C414E4531
+_LANE_FIELDS = 16
+_SURVIVAL_SCALE = 1_000_000
+
+
+class SlotCommitPeerLane:
+    """Lane that carries ``SlotCommit`` records between the packet-serving rank
+    and the maintenance rank of a split-memory topology (role of
+    runner_fast_path.py:1942-2455).  The packet rank publishes its APPEND
+    commits, the maintenance rank publishes confirmed maintenance commits back;
+    train ranks never touch it.
+
+    A commit is a few hundred bytes that the host produces and the host
+    consumes (the slot table is host-managed), so the lane is a pair of SPSC
+    rings in POSIX shared memory, ``<name>_p2m`` and ``<name>_m2p``, not a device
+    send: nothing to match, nothing to abandon at shutdown, and a poll is exact.
+    Record: 16 int64 ``[magic, version, seq, slot_id, action, step,
+    base_generation (-1 = none), new_generation, bucket_id, event_id,
+    survival * 1e6, dtype code, numel, rows, cols, 0]`` plus ``max_payload_bytes``
+    of tensor data.  A full ring drops the oldest queued commit on the sending
+    side (``queue_overwrites``); a commit against a generation the mirror has
+    moved past is dropped on the receiving side (``stale_generation_drops``).
+    The packet rank creates the rings, the maintenance rank attaches."""
+
+    def __init__(self, *, name: str, rank: int, packet_rank: int, maintenance_rank: int,
+                 ring_capacity: int = 1024, queue_capacity: int = 1024, max_payload_bytes: int = 4096,
+                 attach_timeout_s: float = 30.0) -> None:
+        from .episodic import native as N
+        self.rank, self.packet_rank, self.maintenance_rank = int(rank), int(packet_rank), int(maintenance_rank)
+        self.participant = self.rank in (self.packet_rank, self.maintenance_rank)
+        self.capacity = max(1, int(queue_capacity))
+        self.max_payload = int(max_payload_bytes)
+        self._dtype = np.dtype([("hdr", "<i8", (_LANE_FIELDS,)), ("payload", "u1", (self.max_payload,))])
+        self._q: deque = deque()
+        self._seq = 0
+        self._tx = self._rx = None
+        self.metrics: dict[str, Any] = {
+            "mode": "slot_commit_shm_ring", "participant": self.participant, "submitted": 0,
+            "queue_overwrites": 0, "sent": 0, "received": 0, "applied": 0, "dropped": 0,
+            "stale_generation_drops": 0, "append_commits_applied": 0, "maintenance_commits_applied": 0,
+            "oversize_drops": 0, "last_drop_reason": ""}
+        if not self.participant:
+            return
+        creator = self.rank == self.packet_rank
+        self._creator = creator
+        self._names = (f"{name}_p2m", f"{name}_m2p")
+        t_end = time.monotonic() + float(attach_timeout_s)
+        while True:
+            opened: list = []
+            try:
+                for nm in self._names:
+                    opened.append(N.Ring(self._dtype, int(ring_capacity), shm_name=nm, create=creator))
+                break
+            except ValueError:
+                for o in opened:
+                    o.close()
+                if creator or time.monotonic() > t_end:
+                    raise
+                time.sleep(0.01)
+        p2m, m2p = opened
+        self._tx, self._rx = (p2m, m2p) if creator else (m2p, p2m)
+
+    def _record(self, c) -> Optional[np.ndarray]:
+        from .slot_commit import slot_commit_dtype_code
+        rec = np.zeros((), dtype=self._dtype)
+        t = None if c.tensor is None else c.tensor.detach().cpu().contiguous()
+        rows = cols = nbytes = 0
+        if t is not None:
+            rows, cols = t.reshape(-1, t.shape[-1]).shape if t.dim() else (1, 1)
+            nbytes = t.numel() * t.element_size()
+            if nbytes > self.max_payload:
+                return None
+            rec["payload"][:nbytes] = t.reshape(-1).view(torch.uint8).numpy()
+        rec["hdr"] = [_LANE_MAGIC, 1, self._seq, c.slot_id, int(c.action), c.step,
+                      -1 if c.base_generation is None else c.base_generation, c.new_generation, c.bucket_id,
+                      c.event_id, int(round(float(c.survival_factor) * _SURVIVAL_SCALE)),
+                      0 if t is None else slot_commit_dtype_code(t.dtype), 0 if t is None else t.numel(),
+                      rows, cols, nbytes]
+        return rec
+
+    def submit(self, commit) -> None:
+        if not self.participant:
+            return
+        if len(self._q) >= self.capacity:
+            self._q.popleft()
+            self.metrics["queue_overwrites"] += 1
+        self._q.append(commit)
+        self.metrics["submitted"] += 1
+
+    def pump(self, model: Any) -> int:
+        """Push queued commits while the ring has room, then apply every commit
+        that has arrived.  Returns how many were applied."""
+        if not self.participant or self._tx is None:
+            return 0
+        while self._q:
+            rec = self._record(self._q[0])
+            if rec is None:
+                self._q.popleft()
+                self.metrics["oversize_drops"] += 1
+                continue
+            if not self._tx.push(rec):
+                break
+            self._q.popleft()
+            self._seq += 1
+            self.metrics["sent"] += 1
+        applied = 0
+        while True:
+            rec = self._rx.pop()
+            if rec is None:
+                break
+            self.metrics["received"] += 1
+            applied += self._apply(model, rec)
+        return applied
+
+    def _apply(self, model: Any, rec) -> int:
+        from .slot_commit import (SlotCommit, SlotCommitAction, apply_append_slot_commit_to_model,
+                                  apply_slot_commit_to_model, slot_commit_dtype_from_code)
+        m = [int(v) for v in rec["hdr"]]
+        if m[0] != _LANE_MAGIC:
+            self.metrics["dropped"] += 1
+            self.metrics["last_drop_reason"] = "bad_magic"
+            return 0
+        tensor = None
+        if m[12] > 0:
+            raw = torch.from_numpy(np.array(rec["payload"][: m[15]], copy=True))
+            tensor = raw.view(slot_commit_dtype_from_code(m[11])).reshape(m[13], m[14])
+            dev = next(model.parameters()).device
+            tensor = tensor.to(dev)
+        action = SlotCommitAction(m[4])
+        c = SlotCommit(slot_id=m[3], action=action, step=m[5], base_generation=None if m[6] < 0 else m[6],
+                       new_generation=m[7], bucket_id=m[8], event_id=m[9],
+                       survival_factor=m[10] / _SURVIVAL_SCALE, tensor=tensor)
+        append = action is SlotCommitAction.APPEND
+        ok, why = (apply_append_slot_commit_to_model if append else apply_slot_commit_to_model)(model, c)
+        if ok:
+            self.metrics["applied"] += 1
+            self.metrics["append_commits_applied" if append else "maintenance_commits_applied"] += 1
+            return 1
+        self.metrics["dropped"] += 1
+        self.metrics["last_drop_reason"] = why
+        if why == "stale_generation":
+            self.metrics["stale_generation_drops"] += 1
+        return 0
+
+    def close(self, model: Any = None) -> None:
+        """Drain what has already arrived, then release (and, on the creating side, unlink) the rings."""
+        if not self.participant or self._tx is None:
+            return
+        if model is not None:
+            self.pump(model)
+        for r in (self._tx, self._rx):
+            r.close(unlink=self._creator)
+        self._tx = self._rx = None
+        self.participant = False
+
+
+# ---------------------------------------------------------------------------
 # runtime object the training loop talks to
 # ---------------------------------------------------------------------------
 def _weight_bytes(model: torch.nn.Module, scope: str) -> int:
@@ -828,7 +987,7 @@ class CrctRuntime:
         self.total_steps = total_steps
         self.topology = crct_rank_topology(world_size=world_size,
                                            split_memory_ranks=bool(get("crct_split_memory_ranks", False)))
-        self.memory_rank = self.topology["packet_rank"] if world_size > 1 else -1
+        self.memory_rank = self.topology["packet_rank"] if world_size > 1 else -1     # the sync teacher
         self.is_memory_rank = world_size > 1 and rank in self.topology["memory_ranks"]
         mode = str(get("crct_teacher_transport_mode", "async_rank0_memory_mailbox")).strip().lower()
         if world_size == 1:
@@ -854,41 +1013,69 @@ class CrctRuntime:
                          if bool(get("crct_scarcity_enabled", True)) else None)
         self.conflict = (CrctGradientConflictMonitor(enabled=True)
                          if bool(get("crct_gradient_conflict_enabled", False)) else None)
+        topo = self.topology
+        split = topo["split_memory_ranks"]
+        self.packet_rank, self.maint_rank = topo["packet_rank"], topo["maintenance_rank"]
+        self.is_packet_rank = world_size > 1 and rank == self.packet_rank
+        self.is_maintenance_rank = world_size > 1 and rank == self.maint_rank
         self.replay_loop = None
-        if bool(get("replay_eviction_enabled", False)) and (self.is_memory_rank or world_size == 1):
+        if bool(get("replay_eviction_enabled", False)) and (self.is_maintenance_rank or world_size == 1):
             from .replay_eviction import ReplayEvictionLoop
             self.replay_loop = ReplayEvictionLoop(**{k[len("replay_eviction_"):]: v for k, v in config.items()
                                                      if k.startswith("replay_eviction_") and
                                                      k != "replay_eviction_enabled"})
         # process groups: every rank must take part in every new_group call, in the same order
         self.all_group = all_group
-        self.train_group = None
-        self.teacher_group = None
+        self.train_group = self.teacher_group = self.maint_group = self.peer_group = None
         if world_size > 1:
             backend = "nccl" if device.type == "cuda" else "gloo"
-            self.train_group = dist.new_group(self.topology["train_ranks"], backend=backend)
-            self.teacher_group = dist.new_group(sorted({0, self.memory_rank}), backend=backend)
-        self.grad_world_size = self.topology["grad_world_size"] if world_size > 1 else 1
-        self.mailbox: Optional[TeacherMailbox] = None
-        if self.mode == "async_rank0_memory_mailbox" and rank in (0, self.memory_rank):
+            self.train_group = dist.new_group(topo["train_ranks"], backend=backend)
+            self.teacher_group = dist.new_group(sorted({0, self.packet_rank}), backend=backend)
+            if split:
+                self.maint_group = dist.new_group(sorted({0, self.maint_rank}), backend=backend)
+                self.peer_group = dist.new_group([self.packet_rank, self.maint_rank], backend=backend)
+        self.grad_world_size = topo["grad_world_size"] if world_size > 1 else 1
+        self.mailbox: Optional[TeacherMailbox] = None           # rank 0 <-> packet rank
+        self.maint_mailbox: Optional[TeacherMailbox] = None     # rank 0 -> maintenance rank (split topology)
+        self.lane: Optional[SlotCommitPeerLane] = None
+        if self.mode == "async_rank0_memory_mailbox" and rank in (0, self.packet_rank, self.maint_rank):
             name = str(get("crct_mailbox_name", "") or
                        f"/ccb_crct_{os.environ.get('MASTER_PORT', '0')}_{os.getppid()}")
             hidden = int(getattr(model, "dim", 0) or get("model_dim", 0))
             dt = {"fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16}[
                 str(get("crct_async_payload_dtype", "fp32")).lower()]
-            scope = "full" if self.topology["packet_rank"] == self.topology["maintenance_rank"] else "packet"
-            if rank != 0:                                    # attach only after rank 0 has created the regions
-                dist.barrier(group=self.teacher_group)
-            self.mailbox = TeacherMailbox(
-                name=name, role="train" if rank == 0 else "memory", batch_size=batch_size, seq_len=seq_len,
-                hidden_dim=hidden, device=device, payload_dtype=dt,
-                capacity=int(get("crct_mailbox_capacity", 8)),
-                max_local_batches=int(get("crct_max_local_batches", 8)),
-                max_payload_lag_steps=int(get("crct_max_payload_lag_steps", 8)),
-                score_interval_steps=self.score_interval, weight_bytes=_weight_bytes(model, scope),
-                weight_snapshot_scope=scope, source_rank=rank)
+            scope = "packet" if split else "full"
+
+            def open_box(box_name: str, role: str, box_scope: str) -> TeacherMailbox:
+                return TeacherMailbox(
+                    name=box_name, role=role, batch_size=batch_size, seq_len=seq_len, hidden_dim=hidden,
+                    device=device, payload_dtype=dt, capacity=int(get("crct_mailbox_capacity", 8)),
+                    max_local_batches=int(get("crct_max_local_batches", 8)),
+                    max_payload_lag_steps=int(get("crct_max_payload_lag_steps", 8)),
+                    score_interval_steps=self.score_interval, weight_bytes=_weight_bytes(model, box_scope),
+                    weight_snapshot_scope=box_scope, source_rank=rank)
+            # rank 0 creates the regions, the memory side attaches after a barrier on their two-rank group
             if rank == 0:
+                self.mailbox = open_box(name, "train", scope)
                 dist.barrier(group=self.teacher_group)
+                if split:
+                    self.maint_mailbox = open_box(name + "_m", "train", "full")
+                    dist.barrier(group=self.maint_group)
+            else:
+                if rank == self.packet_rank:
+                    dist.barrier(group=self.teacher_group)
+                    self.mailbox = open_box(name, "memory", scope)
+                if split and rank == self.maint_rank:
+                    dist.barrier(group=self.maint_group)
+                    self.maint_mailbox = open_box(name + "_m", "memory", "full")
+                if split:
+                    if rank == self.maint_rank:              # attach after the packet rank has created the rings
+                        dist.barrier(group=self.peer_group)
+                    self.lane = SlotCommitPeerLane(name=name + "_lane", rank=rank, packet_rank=self.packet_rank,
+                                                   maintenance_rank=self.maint_rank,
+                                                   queue_capacity=int(get("crct_slot_commit_queue", 1024)))
+                    if rank == self.packet_rank:
+                        dist.barrier(group=self.peer_group)
         self._mailbox_final: Optional[dict[str, Any]] = None
         self.teacher_requests = 0
         self.teacher_payloads = 0
@@ -926,6 +1113,23 @@ class CrctRuntime:
                                          cue=getattr(self.model, "_last_crct_probe_outer_cue", None),
                                          cache_read_cutoff=None, step=int(step))
 
+    def _publish_appends(self, scored: dict[str, Any], step: int) -> None:
+        """Packet rank of a split topology: its slot appends go to the maintenance replica."""
+        if self.lane is None:
+            return
+        from .slot_commit import SlotCommit, SlotCommitAction
+        for r in scored.get("memory_write_records") or []:
+            self.lane.submit(SlotCommit(slot_id=int(r["slot_id"]), action=SlotCommitAction.APPEND, step=int(step),
+                                        base_generation=None, new_generation=int(r["generation"]),
+                                        bucket_id=int(r["bucket_id"]), event_id=int(r["event_id"]),
+                                        tensor=r["tensor"]))
+
+    def _maintenance_tick(self, step: int) -> None:
+        out = self.replay_loop.tick(model=self.model, step=step)
+        if self.lane is not None:                            # confirmed decisions go to the packet rank's mirror
+            for c in out.slot_commits:
+                self.lane.submit(c)
+
     # -- train rank ----------------------------------------------------------
     def begin_step(self, inputs: torch.Tensor, targets: torch.Tensor,
                    step: int) -> tuple[Optional[dict[str, Any]], torch.Tensor, torch.Tensor]:
@@ -947,6 +1151,8 @@ class CrctRuntime:
             return None, inputs, targets
         else:
             self.teacher_requests += 1
+            if self.maint_mailbox is not None:                # probe frames for the maintenance rank
+                self.maint_mailbox.begin_step(inputs=inputs, targets=targets, step=step)
             ready = self.mailbox.begin_step(inputs=inputs, targets=targets, step=step)
             if ready is not None:
                 payload, inputs, targets = ready
@@ -961,6 +1167,9 @@ class CrctRuntime:
         if self.mode == "async_rank0_memory_mailbox" and self.mailbox is not None:
             if self.mailbox.maybe_publish_weight_snapshot(self.model, step=step, interval=self.param_sync_interval):
                 self.param_syncs += 1
+            if self.maint_mailbox is not None:
+                self.maint_mailbox.maybe_publish_weight_snapshot(self.model, step=step,
+                                                                 interval=self.param_sync_interval)
         elif self.mode == "sync" and self.param_sync_interval > 0 and step % self.param_sync_interval == 0:
             if self.rank in (0, self.memory_rank):
                 self.param_syncs += broadcast_params_coalesced(self.model, src=0, group=self.teacher_group)
@@ -1002,7 +1211,8 @@ class CrctRuntime:
                     ticks += 1
                 step += 1
         else:
-            mb = self.mailbox
+            serves = self.mailbox is not None and self.is_packet_rank
+            mb = self.mailbox if serves else self.maint_mailbox
             assert mb is not None
             last_step = 0
             while True:
@@ -1017,21 +1227,33 @@ class CrctRuntime:
                                                        shutdown_requested=False):
                     break
                 mb.poll_weight_snapshot(self.model)
+                if self.lane is not None:
+                    self.lane.pump(self.model)
                 req = mb.pop_request()
                 if req is None:
                     if self.replay_loop is not None and self.replay_loop.has_probe():
-                        self.replay_loop.tick(model=self.model, step=last_step)
+                        self._maintenance_tick(last_step)
                         ticks += 1
                     else:
                         time.sleep(idle_sleep_s)
                     continue
                 rid, step, ids = req
                 last_step = step
+                if not serves:                               # maintenance-only rank: the batch is a probe frame
+                    if self.replay_loop is not None:
+                        full = ids.long()
+                        self.replay_loop.cache_probe(input_ids=full, valid_mask=crct_valid_mask(full), cue=None,
+                                                     cache_read_cutoff=None, step=int(step))
+                    served += 1
+                    continue
                 ts = time_fn()
                 scored = self._score(ids[:, :-1].to(input_dtype), ids[:, 1:].long(), step)
                 self._feed_maintenance(step)
+                self._publish_appends(scored, step)
                 if mb.push_result(request_id=rid, step=step, scored=scored, score_seconds=time_fn() - ts):
                     served += 1
+            if self.lane is not None:
+                self.lane.close(self.model)
         self.packets_served = served
         out = self.diagnostics()
         out.update({"steps": served, "elapsed_s": time_fn() - t0, "rank": self.rank, "world_size": self.world_size,
@@ -1051,6 +1273,12 @@ class CrctRuntime:
             self._mailbox_final = self.mailbox.metrics.as_dict()
             self.mailbox.close()
             self.mailbox = None
+        if self.maint_mailbox is not None:
+            self.maint_mailbox.request_shutdown()
+            if self._mailbox_final is None:
+                self._mailbox_final = self.maint_mailbox.metrics.as_dict()
+            self.maint_mailbox.close()
+            self.maint_mailbox = None
         if self.replay_loop is not None:
             self.replay_loop.close()
 
@@ -1066,6 +1294,8 @@ class CrctRuntime:
             d["mailbox"] = self.mailbox.metrics.as_dict()
         elif self._mailbox_final is not None:
             d["mailbox"] = self._mailbox_final
+        if self.lane is not None:
+            d["slot_commit_lane"] = dict(self.lane.metrics)
         if self.scarcity is not None:
             d["scarcity"] = {k: float(v) for k, v in vars(self.scarcity).items() if isinstance(v, (int, float))}
         if self.replay_loop is not None:

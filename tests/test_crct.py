@@ -204,7 +204,7 @@ def test_train_loop_inline_teacher_and_maintenance():
                               replay_eviction_enabled=True, **_loop_kw())
 
 
-def _crct_rank(rank, world, port, mode, out_dir):
+def _crct_rank(rank, world, port, mode, out_dir, split=False):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
@@ -213,7 +213,9 @@ def _crct_rank(rank, world, port, mode, out_dir):
         tokens = torch.randint(0, 48, (4000,), dtype=torch.int16, generator=torch.Generator().manual_seed(0))
         cfg = dict(crct_enabled=True, crct_teacher_transport_mode=mode, crct_memory_write_tokens_per_step=4,
                    crct_teacher_param_sync_interval=2, crct_mailbox_name=f"/ccb_t_run_{port}", model_dim=16,
-                   crct_max_payload_lag_steps=64, crct_max_local_batches=64, crct_mailbox_capacity=64)
+                   crct_max_payload_lag_steps=64, crct_max_local_batches=64, crct_mailbox_capacity=64,
+                   crct_split_memory_ranks=split, replay_eviction_enabled=split,
+                   replay_eviction_min_slot_age_steps=0)
         rt = C.CrctRuntime(model=model, config=cfg, rank=rank, world_size=world, device=torch.device("cpu"),
                            batch_size=3, seq_len=8, total_steps=12)
         optim = _build_optimizer(dict(optimizer="adamw", base_lr=1e-3), model)
@@ -226,9 +228,11 @@ def _crct_rank(rank, world, port, mode, out_dir):
             return t_real()
         res = train_fast_for_budget(model, train_tokens=tokens, train_num_tokens=4000, optimizer=optim, max_steps=12,
                                     crct=rt, rank=rank, world_size=world, time_fn=slow_clock,
+                                    replay_eviction_enabled=split,
                                     **_loop_kw(budget_seconds=20.0, stop_margin_seconds=0.0))
         torch.save({"res": {k: v for k, v in res.items() if k != "spectral"},
-                    "w": model.lm_head.weight.detach().clone()}, os.path.join(out_dir, f"r{rank}.pt"))
+                    "w": model.lm_head.weight.detach().clone(),
+                    "slots": int(model.outer_model.table.n_active)}, os.path.join(out_dir, f"r{rank}.pt"))
         dist.barrier()
     finally:
         dist.destroy_process_group()
@@ -253,6 +257,67 @@ def test_two_train_ranks_and_a_memory_rank(tmp_path, mode, port):
         assert d0["mailbox"]["weight_snapshots_published"] >= 1
         assert mem["crct"]["mailbox"]["weight_snapshots_applied"] >= 1
         assert mem["crct"]["mailbox"]["requests_served"] == mem["steps"]
+
+
+def test_slot_commit_lane_appends_maintenance_and_drops():
+    from chaoscontrol_b200.slot_commit import SlotCommit, SlotCommitAction
+    packet_model, maint_model = _memory_model(), _memory_model()
+    kw = dict(name=f"/ccb_t_lane_{os.getpid()}", packet_rank=2, maintenance_rank=3, queue_capacity=4)
+    a = C.SlotCommitPeerLane(rank=2, **kw)
+    b = C.SlotCommitPeerLane(rank=3, **kw)
+    idle = C.SlotCommitPeerLane(rank=0, **kw)
+    try:
+        assert not idle.participant and idle.pump(packet_model) == 0
+        # the packet rank appends locally, then publishes the same records
+        hidden = torch.randn(1, 3, 16)
+        recs = packet_model.append_memory_from_hidden(hidden, max_tokens=3)
+        for r in recs:
+            a.submit(SlotCommit(slot_id=r["slot_id"], action=SlotCommitAction.APPEND, step=1, base_generation=None,
+                                new_generation=r["generation"], bucket_id=r["bucket_id"], event_id=r["event_id"],
+                                tensor=r["tensor"]))
+        assert a.pump(packet_model) == 0 and a.metrics["sent"] == 3
+        assert b.pump(maint_model) == 3 and maint_model.outer_model.table.n_active == 3
+        sid = recs[0]["slot_id"]
+        assert torch.allclose(maint_model.outer_model.table.get_tensor(sid), recs[0]["tensor"])
+        # a maintenance decision travels back and lands on the packet rank's mirror
+        gen = int(maint_model.outer_model.table.record(sid).write_generation)
+        b.submit(SlotCommit(slot_id=sid, action=SlotCommitAction.EVICT, step=2, base_generation=gen,
+                            new_generation=gen + 1, reason="test"))
+        b.submit(SlotCommit(slot_id=recs[1]["slot_id"], action=SlotCommitAction.EVICT, step=2,
+                            base_generation=gen + 7, new_generation=gen + 8))
+        b.pump(maint_model)
+        assert a.pump(packet_model) == 1
+        assert a.metrics["maintenance_commits_applied"] == 1 and a.metrics["stale_generation_drops"] == 1
+        assert packet_model.outer_model.table.n_active == 2
+        # bounded queue and payload
+        for i in range(6):
+            a.submit(SlotCommit(slot_id=100 + i, action=SlotCommitAction.APPEND, step=3, base_generation=None,
+                                new_generation=1, tensor=torch.zeros(1, 8)))
+        assert a.metrics["queue_overwrites"] == 2
+        a.submit(SlotCommit(slot_id=999, action=SlotCommitAction.APPEND, step=3, base_generation=None,
+                            new_generation=1, tensor=torch.zeros(1, 2048)))
+        a.pump(packet_model)
+        assert a.metrics["oversize_drops"] == 1
+    finally:
+        b.close(maint_model)
+        a.close(packet_model)
+
+
+def test_split_memory_ranks_exchange_slot_commits(tmp_path):
+    """2 train ranks + packet rank + maintenance rank: appends made while serving packets reach the
+    maintenance replica over the peer lane."""
+    mp.spawn(_crct_rank, args=(4, 29747, "async_rank0_memory_mailbox", str(tmp_path), True), nprocs=4, join=True)
+    r = [torch.load(tmp_path / f"r{i}.pt", weights_only=False) for i in range(4)]
+    assert torch.allclose(r[0]["w"], r[1]["w"], atol=1e-6)
+    packet, maint = r[2]["res"], r[3]["res"]
+    assert packet["crct"]["topology"]["split_memory_ranks"] and packet["crct"]["topology"]["train_ranks"] == [0, 1]
+    pl, ml = packet["crct"]["slot_commit_lane"], maint["crct"]["slot_commit_lane"]
+    assert packet["steps"] >= 1 and pl["submitted"] >= 4 and pl["sent"] >= 1
+    assert ml["append_commits_applied"] >= 1 and ml["append_commits_applied"] == ml["received"] - ml["dropped"]
+    assert r[3]["slots"] == ml["append_commits_applied"]                 # the replica holds what arrived
+    assert pl["mode"] == "slot_commit_shm_ring"
+    assert maint["crct"]["replay_eviction"]["frames_ingested"] >= 1
+    assert "replay_eviction" not in packet["crct"]
 
 
 @pytest.mark.gpu

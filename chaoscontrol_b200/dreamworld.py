@@ -21,7 +21,8 @@ import torch
 from .train_ssm import full_lm_head_backward, fused_lm_head_backend_for_mode, fused_lm_head_backward
 from .utils.arena import get_arena
 
-__all__ = ["DreamReplayEntry", "DreamReplayBuffer", "build_dream_replay_tokens", "capture_dream_entry",
+__all__ = ["LossTriggeredReplayDecision", "LossTriggeredReplayEMA", "DreamReplayEntry", "DreamReplayBuffer",
+           "build_dream_replay_tokens", "capture_dream_entry",
            "dreamworld_replay_backward", "compute_utility_signal", "dreamworld_replay_from_cache_entry",
            "dreamworld_replay_from_cache_slots", "replay_grad_norm"]
 
@@ -195,3 +196,83 @@ def dreamworld_replay_from_cache_entry(*, model: Any, cache: Any, slot: int, cur
             "replay_grad_cos_common": float("nan"), "replay_grad_cos_rare": raw,
             "replay_grad_cos_total": float("nan"), "utility_signal_raw": raw,
             "utility_signal_transformed": transformed}
+
+
+# ---------------------------------------------------------------------------
+# loss-pressure gate for event-triggered replay
+# ---------------------------------------------------------------------------
+class LossTriggeredReplayDecision:
+    """One gate evaluation.  The eight numbers stay on the device in one tensor
+    and travel to pinned host memory with one asynchronous copy; reading a field
+    waits for that copy only if it has not landed yet, so a loop that looks at
+    the decision one step later never stalls (runner_fast_path.py:6035-6132)."""
+
+    FIELDS = ("local_loss", "ema_loss", "local_ratio", "local_pressure", "global_pressure", "fire_count",
+              "local_fire", "triggered")
+
+    def __init__(self, packed: torch.Tensor) -> None:
+        self._event = None
+        if packed.is_cuda:
+            self._host = torch.empty(packed.shape, dtype=packed.dtype, pin_memory=True)
+            self._host.copy_(packed, non_blocking=True)
+            self._event = torch.cuda.Event()
+            self._event.record()
+        else:
+            self._host = packed.detach().clone()
+
+    def ready(self) -> bool:
+        return self._event is None or bool(self._event.query())
+
+    def _get(self, i: int) -> float:
+        if self._event is not None:
+            self._event.synchronize()
+            self._event = None
+        return float(self._host[i])
+
+    local_loss = property(lambda self: self._get(0))
+    ema_loss = property(lambda self: self._get(1))
+    local_ratio = property(lambda self: self._get(2))
+    local_pressure = property(lambda self: self._get(3))
+    global_pressure = property(lambda self: self._get(4))
+    fire_count = property(lambda self: int(round(self._get(5))))
+    local_fire = property(lambda self: self._get(6) > 0.5)
+    triggered = property(lambda self: self._get(7) > 0.5)
+
+
+class LossTriggeredReplayEMA:
+    """Schedules NEXT-step replay from the just-finished loss: pressure is how far
+    ``loss / ema`` exceeds ``threshold``; ranks average their pressure with one
+    two-element all-reduce and all agree on ``triggered``
+    (runner_fast_path.py:6135-6210).  Returns ``None`` during warm-up."""
+
+    def __init__(self, *, decay: float = 0.99, warmup_steps: int = 32, eps: float = 1e-8) -> None:
+        if not 0.0 <= float(decay) < 1.0:
+            raise ValueError(f"decay must be in [0, 1), got {decay}")
+        if int(warmup_steps) < 0:
+            raise ValueError(f"warmup_steps must be >= 0, got {warmup_steps}")
+        self.decay, self.warmup_steps, self.eps = float(decay), int(warmup_steps), float(eps)
+        self.value: Optional[torch.Tensor] = None
+        self.observations = 0
+
+    def update(self, loss: torch.Tensor, *, threshold: float = 1.10, pressure_threshold: float = 0.05,
+               ddp_active: bool = False, world_size: int = 1, group=None) -> Optional[LossTriggeredReplayDecision]:
+        cur = loss.detach().float().reshape(())
+        if self.value is None:
+            self.value, self.observations = cur.clone(), 1
+            return None
+        before = self.value
+        self.value = self.decay * before + (1.0 - self.decay) * cur
+        self.observations += 1
+        if self.observations <= self.warmup_steps:
+            return None
+        ratio = cur / before.clamp_min(self.eps)
+        pressure = (ratio - float(threshold)).clamp_min(0.0)
+        fire = (pressure > 0).float()
+        both = torch.stack((pressure, fire))
+        if ddp_active and int(world_size) > 1:
+            import torch.distributed as dist
+            dist.all_reduce(both, op=dist.ReduceOp.SUM, group=group)
+            both = torch.stack((both[0] / float(world_size), both[1]))
+        triggered = (both[0] > float(pressure_threshold)).float()
+        return LossTriggeredReplayDecision(torch.stack((cur, before, ratio, pressure, both[0], both[1], fire,
+                                                        triggered)))

@@ -27,8 +27,9 @@ from pathlib import Path
 from typing import Any, Callable, Optional
 
 import torch
+import torch.distributed as dist
 
-__all__ = ["batch_from_start_tensor", "steady_state_step_seconds", "summarize_cuda_graph_gate", "BatchPrefetcher",
+__all__ = ["build_token_buckets", "compute_per_bucket_val_ce", "batch_from_start_tensor", "steady_state_step_seconds", "summarize_cuda_graph_gate", "BatchPrefetcher",
            "Exp23BatchPrefetcher", "count_lm_starts", "count_sharded_lm_starts", "sample_sharded_lm_starts",
            "sequential_epoch_steps", "sequential_sharded_lm_starts", "shuffled_epoch_sharded_lm_starts",
            "SequentialShardedStartSampler", "ShuffledEpochShardedStartSampler", "choose_lm_starts_lazy",
@@ -432,3 +433,78 @@ def read_speed_config(path: Path) -> dict[str, Any]:
     else:
         data = json.loads(text)
     return dict(data["config"]) if "config" in data else dict(data)
+
+
+# ---------------------------------------------------------------------------
+# validation CE by token-frequency bucket
+# ---------------------------------------------------------------------------
+def build_token_buckets(token_frequencies: torch.Tensor, num_buckets: int) -> torch.Tensor:
+    """``[vocab]`` int64 bucket id per token from ``log1p(frequency)`` cut into
+    ``num_buckets`` equal spans; bucket 0 holds the rarest tokens
+    (runner_fast_path.py:427-458)."""
+    if token_frequencies.ndim != 1:
+        raise ValueError("token_frequencies must be 1D")
+    if num_buckets < 1:
+        raise ValueError(f"num_buckets must be >= 1, got {num_buckets}")
+    lf = torch.log1p(token_frequencies.to(torch.float32).clamp_min(0.0))
+    lo = float(lf.min())
+    span = max(float(lf.max()) - lo, 1e-6)
+    edges = torch.linspace(lo, lo + span + 1e-6, num_buckets + 1, device=lf.device, dtype=torch.float32)
+    return torch.bucketize(lf, edges[1:-1]).clamp_(0, num_buckets - 1).to(torch.int64)
+
+
+def compute_per_bucket_val_ce(*, model: Any, device: torch.device, tokens: torch.Tensor, num_tokens: int,
+                              seq_len: int, stride: int, batch_size: int, vocab_size: int,
+                              token_frequencies: Optional[torch.Tensor], num_buckets: int, rank: int = 0,
+                              world_size: int = 1, precision: str = "bf16",
+                              max_batches: Optional[int] = None) -> dict[str, Any]:
+    """Deterministic no-grad pass over this rank's sequential validation windows;
+    per-token CE is summed into the frequency buckets of the TARGET tokens
+    (runner_fast_path.py:461-581).  Per-token CE comes from the chunked scorer
+    (the fused head on a GPU), so ``[B, T, V]`` logits never exist; per-window
+    sums stay on the device and come back in one transfer at the end."""
+    from .cache_utility import chunked_nll_from_hidden
+    from .precision import autocast_context
+    if token_frequencies is None:
+        raise ValueError("rare_bucket_ce_enabled=True requires rare_bucket_ce_token_frequencies")
+    nb = int(num_buckets)
+    bucket_of = build_token_buckets(token_frequencies, nb).to(device)
+    total = count_lm_starts(num_tokens, seq_len, stride)
+    mine = count_sharded_lm_starts(total_starts=total, rank=rank, world_size=world_size)
+    empty = {"per_bucket_val_ce": [0.0] * nb, "rare_bucket_val_ce": 0.0, "val_bucket_num_buckets": nb,
+             "val_bucket_token_counts": [0] * nb, "per_window_bucket_ce_sum": [], "per_window_bucket_count": []}
+    if mine <= 0:
+        return empty
+    n_steps = (mine + batch_size - 1) // batch_size
+    if max_batches is not None:
+        n_steps = min(n_steps, int(max_batches))
+    sums, counts = [], []
+    was_training = model.training
+    model.eval()
+    try:
+        with torch.no_grad():
+            for step in range(n_steps):
+                starts = sequential_sharded_lm_starts(num_tokens=num_tokens, seq_len=seq_len, stride=stride,
+                                                      batch_size=batch_size, rank=rank, world_size=world_size,
+                                                      step=step)
+                inputs, targets = batch_from_start_tensor(tokens=tokens, starts=starts, seq_len=seq_len,
+                                                          device=device, vocab_size=vocab_size)
+                with autocast_context(precision, device_type=inputs.device.type):
+                    hidden = model.encode(inputs)
+                ce = chunked_nll_from_hidden(model, hidden, targets).reshape(-1).to(torch.float64)
+                idx = bucket_of[targets.reshape(-1).long()]
+                sums.append(torch.zeros(nb, dtype=torch.float64, device=device).scatter_add_(0, idx, ce))
+                counts.append(torch.zeros(nb, dtype=torch.int64, device=device).scatter_add_(
+                    0, idx, torch.ones_like(idx)))
+    finally:
+        model.train(was_training)
+    win_sum, win_cnt = torch.stack(sums), torch.stack(counts)
+    b_sum, b_cnt = win_sum.sum(0), win_cnt.sum(0)
+    if world_size > 1 and dist.is_available() and dist.is_initialized():
+        dist.all_reduce(b_sum, op=dist.ReduceOp.SUM)
+        dist.all_reduce(b_cnt, op=dist.ReduceOp.SUM)
+    per = (b_sum / b_cnt.to(torch.float64).clamp_min(1.0)).cpu().tolist()
+    k = max(1, nb // 4)
+    return {"per_bucket_val_ce": [float(x) for x in per], "rare_bucket_val_ce": float(sum(per[:k]) / k),
+            "val_bucket_num_buckets": nb, "val_bucket_token_counts": [int(x) for x in b_cnt.cpu().tolist()],
+            "per_window_bucket_ce_sum": win_sum.cpu().tolist(), "per_window_bucket_count": win_cnt.cpu().tolist()}

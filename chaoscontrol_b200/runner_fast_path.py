@@ -51,14 +51,19 @@ from .optim.schedule import eval_with_ema, wrap_optimizer_step
 from .parallel.distributed import (allreduce_grads, broadcast_params, clip_arena_grad_norm, clip_grad_norm_fused,
                                    should_stop_now)
 from .train_ssm import _FUSED_LM_HEAD_BACKENDS, _reject_unsupported, train_ssm_step
-from .training_hooks import FastSlowConsolidator, spectral_summary, zero_embedding_grad_until
+from .training_hooks import (CriticalityDistillHook, FastSlowConsolidator, spectral_summary,
+                             zero_embedding_grad_until)
 from .utils.arena import get_arena
 
 __all__ = ["run_condition", "train_fast_for_budget", "build_model", "main", "UNSUPPORTED_OPTIONS"]
 
 # options that switch on research machinery this runner does not carry
-UNSUPPORTED_OPTIONS = ("episodic_enabled", "dreamworld_enabled", "rare_bucket_ce_enabled", "event_sleep_enabled",
-                       "criticality_distill_enabled")
+UNSUPPORTED_OPTIONS = ("episodic_enabled",)
+_DREAM_KEYS = ("dreamworld_enabled", "dreamworld_cache_interval", "dreamworld_interval", "dreamworld_weight",
+               "dreamworld_prefix_tokens", "dreamworld_replay_tokens", "dreamworld_replay_batch_size",
+               "dreamworld_buffer_size", "dreamworld_min_size", "dreamworld_max_age_steps", "event_sleep_enabled",
+               "event_sleep_loss_ratio", "event_sleep_pressure_threshold", "event_sleep_ema_decay",
+               "event_sleep_warmup_steps", "event_sleep_min_interval", "event_sleep_weight")
 
 
 # ---------------------------------------------------------------------------
@@ -415,7 +420,16 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
                           distributed_muon: bool = False, cuda_graph_min_total_speedup: float = 0.05,
                           cuda_graph_max_capture_seconds: float = 30.0, cuda_graph_warmup_steps: int = 3,
                           crct_enabled: bool = False, crct: Optional["CrctRuntime"] = None,
-                          replay_eviction_enabled: bool = False,
+                          replay_eviction_enabled: bool = False, dreamworld_enabled: bool = False,
+                          dreamworld_cache_interval: int = 0, dreamworld_interval: int = 0,
+                          dreamworld_weight: float = 0.0, dreamworld_prefix_tokens: int = 128,
+                          dreamworld_replay_tokens: int = 64, dreamworld_replay_batch_size: int = 0,
+                          dreamworld_buffer_size: int = 16, dreamworld_min_size: int = 2,
+                          dreamworld_max_age_steps: int = 256, event_sleep_enabled: bool = False,
+                          event_sleep_loss_ratio: float = 1.10, event_sleep_pressure_threshold: float = 0.05,
+                          event_sleep_ema_decay: float = 0.99, event_sleep_warmup_steps: int = 32,
+                          event_sleep_min_interval: int = 8, event_sleep_weight: float = 0.0,
+                          criticality: Optional[CriticalityDistillHook] = None,
                           time_fn: Callable[[], float] = time.perf_counter, **unused: Any) -> dict[str, Any]:
     """Budgeted hot loop.  Returns the train-result dict (``steps``, ``elapsed_s``,
     ``initial_loss``, ``final_loss``, ``loss_history``, throughput keys,
@@ -427,6 +441,13 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
         raise NotImplementedError(f"options {bad} are not supported by this runner")
     if replay_eviction_enabled and not crct_enabled:
         raise ValueError("replay_eviction_enabled needs crct_enabled: slot maintenance runs beside the teacher")
+    if event_sleep_enabled and not dreamworld_enabled:
+        raise ValueError("event_sleep_enabled requires dreamworld_enabled=True")
+    if dreamworld_enabled and crct_enabled:
+        raise ValueError("dreamworld_enabled and crct_enabled cannot be combined in this runner")
+    if criticality is not None and world_size > 1:
+        raise ValueError("criticality_distill_enabled=True is single-rank only: seat masks, the score "
+                         "accumulators and the log_a loss are rank-local")
     ddp = world_size > 1
     if ddp:
         broadcast_params(model)
@@ -469,6 +490,10 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
                                                 train_sampling_mode=mode, model=model)
         if crct_enabled:
             why_not.append("crct_not_supported")
+        if dreamworld_enabled:
+            why_not.append("dreamworld_not_supported")
+        if criticality is not None:
+            why_not.append("criticality_distill_not_supported")
         if why_not:
             graph_summary = _rejected_cuda_graph_summary(mode=graph_mode, reasons=why_not, **gate)
         else:
@@ -505,6 +530,18 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
     epoch_steps = (FP.sequential_epoch_steps(num_tokens=train_num_tokens, seq_len=seq_len, stride=stride,
                                              batch_size=batch_size, world_size=world_size)
                    if mode != "random" else None)
+    dream_buffer = dream_gate = None
+    dream = {"replays": 0, "event_triggers": 0, "event_replays": 0, "event_decisions": 0, "pressure_sum": 0.0,
+             "last_decision": None}
+    if dreamworld_enabled:
+        from .dreamworld import (DreamReplayBuffer, LossTriggeredReplayEMA, capture_dream_entry,
+                                 dreamworld_replay_backward)
+        dream_buffer = DreamReplayBuffer(max_entries=int(dreamworld_buffer_size),
+                                         max_age_steps=int(dreamworld_max_age_steps))
+        if event_sleep_enabled:
+            dream_gate = LossTriggeredReplayEMA(decay=float(event_sleep_ema_decay),
+                                                warmup_steps=int(event_sleep_warmup_steps))
+    event_pending, event_last_replay, queued = False, -10 ** 9, None
     sync_teacher = crct is not None and crct.mode == "sync" and crct.world_size > 1
     if sync_teacher:
         stop_check_interval = 1                    # the memory rank mirrors every step: it needs every flag
@@ -527,7 +564,50 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
             ts = time_fn()
             inputs, targets = prefetch.next()
             optimizer.zero_grad(set_to_none=True)
-            if crct_enabled:
+            # dream replay: last step's gate decision first, then what this step replays and caches
+            dream_entry, dream_w = None, float(dreamworld_weight)
+            if dream_buffer is not None:
+                if queued is not None:
+                    dec, dec_step = queued
+                    queued = None
+                    dream["event_decisions"] += 1
+                    dream["pressure_sum"] += dec.global_pressure
+                    dream["last_decision"] = {"step": dec_step, "local_loss": dec.local_loss,
+                                              "ema_loss": dec.ema_loss, "global_pressure": dec.global_pressure,
+                                              "fire_count": dec.fire_count, "triggered": dec.triggered}
+                    if (dec.triggered and dec_step - event_last_replay >= int(event_sleep_min_interval)
+                            and len(dream_buffer) >= int(dreamworld_min_size)):
+                        dream["event_triggers"] += 1
+                        event_pending = True
+                have = len(dream_buffer) >= int(dreamworld_min_size)
+                scheduled = (have and dreamworld_interval > 0 and dreamworld_weight > 0.0
+                             and steps % int(dreamworld_interval) == 0)
+                if scheduled or (event_pending and have):
+                    dream_entry = dream_buffer.sample(generator=gen, current_step=steps)
+                    if event_pending and have:
+                        dream["event_replays"] += 1
+                        event_pending, event_last_replay = False, steps
+                        if float(event_sleep_weight) > 0.0:
+                            dream_w = float(event_sleep_weight)
+                if dreamworld_cache_interval > 0 and steps % int(dreamworld_cache_interval) == 0:
+                    e = capture_dream_entry(model, inputs, step=steps, prefix_tokens=int(dreamworld_prefix_tokens),
+                                            replay_tokens=int(dreamworld_replay_tokens))
+                    dream_buffer.add(step=e.step, states=e.states, replay_tokens=e.replay_tokens)
+            if dream_entry is not None and dream_w > 0.0:
+                # replay gradients ADD to this step's: reduce once, after both backward passes
+                loss = train_ssm_step(model, inputs, targets, chunk_size, ddp_active=False, world_size=world_size,
+                                      precision=precision, lm_head_backward_mode=lm_head_backward_mode,
+                                      lm_head_tile_size=lm_head_tile_size)
+                dreamworld_replay_backward(model, dream_entry, dream_w, lm_head_backward_mode=lm_head_backward_mode,
+                                           lm_head_tile_size=lm_head_tile_size,
+                                           replay_batch_size=int(dreamworld_replay_batch_size), generator=gen)
+                dream["replays"] += 1
+                arena_now = get_arena(model)
+                if arena_now is not None and arena_now.grads_fresh:
+                    arena_now.pull_grads()
+                if ddp and dist_opt is None:
+                    allreduce_grads(model, world_size)
+            elif crct_enabled:
                 payload = None
                 if crct is not None:
                     payload, inputs, targets = crct.begin_step(inputs, targets, steps)
@@ -542,6 +622,12 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
                                       compile_full_path=compile_full_path,
                                       lm_head_backward_mode=lm_head_backward_mode,
                                       lm_head_tile_size=lm_head_tile_size)
+            if criticality is not None:
+                if criticality.after_backward(model, inputs, targets, step=steps,
+                                              lm_head_tile_size=lm_head_tile_size) is not None:
+                    arena_now = get_arena(model)
+                    if arena_now is not None and arena_now.grads_fresh:
+                        arena_now.pull_grads()       # the log_a loss added to p.grad: fold it into the flat buffer
             zero_embedding_grad_until(model, steps, embed_freeze_steps)
             if dist_opt is not None:
                 dist_opt.step()                     # reduce (sharded) + clip + owned update + gather
@@ -557,6 +643,12 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
             if fast_slow is not None and fast_slow.enabled:
                 fast_slow.after_optimizer_step(model, step=steps)
             losses.append(loss.detach())
+            if dream_gate is not None:
+                d = dream_gate.update(loss, threshold=float(event_sleep_loss_ratio),
+                                      pressure_threshold=float(event_sleep_pressure_threshold), ddp_active=ddp,
+                                      world_size=world_size)
+                if d is not None:
+                    queued = (d, steps - 1)
             step_times.append(time_fn() - ts)
     finally:
         prefetch.close()
@@ -584,6 +676,24 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
         result["cuda_graph"] = graph_summary
     if crct is not None:
         result["crct"] = crct.diagnostics()
+    if criticality is not None:
+        result["criticality_distillation"] = criticality.diagnostics()
+    if dream_buffer is not None:
+        n = max(dream["event_decisions"], 1)
+        result["dreamworld"] = {
+            "enabled": True, "weight": float(dreamworld_weight), "cache_interval": int(dreamworld_cache_interval),
+            "dream_interval": int(dreamworld_interval), "prefix_tokens": int(dreamworld_prefix_tokens),
+            "replay_tokens": int(dreamworld_replay_tokens), "replay_batch_size": int(dreamworld_replay_batch_size),
+            "replays": dream["replays"], "buffer": dream_buffer.diagnostics(steps),
+            "event_sleep": {"enabled": dream_gate is not None, "loss_ratio": float(event_sleep_loss_ratio),
+                            "pressure_threshold": float(event_sleep_pressure_threshold),
+                            "ema_decay": float(event_sleep_ema_decay),
+                            "warmup_steps": int(event_sleep_warmup_steps),
+                            "min_interval": int(event_sleep_min_interval), "weight": float(event_sleep_weight),
+                            "trigger_count": dream["event_triggers"], "replay_count": dream["event_replays"],
+                            "decision_count": dream["event_decisions"],
+                            "mean_global_pressure": dream["pressure_sum"] / n,
+                            "last_decision": dream["last_decision"]}}
     return result
 
 
@@ -592,7 +702,7 @@ _LOOP_KEYS = ("chunk_size", "grad_clip_norm", "fused_grad_clip", "precision", "s
               "lm_head_tile_size", "cuda_graph_mode", "cuda_graph_min_total_speedup",
               "cuda_graph_max_capture_seconds", "cuda_graph_warmup_steps", "train_sampling_mode",
               "embed_freeze_steps", "distributed_muon", "crct_enabled",
-              "replay_eviction_enabled") + UNSUPPORTED_OPTIONS
+              "replay_eviction_enabled") + _DREAM_KEYS + UNSUPPORTED_OPTIONS
 
 
 def _loop_kwargs(config: dict[str, Any]) -> dict[str, Any]:
@@ -715,7 +825,20 @@ def run_condition(config: dict[str, Any], *, data_path: str, sp_model_path: Opti
                                batch_size=batch, seq_len=seq_len, total_steps=max_steps)
         train_result = train_fast_for_budget(
             model, optimizer=optimizer, budget_seconds=budget_seconds, fast_slow=fast_slow, max_steps=max_steps,
-            crct=crct, **common, **_loop_kwargs(config))
+            crct=crct, criticality=CriticalityDistillHook.from_config(model, config), **common,
+            **_loop_kwargs(config))
+        if bool(config.get("rare_bucket_ce_enabled", False)):
+            freq = torch.bincount(train_tokens.to(torch.int64).clamp_(0, vocab - 1), minlength=vocab)
+            is_mem = crct is not None and crct.is_memory_rank
+            ev_rank, ev_world = (rank, world_size) if crct is None or not ddp else (
+                (0, 1) if is_mem else (crct.topology["train_ranks"].index(rank), crct.grad_world_size))
+            if not is_mem and ev_world == world_size:
+                train_result.update(FP.compute_per_bucket_val_ce(
+                    model=model, device=device, tokens=val_tokens, num_tokens=int(val_tokens.numel()),
+                    seq_len=seq_len, stride=stride, batch_size=batch, vocab_size=vocab, token_frequencies=freq,
+                    num_buckets=int(config.get("rare_bucket_ce_num_buckets", 4)), rank=ev_rank,
+                    world_size=ev_world, precision=str(config.get("precision", "bf16")),
+                    max_batches=config.get("rare_bucket_ce_max_batches")))
     if ddp:
         _control_barrier(control, "post_train")
 

@@ -295,3 +295,99 @@ def zero_embedding_grad_until(model: torch.nn.Module, step: int, freeze_steps: i
     w = getattr(getattr(model, "embed", None), "weight", None)
     if w is not None and w.grad is not None:
         w.grad.zero_()
+
+
+# ---------------------------------------------------------------------------
+# criticality distillation in the training loop
+# ---------------------------------------------------------------------------
+class CriticalityDistillHook:
+    """Runs criticality distillation beside a training step
+    (runner_fast_path.py:11127-11190, 12545-12812): captures every layer's
+    recurrence states and the per-token CE / entropy in ONE extra no-grad pass,
+    turns ``relu(CE - entropy)`` into event pressure, folds the device-side
+    aggregates into the seat bookkeeping (host side, ``[L, D]`` sized), refreshes
+    the seats on their interval, and back-propagates the ``log_a`` loss as its own
+    pass (its gradients touch ``log_a`` only).  Single rank only: seats and the
+    loss are rank-local."""
+
+    def __init__(self, model: torch.nn.Module, *, num_layers: int, dim: int, budget_frac: float = 0.15,
+                 critical_value: float = 0.95, trace_ttl_steps: int = 1024, trace_half_life_steps: float = 256.0,
+                 seat_refresh_interval: int = 64, min_weighted_events_per_layer: float = 256.0,
+                 horizon_H: int = 16, event_frac: float = 0.05, weight: float = 1e-3,
+                 uniform_pressure: bool = False, score_permute_before_topk: bool = False,
+                 fixed_random_seats: bool = False) -> None:
+        from .optim.criticality import CriticalityDistillation
+        self.cores = [m for m in model.modules() if callable(getattr(m, "capture_states", None))]
+        if len(self.cores) != int(num_layers):
+            raise ValueError(f"criticality_distill_num_layers mismatch: configured {int(num_layers)} but the model "
+                             f"exposes {len(self.cores)} modules with capture_states()")
+        self.cd = CriticalityDistillation(
+            num_layers=int(num_layers), dim=int(dim), trace_ttl_steps=int(trace_ttl_steps),
+            trace_half_life_steps=float(trace_half_life_steps), seat_refresh_interval=int(seat_refresh_interval),
+            criticality_budget_frac=float(budget_frac), critical_value=float(critical_value),
+            min_weighted_events_per_layer=float(min_weighted_events_per_layer),
+            criticality_distill_weight=float(weight), score_permute_before_topk=bool(score_permute_before_topk),
+            fixed_random_seats=bool(fixed_random_seats))
+        self.horizon_H, self.event_frac, self.uniform = int(horizon_H), float(event_frac), bool(uniform_pressure)
+        self.snapshots: list[dict] = []
+        self.loss_trajectory: list[dict] = []
+        self.ingests = self.seat_refreshes = 0
+
+    @classmethod
+    def from_config(cls, model: torch.nn.Module, config: dict) -> "Optional[CriticalityDistillHook]":
+        if not bool(config.get("criticality_distill_enabled", False)):
+            return None
+        pre = "criticality_distill_"
+        for need in ("num_layers", "dim"):
+            if config.get(pre + need) is None:
+                raise ValueError(f"criticality_distill_enabled=True requires {pre}{need}")
+        kw = {k[len(pre):]: v for k, v in config.items() if k.startswith(pre) and k != pre + "enabled"}
+        return cls(model, **kw)
+
+    def _log_a(self) -> list[torch.Tensor]:
+        return [c.log_a for c in self.cores]
+
+    def after_backward(self, model: torch.nn.Module, inputs: torch.Tensor, targets: torch.Tensor, *, step: int,
+                       lm_head_tile_size: int = 8192) -> Optional[torch.Tensor]:
+        """Call between the step's backward and the gradient clip.  Returns the
+        distillation loss (device scalar) when seats exist, else ``None``."""
+        import contextlib
+
+        from .kernels.lm_head_loss import fused_lm_head_forward_with_ce_entropy
+        with contextlib.ExitStack() as stack, torch.no_grad():
+            getters = [stack.enter_context(c.capture_states()) for c in self.cores]
+            normed = model.final_norm(model.encode(inputs))
+            states = [g() for g in getters]
+            if any(s is None for s in states):
+                raise RuntimeError("criticality distillation: a recurrence core did not record its states; "
+                                   "state capture needs a_mode='diag'")
+            B, T = inputs.shape
+            if self.uniform:
+                pressure = torch.ones(B, T, device=normed.device)
+            else:
+                _, _, ce, ent = fused_lm_head_forward_with_ce_entropy(normed, model.lm_head.weight, targets,
+                                                                      tile_size=int(lm_head_tile_size))
+                pressure = torch.relu(ce.reshape(B, T).float() - ent.reshape(B, T).float())
+            prepared = self.cd.ingest_gpu(pressure=pressure, states_per_layer=states, horizon_H=self.horizon_H,
+                                          event_frac=self.event_frac)
+        host = {k: v.to("cpu") for k, v in prepared.items()}          # [L, D] aggregates and two counters
+        self.cd.ingest_cpu_from_prepared(step=int(step), prepared=host)
+        self.ingests += 1
+        every = int(self.cd.seat_refresh_interval)
+        if step > 0 and every > 0 and step % every == 0:
+            self.cd.allocate_seats_from_accumulators(current_step=int(step))
+            self.seat_refreshes += 1
+            self.snapshots.append(self.cd.diagnostics_snapshot(log_a_per_layer=self._log_a(),
+                                                               current_step=int(step)))
+        if not bool(self.cd.seat_mask.any()):
+            return None
+        loss = self.cd.criticality_loss(self._log_a())
+        if loss.requires_grad:
+            loss.backward()
+        self.loss_trajectory.append({"step": int(step), "cd_loss": float(loss.detach())})
+        return loss.detach()
+
+    def diagnostics(self) -> dict:
+        return {"enabled": True, "ingests": self.ingests, "seat_refreshes": self.seat_refreshes,
+                "seats": int(self.cd.seat_mask.sum()), "loss_trajectory": self.loss_trajectory[-64:],
+                "snapshots": self.snapshots[-8:]}

@@ -257,3 +257,115 @@ def test_cuda_graph_loop_matches_eager_trajectory():
     a, b = torch.tensor(eager["loss_history"]), torch.tensor(graph["loss_history"])
     assert a.shape == b.shape and torch.allclose(a, b, atol=2e-2, rtol=0), (a, b)
     assert b[-1] < b[0]
+
+
+def test_dreamworld_replay_and_event_sleep_in_the_loop():
+    torch.manual_seed(0)
+    tokens = torch.randint(0, 64, (4000,), dtype=torch.int16)
+    model = CareStudentLM(vocab_size=64, dim=16, num_layers=2)
+    optim = _build_optimizer(dict(optimizer="adamw", base_lr=1e-3), model)
+    kw = dict(train_tokens=tokens, train_num_tokens=4000, stride=8, seq_len=16, batch_size=4,
+              device=torch.device("cpu"), optimizer=optim, budget_seconds=600.0, precision="fp32",
+              stop_check_interval=1, lm_head_backward_mode="fused", prefetch_batches=False, max_steps=12)
+    res = train_fast_for_budget(model, dreamworld_enabled=True, dreamworld_cache_interval=2, dreamworld_interval=3,
+                                dreamworld_weight=0.5, dreamworld_prefix_tokens=4, dreamworld_replay_tokens=4,
+                                dreamworld_replay_batch_size=2, dreamworld_min_size=2, event_sleep_enabled=True,
+                                event_sleep_loss_ratio=0.0, event_sleep_pressure_threshold=0.0,
+                                event_sleep_warmup_steps=2, event_sleep_min_interval=4, event_sleep_weight=0.25, **kw)
+    d = res["dreamworld"]
+    assert res["steps"] == 12 and d["buffer"]["add_count"] == 6
+    ev = d["event_sleep"]
+    # the ratio threshold of zero fires on every decision; the minimum interval spaces the replays
+    assert ev["decision_count"] >= 8 and 2 <= ev["replay_count"] <= 3 and ev["trigger_count"] == ev["replay_count"]
+    assert d["replays"] >= ev["replay_count"] and ev["last_decision"]["triggered"] is True
+    assert all(v == v for v in res["loss_history"])
+    with pytest.raises(ValueError):
+        train_fast_for_budget(model, event_sleep_enabled=True, **kw)
+
+
+def test_loss_triggered_replay_gate():
+    from chaoscontrol_b200.dreamworld import LossTriggeredReplayEMA
+    g = LossTriggeredReplayEMA(decay=0.5, warmup_steps=2)
+    assert g.update(torch.tensor(2.0)) is None and g.update(torch.tensor(2.0)) is None
+    calm = g.update(torch.tensor(2.0), threshold=1.1, pressure_threshold=0.05)
+    assert calm.ready() and not calm.triggered and calm.fire_count == 0 and abs(calm.local_ratio - 1.0) < 1e-6
+    spike = g.update(torch.tensor(3.0), threshold=1.1, pressure_threshold=0.05)
+    assert spike.triggered and spike.local_fire and abs(spike.local_pressure - 0.4) < 1e-6
+    assert abs(spike.ema_loss - 2.0) < 1e-6 and abs(float(g.value) - 2.5) < 1e-6
+    with pytest.raises(ValueError):
+        LossTriggeredReplayEMA(decay=1.0)
+
+
+def test_criticality_distillation_hook_in_the_loop():
+    torch.manual_seed(0)
+    tokens = torch.randint(0, 64, (4000,), dtype=torch.int16)
+    model = CareStudentLM(vocab_size=64, dim=16, num_layers=2)
+    optim = _build_optimizer(dict(optimizer="adamw", base_lr=1e-3), model)
+    cfg = dict(criticality_distill_enabled=True, criticality_distill_num_layers=2, criticality_distill_dim=16,
+               criticality_distill_seat_refresh_interval=2, criticality_distill_min_weighted_events_per_layer=0.0,
+               criticality_distill_horizon_H=2, criticality_distill_event_frac=0.25, criticality_distill_weight=1.0,
+               criticality_distill_trace_ttl_steps=16)
+    hook = TH.CriticalityDistillHook.from_config(model, cfg)
+    assert TH.CriticalityDistillHook.from_config(model, {}) is None
+    with pytest.raises(ValueError):
+        TH.CriticalityDistillHook.from_config(model, dict(criticality_distill_enabled=True))
+    with pytest.raises(ValueError):
+        TH.CriticalityDistillHook.from_config(model, dict(cfg, criticality_distill_num_layers=3))
+    kw = dict(train_tokens=tokens, train_num_tokens=4000, stride=8, seq_len=16, batch_size=4,
+              device=torch.device("cpu"), optimizer=optim, budget_seconds=600.0, precision="fp32",
+              stop_check_interval=1, lm_head_backward_mode="fused", prefetch_batches=False, max_steps=8)
+    res = train_fast_for_budget(model, criticality=hook, **kw)
+    d = res["criticality_distillation"]
+    k = max(1, round(16 * 0.15))
+    assert d["ingests"] == 8 and d["seat_refreshes"] == 3 and d["seats"] == 2 * k
+    assert len(d["loss_trajectory"]) >= 5 and all(t["cd_loss"] > 0 for t in d["loss_trajectory"])
+    assert len(d["snapshots"]) == 3
+    # the loss only touches log_a of seated channels
+    model.zero_grad(set_to_none=True)
+    hook.cd.criticality_loss([c.log_a for c in hook.cores]).backward()
+    g = model.layers[0].core.log_a.grad
+    assert int((g != 0).sum()) == k and model.lm_head.weight.grad is None
+    with pytest.raises(ValueError):
+        train_fast_for_budget(model, criticality=hook, world_size=2, **kw)
+
+
+def test_token_buckets_and_per_bucket_val_ce(tmp_path):
+    from chaoscontrol_b200 import fast_path as FP
+    freq = torch.tensor([0, 1, 10, 100, 1000, 10000])
+    b = FP.build_token_buckets(freq, 3)
+    assert b.tolist() == sorted(b.tolist()) and b[0] == 0 and b[-1] == 2
+    with pytest.raises(ValueError):
+        FP.build_token_buckets(freq.reshape(2, 3), 3)
+    torch.manual_seed(0)
+    model = CareStudentLM(vocab_size=64, dim=16, num_layers=1)
+    val = torch.randint(0, 64, (600,), dtype=torch.int16)
+    freq = torch.bincount(val.long(), minlength=64)
+    out = FP.compute_per_bucket_val_ce(model=model, device=torch.device("cpu"), tokens=val, num_tokens=600, seq_len=16,
+                                       stride=8, batch_size=8, vocab_size=64, token_frequencies=freq, num_buckets=4,
+                                       precision="fp32")
+    n_steps = -(-FP.count_lm_starts(600, 16, 8) // 8)
+    assert sum(out["val_bucket_token_counts"]) == n_steps * 8 * 16
+    assert len(out["per_window_bucket_ce_sum"]) == n_steps
+    # weighted mean of the bucket means is the plain mean CE over the same windows
+    xs, ys = [], []
+    for step in range(n_steps):
+        st = FP.sequential_sharded_lm_starts(num_tokens=600, seq_len=16, stride=8, batch_size=8, rank=0,
+                                             world_size=1, step=step)
+        a, b2 = FP.batch_from_start_tensor(tokens=val, starts=st, seq_len=16, device=torch.device("cpu"),
+                                           vocab_size=64)
+        xs.append(a)
+        ys.append(b2)
+    x, y = torch.cat(xs), torch.cat(ys)
+    with torch.no_grad():
+        logits = model.lm_head(model.final_norm(model.encode(x.to(torch.int32))))
+        ce = torch.nn.functional.cross_entropy(logits.reshape(-1, 64), y.reshape(-1).long())
+    cnt = torch.tensor(out["val_bucket_token_counts"], dtype=torch.float64)
+    mean = (torch.tensor(out["per_bucket_val_ce"], dtype=torch.float64) * cnt).sum() / cnt.sum()
+    assert abs(float(mean) - float(ce)) < 1e-4
+    assert abs(out["rare_bucket_val_ce"] - out["per_bucket_val_ce"][0]) < 1e-12
+    _shards(tmp_path)
+    res = run_condition(_config(rare_bucket_ce_enabled=True, rare_bucket_ce_max_batches=3, warmup_steps=0,
+                                fast_slow_enabled=False, eval_batches=0),
+                        data_path=str(tmp_path), sp_model_path=None, budget_seconds=60.0, output_json=None,
+                        output_ckpt=None, world_size_override=None)
+    assert len(res["train"]["per_bucket_val_ce"]) == 4 and res["train"]["val_bucket_num_buckets"] == 4

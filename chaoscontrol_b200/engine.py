@@ -40,6 +40,7 @@ class TrainEngine:
                 "proj": pre + "ff.proj.weight", "wn1": pre + "input_norm.weight",
                 "wn2": pre + "ff_norm.weight", "log_a": pre + "core.log_a"})
         self.last_loss_rows: Optional[torch.Tensor] = None
+        self.last_hidden: Optional[torch.Tensor] = None
 
     # ------------------------------------------------------------------
     @staticmethod
@@ -97,6 +98,7 @@ class TrainEngine:
         T.splitk_reduce(part, colscale=wnF, W=Wlm, out=a.grad_view("lm_head.weight"),
                         dcol_out=a.grad_view("final_norm.weight"))
         self.last_loss_rows = loss_rows
+        self.last_hidden = x                    # [B*T, D] trunk output (pre final norm), for event producers
         if row_weight is None:
             loss = loss_rows.mean()
         else:

@@ -42,6 +42,7 @@ import torch.distributed as dist
 from . import fast_path as FP
 from .config import ssm_constructor_kwargs
 from .crct import CrctRuntime, crct_train_step
+from .episodic.runtime import EpisodicRuntime
 from .data import load_fineweb_tokens, load_fineweb_val_tokens, resolve_param_dtype
 from .models.core import verify_diag_recurrence
 from .models.model import CareStudentLM
@@ -50,7 +51,7 @@ from .optim.param_groups import build_optimizer_params
 from .optim.schedule import eval_with_ema, wrap_optimizer_step
 from .parallel.distributed import (allreduce_grads, broadcast_params, clip_arena_grad_norm, clip_grad_norm_fused,
                                    should_stop_now)
-from .train_ssm import _FUSED_LM_HEAD_BACKENDS, _reject_unsupported, train_ssm_step
+from .train_ssm import _FUSED_LM_HEAD_BACKENDS, _reject_unsupported, train_ssm_step, train_ssm_step_with_ce
 from .training_hooks import (CriticalityDistillHook, FastSlowConsolidator, spectral_summary,
                              zero_embedding_grad_until)
 from .utils.arena import get_arena
@@ -58,7 +59,7 @@ from .utils.arena import get_arena
 __all__ = ["run_condition", "train_fast_for_budget", "build_model", "main", "UNSUPPORTED_OPTIONS"]
 
 # options that switch on research machinery this runner does not carry
-UNSUPPORTED_OPTIONS = ("episodic_enabled",)
+UNSUPPORTED_OPTIONS: tuple[str, ...] = ()      # every research switch of the reference runner is carried
 _DREAM_KEYS = ("dreamworld_enabled", "dreamworld_cache_interval", "dreamworld_interval", "dreamworld_weight",
                "dreamworld_prefix_tokens", "dreamworld_replay_tokens", "dreamworld_replay_batch_size",
                "dreamworld_buffer_size", "dreamworld_min_size", "dreamworld_max_age_steps", "event_sleep_enabled",
@@ -430,6 +431,7 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
                           event_sleep_ema_decay: float = 0.99, event_sleep_warmup_steps: int = 32,
                           event_sleep_min_interval: int = 8, event_sleep_weight: float = 0.0,
                           criticality: Optional[CriticalityDistillHook] = None,
+                          episodic: Optional["EpisodicRuntime"] = None,
                           time_fn: Callable[[], float] = time.perf_counter, **unused: Any) -> dict[str, Any]:
     """Budgeted hot loop.  Returns the train-result dict (``steps``, ``elapsed_s``,
     ``initial_loss``, ``final_loss``, ``loss_history``, throughput keys,
@@ -445,6 +447,8 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
         raise ValueError("event_sleep_enabled requires dreamworld_enabled=True")
     if dreamworld_enabled and crct_enabled:
         raise ValueError("dreamworld_enabled and crct_enabled cannot be combined in this runner")
+    if episodic is not None and (crct_enabled or dreamworld_enabled or criticality is not None):
+        raise ValueError("episodic_enabled cannot be combined with crct, dreamworld or criticality distillation")
     if criticality is not None and world_size > 1:
         raise ValueError("criticality_distill_enabled=True is single-rank only: seat masks, the score "
                          "accumulators and the log_a loss are rank-local")
@@ -465,6 +469,11 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
         rank, world_size = crct.topology["train_ranks"].index(rank), crct.grad_world_size
         ddp = world_size > 1
         distributed_muon = False
+    epi_idle = episodic is not None and episodic.is_episodic_rank     # this rank only replays
+    data_rank, data_world = rank, world_size
+    if episodic is not None and ddp:
+        data_rank, data_world = (0 if epi_idle else rank), episodic.n_train
+        distributed_muon = False
     model.train()
     mode = str(train_sampling_mode).strip().lower()
     sampler = {"random": None, "sequential_epoch": FP.SequentialShardedStartSampler(),
@@ -473,7 +482,7 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
         raise ValueError(f"train_sampling_mode must be random, sequential_epoch or shuffled_epoch; got {mode!r}")
     gen = torch.Generator().manual_seed(int(seed) + int(rank))
     prefetch = FP.BatchPrefetcher(tokens=train_tokens[:train_num_tokens], seq_len=seq_len, stride=stride,
-                                  batch_size=batch_size, rank=rank, world_size=world_size, device=device,
+                                  batch_size=batch_size, rank=data_rank, world_size=data_world, device=device,
                                   generator=gen, vocab_size=vocab_size, batch_sampler=sampler)
     if prefetch_batches:
         prefetch.prime()
@@ -494,6 +503,8 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
             why_not.append("dreamworld_not_supported")
         if criticality is not None:
             why_not.append("criticality_distill_not_supported")
+        if episodic is not None:
+            why_not.append("episodic_not_supported")
         if why_not:
             graph_summary = _rejected_cuda_graph_summary(mode=graph_mode, reasons=why_not, **gate)
         else:
@@ -593,7 +604,21 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
                     e = capture_dream_entry(model, inputs, step=steps, prefix_tokens=int(dreamworld_prefix_tokens),
                                             replay_tokens=int(dreamworld_replay_tokens))
                     dream_buffer.add(step=e.step, states=e.states, replay_tokens=e.replay_tokens)
-            if dream_entry is not None and dream_w > 0.0:
+            if episodic is not None:
+                if epi_idle:
+                    loss = torch.zeros((), device=device)
+                else:
+                    loss, ce_bt, hid = train_ssm_step_with_ce(model, inputs, targets, precision=precision,
+                                                              lm_head_backward_mode=lm_head_backward_mode,
+                                                              lm_head_tile_size=lm_head_tile_size)
+                    episodic.emit(inputs=inputs, targets=targets, per_token_ce=ce_bt, hidden=hid, step=steps)
+                replayed = episodic.consume(model, step=steps, lm_head_backward_mode=lm_head_backward_mode,
+                                            lm_head_tile_size=lm_head_tile_size)
+                arena_now = get_arena(model)
+                if replayed and not epi_idle and arena_now is not None and arena_now.grads_fresh:
+                    arena_now.pull_grads()          # one rank plays both parts: fold replay into the flat buffer
+                episodic.join_gradients(model)
+            elif dream_entry is not None and dream_w > 0.0:
                 # replay gradients ADD to this step's: reduce once, after both backward passes
                 loss = train_ssm_step(model, inputs, targets, chunk_size, ddp_active=False, world_size=world_size,
                                       precision=precision, lm_head_backward_mode=lm_head_backward_mode,
@@ -676,6 +701,10 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
         result["cuda_graph"] = graph_summary
     if crct is not None:
         result["crct"] = crct.diagnostics()
+    if episodic is not None:
+        result["episodic"] = episodic.diagnostics()
+        result.update(FP.summarize_train_timing(steps=steps, elapsed_s=elapsed, batch_size=batch_size,
+                                                seq_len=seq_len, world_size=world_size, episodic_enabled=ddp))
     if criticality is not None:
         result["criticality_distillation"] = criticality.diagnostics()
     if dream_buffer is not None:
@@ -702,7 +731,7 @@ _LOOP_KEYS = ("chunk_size", "grad_clip_norm", "fused_grad_clip", "precision", "s
               "lm_head_tile_size", "cuda_graph_mode", "cuda_graph_min_total_speedup",
               "cuda_graph_max_capture_seconds", "cuda_graph_warmup_steps", "train_sampling_mode",
               "embed_freeze_steps", "distributed_muon", "crct_enabled",
-              "replay_eviction_enabled") + _DREAM_KEYS + UNSUPPORTED_OPTIONS
+              "replay_eviction_enabled") + _DREAM_KEYS
 
 
 def _loop_kwargs(config: dict[str, Any]) -> dict[str, Any]:
@@ -800,6 +829,8 @@ def run_condition(config: dict[str, Any], *, data_path: str, sp_model_path: Opti
     train_result: dict[str, Any]
     optimizer = None
     fast_slow = None
+    episodic = None
+    episodic_cache_blob = None
     if eval_only:
         train_result = {"steps": 0, "elapsed_s": 0.0, "initial_loss": 0.0, "final_loss": 0.0,
                         "aggregate_tokens_per_sec": 0.0, "peak_vram_mb": 0.0, "eval_only": True}
@@ -823,10 +854,23 @@ def run_condition(config: dict[str, Any], *, data_path: str, sp_model_path: Opti
         if bool(config.get("crct_enabled", False)):
             crct = CrctRuntime(model=model, config=config, rank=rank, world_size=world_size, device=device,
                                batch_size=batch, seq_len=seq_len, total_steps=max_steps)
-        train_result = train_fast_for_budget(
-            model, optimizer=optimizer, budget_seconds=budget_seconds, fast_slow=fast_slow, max_steps=max_steps,
-            crct=crct, criticality=CriticalityDistillHook.from_config(model, config), **common,
-            **_loop_kwargs(config))
+        if bool(config.get("episodic_enabled", False)):
+            episodic = EpisodicRuntime(model=model, config=config, rank=rank, world_size=world_size, device=device)
+        try:
+            train_result = train_fast_for_budget(
+                model, optimizer=optimizer, budget_seconds=budget_seconds, fast_slow=fast_slow, max_steps=max_steps,
+                crct=crct, criticality=CriticalityDistillHook.from_config(model, config), episodic=episodic,
+                **common, **_loop_kwargs(config))
+            if episodic is not None:
+                episodic_cache_blob = episodic.cache_state()
+                if ddp:                                   # the cache lives on the episodic rank; rank 0 saves
+                    blobs = [None] * world_size if rank == 0 else None
+                    dist.gather_object(episodic_cache_blob, blobs, dst=0, group=control)
+                    if rank == 0:
+                        episodic_cache_blob = next((b for b in blobs if b is not None), None)
+        finally:
+            if episodic is not None:
+                episodic.close()
         if bool(config.get("rare_bucket_ce_enabled", False)):
             freq = torch.bincount(train_tokens.to(torch.int64).clamp_(0, vocab - 1), minlength=vocab)
             is_mem = crct is not None and crct.is_memory_rank
@@ -892,7 +936,7 @@ def run_condition(config: dict[str, Any], *, data_path: str, sp_model_path: Opti
             tmp.write_text(json.dumps(result, indent=2, default=str))
             tmp.rename(out)
         if output_ckpt:
-            _save_output_ckpt(output_ckpt, model, config)
+            _save_output_ckpt(output_ckpt, model, config, episodic_cache=episodic_cache_blob)
         print(f"[rank 0/{world_size}] done steps={train_result['steps']} "
               f"tok/s={train_result.get('aggregate_tokens_per_sec', 0.0):.0f} "
               f"loss={train_result['final_loss']:.4f} vram={train_result.get('peak_vram_mb', 0.0):.1f}MB", flush=True)

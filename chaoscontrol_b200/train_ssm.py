@@ -218,6 +218,38 @@ def train_ssm_step(model: nn.Module, inputs: torch.Tensor, targets: torch.Tensor
     return loss
 
 
+def train_ssm_step_with_ce(model: nn.Module, inputs: torch.Tensor, targets: torch.Tensor, *,
+                           precision: str = "bf16", lm_head_backward_mode: str = "fused",
+                           lm_head_tile_size: int = 1024) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Forward + backward that also hands back what an event producer needs:
+    ``(loss, per-token CE [B, T], trunk output [B, T, D])``.  No gradient
+    reduction happens here.  The kernel engine already keeps both by-products
+    of its fused head; the autograd path uses the CE-returning fused head."""
+    _reject_unsupported(model)
+    B, Tn = inputs.shape
+    mode = str(lm_head_backward_mode).strip().lower()
+    fused_mode = mode in _FUSED_LM_HEAD_BACKENDS
+    engine = _engine_for(model) if (fused_mode and precision in ("bf16", "fp8_fused") and model.training) else None
+    if engine is not None:
+        loss = engine.step(inputs, targets)
+        engine.arena.materialize_grads()
+        return loss, engine.last_loss_rows.reshape(B, Tn), engine.last_hidden.reshape(B, Tn, -1)
+    with autocast_context(precision, device_type=inputs.device.type):
+        hidden = model.encode(inputs)
+        if fused_mode:
+            loss, ce = fused_lm_head_backward_with_ce(hidden, model.final_norm, model.lm_head, targets,
+                                                      backend=fused_lm_head_backend_for_mode(mode),
+                                                      tile_size=int(lm_head_tile_size))
+        else:
+            logits = model.lm_head(model.final_norm(hidden))
+            ce = F.cross_entropy(logits.reshape(-1, logits.shape[-1]).float(), targets.reshape(-1),
+                                 reduction="none").reshape(B, Tn)
+            loss = ce.mean()
+            loss.backward()
+            loss, ce = loss.detach(), ce.detach()
+    return loss, ce.reshape(B, Tn), hidden.detach()
+
+
 # ---------------------------------------------------------------------------
 # budgeted loop
 # ---------------------------------------------------------------------------

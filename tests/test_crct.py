@@ -351,3 +351,25 @@ def test_mailbox_on_cuda_uses_pinned_shared_memory():
     finally:
         mem.close()
         train.close()
+
+
+@pytest.mark.gpu
+def test_inline_teacher_on_cuda_bf16():
+    from chaoscontrol_b200.runner_fast_path import _build_optimizer, train_fast_for_budget
+    dev = torch.device("cuda:0")
+    torch.manual_seed(0)
+    model = CareStudentLM(vocab_size=256, dim=64, num_layers=2, outer_model_dim=32, outer_model_type="multislot",
+                          outer_max_slots=0, buffer_mode="append_only").to(dev).to(torch.bfloat16)
+    tokens = torch.randint(0, 256, (1 << 15,), dtype=torch.int16)
+    cfg = dict(crct_enabled=True, crct_score_interval_steps=2, crct_memory_write_tokens_per_step=16, model_dim=64,
+               replay_eviction_enabled=True, replay_eviction_min_slot_age_steps=0)
+    rt = C.CrctRuntime(model=model, config=cfg, rank=0, world_size=1, device=dev, batch_size=4, seq_len=64,
+                       total_steps=8)
+    optim = _build_optimizer(dict(optimizer="adamw", base_lr=1e-3), model)
+    res = train_fast_for_budget(model, train_tokens=tokens, train_num_tokens=tokens.numel(), optimizer=optim,
+                                max_steps=8, crct=rt, replay_eviction_enabled=True,
+                                **_loop_kw(device=dev, precision="bf16", seq_len=64, stride=32, batch_size=4,
+                                           vocab_size=256, lm_head_backward_mode="fused_streaming_cached"))
+    d = res["crct"]
+    assert d["teacher_payloads"] == 4 and model.outer_model.table.n_active > 0
+    assert all(v == v for v in res["loss_history"])

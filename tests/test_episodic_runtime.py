@@ -1,0 +1,115 @@
+"""Episodic runtime in the training loop: one rank playing both parts, and two train ranks plus an
+episodic rank over gloo (event rings in shared memory, replay on the episodic rank, one SUM join)."""
+import os
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from chaoscontrol_b200.episodic.runtime import EpisodicRuntime
+from chaoscontrol_b200.models.model import CareStudentLM
+
+
+def _kw(**over):
+    kw = dict(stride=8, seq_len=16, batch_size=4, device=torch.device("cpu"), budget_seconds=600.0, precision="fp32",
+              stop_check_interval=1, lm_head_backward_mode="fused", prefetch_batches=False, vocab_size=64, max_steps=8)
+    kw.update(over)
+    return kw
+
+
+_CFG = dict(episodic_capacity=64, episodic_writes_per_step=4, episodic_fingerprint_window=2, model_dim=16,
+            episodic_replay_max_replays_per_step=2)
+
+
+def test_one_rank_produces_consumes_and_replays(tmp_path):
+    from chaoscontrol_b200.runner_fast_path import _build_optimizer, train_fast_for_budget
+    torch.manual_seed(0)
+    tokens = torch.randint(0, 64, (4000,), dtype=torch.int16)
+    model = CareStudentLM(vocab_size=64, dim=16, num_layers=2)
+    rt = EpisodicRuntime(model=model, config=dict(_CFG, episodic_replay_log_path=str(tmp_path / "replay.ndjson")),
+                         rank=0, world_size=1, device=torch.device("cpu"))
+    optim = _build_optimizer(dict(optimizer="adamw", base_lr=1e-3), model)
+    try:
+        res = train_fast_for_budget(model, train_tokens=tokens, train_num_tokens=4000, optimizer=optim, episodic=rt,
+                                    **_kw())
+    finally:
+        rt.close()
+    e = res["episodic"]
+    assert e["role"] == "solo" and e["write_events_emitted"] == e["write_events_ingested"] > 0
+    assert e["query_events_emitted"] == 8 and e["queries_ingested"] == 8
+    assert 1 <= e["replays"] <= 16 and e["replay_status"]["ok"] == e["replays"]
+    assert e["cache_entries"] == min(e["write_events_ingested"], 64)
+    rows = (tmp_path / "replay.ndjson").read_text().strip().splitlines()
+    assert len(rows) == e["replays"]
+    blob = rt.cache_state()
+    assert blob is not None and "key_fp" in str(blob.keys())
+
+
+def _rank(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from chaoscontrol_b200.runner_fast_path import _build_optimizer, train_fast_for_budget
+        torch.manual_seed(rank)
+        model = CareStudentLM(vocab_size=64, dim=16, num_layers=2)
+        tokens = torch.randint(0, 64, (4000,), dtype=torch.int16, generator=torch.Generator().manual_seed(0))
+        rt = EpisodicRuntime(model=model, config=dict(_CFG, episodic_event_ring_namespace=f"/ccb_t_epi_{port}"),
+                             rank=rank, world_size=world, device=torch.device("cpu"))
+        optim = _build_optimizer(dict(optimizer="adamw", base_lr=1e-3), model)
+        try:
+            res = train_fast_for_budget(model, train_tokens=tokens, train_num_tokens=4000, optimizer=optim,
+                                        episodic=rt, rank=rank, world_size=world, **_kw(max_steps=10))
+        finally:
+            rt.close()
+        torch.save({"res": {k: v for k, v in res.items() if k != "spectral"},
+                    "w": model.lm_head.weight.detach().clone()}, os.path.join(out_dir, f"r{rank}.pt"))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_train_ranks_and_an_episodic_rank(tmp_path):
+    mp.spawn(_rank, args=(3, 29761, str(tmp_path)), nprocs=3, join=True)
+    r = [torch.load(tmp_path / f"r{i}.pt", weights_only=False) for i in range(3)]
+    # every rank applied the same joined gradient, the episodic rank included
+    assert torch.allclose(r[0]["w"], r[1]["w"], atol=1e-6) and torch.allclose(r[0]["w"], r[2]["w"], atol=1e-6)
+    e0, e1, e2 = (x["res"]["episodic"] for x in r)
+    assert e0["role"] == "train" and e2["role"] == "episodic" and e2["n_train"] == 2
+    assert e2["write_events_ingested"] > 0
+    assert e2["write_events_ingested"] <= e0["write_events_emitted"] + e1["write_events_emitted"]
+    assert e2["queries_ingested"] >= 10 and e2["replays"] >= 1 and e2["cache_entries"] > 0
+    assert e0["replays"] == 0 and "cache_entries" not in e0
+    # throughput counts the train ranks only
+    assert r[0]["res"]["tokens_per_step"] == 4 * 16 * 2
+
+
+import pytest  # noqa: E402
+
+
+@pytest.mark.gpu
+def test_kernel_engine_step_feeds_the_episodic_runtime():
+    """bf16 bare trunk on the kernel engine: per-token CE and the trunk output come from the engine,
+    write events are packed on the device and staged through pinned memory."""
+    from chaoscontrol_b200.runner_fast_path import _build_optimizer, train_fast_for_budget
+    from chaoscontrol_b200.utils.arena import ParamArena
+    dev = torch.device("cuda:0")
+    torch.manual_seed(0)
+    tokens = torch.randint(0, 512, (1 << 16,), dtype=torch.int16)
+    model = CareStudentLM(vocab_size=512, dim=256, num_layers=2).to(dev).to(torch.bfloat16)
+    ParamArena.install(model)
+    rt = EpisodicRuntime(model=model, config=dict(episodic_capacity=256, episodic_writes_per_step=8, model_dim=256),
+                         rank=0, world_size=1, device=dev)
+    optim = _build_optimizer(dict(optimizer="muon", base_lr=0.02), model)
+    try:
+        res = train_fast_for_budget(model, train_tokens=tokens, train_num_tokens=tokens.numel(), optimizer=optim,
+                                    episodic=rt, **_kw(device=dev, precision="bf16", seq_len=128, stride=64,
+                                                       batch_size=8, vocab_size=512, max_steps=12,
+                                                       lm_head_backward_mode="fused_streaming_cached"))
+        torch.cuda.synchronize()
+    finally:
+        rt.close()
+    e = res["episodic"]
+    assert e["write_events_ingested"] > 0 and e["replays"] >= 1 and e["replay_status"]["nan"] == 0
+    assert e["key_rep_dim"] == 256 and res["loss_history"][-1] < res["loss_history"][0]
+    from chaoscontrol_b200.ops import _lib
+    _lib.assert_ok()

@@ -92,9 +92,15 @@ def test_run_condition_cpu_end_to_end(tmp_path, monkeypatch):
                        data_path=str(tmp_path), sp_model_path="fake.model", budget_seconds=1.0, output_json=None,
                        output_ckpt=None, world_size_override=None)
     assert ev["train"]["steps"] == 0 and np.isfinite(ev["eval"]["bpb"])
-    with pytest.raises(NotImplementedError):
-        run_condition(_config(episodic_enabled=True, warmup_steps=0), data_path=str(tmp_path), sp_model_path=None,
-                      budget_seconds=1.0, output_json=None, output_ckpt=None, world_size_override=None)
+    epi_ckpt = tmp_path / "epi.pt"
+    epi = run_condition(_config(episodic_enabled=True, warmup_steps=0, episodic_capacity=64, episodic_writes_per_step=4,
+                                episodic_fingerprint_window=2, fast_slow_enabled=False, weight_ema_decay=0.0,
+                                eval_batches=0),
+                        data_path=str(tmp_path), sp_model_path=None, budget_seconds=60.0, output_json=None,
+                        output_ckpt=str(epi_ckpt), world_size_override=None)
+    e = epi["train"]["episodic"]
+    assert e["role"] == "solo" and e["write_events_ingested"] > 0 and e["cache_entries"] > 0 and e["replays"] > 0
+    assert "episodic_cache" in torch.load(epi_ckpt, weights_only=False)
     with pytest.raises(ValueError):                                 # the teacher needs an episodic store
         run_condition(_config(crct_enabled=True, warmup_steps=0), data_path=str(tmp_path), sp_model_path=None,
                       budget_seconds=1.0, output_json=None, output_ckpt=None, world_size_override=None)

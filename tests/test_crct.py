@@ -204,19 +204,27 @@ def test_train_loop_inline_teacher_and_maintenance():
                               replay_eviction_enabled=True, **_loop_kw())
 
 
-def _crct_rank(rank, world, port, mode, out_dir, split=False):
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+def _crct_rank(rank, world, port, mode, out_dir, split=False, cuda=False):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      NCCL_NVLS_ENABLE="0")
+    dev = torch.device("cpu")
+    if cuda:
+        torch.cuda.set_device(rank)
+        dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl" if cuda else "gloo", rank=rank, world_size=world,
+                            **({"device_id": dev} if cuda else {}))
     try:
         from chaoscontrol_b200.runner_fast_path import _build_optimizer, train_fast_for_budget
         model = _memory_model(seed=rank)                                  # different inits: rank 0 must win
+        if cuda:
+            model = model.to(dev).to(torch.bfloat16)
         tokens = torch.randint(0, 48, (4000,), dtype=torch.int16, generator=torch.Generator().manual_seed(0))
         cfg = dict(crct_enabled=True, crct_teacher_transport_mode=mode, crct_memory_write_tokens_per_step=4,
                    crct_teacher_param_sync_interval=2, crct_mailbox_name=f"/ccb_t_run_{port}", model_dim=16,
                    crct_max_payload_lag_steps=64, crct_max_local_batches=64, crct_mailbox_capacity=64,
                    crct_split_memory_ranks=split, replay_eviction_enabled=split,
                    replay_eviction_min_slot_age_steps=0)
-        rt = C.CrctRuntime(model=model, config=cfg, rank=rank, world_size=world, device=torch.device("cpu"),
+        rt = C.CrctRuntime(model=model, config=cfg, rank=rank, world_size=world, device=dev,
                            batch_size=3, seq_len=8, total_steps=12)
         optim = _build_optimizer(dict(optimizer="adamw", base_lr=1e-3), model)
         # slow the train ranks a little so the asynchronous teacher has time to answer
@@ -229,9 +237,10 @@ def _crct_rank(rank, world, port, mode, out_dir, split=False):
         res = train_fast_for_budget(model, train_tokens=tokens, train_num_tokens=4000, optimizer=optim, max_steps=12,
                                     crct=rt, rank=rank, world_size=world, time_fn=slow_clock,
                                     replay_eviction_enabled=split,
-                                    **_loop_kw(budget_seconds=20.0, stop_margin_seconds=0.0))
+                                    **_loop_kw(budget_seconds=20.0, stop_margin_seconds=0.0, device=dev,
+                                               precision="bf16" if cuda else "fp32"))
         torch.save({"res": {k: v for k, v in res.items() if k != "spectral"},
-                    "w": model.lm_head.weight.detach().clone(),
+                    "w": model.lm_head.weight.detach().float().cpu(),
                     "slots": int(model.outer_model.table.n_active)}, os.path.join(out_dir, f"r{rank}.pt"))
         dist.barrier()
     finally:
@@ -373,3 +382,21 @@ def test_inline_teacher_on_cuda_bf16():
     d = res["crct"]
     assert d["teacher_payloads"] == 4 and model.outer_model.table.n_active > 0
     assert all(v == v for v in res["loss_history"])
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(torch.cuda.device_count() < 3, reason="needs 3 GPUs")
+@pytest.mark.parametrize("mode,port", [("async_rank0_memory_mailbox", 29771), ("sync", 29773)])
+def test_crct_on_three_gpus(tmp_path, mode, port):
+    """Two train GPUs in an NCCL gradient subgroup, the third GPU is the memory rank."""
+    mp.spawn(_crct_rank, args=(3, port, mode, str(tmp_path), False, True), nprocs=3, join=True)
+    r = [torch.load(tmp_path / f"r{i}.pt", weights_only=False) for i in range(3)]
+    assert r[0]["res"]["steps"] == 12 and torch.allclose(r[0]["w"], r[1]["w"], atol=1e-6)
+    mem = r[2]["res"]
+    assert mem["role"] == "memory" and mem["steps"] >= 1
+    d0 = r[0]["res"]["crct"]
+    if mode == "sync":
+        assert mem["steps"] == 12 and d0["teacher_payloads"] == 12
+    else:
+        assert d0["teacher_payloads"] + d0["teacher_fail_open"] == 12
+        assert mem["crct"]["mailbox"]["weight_snapshots_applied"] >= 1

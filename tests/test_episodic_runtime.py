@@ -45,24 +45,39 @@ def test_one_rank_produces_consumes_and_replays(tmp_path):
     assert blob is not None and "key_fp" in str(blob.keys())
 
 
-def _rank(rank, world, port, out_dir):
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+def _rank(rank, world, port, out_dir, cuda=False):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      NCCL_NVLS_ENABLE="0")
+    dev = torch.device("cpu")
+    if cuda:
+        torch.cuda.set_device(rank)
+        dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl" if cuda else "gloo", rank=rank, world_size=world,
+                            **({"device_id": dev} if cuda else {}))
     try:
         from chaoscontrol_b200.runner_fast_path import _build_optimizer, train_fast_for_budget
+        from chaoscontrol_b200.utils.arena import ParamArena
         torch.manual_seed(rank)
-        model = CareStudentLM(vocab_size=64, dim=16, num_layers=2)
-        tokens = torch.randint(0, 64, (4000,), dtype=torch.int16, generator=torch.Generator().manual_seed(0))
-        rt = EpisodicRuntime(model=model, config=dict(_CFG, episodic_event_ring_namespace=f"/ccb_t_epi_{port}"),
-                             rank=rank, world_size=world, device=torch.device("cpu"))
+        dim, vocab = (256, 512) if cuda else (16, 64)
+        model = CareStudentLM(vocab_size=vocab, dim=dim, num_layers=2)
+        extra = {}
+        if cuda:
+            model = model.to(dev).to(torch.bfloat16)
+            ParamArena.install(model)                                   # kernel engine on the train ranks
+            extra = dict(device=dev, precision="bf16", seq_len=128, stride=64, batch_size=8, vocab_size=vocab,
+                         lm_head_backward_mode="fused_streaming_cached")
+        tokens = torch.randint(0, vocab, (1 << 15,), dtype=torch.int16, generator=torch.Generator().manual_seed(0))
+        rt = EpisodicRuntime(model=model, config=dict(_CFG, model_dim=dim, episodic_replay_weight=0.1,
+                                                      episodic_event_ring_namespace=f"/ccb_t_epi_{port}"),
+                             rank=rank, world_size=world, device=dev)
         optim = _build_optimizer(dict(optimizer="adamw", base_lr=1e-3), model)
         try:
-            res = train_fast_for_budget(model, train_tokens=tokens, train_num_tokens=4000, optimizer=optim,
-                                        episodic=rt, rank=rank, world_size=world, **_kw(max_steps=10))
+            res = train_fast_for_budget(model, train_tokens=tokens, train_num_tokens=tokens.numel(), optimizer=optim,
+                                        episodic=rt, rank=rank, world_size=world, **_kw(max_steps=10, **extra))
         finally:
             rt.close()
         torch.save({"res": {k: v for k, v in res.items() if k != "spectral"},
-                    "w": model.lm_head.weight.detach().clone()}, os.path.join(out_dir, f"r{rank}.pt"))
+                    "w": model.lm_head.weight.detach().float().cpu()}, os.path.join(out_dir, f"r{rank}.pt"))
         dist.barrier()
     finally:
         dist.destroy_process_group()
@@ -114,3 +129,15 @@ def test_kernel_engine_step_feeds_the_episodic_runtime():
     assert e["key_rep_dim"] == 256 and all(v == v and v < 8.0 for v in res["loss_history"])
     from chaoscontrol_b200.ops import _lib
     _lib.assert_ok()
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(torch.cuda.device_count() < 3, reason="needs 3 GPUs")
+def test_episodic_rank_on_three_gpus(tmp_path):
+    """Two train GPUs on the kernel engine + an episodic GPU; one NCCL SUM join over the flat arena."""
+    mp.spawn(_rank, args=(3, 29763, str(tmp_path), True), nprocs=3, join=True)
+    r = [torch.load(tmp_path / f"r{i}.pt", weights_only=False) for i in range(3)]
+    assert torch.allclose(r[0]["w"], r[1]["w"], atol=1e-6) and torch.allclose(r[0]["w"], r[2]["w"], atol=1e-6)
+    e2 = r[2]["res"]["episodic"]
+    assert e2["role"] == "episodic" and e2["write_events_ingested"] > 0 and e2["replays"] >= 1
+    assert all(v == v for v in r[0]["res"]["loss_history"])

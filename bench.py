@@ -46,6 +46,9 @@ CONFIGS = {
     # streaming score-only evaluation: 50,000 synthetic documents (lognormal lengths, median 700, sigma 1,
     # clipped to [32, 32768]) sharded over the ranks, 512-token chunks, state carried inside a document
     "eval": dict(dim=256, layers=4, ff_mult=2, seq=512, batch=1024, dist_muon=False, fp8=False),
+    # test-time-training evaluation: every 256-token chunk is scored, then one SGD step on log_a and the delta
+    # projection is taken on it from the same carried state; adapted weights are restored after each document
+    "eval_ttt": dict(dim=256, layers=4, ff_mult=2, seq=512, batch=1024, dist_muon=False, fp8=False),
 }
 
 
@@ -367,6 +370,87 @@ def run_eval(args):
 
 
 # ---------------------------------------------------------------------------
+def run_eval_ttt(args):
+    """Score-then-adapt (test-time training) evaluation throughput, whole job.  One step = one pass of
+    this rank's document shard through ``run_ttt_eval``: per 256-token chunk one scoring pass and one
+    SGD step on ``log_a`` + the delta projection, state carried inside a document, adapted weights
+    restored at the document's end."""
+    import numpy as np
+    import torch
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": "the reference's TTT driver is a script outside its "
+                          "installed package (scripts/run_exp20_eval.py); baseline/_ref does not contain it"}))
+        return
+    sys.path.insert(0, str(ROOT))
+    from chaoscontrol_b200.data import lognormal_doc_lengths, zipf_tokens
+    from chaoscontrol_b200.eval_stream.types import DocRecord
+    from chaoscontrol_b200.models.model import CareStudentLM
+    from chaoscontrol_b200.ops import _lib
+    from chaoscontrol_b200.scoring import assign_docs_lpt, run_ttt_eval, run_ttt_eval_graph
+    rank, local, ws = _dist_setup(args)
+    dev = torch.device("cuda", local)
+    torch.manual_seed(0)
+    model = CareStudentLM(vocab_size=VOCAB, dim=DIM, num_layers=LAYERS, ff_mult=FF_MULT).to(dev).to(torch.bfloat16)
+    n_docs, chunk = 512, 256
+    lens_all = lognormal_doc_lengths(n_docs, median=700.0, sigma=1.0, lo=32, hi=8192, seed=0)
+    mine = sorted(assign_docs_lpt(lens_all.tolist(), ws, chunk)[rank])
+    toks = zipf_tokens(int(lens_all[mine].sum()), VOCAB, s=1.1, seed=1 + rank).tolist()
+    docs, off = [], 0
+    for i in mine:
+        n = int(lens_all[i])
+        docs.append(DocRecord(doc_id=int(i), tokens=toks[off: off + n], raw_bytes=4 * n))
+        off += n
+    total_targets = int(np.maximum(lens_all - 1, 0).sum())
+    box = {}
+
+    def one_pass(i):
+        box["res"] = run_ttt_eval_graph(model, docs, adapt_set="log_a+delta_proj", chunk_size=chunk, eval_lr=LR)
+
+    def one_pass_eager(i):
+        box["eager"] = run_ttt_eval(model, docs, adapt_set="log_a+delta_proj", persistence_mode="reset",
+                                    chunk_size=chunk, steps_per_chunk=1, eval_lr=LR, optimizer="sgd",
+                                    budget_seconds=3600.0)
+
+    for i in range(max(1, min(args.warmup, 2))):
+        one_pass(i)
+    l0 = _lib.launch_count()
+    with ClockSampler(local) as cs:
+        ms = _timed(one_pass, max(1, min(args.steps, 3)), ws)
+    launches = _lib.launch_count() - l0
+    _lib.assert_ok()
+    one_pass_eager(0)
+    ms_eager = _timed(one_pass_eager, 1, ws)
+    res = box["res"]
+    out = {"metric": "eval tokens/sec, streaming test-time training (score then 1 SGD step per 256-token chunk), "
+                     "4Lx256d V16384 SSM, 512 docs",
+           "value": total_targets / (ms / 1e3), "unit": "tokens/s", "n_gpus": ws, "steps": max(1, min(args.steps, 3)),
+           "warmup": max(1, min(args.warmup, 2)), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+           "vs_baseline": None, "dtype": "bf16",
+           "data": "synthetic Zipf(1.1) tokens in lognormal-length documents, random-init weights", "impl": "ours",
+           "mean_ce": float(res["mean_ce"]), "adapt_steps_per_pass": int(res["adapt_steps"]),
+           "chunks_per_pass": int(res["chunks_scored"]), "graph_replays_per_pass": int(res["graph_replays"]),
+           "eager_driver": {"value": total_targets / (ms_eager / 1e3), "unit": "tokens/s", "ms_per_step": ms_eager,
+                            "mean_ce": float(box["eager"]["mean_ce"]),
+                            "api": "chaoscontrol_b200.scoring.run_ttt_eval (module path, logits materialised)"},
+           "gpu_launches": launches, "clocks": cs.summary(),
+           "e2e": {"value": total_targets / (ms / 1e3), "unit": "tokens/s", "ms_per_step": ms,
+                   "h2d_bytes_per_step": int(sum(len(d.tokens) for d in docs) * 8),
+                   "d2h_bytes_per_step": len(docs) * 8,
+                   "api": "chaoscontrol_b200.scoring.run_ttt_eval_graph (documents arrive as host token lists, one "
+                          "pinned upload per document; per-document CE is read back once per pass)"},
+           "config": {"model": f"CareStudentLM {LAYERS}x{DIM} V{VOCAB} ff_mult {FF_MULT}", "docs": n_docs,
+                      "tokens_scored_per_pass": total_targets, "chunk_size": chunk, "adapt_set": "log_a+delta_proj",
+                      "steps_per_chunk": 1, "optimizer": "sgd", "persistence_mode": "reset",
+                      "parallelism": f"documents split over {ws} rank(s) by longest-processing-time packing",
+                      "l2": "documents are processed one at a time (batch 1): launch-bound, not cache-bound; "
+                            "gpu_launches counts eager launches only (graph replays re-issue captured kernels)"}}
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    if ws > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
 def run_fp8(args):
     """fp8 trunk linears, module-by-module autograd path, either arm: same loop, same timing."""
     import torch
@@ -574,6 +658,8 @@ if __name__ == "__main__":
     a = _parse()
     if a.config == "eval":
         run_eval(a)
+    elif a.config == "eval_ttt":
+        run_eval_ttt(a)
     elif a.config == "fp8":
         run_fp8(a)
     elif a.impl == "reference":

@@ -124,16 +124,22 @@ class _TrunkFn(torch.autograd.Function):
         ctx.shape = (B, Tn, embed_w.shape[0])
         ctx.has_h0 = h0_stack is not None
         ctx.mark_non_differentiable(ss)
+        # unused outputs arrive in backward as None instead of zero tensors: no value has to be read
+        # back to find out whether the final states carry a gradient
+        ctx.set_materialize_grads(False)
         return x.view(B, Tn, -1), ss, torch.stack(hTs, dim=0)
 
     @staticmethod
     def backward(ctx, dhidden, _dss, dhT_stack):
         B, Tn, V = ctx.shape
+        if dhidden is None:
+            w0 = ctx.ws[0].Wo
+            dhidden = torch.zeros(B * Tn, w0.shape[0], dtype=w0.dtype, device=w0.device)
         dx = dhidden.reshape(B * Tn, -1).contiguous()
         grads: list = []
         L = len(ctx.ws)
         dh0s = []
-        use_dhT = dhT_stack is not None and bool(dhT_stack.abs().sum() != 0) if dhT_stack is not None else False
+        use_dhT = dhT_stack is not None
         for i in reversed(range(L)):
             w, c = ctx.ws[i], ctx.ctxs[i]
             dhT = dhT_stack[i].float().contiguous() if use_dhT else None

@@ -278,3 +278,153 @@ def run_ttt_eval(model: nn.Module, docs, *, adapt_set: str = "log_a+delta_proj",
                    mean_ce=tot_ce / max(tot_tok, 1), tokens_per_s=tot_tok / elapsed if elapsed > 0 else 0.0,
                    adapt_set=adapt_set, persistence_mode=persistence_mode)
     return summary
+
+
+# ---------------------------------------------------------------------------
+# test-time training with the per-chunk work captured in a CUDA graph
+# ---------------------------------------------------------------------------
+class GraphTTTRunner:
+    """Score a fixed-length chunk, then take one SGD step on it, as ONE CUDA graph.
+
+    Per-document TTT runs at batch 1, so a chunk is a few hundred small launches
+    and the Python/driver launch path, not the GPU, sets the pace.  The body
+    (kernel-trunk scoring pass with the carried state, fused-head per-row CE
+    accumulated on the device, autograd forward + backward of the summed CE from
+    the SAME state, ``p -= lr * grad`` on the adapt set, carried state := the
+    scoring pass's final state) is captured once for ``chunk_size`` tokens and
+    replayed per chunk; only the ragged tail of a document runs eagerly.
+    Nothing is read back inside a document."""
+
+    def __init__(self, model: nn.Module, params: list, *, chunk_size: int, lr: float) -> None:
+        if not getattr(model, "kernel_trunk_supported", lambda: False)():
+            raise ValueError("GraphTTTRunner needs the bf16 kernel trunk")
+        self.model, self.params, self.C, self.lr = model, list(params), int(chunk_size), float(lr)
+        dev = model.embed.weight.device
+        self.device = dev
+        self.tok = torch.zeros(1, self.C + 1, dtype=torch.long, device=dev)
+        self.state = [torch.zeros(1, model.dim, device=dev, dtype=model.embed.weight.dtype) for _ in model.layers]
+        self.ce_acc = torch.zeros((), dtype=torch.float32, device=dev)
+        self._frozen = [p for p in model.parameters() if p.requires_grad and all(p is not q for q in self.params)]
+        for p in self._frozen:
+            p.requires_grad_(False)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.replays = self.eager_chunks = 0
+        # warm up off the capture stream (allocator, kernel attributes), then capture
+        snap = [p.detach().clone() for p in self.params]
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self._body(self.tok)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        for p in self.params:
+            p.grad = None
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, capture_error_mode="thread_local"):
+            self._body(self.tok)
+        self.graph = g
+        with torch.no_grad():
+            for p, s in zip(self.params, snap):
+                p.copy_(s)
+        self.start_doc()
+
+    def _body(self, tok: torch.Tensor) -> None:
+        from .kernels.lm_head_loss import fused_linear_cross_entropy, fused_rms_norm
+        m = self.model
+        inp, tgt = tok[:, :-1].to(torch.int32), tok[:, 1:]
+        with torch.no_grad():
+            rows, finals = _chunk_loss_rows(m, inp, tgt, self.state)
+            self.ce_acc += rows.float().sum()
+        if self.params:
+            hidden = m.encode(inp, initial_states=self.state)
+            loss = fused_linear_cross_entropy(fused_rms_norm(hidden, m.final_norm.weight, eps=m.final_norm.eps),
+                                              m.lm_head.weight, tgt, reduction="sum")
+            loss.backward()
+            with torch.no_grad():
+                torch._foreach_add_(self.params, [p.grad for p in self.params], alpha=-self.lr)
+        with torch.no_grad():
+            for s, f in zip(self.state, finals):
+                s.copy_(f)
+
+    def start_doc(self) -> None:
+        for s in self.state:
+            s.zero_()
+        self.ce_acc.zero_()
+
+    def run_doc(self, doc_tokens: torch.Tensor) -> tuple[torch.Tensor, int]:
+        """``doc_tokens``: ``[n]`` long on the device.  Returns ``(summed CE as a
+        device scalar, chunks)``; state and accumulator are reset first."""
+        self.start_doc()
+        n, C, chunks = int(doc_tokens.numel()), self.C, 0
+        for s in range(0, n - 1, C):
+            piece = doc_tokens[s: s + C + 1]
+            if piece.numel() < 2:
+                break
+            if piece.numel() == C + 1:
+                self.tok.copy_(piece.view(1, -1))
+                self.graph.replay()
+                self.replays += 1
+            else:
+                for p in self.params:
+                    p.grad = None
+                self._body(piece.view(1, -1))
+                self.eager_chunks += 1
+            chunks += 1
+        return self.ce_acc.clone(), chunks
+
+    def close(self) -> None:
+        for p in self._frozen:
+            p.requires_grad_(True)
+        self.graph = None
+
+
+def run_ttt_eval_graph(model: nn.Module, docs, *, adapt_set: str = "log_a+delta_proj", chunk_size: int = 256,
+                       eval_lr: float = 0.064, max_docs: Optional[int] = None, metrics=None) -> dict:
+    """``run_ttt_eval`` for its most common setting -- SGD, one step per chunk,
+    ``reset`` persistence, adapted weights restored after every document -- with
+    the per-chunk work replayed from a CUDA graph and per-document CE read back
+    once at the end (per document when ``metrics`` wants rows)."""
+    device = next(model.parameters()).device
+    params = select_adapt_params(model, adapt_set=adapt_set)
+    was_training = model.training
+    model.eval()
+    runner = GraphTTTRunner(model, params, chunk_size=chunk_size, lr=eval_lr)
+    snap = [p.detach().clone() for p in params]
+    t0 = time.perf_counter()
+    ces, toks, byts, n_chunks, ids = [], [], [], 0, []
+    try:
+        for rec in docs:
+            if max_docs is not None and len(ces) >= max_docs:
+                break
+            if len(rec.tokens) < 2:
+                continue
+            host = torch.as_tensor(rec.tokens, dtype=torch.long)
+            dev_toks = (host.pin_memory() if device.type == "cuda" else host).to(device, non_blocking=True)
+            ce, ch = runner.run_doc(dev_toks)
+            with torch.no_grad():
+                for p, s in zip(params, snap):
+                    p.copy_(s)
+            ces.append(ce)
+            toks.append(len(rec.tokens) - 1)
+            byts.append(rec.raw_bytes)
+            ids.append(rec.doc_id)
+            n_chunks += ch
+            if metrics is not None:
+                doc_ce = float(ce)
+                metrics.record_doc(doc_id=rec.doc_id, bpb=compute_bpb(doc_ce, rec.raw_bytes), tokens=toks[-1],
+                                   loss_before=doc_ce / max(toks[-1], 1), loss_after=None, step_count=n_chunks,
+                                   wall_ms=0.0, grad_norm=0.0, state_norm=0.0)
+        ce_all = torch.stack(ces).double().cpu() if ces else torch.zeros(0, dtype=torch.float64)
+    finally:
+        replays, eager = runner.replays, runner.eager_chunks
+        runner.close()
+        model.train(was_training)
+    elapsed = time.perf_counter() - t0
+    tot_ce, tot_tok, tot_bytes = float(ce_all.sum()), int(sum(toks)), int(sum(byts))
+    return {"docs_scored": len(ces), "chunks_scored": n_chunks, "tokens_scored": tot_tok,
+            "adapt_steps": n_chunks if params else 0, "elapsed_seconds": elapsed, "chunk_size": chunk_size,
+            "total_ce_nats": tot_ce, "total_raw_bytes": tot_bytes, "bpb": compute_bpb(tot_ce, tot_bytes),
+            "mean_ce": tot_ce / max(tot_tok, 1), "tokens_per_s": tot_tok / elapsed if elapsed > 0 else 0.0,
+            "adapt_set": adapt_set, "persistence_mode": "reset", "graph_replays": replays, "eager_chunks": eager,
+            "per_doc_ce": {int(i): float(c) for i, c in zip(ids, ce_all.tolist())}}

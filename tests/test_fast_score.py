@@ -117,3 +117,31 @@ def test_graph_chunk_scorer_matches_eager():
     _lib.assert_ok()
     assert torch.equal(gr1, r1) and torch.equal(gr2, r2)
     assert all(torch.equal(a.float(), b.float()) for a, b in zip(gf2, f2))
+
+
+@pytest.mark.gpu
+def test_graph_ttt_matches_the_eager_ttt_driver():
+    """Same documents, same SGD rule: the graph-replayed chunk step gives the eager driver's CE."""
+    import numpy as np
+    from chaoscontrol_b200.eval_stream.types import DocRecord
+    from chaoscontrol_b200.models.model import CareStudentLM
+    from chaoscontrol_b200.scoring import run_ttt_eval, run_ttt_eval_graph
+    dev = torch.device("cuda:0")
+    torch.manual_seed(0)
+    model = CareStudentLM(vocab_size=1024, dim=256, num_layers=2).to(dev).to(torch.bfloat16)
+    rng = np.random.default_rng(0)
+    docs = [DocRecord(doc_id=i, tokens=rng.integers(0, 1024, n).tolist(), raw_bytes=4 * n)
+            for i, n in enumerate([300, 513, 40, 1025, 257])]
+    before = [p.detach().clone() for p in model.parameters()]
+    kw = dict(adapt_set="log_a+delta_proj", chunk_size=256, eval_lr=0.01)
+    fast = run_ttt_eval_graph(model, docs, **kw)
+    for p, b in zip(model.parameters(), before):
+        assert torch.equal(p, b) and p.requires_grad            # weights restored, flags restored
+    slow = run_ttt_eval(model, docs, persistence_mode="reset", steps_per_chunk=1, optimizer="sgd", **kw)
+    assert fast["docs_scored"] == 5 and fast["chunks_scored"] == slow["chunks_scored"] == 2 + 3 + 1 + 4 + 1
+    assert fast["graph_replays"] == 1 + 2 + 0 + 4 + 1 and fast["eager_chunks"] == 1 + 1 + 1 + 0 + 0
+    assert abs(fast["mean_ce"] - slow["mean_ce"]) < 2e-2 * slow["mean_ce"]
+    # adaptation is really happening: a score-only pass gives a different CE on the multi-chunk documents
+    none = run_ttt_eval_graph(model, docs, adapt_set="none", chunk_size=256, eval_lr=0.01)
+    assert none["adapt_steps"] == 0 and abs(none["per_doc_ce"][3] - fast["per_doc_ce"][3]) > 1e-3
+    assert abs(none["per_doc_ce"][2] - fast["per_doc_ce"][2]) < 1e-3 * abs(none["per_doc_ce"][2])

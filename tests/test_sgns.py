@@ -87,3 +87,38 @@ def test_moment_matching_and_controls():
     with pytest.raises(ValueError):
         sgns.frequency_bucket_ids(torch.ones(3), num_buckets=0)
     assert sgns.token_class_bucket_ids(["▁the", "!?", "42", "abc", "a1", " "]).tolist() == [0, 1, 2, 3, 4, 0]
+
+
+def test_cli_train_prepare_report(tmp_path):
+    import json
+
+    import numpy as np
+    from chaoscontrol_b200.sgns import cli
+    rng = np.random.default_rng(0)
+    rng.integers(0, 32, 6000, dtype=np.uint16).tofile(tmp_path / "fineweb_train_000.bin")
+    rng.integers(0, 32, 600, dtype=np.uint16).tofile(tmp_path / "fineweb_val_000.bin")
+    table = tmp_path / "art" / "sgns_v32_d8.pt"
+    assert cli.main(["train", "--data-dir", str(tmp_path), "--vocab-size", "32", "--dim", "8", "--epochs", "1",
+                     "--batch-size", "256", "--max-batches", "4", "--subsample-threshold", "0.05",
+                     "--out", str(table), "--device", "cpu"]) == 0
+    w = torch.load(table, weights_only=True)
+    assert w.shape == (32, 8) and json.loads(table.with_suffix(".json").read_text())["epochs"] == 1
+    assert cli.main(["prepare-inits", "--sgns", str(table), "--out-dir", str(tmp_path / "inits"),
+                     "--data-dir-for-counts", str(tmp_path), "--freq-buckets", "4"]) == 0
+    names = sorted(p.stem.removeprefix("sgns_init_") for p in (tmp_path / "inits").glob("*.pt"))
+    assert names == sorted(["meanstd", "fullcov", "shuffled", "zero", "norm_only", "norm_only_shuffled",
+                            "fullcov_shuffled", "random_fullcov", "freq_bucket_shuffle"])
+    ms = torch.load(tmp_path / "inits" / "sgns_init_meanstd.pt", weights_only=True)
+    sh = torch.load(tmp_path / "inits" / "sgns_init_shuffled.pt", weights_only=True)
+    assert torch.allclose(ms.norm(dim=-1).sort().values, sh.norm(dim=-1).sort().values, atol=1e-5)
+    assert not torch.equal(ms, sh) and float(torch.load(tmp_path / "inits" / "sgns_init_zero.pt").abs().sum()) == 0
+    out = tmp_path / "report.json"
+    assert cli.main(["report", "--embed", str(table), "--n-common", "8", "--k-clusters", "3", "--k-nn", "2",
+                     "--n-random-pairs", "100", "--out", str(out)]) == 0
+    rep = json.loads(out.read_text())
+    assert rep["vocab_size"] == 32 and sum(rep["cluster_sizes"]) == 32 and -1 <= rep["random_pair_mean_cos"] <= 1
+    # subsampling keeps rare tokens and thins frequent ones
+    stream = torch.cat([torch.zeros(9000, dtype=torch.long), torch.arange(1, 11)])
+    kept = cli.subsample_frequent(stream, torch.bincount(stream, minlength=11), 1e-3,
+                                  generator=torch.Generator().manual_seed(0))
+    assert (kept != 0).sum() == 10 and (kept == 0).sum() < 2000

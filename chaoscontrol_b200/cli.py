@@ -1,0 +1,233 @@
+"""Data-preparation and measurement commands that sit beside the runners:
+
+``build-shards``      JSONL text + SentencePiece model -> ``fineweb_{train,val}_NNN.bin`` (flat little-endian
+                      uint16, no header, no EOS appended)            (scripts/build_sp_shards.py)
+``build-val-cache``   JSONL text -> ``tokens.npy`` / ``docs.npy`` / ``manifest.json``  (scripts/build_exp20_val_cache.py)
+``verify-val-cache``  a validation shard against a cache built from the same text     (scripts/verify_sp16384_eval_cache.py)
+``eval-quant``        bits-per-byte of a checkpoint before and after the int6 GPTQ + LZMA round trip
+                                                                       (scripts/eval_quant.py)
+
+``python -m chaoscontrol_b200.cli <command> --help``
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import time
+from pathlib import Path
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+__all__ = ["main", "build_shards", "verify_val_cache", "eval_quant"]
+
+ARTIFACT_LIMIT_BYTES = 16 * 1024 * 1024
+
+
+# ---------------------------------------------------------------------------
+# shards
+# ---------------------------------------------------------------------------
+def build_shards(*, jsonl_paths: Sequence[Path], sp_model_path: Path, out_dir: Path, val_docs: int = 50_000,
+                 shard_tokens: int = 100_000_000, max_docs: Optional[int] = None) -> dict:
+    """The first ``val_docs`` documents become validation shards, the rest
+    training shards; tokens are uint16 and a vocabulary above 65 536 is refused."""
+    import sentencepiece as spm
+    sp = spm.SentencePieceProcessor(model_file=str(sp_model_path))
+    if sp.vocab_size() > 65536:
+        raise ValueError(f"vocabulary {sp.vocab_size()} does not fit uint16 shards")
+    out_dir = Path(out_dir)
+    out_dir.mkdir(parents=True, exist_ok=True)
+    state = {"train": {"buf": [], "n": 0, "idx": 0, "tokens": 0, "docs": 0},
+             "val": {"buf": [], "n": 0, "idx": 0, "tokens": 0, "docs": 0}}
+
+    def flush(split: str) -> None:
+        s = state[split]
+        if not s["buf"]:
+            return
+        arr = np.concatenate(s["buf"]).astype("<u2")
+        arr.tofile(out_dir / f"fineweb_{split}_{s['idx']:03d}.bin")
+        s["buf"], s["n"], s["idx"] = [], 0, s["idx"] + 1
+
+    seen = 0
+    for path in jsonl_paths:
+        with open(path, "r", encoding="utf-8") as fh:
+            for line in fh:
+                line = line.strip()
+                if not line:
+                    continue
+                try:
+                    text = json.loads(line).get("text", "")
+                except json.JSONDecodeError:
+                    continue
+                if not text:
+                    continue
+                if max_docs is not None and seen >= max_docs:
+                    break
+                split = "val" if seen < val_docs else "train"
+                seen += 1
+                ids = np.asarray(sp.encode(text, out_type=int), dtype=np.uint16)
+                s = state[split]
+                s["buf"].append(ids)
+                s["n"] += ids.size
+                s["tokens"] += int(ids.size)
+                s["docs"] += 1
+                if s["n"] >= shard_tokens:
+                    flush(split)
+    flush("train")
+    flush("val")
+    manifest = {"vocab_size": int(sp.vocab_size()), "append_eos": False, "dtype": "uint16-le", "header_bytes": 0,
+                **{f"{k}_{f}": state[k][f] for k in state for f in ("tokens", "docs")},
+                "train_shards": state["train"]["idx"], "val_shards": state["val"]["idx"]}
+    (out_dir / "shards_manifest.json").write_text(json.dumps(manifest, indent=2))
+    return manifest
+
+
+# ---------------------------------------------------------------------------
+# validation cache
+# ---------------------------------------------------------------------------
+def verify_val_cache(*, val_shard: Path, val_cache_dir: Path, expected_tokens: Optional[int] = None,
+                     chunk_tokens: int = 1 << 22) -> dict:
+    """Token-for-token comparison of a flat validation shard with a cache's
+    ``tokens.npy``, streamed in chunks; reports the first mismatch."""
+    from .eval_stream.io import load_val_cache
+    cache = load_val_cache(Path(val_cache_dir))
+    shard = np.memmap(val_shard, dtype="<u2", mode="r")
+    toks = np.asarray(cache.tokens)
+    n = min(shard.size, toks.size)
+    first = None
+    for s in range(0, n, int(chunk_tokens)):
+        a, b = shard[s: s + chunk_tokens], toks[s: s + chunk_tokens]
+        neq = np.nonzero(a[: b.size] != b[: a.size])[0]
+        if neq.size:
+            i = s + int(neq[0])
+            first = {"index": i, "shard": int(shard[i]), "cache": int(toks[i])}
+            break
+    doc_sum = int(np.asarray(cache.docs["token_len"]).sum())
+    out = {"shard_tokens": int(shard.size), "cache_tokens": int(toks.size), "doc_token_sum": doc_sum,
+           "docs": int(len(cache.docs)), "first_mismatch": first,
+           "ok": first is None and shard.size == toks.size == doc_sum and
+           (expected_tokens is None or int(expected_tokens) == int(toks.size))}
+    if expected_tokens is not None:
+        out["expected_tokens"] = int(expected_tokens)
+    return out
+
+
+# ---------------------------------------------------------------------------
+# quantisation round trip
+# ---------------------------------------------------------------------------
+def _score(model, cache, *, chunk_size: int, max_docs: Optional[int], device: torch.device) -> dict:
+    from .scoring import score_val_cache
+    model.eval()
+    with torch.no_grad():
+        return score_val_cache(model, cache, chunk_size=chunk_size, max_docs=max_docs, device=device)
+
+
+def eval_quant(*, ckpt: Path, val_cache_dir: Path, output_json: Path, device: str = "auto", chunk_size: int = 512,
+               max_docs: Optional[int] = None, calibration_seqs: int = 16, calibration_seq_len: int = 128,
+               seed: int = 0) -> dict:
+    """Score the validation cache with the checkpoint as trained, quantise
+    (self-generated calibration text -> Hessians -> GPTQ int6 -> LZMA), write the
+    blob beside the JSON, load it back into a fresh model, score the same
+    documents again, and report both bits-per-byte figures and the artifact size
+    against the 16 MiB limit."""
+    from .eval_stream.io import load_val_cache
+    from .quantization.gptq import GPTQQuantizer, ar_self_generated_calibration
+    from .quantization.packaging import pack_int6_lzma, unpack_int6_lzma
+    from .runner_exp21 import build_model
+    torch.manual_seed(seed)
+    dev = torch.device("cuda" if (device == "auto" and torch.cuda.is_available()) else
+                       ("cpu" if device == "auto" else device))
+    blob = torch.load(ckpt, map_location="cpu", weights_only=False)
+    cfg = dict(blob["config"])
+    dtype = torch.bfloat16 if dev.type == "cuda" else torch.float32
+    model = build_model(cfg, dev, dtype)
+    model.load_state_dict(blob["model"], strict=True)
+    cache = load_val_cache(Path(val_cache_dir))
+    t0 = time.perf_counter()
+    before = _score(model, cache, chunk_size=chunk_size, max_docs=max_docs, device=dev)
+    seqs = ar_self_generated_calibration(model, num_seqs=calibration_seqs, seq_len=calibration_seq_len,
+                                         vocab_size=int(cfg["vocab_size"]), seed=seed, device=dev)
+    q = GPTQQuantizer()
+    q.calibrate(model, seqs, device=dev)
+    quantized, meta = q.quantize_state_dict({k: v for k, v in model.state_dict().items() if torch.is_tensor(v)})
+    packed = pack_int6_lzma(quantized, meta)
+    output_json = Path(output_json)
+    output_json.parent.mkdir(parents=True, exist_ok=True)
+    blob_path = output_json.with_suffix(output_json.suffix + ".int6.ptz.lzma")
+    blob_path.write_bytes(packed)
+    del model
+    result, meta2 = unpack_int6_lzma(packed)
+    restored = build_model(cfg, dev, dtype)
+    sd = GPTQQuantizer.dequantize_state_dict(result, meta2)
+    missing = restored.load_state_dict({k: v.to(dtype) if v.is_floating_point() else v for k, v in sd.items()},
+                                       strict=False)
+    after = _score(restored, cache, chunk_size=chunk_size, max_docs=max_docs, device=dev)
+    out = {"ckpt": str(ckpt), "bpb_bf16": before["bpb"], "bpb_int6": after["bpb"],
+           "delta_bpb": after["bpb"] - before["bpb"], "artifact_bytes": len(packed),
+           "artifact_margin_mb": (ARTIFACT_LIMIT_BYTES - len(packed)) / 2 ** 20,
+           "docs_scored": before["docs_scored"], "tokens_scored": before["tokens_scored"],
+           "int6_tensors": sum(1 for m in meta.values() if m["type"] == "int6"),
+           "missing_keys": list(missing.missing_keys), "unexpected_keys": list(missing.unexpected_keys),
+           "blob_path": str(blob_path), "elapsed_s": time.perf_counter() - t0,
+           "pass_bf16": before, "pass_int6": after}
+    output_json.write_text(json.dumps(out, indent=2, default=str))
+    return out
+
+
+# ---------------------------------------------------------------------------
+def main(argv: Optional[Sequence[str]] = None) -> int:
+    ap = argparse.ArgumentParser(prog="chaoscontrol_b200.cli")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    s = sub.add_parser("build-shards")
+    s.add_argument("--jsonl-path", type=Path, nargs="+", required=True)
+    s.add_argument("--sp-model-path", type=Path, required=True)
+    s.add_argument("--out-dir", type=Path, required=True)
+    s.add_argument("--val-docs", type=int, default=50_000)
+    s.add_argument("--shard-tokens", type=int, default=100_000_000)
+    s.add_argument("--max-docs", type=int, default=None)
+    c = sub.add_parser("build-val-cache")
+    c.add_argument("--jsonl-path", type=Path, nargs="+", required=True)
+    c.add_argument("--sp-model-path", type=Path, required=True)
+    c.add_argument("--cache-dir", type=Path, required=True)
+    c.add_argument("--max-docs", type=int, default=50_000)
+    c.add_argument("--force", action="store_true")
+    v = sub.add_parser("verify-val-cache")
+    v.add_argument("--val-shard", type=Path, required=True)
+    v.add_argument("--val-cache-dir", type=Path, required=True)
+    v.add_argument("--expected-tokens", type=int, default=None)
+    v.add_argument("--chunk-tokens", type=int, default=1 << 22)
+    e = sub.add_parser("eval-quant")
+    e.add_argument("--ckpt", type=Path, required=True)
+    e.add_argument("--val-cache-dir", type=Path, required=True)
+    e.add_argument("--output-json", type=Path, required=True)
+    e.add_argument("--device", default="auto")
+    e.add_argument("--chunk-size", type=int, default=512)
+    e.add_argument("--max-docs", type=int, default=None)
+    e.add_argument("--calibration-seqs", type=int, default=16)
+    e.add_argument("--calibration-seq-len", type=int, default=128)
+    e.add_argument("--seed", type=int, default=0)
+    a = ap.parse_args(argv)
+    if a.cmd == "build-shards":
+        out = build_shards(jsonl_paths=a.jsonl_path, sp_model_path=a.sp_model_path, out_dir=a.out_dir,
+                           val_docs=a.val_docs, shard_tokens=a.shard_tokens, max_docs=a.max_docs)
+    elif a.cmd == "build-val-cache":
+        from .eval_stream.io import write_val_cache
+        out = write_val_cache(jsonl_paths=a.jsonl_path, sp_model_path=a.sp_model_path, cache_dir=a.cache_dir,
+                              max_docs=a.max_docs, force=a.force)
+    elif a.cmd == "verify-val-cache":
+        out = verify_val_cache(val_shard=a.val_shard, val_cache_dir=a.val_cache_dir,
+                               expected_tokens=a.expected_tokens, chunk_tokens=a.chunk_tokens)
+        print(json.dumps(out, indent=2))
+        return 0 if out["ok"] else 1
+    else:
+        out = eval_quant(ckpt=a.ckpt, val_cache_dir=a.val_cache_dir, output_json=a.output_json, device=a.device,
+                         chunk_size=a.chunk_size, max_docs=a.max_docs, calibration_seqs=a.calibration_seqs,
+                         calibration_seq_len=a.calibration_seq_len, seed=a.seed)
+        out = {k: v for k, v in out.items() if not k.startswith("pass_")}
+    print(json.dumps(out, indent=2, default=str))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -15,6 +15,14 @@
 //               a bf16 tile in shared memory and accumulates dX += g . W' in a
 //               TMEM accumulator that lives across the sweep; the final
 //               epilogue applies the RMSNorm backward and writes dX.
+//   MODE_TRAIN1 MODE_TRAIN in ONE sweep (no separate lse pass): the unit's first
+//               32 logits fix a per-row reference m (log2 domain, plus a margin
+//               of 60 so later, larger logits cannot overflow); every tile adds
+//               p~ = 2^(z - m) to the row sum S and stores p~ (bf16) as the g
+//               tile, so the TMEM accumulator holds sum_v p~ W'.  The final
+//               epilogue forms q = (acc / S - W'[target]) * gscale * rs, then the
+//               RMSNorm backward as before; lse = m + log2 S.  Saves one of the
+//               five logits-sized GEMMs of a training step.
 //   MODE_DW     CTA owns a 128-row tile of W' (kept in shared memory) and a
 //               chunk of rows; recomputes logits tiles against streamed X
 //               tiles, forms the same g tile and accumulates dW' += g^T . X in
@@ -53,7 +61,8 @@ constexpr int LH_SMEM = LH_OFF_BAR + 256;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 
-enum { MODE_LSE = 0, MODE_TRAIN = 1, MODE_DW = 2 };
+enum { MODE_LSE = 0, MODE_TRAIN = 1, MODE_DW = 2, MODE_TRAIN1 = 3 };
+constexpr float LH_REF_MARGIN = 60.f;   // log2 units between the first-logits max and the reference
 
 struct LmHeadArgs {
   int R, V;
@@ -70,6 +79,7 @@ struct LmHeadArgs {
   int skip_lse;             // TRAIN: lse[] is an input, run only the gradient sweep
   const __nv_bfloat16* X;   // [R, 256] for the final epilogue of TRAIN
   __nv_bfloat16* dX;        // [R, 256] out (TRAIN)
+  const __nv_bfloat16* W;   // [V, 256] folded head weight (TRAIN1: target rows are gathered)
   float* dWpart;            // [row_chunks, V, 256] out (DW)
   int* status;
 };
@@ -137,6 +147,8 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
   // LSE / TRAIN: unit = m-tile; inner = v-tiles (x sweeps).
   // DW: unit = (v-tile, row chunk); inner = m-tiles of the chunk.
   const int n_units = (MODE == MODE_DW) ? p.n_vtiles * p.row_chunks : p.n_mtiles;
+  constexpr bool IS_TRAIN = (MODE == MODE_TRAIN) || (MODE == MODE_TRAIN1);
+  constexpr bool FUSED1 = (MODE == MODE_TRAIN1);
   const int n_sweeps = (MODE == MODE_TRAIN && !p.skip_lse) ? 2 : 1;
 
   if (warp == 0) {
@@ -238,7 +250,7 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         res_phase ^= 1u;
         tc_fence_after_sync();
         for (int sw = 0; sw < n_sweeps && ok; ++sw) {
-          const bool second = (MODE == MODE_DW) || (MODE == MODE_TRAIN && sw == n_sweeps - 1);
+          const bool second = (MODE == MODE_DW) || (IS_TRAIN && sw == n_sweeps - 1);
           int prev_stage = -1;
           bool prev_first = true;
           for (int it = inner0; it < inner1; ++it) {
@@ -332,9 +344,10 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         if (need_lse) c2 = row_ok ? p.lse[r] * LOG2E : 0.f;
       };
       if (MODE != MODE_DW) load_row(unit, MODE == MODE_TRAIN && p.skip_lse);
+      float inv_s = 0.f;                   // TRAIN1: 1 / row sum, known after the sweep
 
       for (int sw = 0; sw < n_sweeps && ok; ++sw) {
-        const bool second = (MODE == MODE_DW) || (MODE == MODE_TRAIN && sw == n_sweeps - 1);
+        const bool second = (MODE == MODE_DW) || (IS_TRAIN && sw == n_sweeps - 1);
         float run_m = -INFINITY, run_s = 0.f, run_e = 0.f, tacc = 0.f, zt = 0.f;
         for (int it = inner0; it < inner1 && ok; ++it) {
           const int b = n_d1 & 1;
@@ -391,6 +404,18 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             if (MODE == MODE_DW) {
               if (!wait_all(&bars->g_empty[q >> 1], gph ^ 1u)) { ok = false; break; }
             }
+            if (FUSED1 && it == inner0) {
+              // per-row reference: max of the unit's first 32 logits (every warp reads the same
+              // 32 columns, so the two column halves of a row agree without an exchange)
+              uint32_t a0[32];
+              __syncwarp();
+              tmem_ld32(t_addr, a0);
+              tmem_ld_wait();
+              float mx = __uint_as_float(a0[0]);
+#pragma unroll
+              for (int i = 1; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(a0[i]));
+              c2 = fmaf(mx, c1, LH_REF_MARGIN);
+            }
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
               const int col0 = h * 64 + part * 32;
@@ -402,12 +427,20 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
               uint32_t packed[16];
 #pragma unroll
               for (int i = 0; i < 32; i += 2) {
-                const float z0 = fmaf(__uint_as_float(a[i]), c1, -c2);
-                const float z1 = fmaf(__uint_as_float(a[i + 1]), c1, -c2);
+                float z0 = fmaf(__uint_as_float(a[i]), c1, -c2);
+                float z1 = fmaf(__uint_as_float(a[i + 1]), c1, -c2);
+                if (FUSED1) { z0 = fminf(z0, 126.f); z1 = fminf(z1, 126.f); }
                 float p0 = ex2f(z0), p1 = ex2f(z1);
-                if (i == tl) { p0 -= 1.f; zt = z0; }
-                if (i + 1 == tl) { p1 -= 1.f; zt = z1; }
-                packed[i >> 1] = pack_bf16x2(p0 * gs, p1 * gs);
+                if (FUSED1) {
+                  if (i == tl) zt = z0;
+                  if (i + 1 == tl) zt = z1;
+                  run_s += p0 + p1;
+                  packed[i >> 1] = pack_bf16x2(p0, p1);
+                } else {
+                  if (i == tl) { p0 -= 1.f; zt = z0; }
+                  if (i + 1 == tl) { p1 -= 1.f; zt = z1; }
+                  packed[i >> 1] = pack_bf16x2(p0 * gs, p1 * gs);
+                }
               }
               if (MODE != MODE_DW) {
                 if (!wait_all(&bars->g_empty[h], gph ^ 1u)) { ok = false; break; }
@@ -467,6 +500,19 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
               if (row_ok && part == 0) p.entropy[r] = lse2 * LN2 - rs * e_tot / s;
             }
           }
+        } else if (FUSED1) {
+          // combine the two column halves: S = sum p~, target logit relative to the reference
+          if (!epi_sync()) { ok = false; break; }
+          xchg[part * 128 + row_in_tile] = make_float2(zt, run_s);
+          if (!epi_sync()) { ok = false; break; }
+          const float2 o = xchg[(part ^ 1) * 128 + row_in_tile];
+          const float S = run_s + o.y;
+          const float lg = __log2f(S);
+          inv_s = 1.f / S;
+          if (row_ok && part == 0) {
+            p.lse[r] = (c2 + lg) * LN2;
+            p.loss[r] = (lg - (zt + o.x)) * LN2;
+          }
         } else if (MODE == MODE_TRAIN) {
           // per-row CE = -log p_target = -zt * ln2 (zt captured by one of the two warps)
           if (!epi_sync()) { ok = false; break; }
@@ -484,9 +530,28 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
           if (!wait_all(&bars->d2_full, n_d2 & 1u)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t t2 = tmem_base + 256 + lane_addr;
-          if (MODE == MODE_TRAIN) {
+          if (IS_TRAIN) {
             // dx = q - x * (rs^2 / D) * sum_d q * x   (RMSNorm backward, weight folded)
             const __nv_bfloat16* xrow = p.X + (long long)r * LH_D;
+            // TRAIN1: the accumulator holds sum_v p~ W'; q = (acc / S - W'[target]) * gs
+            const __nv_bfloat16* wrow = p.W + (long long)(row_ok ? tgt : 0) * LH_D;
+            auto finish_q = [&](uint32_t (&a)[32], int c) {
+              if (FUSED1) {
+                const uint4* w4 = reinterpret_cast<const uint4*>(wrow + c * 32);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const uint4 wv = __ldg(w4 + j);
+                  const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const float2 f = unpack_bf16x2(ww[e]);
+                    a[j * 8 + 2 * e] = __float_as_uint((__uint_as_float(a[j * 8 + 2 * e]) * inv_s - f.x) * gs);
+                    a[j * 8 + 2 * e + 1] =
+                        __float_as_uint((__uint_as_float(a[j * 8 + 2 * e + 1]) * inv_s - f.y) * gs);
+                  }
+                }
+              }
+            };
             float dot = 0.f;
             for (int c = 0; c < 8; ++c) {
               uint32_t a[32];
@@ -494,6 +559,7 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
               tmem_ld32(t2 + c * 32, a);
               tmem_ld_wait();
               if (row_ok) {
+                finish_q(a, c);
                 const uint4* x4 = reinterpret_cast<const uint4*>(xrow + c * 32);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -513,6 +579,7 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
               tmem_ld32(t2 + c * 32, a);
               tmem_ld_wait();
               if (row_ok) {
+                finish_q(a, c);
                 const uint4* x4 = reinterpret_cast<const uint4*>(xrow + c * 32);
                 uint4* o4 = reinterpret_cast<uint4*>(p.dX + (long long)r * LH_D + c * 32);
 #pragma unroll
@@ -624,7 +691,8 @@ extern "C" int ccb_lmhead_lse(const void* X, const void* W, const float* rowss, 
 }
 
 // lse, per-row loss and dX (gradient w.r.t. the un-normalised hidden state).
-// With lse_is_input the lse sweep is skipped and lse[] is read instead.
+// lse_is_input: 0 = two sweeps (lse, then gradient); 1 = lse[] is read, gradient sweep only;
+// 2 = one sweep with a fixed per-row reference (MODE_TRAIN1), lse[] is written.
 extern "C" int ccb_lmhead_train(const void* X, const void* W, const float* rowss, float eps,
                                 const int64_t* targets, const float* rowweight, float gscale,
                                 float* lse, int64_t lse_is_input, float* loss, void* dX, int64_t R,
@@ -635,10 +703,12 @@ extern "C" int ccb_lmhead_train(const void* X, const void* W, const float* rowss
   a.rowweight = rowweight;
   a.gscale = gscale;
   a.lse = lse;
-  a.skip_lse = lse_is_input ? 1 : 0;
+  a.skip_lse = lse_is_input == 1 ? 1 : 0;
   a.loss = loss;
   a.X = (const __nv_bfloat16*)X;
   a.dX = (__nv_bfloat16*)dX;
+  a.W = (const __nv_bfloat16*)W;
+  if (lse_is_input == 2) return launch_lmhead<MODE_TRAIN1>(X, W, a, (cudaStream_t)stream);
   return launch_lmhead<MODE_TRAIN>(X, W, a, (cudaStream_t)stream);
 }
 

@@ -175,12 +175,25 @@ def default_row_chunks(R: int, V: int) -> int:
     return best
 
 
+ONE_SWEEP = True      # module switch: lse + dX in one vocabulary sweep (see lm_head_train)
+
+
 def lm_head_train(x, rowss, W_f, targets, *, gscale: float, rowweight=None, eps: float = EPS,
-                  row_chunks: Optional[int] = None, lse: Optional[torch.Tensor] = None):
+                  row_chunks: Optional[int] = None, lse: Optional[torch.Tensor] = None,
+                  one_sweep: Optional[bool] = None):
     """Loss and both gradients.  Returns ``(loss_rows, lse, dX bf16, dW_f_partials fp32 [C,V,D])``.
 
     ``dX`` is the gradient w.r.t. the un-normalised hidden state (RMSNorm
     backward applied); the partials sum to the gradient w.r.t. ``W_f``.
+
+    ``one_sweep`` (default: the module switch ``ONE_SWEEP``) computes lse and
+    ``dX`` in a single pass over the vocabulary: the softmax numerators are
+    taken against a fixed per-row reference (the maximum of the row's first 32
+    logits plus a 60-bit margin) instead of the true maximum, so no first pass
+    is needed and nothing is ever rescaled; the row sum normalises the
+    accumulated ``sum p W`` at the end.  Four logits-sized GEMMs per step
+    instead of five.  Logits more than ~130 nats above that reference would
+    saturate (clamped, never inf); more than ~46 nats below it flush to zero.
     """
     R, D = x.shape
     V = W_f.shape[0]
@@ -199,7 +212,8 @@ def lm_head_train(x, rowss, W_f, targets, *, gscale: float, rowweight=None, eps:
     dX = torch.empty_like(x)
     L = _lib.lib()
     _lib.check(L.ccb_lmhead_train(x.data_ptr(), W_f.data_ptr(), _lib.ptr(rowss), eps, t.data_ptr(),
-                                  _lib.ptr(rowweight), gscale, lse.data_ptr(), int(lse_given),
+                                  _lib.ptr(rowweight), gscale, lse.data_ptr(),
+                                  1 if lse_given else (2 if (ONE_SWEEP if one_sweep is None else one_sweep) else 0),
                                   loss.data_ptr(), dX.data_ptr(), R, V, D, _lib.stream_ptr()),
                "lmhead_train")
     C = row_chunks or default_row_chunks(R, V)

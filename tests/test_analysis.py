@@ -1,0 +1,59 @@
+"""Result analysis: loading, per-arm summaries, seed-paired comparisons, verdicts, scaling fit."""
+import json
+import math
+
+import pytest
+
+from chaoscontrol_b200 import analysis as A
+
+
+def _res(name, seed, arm, bpb, tok, loss=2.0, vram=1000.0, params=1000):
+    return {"config": {"name": name, "seed": seed, "arm": arm}, "params": params,
+            "train": {"aggregate_tokens_per_sec": tok, "steps": 10, "final_loss": loss, "peak_vram_mb": vram},
+            "eval": {"bpb": bpb, "loss": 1.0}}
+
+
+def test_load_summarize_compare_and_verdict(tmp_path, capsys):
+    runs = []
+    for s in range(5):
+        runs.append(_res(f"ctl_s{s}", s, "control", 1.50 + 0.01 * s, 1000 + 5 * s))
+        runs.append(_res(f"fast_s{s}", s, "fast", 1.47 + 0.01 * s, 1100 + 5 * s + (s % 2)))
+        runs.append(_res(f"leaky_s{s}", s, "leaky", 1.50 + 0.01 * s, 1100 + 5 * s + (s % 2), vram=1200.0))
+    for i, r in enumerate(runs):
+        (tmp_path / f"r{i}.json").write_text(json.dumps(r))
+    (tmp_path / "err.json").write_text(json.dumps({"error": "boom", "config": {"name": "x_s0", "seed": 0}}))
+    (tmp_path / "junk.json").write_text("{not json")
+    rows = A.load_results([tmp_path])
+    assert len(rows) == 16 and sum(1 for r in rows if r["error"]) == 1
+    table = A.summary_table(rows, "bpb")
+    assert [t["arm"] for t in table][0] == "fast" and table[0]["n"] == 5
+    assert abs(table[0]["std"] - math.sqrt(sum((0.01 * (s - 2)) ** 2 for s in range(5)) / 4)) < 1e-9
+    cmp_ = {c["arm"]: c for c in A.paired_comparison(rows, control="control", metric="bpb")}
+    assert abs(cmp_["fast"]["mean_delta"] + 0.03) < 1e-9 and cmp_["fast"]["fraction_beating_control"] == 1.0
+    assert cmp_["fast"]["p"] == 0.0 and cmp_["leaky"]["fraction_beating_control"] == 0.0
+    assert A.lever_verdict(rows, on="fast", off="control")["verdict"] == "SHIP"
+    assert A.lever_verdict(rows, on="leaky", off="control")["verdict"] == "PARK"          # +20 % memory
+    assert A.lever_verdict(rows, on="control", off="fast")["verdict"] == "PARK"          # slower
+    assert A.main(["summarize", str(tmp_path)]) == 0 and "fast" in capsys.readouterr().out
+    assert A.main(["compare", str(tmp_path), "--control", "control"]) == 0
+    with pytest.raises(KeyError):
+        A.paired_comparison(rows, control="nope")
+
+
+def test_paired_ttest_matches_known_values():
+    # hand-checked against the closed form: d = [1,2,3,4], mean 2.5, sd 1.2910, t = 3.873, df = 3, p = 0.03047
+    t, p = A.paired_ttest([2, 4, 6, 8], [1, 2, 3, 4])
+    assert abs(t - 3.8729833) < 1e-6 and abs(p - 0.030466) < 1e-5
+    t, p = A.paired_ttest([1, 2, 3], [1, 2, 3])
+    assert t == 0.0 and p == 1.0
+    assert all(math.isnan(v) for v in A.paired_ttest([1.0], [2.0]))
+
+
+def test_power_law_fit_recovers_its_parameters():
+    A0, alpha, irr = 30.0, 0.25, 0.9
+    params = [1e5, 3e5, 1e6, 3e6, 1e7]
+    bpbs = [A0 * n ** -alpha + irr for n in params]
+    fit = A.fit_power_law(params, bpbs)
+    assert abs(fit["alpha"] - alpha) < 0.02 and abs(fit["bpb_irr"] - irr) < 0.02 and fit["r2"] > 0.999
+    with pytest.raises(ValueError):
+        A.fit_power_law([1, 2], [1.0, 0.9])

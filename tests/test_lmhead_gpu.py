@@ -92,3 +92,32 @@ def test_lmhead_general_dims(R, V, D, norm):
     again = LH.lm_head_train(x, rowss, W, t, gscale=gscale, rowweight=w)
     for u, v in zip((loss2, lse2, dX, part), again):
         assert torch.equal(u, v)
+
+
+@pytest.mark.parametrize("wscale,peak", [(0.08, 0.0), (1.5, 0.0), (0.3, 40.0)])
+def test_lmhead_one_sweep_matches_two_sweeps_and_the_reference(wscale, peak):
+    """The single-sweep training kernel (fixed per-row reference instead of the true row maximum)
+    against the two-sweep kernel and the fp32 statement: ordinary logits, logits spread over tens of
+    nats, and a target column that towers over the row's first 32 logits."""
+    R, V = 1024, 4096
+    x, W, t, ss = _mk(R, V, seed=3, wscale=wscale)
+    if peak:
+        # make each row's target logit ~`peak` nats larger than the rest: align W[t] with x
+        xn = torch.nn.functional.normalize(x.float(), dim=-1)
+        Wf = W.float()
+        Wf[t] = Wf[t] + xn * (peak / 16.0)
+        W = Wf.bfloat16()
+    w = torch.rand(R, device="cuda") + 0.5
+    kw = dict(gscale=1.0 / R, rowweight=w, row_chunks=2)
+    l1, lse1, dX1, p1 = LH.lm_head_train(x, ss, W, t, one_sweep=True, **kw)
+    l2, lse2, dX2, p2 = LH.lm_head_train(x, ss, W, t, one_sweep=False, **kw)
+    _lib.assert_ok()
+    rl, rlse, rdX, rdW = LH.lm_head_reference(x, ss, W, t, gscale=1.0 / R, rowweight=w)
+    assert torch.isfinite(dX1.float()).all() and torch.isfinite(lse1).all()
+    assert torch.allclose(lse1, rlse, rtol=1e-3, atol=3e-2), (lse1 - rlse).abs().max()
+    assert torch.allclose(l1, rl, rtol=2e-3, atol=5e-2), (l1 - rl).abs().max()
+
+    def rel(a, b):
+        return float((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-12))
+    assert rel(dX1, rdX) < 2e-2 and rel(dX1, dX2) < 2e-2, (rel(dX1, rdX), rel(dX1, dX2))
+    assert rel(p1.sum(0), rdW) < 2e-2 and rel(p1.sum(0), p2.sum(0)) < 1e-2

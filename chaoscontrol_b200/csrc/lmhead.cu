@@ -432,8 +432,6 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                 if (FUSED1) { z0 = fminf(z0, 126.f); z1 = fminf(z1, 126.f); }
                 float p0 = ex2f(z0), p1 = ex2f(z1);
                 if (FUSED1) {
-                  if (i == tl) zt = z0;
-                  if (i + 1 == tl) zt = z1;
                   run_s += p0 + p1;
                   packed[i >> 1] = pack_bf16x2(p0, p1);
                 } else {
@@ -441,6 +439,13 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                   if (i + 1 == tl) { p1 -= 1.f; zt = z1; }
                   packed[i >> 1] = pack_bf16x2(p0 * gs, p1 * gs);
                 }
+              }
+              if (FUSED1 && (unsigned)tl < 32u) {
+                // the target's logit (relative to the reference): looked up outside the hot loop,
+                // a lane meets its target column once per vocabulary sweep
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  if (i == tl) zt = fminf(fmaf(__uint_as_float(a[i]), c1, -c2), 126.f);
               }
               if (MODE != MODE_DW) {
                 if (!wait_all(&bars->g_empty[h], gph ^ 1u)) { ok = false; break; }

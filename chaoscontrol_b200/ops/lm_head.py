@@ -128,11 +128,21 @@ def _prep(x, rowss, W_f, targets):
     return t.contiguous()
 
 
+SMALL_R_TILES = 32     # below this many 128-row tiles the vocabulary-parallel GEMM-epilogue head is used
+
+
+def _few_rows(R: int) -> bool:
+    """The single-kernel head gives one CTA a 128-row tile and the whole vocabulary: with few
+    rows (per-document evaluation, test-time training) that leaves most SMs idle, while the
+    GEMM-epilogue head tiles the vocabulary across CTAs."""
+    return (R + 127) // 128 < SMALL_R_TILES
+
+
 def lm_head_lse(x, rowss, W_f, targets, *, eps: float = EPS, want_entropy: bool = False):
     """Forward only: ``(loss_rows, lse)`` fp32 ``[R]`` (plus the softmax entropy
     when asked); no logits in memory."""
     R, D = x.shape
-    if not fused_supported(x, W_f) and general_supported(x, W_f) and not want_entropy:
+    if (not fused_supported(x, W_f) or _few_rows(R)) and general_supported(x, W_f) and not want_entropy:
         return _lse_general(x, rowss, W_f, _prep(x, rowss, W_f, targets), eps)
     if not fused_supported(x, W_f):
         lr, lse, _, _ = lm_head_reference(x, rowss, W_f, targets, eps=eps, want_grads=False)
@@ -197,7 +207,7 @@ def lm_head_train(x, rowss, W_f, targets, *, gscale: float, rowweight=None, eps:
     """
     R, D = x.shape
     V = W_f.shape[0]
-    if not fused_supported(x, W_f) and general_supported(x, W_f):
+    if (not fused_supported(x, W_f) or (_few_rows(R) and one_sweep is None)) and general_supported(x, W_f):
         return _train_general(x, rowss, W_f, _prep(x, rowss, W_f, targets), gscale, rowweight, eps, lse)
     if not fused_supported(x, W_f):
         lr, lse, dX, dW = lm_head_reference(x, rowss, W_f, targets, gscale=gscale,

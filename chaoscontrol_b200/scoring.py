@@ -304,11 +304,14 @@ class GraphTTTRunner:
         self.tok = torch.zeros(1, self.C + 1, dtype=torch.long, device=dev)
         self.state = [torch.zeros(1, model.dim, device=dev, dtype=model.embed.weight.dtype) for _ in model.layers]
         self.ce_acc = torch.zeros((), dtype=torch.float32, device=dev)
+        self.n_valid = torch.full((), self.C, dtype=torch.long, device=dev)     # targets that count in this chunk
+        self._pos = torch.arange(self.C, device=dev).view(1, -1)
+        self._one = torch.ones((), dtype=torch.float32, device=dev)
         self._frozen = [p for p in model.parameters() if p.requires_grad and all(p is not q for q in self.params)]
         for p in self._frozen:
             p.requires_grad_(False)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
-        self.replays = self.eager_chunks = 0
+        self.replays = self.padded_chunks = 0
         # warm up off the capture stream (allocator, kernel attributes), then capture
         snap = [p.detach().clone() for p in self.params]
         side = torch.cuda.Stream(device=dev)
@@ -330,16 +333,18 @@ class GraphTTTRunner:
         self.start_doc()
 
     def _body(self, tok: torch.Tensor) -> None:
-        from .kernels.lm_head_loss import fused_linear_cross_entropy, fused_rms_norm
+        from .kernels.lm_head_loss import fused_linear_cross_entropy_weighted, fused_rms_norm
         m = self.model
         inp, tgt = tok[:, :-1].to(torch.int32), tok[:, 1:]
+        mask = (self._pos < self.n_valid).float()             # a document's ragged tail is padded, not re-traced
         with torch.no_grad():
             rows, finals = _chunk_loss_rows(m, inp, tgt, self.state)
-            self.ce_acc += rows.float().sum()
+            self.ce_acc += (rows.float() * mask).sum()
         if self.params:
             hidden = m.encode(inp, initial_states=self.state)
-            loss = fused_linear_cross_entropy(fused_rms_norm(hidden, m.final_norm.weight, eps=m.final_norm.eps),
-                                              m.lm_head.weight, tgt, reduction="sum")
+            loss, _ = fused_linear_cross_entropy_weighted(
+                fused_rms_norm(hidden, m.final_norm.weight, eps=m.final_norm.eps), m.lm_head.weight, tgt,
+                mask.reshape(-1), normalizer=self._one)
             loss.backward()
             with torch.no_grad():
                 torch._foreach_add_(self.params, [p.grad for p in self.params], alpha=-self.lr)
@@ -348,28 +353,31 @@ class GraphTTTRunner:
                 s.copy_(f)
 
     def start_doc(self) -> None:
-        for s in self.state:
-            s.zero_()
-        self.ce_acc.zero_()
+        torch._foreach_zero_(self.state + [self.ce_acc])
 
     def run_doc(self, doc_tokens: torch.Tensor) -> tuple[torch.Tensor, int]:
         """``doc_tokens``: ``[n]`` long on the device.  Returns ``(summed CE as a
-        device scalar, chunks)``; state and accumulator are reset first."""
+        device scalar, chunks)``; state and accumulator are reset first.  The last,
+        shorter chunk is zero-padded to the captured length and masked out of both
+        the score and the adaptation loss (its state is never used again)."""
         self.start_doc()
         n, C, chunks = int(doc_tokens.numel()), self.C, 0
         for s in range(0, n - 1, C):
             piece = doc_tokens[s: s + C + 1]
-            if piece.numel() < 2:
+            k = int(piece.numel())
+            if k < 2:
                 break
-            if piece.numel() == C + 1:
+            if k == C + 1:
                 self.tok.copy_(piece.view(1, -1))
-                self.graph.replay()
-                self.replays += 1
             else:
-                for p in self.params:
-                    p.grad = None
-                self._body(piece.view(1, -1))
-                self.eager_chunks += 1
+                self.tok.zero_()
+                self.tok[0, :k].copy_(piece)
+                self.n_valid.fill_(k - 1)
+                self.padded_chunks += 1
+            self.graph.replay()
+            if k != C + 1:
+                self.n_valid.fill_(C)
+            self.replays += 1
             chunks += 1
         return self.ce_acc.clone(), chunks
 
@@ -393,31 +401,47 @@ def run_ttt_eval_graph(model: nn.Module, docs, *, adapt_set: str = "log_a+delta_
     snap = [p.detach().clone() for p in params]
     t0 = time.perf_counter()
     ces, toks, byts, n_chunks, ids = [], [], [], 0, []
-    try:
-        for rec in docs:
-            if max_docs is not None and len(ces) >= max_docs:
+
+    def groups(it, n_tokens=1 << 20):
+        """Documents in groups of about a million tokens: one pinned upload per group."""
+        batch, count = [], 0
+        for rec in it:
+            if max_docs is not None and len(ces) + len(batch) >= max_docs:
                 break
             if len(rec.tokens) < 2:
                 continue
-            host = torch.as_tensor(rec.tokens, dtype=torch.long)
-            dev_toks = (host.pin_memory() if device.type == "cuda" else host).to(device, non_blocking=True)
-            ce, ch = runner.run_doc(dev_toks)
-            with torch.no_grad():
-                for p, s in zip(params, snap):
-                    p.copy_(s)
-            ces.append(ce)
-            toks.append(len(rec.tokens) - 1)
-            byts.append(rec.raw_bytes)
-            ids.append(rec.doc_id)
-            n_chunks += ch
-            if metrics is not None:
-                doc_ce = float(ce)
-                metrics.record_doc(doc_id=rec.doc_id, bpb=compute_bpb(doc_ce, rec.raw_bytes), tokens=toks[-1],
-                                   loss_before=doc_ce / max(toks[-1], 1), loss_after=None, step_count=n_chunks,
-                                   wall_ms=0.0, grad_norm=0.0, state_norm=0.0)
+            batch.append(rec)
+            count += len(rec.tokens)
+            if count >= n_tokens:
+                yield batch
+                batch, count = [], 0
+        if batch:
+            yield batch
+    try:
+        for batch in groups(docs):
+            flat = torch.as_tensor(np.concatenate([np.asarray(r.tokens, dtype=np.int64) for r in batch]))
+            flat = (flat.pin_memory() if device.type == "cuda" else flat).to(device, non_blocking=True)
+            off = 0
+            for rec in batch:
+                dev_toks = flat[off: off + len(rec.tokens)]
+                off += len(rec.tokens)
+                ce, ch = runner.run_doc(dev_toks)
+                if params:
+                    with torch.no_grad():
+                        torch._foreach_copy_(params, snap)
+                ces.append(ce)
+                toks.append(len(rec.tokens) - 1)
+                byts.append(rec.raw_bytes)
+                ids.append(rec.doc_id)
+                n_chunks += ch
+                if metrics is not None:
+                    doc_ce = float(ce)
+                    metrics.record_doc(doc_id=rec.doc_id, bpb=compute_bpb(doc_ce, rec.raw_bytes), tokens=toks[-1],
+                                       loss_before=doc_ce / max(toks[-1], 1), loss_after=None, step_count=n_chunks,
+                                       wall_ms=0.0, grad_norm=0.0, state_norm=0.0)
         ce_all = torch.stack(ces).double().cpu() if ces else torch.zeros(0, dtype=torch.float64)
     finally:
-        replays, eager = runner.replays, runner.eager_chunks
+        replays, eager = runner.replays, runner.padded_chunks
         runner.close()
         model.train(was_training)
     elapsed = time.perf_counter() - t0
@@ -426,5 +450,5 @@ def run_ttt_eval_graph(model: nn.Module, docs, *, adapt_set: str = "log_a+delta_
             "adapt_steps": n_chunks if params else 0, "elapsed_seconds": elapsed, "chunk_size": chunk_size,
             "total_ce_nats": tot_ce, "total_raw_bytes": tot_bytes, "bpb": compute_bpb(tot_ce, tot_bytes),
             "mean_ce": tot_ce / max(tot_tok, 1), "tokens_per_s": tot_tok / elapsed if elapsed > 0 else 0.0,
-            "adapt_set": adapt_set, "persistence_mode": "reset", "graph_replays": replays, "eager_chunks": eager,
+            "adapt_set": adapt_set, "persistence_mode": "reset", "graph_replays": replays, "padded_chunks": eager,
             "per_doc_ce": {int(i): float(c) for i, c in zip(ids, ce_all.tolist())}}

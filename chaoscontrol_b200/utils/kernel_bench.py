@@ -104,7 +104,8 @@ def build(kernel: str, R: int, D: int = 256, V: int = 16384, T: int = 512):
             fn = lambda: LH.lm_head_lse(x, ss, W, t)
             return fn, 2 * R * D + 2 * V * D, 2.0 * R * D * V
         fn = lambda: LH.lm_head_train(x, ss, W, t, gscale=1.0 / R)
-        return fn, 2 * 2 * R * D + 2 * V * D, 5 * 2.0 * R * D * V
+        # logits-sized GEMMs actually executed: one sweep = logits + dX, then logits + dW
+        return fn, 2 * 2 * R * D + 2 * V * D, (4 if LH.ONE_SWEEP else 5) * 2.0 * R * D * V
     raise SystemExit(f"unknown kernel {kernel}")
 
 

@@ -151,12 +151,15 @@ __device__ __forceinline__ float gemm_ex2(float x) {
 }
 
 // LM = 1 compiles the LM-head epilogues (LSE_PART, CE_GRAD) instead of the trunk set.
-template <int BN, int A_MN, int B_MN, int LM>
+// EPI_T >= 0 fixes the epilogue at compile time (the hot trunk epilogues: no dispatch, less
+// code, fewer live registers in the chunk loop); EPI_T = -1 reads it from the arguments.
+template <int BN, int A_MN, int B_MN, int LM, int EPI_T>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmC2,
             const GemmKArgs p) {
   using Cfg = GemmCfg<BN>;
+  const int epi_k = (EPI_T >= 0) ? EPI_T : p.epi;
   constexpr int STAGES = Cfg::STAGES;
   constexpr int B_STAGE_BYTES = Cfg::B_STAGE_BYTES;
 
@@ -323,7 +326,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
       // TMA-store path: 64-column groups staged in this warp's swizzled buffers
       uint8_t* my_stage = sStage + (warp - 2) * (STG_BUFS_PER_WARP * STG_BUF_BYTES);
-      const bool two_out = (p.epi == CCB_EPI_ROWSCALE_SILU);
+      const bool two_out = (epi_k == CCB_EPI_ROWSCALE_SILU);
       auto stage_write = [&](uint8_t* buf, int half, const float (&vals)[32]) {
         uint8_t* row = buf + lane * 128;
 #pragma unroll
@@ -342,7 +345,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       // before this tile's MMAs have even finished -- and the other warp of the
       // scheduler covers what latency is left.
       const __nv_bfloat16* aux1_row = nullptr;
-      if (p.epi == CCB_EPI_STORE) {
+      if (epi_k == CCB_EPI_STORE) {
         if (p.Cin != nullptr)
           aux1_row = reinterpret_cast<const __nv_bfloat16*>(p.Cin) + (long long)t.b * p.cin_batch +
                      (long long)m * p.ldcin;
@@ -350,9 +353,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         aux1_row = reinterpret_cast<const __nv_bfloat16*>(p.R1) + (long long)m * p.ldr;
       }
       const __nv_bfloat16* aux2_row =
-          (p.epi == CCB_EPI_RMSBWD && p.R2 != nullptr)
+          (epi_k == CCB_EPI_RMSBWD && p.R2 != nullptr)
               ? reinterpret_cast<const __nv_bfloat16*>(p.R2) + (long long)m * p.ldr : nullptr;
-      const int aux1_total = aux1_row ? nmine * (p.epi == CCB_EPI_RMSBWD ? 2 : 1) : 0;
+      const int aux1_total = aux1_row ? nmine * (epi_k == CCB_EPI_RMSBWD ? 2 : 1) : 0;
       const int aux2_total = aux2_row ? nmine : 0;
       auto aux_issue = [&](const __nv_bfloat16* rowp, int s_idx, int total, uint4 (&qv)[4]) {
         if (rowp == nullptr || !row_ok || s_idx >= total) return;
@@ -411,14 +414,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       if (LM && row_ok) {
         lm_c1 = rs * GEMM_LOG2E;
         lm_tgt = (int)p.targets[m];
-        if (p.epi == CCB_EPI_CE_GRAD) {
+        if (epi_k == CCB_EPI_CE_GRAD) {
           lm_c2 = p.lse[m] * GEMM_LOG2E;
           lm_gs = alpha * rs * (p.rowweight ? p.rowweight[m] : 1.f);
         }
       }
 
       float row_acc = 0.f;   // RESID_SS: sum of squares; RMSBWD: dot(acc, x)
-      if (!LM && p.epi == CCB_EPI_RMSBWD) {
+      if (!LM && epi_k == CCB_EPI_RMSBWD) {
         for (int k = 0; k < nmine; ++k) {
           const int c = chunk_of(k);
           uint32_t r[32];
@@ -462,7 +465,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
         if (LM) {
           const int tl = lm_tgt - n;
-          if (p.epi == CCB_EPI_LSE_PART) {
+          if (epi_k == CCB_EPI_LSE_PART) {
             float mx = -INFINITY;
 #pragma unroll
             for (int i = 0; i < 32; ++i)
@@ -486,7 +489,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             v[i] = pr * lm_gs;
           }
         } else
-        switch (p.epi) {
+        switch (epi_k) {
           case CCB_EPI_STORE: {
             if (p.Cin != nullptr) {
               float cin[32];
@@ -581,11 +584,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       }
       if (LM) {
         if (row_ok) {
-          if (p.epi == CCB_EPI_LSE_PART)
+          if (epi_k == CCB_EPI_LSE_PART)
             p.part_out[(long long)((t.n0 / BN) * EPI_PARTS + part) * p.M + m] = make_float2(run_m, run_s);
           if (lm_hit && p.zt_out != nullptr) p.zt_out[m] = lm_zt;
         }
-      } else if (p.epi == CCB_EPI_RESID_SS && p.ss_out != nullptr) {
+      } else if (epi_k == CCB_EPI_RESID_SS && p.ss_out != nullptr) {
         // one value per row and tile: the second warp of the quadrant hands its
         // half over, so a row split over two N tiles gets exactly two (commutative,
         // hence order-independent) atomic adds
@@ -617,13 +620,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 // ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
-template <int BN, int A_MN, int B_MN, int LM = 0>
+template <int BN, int A_MN, int B_MN, int LM = 0, int EPI_T = -1>
 static int launch_gemm(const CcbGemmArgs* a, cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
   static bool attr_set[16] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
-  auto kern = gemm_kernel<BN, A_MN, B_MN, LM>;
+  auto kern = gemm_kernel<BN, A_MN, B_MN, LM, EPI_T>;
   if (!attr_set[dev & 15]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg::SMEM_BYTES);
@@ -753,6 +756,21 @@ extern "C" int ccb_gemm(const CcbGemmArgs* a, void* stream_) {
       default: break;
     }
   } else {
+    if (key == 0) {
+      // K-major x K-major carries the trunk's fused epilogues: one instantiation each
+      switch ((int)a->epi) {
+        case CCB_EPI_ROWSCALE: return launch_gemm<256, 0, 0, 0, CCB_EPI_ROWSCALE>(a, stream);
+        case CCB_EPI_ROWSCALE_SILU: return launch_gemm<256, 0, 0, 0, CCB_EPI_ROWSCALE_SILU>(a, stream);
+        case CCB_EPI_RESID_SS: return launch_gemm<256, 0, 0, 0, CCB_EPI_RESID_SS>(a, stream);
+        default: break;
+      }
+    } else if (key == 1) {
+      switch ((int)a->epi) {
+        case CCB_EPI_DSILU: return launch_gemm<256, 0, 1, 0, CCB_EPI_DSILU>(a, stream);
+        case CCB_EPI_RMSBWD: return launch_gemm<256, 0, 1, 0, CCB_EPI_RMSBWD>(a, stream);
+        default: break;
+      }
+    }
     switch (key) {
       case 0: return launch_gemm<256, 0, 0>(a, stream);
       case 1: return launch_gemm<256, 0, 1>(a, stream);

@@ -443,20 +443,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         row_acc *= rs * rs * p.inv_dim;
       }
 
-      for (int k = 0; k < nmine; ++k) {
-        const int c = chunk_of(k);
-        uint32_t r[32];
-        __syncwarp();
+      // the staging buffers a 64-column group will use must have been read out by their last store
+      auto store_gate = [&](int c) {
         if (p.tma_store && (c & 1) == 0) {
-          // the buffers this 64-column group will use must have been read out
+          __syncwarp();
           if (lane == 0) {
             if (two_out) tma_store_wait_read<0>(); else tma_store_wait_read<1>();
           }
           __syncwarp();
         }
-        tmem_ld32(t_addr + c * 32, r);
-        tmem_ld_wait();
-        if (!row_ok && !p.tma_store) continue;
+      };
+      // one 32-column chunk whose accumulator values are already in `r`
+      auto chunk_body = [&](int c, const uint32_t (&r)[32]) {
+        if (!row_ok && !p.tma_store) return;
         const int n = t.n0 + c * 32;
         const int nvalid = p.N - n;
         float v[32];
@@ -479,7 +478,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             }
             run_s = run_s * gemm_ex2(run_m - new_m) + sacc;
             run_m = new_m;
-            continue;   // nothing is stored per column
+            return;   // nothing is stored per column
           }
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
@@ -580,6 +579,44 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           store_f32x32(reinterpret_cast<float*>(p.C) + out_off + n, v, nvalid);
         } else {
           store_bf16x32(reinterpret_cast<__nv_bfloat16*>(p.C) + out_off + n, v, nvalid);
+        }
+      };
+      // The specialised memory-bound epilogues keep the TMEM load of the next chunk in flight
+      // while the current one is scaled, packed and staged (two register buffers).
+      constexpr bool PIPE = (EPI_T == CCB_EPI_ROWSCALE || EPI_T == CCB_EPI_RESID_SS);
+      if constexpr (PIPE) {
+        uint32_t ra[32], rb[32];
+        if (nmine > 0) {
+          __syncwarp();
+          tmem_ld32(t_addr + chunk_of(0) * 32, ra);
+        }
+        for (int k = 0; k < nmine; k += 2) {
+          tmem_ld_wait();
+          if (k + 1 < nmine) {
+            __syncwarp();
+            tmem_ld32(t_addr + chunk_of(k + 1) * 32, rb);
+          }
+          store_gate(chunk_of(k));
+          chunk_body(chunk_of(k), ra);
+          if (k + 1 < nmine) {
+            tmem_ld_wait();
+            if (k + 2 < nmine) {
+              __syncwarp();
+              tmem_ld32(t_addr + chunk_of(k + 2) * 32, ra);
+            }
+            store_gate(chunk_of(k + 1));
+            chunk_body(chunk_of(k + 1), rb);
+          }
+        }
+      } else {
+        for (int k = 0; k < nmine; ++k) {
+          const int c = chunk_of(k);
+          uint32_t r[32];
+          store_gate(c);
+          __syncwarp();
+          tmem_ld32(t_addr + c * 32, r);
+          tmem_ld_wait();
+          chunk_body(c, r);
         }
       }
       if (LM) {

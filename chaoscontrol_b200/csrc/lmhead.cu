@@ -401,9 +401,6 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             // ---- sweep 2 / DW: g tile -> shared memory ------------------------
             const uint32_t gph = n_g & 1u;
             ++n_g;
-            if (MODE == MODE_DW) {
-              if (!wait_all(&bars->g_empty[q >> 1], gph ^ 1u)) { ok = false; break; }
-            }
             if (FUSED1 && it == inner0) {
               // per-row reference: max of the unit's first 32 logits (every warp reads the same
               // 32 columns, so the two column halves of a row agree without an exchange)
@@ -416,13 +413,25 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
               for (int i = 1; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(a0[i]));
               c2 = fmaf(mx, c1, LH_REF_MARGIN);
             }
+            // both 32-column halves of this warp are requested before either is used: one TMEM
+            // round trip per tile instead of two on the path between the two MMAs
+            uint32_t ah[2][32];
+            __syncwarp();
+            tmem_ld32(t_addr + part * 32, ah[0]);
+            tmem_ld32(t_addr + 64 + part * 32, ah[1]);
+            tmem_ld_wait();
+            // the logits now live in registers: hand the TMEM buffer back at once, so the MMA
+            // warp can start the tile after next while this one is still being turned into g
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->d1_empty[b]);
+            if (MODE == MODE_DW) {
+              if (!wait_all(&bars->g_empty[q >> 1], gph ^ 1u)) { ok = false; break; }
+            }
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
               const int col0 = h * 64 + part * 32;
-              uint32_t a[32];
-              __syncwarp();
-              tmem_ld32(t_addr + col0, a);
-              tmem_ld_wait();
+              const uint32_t (&a)[32] = ah[h];
               const int tl = tgt - (v0 + col0);
               uint32_t packed[16];
 #pragma unroll
@@ -470,9 +479,6 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
               __syncwarp();
               if (lane == 0) mbar_arrive(&bars->g_full[q >> 1]);
             }
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bars->d1_empty[b]);
           }
         }
         if (!ok) break;

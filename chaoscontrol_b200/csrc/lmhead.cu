@@ -91,6 +91,7 @@ struct LhBars {
   uint64_t g_full[2], g_empty[2];
   uint64_t d2_full, d2_empty;
   uint64_t xbar;            // epilogue-group rendezvous (8 warps)
+  uint64_t xt_full, xt_empty;   // X row tile resident in tensor memory (A operand of the logits MMA)
   uint32_t tmem_slot;
   int abort_flag;
 };
@@ -129,6 +130,8 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
     mbar_init(&bars->d2_full, 1);
     mbar_init(&bars->d2_empty, 4);
     mbar_init(&bars->xbar, 8);
+    mbar_init(&bars->xt_full, 4);
+    mbar_init(&bars->xt_empty, 1);
     bars->abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmX);
@@ -149,6 +152,15 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
   const int n_units = (MODE == MODE_DW) ? p.n_vtiles * p.row_chunks : p.n_mtiles;
   constexpr bool IS_TRAIN = (MODE == MODE_TRAIN) || (MODE == MODE_TRAIN1);
   constexpr bool FUSED1 = (MODE == MODE_TRAIN1);
+  // Scoring and one-sweep training keep the unit's X tile in tensor memory and feed it to the
+  // logits MMA from there: an M=128, N=128 instruction with both operands in shared memory needs
+  // 8 KiB of it per ~65 cycles and is bound by that, with A in tensor memory it needs 4 KiB.
+  // Tensor-memory columns: scoring  [0,256) two logits buffers, [256,384) X;
+  //                        training [0,128) one logits buffer (released as soon as the epilogue
+  //                        holds it in registers), [128,256) X, [256,512) the dX accumulator.
+  constexpr bool TA = (MODE == MODE_LSE) || FUSED1;
+  constexpr bool ONEBUF = FUSED1;
+  constexpr uint32_t X_COL = (MODE == MODE_LSE) ? 256u : 128u;
   const int n_sweeps = (MODE == MODE_TRAIN && !p.skip_lse) ? 2 : 1;
 
   if (warp == 0) {
@@ -247,6 +259,9 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
           inner1 = min(p.n_mtiles, inner0 + p.mtiles_per_chunk);
         }
         if (!mbar_wait(&bars->res_full, res_phase, abort_flag, p.status)) { ok = false; break; }
+        if (TA) {
+          if (!mbar_wait(&bars->xt_full, res_phase, abort_flag, p.status)) { ok = false; break; }
+        }
         res_phase ^= 1u;
         tc_fence_after_sync();
         for (int sw = 0; sw < n_sweeps && ok; ++sw) {
@@ -257,8 +272,8 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             const int s = n_stg & 1;
             const uint32_t sph = (n_stg >> 1) & 1u;
             ++n_stg;
-            const int b = n_d1 & 1;
-            const uint32_t dph = (n_d1 >> 1) & 1u;
+            const int b = ONEBUF ? 0 : (n_d1 & 1);
+            const uint32_t dph = ONEBUF ? (n_d1 & 1u) : ((n_d1 >> 1) & 1u);
             ++n_d1;
             if (!mbar_wait(&bars->stg_full[s], sph, abort_flag, p.status)) { ok = false; break; }
             if (!mbar_wait(&bars->d1_empty[b], dph ^ 1u, abort_flag, p.status)) { ok = false; break; }
@@ -270,9 +285,15 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             for (int c = 0; c < 4; ++c) {
 #pragma unroll
               for (int k = 0; k < 4; ++k) {
-                const uint64_t adesc = make_smem_desc(xa + c * LH_CHUNK + k * 32, 16, 1024);
                 const uint64_t bdesc = make_smem_desc(wb + c * LH_CHUNK + k * 32, 16, 1024);
-                umma_bf16(tmem_base + b * 128, adesc, bdesc, idesc1, (c > 0 || k > 0) ? 1u : 0u);
+                if (TA) {
+                  // K step (c, k) = bf16 columns [64c + 16k, +16) of X = 8 packed 32-bit columns
+                  umma_bf16_ta(tmem_base + b * 128, tmem_base + X_COL + (uint32_t)(c * 4 + k) * 8u, bdesc,
+                               idesc1, (c > 0 || k > 0) ? 1u : 0u);
+                } else {
+                  const uint64_t adesc = make_smem_desc(xa + c * LH_CHUNK + k * 32, 16, 1024);
+                  umma_bf16(tmem_base + b * 128, adesc, bdesc, idesc1, (c > 0 || k > 0) ? 1u : 0u);
+                }
               }
             }
             umma_commit(&bars->d1_full[b]);
@@ -292,7 +313,10 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             ++n_d2;
           }
         }
-        if (ok) umma_commit(&bars->res_empty);
+        if (ok) {
+          umma_commit(&bars->res_empty);
+          if (TA) umma_commit(&bars->xt_empty);   // every MMA that read the X columns has completed
+        }
       }
     }
   } else {
@@ -302,7 +326,7 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
     const int row_in_tile = q * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
     float2* xchg = reinterpret_cast<float2*>(smem + LH_OFF_X);
-    uint32_t n_d1 = 0, n_g = 0, n_d2 = 0, n_x = 0;
+    uint32_t n_d1 = 0, n_g = 0, n_d2 = 0, n_x = 0, n_xt = 0;
     bool ok = true;
     // Every wait below is made warp-uniform, so the warp-collective TMEM loads
     // that follow never run with part of the warp on the abort path.
@@ -345,13 +369,38 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
       };
       if (MODE != MODE_DW) load_row(unit, MODE == MODE_TRAIN && p.skip_lse);
       float inv_s = 0.f;                   // TRAIN1: 1 / row sum, known after the sweep
+      if (TA) {
+        // this unit's X rows -> tensor memory (one row per lane, 256 bf16 = 128 packed columns);
+        // the previous unit's MMAs must have finished reading those columns
+        if (part == 0) {
+          if (!wait_all(&bars->xt_empty, (n_xt & 1u) ^ 1u)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint4* xrow4 = reinterpret_cast<const uint4*>(p.X + (long long)(row_ok ? r : 0) * LH_D);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t xv[32];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const uint4 v4 = row_ok ? __ldg(xrow4 + c * 8 + j) : make_uint4(0u, 0u, 0u, 0u);
+              xv[j * 4] = v4.x; xv[j * 4 + 1] = v4.y; xv[j * 4 + 2] = v4.z; xv[j * 4 + 3] = v4.w;
+            }
+            __syncwarp();
+            tmem_st32(tmem_base + X_COL + (uint32_t)(c * 32) + lane_addr, xv);
+          }
+          tmem_st_wait();
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars->xt_full);
+        }
+        ++n_xt;
+      }
 
       for (int sw = 0; sw < n_sweeps && ok; ++sw) {
         const bool second = (MODE == MODE_DW) || (IS_TRAIN && sw == n_sweeps - 1);
         float run_m = -INFINITY, run_s = 0.f, run_e = 0.f, tacc = 0.f, zt = 0.f;
         for (int it = inner0; it < inner1 && ok; ++it) {
-          const int b = n_d1 & 1;
-          const uint32_t dph = (n_d1 >> 1) & 1u;
+          const int b = ONEBUF ? 0 : (n_d1 & 1);
+          const uint32_t dph = ONEBUF ? (n_d1 & 1u) : ((n_d1 >> 1) & 1u);
           ++n_d1;
           int v0;
           if (MODE == MODE_DW) {
@@ -698,6 +747,7 @@ extern "C" int ccb_lmhead_lse(const void* X, const void* W, const float* rowss, 
   a.lse = lse;
   a.loss = loss;
   a.entropy = entropy;
+  a.X = (const __nv_bfloat16*)X;      // rows are copied into tensor memory for the logits MMA
   return launch_lmhead<MODE_LSE>(X, W, a, (cudaStream_t)stream);
 }
 

@@ -152,15 +152,16 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
   const int n_units = (MODE == MODE_DW) ? p.n_vtiles * p.row_chunks : p.n_mtiles;
   constexpr bool IS_TRAIN = (MODE == MODE_TRAIN) || (MODE == MODE_TRAIN1);
   constexpr bool FUSED1 = (MODE == MODE_TRAIN1);
-  // Scoring and one-sweep training keep the unit's X tile in tensor memory and feed it to the
-  // logits MMA from there: an M=128, N=128 instruction with both operands in shared memory needs
-  // 8 KiB of it per ~65 cycles and is bound by that, with A in tensor memory it needs 4 KiB.
-  // Tensor-memory columns: scoring  [0,256) two logits buffers, [256,384) X;
-  //                        training [0,128) one logits buffer (released as soon as the epilogue
-  //                        holds it in registers), [128,256) X, [256,512) the dX accumulator.
-  constexpr bool TA = (MODE == MODE_LSE) || FUSED1;
-  constexpr bool ONEBUF = FUSED1;
-  constexpr uint32_t X_COL = (MODE == MODE_LSE) ? 256u : 128u;
+  // Scoring keeps the unit's X tile in tensor memory and feeds it to the logits MMA from there:
+  // an M=128, N=128 instruction with both operands in shared memory needs 8 KiB of it per ~65
+  // cycles, with A in tensor memory 4 KiB (2.02 -> 1.88 ms on 262 144 rows).  Tensor-memory
+  // columns: [0,256) two logits buffers, [256,384) X.
+  // The same was tried for one-sweep training (X in [128,256), ONE logits buffer released as soon
+  // as the epilogue holds it in registers, dX in [256,512)): 7.95 -> 8.10 ms, i.e. no gain once
+  // the second MMA shares the pipe, so training keeps A in shared memory and two logits buffers.
+  constexpr bool TA = (MODE == MODE_LSE);
+  constexpr bool ONEBUF = false;
+  constexpr uint32_t X_COL = 256u;
   const int n_sweeps = (MODE == MODE_TRAIN && !p.skip_lse) ? 2 : 1;
 
   if (warp == 0) {

@@ -113,6 +113,24 @@ class EpisodicRuntime:
         self.query_queue: list[dict[str, Any]] = []
         self.tagged: list[dict[str, Any]] = []
         self._lock = threading.Lock()
+        # "simplex": the native 16-vertex policy picks the replay among the top-k candidates and the
+        # native online learner (credit, Gerber gate, REINFORCE step, slow EMA) learns from every
+        # replay outcome; "heuristic": cosine x utility ranking
+        self.simplex = None
+        self.controller_mode = str(get("episodic_controller_runtime", "heuristic")).strip().lower()
+        if self.controller_mode not in ("heuristic", "simplex"):
+            raise ValueError(f"episodic_controller_runtime must be heuristic or simplex; got {self.controller_mode!r}")
+        if self.consumer and self.controller_mode == "simplex":
+            from .controller import SimplexRuntime
+            self.simplex = SimplexRuntime(
+                num_slots=int(get("episodic_capacity", 4096)),
+                learning_rate=float(get("episodic_controller_lr", 1e-3)),
+                sgd_interval=int(get("episodic_controller_sgd_interval", 16)),
+                ema_interval=int(get("episodic_controller_ema_interval", 64)),
+                entropy_beta=float(get("episodic_controller_entropy_beta", 0.0)))
+            self._sel_gen = torch.Generator().manual_seed(int(get("seed", 0)))
+            self.selection_mode = str(get("episodic_simplex_selection_mode", "sample"))
+        self._closed_learner = False
         self.logger = None
         if self.consumer and get("episodic_replay_log_path"):
             from .diagnostics import DiagnosticsLogger
@@ -238,8 +256,13 @@ class EpisodicRuntime:
             self._flush()
         self._drain_rings(step)
         if len(self.cache) > 0 and self.query_queue:
+            extra = {}
+            if self.simplex is not None:
+                extra = dict(controller_runtime=self.simplex, action_recorder=self.simplex,
+                             simplex_selection_mode=self.selection_mode, simplex_generator=self._sel_gen)
             run_controller_cycle(controller_query_queue=self.query_queue, tagged_replay_queue=self.tagged,
-                                 cache=self.cache, k=self.topk, score_mode=self.score_mode, queue_lock=self._lock)
+                                 cache=self.cache, k=self.topk, score_mode=self.score_mode, queue_lock=self._lock,
+                                 **extra)
         else:
             self.query_queue.clear()
         done = 0
@@ -269,6 +292,21 @@ class EpisodicRuntime:
             self.stats["replay_status"]["ok" if ok else "nan"] += 1
             self.stats["replay_loss_sum"] += loss if ok else 0.0
             done += 1
+            if self.simplex is not None and ok:
+                # reward: how much this replay's loss beats the running replay-loss baseline
+                base = self.stats["replay_loss_sum"] / max(self.stats["replay_status"]["ok"], 1)
+                out = np.zeros((), dtype=N.REPLAY_OUTCOME)
+                out["event_type"], out["selected_rank"] = 3, int(tag.get("selected_rank", 0)) & 0xFF
+                out["replay_id"] = int(tag.get("replay_id", 0)) & 0xFFFFFFFFFFFFFFFF
+                out["gpu_step"], out["selection_step"] = int(step), int(tag.get("selection_step", step))
+                out["query_event_id"] = int(tag.get("query_event_id", 0)) & 0xFFFFFFFFFFFFFFFF
+                out["source_write_id"] = int(tag.get("source_write_id", 0)) & 0xFFFFFFFFFFFFFFFF
+                out["slot_id"], out["policy_version"] = slot, int(tag.get("policy_version", 0))
+                out["teacher_score"] = float(tag.get("teacher_score", 0.0))
+                out["controller_logit"] = float(tag.get("controller_logit", 0.0))
+                out["ce_before_replay"], out["bucket_baseline"] = loss, base
+                out["ce_delta_raw"] = out["reward_shaped"] = base - loss
+                self.simplex.learner.on_replay_outcome(out)
             if self.logger is not None:
                 from .diagnostics import REPLAY_LOG_SCHEMA
                 nan = float("nan")
@@ -325,6 +363,9 @@ class EpisodicRuntime:
         self._flush()
         if self.logger is not None:
             self.logger.close()
+        if self.simplex is not None and not self._closed_learner:
+            self._final_controller = self.simplex.learner.telemetry()
+            self._closed_learner = True
         for ring in list(self._write_rings.values()) + list(self._query_rings.values()):
             ring.close(unlink=self._creator and not self.solo)
         self._write_rings.clear()
@@ -333,6 +374,9 @@ class EpisodicRuntime:
     def diagnostics(self) -> dict[str, Any]:
         d = {"enabled": True, "role": "episodic" if self.is_episodic_rank else ("solo" if self.solo else "train"),
              "n_train": self.n_train, "key_rep_dim": self.key_rep_dim, "span_length": self.span, **self.stats}
+        if self.simplex is not None:
+            d["controller"] = {"mode": "simplex", "decisions": len(self.simplex.decisions),
+                               **self.simplex.learner.telemetry()}
         if self.cache is not None:
             d["cache_entries"] = len(self.cache)
             d["cache_capacity"] = int(self.cache.capacity)

@@ -141,3 +141,24 @@ def test_episodic_rank_on_three_gpus(tmp_path):
     e2 = r[2]["res"]["episodic"]
     assert e2["role"] == "episodic" and e2["write_events_ingested"] > 0 and e2["replays"] >= 1
     assert all(v == v for v in r[0]["res"]["loss_history"])
+
+
+def test_simplex_controller_learns_from_replay_outcomes():
+    """The native simplex policy chooses the replays and its online learner is credited by every outcome."""
+    from chaoscontrol_b200.runner_fast_path import _build_optimizer, train_fast_for_budget
+    torch.manual_seed(0)
+    tokens = torch.randint(0, 64, (4000,), dtype=torch.int16)
+    model = CareStudentLM(vocab_size=64, dim=16, num_layers=2)
+    rt = EpisodicRuntime(model=model, config=dict(_CFG, episodic_controller_runtime="simplex",
+                                                  episodic_controller_sgd_interval=2, episodic_writes_per_step=8),
+                         rank=0, world_size=1, device=torch.device("cpu"))
+    optim = _build_optimizer(dict(optimizer="adamw", base_lr=1e-3), model)
+    try:
+        res = train_fast_for_budget(model, train_tokens=tokens, train_num_tokens=4000, optimizer=optim, episodic=rt,
+                                    **_kw(max_steps=16))
+    finally:
+        rt.close()
+    c = res["episodic"]["controller"]
+    assert c["mode"] == "simplex" and c["decisions"] >= res["episodic"]["replays"] >= 4
+    assert c["replay_outcomes"] == res["episodic"]["replays"] and c["history_appends"] == c["decisions"]
+    assert c["credited_actions"] >= 1

@@ -38,17 +38,27 @@ def test_calc_types_run_and_relate(setup):
         calc_types=["score_only_reset", "carry_state", "adaptive_carry", "dreamworld_eval",
                     "packet_online_cache"],
         calc_type_configs={"carry_state": {"decay": 0.0}, "score_only_reset": {"chunk_size": 8},
+                           "packet_online_cache": {"decay": 0.0},
                            "dreamworld_eval": {"K": 2, "L": 4, "lr": 1e-3},
-                           "adaptive_carry": {"decays": [0.0, 1.0]}})
+                           "adaptive_carry": {"horizon_shifts": [-0.5, 0.0, 0.5]}})
     ntok = vc.total_tokens - vc.num_docs
     for name, e in out.items():
         assert e["tokens_scored"] == ntok and e["docs_scored"] == vc.num_docs, name
         assert math.isfinite(e["bpb"]) and e["bpb"] > 0
-    # carry with decay 0 is exactly a reset; no memory => the cache pass is a reset too
+    # carry with decay 0 is exactly a reset; no memory and no carried state => the cache pass is a reset too
     assert out["carry_state"]["loss"] == pytest.approx(out["score_only_reset"]["loss"], rel=1e-4)
     assert out["packet_online_cache"]["loss"] == pytest.approx(out["score_only_reset"]["loss"], rel=1e-4)
-    # the mixture can only lose log(n_experts) per document against its best expert
-    assert out["adaptive_carry"]["loss"] <= out["score_only_reset"]["loss"] + math.log(2) * vc.num_docs / ntok + 1e-6
+    # exponential weights with eta = 1: the mixture loses at most log(n_experts) in total against its best head
+    ac = out["adaptive_carry"]
+    assert ac["loss"] <= min(ac["per_head_loss"].values()) + math.log(3) / ntok + 1e-6
+    assert sum(ac["winner_counts"].values()) == ntok and abs(sum(ac["final_online_weights"]) - 1) < 1e-9
+    # one unshifted head with full carry is the carried-state pass
+    one = evaluate_with_calc_types(model=model, val_cache=vc, device=torch.device("cpu"),
+                                   calc_types=["adaptive_carry", "carry_state"],
+                                   calc_type_configs={"adaptive_carry": {"horizon_shifts": "0.0",
+                                                                         "online_episodic_chunk_tokens": 7}})
+    assert one["adaptive_carry"]["loss"] == pytest.approx(one["carry_state"]["loss"], rel=1e-4)
+    assert one["adaptive_carry"]["final_online_weights"] is None
     for n, p in model.named_parameters():
         assert torch.equal(p, before[n]), n            # dreamworld restored every document
     with pytest.raises(ValueError):
@@ -75,3 +85,86 @@ def test_dispatch(setup):
     legacy = dispatch_eval_for_config({}, model=model, val_cache=None, device=torch.device("cpu"),
                                       legacy_evaluate_fn=lambda m, **kw: {"bpb": 1.0, "loss": 2.0})
     assert legacy == {"bpb": 1.0, "loss": 2.0}
+
+
+def _memory_model():
+    torch.manual_seed(0)
+    return CareStudentLM(vocab_size=64, dim=16, num_layers=2, outer_model_dim=8, outer_model_type="multislot",
+                         outer_max_slots=0, buffer_mode="append_only")
+
+
+def test_packet_online_cache_reads_then_writes(setup):
+    _, vc = setup
+    model = _memory_model()
+    run = lambda **cfg: evaluate_with_calc_types(                                       # noqa: E731
+        model=model, val_cache=vc, device=torch.device("cpu"), calc_types=["packet_online_cache"],
+        calc_type_configs={"packet_online_cache": cfg})["packet_online_cache"]
+    ntok = vc.total_tokens - vc.num_docs
+    a = run(chunk_tokens=8, write_tokens_per_chunk=2, seeded=False)
+    x = a                                           # extras are merged into the result entry
+    assert a["tokens_scored"] == ntok and a["docs_scored"] == vc.num_docs
+    assert x["slot_count_initial"] == 0 and x["slot_count_final"] == 2 * x["episodic_writes"] > 0
+    # the very first chunk has nothing to read; every later chunk (and every document tail) reads
+    assert x["episodic_reads"] == x["chunks_scored"] - 1 + vc.num_docs
+    # seeded: the store left by the previous pass is read from the first chunk on and keeps growing
+    b = run(chunk_tokens=8, write_tokens_per_chunk=2, seeded=True, controller_read_enabled=True, controller_topk_k=3)
+    y = b
+    assert y["slot_count_initial"] == x["slot_count_final"] and y["slot_count_final"] > y["slot_count_initial"]
+    assert y["episodic_reads"] == y["chunks_scored"] + vc.num_docs
+    assert y["controller_reads"] == y["episodic_reads"] and y["controller_selected_slots"] == 3 * y["controller_reads"]
+    assert b["loss"] != pytest.approx(a["loss"], rel=1e-6)
+    # gate 0 switches the residual off entirely; writes still happen
+    c = run(chunk_tokens=8, write_tokens_per_chunk=1, gate_value=0.0, seeded=False)
+    assert c["episodic_reads"] == 0 and c["episodic_writes"] > 0
+    # microbatches of whole documents: one read and one commit per group
+    d = run(batch_docs=4, write_tokens_per_chunk=2, seeded=False)
+    z = d
+    assert d["tokens_scored"] == ntok and z["chunks_scored"] == math.ceil(vc.num_docs / 4)
+    assert z["episodic_reads"] == z["chunks_scored"] - 1 and z["slot_count_final"] == 2 * vc.num_docs
+    for bad in (dict(chunk_tokens=0), dict(write_tokens_per_chunk=-1), dict(gate_value=-1.0), dict(batch_docs=0),
+                dict(controller_read_enabled=True, controller_score_mode="nope")):
+        with pytest.raises(ValueError):
+            run(**bad)
+    # a store that grows between the cue read and the score is refused
+    real = model.encode
+
+    def leaky(ids, **kw):
+        out = real(ids, **kw)
+        model.append_memory_from_hidden(out[0].detach(), max_tokens=1)
+        return out
+    model.encode = leaky
+    try:
+        with pytest.raises(RuntimeError, match="score-before-write"):
+            run(chunk_tokens=8, seeded=False)
+    finally:
+        model.encode = real
+
+
+def test_online_mixer_matches_the_per_token_loop():
+    from chaoscontrol_b200.eval.calc_types import _online_mix
+    torch.manual_seed(0)
+    nll = torch.rand(3, 11, dtype=torch.float64) * 3
+    lw = torch.log_softmax(torch.randn(3, dtype=torch.float64), 0)
+    mixed, lw_end = _online_mix(nll, lw, eta=0.7)
+    w, want = lw.clone(), []
+    for t in range(11):
+        want.append(-torch.logsumexp(w - nll[:, t], 0))
+        w = torch.log_softmax(w - 0.7 * nll[:, t], 0)
+    assert torch.allclose(mixed, torch.stack(want)) and torch.allclose(lw_end, w)
+
+
+def test_dreamworld_eval_modes(setup):
+    model, vc = setup
+    before = {n: p.detach().clone() for n, p in model.named_parameters()}
+    run = lambda **cfg: evaluate_with_calc_types(                                       # noqa: E731
+        model=model, val_cache=vc, device=torch.device("cpu"), calc_types=["dreamworld_eval"],
+        calc_type_configs={"dreamworld_eval": dict(K=2, L=4, lr=0.05, **cfg)})["dreamworld_eval"]
+    a, b = run(), run(dream_target_mode="softmax", dream_temperature=0.7, seed=3)
+    c = run(per_doc_reset=False)
+    assert a["hyperparams"]["dream_target_mode"] == "argmax" and b["hyperparams"]["prefix_len"] == 16
+    assert a["loss"] != pytest.approx(b["loss"], rel=1e-9)          # different dreams, different step
+    assert c["loss"] != pytest.approx(a["loss"], rel=1e-9)          # adaptation carried across documents
+    for n, p in model.named_parameters():
+        assert torch.equal(p, before[n]), n                          # both modes leave the weights as found
+    with pytest.raises(ValueError):
+        run(dream_target_mode="beam")

@@ -23,7 +23,18 @@ from ..ops import gemm as G
 from ..ops import trunk as T
 from .core import CareSSMCore, FeedForward, RMSNorm
 
-__all__ = ["FusedCareSSMBlock", "post_scan_fused", "post_scan_reference"]
+__all__ = ["FusedCareSSMBlock", "post_scan_fused", "post_scan_reference", "get_post_scan_backend"]
+
+
+def get_post_scan_backend() -> dict[str, str]:
+    """Which implementation ``post_scan_fused`` runs (core_fused.py:196-202 of the reference reports
+    its compiled / eager choice; here there is no tracing compiler to fall back from)."""
+    import torch as _t
+    if _t.cuda.is_available():
+        return {"backend": "tcgen05_gemm_epilogues",
+                "note": "bf16 CUDA operands run two GEMMs with RMSNorm, SiLU and residual adds fused in their "
+                        "epilogues; other operands run the PyTorch statement"}
+    return {"backend": "eager", "note": "no CUDA device: PyTorch statement"}
 
 
 def post_scan_reference(x_pre_residual, scan_out, ff_norm_weight, ff_norm_eps, ff_fc_weight, ff_proj_weight):

@@ -22,7 +22,16 @@ from torch.utils.checkpoint import checkpoint as _checkpoint
 from ..ops import trunk as T
 from .core import CareSSMCore, FeedForward, RMSNorm
 
-__all__ = ["CareSSMBlock", "CareStudentLM", "RMSNorm", "FeedForward", "CareSSMCore"]
+__all__ = ["CareSSMBlock", "CareStudentLM", "RMSNorm", "FeedForward", "CareSSMCore", "CareSSMHybridBlock",
+           "AttentionControlBlock"]
+
+
+def __getattr__(name: str):
+    # the hybrid / attention blocks live in .attention (which imports this module's blocks): resolve lazily
+    if name in ("CareSSMHybridBlock", "AttentionControlBlock"):
+        from . import attention
+        return getattr(attention, name)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
 
 
 class CareSSMBlock(nn.Module):

@@ -130,6 +130,27 @@ def fused_lm_head_loss_with_ce(*, hidden, final_norm, lm_head, targets, backend:
     return loss, ce.view(targets.shape)
 
 
+def fused_lm_head_weighted_loss_with_ce(*, hidden, final_norm, lm_head, targets, token_weight,
+                                        backend: str = "auto", tile_size: int = 1024):
+    """``(sum(ce * w) / max(sum w, 1), detached per-token CE)``, differentiable in ``hidden`` and the
+    head / norm weights; ``token_weight`` is treated as a constant (train_ssm.py:210-270)."""
+    from .kernels.lm_head_loss import fused_linear_cross_entropy_weighted
+    if token_weight.device != hidden.device:
+        raise ValueError("fused_lm_head_weighted_loss_with_ce: token_weight must be on the same device as hidden, "
+                         f"got {token_weight.device} and {hidden.device}")
+    weight = getattr(final_norm, "weight", None)
+    eps = float(getattr(final_norm, "eps", 1e-6))
+    w = token_weight.reshape(-1).detach().float()
+    if weight is None:
+        logits = lm_head(final_norm(hidden))
+        ce = F.cross_entropy(logits.reshape(-1, logits.shape[-1]).float(), targets.reshape(-1), reduction="none")
+        return (ce * w).sum() / w.sum().clamp_min(1.0), ce.detach()
+    b = "streaming_v2" if str(backend).strip().lower() == "norm_streaming_v2" else backend
+    loss, ce = fused_linear_cross_entropy_weighted(fused_rms_norm(hidden, weight, eps=eps), lm_head.weight,
+                                                   targets.reshape(-1), w, backend=b, tile_size=int(tile_size))
+    return loss, ce.detach()
+
+
 def fused_lm_head_backward(hidden, final_norm, lm_head, targets, *, backend: str = "auto",
                            tile_size: int = 1024, loss_weight: float = 1.0) -> torch.Tensor:
     """Fused RMSNorm + tiled linear+CE, one backward.  Returns the detached loss."""

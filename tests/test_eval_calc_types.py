@@ -168,3 +168,20 @@ def test_dreamworld_eval_modes(setup):
         assert torch.equal(p, before[n]), n                          # both modes leave the weights as found
     with pytest.raises(ValueError):
         run(dream_target_mode="beam")
+
+
+def test_seeded_versus_empty_store_compare(setup, tmp_path):
+    from chaoscontrol_b200.eval.packet_online_cache_compare import run_packet_online_cache_compare
+    _, vc = setup
+    model = _memory_model()
+    # give the model a trained-in store
+    with torch.no_grad():
+        model.append_memory_from_hidden(torch.randn(1, 6, 16), max_tokens=6)
+    n0 = model.outer_model.table.n_active
+    out = run_packet_online_cache_compare(model=model, val_cache=vc, device=torch.device("cpu"),
+                                          compare_config={"chunk_tokens": 8, "write_tokens_per_chunk": 1},
+                                          output_json=tmp_path / "cmp.json")
+    assert out["seeded"]["slot_count_initial"] == n0 and out["empty"]["slot_count_initial"] == 0
+    assert out["seeded"]["tokens_scored"] == out["empty"]["tokens_scored"]
+    assert out["delta_bpb"] == pytest.approx(out["empty"]["bpb"] - out["seeded"]["bpb"])
+    assert (tmp_path / "cmp.json").exists() and out["compare_type"] == "packet_online_cache"

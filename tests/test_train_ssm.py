@@ -127,3 +127,47 @@ def test_ddp_two_ranks_gloo_identical_params():
     assert a["steps"] == b["steps"] == 4
     for k in a["sd"]:
         assert torch.equal(a["sd"][k], b["sd"][k]), k
+
+
+def test_reference_module_paths_and_names_resolve():
+    """Import paths a user of the reference package relies on."""
+    import importlib
+    for mod, names in {
+        "chaoscontrol_b200.local_attn": ["LocalAttention", "RollingKVCache"],
+        "chaoscontrol_b200.eval.ttt_eval": ["register_calc_type", "evaluate_with_calc_types", "CalcTypeContext"],
+        "chaoscontrol_b200.eval.runner_dispatch": ["dispatch_eval_for_config"],
+        "chaoscontrol_b200.eval.packet_online_cache_compare": ["run_packet_online_cache_compare"],
+        "chaoscontrol_b200.eval_stream.delta_mod": ["DeltaModulator"],
+        "chaoscontrol_b200.eval_stream.persistence": ["StateManager", "attach_trainable_h0"],
+        "chaoscontrol_b200.eval_stream.ttt_runner": ["select_adapt_params"],
+        "chaoscontrol_b200.eval_stream.doc_stream": ["DocStreamer"],
+        "chaoscontrol_b200.eval_stream.metrics": ["MetricsCollector"],
+        "chaoscontrol_b200.eval_stream.val_cache": ["ValCache", "write_val_cache", "load_val_cache"],
+        "chaoscontrol_b200.optim.momentum_warmup": ["apply_momentum_warmup"],
+        "chaoscontrol_b200.optim.step_wrapper": ["wrap_optimizer_step"],
+        "chaoscontrol_b200.optim.weight_ema": ["WeightEMA", "eval_with_ema"],
+        "chaoscontrol_b200.models.model": ["CareSSMHybridBlock", "AttentionControlBlock"],
+        "chaoscontrol_b200.models.core_fused": ["get_post_scan_backend"],
+        "chaoscontrol_b200.train_ssm": ["fused_lm_head_weighted_loss_with_ce"],
+    }.items():
+        m = importlib.import_module(mod)
+        for n in names:
+            assert getattr(m, n) is not None, (mod, n)
+
+
+def test_weighted_lm_head_loss_with_ce_matches_the_formula():
+    import torch.nn.functional as F2
+    from chaoscontrol_b200.models.core import RMSNorm
+    from chaoscontrol_b200.train_ssm import fused_lm_head_weighted_loss_with_ce
+    torch.manual_seed(0)
+    hidden = torch.randn(2, 5, 16, requires_grad=True)
+    norm, head = RMSNorm(16), torch.nn.Linear(16, 32, bias=False)
+    tgt = torch.randint(0, 32, (2, 5))
+    w = torch.rand(2, 5)
+    loss, ce = fused_lm_head_weighted_loss_with_ce(hidden=hidden, final_norm=norm, lm_head=head, targets=tgt,
+                                                   token_weight=w)
+    ref_ce = F2.cross_entropy(head(norm(hidden)).reshape(-1, 32), tgt.reshape(-1), reduction="none")
+    assert torch.allclose(ce.reshape(-1), ref_ce.detach(), atol=1e-5)
+    assert torch.allclose(loss, (ref_ce * w.reshape(-1)).sum() / w.sum().clamp_min(1.0), atol=1e-5)
+    loss.backward()
+    assert hidden.grad is not None and head.weight.grad is not None

@@ -233,8 +233,43 @@ void SimplexOnlineLearner::initialize(const SimplexWeights& w) {
   init_ = true;
 }
 
+SimplexOnlineLearner::~SimplexOnlineLearner() { set_trace_path(""); }
+
+void SimplexOnlineLearner::set_trace_path(const std::string& path) {
+  if (trace_fp_) { std::fclose(trace_fp_); trace_fp_ = nullptr; }
+  trace_path_ = path;
+  if (!path.empty()) {
+    trace_fp_ = std::fopen(path.c_str(), "a");
+    if (trace_fp_) std::setvbuf(trace_fp_, nullptr, _IOLBF, 0);
+  }
+}
+
+static double entropy_of(const std::vector<float>& p) {
+  double ent = 0.0;
+  for (float x : p) if (x > 0.f) ent -= x * std::log(x);
+  return ent;
+}
+
+void SimplexOnlineLearner::trace_skip(const wire::ReplayOutcome& ev, const char* reason) {
+  if (!trace_fp_) return;
+  std::fprintf(trace_fp_, "{\"row_type\":\"skip\",\"status\":\"skipped\",\"status_reason\":\"%s\","
+                          "\"gpu_step\":%llu,\"slot_id\":%u,\"outcome_status\":%u}\n",
+               reason, static_cast<unsigned long long>(ev.gpu_step), ev.slot_id,
+               static_cast<unsigned>(ev.outcome_status));
+}
+
 void SimplexOnlineLearner::record_decision(uint64_t slot_id, ActionRecord rec) {
   if (slot_id >= num_slots_) { ++tel_.invalid_slot_skips; return; }
+  if (trace_fp_ && init_ && rec.V.size() == static_cast<std::size_t>(fast_.N) * fast_.K_v &&
+      rec.E.size() == static_cast<std::size_t>(fast_.N) * fast_.N && rec.feats.size() == fast_.K_s) {
+    SimplexForward f = simplex_forward(fast_, rec.V.data(), rec.E.data(), rec.feats.data());
+    std::fprintf(trace_fp_, "{\"row_type\":\"decision\",\"status\":\"ok\",\"gpu_step\":%llu,"
+                            "\"slot_id\":%llu,\"chosen_idx\":%u,\"p_chosen\":%g,\"entropy\":%g,"
+                            "\"temperature\":%g,\"entropy_beta\":%g,\"sgd_steps\":%llu}\n",
+                 static_cast<unsigned long long>(rec.gpu_step),
+                 static_cast<unsigned long long>(slot_id), rec.chosen, rec.p_chosen, entropy_of(f.p),
+                 fast_.temperature, entropy_beta_, static_cast<unsigned long long>(tel_.sgd_steps));
+  }
   auto& q = history_[static_cast<uint32_t>(slot_id)];
   q.push_back(std::move(rec));
   while (q.size() > max_entries_) q.pop_front();
@@ -248,10 +283,13 @@ std::size_t SimplexOnlineLearner::history_size(uint32_t slot) const {
 
 void SimplexOnlineLearner::on_replay_outcome(const wire::ReplayOutcome& ev) {
   ++tel_.replay_outcomes;
-  if (ev.outcome_status != 0 || !std::isfinite(ev.reward_shaped)) return;
-  if (ev.slot_id >= num_slots_) { ++tel_.invalid_slot_skips; return; }
+  if (ev.outcome_status != 0 || !std::isfinite(ev.reward_shaped)) { trace_skip(ev, "outcome_status"); return; }
+  if (ev.slot_id >= num_slots_) { ++tel_.invalid_slot_skips; trace_skip(ev, "invalid_slot"); return; }
   auto it = history_.find(ev.slot_id);
-  if (it == history_.end() || it->second.empty() || !init_) { ++tel_.skipped_missing_state; return; }
+  if (!init_) { ++tel_.skipped_missing_state; trace_skip(ev, "missing_weights"); return; }
+  if (it == history_.end() || it->second.empty()) {
+    ++tel_.skipped_missing_state; trace_skip(ev, "missing_decision"); return;
+  }
   const float reward = ev.reward_shaped;
   const float mean = reward_stats_.mean();
   const float sd = reward_stats_.stddev();
@@ -276,23 +314,30 @@ void SimplexOnlineLearner::on_replay_outcome(const wire::ReplayOutcome& ev) {
     const float adv = recency_decay(adv_std, ev.gpu_step, rec.gpu_step, gamma_);
     simplex_backward(fast_, f, rec.V.data(), rec.E.data(), rec.feats.data(), rec.chosen, adv,
                      entropy_beta_, grad_.data());
-    double ent = 0.0;
-    for (float p : f.p) if (p > 0.f) ent -= p * std::log(p);
+    const double ent = entropy_of(f.p);
     tel_.last_entropy = static_cast<float>(ent);
     ++tel_.credited_actions;
+    if (trace_fp_)
+      std::fprintf(trace_fp_, "{\"row_type\":\"credit\",\"status\":\"ok\",\"gpu_step\":%llu,"
+                              "\"slot_id\":%u,\"selection_step\":%llu,\"chosen_idx\":%u,\"p_chosen\":%g,"
+                              "\"p_current_chosen\":%g,\"current_entropy\":%g,\"reward_shaped\":%g,"
+                              "\"advantage_raw\":%g,\"advantage_standardized\":%g,\"gerber_weight\":%g,"
+                              "\"advantage_final\":%g,\"behavior_logprob_margin\":%g,"
+                              "\"current_logprob_margin\":%g,\"sgd_steps\":%llu,\"ema_blends\":%llu}\n",
+                   static_cast<unsigned long long>(ev.gpu_step), ev.slot_id,
+                   static_cast<unsigned long long>(rec.gpu_step), rec.chosen, rec.p_chosen,
+                   f.p[rec.chosen], ent, reward, adv_raw, adv_std, gw, adv, then, now,
+                   static_cast<unsigned long long>(tel_.sgd_steps),
+                   static_cast<unsigned long long>(tel_.ema_blends));
     ++since_sgd_;
     ema_.tick();
     maybe_sgd();
   }
-  if (!trace_path_.empty()) {
-    if (FILE* fp = std::fopen(trace_path_.c_str(), "a")) {
-      std::fprintf(fp, "{\"row_type\":\"replay_outcome\",\"gpu_step\":%llu,\"slot_id\":%u,"
-                       "\"reward\":%g,\"advantage\":%g,\"sgd_steps\":%llu}\n",
-                   static_cast<unsigned long long>(ev.gpu_step), ev.slot_id, reward, adv_std,
-                   static_cast<unsigned long long>(tel_.sgd_steps));
-      std::fclose(fp);
-    }
-  }
+  if (trace_fp_)
+    std::fprintf(trace_fp_, "{\"row_type\":\"replay_outcome\",\"gpu_step\":%llu,\"slot_id\":%u,"
+                            "\"reward\":%g,\"advantage\":%g,\"sgd_steps\":%llu}\n",
+                 static_cast<unsigned long long>(ev.gpu_step), ev.slot_id, reward, adv_std,
+                 static_cast<unsigned long long>(tel_.sgd_steps));
 }
 
 void SimplexOnlineLearner::maybe_sgd() {

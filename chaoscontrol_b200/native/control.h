@@ -16,6 +16,7 @@
 #pragma once
 #include <cstdint>
 #include <deque>
+#include <cstdio>
 #include <string>
 #include <unordered_map>
 #include <vector>
@@ -128,9 +129,16 @@ class SimplexOnlineLearner {
   const SimplexWeights& slow() const { return slow_; }
   const LearnerTelemetry& telemetry() const { return tel_; }
   std::size_t history_size(uint32_t slot) const;
-  void set_trace_path(const std::string& path) { trace_path_ = path; }
+  // NDJSON trace, one row per event: "decision" when an action is recorded, "credit" for every
+  // action a replay outcome reaches, "skip" (with status_reason) when an outcome reaches none,
+  // "replay_outcome" once per outcome.  An empty path closes the file.
+  void set_trace_path(const std::string& path);
+  ~SimplexOnlineLearner();
+  SimplexOnlineLearner(const SimplexOnlineLearner&) = delete;
+  SimplexOnlineLearner& operator=(const SimplexOnlineLearner&) = delete;
  private:
   void maybe_sgd();
+  void trace_skip(const wire::ReplayOutcome& ev, const char* reason);
   uint32_t num_slots_, max_entries_;
   float gamma_, gerber_c_, entropy_beta_;
   uint32_t sgd_interval_, since_sgd_ = 0;
@@ -144,6 +152,7 @@ class SimplexOnlineLearner {
   std::unordered_map<uint32_t, std::deque<ActionRecord>> history_;
   LearnerTelemetry tel_;
   std::string trace_path_;
+  std::FILE* trace_fp_ = nullptr;
 };
 
 // ------------------------------------------------------------------ CSWG ----

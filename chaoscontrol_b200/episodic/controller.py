@@ -40,7 +40,7 @@ FEATURE_MANIFEST = ("simplex_v1:V0=utility_u,V1=query_cosine,V2=age_steps/1000,V
 FEATURE_MANIFEST_HASH = hashlib.sha256(FEATURE_MANIFEST.encode("utf-8")).hexdigest()[:16]
 
 __all__ = ["run_controller_cycle", "controller_main", "build_simplex_inputs", "choose_simplex_vertex",
-           "SimplexRuntime", "FEATURE_MANIFEST", "FEATURE_MANIFEST_HASH"]
+           "SimplexRuntime", "load_simplex_policy", "save_simplex_policy", "FEATURE_MANIFEST", "FEATURE_MANIFEST_HASH"]
 
 
 def _is_simplex_runtime(runtime: Any) -> bool:
@@ -63,6 +63,14 @@ class SimplexRuntime:
     def fast_weights(self):
         return self.policy
 
+    def sync_policy(self, seen_sgd_steps: int = -1) -> int:
+        """Copies the learner's fast weights into the selection policy once the learner has
+        taken a step since ``seen_sgd_steps``; returns the learner's step count."""
+        steps = int(self.learner.telemetry()["sgd_steps"])
+        if steps != seen_sgd_steps:
+            self.policy.flat[:] = self.learner.weights(slow=False)
+        return steps
+
     def simplex_forward(self, V, E, sf):
         return self.policy.forward(V, E, sf)
 
@@ -81,6 +89,60 @@ class SimplexRuntime:
                                      V, E, simplex_features)
         self.decisions.append({"chosen_slot_id": int(chosen_slot_id), "gpu_step": int(gpu_step),
                                "chosen_idx": int(chosen_idx), "p_chosen": float(p_chosen_decision), **meta})
+
+
+_SIMPLEX_TENSORS = ("W_vp", "b_vp", "W_lh", "b_lh", "W_sb", "alpha")
+
+
+def _simplex_sizes(K_v: int, K_s: int, H: int) -> tuple[int, ...]:
+    return (K_v * H, H, H, 1, K_s, 1)
+
+
+def save_simplex_policy(path, policy) -> None:
+    """Writes a simplex policy.  ``*.pt``: ``{"manifest": {"dims": {k_v, k_s, h, n_vertices}},
+    "tensors": {W_vp, b_vp, W_lh, b_lh, W_sb, alpha, temperature}}`` (the layout the reference
+    reads in experiments/23_fast_path/runner_fast_path.py:8423-8443); anything else: a CSWG file
+    whose header carries ``(N, K_v, K_s, H)`` and whose payload is the flat weights followed by
+    the temperature."""
+    flat = np.asarray(policy.flat, np.float32)
+    if str(path).endswith(".pt"):
+        tensors, o = {}, 0
+        for name, n in zip(_SIMPLEX_TENSORS, _simplex_sizes(policy.K_v, policy.K_s, policy.H)):
+            tensors[name] = torch.from_numpy(flat[o:o + n].copy())
+            o += n
+        tensors["W_vp"] = tensors["W_vp"].view(policy.K_v, policy.H)
+        tensors["temperature"] = torch.tensor(float(policy.temperature))
+        torch.save({"manifest": {"dims": {"k_v": policy.K_v, "k_s": policy.K_s, "h": policy.H,
+                                          "n_vertices": policy.N},
+                                 "feature_manifest_hash": FEATURE_MANIFEST_HASH},
+                    "tensors": tensors}, str(path))
+        return
+    from . import native
+    native.write_cswg(str(path), np.concatenate([flat, [np.float32(policy.temperature)]]),
+                      n_layers=policy.N, d_global=policy.K_v, d_slot=policy.K_s, feature_dim=policy.H)
+
+
+def load_simplex_policy(path):
+    """Inverse of `save_simplex_policy`; raises ``ValueError`` on a size mismatch."""
+    from . import native
+    if str(path).endswith(".pt"):
+        art = torch.load(str(path), map_location="cpu", weights_only=False)
+        dims, t = art["manifest"]["dims"], art["tensors"]
+        pol = native.SimplexPolicy(N=int(dims["n_vertices"]), K_v=int(dims["k_v"]), K_s=int(dims["k_s"]),
+                                   H=int(dims["h"]), temperature=float(t["temperature"]))
+        flat = np.concatenate([np.asarray(t[k], np.float32).reshape(-1) for k in _SIMPLEX_TENSORS])
+    else:
+        hdr, payload = native.load_cswg(str(path))
+        pol = native.SimplexPolicy(N=hdr["n_layers"], K_v=hdr["d_global"], K_s=hdr["d_slot"],
+                                   H=hdr["feature_dim"])
+        if payload.size != pol.flat.size + 1:
+            raise ValueError(f"{path}: payload of {payload.size} values does not fit a simplex policy "
+                             f"of {pol.flat.size} weights + temperature")
+        flat, pol.temperature = payload[:-1], float(payload[-1])
+    if flat.size != pol.flat.size:
+        raise ValueError(f"{path}: {flat.size} weights, the dims ask for {pol.flat.size}")
+    pol.flat[:] = flat
+    return pol
 
 
 # ---------------------------------------------------------------------------

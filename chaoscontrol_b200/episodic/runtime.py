@@ -118,18 +118,52 @@ class EpisodicRuntime:
         # replay outcome; "heuristic": cosine x utility ranking
         self.simplex = None
         self.controller_mode = str(get("episodic_controller_runtime", "heuristic")).strip().lower()
+        if self.controller_mode in ("", "python_heuristic"):
+            self.controller_mode = "heuristic"
+        # "simplex_v1" is the pretrained policy: it must come with a weight file, so a run cannot
+        # silently score with random weights (experiments/23_fast_path/runner_fast_path.py:8509-8520)
+        pretrained = self.controller_mode == "simplex_v1"
+        if pretrained:
+            self.controller_mode = "simplex"
         if self.controller_mode not in ("heuristic", "simplex"):
-            raise ValueError(f"episodic_controller_runtime must be heuristic or simplex; got {self.controller_mode!r}")
+            raise ValueError("episodic_controller_runtime must be heuristic, simplex or simplex_v1; "
+                             f"got {self.controller_mode!r}")
+        weights_path = get("episodic_controller_weights_path")
+        if pretrained and not weights_path:
+            raise ValueError("episodic_controller_runtime='simplex_v1' requires episodic_controller_weights_path")
+        self.train_online = bool(get("controller_train_online", True))
+        self._synced_sgd_steps = 0
         if self.consumer and self.controller_mode == "simplex":
-            from .controller import SimplexRuntime
+            from .controller import SimplexRuntime, load_simplex_policy
+            policy = load_simplex_policy(str(weights_path)) if weights_path else None
+            if policy is None:
+                from . import native
+                policy = native.SimplexPolicy(seed=int(get("seed", 0)))
+            if get("episodic_controller_initial_temperature") is not None:
+                # a sharper start than the file's temperature: near-uniform sampling gives the
+                # policy-gradient step nothing to lock onto (runner_fast_path.py:8477-8489)
+                policy.temperature = float(get("episodic_controller_initial_temperature"))
             self.simplex = SimplexRuntime(
+                policy=policy,
                 num_slots=int(get("episodic_capacity", 4096)),
-                learning_rate=float(get("episodic_controller_lr", 1e-3)),
+                max_entries_per_slot=int(get("episodic_controller_history_entries", 64)),
+                gamma=float(get("episodic_controller_credit_gamma", 0.995)),
+                learning_rate=float(get("episodic_controller_learning_rate",
+                                        get("episodic_controller_lr", 1e-3))),
                 sgd_interval=int(get("episodic_controller_sgd_interval", 16)),
+                ema_alpha=float(get("episodic_controller_ema_alpha", 0.25)),
                 ema_interval=int(get("episodic_controller_ema_interval", 64)),
                 entropy_beta=float(get("episodic_controller_entropy_beta", 0.0)))
+            trace = str(get("episodic_controller_simplex_trace_path", "") or "")
+            if trace:
+                os.makedirs(os.path.dirname(trace) or ".", exist_ok=True)
+                self.simplex.learner.set_trace_path(trace)
             self._sel_gen = torch.Generator().manual_seed(int(get("seed", 0)))
-            self.selection_mode = str(get("episodic_simplex_selection_mode", "sample"))
+            self.selection_mode = str(get("episodic_controller_selection_mode",
+                                          get("episodic_simplex_selection_mode", "sample")))
+            if self.selection_mode not in ("argmax", "sample"):
+                raise ValueError("episodic_controller_selection_mode must be argmax or sample; "
+                                 f"got {self.selection_mode!r}")
         self._closed_learner = False
         self.logger = None
         if self.consumer and get("episodic_replay_log_path"):
@@ -306,7 +340,8 @@ class EpisodicRuntime:
                 out["controller_logit"] = float(tag.get("controller_logit", 0.0))
                 out["ce_before_replay"], out["bucket_baseline"] = loss, base
                 out["ce_delta_raw"] = out["reward_shaped"] = base - loss
-                self.simplex.learner.on_replay_outcome(out)
+                if self.train_online:                      # frozen: select with the loaded weights, never learn
+                    self.simplex.learner.on_replay_outcome(out)
             if self.logger is not None:
                 from .diagnostics import REPLAY_LOG_SCHEMA
                 nan = float("nan")
@@ -325,6 +360,8 @@ class EpisodicRuntime:
                     "outcome_status": REPLAY_STATUS["ok" if ok else "nan"], "flags": 0})
                 self.logger.write_row(row)
         self.stats["replays"] += done
+        if self.simplex is not None and self.train_online and done:
+            self._synced_sgd_steps = self.simplex.sync_policy(self._synced_sgd_steps)
         return done
 
     # ------------------------------------------------------------------ gradient join
@@ -376,6 +413,8 @@ class EpisodicRuntime:
              "n_train": self.n_train, "key_rep_dim": self.key_rep_dim, "span_length": self.span, **self.stats}
         if self.simplex is not None:
             d["controller"] = {"mode": "simplex", "decisions": len(self.simplex.decisions),
+                               "train_online": self.train_online, "selection_mode": self.selection_mode,
+                               "temperature": float(self.simplex.policy.temperature),
                                **self.simplex.learner.telemetry()}
         if self.cache is not None:
             d["cache_entries"] = len(self.cache)

@@ -2,6 +2,7 @@
 episodic rank over gloo (event rings in shared memory, replay on the episodic rank, one SUM join)."""
 import os
 
+import numpy as np
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
@@ -162,3 +163,72 @@ def test_simplex_controller_learns_from_replay_outcomes():
     assert c["mode"] == "simplex" and c["decisions"] >= res["episodic"]["replays"] >= 4
     assert c["replay_outcomes"] == res["episodic"]["replays"] and c["history_appends"] == c["decisions"]
     assert c["credited_actions"] >= 1
+
+
+@pytest.mark.parametrize("suffix", [".pt", ".cswg"])
+def test_simplex_policy_file_round_trip(tmp_path, suffix):
+    from chaoscontrol_b200.episodic import native
+    from chaoscontrol_b200.episodic.controller import load_simplex_policy, save_simplex_policy
+    pol = native.SimplexPolicy(seed=3, temperature=0.4)
+    path = tmp_path / f"policy{suffix}"
+    save_simplex_policy(path, pol)
+    back = load_simplex_policy(path)
+    assert (back.N, back.K_v, back.K_s, back.H) == (pol.N, pol.K_v, pol.K_s, pol.H)
+    assert back.temperature == pytest.approx(0.4, rel=1e-3)
+    np.testing.assert_allclose(back.flat, pol.flat, atol=2e-3 if suffix == ".cswg" else 0)
+
+
+def _run_simplex(tmp_path, **cfg):
+    from chaoscontrol_b200.runner_fast_path import _build_optimizer, train_fast_for_budget
+    torch.manual_seed(0)
+    tokens = torch.randint(0, 64, (4000,), dtype=torch.int16)
+    model = CareStudentLM(vocab_size=64, dim=16, num_layers=2)
+    rt = EpisodicRuntime(model=model, config=dict(_CFG, episodic_controller_sgd_interval=2,
+                                                  episodic_writes_per_step=8, **cfg),
+                         rank=0, world_size=1, device=torch.device("cpu"))
+    optim = _build_optimizer(dict(optimizer="adamw", base_lr=1e-3), model)
+    try:
+        res = train_fast_for_budget(model, train_tokens=tokens, train_num_tokens=4000, optimizer=optim,
+                                    episodic=rt, **_kw(max_steps=16))
+        flat = rt.simplex.policy.flat.copy()
+    finally:
+        rt.close()
+    return res["episodic"], flat
+
+
+def test_pretrained_simplex_frozen_and_online(tmp_path):
+    """simplex_v1 needs a weight file; frozen runs select with it and never learn; online runs
+    learn, copy the learner's weights into the selection policy and trace decision/credit rows."""
+    import json
+    from chaoscontrol_b200.episodic import native
+    from chaoscontrol_b200.episodic.controller import save_simplex_policy
+    model = CareStudentLM(vocab_size=64, dim=16, num_layers=2)
+    with pytest.raises(ValueError, match="episodic_controller_weights_path"):
+        EpisodicRuntime(model=model, config=dict(_CFG, episodic_controller_runtime="simplex_v1"),
+                        rank=0, world_size=1, device=torch.device("cpu"))
+    pol = native.SimplexPolicy(seed=5)
+    wpath = tmp_path / "w.pt"
+    save_simplex_policy(wpath, pol)
+    common = dict(episodic_controller_runtime="simplex_v1", episodic_controller_weights_path=str(wpath),
+                  episodic_controller_selection_mode="sample")
+
+    frozen, flat_frozen = _run_simplex(tmp_path, controller_train_online=False, **common)
+    c = frozen["controller"]
+    assert not c["train_online"] and c["decisions"] >= 4 and c["replay_outcomes"] == 0 and c["sgd_steps"] == 0
+    np.testing.assert_array_equal(flat_frozen, pol.flat)
+
+    trace = tmp_path / "traces" / "t.ndjson"
+    online, flat_online = _run_simplex(tmp_path, controller_train_online=True,
+                                       episodic_controller_initial_temperature=0.2,
+                                       episodic_controller_entropy_beta=0.05,
+                                       episodic_controller_simplex_trace_path=str(trace), **common)
+    c = online["controller"]
+    assert c["train_online"] and c["temperature"] == pytest.approx(0.2) and c["sgd_steps"] >= 1
+    assert not np.array_equal(flat_online, pol.flat)          # selection follows the learner
+    rows = [json.loads(line) for line in trace.read_text().splitlines()]
+    kinds = {r["row_type"] for r in rows}
+    assert {"decision", "credit", "replay_outcome"} <= kinds
+    dec = next(r for r in rows if r["row_type"] == "decision")
+    assert 0.0 < dec["entropy"] <= np.log(16) + 1e-4 and dec["temperature"] == pytest.approx(0.2)
+    cred = next(r for r in rows if r["row_type"] == "credit")
+    assert {"p_chosen", "p_current_chosen", "gerber_weight", "advantage_final"} <= set(cred)

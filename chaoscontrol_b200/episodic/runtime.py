@@ -77,7 +77,17 @@ class EpisodicRuntime:
         self.replay_weight = float(get("episodic_replay_weight", 1.0))
         self.max_replays = int(get("episodic_replay_max_replays_per_step", 4))
         self.topk = int(get("episodic_controller_topk_k", 16))
-        self.score_mode = str(get("episodic_controller_score_mode", "cosine_utility_weighted"))
+        # the run matrices write ``controller_query_mode``; a disagreement between the two keys is
+        # refused, since picking one silently would spoil the pressure-only control
+        # (experiments/23_fast_path/runner_fast_path.py:8382-8401)
+        primary, alias = get("episodic_controller_score_mode"), get("controller_query_mode")
+        if primary is not None and alias is not None and str(primary) != str(alias):
+            raise ValueError(f"conflicting controller score mode keys: episodic_controller_score_mode={primary!r}, "
+                             f"controller_query_mode={alias!r}")
+        self.score_mode = str(primary if primary is not None else alias if alias is not None
+                              else "cosine_utility_weighted").strip()
+        # without queries the cache still fills (writes) but nothing is ever tagged for replay
+        self.query_enabled = bool(get("controller_query_enabled", True))
         self.ring_capacity = int(get("episodic_ring_capacity", 4096))
         ns = str(get("episodic_event_ring_namespace", "") or
                  f"/ccb_epi_{os.environ.get('MASTER_PORT', '0')}_{os.getppid()}")
@@ -236,7 +246,8 @@ class EpisodicRuntime:
             host_w.copy_(recs)
             host_q.copy_(torch.cat([q_vec, q_ce.reshape(1)]))
         self._pending.append((ev, host_w, "write", int(pos.shape[0])))
-        self._pending.append((ev, host_q, "query", int(step)))        # built once its host values have landed
+        if self.query_enabled:
+            self._pending.append((ev, host_q, "query", int(step)))    # built once its host values have landed
         self._flush()
 
     def _query_record(self, host_q: torch.Tensor, step: int) -> np.ndarray:

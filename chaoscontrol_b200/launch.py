@@ -84,22 +84,32 @@ def summarize_result_dir(results_dir: Path) -> dict[str, Any]:
 
 
 def run_matrix(entries: list[dict[str, Any]], *, results_dir: Path, data_path: str, sp_model_path: Optional[str],
-               world_size: int, dry_run: bool = False, val_cache_dir: Optional[str] = None) -> dict[str, Any]:
-    """Runs every entry that has no result file yet (idempotent re-runs); a failed
-    entry leaves ``{"config", "error"}`` in its place so the sweep continues."""
+               world_size: int, dry_run: bool = False, val_cache_dir: Optional[str] = None,
+               limit: Optional[int] = None, skip_existing: bool = True,
+               checkpoint_dir: Optional[Path] = None) -> dict[str, Any]:
+    """Runs the first ``limit`` entries (all by default).  With ``skip_existing`` an entry whose
+    result file exists is left alone (idempotent re-runs); a failed entry leaves
+    ``{"config", "error"}`` in its place so the sweep continues.  ``checkpoint_dir`` makes every
+    run save ``<name>.pt`` there."""
     results_dir.mkdir(parents=True, exist_ok=True)
+    if checkpoint_dir is not None and not dry_run:
+        Path(checkpoint_dir).mkdir(parents=True, exist_ok=True)
     cmds = []
-    for e in entries:
+    for e in entries[:limit] if limit is not None else entries:
         out = results_dir / f"{e['name']}.json"
-        if out.exists():
+        if out.exists() and skip_existing:
             continue
         cfg = write_entry_config(e, results_dir / "configs")
         cmd = build_torchrun_cmd(config_path=cfg, data_path=data_path, sp_model_path=sp_model_path, output_json=out,
-                                 world_size=world_size, budget_seconds=e.get("budget_seconds"),
-                                 val_cache_dir=val_cache_dir, dry_run=dry_run)
+                                 world_size=world_size,
+                                 budget_seconds=e.get("budget_seconds"), val_cache_dir=val_cache_dir,
+                                 output_ckpt=None if checkpoint_dir is None else Path(checkpoint_dir) / f"{e['name']}.pt",
+                                 dry_run=dry_run)
         cmds.append(cmd)
         if dry_run:
             continue
+        if out.exists():
+            out.unlink()
         proc = subprocess.run(cmd, capture_output=True, text=True)
         if proc.returncode != 0 and not out.exists():
             out.write_text(json.dumps({"config": e, "error": proc.stderr[-2000:]}, indent=2, default=str))

@@ -52,7 +52,8 @@ from .optim.schedule import eval_with_ema, wrap_optimizer_step
 from .parallel.distributed import (allreduce_grads, broadcast_params, clip_arena_grad_norm, clip_grad_norm_fused,
                                    should_stop_now)
 from .train_ssm import _FUSED_LM_HEAD_BACKENDS, _reject_unsupported, train_ssm_step, train_ssm_step_with_ce
-from .training_hooks import (CriticalityDistillHook, FastSlowConsolidator, spectral_summary,
+from .training_hooks import (CriticalityDistillHook, FastSlowConsolidator, predictive_auxiliary_loss,
+                             spectral_regularization_loss, spectral_summary,
                              zero_embedding_grad_until)
 from .utils.arena import get_arena
 
@@ -432,6 +433,10 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
                           event_sleep_min_interval: int = 8, event_sleep_weight: float = 0.0,
                           criticality: Optional[CriticalityDistillHook] = None,
                           episodic: Optional["EpisodicRuntime"] = None,
+                          spectral_reg_lambda_dead: float = 0.0, spectral_reg_lambda_sticky: float = 0.0,
+                          spectral_reg_min_a: float = 0.05, spectral_reg_max_a: float = 0.98,
+                          predictive_aux_weight: float = 0.0, predictive_aux_horizon: int = 0,
+                          predictive_aux_dim: int = 0,
                           time_fn: Callable[[], float] = time.perf_counter, **unused: Any) -> dict[str, Any]:
     """Budgeted hot loop.  Returns the train-result dict (``steps``, ``elapsed_s``,
     ``initial_loss``, ``final_loss``, ``loss_history``, throughput keys,
@@ -452,6 +457,12 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
     if criticality is not None and world_size > 1:
         raise ValueError("criticality_distill_enabled=True is single-rank only: seat masks, the score "
                          "accumulators and the log_a loss are rank-local")
+    spectral_on = float(spectral_reg_lambda_dead) > 0.0 or float(spectral_reg_lambda_sticky) > 0.0
+    predictive_on = float(predictive_aux_weight) > 0.0 and int(predictive_aux_horizon) > 0
+    if predictive_on and (episodic is not None or crct_enabled):
+        # the auxiliary gradient is rank-local and is reduced with the main one; the memory-rank
+        # topologies reduce with a SUM over a mixed group (runner_fast_path.py:10942-10951)
+        raise ValueError("predictive_aux_weight > 0 cannot be combined with episodic_enabled or crct_enabled")
     ddp = world_size > 1
     if ddp:
         broadcast_params(model)
@@ -476,6 +487,9 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
         distributed_muon = False
     model.train()
     mode = str(train_sampling_mode).strip().lower()
+    # Epoch samplers shard over the ranks that train (data_world): with an episodic or memory rank in
+    # the job no shard of the epoch is lost, so the reference's random-sampling-only restriction
+    # (experiments/23_fast_path/runner_fast_path.py:10755-10782) is not needed here.
     sampler = {"random": None, "sequential_epoch": FP.SequentialShardedStartSampler(),
                "shuffled_epoch": FP.ShuffledEpochShardedStartSampler(seed=seed)}.get(mode, "bad")
     if sampler == "bad":
@@ -505,6 +519,8 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
             why_not.append("criticality_distill_not_supported")
         if episodic is not None:
             why_not.append("episodic_not_supported")
+        if spectral_on or predictive_on:
+            why_not.append("auxiliary_loss_not_supported")
         if why_not:
             graph_summary = _rejected_cuda_graph_summary(mode=graph_mode, reasons=why_not, **gate)
         else:
@@ -553,6 +569,46 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
             dream_gate = LossTriggeredReplayEMA(decay=float(event_sleep_ema_decay),
                                                 warmup_steps=int(event_sleep_warmup_steps))
     event_pending, event_last_replay, queued = False, -10 ** 9, None
+    # predictive auxiliary head: a bias-free dim x dim projection with its own AdamW at the trunk's
+    # learning rate (runner_fast_path.py:11333-11350); it is a training aid and is not saved
+    aux_proj = aux_opt = None
+    aux_stats = {"steps": 0, "last_loss": float("nan"), "spectral_steps": 0}
+    if predictive_on:
+        dim = int(getattr(model, "dim", 0) or model.lm_head.in_features)
+        if int(predictive_aux_dim) not in (0, dim):
+            raise ValueError("predictive_aux_dim must be 0 or equal to the model dim")
+        aux_proj = torch.nn.Linear(dim, dim, bias=False).to(device=device, dtype=next(model.parameters()).dtype)
+        aux_opt = torch.optim.AdamW(aux_proj.parameters(), lr=float(optimizer.param_groups[0]["lr"]),
+                                    weight_decay=0.0)
+        if ddp:
+            broadcast_params(aux_proj)
+
+    def aux_backward(inputs: torch.Tensor) -> None:
+        """Adds the auxiliary gradients to ``p.grad`` after the main backward: the predictive loss
+        through a second (autograd) encoder pass, the spectral hinge straight on ``log_a``."""
+        added = False
+        if aux_proj is not None:
+            aux_opt.zero_grad(set_to_none=True)
+            aux = predictive_auxiliary_loss(model.encode(inputs), projection=aux_proj,
+                                            horizon=int(predictive_aux_horizon))
+            if aux is not None:
+                (float(predictive_aux_weight) * aux).backward()
+                aux_stats["steps"] += 1
+                if steps % 64 == 0:                 # sampled: reading the value waits for the device
+                    aux_stats["last_loss"] = float(aux.detach())
+                added = True
+        if spectral_on:
+            reg = spectral_regularization_loss(model, float(spectral_reg_lambda_dead),
+                                               float(spectral_reg_lambda_sticky), float(spectral_reg_min_a),
+                                               float(spectral_reg_max_a))
+            if reg is not None and reg.requires_grad:
+                reg.backward()
+                aux_stats["spectral_steps"] += 1
+                added = True
+        arena_now = get_arena(model)
+        if added and arena_now is not None and arena_now.grads_fresh:
+            arena_now.pull_grads()                  # fold what autograd added into the flat gradient buffer
+
     sync_teacher = crct is not None and crct.mode == "sync" and crct.world_size > 1
     if sync_teacher:
         stop_check_interval = 1                    # the memory rank mirrors every step: it needs every flag
@@ -630,8 +686,12 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
                 arena_now = get_arena(model)
                 if arena_now is not None and arena_now.grads_fresh:
                     arena_now.pull_grads()
+                if predictive_on:
+                    aux_backward(inputs)
                 if ddp and dist_opt is None:
                     allreduce_grads(model, world_size)
+                    if aux_proj is not None:
+                        allreduce_grads(aux_proj, world_size)
             elif crct_enabled:
                 payload = None
                 if crct is not None:
@@ -642,11 +702,20 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
                 if ddp:
                     allreduce_grads(model, world_size, group=grad_group)
             else:
-                loss = train_ssm_step(model, inputs, targets, chunk_size, ddp_active=ddp and dist_opt is None,
+                # a rank-local auxiliary gradient joins before the one reduction of the step
+                loss = train_ssm_step(model, inputs, targets, chunk_size,
+                                      ddp_active=ddp and dist_opt is None and not predictive_on,
                                       world_size=world_size, precision=precision,
                                       compile_full_path=compile_full_path,
                                       lm_head_backward_mode=lm_head_backward_mode,
                                       lm_head_tile_size=lm_head_tile_size)
+                if predictive_on:
+                    aux_backward(inputs)
+                    if ddp and dist_opt is None:
+                        allreduce_grads(model, world_size)
+                        allreduce_grads(aux_proj, world_size)
+            if spectral_on and not predictive_on and not epi_idle:
+                aux_backward(inputs)               # a function of the weights alone: identical on every rank
             if criticality is not None:
                 if criticality.after_backward(model, inputs, targets, step=steps,
                                               lm_head_tile_size=lm_head_tile_size) is not None:
@@ -659,6 +728,10 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
             else:
                 _clip(model, grad_clip_norm, fused_grad_clip)
                 optimizer.step()
+            if aux_opt is not None:
+                if dist_opt is not None and ddp:
+                    allreduce_grads(aux_proj, world_size)
+                aux_opt.step()
             if precision == "fp8_fused":
                 from .ops.fp8_linear import fused_fp8_flush_all
                 fused_fp8_flush_all(model)
@@ -705,6 +778,12 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
         result["episodic"] = episodic.diagnostics()
         result.update(FP.summarize_train_timing(steps=steps, elapsed_s=elapsed, batch_size=batch_size,
                                                 seq_len=seq_len, world_size=world_size, episodic_enabled=ddp))
+    if predictive_on:
+        result["predictive_aux"] = {"weight": float(predictive_aux_weight), "horizon": int(predictive_aux_horizon),
+                                    "steps": aux_stats["steps"], "last_loss": aux_stats["last_loss"],
+                                    "projection_norm": float(aux_proj.weight.detach().float().norm())}
+    if spectral_on:
+        result["spectral"]["regularized_steps"] = aux_stats["spectral_steps"]
     if criticality is not None:
         result["criticality_distillation"] = criticality.diagnostics()
     if dream_buffer is not None:
@@ -731,7 +810,9 @@ _LOOP_KEYS = ("chunk_size", "grad_clip_norm", "fused_grad_clip", "precision", "s
               "lm_head_tile_size", "cuda_graph_mode", "cuda_graph_min_total_speedup",
               "cuda_graph_max_capture_seconds", "cuda_graph_warmup_steps", "train_sampling_mode",
               "embed_freeze_steps", "distributed_muon", "crct_enabled",
-              "replay_eviction_enabled") + _DREAM_KEYS
+              "replay_eviction_enabled", "spectral_reg_lambda_dead", "spectral_reg_lambda_sticky",
+              "spectral_reg_min_a", "spectral_reg_max_a", "predictive_aux_weight", "predictive_aux_horizon",
+              "predictive_aux_dim") + _DREAM_KEYS
 
 
 def _loop_kwargs(config: dict[str, Any]) -> dict[str, Any]:
@@ -888,6 +969,9 @@ def run_condition(config: dict[str, Any], *, data_path: str, sp_model_path: Opti
 
     eval_result: dict[str, Any] = {}
     if rank == 0 and (eval_batches > 0 or calc_types):
+        if luts[0] is None:
+            raise ValueError("evaluation reports bits per byte and needs the SentencePiece model: pass "
+                             "--sp-model-path, or set eval_batches: 0 (and no calc_types) to train only")
         from .eval import dispatch_eval_for_config
         from .sp_eval import evaluate_bpb_sp
         val_cache = None

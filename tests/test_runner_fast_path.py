@@ -289,6 +289,39 @@ def test_dreamworld_replay_and_event_sleep_in_the_loop():
         train_fast_for_budget(model, event_sleep_enabled=True, **kw)
 
 
+def _aux_run(**mech):
+    torch.manual_seed(0)
+    tokens = torch.randint(0, 64, (4000,), dtype=torch.int16)
+    model = CareStudentLM(vocab_size=64, dim=16, num_layers=2)
+    with torch.no_grad():
+        for _, log_a in TH.iter_log_a_params(model):
+            log_a.fill_(6.0)                          # a = sigmoid(6) = 0.9975: "sticky" channels
+    optim = torch.optim.SGD(model.parameters(), lr=0.5)
+    res = train_fast_for_budget(model, train_tokens=tokens, train_num_tokens=4000, stride=8, seq_len=16,
+                                batch_size=4, device=torch.device("cpu"), optimizer=optim, budget_seconds=600.0,
+                                precision="fp32", stop_check_interval=1, lm_head_backward_mode="fused",
+                                prefetch_batches=False, max_steps=8, grad_clip_norm=0.0, **mech)
+    return model, res
+
+
+def test_spectral_and_predictive_aux_losses_act_in_the_loop():
+    base, res0 = _aux_run()
+    spec, res1 = _aux_run(spectral_reg_lambda_sticky=1e4, spectral_reg_max_a=0.9)
+    a0 = torch.cat([torch.sigmoid(p).reshape(-1) for _, p in TH.iter_log_a_params(base)])
+    a1 = torch.cat([torch.sigmoid(p).reshape(-1) for _, p in TH.iter_log_a_params(spec)])
+    assert res1["spectral"]["regularized_steps"] == 8 and "regularized_steps" not in res0["spectral"]
+    assert a1.mean() < a0.mean() - 1e-4                 # the hinge pulls the decay back under max_a
+    # identical data and seed: the predictive loss reaches the trunk through the second encoder pass
+    pred, res2 = _aux_run(predictive_aux_weight=5.0, predictive_aux_horizon=2)
+    assert res2["predictive_aux"]["steps"] == 8 and res2["predictive_aux"]["projection_norm"] > 0
+    assert not torch.allclose(pred.embed.weight, base.embed.weight)
+    assert torch.allclose(_aux_run()[0].embed.weight, base.embed.weight)          # the harness is deterministic
+    with pytest.raises(ValueError, match="predictive_aux_dim"):
+        _aux_run(predictive_aux_weight=1.0, predictive_aux_horizon=2, predictive_aux_dim=7)
+    with pytest.raises(ValueError, match="predictive_aux_weight"):
+        _aux_run(predictive_aux_weight=1.0, predictive_aux_horizon=2, crct_enabled=True)
+
+
 def test_loss_triggered_replay_gate():
     from chaoscontrol_b200.dreamworld import LossTriggeredReplayEMA
     g = LossTriggeredReplayEMA(decay=0.5, warmup_steps=2)

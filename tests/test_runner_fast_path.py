@@ -322,6 +322,36 @@ def test_spectral_and_predictive_aux_losses_act_in_the_loop():
         _aux_run(predictive_aux_weight=1.0, predictive_aux_horizon=2, crct_enabled=True)
 
 
+@pytest.mark.gpu
+def test_aux_losses_on_the_kernel_engine_path():
+    """With the flat arena installed the main gradients come from the kernel engine; the auxiliary
+    losses add theirs through autograd and must end up in the same flat buffer."""
+    dev = torch.device("cuda:0")
+    tokens = torch.randint(0, 512, (1 << 18,), dtype=torch.int16, generator=torch.Generator().manual_seed(1))
+
+    def run(**mech):
+        torch.manual_seed(0)
+        model = CareStudentLM(vocab_size=512, dim=256, num_layers=2).to(dev).to(torch.bfloat16)
+        with torch.no_grad():
+            for _, log_a in TH.iter_log_a_params(model):
+                log_a.fill_(6.0)
+        ParamArena.install(model)
+        optim = _build_optimizer(dict(optimizer="muon", base_lr=0.02), model)
+        res = train_fast_for_budget(model, train_tokens=tokens, train_num_tokens=tokens.numel(), stride=64,
+                                    seq_len=256, batch_size=16, device=dev, optimizer=optim, budget_seconds=600.0,
+                                    precision="bf16", max_steps=8, stop_check_interval=1, seed=5,
+                                    lm_head_backward_mode="fused_streaming_cached", vocab_size=512, **mech)
+        a = torch.cat([torch.sigmoid(p.float()).reshape(-1) for _, p in TH.iter_log_a_params(model)])
+        return res, a.mean().item(), model.embed.weight.detach().float().clone()
+
+    r0, a0, e0 = run()
+    r1, a1, _ = run(spectral_reg_lambda_sticky=1e5, spectral_reg_max_a=0.9)
+    r2, _, e2 = run(predictive_aux_weight=5.0, predictive_aux_horizon=4)
+    assert r1["spectral"]["regularized_steps"] == 8 and a1 < a0 - 1e-4
+    assert r2["predictive_aux"]["steps"] == 8 and not torch.allclose(e2, e0)
+    assert all(v == v for v in r1["loss_history"] + r2["loss_history"])
+
+
 def test_loss_triggered_replay_gate():
     from chaoscontrol_b200.dreamworld import LossTriggeredReplayEMA
     g = LossTriggeredReplayEMA(decay=0.5, warmup_steps=2)

@@ -32,6 +32,15 @@ def _doc_tensor(ctx: CalcTypeContext, doc) -> torch.Tensor:
                            device=ctx.device).unsqueeze(0)
 
 
+def _docs(ctx: CalcTypeContext):
+    """The cache's documents in source order, cut to the first ``max_docs`` when the pass's
+    config sets it (calibration probes and smoke runs)."""
+    import itertools
+    limit = int(ctx.config.get("max_docs", 0) or 0)
+    it = ctx.val_cache.iter_docs()
+    return itertools.islice(it, limit) if limit > 0 else it
+
+
 def _score(model, ids, states):
     out = model(ids, initial_states=states)
     ce = F.cross_entropy(out["logits"][0, :-1].float(), ids[0, 1:], reduction="sum")
@@ -75,7 +84,7 @@ def carry_state(ctx: CalcTypeContext) -> CalcTypeResult:
     prev = None
     try:
         with torch.no_grad():
-            for doc in ctx.val_cache.iter_docs():
+            for doc in _docs(ctx):
                 if doc.token_len < 2:
                     continue
                 ids = _doc_tensor(ctx, doc)
@@ -178,7 +187,7 @@ def adaptive_carry(ctx: CalcTypeContext) -> CalcTypeResult:
     model.eval()
     try:
         with torch.no_grad():
-            for doc in ctx.val_cache.iter_docs():
+            for doc in _docs(ctx):
                 if doc.token_len < 2:
                     continue
                 ids = _doc_tensor(ctx, doc)
@@ -259,7 +268,7 @@ def dreamworld_eval(ctx: CalcTypeContext) -> CalcTypeResult:
     ce = 0.0
     ntok = nbytes = ndocs = 0
     try:
-        for doc in ctx.val_cache.iter_docs():
+        for doc in _docs(ctx):
             if doc.token_len < 2:
                 continue
             ids = _doc_tensor(ctx, doc)

@@ -385,6 +385,22 @@ def test_inline_teacher_on_cuda_bf16():
 
 
 @pytest.mark.gpu
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("mode,port", [("async_rank0_memory_mailbox", 29775), ("sync", 29777)])
+def test_crct_on_two_gpus(tmp_path, mode, port):
+    """One train GPU and one memory GPU: pinned mailbox, side-stream copies and weight snapshots on hardware."""
+    mp.spawn(_crct_rank, args=(2, port, mode, str(tmp_path), False, True), nprocs=2, join=True)
+    r = [torch.load(tmp_path / f"r{i}.pt", weights_only=False) for i in range(2)]
+    assert r[0]["res"]["steps"] == 12 and r[1]["res"]["role"] == "memory" and r[1]["res"]["steps"] >= 1
+    d0 = r[0]["res"]["crct"]
+    if mode == "sync":
+        assert r[1]["res"]["steps"] == 12 and d0["teacher_payloads"] == 12
+    else:
+        assert d0["teacher_payloads"] + d0["teacher_fail_open"] == 12
+    assert all(v == v for v in r[0]["res"]["loss_history"])
+
+
+@pytest.mark.gpu
 @pytest.mark.skipif(torch.cuda.device_count() < 3, reason="needs 3 GPUs")
 @pytest.mark.parametrize("mode,port", [("async_rank0_memory_mailbox", 29771), ("sync", 29773)])
 def test_crct_on_three_gpus(tmp_path, mode, port):

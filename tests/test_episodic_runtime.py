@@ -133,6 +133,18 @@ def test_kernel_engine_step_feeds_the_episodic_runtime():
 
 
 @pytest.mark.gpu
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_episodic_rank_on_two_gpus(tmp_path):
+    """One train GPU on the kernel engine + an episodic GPU that replays; one NCCL SUM join."""
+    mp.spawn(_rank, args=(2, 29765, str(tmp_path), True), nprocs=2, join=True)
+    r = [torch.load(tmp_path / f"r{i}.pt", weights_only=False) for i in range(2)]
+    assert torch.allclose(r[0]["w"], r[1]["w"], atol=1e-6)
+    e1 = r[1]["res"]["episodic"]
+    assert e1["role"] == "episodic" and e1["write_events_ingested"] > 0 and e1["replays"] >= 1
+    assert all(v == v for v in r[0]["res"]["loss_history"])
+
+
+@pytest.mark.gpu
 @pytest.mark.skipif(torch.cuda.device_count() < 3, reason="needs 3 GPUs")
 def test_episodic_rank_on_three_gpus(tmp_path):
     """Two train GPUs on the kernel engine + an episodic GPU; one NCCL SUM join over the flat arena."""

@@ -177,13 +177,21 @@ def full_val_commands(*, entries: list[dict[str, Any]], checkpoint_dir: Path, re
         ckpt, done = Path(checkpoint_dir) / f"{name}.pt", out_dir / f"{name}.summary.json"
         if done.exists() or (not dry_run and not ckpt.exists()):
             continue
-        port = DRY_RUN_RDZV_PORT if dry_run else pick_free_port()
-        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={int(world_size)}",
-               "--master-addr", "127.0.0.1", "--master-port", str(port), "-m", "chaoscontrol_b200.fast_score",
-               "--cache-dir", str(cache_dir), "--checkpoint-path", str(ckpt),
-               "--output-path", str(out_dir / f"{name}.jsonl"), "--chunk-size", "256",
-               "--budget-seconds", str(float(budget_seconds)), "--doc-batch-size", "4096",
-               "--max-forward-tokens", "auto", "--doc-packing", "chunk_count_tail"]
+        adapt, steps = str(e.get("eval_adapt_set", "none")), int(e.get("eval_steps_per_chunk", 0) or 0)
+        if adapt != "none" and steps > 0:
+            # a test-time-training cell: score-then-adapt per chunk, one process (weights change per document)
+            cmd = [sys.executable, "-m", "chaoscontrol_b200.eval_stream.run_eval", "--val-cache-dir", str(cache_dir),
+                   "--checkpoint-path", str(ckpt), "--output-path", str(out_dir / f"{name}.jsonl"),
+                   "--summary-path", str(done), "--adapt-set", adapt, "--steps-per-chunk", str(steps),
+                   "--chunk-size", "256", "--budget-seconds", str(float(budget_seconds))]
+        else:
+            port = DRY_RUN_RDZV_PORT if dry_run else pick_free_port()
+            cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={int(world_size)}",
+                   "--master-addr", "127.0.0.1", "--master-port", str(port), "-m", "chaoscontrol_b200.fast_score",
+                   "--cache-dir", str(cache_dir), "--checkpoint-path", str(ckpt),
+                   "--output-path", str(out_dir / f"{name}.jsonl"), "--chunk-size", "256",
+                   "--budget-seconds", str(float(budget_seconds)), "--doc-batch-size", "4096",
+                   "--max-forward-tokens", "auto", "--doc-packing", "chunk_count_tail"]
         cmds.append(cmd)
         if dry_run or not run:
             continue
@@ -192,7 +200,7 @@ def full_val_commands(*, entries: list[dict[str, Any]], checkpoint_dir: Path, re
             proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
             log.write(proc.stdout + f"\n[returncode] {proc.returncode}\n")
         last = [ln for ln in proc.stdout.splitlines() if ln.startswith("{")]
-        if proc.returncode == 0 and last:
+        if proc.returncode == 0 and last and not done.exists():
             done.write_text(last[-1])
     return cmds
 

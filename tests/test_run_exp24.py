@@ -44,6 +44,17 @@ def test_dry_run_writes_matrix_and_commands(tmp_path, capsys, monkeypatch):
     assert not list((tmp_path / "out").glob("exp24_*.json"))                   # nothing ran
 
 
+def test_full_val_pass_routes_ttt_cells_to_the_adapting_driver(tmp_path):
+    entries = R.build_entries(matrix="episodic_ttt_v1", speed_config={}, world_size=4, budget_seconds=5.0, seeds=[1])
+    cmds = R.full_val_commands(entries=entries, checkpoint_dir=tmp_path / "ck", results_dir=tmp_path / "res",
+                               world_size=4, cache_dir=tmp_path / "val", budget_seconds=60.0, dry_run=True)
+    assert len(cmds) == 4
+    kinds = ["run_eval" if "chaoscontrol_b200.eval_stream.run_eval" in c else "fast_score" for c in cmds]
+    assert kinds == ["fast_score", "run_eval", "fast_score", "run_eval"]          # arms a, b, c, d
+    ttt = cmds[1]
+    assert ttt[ttt.index("--adapt-set") + 1] == "lm_head" and ttt[ttt.index("--steps-per-chunk") + 1] == "1"
+
+
 def _result(tmp_path, train):
     p = tmp_path / "r.json"
     p.write_text(json.dumps({"config": {}, "train": train}))

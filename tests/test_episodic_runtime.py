@@ -135,10 +135,11 @@ def test_kernel_engine_step_feeds_the_episodic_runtime():
 def _assert_ranks_agree_to_a_bf16_ulp(a: torch.Tensor, b: torch.Tensor) -> None:
     """Every rank applies the same joined gradient.  On bf16 weights the train rank (kernel engine)
     and the episodic rank (autograd replay) have been measured to end one bf16 ulp apart in a few
-    entries (5 of 131072 after 10 steps on two B200s); anything beyond one ulp, or more than 0.1 %
-    of the entries, is a real divergence."""
+    entries (5 and 6 of 131072 after 10 steps in two runs on two B200s, largest 2.4e-4 at |w| near
+    2^-5); anything beyond two ulps (a binade boundary can sit between the two values), or more than
+    0.1 % of the entries, is a real divergence."""
     diff = (a - b).abs()
-    ulp = a.abs().clamp_min(2.0 ** -14) * 2.0 ** -7
+    ulp = torch.maximum(a.abs(), b.abs()).clamp_min(2.0 ** -14) * 2.0 ** -6
     msg = (f"ranks disagree: max |dw| {float(diff.max()):.3e}, {int((diff > 0).sum())} of {diff.numel()} "
            f"entries differ, |w| max {float(a.abs().max()):.3e}")
     assert bool((diff <= ulp).all()) and int((diff > 0).sum()) <= diff.numel() // 1000, msg

@@ -49,14 +49,16 @@ CONFIGS = {
     # test-time-training evaluation: every 256-token chunk is scored, then one SGD step on log_a and the delta
     # projection is taken on it from the same carried state; adapted weights are restored after each document
     "eval_ttt": dict(dim=256, layers=4, ff_mult=2, seq=512, batch=1024, dist_muon=False, fp8=False),
+    # both implementations from identical initial weights on identical batches: per-step loss curves
+    "parity": dict(dim=256, layers=4, ff_mult=2, seq=512, batch=1024, dist_muon=False, fp8=False),
 }
 
 
 def _parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=BATCH, help=argparse.SUPPRESS)
     ap.add_argument("--seq", type=int, default=SEQ, help=argparse.SUPPRESS)
@@ -72,6 +74,14 @@ def _parse():
         if a.seq == SEQ:
             a.seq = cfg["seq"]
     a.dist_muon = bool(cfg["dist_muon"])
+    # defaults: the headline protocol (200 timed steps after 20 warm-up); the other configurations
+    # have longer steps (a whole evaluation pass is one step) and get counts that end within minutes
+    d_steps, d_warm = {"submission": (200, 20), "fp8": (100, 10), "scaled": (50, 10), "eval": (5, 3),
+                       "eval_ttt": (3, 2), "parity": (200, 0)}[a.config]
+    if a.steps is None:
+        a.steps = d_steps
+    if a.warmup is None:
+        a.warmup = d_warm
     return a
 
 
@@ -117,21 +127,31 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(self.rows)}
 
 
-def _make_batches(n_steps: int, batch: int, seq: int, rank: int):
-    """Pinned-host int64 Zipf(1.1) windows, one [batch, seq + 1] block per step, per-rank seed."""
+def _make_batches(n_steps: int, batch: int, seq: int, rank: int, distinct: int = 8):
+    """Pinned-host int64 Zipf(1.1) windows, one [batch, seq + 1] block per step, per-rank seed
+    (``distinct`` different blocks, cycled)."""
     import numpy as np
     import torch
     ranks = np.arange(1, VOCAB + 1, dtype=np.float64)
     cdf = np.cumsum(ranks ** (-1.1))
     cdf /= cdf[-1]
     rng = np.random.default_rng(1234 + rank)
-    n_distinct = min(n_steps, 8)
+    n_distinct = min(n_steps, distinct)
     blocks = []
     for _ in range(n_distinct):
         ids = np.searchsorted(cdf, rng.random(batch * (seq + 1)), side="left").clip(0, VOCAB - 1)
         t = torch.from_numpy(ids.astype(np.int64)).view(batch, seq + 1)
         blocks.append(t.pin_memory() if torch.cuda.is_available() else t)
     return [blocks[i % n_distinct] for i in range(n_steps)]
+
+
+def _train_config(args, ws: int, nparams: int, sharded_muon: bool) -> dict:
+    """The workload description, printed identically by both arms (``--impl ours|reference``)."""
+    return {"model": f"CareStudentLM {LAYERS}x{DIM} V{VOCAB} ff_mult {FF_MULT}", "params": int(nparams),
+            "global_batch": ws * args.batch, "seq_len": args.seq,
+            "parallelism": f"dp{ws}" + (" + Muon sharded by matrix ownership" if sharded_muon else ""),
+            "optimizer": f"Muon lr {LR} wd {WD} clip {CLIP}",
+            "l2": "working set per step (>10 GB of activations) exceeds the 126 MB L2"}
 
 
 def _dist_setup(args):
@@ -200,15 +220,27 @@ def run_ours(args):
     model = model.to(dev).to(torch.bfloat16)
     arena = ParamArena.install(model)
     model.train()
+    collective = "none (one GPU)"
     if ws > 1:
+        # the product is the in-kernel peer-memory exchange: refuse to time a library fallback
         from chaoscontrol_b200.parallel import symm_comm
-        symm_comm.try_enable(arena.flat_grad.numel())
+        symm_comm.enable(arena.flat_grad.numel())
         broadcast_params(model)
     opt = Muon(model.parameters(), lr=LR, weight_decay=WD, adamw_lr=LR, adamw_weight_decay=WD, fused=True)
     opt.bind_arena(arena)
     engine = _engine_for(model)
     if engine is None:
         raise RuntimeError("kernel training engine unavailable: refusing to bench a fallback path")
+    reducer = None
+    if ws > 1 and not args.dist_muon:
+        from chaoscontrol_b200.parallel.grad_overlap import reducer_for
+        reducer = reducer_for(engine, ws)
+        if reducer is None:
+            raise RuntimeError("overlapped peer-memory gradient exchange unavailable: refusing to bench a fallback")
+        collective = (f"peer-oneshot over CUDA-IPC symmetric buffers, {reducer.n_buckets} buckets overlapped "
+                      "with backward")
+    elif ws > 1:
+        collective = "peer-memory reduce of owned ranges + parameter gather (distributed Muon)"
     dist_opt = None
     if args.dist_muon and ws > 1:
         from chaoscontrol_b200.parallel import symm
@@ -224,12 +256,12 @@ def run_ours(args):
 
     def step_resident(i):
         j = i % len(dev_in)
-        loss = engine.step(dev_in[j], dev_tg[j])
+        loss = engine.step(dev_in[j], dev_tg[j], reducer=reducer)
         if dist_opt is not None:
             dist_opt.step()
         else:
             if ws > 1:
-                allreduce_grads(model, ws)
+                allreduce_grads(model, ws)           # no-op: the reducer ran inside the step
             clip_arena_grad_norm(arena, CLIP)
             opt.step()
         losses.append(loss)
@@ -283,18 +315,17 @@ def run_ours(args):
            "data": "synthetic Zipf(1.1) tokens, random-init weights",
            "impl": "ours", "final_loss": final_loss, "gpu_launches": launches,
            "clocks": cs.summary(), "e2e": e2e,
-           "config": {"model": f"CareStudentLM {LAYERS}x{DIM} V{VOCAB} ff_mult {FF_MULT}", "params": nparams,
-                      "global_batch": ws * args.batch, "seq_len": args.seq,
-                      "parallelism": f"dp{ws}" + (" + Muon sharded by matrix ownership" if dist_opt is not None else ""),
-                      "optimizer": f"Muon lr {LR} wd {WD} clip {CLIP}",
-                      "lm_head": ("fused tcgen05 linear+CE, logits recomputed in backward" if DIM == 256 else
-                                  "tcgen05 GEMM-epilogue linear+CE (lse partials; chunked softmax-gradient tiles)"),
-                      "l2": "working set per step (>10 GB of activations) exceeds the 126 MB L2",
-                      "vs_baseline_ref": "reference 8xH100 headline 25,023,217 tok/s scaled by n_gpus/8"}}
+           "config": _train_config(args, ws, nparams, dist_opt is not None),
+           "impl_detail": {"lm_head": ("fused tcgen05 linear+CE, logits recomputed in backward" if DIM == 256 else
+                                       "tcgen05 GEMM-epilogue linear+CE (lse partials; chunked softmax-gradient tiles)"),
+                           "collective": collective,
+                           "vs_baseline_ref": "reference 8xH100 headline 25,023,217 tok/s scaled by n_gpus/8"}}
     if rank == 0:
         print(json.dumps(out), flush=True)
     if ws > 1:
         import torch.distributed as dist
+        from chaoscontrol_b200.parallel import symm_comm
+        symm_comm.disable()
         dist.destroy_process_group()
 
 
@@ -560,6 +591,102 @@ def run_fp8(args):
 
 
 # ---------------------------------------------------------------------------
+def run_parity(args):
+    """Loss curves of both implementations from the SAME initial weights on the SAME batches, one GPU.
+
+    The reference model is built first (seed 0); its ``state_dict`` is loaded, strictly, into this
+    package's model, so both arms start from identical bf16 weights.  Every arm then runs the
+    headline recipe (Muon lr 0.064, wd 0.01, clip 1.0) for ``--steps`` steps on the same Zipf(1.1)
+    batches and the per-step training losses are compared.  This package runs twice: with the
+    one-sweep LM head (default) and with the two-sweep one.  Prints one JSON line."""
+    import torch
+    ref = ROOT / "baseline" / "_ref"
+    if not (ref / "chaoscontrol").exists():
+        print(json.dumps({"config": "parity", "unavailable": "baseline/_ref is missing"}))
+        return
+    sys.path.insert(0, str(ref))
+    sys.path.insert(0, str(ROOT))
+    os.environ.setdefault("CHAOSCONTROL_DIAG_SCAN_BACKEND", "ssm_scan")
+    from chaoscontrol.distributed import clip_grad_norm_fused as ref_clip
+    from chaoscontrol.model import CareStudentLM as RefLM
+    from chaoscontrol.optim.muon import Muon as RefMuon
+    from chaoscontrol.train_ssm import train_ssm_step as ref_step
+    from chaoscontrol_b200.models.model import CareStudentLM
+    from chaoscontrol_b200.ops import _lib
+    from chaoscontrol_b200.ops import lm_head as LH
+    from chaoscontrol_b200.optim.muon import Muon
+    from chaoscontrol_b200.parallel.distributed import clip_arena_grad_norm
+    from chaoscontrol_b200.train_ssm import _engine_for
+    from chaoscontrol_b200.utils.arena import ParamArena
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    n = args.steps
+    host = _make_batches(n, args.batch, args.seq, 0, distinct=n)
+    torch.manual_seed(0)
+    rmodel = RefLM(vocab_size=VOCAB, dim=DIM, num_layers=LAYERS, ff_mult=FF_MULT).to(dev).to(torch.bfloat16)
+    init = {k: v.detach().clone() for k, v in rmodel.state_dict().items()}
+    rmodel.train()
+    ropt = RefMuon(rmodel.parameters(), lr=LR, weight_decay=WD, adamw_lr=LR, adamw_weight_decay=WD, fused=True)
+    ropt.bind_param_names(list(rmodel.named_parameters()))
+    ref_losses = []
+    for i in range(n):
+        blk = host[i].to(dev, non_blocking=True)
+        ropt.zero_grad(set_to_none=True)
+        loss = ref_step(rmodel, blk[:, :-1].to(torch.int32), blk[:, 1:], 64, ddp_active=False, world_size=1,
+                        precision="bf16", lm_head_backward_mode="fused_streaming_cached", lm_head_tile_size=8192)
+        ref_clip(rmodel.parameters(), CLIP)
+        ropt.step()
+        ref_losses.append(loss.detach().float())
+    ref_curve = torch.stack(ref_losses).cpu().tolist()
+    del rmodel, ropt
+    torch.cuda.empty_cache()
+
+    def ours(one_sweep: bool):
+        LH.ONE_SWEEP = bool(one_sweep)
+        model = CareStudentLM(vocab_size=VOCAB, dim=DIM, num_layers=LAYERS, ff_mult=FF_MULT).to(dev).to(torch.bfloat16)
+        missing = model.load_state_dict(init, strict=True)
+        assert not missing.missing_keys and not missing.unexpected_keys
+        arena = ParamArena.install(model)
+        model.train()
+        opt = Muon(model.parameters(), lr=LR, weight_decay=WD, adamw_lr=LR, adamw_weight_decay=WD, fused=True)
+        opt.bind_arena(arena)
+        eng = _engine_for(model)
+        if eng is None:
+            raise RuntimeError("kernel training engine unavailable")
+        out = []
+        for i in range(n):
+            blk = host[i].to(dev, non_blocking=True)
+            loss = eng.step(blk[:, :-1].to(torch.int32).contiguous(), blk[:, 1:].contiguous())
+            clip_arena_grad_norm(arena, CLIP)
+            opt.step()
+            out.append(loss.detach().float())
+        _lib.assert_ok()
+        curve = torch.stack(out).cpu().tolist()
+        del model, opt, eng, arena
+        torch.cuda.empty_cache()
+        return curve
+
+    curves = {"reference": ref_curve, "ours_one_sweep": ours(True), "ours_two_sweeps": ours(False),
+              "ours_one_sweep_again": ours(True)}
+
+    def cmp(a, b):
+        d = [abs(x - y) for x, y in zip(a, b)]
+        tail = max(1, len(d) // 10)
+        return {"max_abs": max(d), "mean_abs": sum(d) / len(d), "final_abs": d[-1],
+                "mean_abs_last_tenth": sum(d[-tail:]) / tail, "first_step_abs": d[0]}
+
+    out = {"config": "parity", "steps": n, "model": f"CareStudentLM {LAYERS}x{DIM} V{VOCAB} ff_mult {FF_MULT}",
+           "global_batch": args.batch, "seq_len": args.seq, "optimizer": f"Muon lr {LR} wd {WD} clip {CLIP}",
+           "init": "reference model, torch.manual_seed(0), state_dict loaded strictly into this package's model",
+           "vs_reference": {k: cmp(v, ref_curve) for k, v in curves.items() if k != "reference"},
+           "one_vs_two_sweeps": cmp(curves["ours_one_sweep"], curves["ours_two_sweeps"]),
+           "rerun_identical": curves["ours_one_sweep"] == curves["ours_one_sweep_again"],
+           "curves": {k: [round(x, 5) for x in v] for k, v in curves.items() if k != "ours_one_sweep_again"}}
+    print(json.dumps(out), flush=True)
+
+
+# ---------------------------------------------------------------------------
 def run_reference(args):
     ref = ROOT / "baseline" / "_ref"
     if not (ref / "chaoscontrol").exists():
@@ -643,10 +770,9 @@ def run_reference(args):
            "vs_baseline": toks / (BASELINE_TOKS_8XH100 * ws / 8.0), "dtype": "bf16",
            "data": "synthetic Zipf(1.1) tokens, random-init weights", "impl": "reference",
            "final_loss": final_loss, "clocks": cs.summary(), "e2e": e2e,
-           "config": {"model": f"CareStudentLM {LAYERS}x{DIM} V{VOCAB} ff_mult {FF_MULT}",
-                      "global_batch": ws * args.batch, "seq_len": args.seq, "parallelism": f"dp{ws}",
-                      "optimizer": f"Muon lr {LR} wd {WD} clip {CLIP}", "lm_head": mode,
-                      "scan_backend": os.environ.get("CHAOSCONTROL_DIAG_SCAN_BACKEND")}}
+           "config": _train_config(args, ws, sum(p.numel() for p in model.parameters()), False),
+           "impl_detail": {"lm_head": mode, "scan_backend": os.environ.get("CHAOSCONTROL_DIAG_SCAN_BACKEND"),
+                           "collective": "NCCL (torch.distributed)" if ws > 1 else "none"}}
     if rank == 0:
         print(json.dumps(out), flush=True)
     if ws > 1:
@@ -656,7 +782,9 @@ def run_reference(args):
 
 if __name__ == "__main__":
     a = _parse()
-    if a.config == "eval":
+    if a.config == "parity":
+        run_parity(a)
+    elif a.config == "eval":
         run_eval(a)
     elif a.config == "eval_ttt":
         run_eval_ttt(a)

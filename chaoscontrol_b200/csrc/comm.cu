@@ -35,8 +35,13 @@ struct PeerPtrs {
   float* buf2[COMM_MAX_RANKS];          // fp32 reduced-slice staging (two-shot)
   uint32_t* pad[COMM_MAX_RANKS];        // signal pads: [4][COMM_MAX_RANKS] uint32 each
 };
+struct CommRange {
+  long long off8, len8;
+  int owner, pad;
+};
 // pad rows: 0 = "packed epoch e", 1 = "done reading the packed data of epoch e",
-// 2 = "slice reduced / owned parameters published, epoch e", 3 = "epoch e finished: my buffer may be reused"
+// 2 = "slice reduced / owned parameters published, epoch e", 3 = "epoch e finished: my buffer may be reused",
+// 4 / 5 = stop-flag words of even / odd sequence numbers (comm_flag_max_kernel).  A pad is 8 rows.
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -84,8 +89,12 @@ __device__ __forceinline__ bool wait_all_peers(const uint32_t* my_pad, int row, 
 }
 
 // Last block to arrive publishes `epoch` into row `row`, column `rank` of every peer's pad.
+// Every block arrives, also one whose flag wait ran out (`ok` false): the arrival counter then
+// still returns to zero for the next launch, and nothing is published for an epoch whose data
+// this rank did not produce.
 __device__ __forceinline__ void last_block_signal(unsigned* counter, const PeerPtrs& pp, int row,
-                                                  int rank, int ws, uint32_t epoch, int row2 = -1) {
+                                                  int rank, int ws, uint32_t epoch, int row2 = -1,
+                                                  bool ok = true) {
   __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -93,9 +102,11 @@ __device__ __forceinline__ void last_block_signal(unsigned* counter, const PeerP
     if (old == gridDim.x - 1) {
       *counter = 0;
       __threadfence_system();
-      for (int p = 0; p < ws; ++p) {
-        st_release_sys(pp.pad[p] + row * COMM_MAX_RANKS + rank, epoch);
-        if (row2 >= 0) st_release_sys(pp.pad[p] + row2 * COMM_MAX_RANKS + rank, epoch);
+      if (ok) {
+        for (int p = 0; p < ws; ++p) {
+          st_release_sys(pp.pad[p] + row * COMM_MAX_RANKS + rank, epoch);
+          if (row2 >= 0) st_release_sys(pp.pad[p] + row2 * COMM_MAX_RANKS + rank, epoch);
+        }
       }
     }
   }
@@ -106,7 +117,10 @@ comm_pack_kernel(const float* __restrict__ grad, long long n, float scale, PeerP
                  int ws, uint32_t epoch, unsigned* counter, uint64_t limit_ns, int* status) {
   __shared__ int sm_ok;
   // peers must have finished with everything I staged in the previous epoch
-  if (!wait_all_peers(pp.pad[rank], 3, ws, epoch - 1, limit_ns, status, &sm_ok)) return;
+  if (!wait_all_peers(pp.pad[rank], 3, ws, epoch - 1, limit_ns, status, &sm_ok)) {
+    last_block_signal(counter, pp, 0, rank, ws, epoch, -1, false);   // count the arrival, publish nothing
+    return;
+  }
   __nv_bfloat16* out = pp.buf[rank];
   const long long n8 = n / 8;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8;
@@ -135,7 +149,10 @@ __global__ void __launch_bounds__(COMM_THREADS)
 comm_oneshot_kernel(float* __restrict__ grad, long long n, PeerPtrs pp, int rank, int ws,
                     uint32_t epoch, unsigned* counter, uint64_t limit_ns, int* status) {
   __shared__ int sm_ok;
-  if (!wait_all_peers(pp.pad[rank], 0, ws, epoch, limit_ns, status, &sm_ok)) return;
+  if (!wait_all_peers(pp.pad[rank], 0, ws, epoch, limit_ns, status, &sm_ok)) {
+    last_block_signal(counter, pp, 1, rank, ws, epoch, 3, false);   // count the arrival, publish nothing
+    return;
+  }
   const long long n8 = n / 8;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8;
        i += (long long)gridDim.x * blockDim.x) {
@@ -158,7 +175,10 @@ __global__ void __launch_bounds__(COMM_THREADS)
 comm_reduce_scatter_kernel(long long n, PeerPtrs pp, int rank, int ws, uint32_t epoch,
                            unsigned* counter, uint64_t limit_ns, int* status) {
   __shared__ int sm_ok;
-  if (!wait_all_peers(pp.pad[rank], 0, ws, epoch, limit_ns, status, &sm_ok)) return;
+  if (!wait_all_peers(pp.pad[rank], 0, ws, epoch, limit_ns, status, &sm_ok)) {
+    last_block_signal(counter, pp, 2, rank, ws, epoch, -1, false);   // count the arrival, publish nothing
+    return;
+  }
   const long long slice8 = (n / 8) / ws;           // host guarantees divisibility
   const long long base = (long long)rank * slice8;
   float* out = pp.buf2[rank];
@@ -183,7 +203,10 @@ __global__ void __launch_bounds__(COMM_THREADS)
 comm_all_gather_kernel(float* __restrict__ grad, long long n, PeerPtrs pp, int rank, int ws,
                        uint32_t epoch, unsigned* counter, uint64_t limit_ns, int* status) {
   __shared__ int sm_ok;
-  if (!wait_all_peers(pp.pad[rank], 2, ws, epoch, limit_ns, status, &sm_ok)) return;
+  if (!wait_all_peers(pp.pad[rank], 2, ws, epoch, limit_ns, status, &sm_ok)) {
+    last_block_signal(counter, pp, 1, rank, ws, epoch, 3, false);   // count the arrival, publish nothing
+    return;
+  }
   const long long slice4 = (n / 4) / ws;
   const long long total4 = slice4 * ws;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total4;
@@ -211,17 +234,16 @@ comm_all_gather_kernel(float* __restrict__ grad, long long n, PeerPtrs pp, int r
 //   gather_params      every other owner's ranges, from its staging buffer, into
 //                      my flat parameters, rows 1 + 3
 // ---------------------------------------------------------------------------
-struct CommRange {
-  long long off8, len8;
-  int owner, pad;
-};
 
 __global__ void __launch_bounds__(COMM_THREADS)
 comm_reduce_ranges_kernel(float* __restrict__ grad, const CommRange* __restrict__ ranges, int nranges,
                           PeerPtrs pp, int rank, int ws, uint32_t epoch, unsigned* counter,
                           uint64_t limit_ns, int* status) {
   __shared__ int sm_ok;
-  if (!wait_all_peers(pp.pad[rank], 0, ws, epoch, limit_ns, status, &sm_ok)) return;
+  if (!wait_all_peers(pp.pad[rank], 0, ws, epoch, limit_ns, status, &sm_ok)) {
+    last_block_signal(counter, pp, 1, rank, ws, epoch, -1, false);   // count the arrival, publish nothing
+    return;
+  }
   for (int r = 0; r < nranges; ++r) {
     const CommRange rg = ranges[r];
     if (rg.owner >= 0 && rg.owner != rank) continue;
@@ -249,7 +271,10 @@ comm_publish_params_kernel(const __nv_bfloat16* __restrict__ param, const CommRa
                            uint64_t limit_ns, int* status) {
   __shared__ int sm_ok;
   // my staging buffer still holds gradients until every peer has read them
-  if (!wait_all_peers(pp.pad[rank], 1, ws, epoch, limit_ns, status, &sm_ok)) return;
+  if (!wait_all_peers(pp.pad[rank], 1, ws, epoch, limit_ns, status, &sm_ok)) {
+    last_block_signal(counter, pp, 2, rank, ws, epoch, -1, false);   // count the arrival, publish nothing
+    return;
+  }
   uint4* out = reinterpret_cast<uint4*>(pp.buf[rank]);
   for (int r = 0; r < nranges; ++r) {
     const CommRange rg = ranges[r];
@@ -266,7 +291,10 @@ comm_gather_params_kernel(__nv_bfloat16* __restrict__ param, const CommRange* __
                           int nranges, PeerPtrs pp, int rank, int ws, uint32_t epoch, unsigned* counter,
                           uint64_t limit_ns, int* status) {
   __shared__ int sm_ok;
-  if (!wait_all_peers(pp.pad[rank], 2, ws, epoch, limit_ns, status, &sm_ok)) return;
+  if (!wait_all_peers(pp.pad[rank], 2, ws, epoch, limit_ns, status, &sm_ok)) {
+    last_block_signal(counter, pp, 3, rank, ws, epoch, -1, false);   // count the arrival, publish nothing
+    return;
+  }
   for (int r = 0; r < nranges; ++r) {
     const CommRange rg = ranges[r];
     if (rg.owner < 0 || rg.owner == rank || rg.owner >= ws) continue;
@@ -276,6 +304,149 @@ comm_gather_params_kernel(__nv_bfloat16* __restrict__ param, const CommRange* __
       reinterpret_cast<uint4*>(param)[rg.off8 + i] = ld_relaxed_sys_v4(src + rg.off8 + i);
   }
   last_block_signal(counter, pp, 3, rank, ws, epoch);
+}
+
+// ---------------------------------------------------------------------------
+// Bucketed exchange, overlapped with backward.  A bucket is a slice [r0, r1) of a
+// device range table (units of 8 elements, disjoint ranges of the flat gradient).
+// Each bucket is a complete one-shot all-reduce with its own epoch, launched on a
+// side stream as soon as the backward pass has produced the bucket's gradients,
+// with a small grid of small blocks so that it shares the GPU with the GEMMs of
+// the layers still to come instead of displacing them.
+// ---------------------------------------------------------------------------
+constexpr int COMM_BUCKET_THREADS = 256;
+
+__global__ void __launch_bounds__(COMM_BUCKET_THREADS)
+comm_pack_ranges_kernel(const float* __restrict__ grad, const CommRange* __restrict__ ranges, int r0,
+                        int r1, float scale, PeerPtrs pp, int rank, int ws, uint32_t epoch,
+                        unsigned* counter, uint64_t limit_ns, int* status) {
+  __shared__ int sm_ok;
+  if (!wait_all_peers(pp.pad[rank], 3, ws, epoch - 1, limit_ns, status, &sm_ok)) {
+    last_block_signal(counter, pp, 0, rank, ws, epoch, -1, false);
+    return;
+  }
+  uint4* out = reinterpret_cast<uint4*>(pp.buf[rank]);
+  for (int r = r0; r < r1; ++r) {
+    const CommRange rg = ranges[r];
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < rg.len8;
+         i += (long long)gridDim.x * blockDim.x) {
+      const long long e = rg.off8 + i;
+      const float4 a = reinterpret_cast<const float4*>(grad)[2 * e];
+      const float4 b = reinterpret_cast<const float4*>(grad)[2 * e + 1];
+      uint4 q;
+      q.x = pack_bf16x2(a.x * scale, a.y * scale);
+      q.y = pack_bf16x2(a.z * scale, a.w * scale);
+      q.z = pack_bf16x2(b.x * scale, b.y * scale);
+      q.w = pack_bf16x2(b.z * scale, b.w * scale);
+      out[e] = q;
+    }
+  }
+  last_block_signal(counter, pp, 0, rank, ws, epoch);
+}
+
+__global__ void __launch_bounds__(COMM_BUCKET_THREADS)
+comm_oneshot_ranges_kernel(float* __restrict__ grad, const CommRange* __restrict__ ranges, int r0, int r1,
+                           PeerPtrs pp, int rank, int ws, uint32_t epoch, unsigned* counter,
+                           uint64_t limit_ns, int* status) {
+  __shared__ int sm_ok;
+  if (!wait_all_peers(pp.pad[rank], 0, ws, epoch, limit_ns, status, &sm_ok)) {
+    last_block_signal(counter, pp, 1, rank, ws, epoch, 3, false);
+    return;
+  }
+  for (int r = r0; r < r1; ++r) {
+    const CommRange rg = ranges[r];
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < rg.len8;
+         i += (long long)gridDim.x * blockDim.x) {
+      const long long e = rg.off8 + i;
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      uint4 q[COMM_MAX_RANKS];
+#pragma unroll
+      for (int p = 0; p < COMM_MAX_RANKS; ++p)
+        if (p < ws) q[p] = ld_relaxed_sys_v4(reinterpret_cast<const uint4*>(pp.buf[p]) + e);
+#pragma unroll
+      for (int p = 0; p < COMM_MAX_RANKS; ++p)
+        if (p < ws) acc_bf16x8(acc, q[p]);
+      reinterpret_cast<float4*>(grad)[2 * e] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      reinterpret_cast<float4*>(grad)[2 * e + 1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    }
+  }
+  last_block_signal(counter, pp, 1, rank, ws, epoch, 3);
+}
+
+// ---------------------------------------------------------------------------
+// Broadcast through the symmetric buffers (parameter broadcast at start-up, coalesced
+// parameter refresh): the root stages `n16` 16-byte words and raises flag row 0; every
+// other rank waits for the ROOT's flag only, copies the words out of the root's buffer
+// and, like the root, reports rows 1 and 3 ("done with the staged data of this epoch").
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(COMM_THREADS)
+comm_bcast_put_kernel(const uint4* __restrict__ src, long long n16, PeerPtrs pp, int rank, int ws,
+                      uint32_t epoch, unsigned* counter, uint64_t limit_ns, int* status) {
+  __shared__ int sm_ok;
+  if (!wait_all_peers(pp.pad[rank], 3, ws, epoch - 1, limit_ns, status, &sm_ok)) {
+    last_block_signal(counter, pp, 0, rank, ws, epoch, -1, false);
+    return;
+  }
+  uint4* out = reinterpret_cast<uint4*>(pp.buf[rank]);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n16;
+       i += (long long)gridDim.x * blockDim.x)
+    out[i] = src[i];
+  last_block_signal(counter, pp, 0, rank, ws, epoch);
+}
+
+__global__ void __launch_bounds__(COMM_THREADS)
+comm_bcast_get_kernel(uint4* __restrict__ dst, long long n16, int root, PeerPtrs pp, int rank, int ws,
+                      uint32_t epoch, unsigned* counter, uint64_t limit_ns, int* status) {
+  __shared__ int sm_ok;
+  if (threadIdx.x == 0)
+    sm_ok = wait_flag(pp.pad[rank] + 0 * COMM_MAX_RANKS + root, epoch, limit_ns, status) ? 1 : 0;
+  __syncthreads();
+  if (!sm_ok) {
+    last_block_signal(counter, pp, 1, rank, ws, epoch, 3, false);
+    return;
+  }
+  if (rank != root) {
+    const uint4* src = reinterpret_cast<const uint4*>(pp.buf[root]);
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n16;
+         i += (long long)gridDim.x * blockDim.x)
+      dst[i] = ld_relaxed_sys_v4(src + i);
+  }
+  last_block_signal(counter, pp, 1, rank, ws, epoch, 3);
+}
+
+// ---------------------------------------------------------------------------
+// Stop-flag consensus (maximum of one small integer per rank) through the signal pads:
+// no collective library call and no buffer traffic.  Rows 4 and 5 alternate by the
+// sequence number's parity, word = (seq << 8) | value: a rank can run at most one
+// sequence ahead of the slowest peer, so the word a late reader wants is never overwritten.
+// One warp; lane p talks to rank p.  out[0] = max over ranks, or -1 after a timeout.
+// ---------------------------------------------------------------------------
+__global__ void comm_flag_max_kernel(int value, PeerPtrs pp, int rank, int ws, uint32_t seq, int* out,
+                                     uint64_t limit_ns, int* status) {
+  const int p = threadIdx.x;
+  const int row = 4 + (int)(seq & 1u);
+  const uint32_t word = (seq << 8) | (uint32_t)(value & 0xFF);
+  int got = 0;
+  bool ok = true;
+  if (p < ws) {
+    st_release_sys(pp.pad[p] + row * COMM_MAX_RANKS + rank, word);
+    const uint32_t* mine = pp.pad[rank] + row * COMM_MAX_RANKS + p;
+    const uint64_t t0 = globaltimer_ns();
+    while (true) {
+      const uint32_t w = ld_acquire_sys(mine);
+      if ((((w >> 8) - seq) & 0xFFFFFFu) < 0x800000u) { got = (int)(w & 0xFFu); break; }
+      if (globaltimer_ns() - t0 > limit_ns) {
+        atomicCAS(status, CCB_OK, CCB_ERR_PEER_TIMEOUT);
+        ok = false;
+        break;
+      }
+      __nanosleep(64);
+    }
+  }
+  const bool all_ok = __all_sync(0xffffffffu, ok);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) got = max(got, __shfl_xor_sync(0xffffffffu, got, o));
+  if (p == 0) out[0] = all_ok ? got : -1;
 }
 
 }  // namespace ccb
@@ -318,7 +489,8 @@ extern "C" int ccb_ipc_close(void* p) {
 }
 
 // bufs / bufs2 / pads: host arrays of `ws` device pointers (peer-mapped; index
-// `rank` is this rank's own allocation).  counters: 4 device uint32, zeroed.
+// `rank` is this rank's own allocation).  counters: 16 device uint32, zeroed (one arrival
+// counter per kernel of this file).
 // mode 0 = one-shot, 1 = two-shot.  n must be a multiple of 8 * ws.
 extern "C" int ccb_allreduce(float* grad, int64_t n, float scale, void* const* bufs,
                              void* const* bufs2, void* const* pads, int64_t rank, int64_t ws,
@@ -404,6 +576,81 @@ extern "C" int ccb_sharded_sync(int64_t phase, float* grad, void* param, int64_t
   }
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : set_error("sharded sync launch: %s", cudaGetErrorString(e));
+}
+
+// One bucket of the overlapped exchange: pack + one-shot reduce of ranges [r0, r1) of the device
+// table (records {int64 off8, int64 len8, int32 owner, int32 pad}; owner is ignored here) on
+// `stream`, with `blocks` blocks of 256 threads per kernel (0: one block per SM).
+extern "C" int ccb_allreduce_ranges(float* grad, const void* ranges, int64_t r0, int64_t r1, float scale,
+                                    void* const* bufs, void* const* bufs2, void* const* pads, int64_t rank,
+                                    int64_t ws, int64_t epoch, void* counters, int64_t blocks,
+                                    int64_t timeout_ms, void* stream) {
+  if (ws < 1 || ws > COMM_MAX_RANKS) return set_error("ccb_allreduce_ranges: world size %lld unsupported", (long long)ws);
+  if (r1 <= r0) return 0;
+  PeerPtrs pp;
+  fill_peers(pp, bufs, bufs2, pads, ws);
+  cudaStream_t s = (cudaStream_t)stream;
+  unsigned* ctr = (unsigned*)counters;
+  int* status = ccb_status_ptr();
+  const uint64_t limit = (uint64_t)(timeout_ms > 0 ? timeout_ms : 2000) * 1000000ull;
+  const int grid = (int)(blocks > 0 ? blocks : ccb_num_sms());
+  const CommRange* rg = reinterpret_cast<const CommRange*>(ranges);
+  comm_pack_ranges_kernel<<<grid, COMM_BUCKET_THREADS, 0, s>>>(grad, rg, (int)r0, (int)r1, scale, pp, (int)rank,
+                                                               (int)ws, (uint32_t)epoch, ctr + 8, limit, status);
+  count_launch();
+  comm_oneshot_ranges_kernel<<<grid, COMM_BUCKET_THREADS, 0, s>>>(grad, rg, (int)r0, (int)r1, pp, (int)rank,
+                                                                  (int)ws, (uint32_t)epoch, ctr + 9, limit, status);
+  count_launch();
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : set_error("allreduce_ranges launch: %s", cudaGetErrorString(e));
+}
+
+// Broadcast `nbytes` (a multiple of 16, at most the symmetric buffer) from rank `root`'s `data` into every
+// other rank's `data`.
+extern "C" int ccb_comm_bcast(void* data, int64_t nbytes, int64_t root, void* const* bufs, void* const* bufs2,
+                              void* const* pads, int64_t rank, int64_t ws, int64_t epoch, void* counters,
+                              int64_t timeout_ms, void* stream) {
+  if (ws < 1 || ws > COMM_MAX_RANKS) return set_error("ccb_comm_bcast: world size %lld unsupported", (long long)ws);
+  if (nbytes % 16) return set_error("ccb_comm_bcast: nbytes=%lld must be a multiple of 16", (long long)nbytes);
+  if (root < 0 || root >= ws) return set_error("ccb_comm_bcast: root %lld out of range", (long long)root);
+  PeerPtrs pp;
+  fill_peers(pp, bufs, bufs2, pads, ws);
+  cudaStream_t s = (cudaStream_t)stream;
+  unsigned* ctr = (unsigned*)counters;
+  int* status = ccb_status_ptr();
+  const uint64_t limit = (uint64_t)(timeout_ms > 0 ? timeout_ms : 2000) * 1000000ull;
+  const long long n16 = nbytes / 16;
+  const int sms = ccb_num_sms();
+  long long want = (n16 + COMM_THREADS - 1) / COMM_THREADS;
+  const int grid = (int)(want < sms ? (want < 1 ? 1 : want) : sms);
+  if (rank == root) {
+    comm_bcast_put_kernel<<<grid, COMM_THREADS, 0, s>>>((const uint4*)data, n16, pp, (int)rank, (int)ws,
+                                                        (uint32_t)epoch, ctr + 10, limit, status);
+    count_launch();
+  }
+  comm_bcast_get_kernel<<<grid, COMM_THREADS, 0, s>>>((uint4*)data, n16, (int)root, pp, (int)rank, (int)ws,
+                                                      (uint32_t)epoch, ctr + 11, limit, status);
+  count_launch();
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : set_error("bcast launch: %s", cudaGetErrorString(e));
+}
+
+// out[0] (device int) = max over ranks of `value` (0..255), or -1 when a peer did not answer in time.
+extern "C" int ccb_comm_flag_max(int64_t value, void* const* pads, int64_t rank, int64_t ws, int64_t seq,
+                                 int* out, int64_t timeout_ms, void* stream) {
+  if (ws < 1 || ws > COMM_MAX_RANKS) return set_error("ccb_comm_flag_max: world size %lld unsupported", (long long)ws);
+  PeerPtrs pp;
+  for (int i = 0; i < COMM_MAX_RANKS; ++i) {
+    pp.buf[i] = nullptr;
+    pp.buf2[i] = nullptr;
+    pp.pad[i] = i < ws ? (uint32_t*)pads[i] : nullptr;
+  }
+  const uint64_t limit = (uint64_t)(timeout_ms > 0 ? timeout_ms : 2000) * 1000000ull;
+  comm_flag_max_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((int)value, pp, (int)rank, (int)ws,
+                                                           (uint32_t)seq & 0xFFFFFFu, out, limit, ccb_status_ptr());
+  count_launch();
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : set_error("flag_max launch: %s", cudaGetErrorString(e));
 }
 
 // Single-GPU self-test hook: waits on a flag that nothing sets, with a short

@@ -62,60 +62,159 @@ __global__ void embed_fwd_kernel(const TokT* __restrict__ tok, const __nv_bfloat
 }
 
 // ---------------------------------------------------------------------------
-// Embedding backward over token-sorted rows.  Each warp owns CH consecutive
-// sorted positions, accumulates rows of equal token in registers and flushes
-// with fp32 atomics when the token changes: at most (#chunks + #tokens) * D
-// atomics in total, and hot tokens spread over many warps.
-// dE must be zeroed by the caller (or hold a running accumulation).
+// Embedding backward over token-sorted rows, bit-reproducible (no atomics).
+//
+// Stage 1: each warp owns CH = 32 consecutive sorted positions and sums the
+// rows of each run of equal tokens in position order.  A run that lies wholly
+// inside the chunk has one owner and is stored straight to dE.  A run that
+// continues from the previous chunk or into the next one is written to the
+// chunk's boundary slot instead: slot 0 for a run that starts at the chunk's
+// first position, slot 1 for a run that starts later and runs off its end.
+// Stage 2: one block per token whose rows span several chunks adds the
+// boundary slots of those chunks in chunk order and stores the row of dE.
+// The summation order is a function of the sorted token array alone, so two
+// runs over the same batch give the same bits (the sort must be stable for
+// `perm` itself to be reproducible).  dE must be zeroed by the caller: rows of
+// tokens that do not occur are never written.
 // ---------------------------------------------------------------------------
+constexpr int EMB_CH = 32;
+
 template <int VPL>   // uint4 vectors per lane: D = 256 * VPL
-__global__ void embed_bwd_sorted_kernel(const long long* __restrict__ sorted_tok,
-                                        const long long* __restrict__ perm,
-                                        const __nv_bfloat16* __restrict__ dx,
-                                        float* __restrict__ dE, long long R, int D, int V, int CH) {
+__global__ void embed_bwd_runs_kernel(const long long* __restrict__ sorted_tok,
+                                      const long long* __restrict__ perm,
+                                      const __nv_bfloat16* __restrict__ dx,
+                                      float* __restrict__ dE, float* __restrict__ slots,
+                                      long long R, int D, int V) {
   const long long chunk = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const long long p0 = chunk * CH;
+  const long long p0 = chunk * EMB_CH;
   if (p0 >= R) return;
-  const long long p1 = (p0 + CH < R) ? p0 + CH : R;
+  const long long p1 = (p0 + EMB_CH < R) ? p0 + EMB_CH : R;
   const int lane = threadIdx.x & 31;
+  const int n = (int)(p1 - p0);
+  // one coalesced load of the chunk's tokens and row indices, handed round by shuffles
+  const long long my_tok = (lane < n) ? sorted_tok[p0 + lane] : -1;
+  const long long my_row = (lane < n) ? perm[p0 + lane] : 0;
+  const long long tok_before = (p0 > 0) ? sorted_tok[p0 - 1] : -1;
+  const long long tok_after = (p1 < R) ? sorted_tok[p1] : -1;
   float acc[VPL][8];
 #pragma unroll
   for (int v = 0; v < VPL; ++v)
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[v][i] = 0.f;
-  long long cur = sorted_tok[p0];
-  for (long long p = p0; p < p1; ++p) {
-    const long long tk = sorted_tok[p];
-    if (tk != cur) {
-      if (cur >= 0 && cur < V) {
+  long long cur = __shfl_sync(0xffffffffu, my_tok, 0);
+  int run_start = 0;
+  auto flush = [&](long long tk, int a, int b) {
+    // run of token tk over chunk positions [a, b)
+    if (tk < 0 || tk >= V) return;
+    const bool open_left = (a == 0) && (tok_before == tk);
+    const bool open_right = (b == n) && (tok_after == tk);
+    float* o;
+    if (!open_left && !open_right) o = dE + tk * D;
+    else o = slots + (chunk * 2 + (a == 0 ? 0 : 1)) * (long long)D;
 #pragma unroll
-        for (int v = 0; v < VPL; ++v) {
-          float* o = dE + cur * D + (v * 32 + lane) * 8;
+    for (int v = 0; v < VPL; ++v) {
+      float4* o4 = reinterpret_cast<float4*>(o + (v * 32 + lane) * 8);
+      o4[0] = make_float4(acc[v][0], acc[v][1], acc[v][2], acc[v][3]);
+      o4[1] = make_float4(acc[v][4], acc[v][5], acc[v][6], acc[v][7]);
+    }
+  };
+  for (int j0 = 0; j0 < n; j0 += 4) {
+    // four rows are requested before any is added: the adds stay in position order
+    uint4 q[4][VPL];
+    long long tk[4];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) { atomicAdd(o + i, acc[v][i]); acc[v][i] = 0.f; }
-        }
+    for (int u = 0; u < 4; ++u) {
+      const int j = j0 + u;
+      tk[u] = __shfl_sync(0xffffffffu, my_tok, j & 31);
+      const long long row = __shfl_sync(0xffffffffu, my_row, j & 31);
+      if (j < n) {
+        const uint4* src = reinterpret_cast<const uint4*>(dx + row * D);
+#pragma unroll
+        for (int v = 0; v < VPL; ++v) q[u][v] = __ldg(src + v * 32 + lane);
       }
-      cur = tk;
     }
-    const uint4* src = reinterpret_cast<const uint4*>(dx + perm[p] * D);
 #pragma unroll
-    for (int v = 0; v < VPL; ++v) {
-      uint4 q = __ldg(src + v * 32 + lane);
-      float2 f;
-      f = unpack_bf16x2(q.x); acc[v][0] += f.x; acc[v][1] += f.y;
-      f = unpack_bf16x2(q.y); acc[v][2] += f.x; acc[v][3] += f.y;
-      f = unpack_bf16x2(q.z); acc[v][4] += f.x; acc[v][5] += f.y;
-      f = unpack_bf16x2(q.w); acc[v][6] += f.x; acc[v][7] += f.y;
+    for (int u = 0; u < 4; ++u) {
+      const int j = j0 + u;
+      if (j >= n) break;
+      if (tk[u] != cur) {
+        flush(cur, run_start, j);
+#pragma unroll
+        for (int v = 0; v < VPL; ++v)
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[v][i] = 0.f;
+        cur = tk[u];
+        run_start = j;
+      }
+#pragma unroll
+      for (int v = 0; v < VPL; ++v) {
+        float2 f;
+        f = unpack_bf16x2(q[u][v].x); acc[v][0] += f.x; acc[v][1] += f.y;
+        f = unpack_bf16x2(q[u][v].y); acc[v][2] += f.x; acc[v][3] += f.y;
+        f = unpack_bf16x2(q[u][v].z); acc[v][4] += f.x; acc[v][5] += f.y;
+        f = unpack_bf16x2(q[u][v].w); acc[v][6] += f.x; acc[v][7] += f.y;
+      }
     }
   }
-  if (cur >= 0 && cur < V) {
-#pragma unroll
-    for (int v = 0; v < VPL; ++v) {
-      float* o = dE + cur * D + (v * 32 + lane) * 8;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) atomicAdd(o + i, acc[v][i]);
-    }
+  flush(cur, run_start, n);
+}
+
+// first position p in [0, R) with sorted_tok[p] >= key (R if none)
+__device__ __forceinline__ long long emb_lower_bound(const long long* __restrict__ a, long long R,
+                                                     long long key) {
+  long long lo = 0, hi = R;
+  while (lo < hi) {
+    const long long mid = (lo + hi) >> 1;
+    if (a[mid] < key) lo = mid + 1; else hi = mid;
   }
+  return lo;
+}
+
+// grid: V blocks of 128 threads; thread t owns columns [t * D/128, (t+1) * D/128).
+template <int CPT>   // columns per thread: D = 128 * CPT
+__global__ void embed_bwd_join_kernel(const long long* __restrict__ sorted_tok,
+                                      const float* __restrict__ slots, float* __restrict__ dE,
+                                      long long R, int D) {
+  __shared__ long long se[2];
+  const long long tk = blockIdx.x;
+  if (threadIdx.x == 0) {
+    se[0] = emb_lower_bound(sorted_tok, R, tk);
+    se[1] = emb_lower_bound(sorted_tok, R, tk + 1);
+  }
+  __syncthreads();
+  const long long s = se[0], e = se[1];
+  if (e <= s) return;
+  const long long cs = s / EMB_CH, ce = (e - 1) / EMB_CH;
+  if (cs == ce) return;                       // one owner: stored by stage 1
+  float acc[CPT];
+  const int c0 = threadIdx.x * CPT;
+  {
+    const float* p = slots + (cs * 2 + ((s % EMB_CH) == 0 ? 0 : 1)) * (long long)D + c0;
+#pragma unroll
+    for (int i = 0; i < CPT; ++i) acc[i] = p[i];
+  }
+  long long c = cs + 1;
+  for (; c + 4 <= ce + 1; c += 4) {
+    float t[4][CPT];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const float* p = slots + ((c + u) * 2) * (long long)D + c0;
+#pragma unroll
+      for (int i = 0; i < CPT; ++i) t[u][i] = p[i];
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int i = 0; i < CPT; ++i) acc[i] += t[u][i];
+  }
+  for (; c <= ce; ++c) {
+    const float* p = slots + (c * 2) * (long long)D + c0;
+#pragma unroll
+    for (int i = 0; i < CPT; ++i) acc[i] += p[i];
+  }
+  float* o = dE + tk * D + c0;
+#pragma unroll
+  for (int i = 0; i < CPT; ++i) o[i] = acc[i];
 }
 
 // ---------------------------------------------------------------------------
@@ -150,13 +249,35 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ part, int S, long
   }
 }
 
+// out[k] (+)= sum_b part[b, k].  Block: 32 columns x 32 row groups; group g adds rows g, g+32, ...
+// in order, then the group sums are added in group order: a fixed tree, so the result
+// does not depend on scheduling.
+constexpr int COLSUM_COLS = 32, COLSUM_GROUPS = 32;
 __global__ void colsum_kernel(const float* __restrict__ part, int NB, int K, float* __restrict__ out,
                               int accumulate) {
-  const int k = blockIdx.x * blockDim.x + threadIdx.x;
-  if (k >= K) return;
+  __shared__ float sm[COLSUM_GROUPS][COLSUM_COLS];
+  const int col = threadIdx.x & (COLSUM_COLS - 1), grp = threadIdx.x / COLSUM_COLS;
+  const int k = blockIdx.x * COLSUM_COLS + col;
   float s = 0.f;
-  for (int b = 0; b < NB; ++b) s += part[(long long)b * K + k];
-  out[k] = accumulate ? out[k] + s : s;
+  if (k < K) {
+    int b = grp;
+    for (; b + 3 * COLSUM_GROUPS < NB; b += 4 * COLSUM_GROUPS) {
+      const float v0 = part[(long long)b * K + k];
+      const float v1 = part[(long long)(b + COLSUM_GROUPS) * K + k];
+      const float v2 = part[(long long)(b + 2 * COLSUM_GROUPS) * K + k];
+      const float v3 = part[(long long)(b + 3 * COLSUM_GROUPS) * K + k];
+      s += v0; s += v1; s += v2; s += v3;
+    }
+    for (; b < NB; b += COLSUM_GROUPS) s += part[(long long)b * K + k];
+  }
+  sm[grp][col] = s;
+  __syncthreads();
+  if (grp == 0 && k < K) {
+    float t = sm[0][col];
+#pragma unroll
+    for (int g = 1; g < COLSUM_GROUPS; ++g) t += sm[g][col];
+    out[k] = accumulate ? out[k] + t : t;
+  }
 }
 
 // W'[n,k] = W[n,k] * wn[k]  (bf16), the RMSNorm weight folded into a linear.
@@ -208,18 +329,21 @@ __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
   }
 }
 
-// Backward: gx = inv * (go*w - xhat * mean(go*w*xhat)); weight grad as
-// per-block partials [gridDim.x, D] (deterministic second-stage reduce).
+// Backward: gx = inv * (go*w - xhat * mean(go*w*xhat)); weight grad as per-block partials
+// [gridDim.x, D].  Inside a block every warp adds its rows, in row order, into its own [D] strip of
+// shared memory (a lane owns its columns, so no atomics), the strips are added in warp order, and a
+// second-stage column sum adds the blocks in order: the weight gradient is bit-reproducible.
 __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x,
                                    const __nv_bfloat16* __restrict__ w,
                                    const __nv_bfloat16* __restrict__ go,
                                    const float* __restrict__ inv_rms, __nv_bfloat16* __restrict__ gx,
                                    float* __restrict__ gw_part, long long R, int D,
                                    int rows_per_block) {
-  extern __shared__ float sm_gw[];   // [D]
-  for (int c = threadIdx.x; c < D; c += blockDim.x) sm_gw[c] = 0.f;
-  __syncthreads();
+  extern __shared__ float sm_gw[];   // [warps][D]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  float* mine = sm_gw + warp * D;
+  for (int c = lane; c < D; c += 32) mine[c] = 0.f;
+  __syncwarp();
   const long long r0 = (long long)blockIdx.x * rows_per_block;
   for (long long r = r0 + warp; r < r0 + rows_per_block && r < R; r += nw) {
     const float inv = inv_rms[r];
@@ -238,23 +362,31 @@ __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x,
       const float xh0 = xv.x * inv, xh1 = xv.y * inv;
       *reinterpret_cast<uint32_t*>(gx + r * D + c) =
           pack_bf16x2(inv * (gv.x * wv.x - xh0 * dot), inv * (gv.y * wv.y - xh1 * dot));
-      atomicAdd(&sm_gw[c], gv.x * xh0);       // shared-memory atomics: block-local only
-      atomicAdd(&sm_gw[c + 1], gv.y * xh1);
+      mine[c] += gv.x * xh0;
+      mine[c + 1] += gv.y * xh1;
     }
   }
   __syncthreads();
-  for (int c = threadIdx.x; c < D; c += blockDim.x) gw_part[(long long)blockIdx.x * D + c] = sm_gw[c];
+  for (int c = threadIdx.x; c < D; c += blockDim.x) {
+    float t = sm_gw[c];
+    for (int k = 1; k < nw; ++k) t += sm_gw[k * D + c];
+    gw_part[(long long)blockIdx.x * D + c] = t;
+  }
 }
 
 // ---------------------------------------------------------------------------
 // Optimizer kernels
 // ---------------------------------------------------------------------------
-// Muon momentum: buf = mu*buf + g ; dir = nesterov ? g + mu*buf : buf.  Writes
-// dir in bf16 and accumulates per-matrix sum of squares of the bf16-rounded
-// direction (one atomicAdd per block).  grid: (blocks_per_mat, G).
+// Muon momentum: buf = mu*buf + g ; dir = nesterov ? g + mu*buf : buf.  Writes dir in bf16 and the
+// sum of squares of the bf16-rounded direction of each block's slice to a per-device scratch slot
+// (grid: (blocks_per_mat, G); slot = matrix * blocks_per_mat + block).  No atomics: the normalise
+// kernel adds a matrix's slots in index order, so the Frobenius norm is reproducible.
+constexpr int MUON_PART_SLOTS = 16384;
+__device__ float g_muon_part[MUON_PART_SLOTS];
+
 __global__ void muon_momentum_kernel(const float* __restrict__ g, float* __restrict__ buf,
-                                     __nv_bfloat16* __restrict__ dir, float* __restrict__ sumsq,
-                                     long long numel_per_mat, float mu, int nesterov) {
+                                     __nv_bfloat16* __restrict__ dir, long long numel_per_mat, float mu,
+                                     int nesterov) {
   __shared__ float sm[32];
   const long long base = (long long)blockIdx.y * numel_per_mat;
   float acc = 0.f;
@@ -270,14 +402,20 @@ __global__ void muon_momentum_kernel(const float* __restrict__ g, float* __restr
     acc += qf * qf;
   }
   acc = block_sum(acc, sm);
-  if (threadIdx.x == 0) atomicAdd(sumsq + blockIdx.y, acc);
+  if (threadIdx.x == 0) g_muon_part[blockIdx.y * gridDim.x + blockIdx.x] = acc;
 }
 
-// X = dir / (||dir||_F + eps) in bf16, in place.
-__global__ void muon_normalize_kernel(__nv_bfloat16* __restrict__ dir, const float* __restrict__ sumsq,
-                                      long long numel_per_mat, float eps) {
+// X = dir / (||dir||_F + eps) in bf16, in place; sumsq[matrix] receives the squared norm.
+// `nparts` is the momentum kernel's blocks_per_mat.
+__global__ void muon_normalize_kernel(__nv_bfloat16* __restrict__ dir, float* __restrict__ sumsq,
+                                      int nparts, long long numel_per_mat, float eps) {
+  __shared__ float sm[32];
+  float tot = 0.f;
+  for (int i = threadIdx.x; i < nparts; i += blockDim.x) tot += g_muon_part[blockIdx.y * nparts + i];
+  tot = block_sum(tot, sm);                    // same fixed tree in every block of the matrix
+  if (threadIdx.x == 0 && blockIdx.x == 0) sumsq[blockIdx.y] = tot;
   const long long base = (long long)blockIdx.y * numel_per_mat;
-  const float inv = 1.f / (sqrtf(sumsq[blockIdx.y]) + eps);
+  const float inv = 1.f / (sqrtf(tot) + eps);
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < numel_per_mat;
        i += (long long)gridDim.x * blockDim.x)
     dir[base + i] = __float2bfloat16(__bfloat162float(dir[base + i]) * inv);
@@ -314,23 +452,35 @@ __global__ void adamw_kernel(PT* __restrict__ p, const float* __restrict__ g, fl
   }
 }
 
-// Sum of squares over a flat fp32 range -> out[0] (atomic, caller zeroes).
-__global__ void sumsq_kernel(const float* __restrict__ g, long long n, float* __restrict__ out) {
+// Global L2 norm in two stages with a fixed summation order (no atomics): every block writes
+// the sum of squares of its grid-stride slice to its own slot of a per-device scratch array, and
+// the single-block second stage adds the slots in index order.  Two replicas that hold the same
+// gradient bits therefore compute the same clip coefficient.
+constexpr int SUMSQ_MAX_BLOCKS = 148 * 8;
+__device__ float g_sumsq_part[SUMSQ_MAX_BLOCKS];
+
+__global__ void sumsq_kernel(const float* __restrict__ g, long long n) {
   __shared__ float sm[32];
   float acc = 0.f;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
        i += (long long)gridDim.x * blockDim.x)
     acc += g[i] * g[i];
   acc = block_sum(acc, sm);
-  if (threadIdx.x == 0) atomicAdd(out, acc);
+  if (threadIdx.x == 0) g_sumsq_part[blockIdx.x] = acc;
 }
 
-// clip coefficient = min(1, max_norm / (sqrt(sumsq) + 1e-6)) written to out[1];
-// then g *= coef over the range (second launch reads out[1]).
-__global__ void clip_coef_kernel(float* __restrict__ stat, float max_norm) {
-  const float norm = sqrtf(stat[0]);
-  stat[1] = fminf(1.f, max_norm / (norm + 1e-6f));
-  stat[2] = norm;
+// stat = {sumsq, coef, norm}; coef = min(1, max_norm / (norm + 1e-6)).  One block of 256 threads.
+__global__ void clip_coef_kernel(float* __restrict__ stat, int nparts, float max_norm) {
+  __shared__ float sm[32];
+  float acc = 0.f;
+  for (int i = threadIdx.x; i < nparts; i += blockDim.x) acc += g_sumsq_part[i];
+  acc = block_sum(acc, sm);
+  if (threadIdx.x == 0) {
+    const float norm = sqrtf(acc);
+    stat[0] = acc;
+    stat[1] = fminf(1.f, max_norm / (norm + 1e-6f));
+    stat[2] = norm;
+  }
 }
 __global__ void scale_by_ptr_kernel(float* __restrict__ g, long long n, const float* __restrict__ coef) {
   const float c = *coef;
@@ -413,25 +563,38 @@ extern "C" int ccb_embed_fwd(const void* tok, int64_t tok_is_i64, const void* E,
   return 0;
 }
 
+// slots: workspace of ccb_embed_bwd_slots(R, D) floats (boundary sums of stage 1; need not be zeroed).
+extern "C" int64_t ccb_embed_bwd_slots(int64_t R, int64_t D) {
+  return ((R + EMB_CH - 1) / EMB_CH) * 2 * D;
+}
 extern "C" int ccb_embed_bwd_sorted(const int64_t* sorted_tok, const int64_t* perm, const void* dx,
-                                    float* dE, int64_t R, int64_t D, int64_t V, void* stream) {
+                                    float* dE, float* slots, int64_t R, int64_t D, int64_t V,
+                                    void* stream) {
   if (R <= 0) return 0;
-  const int CH = 32, wpb = 4;
-  const long long chunks = (R + CH - 1) / CH;
+  if (slots == nullptr) return set_error("ccb_embed_bwd_sorted: the boundary-slot workspace is required");
+  const int wpb = 4;
+  const long long chunks = (R + EMB_CH - 1) / EMB_CH;
   const unsigned grid = (unsigned)((chunks + wpb - 1) / wpb);
   cudaStream_t s = (cudaStream_t)stream;
-  if (D == 256)
-    embed_bwd_sorted_kernel<1><<<grid, wpb * 32, 0, s>>>((const long long*)sorted_tok,
-        (const long long*)perm, (const __nv_bfloat16*)dx, dE, R, (int)D, (int)V, CH);
-  else if (D == 512)
-    embed_bwd_sorted_kernel<2><<<grid, wpb * 32, 0, s>>>((const long long*)sorted_tok,
-        (const long long*)perm, (const __nv_bfloat16*)dx, dE, R, (int)D, (int)V, CH);
-  else if (D == 1024)
-    embed_bwd_sorted_kernel<4><<<grid, wpb * 32, 0, s>>>((const long long*)sorted_tok,
-        (const long long*)perm, (const __nv_bfloat16*)dx, dE, R, (int)D, (int)V, CH);
-  else
+  const long long* st = (const long long*)sorted_tok;
+  const long long* pm = (const long long*)perm;
+  const __nv_bfloat16* g = (const __nv_bfloat16*)dx;
+  if (D == 256) {
+    embed_bwd_runs_kernel<1><<<grid, wpb * 32, 0, s>>>(st, pm, g, dE, slots, R, (int)D, (int)V);
+    CCB_CHECK_LAUNCH("embed_bwd_runs");
+    embed_bwd_join_kernel<2><<<(unsigned)V, 128, 0, s>>>(st, slots, dE, R, (int)D);
+  } else if (D == 512) {
+    embed_bwd_runs_kernel<2><<<grid, wpb * 32, 0, s>>>(st, pm, g, dE, slots, R, (int)D, (int)V);
+    CCB_CHECK_LAUNCH("embed_bwd_runs");
+    embed_bwd_join_kernel<4><<<(unsigned)V, 128, 0, s>>>(st, slots, dE, R, (int)D);
+  } else if (D == 1024) {
+    embed_bwd_runs_kernel<4><<<grid, wpb * 32, 0, s>>>(st, pm, g, dE, slots, R, (int)D, (int)V);
+    CCB_CHECK_LAUNCH("embed_bwd_runs");
+    embed_bwd_join_kernel<8><<<(unsigned)V, 128, 0, s>>>(st, slots, dE, R, (int)D);
+  } else {
     return set_error("ccb_embed_bwd_sorted: D=%lld unsupported (256, 512, 1024)", (long long)D);
-  CCB_CHECK_LAUNCH("embed_bwd_sorted");
+  }
+  CCB_CHECK_LAUNCH("embed_bwd_join");
   return 0;
 }
 
@@ -447,8 +610,8 @@ extern "C" int ccb_splitk_reduce(const float* part, int64_t S, int64_t split_str
                                           out, (int)accumulate, W ? colpart : nullptr);
   CCB_CHECK_LAUNCH("splitk_reduce");
   if (W && colpart && colsum_out) {
-    colsum_kernel<<<(unsigned)((K + 127) / 128), 128, 0, s>>>(colpart, (int)nb, (int)K, colsum_out,
-                                                              (int)colsum_accumulate);
+    colsum_kernel<<<(unsigned)((K + COLSUM_COLS - 1) / COLSUM_COLS), COLSUM_COLS * COLSUM_GROUPS, 0, s>>>(
+        colpart, (int)nb, (int)K, colsum_out, (int)colsum_accumulate);
     CCB_CHECK_LAUNCH("colsum");
   }
   return 0;
@@ -457,8 +620,8 @@ extern "C" int ccb_splitk_reduce(const float* part, int64_t S, int64_t split_str
 extern "C" int ccb_colsum(const float* part, int64_t NB, int64_t K, float* out, int64_t accumulate,
                           void* stream) {
   if (K <= 0) return 0;
-  colsum_kernel<<<(unsigned)((K + 127) / 128), 128, 0, (cudaStream_t)stream>>>(part, (int)NB, (int)K,
-                                                                               out, (int)accumulate);
+  colsum_kernel<<<(unsigned)((K + COLSUM_COLS - 1) / COLSUM_COLS), COLSUM_COLS * COLSUM_GROUPS, 0,
+                  (cudaStream_t)stream>>>(part, (int)NB, (int)K, out, (int)accumulate);
   CCB_CHECK_LAUNCH("colsum");
   return 0;
 }
@@ -484,7 +647,9 @@ extern "C" int ccb_rmsnorm_fwd(const void* x, const void* res, const void* w, vo
   return 0;
 }
 
-// gw_part must hold ccb_rmsnorm_bwd_blocks(R) * D floats.
+// gw_part must hold ccb_rmsnorm_bwd_blocks(R) * D floats.  Eight per-warp [D] strips of shared
+// memory bound the channel count (48 KiB without an opt-in).
+constexpr int RMSNORM_BWD_MAX_DIM = 1536;
 extern "C" int64_t ccb_rmsnorm_bwd_blocks(int64_t R) {
   const int64_t rpb = 256;
   return (R + rpb - 1) / rpb;
@@ -495,34 +660,44 @@ extern "C" int ccb_rmsnorm_bwd(const void* x, const void* w, const void* go, con
   if (R <= 0) return 0;
   const int rpb = 256;
   const unsigned nb = (unsigned)ccb_rmsnorm_bwd_blocks(R);
-  rmsnorm_bwd_kernel<<<nb, 256, (size_t)D * sizeof(float), (cudaStream_t)stream>>>(
+  if (D > RMSNORM_BWD_MAX_DIM) return set_error("ccb_rmsnorm_bwd: D=%lld exceeds %d", (long long)D, RMSNORM_BWD_MAX_DIM);
+  rmsnorm_bwd_kernel<<<nb, 256, (size_t)8 * D * sizeof(float), (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)go, inv_rms,
       (__nv_bfloat16*)gx, gw_part, R, (int)D, rpb);
   CCB_CHECK_LAUNCH("rmsnorm_bwd");
   if (gw_out) {
-    colsum_kernel<<<(unsigned)((D + 127) / 128), 128, 0, (cudaStream_t)stream>>>(gw_part, (int)nb,
-                                                                                 (int)D, gw_out, 0);
+    colsum_kernel<<<(unsigned)((D + COLSUM_COLS - 1) / COLSUM_COLS), COLSUM_COLS * COLSUM_GROUPS, 0,
+                    (cudaStream_t)stream>>>(gw_part, (int)nb, (int)D, gw_out, 0);
     CCB_CHECK_LAUNCH("colsum");
   }
   return 0;
 }
 
+static inline int muon_blocks_per_mat(int64_t G, int64_t numel_per_mat) {
+  int cap = (int)(G >= 16 ? 74 : 1184 / G);
+  if ((int64_t)cap * G > MUON_PART_SLOTS) cap = (int)(MUON_PART_SLOTS / G);
+  return grid_for(numel_per_mat, 256, cap < 1 ? 1 : cap);
+}
+// The two calls form one unit: normalize reads the per-block sums the momentum launch left in the
+// per-device scratch, so they must run back to back on one stream with the same (G, numel_per_mat).
 extern "C" int ccb_muon_momentum(const float* g, float* buf, void* dir, float* sumsq, int64_t G,
                                  int64_t numel_per_mat, float mu, int64_t nesterov, void* stream) {
   if (G <= 0 || numel_per_mat <= 0) return 0;
-  cudaStream_t s = (cudaStream_t)stream;
-  cudaMemsetAsync(sumsq, 0, sizeof(float) * (size_t)G, s);
-  dim3 grid((unsigned)grid_for(numel_per_mat, 256, (int)(G >= 16 ? 74 : 1184 / G)), (unsigned)G);
-  muon_momentum_kernel<<<grid, 256, 0, s>>>(g, buf, (__nv_bfloat16*)dir, sumsq, numel_per_mat, mu,
-                                            (int)nesterov);
+  if (G > MUON_PART_SLOTS) return set_error("ccb_muon_momentum: at most %d matrices per call", MUON_PART_SLOTS);
+  (void)sumsq;
+  dim3 grid((unsigned)muon_blocks_per_mat(G, numel_per_mat), (unsigned)G);
+  muon_momentum_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(g, buf, (__nv_bfloat16*)dir,
+                                                               numel_per_mat, mu, (int)nesterov);
   CCB_CHECK_LAUNCH("muon_momentum");
   return 0;
 }
-extern "C" int ccb_muon_normalize(void* dir, const float* sumsq, int64_t G, int64_t numel_per_mat,
+extern "C" int ccb_muon_normalize(void* dir, float* sumsq, int64_t G, int64_t numel_per_mat,
                                   float eps, void* stream) {
   if (G <= 0 || numel_per_mat <= 0) return 0;
-  dim3 grid((unsigned)grid_for(numel_per_mat, 256, (int)(G >= 16 ? 74 : 1184 / G)), (unsigned)G);
-  muon_normalize_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)dir, sumsq,
+  if (G > MUON_PART_SLOTS) return set_error("ccb_muon_normalize: at most %d matrices per call", MUON_PART_SLOTS);
+  const int nparts = muon_blocks_per_mat(G, numel_per_mat);
+  dim3 grid((unsigned)nparts, (unsigned)G);
+  muon_normalize_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)dir, sumsq, nparts,
                                                                 numel_per_mat, eps);
   CCB_CHECK_LAUNCH("muon_normalize");
   return 0;
@@ -553,10 +728,10 @@ extern "C" int ccb_adamw(void* p, int64_t p_is_bf16, const float* g, float* m, f
 extern "C" int ccb_clip_grad_norm(float* g, int64_t n, float max_norm, float* stat, void* stream) {
   if (n <= 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
-  cudaMemsetAsync(stat, 0, 3 * sizeof(float), s);
-  sumsq_kernel<<<grid_for(n, 256), 256, 0, s>>>(g, n, stat);
+  const int nb = grid_for(n, 256, SUMSQ_MAX_BLOCKS);
+  sumsq_kernel<<<nb, 256, 0, s>>>(g, n);
   CCB_CHECK_LAUNCH("sumsq");
-  clip_coef_kernel<<<1, 1, 0, s>>>(stat, max_norm);
+  clip_coef_kernel<<<1, 256, 0, s>>>(stat, nb, max_norm);
   CCB_CHECK_LAUNCH("clip_coef");
   scale_by_ptr_kernel<<<grid_for(n, 256), 256, 0, s>>>(g, n, stat + 1);
   CCB_CHECK_LAUNCH("scale_by_ptr");
@@ -634,11 +809,12 @@ extern "C" int ccb_rmsnorm_bwd_noalloc(const void* x, const void* w, const void*
   float* part = g_noalloc_part_ptr[dev];
   const unsigned nb = (unsigned)((R + kNoallocRowsPerBlock - 1) / kNoallocRowsPerBlock);
   cudaStream_t s = (cudaStream_t)stream;
-  rmsnorm_bwd_kernel<<<nb, 256, (size_t)D * sizeof(float), s>>>(
+  rmsnorm_bwd_kernel<<<nb, 256, (size_t)8 * D * sizeof(float), s>>>(
       (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)go, inv_rms,
       (__nv_bfloat16*)gx, part, R, (int)D, (int)kNoallocRowsPerBlock);
   CCB_CHECK_LAUNCH("rmsnorm_bwd(noalloc)");
-  colsum_kernel<<<(unsigned)((D + 127) / 128), 128, 0, s>>>(part, (int)nb, (int)D, gw_out, 0);
+  colsum_kernel<<<(unsigned)((D + COLSUM_COLS - 1) / COLSUM_COLS), COLSUM_COLS * COLSUM_GROUPS, 0, s>>>(
+      part, (int)nb, (int)D, gw_out, 0);
   CCB_CHECK_LAUNCH("colsum(noalloc)");
   return 0;
 }

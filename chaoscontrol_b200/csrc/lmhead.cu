@@ -38,8 +38,11 @@
 // library calls with separate row-reduction kernels between them
 // (kernels/_lm_head_loss/src/rms_norm_binding.cpp:139-551, linear_ce.cu:24-304).
 //
-// Warp roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM
-// owner, warps 2..9 epilogue (warp w: TMEM lanes 32*(w%4).., column half (w-2)/4).
+// Warp roles: warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, then 4 * PARTS epilogue
+// warps (warp w: TMEM lanes 32*(w%4).., column part (w-2)/4).  PARTS = 2 gives each epilogue warp
+// two 32-column groups of every 128-column logits tile, PARTS = 4 one group: the epilogue is a
+// latency chain (TMEM load -> exp2 -> pack -> shared-memory store) between the two MMAs, and
+// sixteen warps, four per scheduler, cover each other's stalls where eight cannot.
 #include "ptx.cuh"
 #include "ccb_api.h"
 #include "runtime.h"
@@ -51,11 +54,11 @@ constexpr int LH_ROWS = 128;         // rows per tile
 constexpr int LH_VT = 128;           // vocabulary entries per tile
 constexpr int LH_CHUNK = 16384;      // one [128 rows][64 bf16] operand chunk
 constexpr int LH_TILE = 4 * LH_CHUNK;   // 128 x 256 bf16
-constexpr int LH_THREADS = 320;
+constexpr int lh_threads(int parts) { return 64 + 128 * parts; }
 constexpr int LH_OFF_RES = 0;
 constexpr int LH_OFF_STG = LH_TILE;
 constexpr int LH_OFF_G = 3 * LH_TILE;
-constexpr int LH_OFF_X = LH_OFF_G + 2 * LH_CHUNK;      // (m, s) exchange: 2 x 128 float2
+constexpr int LH_OFF_X = LH_OFF_G + 2 * LH_CHUNK;      // per-row exchange between parts: up to 4 x 128 floats
 constexpr int LH_OFF_BAR = LH_OFF_X + 2048;
 constexpr int LH_SMEM = LH_OFF_BAR + 256;
 constexpr float LOG2E = 1.4426950408889634f;
@@ -102,8 +105,8 @@ __device__ __forceinline__ float ex2f(float x) {
   return y;
 }
 
-template <int MODE>
-__global__ void __launch_bounds__(LH_THREADS, 1)
+template <int MODE, int PARTS>
+__global__ void __launch_bounds__(lh_threads(PARTS), 1)
 lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
               const LmHeadArgs p) {
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -123,13 +126,13 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
       mbar_init(&bars->stg_full[i], 1);
       mbar_init(&bars->stg_empty[i], 1);
       mbar_init(&bars->d1_full[i], 1);
-      mbar_init(&bars->d1_empty[i], 8);
-      mbar_init(&bars->g_full[i], MODE == MODE_DW ? 4 : 8);
+      mbar_init(&bars->d1_empty[i], 4 * PARTS);
+      mbar_init(&bars->g_full[i], MODE == MODE_DW ? 2 * PARTS : 8);
       mbar_init(&bars->g_empty[i], 1);
     }
     mbar_init(&bars->d2_full, 1);
     mbar_init(&bars->d2_empty, 4);
-    mbar_init(&bars->xbar, 8);
+    mbar_init(&bars->xbar, 4 * PARTS);
     mbar_init(&bars->xt_full, 4);
     mbar_init(&bars->xt_empty, 1);
     bars->abort_flag = 0;
@@ -322,11 +325,12 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
     }
   } else {
     // =========================== epilogue ====================================
+    constexpr int NG = 4 / PARTS;           // 32-column groups of each 128-column tile per warp
     const int q = warp & 3;                 // TMEM lane quadrant
-    const int part = (warp - 2) >> 2;       // which 32 columns of each 64-column chunk
+    const int part = (warp - 2) >> 2;       // this warp's groups: g * PARTS + part, g < NG
     const int row_in_tile = q * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-    float2* xchg = reinterpret_cast<float2*>(smem + LH_OFF_X);
+    float* xchg = reinterpret_cast<float*>(smem + LH_OFF_X);     // [PARTS][128]
     uint32_t n_d1 = 0, n_g = 0, n_d2 = 0, n_x = 0, n_xt = 0;
     bool ok = true;
     // Every wait below is made warp-uniform, so the warp-collective TMEM loads
@@ -335,13 +339,34 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
       const bool w = mbar_wait(bar, parity, abort_flag, p.status);
       return __all_sync(0xffffffffu, w);
     };
-    // Bounded rendezvous of the eight epilogue warps (orders the xchg traffic).
+    // Bounded rendezvous of all epilogue warps (orders the xchg traffic).
     auto epi_sync = [&]() -> bool {
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->xbar);
       const bool w = wait_all(&bars->xbar, n_x & 1u);
       ++n_x;
       return w;
+    };
+    // A row's per-part values combined in part order: every part ends with the same bits.
+    auto parts_sum = [&](float v, float& out) -> bool {
+      if (!epi_sync()) return false;
+      xchg[part * 128 + row_in_tile] = v;
+      if (!epi_sync()) return false;
+      float t = xchg[row_in_tile];
+#pragma unroll
+      for (int k = 1; k < PARTS; ++k) t += xchg[k * 128 + row_in_tile];
+      out = t;
+      return true;
+    };
+    auto parts_max = [&](float v, float& out) -> bool {
+      if (!epi_sync()) return false;
+      xchg[part * 128 + row_in_tile] = v;
+      if (!epi_sync()) return false;
+      float t = xchg[row_in_tile];
+#pragma unroll
+      for (int k = 1; k < PARTS; ++k) t = fmaxf(t, xchg[k * 128 + row_in_tile]);
+      out = t;
+      return true;
     };
 
     for (int unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x) {
@@ -416,8 +441,8 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
           if (!second) {
             // ---- sweep 1: online max / sum (log2 domain) ----------------------
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              const int col0 = h * 64 + part * 32;
+            for (int g = 0; g < NG; ++g) {
+              const int col0 = (g * PARTS + part) * 32;
               uint32_t a[32];
               __syncwarp();
               tmem_ld32(t_addr + col0, a);
@@ -438,10 +463,13 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
               if (MODE == MODE_LSE) run_e = run_e * resc + eacc;
               run_m = new_m;
               if (MODE == MODE_LSE) {
+                // a lane meets its target column once per sweep: looked up outside the hot loop
                 const int tl = tgt - (v0 + col0);
+                if ((unsigned)tl < 32u) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i)
-                  if (i == tl) tacc = __uint_as_float(a[i]);
+                  for (int i = 0; i < 32; ++i)
+                    if (i == tl) tacc = __uint_as_float(a[i]);
+                }
               }
             }
             tc_fence_before_sync();
@@ -453,7 +481,7 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             ++n_g;
             if (FUSED1 && it == inner0) {
               // per-row reference: max of the unit's first 32 logits (every warp reads the same
-              // 32 columns, so the two column halves of a row agree without an exchange)
+              // 32 columns, so all parts of a row agree without an exchange)
               uint32_t a0[32];
               __syncwarp();
               tmem_ld32(t_addr, a0);
@@ -463,12 +491,12 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
               for (int i = 1; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(a0[i]));
               c2 = fmaf(mx, c1, LH_REF_MARGIN);
             }
-            // both 32-column halves of this warp are requested before either is used: one TMEM
-            // round trip per tile instead of two on the path between the two MMAs
-            uint32_t ah[2][32];
+            // all of this warp's groups are requested before any is used: one TMEM round trip
+            // per tile on the path between the two MMAs
+            uint32_t ah[NG][32];
             __syncwarp();
-            tmem_ld32(t_addr + part * 32, ah[0]);
-            tmem_ld32(t_addr + 64 + part * 32, ah[1]);
+#pragma unroll
+            for (int g = 0; g < NG; ++g) tmem_ld32(t_addr + (g * PARTS + part) * 32, ah[g]);
             tmem_ld_wait();
             // the logits now live in registers: hand the TMEM buffer back at once, so the MMA
             // warp can start the tile after next while this one is still being turned into g
@@ -479,9 +507,11 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
               if (!wait_all(&bars->g_empty[q >> 1], gph ^ 1u)) { ok = false; break; }
             }
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              const int col0 = h * 64 + part * 32;
-              const uint32_t (&a)[32] = ah[h];
+            for (int g = 0; g < NG; ++g) {
+              const int grp = g * PARTS + part;      // 32-column group of the tile
+              const int h = grp >> 1;                // 64-column chunk of the g tile
+              const int col0 = grp * 32;
+              const uint32_t (&a)[32] = ah[g];
               const int tl = tgt - (v0 + col0);
               uint32_t packed[16];
 #pragma unroll
@@ -494,26 +524,36 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
                   run_s += p0 + p1;
                   packed[i >> 1] = pack_bf16x2(p0, p1);
                 } else {
-                  if (i == tl) { p0 -= 1.f; zt = z0; }
-                  if (i + 1 == tl) { p1 -= 1.f; zt = z1; }
                   packed[i >> 1] = pack_bf16x2(p0 * gs, p1 * gs);
                 }
               }
-              if (FUSED1 && (unsigned)tl < 32u) {
-                // the target's logit (relative to the reference): looked up outside the hot loop,
-                // a lane meets its target column once per vocabulary sweep
+              if ((unsigned)tl < 32u) {
+                // the target column: handled outside the hot loop, a lane meets it once per sweep
 #pragma unroll
                 for (int i = 0; i < 32; ++i)
-                  if (i == tl) zt = fminf(fmaf(__uint_as_float(a[i]), c1, -c2), 126.f);
+                  if (i == tl) {
+                    const float z = fmaf(__uint_as_float(a[i]), c1, -c2);
+                    if (FUSED1) {
+                      zt = fminf(z, 126.f);
+                    } else {
+                      zt = z;
+                      // redo the target's pair with the one-hot subtracted
+                      const int i0 = i & ~1;
+                      float pa = ex2f(fmaf(__uint_as_float(a[i0]), c1, -c2));
+                      float pb = ex2f(fmaf(__uint_as_float(a[i0 + 1]), c1, -c2));
+                      if (i & 1) pb -= 1.f; else pa -= 1.f;
+                      packed[i >> 1] = pack_bf16x2(pa * gs, pb * gs);
+                    }
+                  }
               }
               if (MODE != MODE_DW) {
                 if (!wait_all(&bars->g_empty[h], gph ^ 1u)) { ok = false; break; }
               }
-              // row `row_in_tile` of chunk h, 16-byte slots part*4 .. part*4+3, 128B swizzle
+              // row `row_in_tile` of chunk h, 16-byte slots (grp & 1) * 4 .. + 3, 128B swizzle
               uint8_t* grow = smem + LH_OFF_G + h * LH_CHUNK + row_in_tile * 128;
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
-                const int slot = (part * 4 + j) ^ (row_in_tile & 7);
+                const int slot = ((grp & 1) * 4 + j) ^ (row_in_tile & 7);
                 *reinterpret_cast<uint4*>(grow + slot * 16) =
                     make_uint4(packed[j * 4], packed[j * 4 + 1], packed[j * 4 + 2], packed[j * 4 + 3]);
               }
@@ -534,53 +574,42 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         if (!ok) break;
 
         if (!second) {
-          // combine the two column halves of each row -> lse
-          if (!epi_sync()) { ok = false; break; }
-          xchg[part * 128 + row_in_tile] = make_float2(run_m, run_s);
-          if (!epi_sync()) { ok = false; break; }
-          const float2 o = xchg[(part ^ 1) * 128 + row_in_tile];
-          const float m = fmaxf(run_m, o.x);
-          const float my_resc = ex2f(run_m - m), o_resc = ex2f(o.x - m);
-          const float s = run_s * my_resc + o.y * o_resc;
+          // combine the column parts of each row -> lse
+          float m = 0.f, s = 0.f;
+          if (!parts_max(run_m, m)) { ok = false; break; }
+          const float my_resc = ex2f(run_m - m);
+          if (!parts_sum(run_s * my_resc, s)) { ok = false; break; }
           const float lse2 = m + __log2f(s);
           c2 = lse2;
           if (row_ok && part == 0) p.lse[r] = lse2 * LN2;
           if (MODE == MODE_LSE) {
-            // the target column lived in exactly one of the two halves
-            if (!epi_sync()) { ok = false; break; }
-            xchg[part * 128 + row_in_tile] = make_float2(tacc, 0.f);
-            if (!epi_sync()) { ok = false; break; }
-            const float t_other = xchg[(part ^ 1) * 128 + row_in_tile].x;
-            if (row_ok && part == 0) p.loss[r] = lse2 * LN2 - (tacc + t_other) * rs;
+            // the target column lived in exactly one part
+            float t_all = 0.f;
+            if (!parts_sum(tacc, t_all)) { ok = false; break; }
+            if (row_ok && part == 0) p.loss[r] = lse2 * LN2 - t_all * rs;
             if (p.entropy != nullptr) {
               // H = lse - E[logit],  E[logit] = rs * sum(p~ * raw) / sum(p~)
-              if (!epi_sync()) { ok = false; break; }
-              xchg[part * 128 + row_in_tile] = make_float2(run_e * my_resc, 0.f);
-              if (!epi_sync()) { ok = false; break; }
-              const float e_tot = run_e * my_resc + xchg[(part ^ 1) * 128 + row_in_tile].x;
+              float e_tot = 0.f;
+              if (!parts_sum(run_e * my_resc, e_tot)) { ok = false; break; }
               if (row_ok && part == 0) p.entropy[r] = lse2 * LN2 - rs * e_tot / s;
             }
           }
         } else if (FUSED1) {
-          // combine the two column halves: S = sum p~, target logit relative to the reference
-          if (!epi_sync()) { ok = false; break; }
-          xchg[part * 128 + row_in_tile] = make_float2(zt, run_s);
-          if (!epi_sync()) { ok = false; break; }
-          const float2 o = xchg[(part ^ 1) * 128 + row_in_tile];
-          const float S = run_s + o.y;
+          // combine the parts: S = sum p~, target logit relative to the reference
+          float S = 0.f, z_all = 0.f;
+          if (!parts_sum(run_s, S)) { ok = false; break; }
+          if (!parts_sum(zt, z_all)) { ok = false; break; }
           const float lg = __log2f(S);
           inv_s = 1.f / S;
           if (row_ok && part == 0) {
             p.lse[r] = (c2 + lg) * LN2;
-            p.loss[r] = (lg - (zt + o.x)) * LN2;
+            p.loss[r] = (lg - z_all) * LN2;
           }
         } else if (MODE == MODE_TRAIN) {
-          // per-row CE = -log p_target = -zt * ln2 (zt captured by one of the two warps)
-          if (!epi_sync()) { ok = false; break; }
-          xchg[part * 128 + row_in_tile] = make_float2(zt, 0.f);
-          if (!epi_sync()) { ok = false; break; }
-          const float z_other = xchg[(part ^ 1) * 128 + row_in_tile].x;
-          if (row_ok && part == 0) p.loss[r] = -(zt + z_other) * LN2;
+          // per-row CE = -log p_target = -zt * ln2 (zt captured by exactly one warp of the row)
+          float z_all = 0.f;
+          if (!parts_sum(zt, z_all)) { ok = false; break; }
+          if (row_ok && part == 0) p.loss[r] = -z_all * LN2;
         }
       }
       if (!ok) break;
@@ -693,12 +722,14 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
   }
 }
 
-template <int MODE>
-static int launch_lmhead(const void* X, const void* W, LmHeadArgs& a, cudaStream_t stream) {
+static int g_lh_parts = 4;   // epilogue column parts (2: eight epilogue warps, 4: sixteen)
+
+template <int MODE, int PARTS>
+static int launch_lmhead_p(const void* X, const void* W, LmHeadArgs& a, cudaStream_t stream) {
   static bool attr_set[16] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
-  auto kern = lmhead_kernel<MODE>;
+  auto kern = lmhead_kernel<MODE, PARTS>;
   if (!attr_set[dev & 15]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, LH_SMEM);
     if (e != cudaSuccess) return set_error("cudaFuncSetAttribute(lmhead): %s", cudaGetErrorString(e));
@@ -710,15 +741,29 @@ static int launch_lmhead(const void* X, const void* W, LmHeadArgs& a, cudaStream
   a.status = ccb_status_ptr();
   const int units = (MODE == MODE_DW) ? a.n_vtiles * a.row_chunks : a.n_mtiles;
   const int grid = units < ccb_num_sms() ? units : ccb_num_sms();
-  kern<<<grid, LH_THREADS, LH_SMEM, stream>>>(tmX, tmW, a);
+  kern<<<grid, lh_threads(PARTS), LH_SMEM, stream>>>(tmX, tmW, a);
   count_launch();
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : set_error("lmhead launch: %s", cudaGetErrorString(e));
 }
 
+template <int MODE>
+static int launch_lmhead(const void* X, const void* W, LmHeadArgs& a, cudaStream_t stream) {
+  return g_lh_parts == 2 ? launch_lmhead_p<MODE, 2>(X, W, a, stream)
+                         : launch_lmhead_p<MODE, 4>(X, W, a, stream);
+}
+
 }  // namespace ccb
 
 using namespace ccb;
+
+// Epilogue width of the fused LM-head kernels: 2 (eight epilogue warps) or 4 (sixteen, default).
+// Returns the previous value; other arguments leave it unchanged.
+extern "C" int ccb_lmhead_epilogue_parts(int parts) {
+  const int old = g_lh_parts;
+  if (parts == 2 || parts == 4) g_lh_parts = parts;
+  return old;
+}
 
 static int lmhead_common(LmHeadArgs& a, int64_t R, int64_t V, int64_t D, const float* rowss,
                          float eps, const int64_t* targets) {

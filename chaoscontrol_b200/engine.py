@@ -73,14 +73,17 @@ class TrainEngine:
     # ------------------------------------------------------------------
     @torch.no_grad()
     def step(self, inputs: torch.Tensor, targets: torch.Tensor, *, loss_weight: float = 1.0,
-             row_weight: Optional[torch.Tensor] = None) -> torch.Tensor:
+             row_weight: Optional[torch.Tensor] = None, reducer=None) -> torch.Tensor:
+        """``reducer`` (an :class:`~chaoscontrol_b200.parallel.grad_overlap.OverlappedGradReducer`)
+        averages the gradients over the data-parallel ranks bucket by bucket while the rest of
+        backward runs; the step then returns with reduced gradients and ``arena.grads_reduced`` set."""
         model, a = self.model, self.arena
         B, Tn = inputs.shape
         R = B * Tn
         V = model.lm_head.weight.shape[0]
         flat_in = inputs.reshape(-1)
         # token sort for the embedding backward: depends on the inputs only
-        sort_cache = torch.sort(flat_in.long())
+        sort_cache = torch.sort(flat_in.long(), stable=True)
         x, ss = T.embed_fwd(inputs, a.param_view("embed.weight"))
         ws, ctxs = [], []
         for i in range(len(model.layers)):
@@ -97,6 +100,8 @@ class TrainEngine:
                                                      rowweight=row_weight)
         T.splitk_reduce(part, colscale=wnF, W=Wlm, out=a.grad_view("lm_head.weight"),
                         dcol_out=a.grad_view("final_norm.weight"))
+        if reducer is not None:
+            reducer.bucket_ready(reducer.head_bucket)
         self.last_loss_rows = loss_rows
         self.last_hidden = x                    # [B*T, D] trunk output (pre final norm), for event producers
         if row_weight is None:
@@ -112,6 +117,11 @@ class TrainEngine:
                     "dwn2": a.grad_view(n["wn2"]), "dlog_a": a.grad_view(n["log_a"])}
             dx, _ = T.layer_backward(dx, ctxs[i], ws[i], B, Tn, None, outs=outs)
             ctxs[i] = None
+            if reducer is not None:
+                reducer.bucket_ready(reducer.layer_bucket(i, len(model.layers)))
         T.embed_bwd(inputs, dx, V, sort_cache=sort_cache, out=a.grad_view("embed.weight"))
         a.grads_fresh = True
+        if reducer is not None:
+            reducer.bucket_ready(reducer.last_bucket)
+            reducer.finish()
         return loss

@@ -72,7 +72,10 @@ def embed_fwd(tokens: torch.Tensor, E: torch.Tensor):
 
 def embed_bwd(tokens: torch.Tensor, dx: torch.Tensor, V: int,
               sort_cache: Optional[tuple] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """fp32 ``[V, D]`` gradient of the embedding table (scatter-add of ``dx`` rows)."""
+    """fp32 ``[V, D]`` gradient of the embedding table (sum of the ``dx`` rows of each token).
+
+    On the GPU the rows are added in a fixed order derived from the stably sorted token array, so
+    the same batch gives the same bits on every run and on every replica."""
     flat = tokens.reshape(-1).long()
     D = dx.shape[1]
     if out is not None:
@@ -81,11 +84,14 @@ def embed_bwd(tokens: torch.Tensor, dx: torch.Tensor, V: int,
         dE = torch.zeros(V, D, dtype=torch.float32, device=dx.device)
     if dx.is_cuda and D in (256, 512, 1024):
         if sort_cache is None:
-            sort_cache = torch.sort(flat)
+            sort_cache = torch.sort(flat, stable=True)
         st, perm = sort_cache
-        _lib.check(_lib.lib().ccb_embed_bwd_sorted(st.data_ptr(), perm.data_ptr(), dx.data_ptr(),
-                                                   dE.data_ptr(), flat.numel(), D, V,
-                                                   _lib.stream_ptr()), "embed_bwd")
+        L = _lib.lib()
+        slots = torch.empty(int(L.ccb_embed_bwd_slots(flat.numel(), D)), dtype=torch.float32,
+                            device=dx.device)
+        _lib.check(L.ccb_embed_bwd_sorted(st.data_ptr(), perm.data_ptr(), dx.data_ptr(), dE.data_ptr(),
+                                          slots.data_ptr(), flat.numel(), D, V, _lib.stream_ptr()),
+                   "embed_bwd")
         return dE
     dE.index_add_(0, flat, dx.float())
     return dE

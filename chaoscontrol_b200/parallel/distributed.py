@@ -22,11 +22,19 @@ from ..utils.arena import get_arena
 
 
 def broadcast_params(model: torch.nn.Module) -> None:
-    """Make every rank start from rank 0's parameters (one flat broadcast when
-    the parameters share an arena, per-tensor otherwise)."""
+    """Make every rank start from rank 0's parameters: one flat broadcast when the parameters share
+    an arena -- through rank 0's symmetric buffer when the peer-memory communicator is up, a library
+    broadcast otherwise -- and per-tensor broadcasts without an arena."""
     arena = get_arena(model)
     if arena is not None:
-        dist.broadcast(arena.flat_param, src=0)
+        from . import symm
+        comm = symm.active_comm(None)
+        flat = arena.flat_param
+        nbytes = flat.numel() * flat.element_size()
+        if comm is not None and flat.is_cuda and nbytes % 16 == 0 and nbytes <= comm.numel * 2:
+            comm.broadcast_(flat, src=0)
+            return
+        dist.broadcast(flat, src=0)
         return
     for p in model.parameters():
         dist.broadcast(p.data, src=0)
@@ -45,6 +53,9 @@ def allreduce_grads(model: torch.nn.Module, world_size: int, *,
     """
     arena = get_arena(model)
     if arena is not None and arena.grads_fresh:
+        if getattr(arena, "grads_reduced", False):
+            arena.grads_reduced = False              # the engine's overlapped exchange already ran
+            return
         _allreduce_flat(arena.flat_grad, world_size, group, op)
         return
     if materialize_zeros:
@@ -155,13 +166,30 @@ def clip_arena_grad_norm(arena, max_norm: float) -> torch.Tensor:
 
 def should_stop_now(local_should_stop: bool, device: torch.device, ddp_active: bool, *,
                     group: "dist.ProcessGroup | None" = None) -> bool:
-    """Any rank wants to stop => every rank stops on the same step.  All ranks
-    run the same MAX all-reduce unconditionally when DDP is active."""
-    if ddp_active:
-        flag = torch.tensor([1.0 if local_should_stop else 0.0], device=device)
-        dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=group)
-        return flag.item() > 0.5
-    return local_should_stop
+    """Any rank wants to stop => every rank stops on the same step.  All ranks run the same
+    exchange unconditionally when DDP is active.
+
+    With the peer-memory communicator the flag travels through the signal pads (one one-warp kernel,
+    no library collective), and it carries a second bit: "one of my peer-memory collectives timed
+    out since the last check".  If any rank reports that, EVERY rank marks the communicator dead and
+    raises ``PeerCommError`` here, on the same step, instead of stepping on unreduced gradients.
+    """
+    if not ddp_active:
+        return local_should_stop
+    from . import symm
+    comm = symm.active_comm(group)
+    if comm is not None and device.type == "cuda":
+        from .peer import PeerCommError
+        value = (1 if local_should_stop else 0) | (2 if comm.timed_out() else 0)
+        got = comm.flag_max(value)
+        if got >= 2:
+            comm.dead = True
+            raise PeerCommError("a rank reported that a peer-memory collective timed out: gradients of the "
+                                "last steps may be unreduced; stopping on every rank")
+        return got == 1
+    flag = torch.tensor([1.0 if local_should_stop else 0.0], device=device)
+    dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=group)
+    return flag.item() > 0.5
 
 
 def resolve_ddp_context(rank: Optional[int], world_size: Optional[int]) -> tuple[int, int]:

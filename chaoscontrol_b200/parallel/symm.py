@@ -14,7 +14,12 @@ def set_active_comm(comm, group=None) -> None:
 
 
 def active_comm(group=None):
-    return _ACTIVE.get(id(group) if group is not None else None)
+    """The live communicator of ``group``, or None (none registered, or it was marked dead
+    after a peer timeout)."""
+    comm = _ACTIVE.get(id(group) if group is not None else None)
+    if comm is not None and getattr(comm, "dead", False):
+        return None
+    return comm
 
 
 def clear() -> None:

@@ -215,9 +215,13 @@ def train_ssm_step(model: nn.Module, inputs: torch.Tensor, targets: torch.Tensor
     engine = _engine_for(model) if (fused_mode and precision in ("bf16", "fp8_fused") and
                                     model.training) else None
     if engine is not None:
-        loss = engine.step(inputs, targets)
+        reducer = None
         if ddp_active and world_size > 1:
-            allreduce_grads(model, world_size)
+            from .parallel.grad_overlap import reducer_for
+            reducer = reducer_for(engine, world_size)
+        loss = engine.step(inputs, targets, reducer=reducer)
+        if ddp_active and world_size > 1:
+            allreduce_grads(model, world_size)       # no-op when the reducer already did the exchange
         engine.arena.materialize_grads()
         return loss
 

@@ -106,6 +106,14 @@ def build(kernel: str, R: int, D: int = 256, V: int = 16384, T: int = 512):
         fn = lambda: LH.lm_head_train(x, ss, W, t, gscale=1.0 / R)
         # logits-sized GEMMs actually executed: one sweep = logits + dX, then logits + dW
         return fn, 2 * 2 * R * D + 2 * V * D, (4 if LH.ONE_SWEEP else 5) * 2.0 * R * D * V
+    if kernel == "embed_bwd":
+        from ..ops import trunk as T
+        p = torch.arange(1, V + 1, dtype=torch.float64) ** -1.1
+        tok = torch.multinomial(p / p.sum(), R, replacement=True).cuda()
+        sc = torch.sort(tok, stable=True)
+        dE = torch.empty(V, D, dtype=torch.float32, device="cuda")
+        fn = lambda: T.embed_bwd(tok, x, V, sort_cache=sc, out=dE)
+        return fn, 2 * R * D + 4 * V * D, 0.0
     raise SystemExit(f"unknown kernel {kernel}")
 
 
@@ -117,7 +125,11 @@ def main() -> None:
     ap.add_argument("--vocab", type=int, default=16384)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--lmhead-parts", type=int, default=0, choices=[0, 2, 4],
+                    help="epilogue width of the fused LM head: 2 = eight warps, 4 = sixteen (0: library default)")
     a = ap.parse_args()
+    if a.lmhead_parts:
+        _lib.lib().ccb_lmhead_epilogue_parts(a.lmhead_parts)
     torch.manual_seed(0)
     fn, nbytes, flops = build(a.kernel, a.rows, a.dim, a.vocab)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
@@ -137,7 +149,7 @@ def main() -> None:
     times.sort()
     ms = times[len(times) // 2]
     pk = peaks()
-    out = {"kernel": a.kernel, "rows": a.rows, "ms_median": ms, "ms_min": times[0],
+    out = {"kernel": a.kernel, "rows": a.rows, "lmhead_parts": a.lmhead_parts or None, "ms_median": ms, "ms_min": times[0],
            "GBps": nbytes / ms / 1e6, "frac_hbm": nbytes / ms / 1e6 / pk["hbm_gbs"],
            "TFLOPs": flops / ms / 1e9, "frac_bf16_burst": flops / ms / 1e9 / pk["bf16_tflops"],
            "peaks": pk["src"]}

@@ -8,6 +8,15 @@ from chaoscontrol_b200.ops import lm_head as LH
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(params=[4, 2], ids=["epi16warps", "epi8warps"])
+def epilogue_parts(request):
+    """Run a test with both widths of the fused head's epilogue (sixteen or eight warps)."""
+    L = _lib.lib()
+    old = L.ccb_lmhead_epilogue_parts(request.param)
+    yield request.param
+    L.ccb_lmhead_epilogue_parts(old)
+
+
 def _mk(R, V, seed=0, wscale=0.08):
     torch.manual_seed(seed)
     x = torch.randn(R, 256, device="cuda").bfloat16()
@@ -18,7 +27,7 @@ def _mk(R, V, seed=0, wscale=0.08):
 
 
 @pytest.mark.parametrize("R,V", [(128, 128), (256, 512), (1000, 1024), (4096, 16384)])
-def test_lmhead_lse(R, V):
+def test_lmhead_lse(R, V, epilogue_parts):
     x, W, t, ss = _mk(R, V)
     loss, lse = LH.lm_head_lse(x, ss, W, t)
     _lib.assert_ok()
@@ -29,7 +38,7 @@ def test_lmhead_lse(R, V):
 
 @pytest.mark.parametrize("R,V,chunks,norm", [(128, 128, 1, True), (384, 512, 3, True),
                                              (1000, 1024, 2, False), (2048, 16384, 4, True)])
-def test_lmhead_train(R, V, chunks, norm):
+def test_lmhead_train(R, V, chunks, norm, epilogue_parts):
     x, W, t, ss = _mk(R, V, seed=1)
     w = torch.rand(R, device="cuda")
     gscale = 1.0 / R
@@ -48,7 +57,7 @@ def test_lmhead_train(R, V, chunks, norm):
     assert (dW - rdW).abs().max().item() <= 0.03 * sw + 1e-7, ((dW - rdW).abs().max().item(), sw)
 
 
-def test_lmhead_train_deterministic():
+def test_lmhead_train_deterministic(epilogue_parts):
     x, W, t, ss = _mk(1024, 2048, seed=2)
     a = LH.lm_head_train(x, ss, W, t, gscale=1e-3)
     b = LH.lm_head_train(x, ss, W, t, gscale=1e-3)
@@ -95,7 +104,7 @@ def test_lmhead_general_dims(R, V, D, norm):
 
 
 @pytest.mark.parametrize("wscale,peak", [(0.08, 0.0), (1.5, 0.0), (0.3, 40.0)])
-def test_lmhead_one_sweep_matches_two_sweeps_and_the_reference(wscale, peak):
+def test_lmhead_one_sweep_matches_two_sweeps_and_the_reference(wscale, peak, epilogue_parts):
     """The single-sweep training kernel (fixed per-row reference instead of the true row maximum)
     against the two-sweep kernel and the fp32 statement: ordinary logits, logits spread over tens of
     nats, and a target column that towers over the row's first 32 logits."""

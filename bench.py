@@ -626,21 +626,37 @@ def run_parity(args):
     torch.manual_seed(0)
     rmodel = RefLM(vocab_size=VOCAB, dim=DIM, num_layers=LAYERS, ff_mult=FF_MULT).to(dev).to(torch.bfloat16)
     init = {k: v.detach().clone() for k, v in rmodel.state_dict().items()}
-    rmodel.train()
-    ropt = RefMuon(rmodel.parameters(), lr=LR, weight_decay=WD, adamw_lr=LR, adamw_weight_decay=WD, fused=True)
-    ropt.bind_param_names(list(rmodel.named_parameters()))
-    ref_losses = []
-    for i in range(n):
-        blk = host[i].to(dev, non_blocking=True)
-        ropt.zero_grad(set_to_none=True)
-        loss = ref_step(rmodel, blk[:, :-1].to(torch.int32), blk[:, 1:], 64, ddp_active=False, world_size=1,
-                        precision="bf16", lm_head_backward_mode="fused_streaming_cached", lm_head_tile_size=8192)
-        ref_clip(rmodel.parameters(), CLIP)
-        ropt.step()
-        ref_losses.append(loss.detach().float())
-    ref_curve = torch.stack(ref_losses).cpu().tolist()
-    del rmodel, ropt
-    torch.cuda.empty_cache()
+    del rmodel
+
+    def reference(perturb: bool):
+        """The reference recipe from ``init``; ``perturb`` nudges ONE weight (embed[0, 0]) by one bf16
+        ulp first: the control that shows how far this recipe's loss curve moves under the smallest
+        possible change of the starting point."""
+        rmodel = RefLM(vocab_size=VOCAB, dim=DIM, num_layers=LAYERS, ff_mult=FF_MULT).to(dev).to(torch.bfloat16)
+        rmodel.load_state_dict(init, strict=True)
+        if perturb:
+            with torch.no_grad():
+                w = rmodel.embed.weight
+                w[0, 0] = (w[0, 0].view(torch.int16) + 1).view(torch.bfloat16)
+        rmodel.train()
+        ropt = RefMuon(rmodel.parameters(), lr=LR, weight_decay=WD, adamw_lr=LR, adamw_weight_decay=WD, fused=True)
+        ropt.bind_param_names(list(rmodel.named_parameters()))
+        out = []
+        for i in range(n):
+            blk = host[i].to(dev, non_blocking=True)
+            ropt.zero_grad(set_to_none=True)
+            loss = ref_step(rmodel, blk[:, :-1].to(torch.int32), blk[:, 1:], 64, ddp_active=False, world_size=1,
+                            precision="bf16", lm_head_backward_mode="fused_streaming_cached", lm_head_tile_size=8192)
+            ref_clip(rmodel.parameters(), CLIP)
+            ropt.step()
+            out.append(loss.detach().float())
+        curve = torch.stack(out).cpu().tolist()
+        del rmodel, ropt
+        torch.cuda.empty_cache()
+        return curve
+
+    ref_curve = reference(False)
+    ref_perturbed = reference(True)
 
     def ours(one_sweep: bool):
         LH.ONE_SWEEP = bool(one_sweep)
@@ -667,14 +683,18 @@ def run_parity(args):
         torch.cuda.empty_cache()
         return curve
 
-    curves = {"reference": ref_curve, "ours_one_sweep": ours(True), "ours_two_sweeps": ours(False),
-              "ours_one_sweep_again": ours(True)}
+    curves = {"reference": ref_curve, "reference_one_ulp_perturbed": ref_perturbed,
+              "ours_one_sweep": ours(True), "ours_two_sweeps": ours(False), "ours_one_sweep_again": ours(True)}
 
     def cmp(a, b):
         d = [abs(x - y) for x, y in zip(a, b)]
         tail = max(1, len(d) // 10)
+        sm = lambda x, i: sum(x[i:i + 10]) / len(x[i:i + 10])          # 10-step means
+        ds = [abs(sm(a, i) - sm(b, i)) for i in range(0, len(a), 10)]
+        half = len(ds) // 2
         return {"max_abs": max(d), "mean_abs": sum(d) / len(d), "final_abs": d[-1],
-                "mean_abs_last_tenth": sum(d[-tail:]) / tail, "first_step_abs": d[0]}
+                "mean_abs_last_tenth": sum(d[-tail:]) / tail, "first_step_abs": d[0],
+                "max_abs_of_10_step_means": max(ds), "max_abs_of_10_step_means_second_half": max(ds[half:] or ds)}
 
     out = {"config": "parity", "steps": n, "model": f"CareStudentLM {LAYERS}x{DIM} V{VOCAB} ff_mult {FF_MULT}",
            "global_batch": args.batch, "seq_len": args.seq, "optimizer": f"Muon lr {LR} wd {WD} clip {CLIP}",

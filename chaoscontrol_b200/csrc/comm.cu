@@ -466,6 +466,11 @@ extern "C" void* ccb_comm_malloc(int64_t bytes) {
 extern "C" int ccb_comm_free(void* p) {
   return cudaFree(p) == cudaSuccess ? 0 : set_error("cudaFree failed");
 }
+// Zero `bytes` of a communicator allocation and wait for it (pad reset during a resynchronisation).
+extern "C" int ccb_comm_clear(void* p, int64_t bytes) {
+  if (cudaMemset(p, 0, (size_t)bytes) != cudaSuccess) return set_error("ccb_comm_clear: cudaMemset failed");
+  return cudaDeviceSynchronize() == cudaSuccess ? 0 : set_error("ccb_comm_clear: synchronize failed");
+}
 extern "C" int ccb_ipc_get(void* ptr, void* out64) {
   cudaIpcMemHandle_t h;
   cudaError_t e = cudaIpcGetMemHandle(&h, ptr);

@@ -70,6 +70,7 @@ __global__ void embed_fwd_kernel(const TokT* __restrict__ tok, const __nv_bfloat
 // continues from the previous chunk or into the next one is written to the
 // chunk's boundary slot instead: slot 0 for a run that starts at the chunk's
 // first position, slot 1 for a run that starts later and runs off its end.
+// Stage 1 also records, per token, the first and the last sorted position it occupies.
 // Stage 2: one block per token whose rows span several chunks adds the
 // boundary slots of those chunks in chunk order and stores the row of dE.
 // The summation order is a function of the sorted token array alone, so two
@@ -84,7 +85,8 @@ __global__ void embed_bwd_runs_kernel(const long long* __restrict__ sorted_tok,
                                       const long long* __restrict__ perm,
                                       const __nv_bfloat16* __restrict__ dx,
                                       float* __restrict__ dE, float* __restrict__ slots,
-                                      long long R, int D, int V) {
+                                      long long* __restrict__ first_pos,
+                                      long long* __restrict__ last_pos, long long R, int D, int V) {
   const long long chunk = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const long long p0 = chunk * EMB_CH;
   if (p0 >= R) return;
@@ -96,6 +98,17 @@ __global__ void embed_bwd_runs_kernel(const long long* __restrict__ sorted_tok,
   const long long my_row = (lane < n) ? perm[p0 + lane] : 0;
   const long long tok_before = (p0 > 0) ? sorted_tok[p0 - 1] : -1;
   const long long tok_after = (p1 < R) ? sorted_tok[p1] : -1;
+  {
+    // token boundaries: where a token's rows begin and end in the sorted order
+    long long prev = __shfl_up_sync(0xffffffffu, my_tok, 1);
+    long long next = __shfl_down_sync(0xffffffffu, my_tok, 1);
+    if (lane == 0) prev = tok_before;
+    if (lane == n - 1) next = tok_after;
+    if (lane < n && my_tok >= 0 && my_tok < V) {
+      if (prev != my_tok) first_pos[my_tok] = p0 + lane;
+      if (next != my_tok) last_pos[my_tok] = p0 + lane;
+    }
+  }
   float acc[VPL][8];
 #pragma unroll
   for (int v = 0; v < VPL; ++v)
@@ -159,62 +172,67 @@ __global__ void embed_bwd_runs_kernel(const long long* __restrict__ sorted_tok,
   flush(cur, run_start, n);
 }
 
-// first position p in [0, R) with sorted_tok[p] >= key (R if none)
-__device__ __forceinline__ long long emb_lower_bound(const long long* __restrict__ a, long long R,
-                                                     long long key) {
-  long long lo = 0, hi = R;
-  while (lo < hi) {
-    const long long mid = (lo + hi) >> 1;
-    if (a[mid] < key) lo = mid + 1; else hi = mid;
-  }
-  return lo;
-}
-
-// grid: V blocks of 128 threads; thread t owns columns [t * D/128, (t+1) * D/128).
-template <int CPT>   // columns per thread: D = 128 * CPT
-__global__ void embed_bwd_join_kernel(const long long* __restrict__ sorted_tok,
-                                      const float* __restrict__ slots, float* __restrict__ dE,
-                                      long long R, int D) {
-  __shared__ long long se[2];
+// grid: V blocks of 16 warps.  Warp w adds the boundary slots k = w, w + 16, ... of the token's
+// chunk run in order (lane l owns columns [l * D/32, (l+1) * D/32)), then warp 0 adds the sixteen
+// warp sums in warp order: a fixed tree, wide enough that the most frequent token of a Zipf batch
+// (thousands of chunks) does not serialise behind one warp.
+// first_pos / last_pos come from stage 1; last_pos is -1 for tokens that do not occur.
+constexpr int EMB_JOIN_WARPS = 16;
+template <int FPL>   // floats per lane: D = 32 * FPL
+__global__ void __launch_bounds__(EMB_JOIN_WARPS * 32)
+embed_bwd_join_kernel(const long long* __restrict__ first_pos, const long long* __restrict__ last_pos,
+                      const float* __restrict__ slots, float* __restrict__ dE, int D) {
   const long long tk = blockIdx.x;
-  if (threadIdx.x == 0) {
-    se[0] = emb_lower_bound(sorted_tok, R, tk);
-    se[1] = emb_lower_bound(sorted_tok, R, tk + 1);
-  }
-  __syncthreads();
-  const long long s = se[0], e = se[1];
-  if (e <= s) return;
+  const long long e = last_pos[tk] + 1;
+  if (e <= 0) return;
+  const long long s = first_pos[tk];
   const long long cs = s / EMB_CH, ce = (e - 1) / EMB_CH;
   if (cs == ce) return;                       // one owner: stored by stage 1
-  float acc[CPT];
-  const int c0 = threadIdx.x * CPT;
-  {
-    const float* p = slots + (cs * 2 + ((s % EMB_CH) == 0 ? 0 : 1)) * (long long)D + c0;
+  extern __shared__ float sm_join[];          // [EMB_JOIN_WARPS][D]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c0 = lane * FPL;
+  const long long n = ce - cs + 1;            // slots to add: chunk cs (first or second slot), then first slots
+  const int first_slot = ((s % EMB_CH) == 0) ? 0 : 1;
+  float acc[FPL];
 #pragma unroll
-    for (int i = 0; i < CPT; ++i) acc[i] = p[i];
-  }
-  long long c = cs + 1;
-  for (; c + 4 <= ce + 1; c += 4) {
-    float t[4][CPT];
+  for (int i = 0; i < FPL; ++i) acc[i] = 0.f;
+  auto slot_ptr = [&](long long k) {
+    return slots + ((cs + k) * 2 + (k == 0 ? first_slot : 0)) * (long long)D + c0;
+  };
+  long long k = warp;
+  for (; k + 3 * EMB_JOIN_WARPS < n; k += 4 * EMB_JOIN_WARPS) {
+    float4 t[4][FPL / 4];
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-      const float* p = slots + ((c + u) * 2) * (long long)D + c0;
+      const float4* p = reinterpret_cast<const float4*>(slot_ptr(k + u * EMB_JOIN_WARPS));
 #pragma unroll
-      for (int i = 0; i < CPT; ++i) t[u][i] = p[i];
+      for (int i = 0; i < FPL / 4; ++i) t[u][i] = p[i];
     }
 #pragma unroll
     for (int u = 0; u < 4; ++u)
 #pragma unroll
-      for (int i = 0; i < CPT; ++i) acc[i] += t[u][i];
+      for (int i = 0; i < FPL / 4; ++i) {
+        acc[4 * i] += t[u][i].x; acc[4 * i + 1] += t[u][i].y;
+        acc[4 * i + 2] += t[u][i].z; acc[4 * i + 3] += t[u][i].w;
+      }
   }
-  for (; c <= ce; ++c) {
-    const float* p = slots + (c * 2) * (long long)D + c0;
+  for (; k < n; k += EMB_JOIN_WARPS) {
+    const float4* p = reinterpret_cast<const float4*>(slot_ptr(k));
 #pragma unroll
-    for (int i = 0; i < CPT; ++i) acc[i] += p[i];
+    for (int i = 0; i < FPL / 4; ++i) {
+      const float4 v = p[i];
+      acc[4 * i] += v.x; acc[4 * i + 1] += v.y; acc[4 * i + 2] += v.z; acc[4 * i + 3] += v.w;
+    }
   }
-  float* o = dE + tk * D + c0;
 #pragma unroll
-  for (int i = 0; i < CPT; ++i) o[i] = acc[i];
+  for (int i = 0; i < FPL; ++i) sm_join[warp * D + c0 + i] = acc[i];
+  __syncthreads();
+  for (int c = threadIdx.x; c < D; c += blockDim.x) {
+    float t = sm_join[c];
+#pragma unroll
+    for (int w = 1; w < EMB_JOIN_WARPS; ++w) t += sm_join[w * D + c];
+    dE[tk * D + c] = t;
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -563,9 +581,10 @@ extern "C" int ccb_embed_fwd(const void* tok, int64_t tok_is_i64, const void* E,
   return 0;
 }
 
-// slots: workspace of ccb_embed_bwd_slots(R, D) floats (boundary sums of stage 1; need not be zeroed).
-extern "C" int64_t ccb_embed_bwd_slots(int64_t R, int64_t D) {
-  return ((R + EMB_CH - 1) / EMB_CH) * 2 * D;
+// slots: workspace of ccb_embed_bwd_slots(R, D, V) floats, 16-byte aligned: the boundary sums of
+// stage 1 followed by the per-token first / last positions (need not be initialised).
+extern "C" int64_t ccb_embed_bwd_slots(int64_t R, int64_t D, int64_t V) {
+  return ((R + EMB_CH - 1) / EMB_CH) * 2 * D + 4 * V;
 }
 extern "C" int ccb_embed_bwd_sorted(const int64_t* sorted_tok, const int64_t* perm, const void* dx,
                                     float* dE, float* slots, int64_t R, int64_t D, int64_t V,
@@ -579,18 +598,27 @@ extern "C" int ccb_embed_bwd_sorted(const int64_t* sorted_tok, const int64_t* pe
   const long long* st = (const long long*)sorted_tok;
   const long long* pm = (const long long*)perm;
   const __nv_bfloat16* g = (const __nv_bfloat16*)dx;
+  long long* fp = reinterpret_cast<long long*>(slots + chunks * 2 * D);
+  long long* lp = fp + V;
+  cudaMemsetAsync(lp, 0xFF, sizeof(long long) * (size_t)V, s);      // -1: token does not occur
   if (D == 256) {
-    embed_bwd_runs_kernel<1><<<grid, wpb * 32, 0, s>>>(st, pm, g, dE, slots, R, (int)D, (int)V);
+    embed_bwd_runs_kernel<1><<<grid, wpb * 32, 0, s>>>(st, pm, g, dE, slots, fp, lp, R, (int)D, (int)V);
     CCB_CHECK_LAUNCH("embed_bwd_runs");
-    embed_bwd_join_kernel<2><<<(unsigned)V, 128, 0, s>>>(st, slots, dE, R, (int)D);
+    embed_bwd_join_kernel<8><<<(unsigned)V, EMB_JOIN_WARPS * 32, EMB_JOIN_WARPS * D * sizeof(float), s>>>(
+        fp, lp, slots, dE, (int)D);
   } else if (D == 512) {
-    embed_bwd_runs_kernel<2><<<grid, wpb * 32, 0, s>>>(st, pm, g, dE, slots, R, (int)D, (int)V);
+    embed_bwd_runs_kernel<2><<<grid, wpb * 32, 0, s>>>(st, pm, g, dE, slots, fp, lp, R, (int)D, (int)V);
     CCB_CHECK_LAUNCH("embed_bwd_runs");
-    embed_bwd_join_kernel<4><<<(unsigned)V, 128, 0, s>>>(st, slots, dE, R, (int)D);
+    embed_bwd_join_kernel<16><<<(unsigned)V, EMB_JOIN_WARPS * 32, EMB_JOIN_WARPS * D * sizeof(float), s>>>(
+        fp, lp, slots, dE, (int)D);
   } else if (D == 1024) {
-    embed_bwd_runs_kernel<4><<<grid, wpb * 32, 0, s>>>(st, pm, g, dE, slots, R, (int)D, (int)V);
+    embed_bwd_runs_kernel<4><<<grid, wpb * 32, 0, s>>>(st, pm, g, dE, slots, fp, lp, R, (int)D, (int)V);
     CCB_CHECK_LAUNCH("embed_bwd_runs");
-    embed_bwd_join_kernel<8><<<(unsigned)V, 128, 0, s>>>(st, slots, dE, R, (int)D);
+    // sixteen [1024] strips are 64 KiB of shared memory: above the default limit, opt in
+    cudaFuncSetAttribute(embed_bwd_join_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         (int)(EMB_JOIN_WARPS * 1024 * sizeof(float)));
+    embed_bwd_join_kernel<32><<<(unsigned)V, EMB_JOIN_WARPS * 32, EMB_JOIN_WARPS * D * sizeof(float), s>>>(
+        fp, lp, slots, dE, (int)D);
   } else {
     return set_error("ccb_embed_bwd_sorted: D=%lld unsupported (256, 512, 1024)", (long long)D);
   }

@@ -40,9 +40,8 @@
 //
 // Warp roles: warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, then 4 * PARTS epilogue
 // warps (warp w: TMEM lanes 32*(w%4).., column part (w-2)/4).  PARTS = 2 gives each epilogue warp
-// two 32-column groups of every 128-column logits tile, PARTS = 4 one group: the epilogue is a
-// latency chain (TMEM load -> exp2 -> pack -> shared-memory store) between the two MMAs, and
-// sixteen warps, four per scheduler, cover each other's stalls where eight cannot.
+// two 32-column groups of every 128-column logits tile, PARTS = 4 one group (four warps per
+// scheduler instead of two).
 #include "ptx.cuh"
 #include "ccb_api.h"
 #include "runtime.h"
@@ -722,7 +721,10 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
   }
 }
 
-static int g_lh_parts = 4;   // epilogue column parts (2: eight epilogue warps, 4: sixteen)
+// Epilogue column parts: 2 = eight epilogue warps, 4 = sixteen; 0 = per mode, as measured on a B200
+// at 262 144 rows: the scoring sweep gains from sixteen warps (1.81 -> 1.77 ms), the training kernels
+// lose (7.76 -> 8.11 ms for the one-sweep kernel plus the dW kernel).
+static int g_lh_parts = 0;
 
 template <int MODE, int PARTS>
 static int launch_lmhead_p(const void* X, const void* W, LmHeadArgs& a, cudaStream_t stream) {
@@ -749,19 +751,20 @@ static int launch_lmhead_p(const void* X, const void* W, LmHeadArgs& a, cudaStre
 
 template <int MODE>
 static int launch_lmhead(const void* X, const void* W, LmHeadArgs& a, cudaStream_t stream) {
-  return g_lh_parts == 2 ? launch_lmhead_p<MODE, 2>(X, W, a, stream)
-                         : launch_lmhead_p<MODE, 4>(X, W, a, stream);
+  const int parts = g_lh_parts ? g_lh_parts : (MODE == MODE_LSE ? 4 : 2);
+  return parts == 2 ? launch_lmhead_p<MODE, 2>(X, W, a, stream)
+                    : launch_lmhead_p<MODE, 4>(X, W, a, stream);
 }
 
 }  // namespace ccb
 
 using namespace ccb;
 
-// Epilogue width of the fused LM-head kernels: 2 (eight epilogue warps) or 4 (sixteen, default).
-// Returns the previous value; other arguments leave it unchanged.
+// Epilogue width of the fused LM-head kernels: 2 (eight epilogue warps), 4 (sixteen) or 0 (the
+// per-mode default).  Returns the previous value; other arguments leave it unchanged.
 extern "C" int ccb_lmhead_epilogue_parts(int parts) {
   const int old = g_lh_parts;
-  if (parts == 2 || parts == 4) g_lh_parts = parts;
+  if (parts == 0 || parts == 2 || parts == 4) g_lh_parts = parts;
   return old;
 }
 

@@ -65,7 +65,7 @@ _SIGS = {
     "ccb_plain_scan_bwd": ([vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, vp], C.c_int),
     "ccb_embed_fwd": ([vp, i64, vp, vp, vp, i64, i64, i64, vp], C.c_int),
     "ccb_embed_bwd_sorted": ([vp, vp, vp, vp, vp, i64, i64, i64, vp], C.c_int),
-    "ccb_embed_bwd_slots": ([i64, i64], C.c_int64),
+    "ccb_embed_bwd_slots": ([i64, i64, i64], C.c_int64),
     "ccb_lmhead_epilogue_parts": ([C.c_int], C.c_int),
     "ccb_splitk_reduce": ([vp, i64, i64, i64, i64, vp, vp, vp, i64, vp, vp, i64, vp], C.c_int),
     "ccb_colsum": ([vp, i64, i64, vp, i64, vp], C.c_int),

@@ -45,8 +45,14 @@ def diag_recurrence_reference(decay: torch.Tensor, update: torch.Tensor,
 
 def diag_recurrence_chunked(decay: torch.Tensor, update: torch.Tensor, chunk: int = 32,
                             h0: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Chunked cumprod/cumsum form of the same recurrence (fp64 inside a chunk),
-    the vectorised CPU path (cf. src/chaoscontrol/core.py:46-119)."""
+    """Chunked parallel form of the same recurrence (fp64 inside a chunk), the vectorised CPU
+    path (cf. src/chaoscontrol/core.py:46-119).
+
+    Inside a chunk ``h[t] = sum_{j<=t} exp(L[t] - L[j]) u[j] + exp(L[t]) carry`` with ``L`` the
+    running sum of ``log decay``.  Every exponent is <= 0, so nothing overflows or divides by an
+    underflowed product however small the decays get (a cumulative-product form ``cp * cumsum(u /
+    cp)`` turns into 0 * inf once a chunk's product underflows, which strongly decaying channels
+    reach after a few optimizer steps)."""
     B, T, D = update.shape
     dt = torch.float64
     dec = decay.to(dt)
@@ -56,10 +62,12 @@ def diag_recurrence_chunked(decay: torch.Tensor, update: torch.Tensor, chunk: in
     for t0 in range(0, T, chunk):
         d = dec[:, t0:t0 + chunk]
         u = upd[:, t0:t0 + chunk]
-        logp = torch.cumsum(torch.log(d.clamp_min(1e-300)), dim=1)
-        cp = torch.exp(logp)
-        # h[t] = cp[t] * (carry + sum_{j<=t} u[j] / cp[j])
-        h = cp * (carry.unsqueeze(1) + torch.cumsum(u / cp, dim=1))
+        c = d.shape[1]
+        logp = torch.cumsum(torch.log(d.clamp_min(1e-300)), dim=1)           # [B, c, D]
+        diff = logp.unsqueeze(2) - logp.unsqueeze(1)                          # [B, t, j, D] = L[t] - L[j]
+        lower = torch.ones(c, c, dtype=torch.bool, device=update.device).tril()
+        w = torch.exp(diff.masked_fill(~lower[None, :, :, None], float("-inf")))
+        h = torch.einsum("btjd,bjd->btd", w, u) + torch.exp(logp) * carry.unsqueeze(1)
         outs.append(h)
         carry = h[:, -1]
     return torch.cat(outs, dim=1).to(torch.float32)

@@ -87,7 +87,7 @@ def embed_bwd(tokens: torch.Tensor, dx: torch.Tensor, V: int,
             sort_cache = torch.sort(flat, stable=True)
         st, perm = sort_cache
         L = _lib.lib()
-        slots = torch.empty(int(L.ccb_embed_bwd_slots(flat.numel(), D)), dtype=torch.float32,
+        slots = torch.empty(int(L.ccb_embed_bwd_slots(flat.numel(), D, V)), dtype=torch.float32,
                             device=dx.device)
         _lib.check(L.ccb_embed_bwd_sorted(st.data_ptr(), perm.data_ptr(), dx.data_ptr(), dE.data_ptr(),
                                           slots.data_ptr(), flat.numel(), D, V, _lib.stream_ptr()),

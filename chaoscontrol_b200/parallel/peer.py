@@ -41,6 +41,7 @@ _lib.register_sig("ccb_sharded_sync", [i64, vp, vp, i64, C.c_float, vp, i64, vp,
 _lib.register_sig("ccb_allreduce_ranges", [vp, vp, i64, i64, C.c_float, vp, vp, vp, i64, i64, i64, vp, i64, i64, vp])
 _lib.register_sig("ccb_comm_bcast", [vp, i64, i64, vp, vp, vp, i64, i64, i64, vp, i64, vp])
 _lib.register_sig("ccb_comm_flag_max", [i64, vp, i64, i64, i64, vp, i64, vp])
+_lib.register_sig("ccb_comm_clear", [vp, i64])
 
 MAX_RANKS = 8
 PAD_ROWS = 8
@@ -263,6 +264,23 @@ class PeerComm:
             _lib.read_status(reset=True)
             return True
         return False
+
+    def resync(self) -> None:
+        """Collective recovery after a timeout (every rank of the group calls it, between steps, with
+        no collective of this communicator in flight): drain the GPU, meet on the host, clear this
+        rank's own signal pad and arrival counters, restart the epoch and flag sequence from zero,
+        meet again.  Afterwards the communicator is usable as if freshly created; buffers stay mapped."""
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        own_pad = self._pads[self.rank]
+        _lib.check(_lib.lib().ccb_comm_clear(own_pad, PAD_ROWS * MAX_RANKS * 4), "comm_clear")
+        self._counters.zero_()
+        self.epoch = 0
+        self._flag_seq = 0
+        _lib.read_status(reset=True)
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        self.dead = False
 
     def _release(self, barriers: bool) -> None:
         """Unmap the peers' buffers, then free this rank's own.  With ``barriers`` every rank first

@@ -70,6 +70,84 @@ def _worker(rank, ws, port, outdir):
         st = _lib.read_status()
         if st != 0:
             ok, msg = False, f"status {st}"
+        # --- bucketed exchange on a side stream: disjoint ranges, one epoch each -------------
+        x = torch.randn(n, device="cuda", generator=g)
+        ref = x.bfloat16().float() / ws
+        dist.all_reduce(ref)
+        table = comm.make_ranges([(0, 4096, -1), (8192, 65536, -1), (4096, 4096, -1), (73728, n - 73728, -1)])
+        side = torch.cuda.Stream()
+        y = x.clone()
+        ev = torch.cuda.Event()
+        ev.record()
+        side.wait_event(ev)
+        for r0, r1, blocks in ((0, 1, 4), (1, 3, 8), (3, 4, 0)):
+            comm.all_reduce_ranges_(y, table, r0, r1, blocks=blocks, stream=side.cuda_stream)
+        done = torch.cuda.Event()
+        done.record(side)
+        torch.cuda.current_stream().wait_event(done)
+        torch.cuda.synchronize()
+        err = (y - ref).abs().max().item()
+        if err > 2e-2:
+            ok, msg = False, f"bucketed exchange err {err}"
+        # --- broadcast through the root's buffer ------------------------------------------------
+        p = torch.full((n,), float(rank + 1), device="cuda").bfloat16()
+        comm.broadcast_(p, src=1)
+        torch.cuda.synchronize()
+        if not bool((p == 2).all()):
+            ok, msg = False, "broadcast did not deliver rank 1's values"
+        # --- stop-flag consensus through the pads -------------------------------------------
+        from chaoscontrol_b200.parallel import symm
+        from chaoscontrol_b200.parallel.distributed import should_stop_now
+        for want in (0, 1, 0, 3, 7):
+            got = comm.flag_max(want if rank == 1 else 0)
+            if got != want:
+                ok, msg = False, f"flag_max gave {got}, wanted {want}"
+        symm.set_active_comm(comm)
+        dev = torch.device("cuda", rank)
+        if should_stop_now(False, dev, True) or not should_stop_now(rank == 0, dev, True):
+            ok, msg = False, "should_stop_now consensus wrong"
+        # --- a rank skips one collective: the other times out, nothing is touched, both resync ---
+        comm.timeout_ms = 300
+        z = torch.randn(n, device="cuda", generator=g)
+        z0 = z.clone()
+        if rank == 0:
+            comm.all_reduce_(z)
+            torch.cuda.synchronize()
+            if not comm.timed_out():
+                ok, msg = False, "missing peer did not produce a timeout status"
+            if not torch.equal(z, z0):
+                ok, msg = False, "a timed-out all-reduce modified the gradient"
+        else:
+            if comm.timed_out():
+                ok, msg = False, "the rank that skipped reports a timeout"
+        comm.resync()
+        comm.timeout_ms = 2000
+        for rnd in range(2):
+            x = torch.randn(n, device="cuda", generator=g)
+            ref = x.bfloat16().float() / ws
+            dist.all_reduce(ref)
+            comm.all_reduce_(x)
+            torch.cuda.synchronize()
+            err = (x - ref).abs().max().item()
+            if err > 2e-2:
+                ok, msg = False, f"after resync round {rnd} err {err}"
+        # --- a reported timeout makes every rank raise on the same step --------------------
+        from chaoscontrol_b200.parallel.peer import PeerCommError
+        if rank == 0:
+            _lib.check(_lib.lib().ccb_comm_wait_probe(torch.zeros(4, dtype=torch.int32, device="cuda").data_ptr(),
+                                                      5, 20, torch.zeros(1, dtype=torch.int32, device="cuda").data_ptr(),
+                                                      _lib.stream_ptr()), "probe")      # leaves status 3
+        raised = False
+        try:
+            should_stop_now(False, dev, True)
+        except PeerCommError:
+            raised = True
+        if not raised:
+            ok, msg = False, "a timeout on rank 0 did not raise on this rank"
+        symm.set_active_comm(None)
+        comm.resync()
+        if _lib.read_status() != 0:
+            ok, msg = False, f"status {_lib.read_status()} after resync"
         dist.barrier()
         comm.close()
     except Exception as exc:  # pragma: no cover

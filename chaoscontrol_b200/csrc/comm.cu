@@ -314,7 +314,7 @@ comm_gather_params_kernel(__nv_bfloat16* __restrict__ param, const CommRange* __
 // with a small grid of small blocks so that it shares the GPU with the GEMMs of
 // the layers still to come instead of displacing them.
 // ---------------------------------------------------------------------------
-constexpr int COMM_BUCKET_THREADS = 256;
+constexpr int COMM_BUCKET_THREADS = 128;   // 128 x 64 registers: fits beside a resident GEMM / LM-head CTA
 
 __global__ void __launch_bounds__(COMM_BUCKET_THREADS)
 comm_pack_ranges_kernel(const float* __restrict__ grad, const CommRange* __restrict__ ranges, int r0,
@@ -585,7 +585,7 @@ extern "C" int ccb_sharded_sync(int64_t phase, float* grad, void* param, int64_t
 
 // One bucket of the overlapped exchange: pack + one-shot reduce of ranges [r0, r1) of the device
 // table (records {int64 off8, int64 len8, int32 owner, int32 pad}; owner is ignored here) on
-// `stream`, with `blocks` blocks of 256 threads per kernel (0: one block per SM).
+// `stream`, with `blocks` blocks of 128 threads per kernel (0: one block per SM).
 extern "C" int ccb_allreduce_ranges(float* grad, const void* ranges, int64_t r0, int64_t r1, float scale,
                                     void* const* bufs, void* const* bufs2, void* const* pads, int64_t rank,
                                     int64_t ws, int64_t epoch, void* counters, int64_t blocks,

@@ -10,6 +10,13 @@
 //   warps 2..9  epilogue; warp w reads TMEM lanes [32*(w%4), 32*(w%4)+32), the
 //               two warps of a lane quadrant take alternate 64-column groups
 //
+// CG = 2 runs the same pipeline on a CTA pair (2-CTA cluster, tcgen05 cta_group::2): the pair owns a
+// 256-row x BN tile, each CTA stages its own 128 rows of A and HALF of the B tile, the leader CTA's
+// MMA thread issues 256-row instructions that read both CTAs' shared memory, each CTA drains its own
+// 128 accumulator rows.  The trunk GEMMs are bound by the weight tile every CTA re-reads from L2 for
+// each row tile (about 8 TB/s of L2 -> SM traffic measured at N = 1024, K = 256), and the pair halves
+// exactly that stream.  Nothing is multicast: each CTA issues its own plain TMA loads.
+//
 // Replaces the library GEMM call sites of the reference trunk
 // (src/chaoscontrol/core.py:453-474, 503, 545, 327-335) and the batched
 // Newton-Schulz matmuls (src/chaoscontrol/optim/muon.py:42-45).
@@ -62,10 +69,11 @@ constexpr int STG_BUF_BYTES = 32 * 128;
 constexpr int STG_BUFS_PER_WARP = 2;
 constexpr int STG_BYTES = EPI_WARPS * STG_BUFS_PER_WARP * STG_BUF_BYTES;   // 64 KiB
 
-template <int BN>
+template <int BN, int CG = 1>
 struct GemmCfg {
-  static constexpr int B_STAGE_BYTES = BN * BK * 2;
-  static constexpr int STAGES = (BN == 256) ? 3 : 4;
+  static constexpr int B_ROWS = BN / CG;                  // rows of the B tile this CTA stages
+  static constexpr int B_STAGE_BYTES = B_ROWS * BK * 2;
+  static constexpr int STAGES = (BN == 256 && CG == 1) ? 3 : 4;
   static constexpr int TMEM_COLS = 2 * BN;   // 512 or 256: powers of two
   static constexpr int STG_OFF = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);
   static constexpr int BAR_OFF = STG_OFF + STG_BYTES;
@@ -126,7 +134,7 @@ struct TileCoord {
   int b, sp, m0, n0, kb0, kb1;
 };
 
-__device__ __forceinline__ TileCoord decode_tile(const GemmKArgs& p, int tile, int BN) {
+__device__ __forceinline__ TileCoord decode_tile(const GemmKArgs& p, int tile, int BN, int bm = BM) {
   TileCoord t;
   int tn = tile % p.tiles_n;
   int r = tile / p.tiles_n;
@@ -134,7 +142,7 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmKArgs& p, int tile, i
   r /= p.tiles_m;
   t.sp = r % p.splits;
   t.b = r / p.splits;
-  t.m0 = tm * BM;
+  t.m0 = tm * bm;
   t.n0 = tn * BN;
   t.kb0 = t.sp * p.kper;
   t.kb1 = min(p.kblocks, t.kb0 + p.kper);
@@ -153,12 +161,18 @@ __device__ __forceinline__ float gemm_ex2(float x) {
 // LM = 1 compiles the LM-head epilogues (LSE_PART, CE_GRAD) instead of the trunk set.
 // EPI_T >= 0 fixes the epilogue at compile time (the hot trunk epilogues: no dispatch, less
 // code, fewer live registers in the chunk loop); EPI_T = -1 reads it from the arguments.
-template <int BN, int A_MN, int B_MN, int LM, int EPI_T>
+template <int BN, int A_MN, int B_MN, int LM, int EPI_T, int CG>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmC2,
             const GemmKArgs p) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, CG>;
+  static_assert(CG == 1 || (A_MN == 0 && LM == 0), "CTA pairs: K-major A, trunk epilogues");
+  // pair geometry: `cta_rank` 0 is the leader (issues the MMAs, owns the barriers the loads and the
+  // epilogues of both CTAs report to); the pair walks tiles of BM * CG rows together
+  const uint32_t cta_rank = (CG == 2) ? cluster_ctarank() : 0u;
+  const int walker = (int)blockIdx.x / CG, n_walkers = (int)gridDim.x / CG;
+  constexpr int BM_TILE = BM * CG;
   const int epi_k = (EPI_T >= 0) ? EPI_T : p.epi;
   constexpr int STAGES = Cfg::STAGES;
   constexpr int B_STAGE_BYTES = Cfg::B_STAGE_BYTES;
@@ -189,7 +203,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);
-      mbar_init(&tempty_bar[a], EPI_WARPS);
+      mbar_init(&tempty_bar[a], EPI_WARPS * CG);      // the leader's collects both CTAs' epilogue warps
     }
     mbar_init(xbar, EPI_WARPS);
     *abort_flag = 0;
@@ -198,11 +212,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     tma_prefetch_desc(&tmB);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
-    tmem_relinquish();
+    if (CG == 2) {
+      tmem_alloc_cg2(tmem_slot, Cfg::TMEM_COLS);      // one warp of EACH CTA of the pair
+      tmem_relinquish_cg2();
+    } else {
+      tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before_sync();
   __syncthreads();
+  if (CG == 2) cluster_sync_all();     // both CTAs' barriers exist before either touches the peer's
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -212,14 +232,31 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        TileCoord t = decode_tile(p, tile, BN);
+      for (int tile = walker; tile < total_tiles && ok; tile += n_walkers) {
+        TileCoord t = decode_tile(p, tile, BN, BM_TILE);
         for (int hn = 0; hn <= p.pair && ok; ++hn, t.n0 += BN)
         for (int kb = t.kb0; kb < t.kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status)) { ok = false; break; }
-          mbar_arrive_expect_tx(&full_bar[stage], A_STAGE_BYTES + B_STAGE_BYTES);
           uint8_t* a_dst = sA + stage * A_STAGE_BYTES;
           uint8_t* b_dst = sB + stage * B_STAGE_BYTES;
+          if (CG == 2) {
+            // the stage is complete when BOTH CTAs' halves have landed: all four loads report to the
+            // leader's barrier, which expects the bytes of the pair
+            if (cta_rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * (A_STAGE_BYTES + B_STAGE_BYTES));
+            const uint32_t fb = mapa_shared(smem_u32(&full_bar[stage]), 0);
+            tma_load_3d_cg2(a_dst, &tmA, fb, kb * p.bk, t.m0 + BM * (int)cta_rank, t.b);
+            if (B_MN == 0) {
+              tma_load_3d_cg2(b_dst, &tmB, fb, kb * p.bk, t.n0 + Cfg::B_ROWS * (int)cta_rank, t.b);
+            } else {
+#pragma unroll
+              for (int j = 0; j < Cfg::B_ROWS / 64; ++j)
+                tma_load_3d_cg2(b_dst + j * 8192, &tmB, fb, t.n0 + Cfg::B_ROWS * (int)cta_rank + 64 * j,
+                                kb * BK, t.b);
+            }
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            continue;
+          }
+          mbar_arrive_expect_tx(&full_bar[stage], A_STAGE_BYTES + B_STAGE_BYTES);
           if (A_MN == 0) {
             tma_load_3d(a_dst, &tmA, &full_bar[stage], kb * p.bk, t.m0, t.b);
           } else {
@@ -246,14 +283,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+    if (lane == 0 && cta_rank == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM_TILE, BN, A_MN, B_MN);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
-        TileCoord t = decode_tile(p, tile, BN);
+      for (int tile = walker; tile < total_tiles && ok; tile += n_walkers, ++it) {
+        TileCoord t = decode_tile(p, tile, BN, BM_TILE);
         const int acc = p.pair ? 0 : (it & 1);
         const uint32_t acc_phase = (uint32_t)(p.pair ? it : (it >> 1)) & 1u;
         if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, abort_flag, p.status)) { ok = false; break; }
@@ -272,14 +309,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             const uint64_t bdesc = B_MN ? make_smem_desc(b_base + k * 2048, 8192, 1024)
                                         : make_smem_desc(b_base + k * 32, 16, 1024);
             const uint32_t accum = (kb > t.kb0 || k > 0) ? 1u : 0u;
-            if (p.f8) umma_f8(d_tmem, adesc, bdesc, p.idesc_f8, accum);   // 32 one-byte k per MMA
+            if (CG == 2) umma_bf16_cg2(d_tmem, adesc, bdesc, idesc, accum);   // 256 rows over the pair
+            else if (p.f8) umma_f8(d_tmem, adesc, bdesc, p.idesc_f8, accum);   // 32 one-byte k per MMA
             else umma_bf16(d_tmem, adesc, bdesc, idesc, accum);           // 16 two-byte k per MMA
           }
-          umma_commit(&empty_bar[stage]);   // stage reusable once these MMAs retire
+          // stage reusable once these MMAs retire (in both CTAs of a pair)
+          if (CG == 2) umma_commit_cg2(&empty_bar[stage]); else umma_commit(&empty_bar[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
         }
-        if (ok) umma_commit(&tfull_bar[acc]);
+        if (ok) { if (CG == 2) umma_commit_cg2(&tfull_bar[acc]); else umma_commit(&tfull_bar[acc]); }
       }
     }
   } else {
@@ -302,8 +341,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       xphase ^= 1u;
       return __all_sync(0xffffffffu, w);
     };
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
-      TileCoord t = decode_tile(p, tile, BN);
+    for (int tile = walker; tile < total_tiles && ok; tile += n_walkers, ++it) {
+      TileCoord t = decode_tile(p, tile, BN, BM_TILE);
+      t.m0 += BM * (int)cta_rank;             // this CTA's 128 rows of the pair's tile
       const int acc = p.pair ? 0 : (it & 1);
       const uint32_t acc_phase = (uint32_t)(p.pair ? it : (it >> 1)) & 1u;
       const uint32_t t_addr = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(q * 32) << 16);
@@ -612,7 +652,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      if (lane == 0) {
+        if (CG == 2) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty_bar[acc]), 0));
+        else mbar_arrive(&tempty_bar[acc]);
+      }
     }
     // all of this warp's stores must have left shared memory and landed
     if (p.tma_store && lane == 0) tma_store_wait_all<0>();
@@ -622,28 +665,50 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   // ------------------------------ teardown ------------------------------------
   tc_fence_before_sync();
   __syncthreads();
+  // a pair leaves together: the leader's barriers take remote arrivals and its MMAs read the
+  // follower's shared memory until the last tile
+  if (CG == 2) cluster_sync_all();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    if (CG == 2) tmem_dealloc_cg2(tmem_base, Cfg::TMEM_COLS); else tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
 }
 
 // ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
-template <int BN, int A_MN, int B_MN, int LM = 0, int EPI_T = -1>
+template <int BN, int A_MN, int B_MN, int LM = 0, int EPI_T = -1, int CG = 1>
 static int launch_gemm(const CcbGemmArgs* a, cudaStream_t stream) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, CG>;
   static bool attr_set[16] = {false};
+  static int max_pairs[16] = {0};
   int dev = 0;
   cudaGetDevice(&dev);
-  auto kern = gemm_kernel<BN, A_MN, B_MN, LM, EPI_T>;
+  auto kern = gemm_kernel<BN, A_MN, B_MN, LM, EPI_T, CG>;
   if (!attr_set[dev & 15]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return set_error("cudaFuncSetAttribute(gemm): %s", cudaGetErrorString(e));
+    if (CG == 2) {
+      // how many 2-CTA clusters of this kernel the device runs at once (one CTA per SM by shared memory)
+      cudaLaunchConfig_t qc = {};
+      qc.gridDim = dim3((unsigned)(ccb_num_sms() / 2 * 2));
+      qc.blockDim = dim3(GEMM_THREADS);
+      qc.dynamicSmemBytes = Cfg::SMEM_BYTES;
+      cudaLaunchAttribute qa[1];
+      qa[0].id = cudaLaunchAttributeClusterDimension;
+      qa[0].val.clusterDim.x = 2; qa[0].val.clusterDim.y = 1; qa[0].val.clusterDim.z = 1;
+      qc.attrs = qa; qc.numAttrs = 1;
+      int n = 0;
+      e = cudaOccupancyMaxActiveClusters(&n, kern, &qc);
+      if (e != cudaSuccess || n < 1)
+        return set_error("cudaOccupancyMaxActiveClusters(gemm pair): %s", cudaGetErrorString(e));
+      max_pairs[dev & 15] = n;
+    }
     attr_set[dev & 15] = true;
   }
+  if (CG == 2 && (a->a_fp8 != 0 || A_MN != 0))
+    return set_error("ccb_gemm: CTA pairs take K-major bf16 A operands");
   CUtensorMap tmA, tmB;
   const bool f8 = a->a_fp8 != 0;
   if (f8) {
@@ -663,7 +728,7 @@ static int launch_gemm(const CcbGemmArgs* a, cudaStream_t stream) {
   }
   if (B_MN == 0) {
     if (make_tmap_bf16_3d(&tmB, a->B, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)a->batch,
-                          (uint64_t)a->ldb, (uint64_t)a->b_batch, BK, BN)) return -1;
+                          (uint64_t)a->ldb, (uint64_t)a->b_batch, BK, BN / CG)) return -1;
   } else {
     if (make_tmap_bf16_3d(&tmB, a->B, (uint64_t)a->N, (uint64_t)a->K, (uint64_t)a->batch,
                           (uint64_t)a->ldb, (uint64_t)a->b_batch, 64, BK)) return -1;
@@ -693,7 +758,7 @@ static int launch_gemm(const CcbGemmArgs* a, cudaStream_t stream) {
   p.tma_store = tma_ok ? 1 : 0;
   p.M = (int)a->M; p.N = (int)a->N; p.K = (int)a->K;
   p.batch = (int)a->batch;
-  p.tiles_m = (p.M + BM - 1) / BM;
+  p.tiles_m = (p.M + BM * CG - 1) / (BM * CG);
   p.tiles_n = (p.N + BN - 1) / BN;
   p.kblocks = (p.K + p.bk - 1) / p.bk;
   int splits = (int)(a->splits < 1 ? 1 : a->splits);
@@ -730,6 +795,23 @@ static int launch_gemm(const CcbGemmArgs* a, cudaStream_t stream) {
   }
   long long total = (long long)p.batch * p.splits * p.tiles_m * p.tiles_n;
   if (total <= 0) return 0;
+  if (CG == 2) {
+    if (p.pair) return set_error("ccb_gemm: the 512-column RMSNorm-backward tile is not available on CTA pairs");
+    const int pairs = (int)(total < max_pairs[dev & 15] ? total : max_pairs[dev & 15]);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(2 * pairs));
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, tmC2, p);
+    count_launch();
+    if (e != cudaSuccess) return set_error("gemm pair launch: %s", cudaGetErrorString(e));
+    return 0;
+  }
   int grid = (int)(total < ccb_num_sms() ? total : ccb_num_sms());
   kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, tmC, tmC2, p);
   count_launch();
@@ -741,6 +823,15 @@ static int launch_gemm(const CcbGemmArgs* a, cudaStream_t stream) {
 }  // namespace ccb
 
 static inline int64_t b_fp8_of(const CcbGemmArgs* a) { return a->b_fp8; }
+
+// 1: every GEMM runs one CTA per tile; 2: the K-major-A bf16 GEMMs with at least one full 256-row
+// pair tile run on CTA pairs (cta_group::2).
+static int g_gemm_cta_group = 1;
+extern "C" int ccb_gemm_cta_group(int cg) {
+  const int old = g_gemm_cta_group;
+  if (cg == 1 || cg == 2) g_gemm_cta_group = cg;
+  return old;
+}
 
 extern "C" int ccb_gemm(const CcbGemmArgs* a, void* stream_) {
   using namespace ccb;
@@ -767,6 +858,26 @@ extern "C" int ccb_gemm(const CcbGemmArgs* a, void* stream_) {
       default: break;
     }
   } else {
+    // CTA pairs: bf16, K-major A, a whole number of 8-row-aligned rows per 256-row tile is not
+    // needed (TMA clips), but tiny problems gain nothing; the 512-column RMSNorm-backward tile and
+    // split-K stay on single CTAs
+    const bool pair_ok = g_gemm_cta_group == 2 && !a->a_fp8 && a->a_mn == 0 && a->M >= 512 &&
+                         a->batch == 1 && a->splits <= 1 && !(a->epi == CCB_EPI_RMSBWD && a->N > 256);
+    if (pair_ok && key == 0) {
+      switch ((int)a->epi) {
+        case CCB_EPI_ROWSCALE: return launch_gemm<256, 0, 0, 0, CCB_EPI_ROWSCALE, 2>(a, stream);
+        case CCB_EPI_ROWSCALE_SILU: return launch_gemm<256, 0, 0, 0, CCB_EPI_ROWSCALE_SILU, 2>(a, stream);
+        case CCB_EPI_RESID_SS: return launch_gemm<256, 0, 0, 0, CCB_EPI_RESID_SS, 2>(a, stream);
+        default: return launch_gemm<256, 0, 0, 0, -1, 2>(a, stream);
+      }
+    }
+    if (pair_ok && key == 1) {
+      switch ((int)a->epi) {
+        case CCB_EPI_DSILU: return launch_gemm<256, 0, 1, 0, CCB_EPI_DSILU, 2>(a, stream);
+        case CCB_EPI_RMSBWD: return launch_gemm<256, 0, 1, 0, CCB_EPI_RMSBWD, 2>(a, stream);
+        default: return launch_gemm<256, 0, 1, 0, -1, 2>(a, stream);
+      }
+    }
     if (key == 0) {
       // K-major x K-major carries the trunk's fused epilogues: one instantiation each
       switch ((int)a->epi) {

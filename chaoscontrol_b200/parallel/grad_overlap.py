@@ -27,7 +27,7 @@ from ..utils.arena import ParamArena
 
 
 class OverlappedGradReducer:
-    def __init__(self, arena: ParamArena, comm, layer_names: list[dict], *, early_blocks: int = 24) -> None:
+    def __init__(self, arena: ParamArena, comm, layer_names: list[dict], *, early_blocks: int = 32) -> None:
         self.arena, self.comm = arena, comm
         self.early_blocks = int(early_blocks)
         L = len(layer_names)

@@ -127,7 +127,11 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--lmhead-parts", type=int, default=0, choices=[0, 2, 4],
                     help="epilogue width of the fused LM head: 2 = eight warps, 4 = sixteen (0: library default)")
+    ap.add_argument("--gemm-cg", type=int, default=0, choices=[0, 1, 2],
+                    help="1: one CTA per GEMM tile, 2: CTA pairs (cta_group::2); 0: library default")
     a = ap.parse_args()
+    if a.gemm_cg:
+        _lib.lib().ccb_gemm_cta_group(a.gemm_cg)
     if a.lmhead_parts:
         _lib.lib().ccb_lmhead_epilogue_parts(a.lmhead_parts)
     torch.manual_seed(0)
@@ -149,7 +153,8 @@ def main() -> None:
     times.sort()
     ms = times[len(times) // 2]
     pk = peaks()
-    out = {"kernel": a.kernel, "rows": a.rows, "lmhead_parts": a.lmhead_parts or None, "ms_median": ms, "ms_min": times[0],
+    out = {"kernel": a.kernel, "rows": a.rows, "lmhead_parts": a.lmhead_parts or None, "gemm_cg": a.gemm_cg or None,
+           "ms_median": ms, "ms_min": times[0],
            "GBps": nbytes / ms / 1e6, "frac_hbm": nbytes / ms / 1e6 / pk["hbm_gbs"],
            "TFLOPs": flops / ms / 1e9, "frac_bf16_burst": flops / ms / 1e9 / pk["bf16_tflops"],
            "peaks": pk["src"]}

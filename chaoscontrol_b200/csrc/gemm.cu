@@ -61,6 +61,11 @@ struct GemmKArgs {
   const float* rowweight;
   float2* part_out;
   float* zt_out;
+  // stage-isolation switches for bottleneck analysis (results are then wrong by design):
+  // 1 = epilogue skips its TMA / global stores, 2 = epilogue skips math and staging too,
+  // 4 = epilogue skips the TMEM loads as well, 8 = the MMA issuer issues no MMAs
+  int dbg;
+  int l2pf;     // L2 prefetch: 1 = A tiles two tiles ahead (producer), 2 = next tile's epilogue operands
 };
 
 // bf16 outputs leave through shared-memory staging tiles and TMA stores: each
@@ -69,16 +74,30 @@ constexpr int STG_BUF_BYTES = 32 * 128;
 constexpr int STG_BUFS_PER_WARP = 2;
 constexpr int STG_BYTES = EPI_WARPS * STG_BUFS_PER_WARP * STG_BUF_BYTES;   // 64 KiB
 
-template <int BN, int CG = 1>
+// BRES ("B resident"): every tile a CTA walks has the same N coordinate whenever the grid is a
+// multiple of the N-tile count, so for K <= 256 the whole [BN x K] weight tile (128 KiB) is loaded ONCE
+// and stays in shared memory; only A streams, through a four-stage ring of 16 KiB.  Measured on the
+// packed-projection GEMM (N = 1024, K = 256) with MMAs and epilogue switched off, the bare load ring
+// of the streaming layout (192 KiB per tile, 144 KiB in flight, 1.4 us per stage round trip) takes as
+// long as the whole HBM roofline of the kernel, and MMA and epilogue time then ADD to it because no
+// further tile fits in flight; with B resident a tile needs 64 KiB and a full tile of A is in flight.
+// The staging area shrinks to one buffer per epilogue warp to make room.
+constexpr int BRES_KBLOCKS = 4;
+
+template <int BN, int CG = 1, int BRES = 0>
 struct GemmCfg {
   static constexpr int B_ROWS = BN / CG;                  // rows of the B tile this CTA stages
   static constexpr int B_STAGE_BYTES = B_ROWS * BK * 2;
-  static constexpr int STAGES = (BN == 256 && CG == 1) ? 3 : 4;
+  static constexpr int STAGES = BRES ? 4 : ((BN == 256 && CG == 1) ? 3 : 4);
   static constexpr int TMEM_COLS = 2 * BN;   // 512 or 256: powers of two
-  static constexpr int STG_OFF = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);
-  static constexpr int BAR_OFF = STG_OFF + STG_BYTES;
+  static constexpr int STG_BUFS = BRES ? 1 : STG_BUFS_PER_WARP;
+  static constexpr int A_OFF = BRES ? BRES_KBLOCKS * B_STAGE_BYTES : 0;
+  static constexpr int STG_OFF = BRES ? A_OFF + STAGES * A_STAGE_BYTES : STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);
+  static constexpr int BAR_OFF = STG_OFF + EPI_WARPS * STG_BUFS * STG_BUF_BYTES;
   static constexpr int XCH_OFF = BAR_OFF + 256;     // per-row partials exchanged between warps
-  static constexpr int SMEM_BYTES = 1024 + XCH_OFF + 2 * EPI_PARTS * BM * 4;
+  // the resident layout has no room for alignment slack: its kernel checks that the dynamic
+  // shared-memory window starts on a 1 KiB boundary (it does when the kernel has no static shared memory)
+  static constexpr int SMEM_BYTES = (BRES ? 0 : 1024) + XCH_OFF + 2 * EPI_PARTS * BM * 4;
   static_assert(SMEM_BYTES <= 227 * 1024, "tile configuration exceeds the per-CTA shared memory limit");
 };
 
@@ -161,13 +180,16 @@ __device__ __forceinline__ float gemm_ex2(float x) {
 // LM = 1 compiles the LM-head epilogues (LSE_PART, CE_GRAD) instead of the trunk set.
 // EPI_T >= 0 fixes the epilogue at compile time (the hot trunk epilogues: no dispatch, less
 // code, fewer live registers in the chunk loop); EPI_T = -1 reads it from the arguments.
-template <int BN, int A_MN, int B_MN, int LM, int EPI_T, int CG>
+template <int BN, int A_MN, int B_MN, int LM, int EPI_T, int CG, int BRES>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmC2,
             const GemmKArgs p) {
-  using Cfg = GemmCfg<BN, CG>;
+  using Cfg = GemmCfg<BN, CG, BRES>;
   static_assert(CG == 1 || (A_MN == 0 && LM == 0), "CTA pairs: K-major A, trunk epilogues");
+  static_assert(BRES == 0 || (CG == 1 && A_MN == 0 && LM == 0), "resident B: single CTA, K-major A, trunk epilogues");
+  static_assert(BRES == 0 || EPI_T != CCB_EPI_ROWSCALE_SILU, "resident B has one staging buffer per warp: one output");
+  constexpr int STG_BUFS = Cfg::STG_BUFS;
   // pair geometry: `cta_rank` 0 is the leader (issues the MMAs, owns the barriers the loads and the
   // epilogues of both CTAs report to); the pair walks tiles of BM * CG rows together
   const uint32_t cta_rank = (CG == 2) ? cluster_ctarank() : 0u;
@@ -177,18 +199,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   constexpr int STAGES = Cfg::STAGES;
   constexpr int B_STAGE_BYTES = Cfg::B_STAGE_BYTES;
 
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>(
-      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint8_t* sA = smem;
-  uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = BRES ? smem_raw
+                       : reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                                    ~static_cast<uintptr_t>(1023));
+  if (BRES && (smem_u32(smem) & 1023u) != 0u) {   // the swizzled tiles need a 1 KiB aligned base
+    if (threadIdx.x == 0) atomicCAS(p.status, CCB_OK, CCB_ERR_BAD_SHAPE);
+    return;
+  }
+  uint8_t* sA = smem + Cfg::A_OFF;
+  uint8_t* sB = BRES ? smem : smem + STAGES * A_STAGE_BYTES;     // resident: k-block kb at sB + kb * B_STAGE_BYTES
   uint8_t* sStage = smem + Cfg::STG_OFF;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::BAR_OFF);
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* tfull_bar = empty_bar + STAGES;
   uint64_t* tempty_bar = tfull_bar + 2;
   uint64_t* xbar = tempty_bar + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xbar + 1);
+  uint64_t* bres_bar = xbar + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bres_bar + 1);
   float* xch = reinterpret_cast<float*>(smem + Cfg::XCH_OFF);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -206,6 +234,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       mbar_init(&tempty_bar[a], EPI_WARPS * CG);      // the leader's collects both CTAs' epilogue warps
     }
     mbar_init(xbar, EPI_WARPS);
+    mbar_init(bres_bar, 1);
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmA);
@@ -232,6 +261,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      if (BRES && walker < total_tiles) {
+        // the weight tile of this CTA's N coordinate, all k-blocks, once
+        const TileCoord t0 = decode_tile(p, walker, BN, BM_TILE);
+        mbar_arrive_expect_tx(bres_bar, (uint32_t)(p.kblocks * B_STAGE_BYTES));
+        for (int kb = 0; kb < p.kblocks; ++kb) {
+          uint8_t* b_dst = sB + kb * B_STAGE_BYTES;
+          if (B_MN == 0) {
+            tma_load_3d(b_dst, &tmB, bres_bar, kb * p.bk, t0.n0, 0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_3d(b_dst + j * 8192, &tmB, bres_bar, t0.n0 + 64 * j, kb * BK, 0);
+          }
+        }
+      }
       for (int tile = walker; tile < total_tiles && ok; tile += n_walkers) {
         TileCoord t = decode_tile(p, tile, BN, BM_TILE);
         for (int hn = 0; hn <= p.pair && ok; ++hn, t.n0 += BN)
@@ -239,6 +283,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status)) { ok = false; break; }
           uint8_t* a_dst = sA + stage * A_STAGE_BYTES;
           uint8_t* b_dst = sB + stage * B_STAGE_BYTES;
+          if (A_MN == 0 && CG == 1 && !p.pair && (p.l2pf & 1)) {
+            // the same k-block of the tile after next: into L2 now, so that its load is an L2 hit
+            const int t2 = tile + 2 * n_walkers;
+            if (t2 < total_tiles) {
+              const TileCoord tn = decode_tile(p, t2, BN, BM_TILE);
+              tma_prefetch_3d(&tmA, (tn.kb0 + (kb - t.kb0)) * p.bk, tn.m0, tn.b);
+            }
+          }
+          if (BRES) {
+            mbar_arrive_expect_tx(&full_bar[stage], A_STAGE_BYTES);
+            tma_load_3d(a_dst, &tmA, &full_bar[stage], kb * p.bk, t.m0, t.b);
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            continue;
+          }
           if (CG == 2) {
             // the stage is complete when BOTH CTAs' halves have landed: all four loads report to the
             // leader's barrier, which expects the bytes of the pair
@@ -289,6 +347,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
+      if (BRES && walker < total_tiles) {
+        ok = mbar_wait(bres_bar, 0u, abort_flag, p.status);
+        tc_fence_after_sync();
+      }
       for (int tile = walker; tile < total_tiles && ok; tile += n_walkers, ++it) {
         TileCoord t = decode_tile(p, tile, BN, BM_TILE);
         const int acc = p.pair ? 0 : (it & 1);
@@ -301,7 +363,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t a_base = smem_u32(sA + stage * A_STAGE_BYTES);
-          const uint32_t b_base = smem_u32(sB + stage * B_STAGE_BYTES);
+          const uint32_t b_base = smem_u32(sB + (BRES ? (kb - t.kb0) : stage) * B_STAGE_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
             const uint64_t adesc = A_MN ? make_smem_desc(a_base + k * 2048, 8192, 1024)
@@ -309,6 +371,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             const uint64_t bdesc = B_MN ? make_smem_desc(b_base + k * 2048, 8192, 1024)
                                         : make_smem_desc(b_base + k * 32, 16, 1024);
             const uint32_t accum = (kb > t.kb0 || k > 0) ? 1u : 0u;
+            if (p.dbg & 8) continue;
             if (CG == 2) umma_bf16_cg2(d_tmem, adesc, bdesc, idesc, accum);   // 256 rows over the pair
             else if (p.f8) umma_f8(d_tmem, adesc, bdesc, p.idesc_f8, accum);   // 32 one-byte k per MMA
             else umma_bf16(d_tmem, adesc, bdesc, idesc, accum);           // 16 two-byte k per MMA
@@ -365,7 +428,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       float* xch_acc = xch + acc * (EPI_PARTS * BM);
 
       // TMA-store path: 64-column groups staged in this warp's swizzled buffers
-      uint8_t* my_stage = sStage + (warp - 2) * (STG_BUFS_PER_WARP * STG_BUF_BYTES);
+      uint8_t* my_stage = sStage + (warp - 2) * (STG_BUFS * STG_BUF_BYTES);
       const bool two_out = (epi_k == CCB_EPI_ROWSCALE_SILU);
       auto stage_write = [&](uint8_t* buf, int half, const float (&vals)[32]) {
         uint8_t* row = buf + lane * 128;
@@ -424,6 +487,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           load_bf16x32(rowp + n, vals, p.N - n);
         }
       };
+      if ((p.l2pf & 2) && (aux1_row != nullptr || aux2_row != nullptr)) {
+        // the operands the NEXT tile's epilogue will read row by row: into L2 now (one 128-byte line
+        // per 64-column group of this warp), so those loads do not pay the DRAM latency in the loop
+        const int t1 = tile + n_walkers;
+        if (t1 < total_tiles) {
+          TileCoord tn = decode_tile(p, t1, BN, BM_TILE);
+          const int mn = tn.m0 + BM * (int)cta_rank + row_in_tile;
+          if (mn < p.M) {
+            for (int k = 0; k < nmine; k += 2) {
+              const int n = tn.n0 + chunk_of(k) * 32;
+              if (n < p.N) {
+                if (aux1_row != nullptr)
+                  prefetch_l2(aux1_row + (long long)(mn - m) * (epi_k == CCB_EPI_STORE ? p.ldcin : p.ldr) + n +
+                              (long long)(epi_k == CCB_EPI_STORE ? (tn.b - t.b) * p.cin_batch : 0));
+                if (aux2_row != nullptr) prefetch_l2(aux2_row + (long long)(mn - m) * p.ldr + n);
+              }
+            }
+          }
+        }
+      }
       uint4 a1_cur[4], a2_cur[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) a1_cur[i] = a2_cur[i] = make_uint4(0, 0, 0, 0);
@@ -488,13 +571,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (p.tma_store && (c & 1) == 0) {
           __syncwarp();
           if (lane == 0) {
-            if (two_out) tma_store_wait_read<0>(); else tma_store_wait_read<1>();
+            // two outputs, or one staging buffer per warp: every earlier store must have left it
+            if (two_out || STG_BUFS == 1) tma_store_wait_read<0>(); else tma_store_wait_read<1>();
           }
           __syncwarp();
         }
       };
       // one 32-column chunk whose accumulator values are already in `r`
       auto chunk_body = [&](int c, const uint32_t (&r)[32]) {
+        if (p.dbg & 2) return;
         if (!row_ok && !p.tma_store) return;
         const int n = t.n0 + c * 32;
         const int nvalid = p.N - n;
@@ -598,12 +683,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           default: break;
         }
         if (p.tma_store) {
-          uint8_t* buf = my_stage + (two_out ? 0 : (stg_n & 1) * STG_BUF_BYTES);
+          uint8_t* buf = my_stage + ((two_out || STG_BUFS == 1) ? 0 : (stg_n & 1) * STG_BUF_BYTES);
           stage_write(buf, c & 1, v);
           if ((c & 1) == 1 || c == nchunks - 1) {
             fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) {
+            if (lane == 0 && !(p.dbg & 1)) {
               const int col = t.n0 + (c >> 1) * 64;
               const int row = t.m0 + q * 32;
               tma_store_3d(&tmC, buf, col, row, t.b);
@@ -629,8 +714,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         uint32_t r[32];
         store_gate(c);
         __syncwarp();
-        tmem_ld32(t_addr + c * 32, r);
-        tmem_ld_wait();
+        if (!(p.dbg & 4)) {
+          tmem_ld32(t_addr + c * 32, r);
+          tmem_ld_wait();
+        }
         chunk_body(c, r);
       }
       if (LM) {
@@ -677,14 +764,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 // ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
-template <int BN, int A_MN, int B_MN, int LM = 0, int EPI_T = -1, int CG = 1>
+static int g_gemm_dbg = 0;
+// -1: per epilogue, as measured at 262 144 rows on a B200 -- prefetching the next tile's epilogue
+// operands helps the residual and dSiLU GEMMs (0.107 -> 0.099 ms, 0.193 -> 0.177 ms) and hurts the
+// RMSNorm-backward GEMM, whose K = 512 operand stream already fills the L2 path (0.191 -> 0.202 ms);
+// prefetching A helps only the streaming layout (0.206 -> 0.183 ms), which the resident layout beats.
+static int g_gemm_l2pf = -1;
+
+template <int BN, int A_MN, int B_MN, int LM = 0, int EPI_T = -1, int CG = 1, int BRES = 0>
 static int launch_gemm(const CcbGemmArgs* a, cudaStream_t stream) {
-  using Cfg = GemmCfg<BN, CG>;
+  using Cfg = GemmCfg<BN, CG, BRES>;
   static bool attr_set[16] = {false};
   static int max_pairs[16] = {0};
   int dev = 0;
   cudaGetDevice(&dev);
-  auto kern = gemm_kernel<BN, A_MN, B_MN, LM, EPI_T, CG>;
+  auto kern = gemm_kernel<BN, A_MN, B_MN, LM, EPI_T, CG, BRES>;
   if (!attr_set[dev & 15]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg::SMEM_BYTES);
@@ -775,6 +869,9 @@ static int launch_gemm(const CcbGemmArgs* a, cudaStream_t stream) {
   p.rowss = a->rowss; p.ss_out = a->ss_out;
   p.alpha = a->alpha; p.beta = a->beta; p.inv_dim = a->inv_dim; p.eps = a->eps;
   p.status = ccb_status_ptr();
+  p.dbg = g_gemm_dbg;
+  p.l2pf = g_gemm_l2pf >= 0 ? g_gemm_l2pf
+                            : ((a->epi == CCB_EPI_RESID_SS || a->epi == CCB_EPI_DSILU) ? 2 : 0);
   p.pair = 0;
   if (p.epi == CCB_EPI_RMSBWD && p.tiles_n != 1) {
     // the row reduction needs the whole row in tensor memory: both accumulators as one tile
@@ -813,6 +910,12 @@ static int launch_gemm(const CcbGemmArgs* a, cudaStream_t stream) {
     return 0;
   }
   int grid = (int)(total < ccb_num_sms() ? total : ccb_num_sms());
+  if (BRES) {
+    // the resident tile is loaded for the CTA's first N coordinate: every tile it walks must share it
+    if (p.kblocks > BRES_KBLOCKS || p.splits != 1 || p.batch != 1 || p.pair || (grid % p.tiles_n) != 0 ||
+        p.epi == CCB_EPI_ROWSCALE_SILU || p.f8)
+      return set_error("ccb_gemm: shape not eligible for the resident-B layout (dispatch error)");
+  }
   kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, tmC, tmC2, p);
   count_launch();
   cudaError_t e = cudaGetLastError();
@@ -826,6 +929,26 @@ static inline int64_t b_fp8_of(const CcbGemmArgs* a) { return a->b_fp8; }
 
 // 1: every GEMM runs one CTA per tile; 2: the K-major-A bf16 GEMMs with at least one full 256-row
 // pair tile run on CTA pairs (cta_group::2).
+// Stage-isolation switches of GemmKArgs::dbg (0 = normal operation).  For timing experiments only.
+extern "C" int ccb_gemm_debug(int bits) {
+  const int old = ccb::g_gemm_dbg;
+  ccb::g_gemm_dbg = bits;
+  return old;
+}
+// L2 prefetch switches (bit 1: A tiles two tiles ahead, bit 2: the next tile's epilogue operands;
+// -1: the per-epilogue default).
+extern "C" int ccb_gemm_l2_prefetch(int bits) {
+  const int old = ccb::g_gemm_l2pf;
+  if (bits >= -1 && bits <= 3) ccb::g_gemm_l2pf = bits;
+  return old;
+}
+// 1: K <= 256 single-output GEMMs keep their weight tile resident in shared memory (see GemmCfg).
+static int g_gemm_bres = 1;
+extern "C" int ccb_gemm_resident_b(int on) {
+  const int old = g_gemm_bres;
+  if (on == 0 || on == 1) g_gemm_bres = on;
+  return old;
+}
 static int g_gemm_cta_group = 1;
 extern "C" int ccb_gemm_cta_group(int cg) {
   const int old = g_gemm_cta_group;
@@ -876,6 +999,29 @@ extern "C" int ccb_gemm(const CcbGemmArgs* a, void* stream_) {
         case CCB_EPI_DSILU: return launch_gemm<256, 0, 1, 0, CCB_EPI_DSILU, 2>(a, stream);
         case CCB_EPI_RMSBWD: return launch_gemm<256, 0, 1, 0, CCB_EPI_RMSBWD, 2>(a, stream);
         default: return launch_gemm<256, 0, 1, 0, -1, 2>(a, stream);
+      }
+    }
+    {
+      const int sms = ccb_num_sms();
+      const long long tiles_n = (a->N + 255) / 256, tiles_m = (a->M + 127) / 128;
+      const long long grid = tiles_m * tiles_n < sms ? tiles_m * tiles_n : sms;
+      const bool bres_ok = g_gemm_bres && !a->a_fp8 && a->a_mn == 0 && a->K <= 64 * BRES_KBLOCKS &&
+                           a->batch == 1 && a->splits <= 1 && a->epi != CCB_EPI_ROWSCALE_SILU &&
+                           !(a->epi == CCB_EPI_RMSBWD && a->N > 256) && tiles_m >= 2 * sms / tiles_n &&
+                           grid % tiles_n == 0;
+      if (bres_ok && key == 0) {
+        switch ((int)a->epi) {
+          case CCB_EPI_ROWSCALE: return launch_gemm<256, 0, 0, 0, CCB_EPI_ROWSCALE, 1, 1>(a, stream);
+          case CCB_EPI_RESID_SS: return launch_gemm<256, 0, 0, 0, CCB_EPI_RESID_SS, 1, 1>(a, stream);
+          default: return launch_gemm<256, 0, 0, 0, -1, 1, 1>(a, stream);
+        }
+      }
+      if (bres_ok && key == 1) {
+        switch ((int)a->epi) {
+          case CCB_EPI_DSILU: return launch_gemm<256, 0, 1, 0, CCB_EPI_DSILU, 1, 1>(a, stream);
+          case CCB_EPI_RMSBWD: return launch_gemm<256, 0, 1, 0, CCB_EPI_RMSBWD, 1, 1>(a, stream);
+          default: return launch_gemm<256, 0, 1, 0, -1, 1, 1>(a, stream);
+        }
       }
     }
     if (key == 0) {

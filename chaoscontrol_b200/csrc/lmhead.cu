@@ -84,11 +84,15 @@ struct LmHeadArgs {
   const __nv_bfloat16* W;   // [V, 256] folded head weight (TRAIN1: target rows are gathered)
   float* dWpart;            // [row_chunks, V, 256] out (DW)
   int* status;
+  // stage-isolation switches for bottleneck analysis (results are then wrong by design):
+  // 1 = the gradient-sweep epilogue skips exp2 / pack / the shared-memory store of the g tile,
+  // 2 = the second MMA (dX or dW accumulation) is not issued, 4 = the logits MMA is not issued
+  int dbg;
 };
 
 struct LhBars {
   uint64_t res_full, res_empty;
-  uint64_t stg_full[2], stg_empty[2];
+  uint64_t stg_full[3], stg_empty[3];
   uint64_t d1_full[2], d1_empty[2];
   uint64_t g_full[2], g_empty[2];
   uint64_t d2_full, d2_empty;
@@ -104,7 +108,15 @@ __device__ __forceinline__ float ex2f(float x) {
   return y;
 }
 
-template <int MODE, int PARTS>
+// DEEP = 1 (one-sweep training only): the unit's X tile is the logits MMA's A operand from tensor
+// memory instead of shared memory, the 64 KiB it occupied become a THIRD W' stage, and one logits
+// buffer (handed back as soon as the epilogue holds it in registers) makes room for X in tensor
+// memory.  With two stages a W' tile is pinned from its logits MMA until the dX MMA of the same tile
+// retires, about one and a half tile periods, which leaves the next load half a period to cross the
+// L2 -> SM fabric: measured with the MMAs and the epilogue switched off, the bare load-and-handshake
+// skeleton of the two training kernels takes 3.9 of their 8.1 ms, and the stages add up instead
+// of overlapping.
+template <int MODE, int PARTS, int DEEP>
 __global__ void __launch_bounds__(lh_threads(PARTS), 1)
 lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
               const LmHeadArgs p) {
@@ -121,12 +133,14 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
   if (threadIdx.x == 0) {
     mbar_init(&bars->res_full, 1);
     mbar_init(&bars->res_empty, 1);
+    mbar_init(&bars->stg_full[2], 1);
+    mbar_init(&bars->stg_empty[2], 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->stg_full[i], 1);
       mbar_init(&bars->stg_empty[i], 1);
       mbar_init(&bars->d1_full[i], 1);
       mbar_init(&bars->d1_empty[i], 4 * PARTS);
-      mbar_init(&bars->g_full[i], MODE == MODE_DW ? 2 * PARTS : 8);
+      mbar_init(&bars->g_full[i], (MODE == MODE_DW && DEEP == 0) ? 2 * PARTS : 8);
       mbar_init(&bars->g_empty[i], 1);
     }
     mbar_init(&bars->d2_full, 1);
@@ -161,9 +175,21 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
   // The same was tried for one-sweep training (X in [128,256), ONE logits buffer released as soon
   // as the epilogue holds it in registers, dX in [256,512)): 7.95 -> 8.10 ms, i.e. no gain once
   // the second MMA shares the pipe, so training keeps A in shared memory and two logits buffers.
-  constexpr bool TA = (MODE == MODE_LSE);
-  constexpr bool ONEBUF = false;
-  constexpr uint32_t X_COL = 256u;
+  static_assert(DEEP == 0 || MODE == MODE_TRAIN1 || MODE == MODE_DW,
+                "the deep-ring variant exists for one-sweep training and for the dW kernel");
+  // DEEP dW kernel: the logits tile is computed TRANSPOSED (lanes = vocabulary rows of the unit's W'
+  // tile, which is the A operand and therefore can live in tensor memory; columns = token rows of the
+  // streamed X tile), so that the dW kernel gets the same three-stage ring as the dX kernel.
+  constexpr bool DWT = (MODE == MODE_DW) && (DEEP != 0);
+  constexpr bool G_COLMAJ = (MODE == MODE_DW) && (DEEP == 0);   // g tile consumed MN-major (A = g^T)
+  constexpr bool TA = (MODE == MODE_LSE) || (DEEP != 0);
+  constexpr bool ONEBUF = (DEEP != 0);
+  constexpr uint32_t X_COL = (DEEP != 0) ? 128u : 256u;   // DEEP: [0,128) logits, [128,256) A rows, [256,512) acc 2
+  constexpr int NSTG = TA ? 3 : 2;     // with A in tensor memory the resident tile's 64 KiB are a third stage
+  // stage s of the streamed-tile ring; the third stage lives where the resident tile would
+  auto stage_ptr = [&](int st) -> uint8_t* {
+    return smem + (st < 2 ? LH_OFF_STG + st * LH_TILE : LH_OFF_RES);
+  };
   const int n_sweeps = (MODE == MODE_TRAIN && !p.skip_lse) ? 2 : 1;
 
   if (warp == 0) {
@@ -184,24 +210,25 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
           inner0 = 0;
           inner1 = p.n_vtiles;
         }
-        if (!mbar_wait(&bars->res_empty, res_phase ^ 1u, abort_flag, p.status)) { ok = false; break; }
-        mbar_arrive_expect_tx(&bars->res_full, LH_TILE);
         const CUtensorMap* tmRes = (MODE == MODE_DW) ? &tmW : &tmX;
         const CUtensorMap* tmStg = (MODE == MODE_DW) ? &tmX : &tmW;
+        if (!TA) {
+          if (!mbar_wait(&bars->res_empty, res_phase ^ 1u, abort_flag, p.status)) { ok = false; break; }
+          mbar_arrive_expect_tx(&bars->res_full, LH_TILE);
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
-          tma_load_3d(smem + LH_OFF_RES + c * LH_CHUNK, tmRes, &bars->res_full, c * 64, res_row, 0);
-        res_phase ^= 1u;
+          for (int c = 0; c < 4; ++c)
+            tma_load_3d(smem + LH_OFF_RES + c * LH_CHUNK, tmRes, &bars->res_full, c * 64, res_row, 0);
+          res_phase ^= 1u;
+        }
         for (int sw = 0; sw < n_sweeps && ok; ++sw) {
           for (int it = inner0; it < inner1; ++it, ++n_stg) {
-            const int s = n_stg & 1;
-            const uint32_t ph = (n_stg >> 1) & 1u;
+            const int s = (int)(n_stg % NSTG);
+            const uint32_t ph = (n_stg / NSTG) & 1u;
             if (!mbar_wait(&bars->stg_empty[s], ph ^ 1u, abort_flag, p.status)) { ok = false; break; }
             mbar_arrive_expect_tx(&bars->stg_full[s], LH_TILE);
 #pragma unroll
             for (int c = 0; c < 4; ++c)
-              tma_load_3d(smem + LH_OFF_STG + s * LH_TILE + c * LH_CHUNK, tmStg, &bars->stg_full[s],
-                          c * 64, it * 128, 0);
+              tma_load_3d(stage_ptr(s) + c * LH_CHUNK, tmStg, &bars->stg_full[s], c * 64, it * 128, 0);
           }
         }
       }
@@ -214,8 +241,8 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
     // =========================== MMA issuer ==================================
     if (lane == 0) {
       constexpr uint32_t idesc1 = make_idesc_bf16(128, 128, 0, 0);
-      constexpr uint32_t idesc2 = (MODE == MODE_DW) ? make_idesc_bf16(128, 256, 1, 1)
-                                                    : make_idesc_bf16(128, 256, 0, 1);
+      constexpr uint32_t idesc2 = G_COLMAJ ? make_idesc_bf16(128, 256, 1, 1)
+                                           : make_idesc_bf16(128, 256, 0, 1);
       const uint32_t res_base = smem_u32(smem + LH_OFF_RES);
       const uint32_t g_base = smem_u32(smem + LH_OFF_G);
       const uint32_t d2_tmem = tmem_base + 256;
@@ -224,7 +251,7 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
 
       // second MMA for the tile that used stage `s`; `first` = first of its unit
       auto issue_mma2 = [&](int s, bool first) -> bool {
-        const uint32_t stg_base = smem_u32(smem + LH_OFF_STG + s * LH_TILE);
+        const uint32_t stg_base = smem_u32(stage_ptr(s));
         if (first) {
           if (!mbar_wait(&bars->d2_empty, (n_d2 & 1u) ^ 1u, abort_flag, p.status)) return false;
           tc_fence_after_sync();
@@ -237,7 +264,7 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             uint64_t adesc, bdesc;
-            if (MODE == MODE_DW) {
+            if (G_COLMAJ) {
               const int kk = h * 4 + k;   // 16 rows of r per step
               adesc = make_smem_desc(g_base + kk * 2048, LH_CHUNK, 1024);
               bdesc = make_smem_desc(stg_base + kk * 2048, LH_CHUNK, 1024);
@@ -245,7 +272,7 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
               adesc = make_smem_desc(g_base + h * LH_CHUNK + k * 32, 16, 1024);
               bdesc = make_smem_desc(stg_base + h * 8192 + k * 2048, LH_CHUNK, 1024);
             }
-            umma_bf16(d2_tmem, adesc, bdesc, idesc2, (first && h == 0 && k == 0) ? 0u : 1u);
+            if (!(p.dbg & 2)) umma_bf16(d2_tmem, adesc, bdesc, idesc2, (first && h == 0 && k == 0) ? 0u : 1u);
           }
           umma_commit(&bars->g_empty[h]);
         }
@@ -261,7 +288,9 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
           inner0 = ch * p.mtiles_per_chunk;
           inner1 = min(p.n_mtiles, inner0 + p.mtiles_per_chunk);
         }
-        if (!mbar_wait(&bars->res_full, res_phase, abort_flag, p.status)) { ok = false; break; }
+        if (!TA) {
+          if (!mbar_wait(&bars->res_full, res_phase, abort_flag, p.status)) { ok = false; break; }
+        }
         if (TA) {
           if (!mbar_wait(&bars->xt_full, res_phase, abort_flag, p.status)) { ok = false; break; }
         }
@@ -272,8 +301,8 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
           int prev_stage = -1;
           bool prev_first = true;
           for (int it = inner0; it < inner1; ++it) {
-            const int s = n_stg & 1;
-            const uint32_t sph = (n_stg >> 1) & 1u;
+            const int s = (int)(n_stg % NSTG);
+            const uint32_t sph = (n_stg / NSTG) & 1u;
             ++n_stg;
             const int b = ONEBUF ? 0 : (n_d1 & 1);
             const uint32_t dph = ONEBUF ? (n_d1 & 1u) : ((n_d1 >> 1) & 1u);
@@ -281,14 +310,15 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
             if (!mbar_wait(&bars->stg_full[s], sph, abort_flag, p.status)) { ok = false; break; }
             if (!mbar_wait(&bars->d1_empty[b], dph ^ 1u, abort_flag, p.status)) { ok = false; break; }
             tc_fence_after_sync();
-            const uint32_t stg_base = smem_u32(smem + LH_OFF_STG + s * LH_TILE);
-            const uint32_t xa = (MODE == MODE_DW) ? stg_base : res_base;   // X tile
-            const uint32_t wb = (MODE == MODE_DW) ? res_base : stg_base;   // W' tile
+            const uint32_t stg_base = smem_u32(stage_ptr(s));
+            const uint32_t xa = (MODE == MODE_DW) ? stg_base : res_base;   // A operand when it is in shared memory
+            const uint32_t wb = G_COLMAJ ? res_base : stg_base;            // B operand: W' tile, or X for transposed dW
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
 #pragma unroll
               for (int k = 0; k < 4; ++k) {
                 const uint64_t bdesc = make_smem_desc(wb + c * LH_CHUNK + k * 32, 16, 1024);
+                if (p.dbg & 4) continue;
                 if (TA) {
                   // K step (c, k) = bf16 columns [64c + 16k, +16) of X = 8 packed 32-bit columns
                   umma_bf16_ta(tmem_base + b * 128, tmem_base + X_COL + (uint32_t)(c * 4 + k) * 8u, bdesc,
@@ -317,7 +347,7 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
           }
         }
         if (ok) {
-          umma_commit(&bars->res_empty);
+          if (!TA) umma_commit(&bars->res_empty);
           if (TA) umma_commit(&bars->xt_empty);   // every MMA that read the X columns has completed
         }
       }
@@ -400,13 +430,17 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         if (part == 0) {
           if (!wait_all(&bars->xt_empty, (n_xt & 1u) ^ 1u)) { ok = false; break; }
           tc_fence_after_sync();
-          const uint4* xrow4 = reinterpret_cast<const uint4*>(p.X + (long long)(row_ok ? r : 0) * LH_D);
+          // the A rows of the unit: X rows, or the unit's W' rows for the transposed dW kernel
+          const bool a_ok = DWT ? (v_unit0 + row_in_tile < p.V) : row_ok;
+          const uint4* xrow4 = DWT
+              ? reinterpret_cast<const uint4*>(p.W + (long long)(a_ok ? v_unit0 + row_in_tile : 0) * LH_D)
+              : reinterpret_cast<const uint4*>(p.X + (long long)(row_ok ? r : 0) * LH_D);
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             uint32_t xv[32];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-              const uint4 v4 = row_ok ? __ldg(xrow4 + c * 8 + j) : make_uint4(0u, 0u, 0u, 0u);
+              const uint4 v4 = a_ok ? __ldg(xrow4 + c * 8 + j) : make_uint4(0u, 0u, 0u, 0u);
               xv[j * 4] = v4.x; xv[j * 4 + 1] = v4.y; xv[j * 4 + 2] = v4.z; xv[j * 4 + 3] = v4.w;
             }
             __syncwarp();
@@ -420,6 +454,123 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
         ++n_xt;
       }
 
+      if (DWT) {
+        // ---- transposed dW sweep: lane = vocabulary row v_unit0 + row_in_tile, columns = the 128
+        // token rows of m-tile `it`.  g^T[v, r] = sign * 2^(acc * |c1[r]| - c2[r]) with
+        // c1 = +-rs * log2e (the sign is that of the row's gradient scale) and
+        // c2 = lse * log2e - log2 |gs|, so the scale rides in the exponent and a column needs two
+        // constants.  They sit in shared memory, double-buffered by tile parity: the warps of the
+        // last part write tile it's pair before the rendezvous at the top of iteration `it`, and a
+        // buffer is next written two rendezvous later, after every reader has left it.
+        // The one-hot term: lane l also holds the target and the scale of column col0 + l; when the
+        // target's vocabulary row lies in this warp's quadrant it subtracts gs from that element of
+        // the tile it has just written (a read-modify-write of one bf16 in shared memory).
+        float2* cst = reinterpret_cast<float2*>(smem + LH_OFF_X);       // [2][128]
+        const bool writer = (part == PARTS - 1);
+        // Raw per-row inputs are REQUESTED one tile ahead and only turned into constants at the top
+        // of the next iteration, so no global-load latency sits on the path between the two MMAs.
+        struct RawRow { float ss, lse, w; int tg; };
+        auto fetch_raw = [&](int rr) -> RawRow {
+          RawRow x;
+          if (rr < p.R) {
+            x.ss = p.rowss ? __ldg(p.rowss + rr) : 0.f;
+            x.lse = __ldg(p.lse + rr);
+            x.w = p.rowweight ? __ldg(p.rowweight + rr) : 1.f;
+            x.tg = (int)__ldg(p.targets + rr);
+          } else {
+            x.ss = 0.f; x.lse = INFINITY; x.w = 0.f; x.tg = -1;      // row past the end: g == 0
+          }
+          return x;
+        };
+        auto scale_of = [&](const RawRow& x, float& rsv) -> float {
+          rsv = p.rowss ? rsqrtf(x.ss * p.inv_dim + p.eps) : 1.f;
+          return p.gscale * x.w * rsv;
+        };
+        RawRow wraw = {0.f, INFINITY, 0.f, -1}, graw[NG];
+        if (writer) wraw = fetch_raw(inner0 * LH_ROWS + row_in_tile);
+#pragma unroll
+        for (int g = 0; g < NG; ++g) graw[g] = fetch_raw(inner0 * LH_ROWS + (g * PARTS + part) * 32 + lane);
+        float col_gs[NG];
+        int col_tg[NG];
+        for (int it = inner0; it < inner1 && ok; ++it) {
+          ++n_d1;
+          const uint32_t dph = (n_d1 - 1) & 1u;            // one logits buffer
+          const uint32_t gph = n_g & 1u;
+          ++n_g;
+          const int buf = (it - inner0) & 1;
+          if (writer) {
+            float rsv;
+            const float gsv = scale_of(wraw, rsv);
+            // gs == 0 (or a row past the end): c2 = +inf, so the exponential is exactly 0
+            cst[buf * 128 + row_in_tile] =
+                make_float2(copysignf(rsv * LOG2E, gsv), wraw.lse * LOG2E - __log2f(fabsf(gsv)));
+          }
+#pragma unroll
+          for (int g = 0; g < NG; ++g) {
+            float rsv;
+            col_gs[g] = scale_of(graw[g], rsv);
+            col_tg[g] = graw[g].tg;
+          }
+          if (!epi_sync()) { ok = false; break; }
+          if (it + 1 < inner1) {
+            if (writer) wraw = fetch_raw((it + 1) * LH_ROWS + row_in_tile);
+#pragma unroll
+            for (int g = 0; g < NG; ++g)
+              graw[g] = fetch_raw((it + 1) * LH_ROWS + (g * PARTS + part) * 32 + lane);
+          }
+          if (!wait_all(&bars->d1_full[0], dph)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t t_addr = tmem_base + lane_addr;
+          uint32_t ah[NG][32];
+          __syncwarp();
+#pragma unroll
+          for (int g = 0; g < NG; ++g) tmem_ld32(t_addr + (g * PARTS + part) * 32, ah[g]);
+          tmem_ld_wait();
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars->d1_empty[0]);
+#pragma unroll
+          for (int g = 0; g < NG; ++g) {
+            const int grp = g * PARTS + part;      // 32-column group: token rows 32 grp .. 32 grp + 31
+            const int h = grp >> 1;
+            const uint32_t (&a)[32] = ah[g];
+            uint32_t packed[16];
+            if (!(p.dbg & 1)) {
+              const float4* c4 = reinterpret_cast<const float4*>(cst + buf * 128 + grp * 32);
+#pragma unroll
+              for (int i = 0; i < 32; i += 2) {
+                const float4 k = c4[i >> 1];       // (c1, c2) of columns i and i + 1: one broadcast load
+                const float p0 = ex2f(fmaf(__uint_as_float(a[i]), fabsf(k.x), -k.y));
+                const float p1 = ex2f(fmaf(__uint_as_float(a[i + 1]), fabsf(k.z), -k.w));
+                packed[i >> 1] = pack_bf16x2(copysignf(p0, k.x), copysignf(p1, k.z));
+              }
+            }
+            if (!wait_all(&bars->g_empty[h], gph ^ 1u)) { ok = false; break; }
+            uint8_t* grow = smem + LH_OFF_G + h * LH_CHUNK + row_in_tile * 128;
+            if (!(p.dbg & 1)) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const int slot = ((grp & 1) * 4 + j) ^ (row_in_tile & 7);
+                *reinterpret_cast<uint4*>(grow + slot * 16) =
+                    make_uint4(packed[j * 4], packed[j * 4 + 1], packed[j * 4 + 2], packed[j * 4 + 3]);
+              }
+              __syncwarp();
+              // one-hot: column grp * 32 + lane, vocabulary row col_tg - v_unit0 (if it is one of mine)
+              const int tv = col_tg[g] - v_unit0;
+              if (tv >= q * 32 && tv < q * 32 + 32) {
+                const int colc = (grp & 1) * 32 + lane;                 // column inside the 64-wide chunk
+                uint8_t* cell = smem + LH_OFF_G + h * LH_CHUNK + tv * 128 + (((colc >> 3) ^ (tv & 7)) * 16) +
+                                (colc & 7) * 2;
+                __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(cell);
+                *e = __float2bfloat16(__bfloat162float(*e) - col_gs[g]);
+              }
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->g_full[h]);
+          }
+        }
+      } else
       for (int sw = 0; sw < n_sweeps && ok; ++sw) {
         const bool second = (MODE == MODE_DW) || (IS_TRAIN && sw == n_sweeps - 1);
         float run_m = -INFINITY, run_s = 0.f, run_e = 0.f, tacc = 0.f, zt = 0.f;
@@ -513,6 +664,14 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
               const uint32_t (&a)[32] = ah[g];
               const int tl = tgt - (v0 + col0);
               uint32_t packed[16];
+              if (p.dbg & 1) {
+                if (MODE != MODE_DW) {
+                  if (!wait_all(&bars->g_empty[h], gph ^ 1u)) { ok = false; break; }
+                  __syncwarp();
+                  if (lane == 0) mbar_arrive(&bars->g_full[h]);
+                }
+                continue;
+              }
 #pragma unroll
               for (int i = 0; i < 32; i += 2) {
                 float z0 = fmaf(__uint_as_float(a[i]), c1, -c2);
@@ -725,13 +884,17 @@ lmhead_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ C
 // at 262 144 rows: the scoring sweep gains from sixteen warps (1.81 -> 1.77 ms), the training kernels
 // lose (7.76 -> 8.11 ms for the one-sweep kernel plus the dW kernel).
 static int g_lh_parts = 0;
+static int g_lh_dbg = 0;
+// 1: one-sweep training and the dW kernel run their three-stage variants (7.94 -> 6.66 ms for the pair
+// at 262 144 rows on a B200); 0: two stages with the resident tile in shared memory
+static int g_lh_deep = 1;
 
-template <int MODE, int PARTS>
+template <int MODE, int PARTS, int DEEP = 0>
 static int launch_lmhead_p(const void* X, const void* W, LmHeadArgs& a, cudaStream_t stream) {
   static bool attr_set[16] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
-  auto kern = lmhead_kernel<MODE, PARTS>;
+  auto kern = lmhead_kernel<MODE, PARTS, DEEP>;
   if (!attr_set[dev & 15]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, LH_SMEM);
     if (e != cudaSuccess) return set_error("cudaFuncSetAttribute(lmhead): %s", cudaGetErrorString(e));
@@ -741,6 +904,7 @@ static int launch_lmhead_p(const void* X, const void* W, LmHeadArgs& a, cudaStre
   if (make_tmap_bf16_3d(&tmX, X, LH_D, (uint64_t)a.R, 1, LH_D, 0, 64, 128)) return -1;
   if (make_tmap_bf16_3d(&tmW, W, LH_D, (uint64_t)a.V, 1, LH_D, 0, 64, 128)) return -1;
   a.status = ccb_status_ptr();
+  a.dbg = g_lh_dbg;
   const int units = (MODE == MODE_DW) ? a.n_vtiles * a.row_chunks : a.n_mtiles;
   const int grid = units < ccb_num_sms() ? units : ccb_num_sms();
   kern<<<grid, lh_threads(PARTS), LH_SMEM, stream>>>(tmX, tmW, a);
@@ -752,6 +916,11 @@ static int launch_lmhead_p(const void* X, const void* W, LmHeadArgs& a, cudaStre
 template <int MODE>
 static int launch_lmhead(const void* X, const void* W, LmHeadArgs& a, cudaStream_t stream) {
   const int parts = g_lh_parts ? g_lh_parts : (MODE == MODE_LSE ? 4 : 2);
+  if ((MODE == MODE_TRAIN1 || MODE == MODE_DW) && g_lh_deep) {
+    // the variant is instantiated for these two modes only
+    constexpr int MD = (MODE == MODE_DW) ? MODE_DW : MODE_TRAIN1;
+    return parts == 2 ? launch_lmhead_p<MD, 2, 1>(X, W, a, stream) : launch_lmhead_p<MD, 4, 1>(X, W, a, stream);
+  }
   return parts == 2 ? launch_lmhead_p<MODE, 2>(X, W, a, stream)
                     : launch_lmhead_p<MODE, 4>(X, W, a, stream);
 }
@@ -765,6 +934,21 @@ using namespace ccb;
 extern "C" int ccb_lmhead_epilogue_parts(int parts) {
   const int old = g_lh_parts;
   if (parts == 0 || parts == 2 || parts == 4) g_lh_parts = parts;
+  return old;
+}
+
+// 1: the one-sweep training kernel uses three W' stages with X held in tensor memory; 0: two stages
+// with X in shared memory.  Returns the previous value.
+extern "C" int ccb_lmhead_deep_ring(int on) {
+  const int old = g_lh_deep;
+  if (on == 0 || on == 1) g_lh_deep = on;
+  return old;
+}
+
+// Stage-isolation switches of LmHeadArgs::dbg (0 = normal operation).  For timing experiments only.
+extern "C" int ccb_lmhead_debug(int bits) {
+  const int old = g_lh_dbg;
+  g_lh_dbg = bits;
   return old;
 }
 
@@ -841,5 +1025,7 @@ extern "C" int ccb_lmhead_dw(const void* X, const void* W, const float* rowss, f
   a.gscale = gscale;
   a.lse = const_cast<float*>(lse);
   a.dWpart = dWpart;
+  a.X = (const __nv_bfloat16*)X;
+  a.W = (const __nv_bfloat16*)W;      // the transposed variant copies its W' rows into tensor memory
   return launch_lmhead<MODE_DW>(X, W, a, (cudaStream_t)stream);
 }

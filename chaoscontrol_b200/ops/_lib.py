@@ -68,6 +68,11 @@ _SIGS = {
     "ccb_embed_bwd_slots": ([i64, i64, i64], C.c_int64),
     "ccb_lmhead_epilogue_parts": ([C.c_int], C.c_int),
     "ccb_gemm_cta_group": ([C.c_int], C.c_int),
+    "ccb_gemm_debug": ([C.c_int], C.c_int),
+    "ccb_gemm_resident_b": ([C.c_int], C.c_int),
+    "ccb_gemm_l2_prefetch": ([C.c_int], C.c_int),
+    "ccb_lmhead_debug": ([C.c_int], C.c_int),
+    "ccb_lmhead_deep_ring": ([C.c_int], C.c_int),
     "ccb_splitk_reduce": ([vp, i64, i64, i64, i64, vp, vp, vp, i64, vp, vp, i64, vp], C.c_int),
     "ccb_colsum": ([vp, i64, i64, vp, i64, vp], C.c_int),
     "ccb_fold_colscale": ([vp, vp, vp, i64, i64, vp], C.c_int),

@@ -438,8 +438,9 @@ class Muon(torch.optim.Optimizer):
         return st
 
     def _step_arena(self, arena) -> None:
-        if self._plasticity_multiplier is not None or self._log_a_beta_coupling:
-            # research knobs are per-parameter features: run them on the general path
+        if self._plasticity_multiplier is not None or self._log_a_beta_coupling or len(self.param_groups) != 1:
+            # research knobs are per-parameter features, and the flat path reads ONE set of
+            # hyper-parameters: several param groups run on the general path too
             if not arena.grads_fresh:
                 pass
             arena.materialize_grads()

@@ -901,11 +901,23 @@ def run_condition(config: dict[str, Any], *, data_path: str, sp_model_path: Opti
     from .engine import TrainEngine
     from .utils.arena import ParamArena
     arena = None
-    if TrainEngine.supported(model) or bool(config.get("distributed_muon", False)):
+    if TrainEngine.supported(model):
         arena = ParamArena.install(model)
+    elif bool(config.get("distributed_muon", False)):
+        # sharded Muon without the kernel engine: the arena's shape checks (8-aligned rows / columns,
+        # 128-element matrices) decide; a model they reject keeps the replicated optimizer
+        try:
+            arena = ParamArena.install(model)
+        except ValueError as exc:
+            if rank == 0:
+                print(f"[rank 0/{world_size}] distributed_muon disabled: {exc}", flush=True)
+            config = dict(config, distributed_muon=False)
     if ddp and device.type == "cuda" and arena is not None:
         from .parallel import symm_comm
-        symm_comm.try_enable(arena.flat_grad.numel())      # peer-memory collectives; NCCL remains the fallback
+        if not symm_comm.try_enable(arena.flat_grad.numel()) and rank == 0:
+            # same answer on every rank (the communicator votes): collectives stay on the library
+            print(f"[rank 0/{world_size}] peer-memory collectives unavailable ({symm_comm.last_reason()}); "
+                  "using the torch.distributed backend", flush=True)
 
     train_result: dict[str, Any]
     optimizer = None
@@ -1024,6 +1036,11 @@ def run_condition(config: dict[str, Any], *, data_path: str, sp_model_path: Opti
         print(f"[rank 0/{world_size}] done steps={train_result['steps']} "
               f"tok/s={train_result.get('aggregate_tokens_per_sec', 0.0):.0f} "
               f"loss={train_result['final_loss']:.4f} vram={train_result.get('peak_vram_mb', 0.0):.1f}MB", flush=True)
+    if ddp and dist.is_initialized():
+        # collective teardown of the peer-memory communicator (drain, barrier, unmap the peers,
+        # barrier, free): must precede the process group's destruction and happens on every rank
+        from .parallel import symm_comm
+        symm_comm.disable()
     if ddp and dist.is_initialized() and not keep_process_group:
         _CONTROL.clear()
         dist.destroy_process_group()

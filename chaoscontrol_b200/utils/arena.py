@@ -131,6 +131,12 @@ class ParamArena:
             g.skip = {i for i in range(g.count) if i % 4 == 3}
             muon_groups.append(g)
         for shp, names in sorted(shapes.items(), key=lambda kv: (kv[0][0] * kv[0][1], kv[0])):
+            # a shape group is read as a dense [count, r, c] batch (stride r * c) by Muon and by the
+            # ownership plan, while `place` pads every tensor to 128 elements: the two agree only when
+            # r * c is a multiple of 128; the Newton-Schulz GEMMs want 8-element aligned rows and columns
+            if (shp[0] * shp[1]) % 128 or shp[0] % 8 or shp[1] % 8:
+                raise ValueError(f"ParamArena: matrix shape {shp} ({names[0]}) needs rows and columns in "
+                                 "multiples of 8 and rows * columns in multiples of 128")
             g = ArenaGroup(shape=shp, names=list(names), offset=offset, count=len(names))
             for n in names:
                 place(n)

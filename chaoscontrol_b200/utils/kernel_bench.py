@@ -129,7 +129,30 @@ def main() -> None:
                     help="epilogue width of the fused LM head: 2 = eight warps, 4 = sixteen (0: library default)")
     ap.add_argument("--gemm-cg", type=int, default=0, choices=[0, 1, 2],
                     help="1: one CTA per GEMM tile, 2: CTA pairs (cta_group::2); 0: library default")
+    ap.add_argument("--gemm-debug", type=int, default=0,
+                    help="stage-isolation bits of the GEMM kernel (1 no stores, 2 no epilogue math, 4 no TMEM "
+                         "loads, 8 no MMAs): the output is wrong by design, only the time means something")
+    ap.add_argument("--lmhead-debug", type=int, default=0,
+                    help="stage-isolation bits of the fused LM head (1 no g-tile epilogue, 2 no second MMA, 4 no "
+                         "logits MMA): wrong output by design, only the time means something")
+    ap.add_argument("--lmhead-deep", type=int, default=-1, choices=[-1, 0, 1],
+                    help="one-sweep LM-head training kernel: 1 = three W' stages with X in tensor memory, 0 = two "
+                         "stages with X in shared memory (-1: library default)")
+    ap.add_argument("--gemm-bres", type=int, default=-1, choices=[-1, 0, 1],
+                    help="1: K <= 256 GEMMs keep their weight tile resident in shared memory (-1: library default)")
+    ap.add_argument("--gemm-l2pf", type=int, default=-2, choices=[-2, -1, 0, 1, 2, 3],
+                    help="(-2: leave the library default) GEMM L2 prefetch bits: 1 = A tiles two tiles ahead, 2 = next tile's epilogue operands")
     a = ap.parse_args()
+    if a.gemm_l2pf >= -1:
+        _lib.lib().ccb_gemm_l2_prefetch(a.gemm_l2pf)
+    if a.gemm_bres >= 0:
+        _lib.lib().ccb_gemm_resident_b(a.gemm_bres)
+    if a.lmhead_deep >= 0:
+        _lib.lib().ccb_lmhead_deep_ring(a.lmhead_deep)
+    if a.lmhead_debug:
+        _lib.lib().ccb_lmhead_debug(a.lmhead_debug)
+    if a.gemm_debug:
+        _lib.lib().ccb_gemm_debug(a.gemm_debug)
     if a.gemm_cg:
         _lib.lib().ccb_gemm_cta_group(a.gemm_cg)
     if a.lmhead_parts:
@@ -153,7 +176,7 @@ def main() -> None:
     times.sort()
     ms = times[len(times) // 2]
     pk = peaks()
-    out = {"kernel": a.kernel, "rows": a.rows, "lmhead_parts": a.lmhead_parts or None, "gemm_cg": a.gemm_cg or None,
+    out = {"kernel": a.kernel, "rows": a.rows, "lmhead_parts": a.lmhead_parts or None, "gemm_cg": a.gemm_cg or None, "gemm_debug": a.gemm_debug or None, "gemm_bres": a.gemm_bres if a.gemm_bres >= 0 else None, "gemm_l2pf": a.gemm_l2pf if a.gemm_l2pf >= -1 else None, "lmhead_debug": a.lmhead_debug or None, "lmhead_deep": a.lmhead_deep if a.lmhead_deep >= 0 else None,
            "ms_median": ms, "ms_min": times[0],
            "GBps": nbytes / ms / 1e6, "frac_hbm": nbytes / ms / 1e6 / pk["hbm_gbs"],
            "TFLOPs": flops / ms / 1e9, "frac_bf16_burst": flops / ms / 1e9 / pk["bf16_tflops"],

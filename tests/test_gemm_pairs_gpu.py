@@ -1,6 +1,8 @@
-"""The tcgen05 GEMM on CTA pairs (2-CTA clusters, ``cta_group::2``) vs the fp32 PyTorch statement
-and vs the single-CTA kernel: plain and MN-major B, ragged shapes (a pair tile whose second CTA is
-partly or wholly past the last row, N that leaves half tiles empty), every fused trunk epilogue."""
+"""The two alternative layouts of the tcgen05 GEMM -- CTA pairs (2-CTA clusters, ``cta_group::2``)
+and the resident weight tile (B loaded once per CTA, only A streams) -- vs the fp32 PyTorch statement
+and vs the default kernel: plain and MN-major B, ragged shapes (a pair tile whose second CTA is
+partly or wholly past the last row, N that leaves half tiles empty, a last row tile that is partly
+empty), every fused trunk epilogue."""
 import pytest
 import torch
 
@@ -10,12 +12,27 @@ from chaoscontrol_b200.ops import gemm as G
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture()
-def pairs():
+@pytest.fixture(params=["pairs", "resident"])
+def pairs(request):
     L = _lib.lib()
-    old = L.ccb_gemm_cta_group(2)
-    yield
-    L.ccb_gemm_cta_group(old)
+    if request.param == "pairs":
+        old = L.ccb_gemm_cta_group(2)
+        yield
+        L.ccb_gemm_cta_group(old)
+    else:
+        old = L.ccb_gemm_resident_b(1)
+        yield
+        L.ccb_gemm_resident_b(old)
+
+
+def _default_layout(fn):
+    L = _lib.lib()
+    cg, rb = L.ccb_gemm_cta_group(1), L.ccb_gemm_resident_b(0)
+    try:
+        return fn()
+    finally:
+        L.ccb_gemm_cta_group(cg)
+        L.ccb_gemm_resident_b(rb)
 
 
 def _rand(*shape, scale=1.0):
@@ -30,20 +47,20 @@ def _close(got, ref, rtol=2e-2, atol=2e-2):
 
 
 @pytest.mark.parametrize("M,N,K", [(512, 256, 64), (512, 256, 256), (1000, 768, 256), (640, 512, 320),
-                                   (4096, 1024, 256), (513, 200, 128), (5000, 256, 1024)])
+                                   (4096, 1024, 256), (513, 200, 128), (5000, 256, 1024),
+                                   (40000, 256, 256), (20001, 1024, 192), (19000, 512, 256), (37999, 200, 64)])
 def test_pair_gemm_tn(pairs, M, N, K):
     torch.manual_seed(0)
     a, b = _rand(M, K), _rand(N, K)
     out = G.gemm(a, b)
     _lib.assert_ok()
     _close(out, G.gemm_reference(a, b), atol=0.05 * (K ** 0.5) / 16)
-    _lib.lib().ccb_gemm_cta_group(1)
-    single = G.gemm(a, b)
-    _lib.lib().ccb_gemm_cta_group(2)
+    single = _default_layout(lambda: G.gemm(a, b))
     assert torch.equal(out, single)           # same k order, same accumulators: same bits
 
 
-@pytest.mark.parametrize("M,N,K", [(512, 256, 256), (1024, 304, 128), (4096, 512, 256), (777, 256, 512)])
+@pytest.mark.parametrize("M,N,K", [(512, 256, 256), (1024, 304, 128), (4096, 512, 256), (777, 256, 512),
+                                   (38000, 256, 256), (19001, 512, 128)])
 def test_pair_gemm_b_mn(pairs, M, N, K):
     torch.manual_seed(1)
     a, b = _rand(M, K), _rand(K, N)
@@ -52,7 +69,7 @@ def test_pair_gemm_b_mn(pairs, M, N, K):
     _close(out, G.gemm_reference(a, b, b_mn=True), atol=0.05 * (K ** 0.5) / 16)
 
 
-@pytest.mark.parametrize("M", [640, 4096, 9000])
+@pytest.mark.parametrize("M", [640, 4096, 9000, 40100])
 def test_pair_gemm_epilogues(pairs, M):
     torch.manual_seed(4)
     D, F = 256, 512

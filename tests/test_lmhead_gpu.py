@@ -8,13 +8,18 @@ from chaoscontrol_b200.ops import lm_head as LH
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(params=[4, 2], ids=["epi16warps", "epi8warps"])
+@pytest.fixture(params=[(4, 0), (2, 0), (2, 1), (4, 1)], ids=["epi16warps", "epi8warps", "epi8warps-deep", "epi16warps-deep"])
 def epilogue_parts(request):
-    """Run a test with both widths of the fused head's epilogue (sixteen or eight warps)."""
+    """Run a test with both widths of the fused head's epilogue (sixteen or eight warps) and with
+    both ring layouts of the one-sweep training kernel (two stages with X in shared memory, three
+    stages with X in tensor memory)."""
     L = _lib.lib()
-    old = L.ccb_lmhead_epilogue_parts(request.param)
+    parts, deep = request.param
+    old = L.ccb_lmhead_epilogue_parts(parts)
+    old_deep = L.ccb_lmhead_deep_ring(deep)
     yield request.param
     L.ccb_lmhead_epilogue_parts(old)
+    L.ccb_lmhead_deep_ring(old_deep)
 
 
 def _mk(R, V, seed=0, wscale=0.08):

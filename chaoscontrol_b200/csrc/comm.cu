@@ -28,6 +28,7 @@
 namespace ccb {
 
 constexpr int COMM_MAX_RANKS = 8;
+constexpr int COMM_EPOCH_SLOT = 15;   // counters[15]: epoch of the last completed operation
 constexpr int COMM_THREADS = 512;
 
 struct PeerPtrs {
@@ -59,6 +60,18 @@ __device__ __forceinline__ uint4 ld_relaxed_sys_v4(const void* p) {
                : "memory");
   return v;
 }
+
+// The epoch of a collective, either a host value or "device counter + add": with the counter in
+// device memory nothing in a launch depends on host state, so a whole training step -- exchange
+// included -- can be captured once in a CUDA graph and replayed.  The first kernel of an operation
+// uses add = 1 (a new epoch), its later kernels too (the counter has not moved yet), and the last
+// one stores the new epoch back (`bump` of last_block_signal); a follow-up operation that belongs
+// to the same epoch (parameter publish / gather after a sharded reduce) uses add = 0.
+struct EpochArg {
+  const uint32_t* dev;
+  uint32_t add;
+  __device__ __forceinline__ uint32_t get() const { return dev ? (*dev + add) : add; }
+};
 
 // Bounded wait until *flag >= epoch.  Returns false on timeout.
 __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, uint64_t limit_ns,
@@ -94,13 +107,14 @@ __device__ __forceinline__ bool wait_all_peers(const uint32_t* my_pad, int row, 
 // this rank did not produce.
 __device__ __forceinline__ void last_block_signal(unsigned* counter, const PeerPtrs& pp, int row,
                                                   int rank, int ws, uint32_t epoch, int row2 = -1,
-                                                  bool ok = true) {
+                                                  bool ok = true, uint32_t* bump = nullptr) {
   __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) {
     const unsigned old = atomicAdd(counter, 1u);
     if (old == gridDim.x - 1) {
       *counter = 0;
+      if (bump != nullptr) *bump = epoch;      // the operation's last kernel moves the device epoch
       __threadfence_system();
       if (ok) {
         for (int p = 0; p < ws; ++p) {
@@ -114,11 +128,12 @@ __device__ __forceinline__ void last_block_signal(unsigned* counter, const PeerP
 
 __global__ void __launch_bounds__(COMM_THREADS)
 comm_pack_kernel(const float* __restrict__ grad, long long n, float scale, PeerPtrs pp, int rank,
-                 int ws, uint32_t epoch, unsigned* counter, uint64_t limit_ns, int* status) {
+                 int ws, EpochArg ea, uint32_t* bump, unsigned* counter, uint64_t limit_ns, int* status) {
+  const uint32_t epoch = ea.get();
   __shared__ int sm_ok;
   // peers must have finished with everything I staged in the previous epoch
   if (!wait_all_peers(pp.pad[rank], 3, ws, epoch - 1, limit_ns, status, &sm_ok)) {
-    last_block_signal(counter, pp, 0, rank, ws, epoch, -1, false);   // count the arrival, publish nothing
+    last_block_signal(counter, pp, 0, rank, ws, epoch, -1, false, bump);   // count the arrival, publish nothing
     return;
   }
   __nv_bfloat16* out = pp.buf[rank];
@@ -134,7 +149,7 @@ comm_pack_kernel(const float* __restrict__ grad, long long n, float scale, PeerP
     q.w = pack_bf16x2(b.z * scale, b.w * scale);
     reinterpret_cast<uint4*>(out)[i] = q;
   }
-  last_block_signal(counter, pp, 0, rank, ws, epoch);
+  last_block_signal(counter, pp, 0, rank, ws, epoch, -1, true, bump);
 }
 
 __device__ __forceinline__ void acc_bf16x8(float (&acc)[8], const uint4& q) {
@@ -147,10 +162,11 @@ __device__ __forceinline__ void acc_bf16x8(float (&acc)[8], const uint4& q) {
 
 __global__ void __launch_bounds__(COMM_THREADS)
 comm_oneshot_kernel(float* __restrict__ grad, long long n, PeerPtrs pp, int rank, int ws,
-                    uint32_t epoch, unsigned* counter, uint64_t limit_ns, int* status) {
+                    EpochArg ea, uint32_t* bump, unsigned* counter, uint64_t limit_ns, int* status) {
+  const uint32_t epoch = ea.get();
   __shared__ int sm_ok;
   if (!wait_all_peers(pp.pad[rank], 0, ws, epoch, limit_ns, status, &sm_ok)) {
-    last_block_signal(counter, pp, 1, rank, ws, epoch, 3, false);   // count the arrival, publish nothing
+    last_block_signal(counter, pp, 1, rank, ws, epoch, 3, false, bump);   // count the arrival, publish nothing
     return;
   }
   const long long n8 = n / 8;
@@ -167,16 +183,17 @@ comm_oneshot_kernel(float* __restrict__ grad, long long n, PeerPtrs pp, int rank
     reinterpret_cast<float4*>(grad)[2 * i] = make_float4(acc[0], acc[1], acc[2], acc[3]);
     reinterpret_cast<float4*>(grad)[2 * i + 1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
   }
-  last_block_signal(counter, pp, 1, rank, ws, epoch, 3);
+  last_block_signal(counter, pp, 1, rank, ws, epoch, 3, true, bump);
 }
 
 // two-shot, stage 1: this rank reduces slice `rank` into its fp32 staging buffer
 __global__ void __launch_bounds__(COMM_THREADS)
-comm_reduce_scatter_kernel(long long n, PeerPtrs pp, int rank, int ws, uint32_t epoch,
+comm_reduce_scatter_kernel(long long n, PeerPtrs pp, int rank, int ws, EpochArg ea, uint32_t* bump,
                            unsigned* counter, uint64_t limit_ns, int* status) {
+  const uint32_t epoch = ea.get();
   __shared__ int sm_ok;
   if (!wait_all_peers(pp.pad[rank], 0, ws, epoch, limit_ns, status, &sm_ok)) {
-    last_block_signal(counter, pp, 2, rank, ws, epoch, -1, false);   // count the arrival, publish nothing
+    last_block_signal(counter, pp, 2, rank, ws, epoch, -1, false, bump);   // count the arrival, publish nothing
     return;
   }
   const long long slice8 = (n / 8) / ws;           // host guarantees divisibility
@@ -195,16 +212,17 @@ comm_reduce_scatter_kernel(long long n, PeerPtrs pp, int rank, int ws, uint32_t 
     reinterpret_cast<float4*>(out)[2 * i] = make_float4(acc[0], acc[1], acc[2], acc[3]);
     reinterpret_cast<float4*>(out)[2 * i + 1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
   }
-  last_block_signal(counter, pp, 2, rank, ws, epoch);
+  last_block_signal(counter, pp, 2, rank, ws, epoch, -1, true, bump);
 }
 
 // two-shot, stage 2: gather every rank's reduced slice
 __global__ void __launch_bounds__(COMM_THREADS)
 comm_all_gather_kernel(float* __restrict__ grad, long long n, PeerPtrs pp, int rank, int ws,
-                       uint32_t epoch, unsigned* counter, uint64_t limit_ns, int* status) {
+                       EpochArg ea, uint32_t* bump, unsigned* counter, uint64_t limit_ns, int* status) {
+  const uint32_t epoch = ea.get();
   __shared__ int sm_ok;
   if (!wait_all_peers(pp.pad[rank], 2, ws, epoch, limit_ns, status, &sm_ok)) {
-    last_block_signal(counter, pp, 1, rank, ws, epoch, 3, false);   // count the arrival, publish nothing
+    last_block_signal(counter, pp, 1, rank, ws, epoch, 3, false, bump);   // count the arrival, publish nothing
     return;
   }
   const long long slice4 = (n / 4) / ws;
@@ -216,7 +234,7 @@ comm_all_gather_kernel(float* __restrict__ grad, long long n, PeerPtrs pp, int r
     const uint4 v = ld_relaxed_sys_v4(reinterpret_cast<const uint4*>(pp.buf2[p]) + j);
     reinterpret_cast<uint4*>(grad)[i] = v;
   }
-  last_block_signal(counter, pp, 1, rank, ws, epoch, 3);
+  last_block_signal(counter, pp, 1, rank, ws, epoch, 3, true, bump);
 }
 
 // ---------------------------------------------------------------------------
@@ -237,11 +255,12 @@ comm_all_gather_kernel(float* __restrict__ grad, long long n, PeerPtrs pp, int r
 
 __global__ void __launch_bounds__(COMM_THREADS)
 comm_reduce_ranges_kernel(float* __restrict__ grad, const CommRange* __restrict__ ranges, int nranges,
-                          PeerPtrs pp, int rank, int ws, uint32_t epoch, unsigned* counter,
+                          PeerPtrs pp, int rank, int ws, EpochArg ea, uint32_t* bump, unsigned* counter,
                           uint64_t limit_ns, int* status) {
+  const uint32_t epoch = ea.get();
   __shared__ int sm_ok;
   if (!wait_all_peers(pp.pad[rank], 0, ws, epoch, limit_ns, status, &sm_ok)) {
-    last_block_signal(counter, pp, 1, rank, ws, epoch, -1, false);   // count the arrival, publish nothing
+    last_block_signal(counter, pp, 1, rank, ws, epoch, -1, false, bump);   // count the arrival, publish nothing
     return;
   }
   for (int r = 0; r < nranges; ++r) {
@@ -262,17 +281,18 @@ comm_reduce_ranges_kernel(float* __restrict__ grad, const CommRange* __restrict_
       reinterpret_cast<float4*>(grad)[2 * e + 1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
     }
   }
-  last_block_signal(counter, pp, 1, rank, ws, epoch);
+  last_block_signal(counter, pp, 1, rank, ws, epoch, -1, true, bump);
 }
 
 __global__ void __launch_bounds__(COMM_THREADS)
 comm_publish_params_kernel(const __nv_bfloat16* __restrict__ param, const CommRange* __restrict__ ranges,
-                           int nranges, PeerPtrs pp, int rank, int ws, uint32_t epoch, unsigned* counter,
+                           int nranges, PeerPtrs pp, int rank, int ws, EpochArg ea, uint32_t* bump, unsigned* counter,
                            uint64_t limit_ns, int* status) {
+  const uint32_t epoch = ea.get();
   __shared__ int sm_ok;
   // my staging buffer still holds gradients until every peer has read them
   if (!wait_all_peers(pp.pad[rank], 1, ws, epoch, limit_ns, status, &sm_ok)) {
-    last_block_signal(counter, pp, 2, rank, ws, epoch, -1, false);   // count the arrival, publish nothing
+    last_block_signal(counter, pp, 2, rank, ws, epoch, -1, false, bump);   // count the arrival, publish nothing
     return;
   }
   uint4* out = reinterpret_cast<uint4*>(pp.buf[rank]);
@@ -283,16 +303,17 @@ comm_publish_params_kernel(const __nv_bfloat16* __restrict__ param, const CommRa
          i += (long long)gridDim.x * blockDim.x)
       out[rg.off8 + i] = reinterpret_cast<const uint4*>(param)[rg.off8 + i];
   }
-  last_block_signal(counter, pp, 2, rank, ws, epoch);
+  last_block_signal(counter, pp, 2, rank, ws, epoch, -1, true, bump);
 }
 
 __global__ void __launch_bounds__(COMM_THREADS)
 comm_gather_params_kernel(__nv_bfloat16* __restrict__ param, const CommRange* __restrict__ ranges,
-                          int nranges, PeerPtrs pp, int rank, int ws, uint32_t epoch, unsigned* counter,
+                          int nranges, PeerPtrs pp, int rank, int ws, EpochArg ea, uint32_t* bump, unsigned* counter,
                           uint64_t limit_ns, int* status) {
+  const uint32_t epoch = ea.get();
   __shared__ int sm_ok;
   if (!wait_all_peers(pp.pad[rank], 2, ws, epoch, limit_ns, status, &sm_ok)) {
-    last_block_signal(counter, pp, 3, rank, ws, epoch, -1, false);   // count the arrival, publish nothing
+    last_block_signal(counter, pp, 3, rank, ws, epoch, -1, false, bump);   // count the arrival, publish nothing
     return;
   }
   for (int r = 0; r < nranges; ++r) {
@@ -303,7 +324,7 @@ comm_gather_params_kernel(__nv_bfloat16* __restrict__ param, const CommRange* __
          i += (long long)gridDim.x * blockDim.x)
       reinterpret_cast<uint4*>(param)[rg.off8 + i] = ld_relaxed_sys_v4(src + rg.off8 + i);
   }
-  last_block_signal(counter, pp, 3, rank, ws, epoch);
+  last_block_signal(counter, pp, 3, rank, ws, epoch, -1, true, bump);
 }
 
 // ---------------------------------------------------------------------------
@@ -318,11 +339,12 @@ constexpr int COMM_BUCKET_THREADS = 128;   // 128 x 64 registers: fits beside a 
 
 __global__ void __launch_bounds__(COMM_BUCKET_THREADS)
 comm_pack_ranges_kernel(const float* __restrict__ grad, const CommRange* __restrict__ ranges, int r0,
-                        int r1, float scale, PeerPtrs pp, int rank, int ws, uint32_t epoch,
+                        int r1, float scale, PeerPtrs pp, int rank, int ws, EpochArg ea, uint32_t* bump,
                         unsigned* counter, uint64_t limit_ns, int* status) {
+  const uint32_t epoch = ea.get();
   __shared__ int sm_ok;
   if (!wait_all_peers(pp.pad[rank], 3, ws, epoch - 1, limit_ns, status, &sm_ok)) {
-    last_block_signal(counter, pp, 0, rank, ws, epoch, -1, false);
+    last_block_signal(counter, pp, 0, rank, ws, epoch, -1, false, bump);
     return;
   }
   uint4* out = reinterpret_cast<uint4*>(pp.buf[rank]);
@@ -341,16 +363,17 @@ comm_pack_ranges_kernel(const float* __restrict__ grad, const CommRange* __restr
       out[e] = q;
     }
   }
-  last_block_signal(counter, pp, 0, rank, ws, epoch);
+  last_block_signal(counter, pp, 0, rank, ws, epoch, -1, true, bump);
 }
 
 __global__ void __launch_bounds__(COMM_BUCKET_THREADS)
 comm_oneshot_ranges_kernel(float* __restrict__ grad, const CommRange* __restrict__ ranges, int r0, int r1,
-                           PeerPtrs pp, int rank, int ws, uint32_t epoch, unsigned* counter,
+                           PeerPtrs pp, int rank, int ws, EpochArg ea, uint32_t* bump, unsigned* counter,
                            uint64_t limit_ns, int* status) {
+  const uint32_t epoch = ea.get();
   __shared__ int sm_ok;
   if (!wait_all_peers(pp.pad[rank], 0, ws, epoch, limit_ns, status, &sm_ok)) {
-    last_block_signal(counter, pp, 1, rank, ws, epoch, 3, false);
+    last_block_signal(counter, pp, 1, rank, ws, epoch, 3, false, bump);
     return;
   }
   for (int r = r0; r < r1; ++r) {
@@ -370,7 +393,7 @@ comm_oneshot_ranges_kernel(float* __restrict__ grad, const CommRange* __restrict
       reinterpret_cast<float4*>(grad)[2 * e + 1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
     }
   }
-  last_block_signal(counter, pp, 1, rank, ws, epoch, 3);
+  last_block_signal(counter, pp, 1, rank, ws, epoch, 3, true, bump);
 }
 
 // ---------------------------------------------------------------------------
@@ -381,28 +404,30 @@ comm_oneshot_ranges_kernel(float* __restrict__ grad, const CommRange* __restrict
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(COMM_THREADS)
 comm_bcast_put_kernel(const uint4* __restrict__ src, long long n16, PeerPtrs pp, int rank, int ws,
-                      uint32_t epoch, unsigned* counter, uint64_t limit_ns, int* status) {
+                      EpochArg ea, uint32_t* bump, unsigned* counter, uint64_t limit_ns, int* status) {
+  const uint32_t epoch = ea.get();
   __shared__ int sm_ok;
   if (!wait_all_peers(pp.pad[rank], 3, ws, epoch - 1, limit_ns, status, &sm_ok)) {
-    last_block_signal(counter, pp, 0, rank, ws, epoch, -1, false);
+    last_block_signal(counter, pp, 0, rank, ws, epoch, -1, false, bump);
     return;
   }
   uint4* out = reinterpret_cast<uint4*>(pp.buf[rank]);
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n16;
        i += (long long)gridDim.x * blockDim.x)
     out[i] = src[i];
-  last_block_signal(counter, pp, 0, rank, ws, epoch);
+  last_block_signal(counter, pp, 0, rank, ws, epoch, -1, true, bump);
 }
 
 __global__ void __launch_bounds__(COMM_THREADS)
 comm_bcast_get_kernel(uint4* __restrict__ dst, long long n16, int root, PeerPtrs pp, int rank, int ws,
-                      uint32_t epoch, unsigned* counter, uint64_t limit_ns, int* status) {
+                      EpochArg ea, uint32_t* bump, unsigned* counter, uint64_t limit_ns, int* status) {
+  const uint32_t epoch = ea.get();
   __shared__ int sm_ok;
   if (threadIdx.x == 0)
     sm_ok = wait_flag(pp.pad[rank] + 0 * COMM_MAX_RANKS + root, epoch, limit_ns, status) ? 1 : 0;
   __syncthreads();
   if (!sm_ok) {
-    last_block_signal(counter, pp, 1, rank, ws, epoch, 3, false);
+    last_block_signal(counter, pp, 1, rank, ws, epoch, 3, false, bump);
     return;
   }
   if (rank != root) {
@@ -411,7 +436,7 @@ comm_bcast_get_kernel(uint4* __restrict__ dst, long long n16, int root, PeerPtrs
          i += (long long)gridDim.x * blockDim.x)
       dst[i] = ld_relaxed_sys_v4(src + i);
   }
-  last_block_signal(counter, pp, 1, rank, ws, epoch, 3);
+  last_block_signal(counter, pp, 1, rank, ws, epoch, 3, true, bump);
 }
 
 // ---------------------------------------------------------------------------
@@ -494,13 +519,12 @@ extern "C" int ccb_ipc_close(void* p) {
 }
 
 // bufs / bufs2 / pads: host arrays of `ws` device pointers (peer-mapped; index
-// `rank` is this rank's own allocation).  counters: 16 device uint32, zeroed (one arrival
-// counter per kernel of this file).
+// `rank` is this rank's own allocation).  counters: 16 device uint32, zeroed: one arrival
+// counter per kernel of this file, and in slot 15 the communicator's epoch (see EpochArg).
 // mode 0 = one-shot, 1 = two-shot.  n must be a multiple of 8 * ws.
 extern "C" int ccb_allreduce(float* grad, int64_t n, float scale, void* const* bufs,
                              void* const* bufs2, void* const* pads, int64_t rank, int64_t ws,
-                             int64_t epoch, void* counters, int64_t mode, int64_t timeout_ms,
-                             void* stream) {
+                             void* counters, int64_t mode, int64_t timeout_ms, void* stream) {
   if (ws < 1 || ws > COMM_MAX_RANKS) return set_error("ccb_allreduce: world size %lld unsupported", (long long)ws);
   if (n % (8 * ws) != 0) return set_error("ccb_allreduce: n=%lld must be a multiple of %lld", (long long)n, (long long)(8 * ws));
   PeerPtrs pp;
@@ -511,24 +535,25 @@ extern "C" int ccb_allreduce(float* grad, int64_t n, float scale, void* const* b
   }
   cudaStream_t s = (cudaStream_t)stream;
   unsigned* ctr = (unsigned*)counters;
+  uint32_t* edev = ctr + COMM_EPOCH_SLOT;          // the communicator's epoch lives in device memory
   int* status = ccb_status_ptr();
   const uint64_t limit = (uint64_t)(timeout_ms > 0 ? timeout_ms : 2000) * 1000000ull;
   const int sms = ccb_num_sms();
   long long want = (n / 8 + COMM_THREADS - 1) / COMM_THREADS;
   const int grid = (int)(want < sms ? (want < 1 ? 1 : want) : sms);
   comm_pack_kernel<<<grid, COMM_THREADS, 0, s>>>(grad, n, scale, pp, (int)rank, (int)ws,
-                                                  (uint32_t)epoch, ctr + 0, limit, status);
+                                                  EpochArg{edev, 1u}, nullptr, ctr + 0, limit, status);
   count_launch();
   if (mode == 0) {
     comm_oneshot_kernel<<<grid, COMM_THREADS, 0, s>>>(grad, n, pp, (int)rank, (int)ws,
-                                                       (uint32_t)epoch, ctr + 1, limit, status);
+                                                       EpochArg{edev, 1u}, edev, ctr + 1, limit, status);
     count_launch();
   } else {
     comm_reduce_scatter_kernel<<<grid, COMM_THREADS, 0, s>>>(n, pp, (int)rank, (int)ws,
-                                                              (uint32_t)epoch, ctr + 2, limit, status);
+                                                              EpochArg{edev, 1u}, nullptr, ctr + 2, limit, status);
     count_launch();
     comm_all_gather_kernel<<<grid, COMM_THREADS, 0, s>>>(grad, n, pp, (int)rank, (int)ws,
-                                                          (uint32_t)epoch, ctr + 3, limit, status);
+                                                          EpochArg{edev, 1u}, edev, ctr + 3, limit, status);
     count_launch();
   }
   cudaError_t e = cudaGetLastError();
@@ -549,7 +574,7 @@ static void fill_peers(ccb::PeerPtrs& pp, void* const* bufs, void* const* bufs2,
 // parameter ranges and gather everyone else's into `param` (bf16 flat buffer).
 extern "C" int ccb_sharded_sync(int64_t phase, float* grad, void* param, int64_t n, float scale,
                                 const void* ranges, int64_t nranges, void* const* bufs, void* const* bufs2,
-                                void* const* pads, int64_t rank, int64_t ws, int64_t epoch, void* counters,
+                                void* const* pads, int64_t rank, int64_t ws, void* counters,
                                 int64_t timeout_ms, void* stream) {
   if (ws < 1 || ws > COMM_MAX_RANKS) return set_error("ccb_sharded_sync: world size %lld unsupported", (long long)ws);
   if (n % 8 != 0) return set_error("ccb_sharded_sync: n=%lld must be a multiple of 8", (long long)n);
@@ -557,6 +582,7 @@ extern "C" int ccb_sharded_sync(int64_t phase, float* grad, void* param, int64_t
   fill_peers(pp, bufs, bufs2, pads, ws);
   cudaStream_t s = (cudaStream_t)stream;
   unsigned* ctr = (unsigned*)counters;
+  uint32_t* edev = ctr + COMM_EPOCH_SLOT;          // the communicator's epoch lives in device memory
   int* status = ccb_status_ptr();
   const uint64_t limit = (uint64_t)(timeout_ms > 0 ? timeout_ms : 2000) * 1000000ull;
   const int sms = ccb_num_sms();
@@ -564,19 +590,19 @@ extern "C" int ccb_sharded_sync(int64_t phase, float* grad, void* param, int64_t
   const int grid = (int)(want < sms ? (want < 1 ? 1 : want) : sms);
   const CommRange* rg = reinterpret_cast<const CommRange*>(ranges);
   if (phase == 0) {
-    comm_pack_kernel<<<grid, COMM_THREADS, 0, s>>>(grad, n, scale, pp, (int)rank, (int)ws, (uint32_t)epoch,
+    comm_pack_kernel<<<grid, COMM_THREADS, 0, s>>>(grad, n, scale, pp, (int)rank, (int)ws, EpochArg{edev, 1u}, nullptr,
                                                     ctr + 0, limit, status);
     count_launch();
     comm_reduce_ranges_kernel<<<grid, COMM_THREADS, 0, s>>>(grad, rg, (int)nranges, pp, (int)rank, (int)ws,
-                                                             (uint32_t)epoch, ctr + 4, limit, status);
+                                                             EpochArg{edev, 1u}, edev, ctr + 4, limit, status);
     count_launch();
   } else {
     comm_publish_params_kernel<<<grid, COMM_THREADS, 0, s>>>((const __nv_bfloat16*)param, rg, (int)nranges, pp,
-                                                              (int)rank, (int)ws, (uint32_t)epoch, ctr + 5, limit,
+                                                              (int)rank, (int)ws, EpochArg{edev, 0u}, nullptr, ctr + 5, limit,
                                                               status);
     count_launch();
     comm_gather_params_kernel<<<grid, COMM_THREADS, 0, s>>>((__nv_bfloat16*)param, rg, (int)nranges, pp, (int)rank,
-                                                             (int)ws, (uint32_t)epoch, ctr + 6, limit, status);
+                                                             (int)ws, EpochArg{edev, 0u}, nullptr, ctr + 6, limit, status);
     count_launch();
   }
   cudaError_t e = cudaGetLastError();
@@ -588,7 +614,7 @@ extern "C" int ccb_sharded_sync(int64_t phase, float* grad, void* param, int64_t
 // `stream`, with `blocks` blocks of 128 threads per kernel (0: one block per SM).
 extern "C" int ccb_allreduce_ranges(float* grad, const void* ranges, int64_t r0, int64_t r1, float scale,
                                     void* const* bufs, void* const* bufs2, void* const* pads, int64_t rank,
-                                    int64_t ws, int64_t epoch, void* counters, int64_t blocks,
+                                    int64_t ws, void* counters, int64_t blocks,
                                     int64_t timeout_ms, void* stream) {
   if (ws < 1 || ws > COMM_MAX_RANKS) return set_error("ccb_allreduce_ranges: world size %lld unsupported", (long long)ws);
   if (r1 <= r0) return 0;
@@ -596,15 +622,16 @@ extern "C" int ccb_allreduce_ranges(float* grad, const void* ranges, int64_t r0,
   fill_peers(pp, bufs, bufs2, pads, ws);
   cudaStream_t s = (cudaStream_t)stream;
   unsigned* ctr = (unsigned*)counters;
+  uint32_t* edev = ctr + COMM_EPOCH_SLOT;          // the communicator's epoch lives in device memory
   int* status = ccb_status_ptr();
   const uint64_t limit = (uint64_t)(timeout_ms > 0 ? timeout_ms : 2000) * 1000000ull;
   const int grid = (int)(blocks > 0 ? blocks : ccb_num_sms());
   const CommRange* rg = reinterpret_cast<const CommRange*>(ranges);
   comm_pack_ranges_kernel<<<grid, COMM_BUCKET_THREADS, 0, s>>>(grad, rg, (int)r0, (int)r1, scale, pp, (int)rank,
-                                                               (int)ws, (uint32_t)epoch, ctr + 8, limit, status);
+                                                               (int)ws, EpochArg{edev, 1u}, nullptr, ctr + 8, limit, status);
   count_launch();
   comm_oneshot_ranges_kernel<<<grid, COMM_BUCKET_THREADS, 0, s>>>(grad, rg, (int)r0, (int)r1, pp, (int)rank,
-                                                                  (int)ws, (uint32_t)epoch, ctr + 9, limit, status);
+                                                                  (int)ws, EpochArg{edev, 1u}, edev, ctr + 9, limit, status);
   count_launch();
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : set_error("allreduce_ranges launch: %s", cudaGetErrorString(e));
@@ -613,7 +640,7 @@ extern "C" int ccb_allreduce_ranges(float* grad, const void* ranges, int64_t r0,
 // Broadcast `nbytes` (a multiple of 16, at most the symmetric buffer) from rank `root`'s `data` into every
 // other rank's `data`.
 extern "C" int ccb_comm_bcast(void* data, int64_t nbytes, int64_t root, void* const* bufs, void* const* bufs2,
-                              void* const* pads, int64_t rank, int64_t ws, int64_t epoch, void* counters,
+                              void* const* pads, int64_t rank, int64_t ws, void* counters,
                               int64_t timeout_ms, void* stream) {
   if (ws < 1 || ws > COMM_MAX_RANKS) return set_error("ccb_comm_bcast: world size %lld unsupported", (long long)ws);
   if (nbytes % 16) return set_error("ccb_comm_bcast: nbytes=%lld must be a multiple of 16", (long long)nbytes);
@@ -622,6 +649,7 @@ extern "C" int ccb_comm_bcast(void* data, int64_t nbytes, int64_t root, void* co
   fill_peers(pp, bufs, bufs2, pads, ws);
   cudaStream_t s = (cudaStream_t)stream;
   unsigned* ctr = (unsigned*)counters;
+  uint32_t* edev = ctr + COMM_EPOCH_SLOT;          // the communicator's epoch lives in device memory
   int* status = ccb_status_ptr();
   const uint64_t limit = (uint64_t)(timeout_ms > 0 ? timeout_ms : 2000) * 1000000ull;
   const long long n16 = nbytes / 16;
@@ -630,11 +658,11 @@ extern "C" int ccb_comm_bcast(void* data, int64_t nbytes, int64_t root, void* co
   const int grid = (int)(want < sms ? (want < 1 ? 1 : want) : sms);
   if (rank == root) {
     comm_bcast_put_kernel<<<grid, COMM_THREADS, 0, s>>>((const uint4*)data, n16, pp, (int)rank, (int)ws,
-                                                        (uint32_t)epoch, ctr + 10, limit, status);
+                                                        EpochArg{edev, 1u}, nullptr, ctr + 10, limit, status);
     count_launch();
   }
   comm_bcast_get_kernel<<<grid, COMM_THREADS, 0, s>>>((uint4*)data, n16, (int)root, pp, (int)rank, (int)ws,
-                                                      (uint32_t)epoch, ctr + 11, limit, status);
+                                                      EpochArg{edev, 1u}, edev, ctr + 11, limit, status);
   count_launch();
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : set_error("bcast launch: %s", cudaGetErrorString(e));

@@ -15,6 +15,7 @@
 // Unlike the reference kernels these take an initial state and return the
 // final state, so carried-state evaluation never drops to a per-token loop.
 #include "ptx.cuh"
+#include <cuda_fp16.h>
 #include "ccb_api.h"
 #include "runtime.h"
 
@@ -213,9 +214,26 @@ scan_bwd_kernel(const __nv_bfloat16* __restrict__ P, long long ldp, const float*
 
 // Plain (unfused) diagonal scan kept for API parity with the reference's
 // ssm_scan(decay, update): fp32 decay, bf16 or fp32 update, fp32 states out.
-template <typename UT>
+// Plain recurrence state[t] = decay[t] * state[t-1] + update[t] for the public ssm_scan op, in
+// the operand dtypes the reference op accepts without a cast
+// (kernels/_ssm_scan/__init__.py:104-113): decay / update = bf16/bf16, bf16/fp16, fp16/fp16,
+// fp32/fp32, fp32/bf16, fp32/fp16.  fp32 accumulator; the states are kept in fp32 for backward.
+template <typename T> __device__ __forceinline__ float scan_ld(const T* p, long long i);
+template <> __device__ __forceinline__ float scan_ld<float>(const float* p, long long i) { return p[i]; }
+template <> __device__ __forceinline__ float scan_ld<__nv_bfloat16>(const __nv_bfloat16* p, long long i) {
+  return __bfloat162float(p[i]);
+}
+template <> __device__ __forceinline__ float scan_ld<__half>(const __half* p, long long i) { return __half2float(p[i]); }
+template <typename T> __device__ __forceinline__ void scan_st(T* p, long long i, float v);
+template <> __device__ __forceinline__ void scan_st<float>(float* p, long long i, float v) { p[i] = v; }
+template <> __device__ __forceinline__ void scan_st<__nv_bfloat16>(__nv_bfloat16* p, long long i, float v) {
+  p[i] = __float2bfloat16(v);
+}
+template <> __device__ __forceinline__ void scan_st<__half>(__half* p, long long i, float v) { p[i] = __float2half(v); }
+
+template <typename DT, typename UT>
 __global__ void __launch_bounds__(SCAN_THREADS)
-plain_scan_fwd_kernel(const float* __restrict__ decay, const UT* __restrict__ update,
+plain_scan_fwd_kernel(const DT* __restrict__ decay, const UT* __restrict__ update,
                       const float* __restrict__ h0, float* __restrict__ states, int T, int D) {
   const int b = blockIdx.y;
   const int d = blockIdx.x * SCAN_THREADS + threadIdx.x;
@@ -224,15 +242,17 @@ plain_scan_fwd_kernel(const float* __restrict__ decay, const UT* __restrict__ up
   const long long base = (long long)b * T * D + d;
   for (int t = 0; t < T; ++t) {
     const long long o = base + (long long)t * D;
-    s = decay[o] * s + (float)update[o];
+    s = scan_ld(decay, o) * s + scan_ld(update, o);
     states[o] = s;
   }
 }
 
+// gstates / gupdate in the update dtype, gdecay in the decay dtype.
+template <typename DT, typename UT>
 __global__ void __launch_bounds__(SCAN_THREADS)
-plain_scan_bwd_kernel(const float* __restrict__ decay, const float* __restrict__ states,
-                      const float* __restrict__ h0, const float* __restrict__ gstates,
-                      float* __restrict__ gdecay, float* __restrict__ gupdate,
+plain_scan_bwd_kernel(const DT* __restrict__ decay, const float* __restrict__ states,
+                      const float* __restrict__ h0, const UT* __restrict__ gstates,
+                      DT* __restrict__ gdecay, UT* __restrict__ gupdate,
                       float* __restrict__ gh0, int T, int D) {
   const int b = blockIdx.y;
   const int d = blockIdx.x * SCAN_THREADS + threadIdx.x;
@@ -241,11 +261,11 @@ plain_scan_bwd_kernel(const float* __restrict__ decay, const float* __restrict__
   float carry = 0.f;
   for (int t = T - 1; t >= 0; --t) {
     const long long o = base + (long long)t * D;
-    const float g = gstates[o] + carry;
+    const float g = scan_ld(gstates, o) + carry;
     const float prev = t > 0 ? states[o - D] : (h0 ? h0[(long long)b * D + d] : 0.f);
-    gupdate[o] = g;
-    gdecay[o] = g * prev;
-    carry = g * decay[o];
+    scan_st(gupdate, o, g);
+    scan_st(gdecay, o, g * prev);
+    carry = g * scan_ld(decay, o);
   }
   if (gh0) gh0[(long long)b * D + d] = carry;
 }
@@ -285,29 +305,49 @@ extern "C" int ccb_scan_bwd(const void* P, int64_t ldp, const float* log_a, cons
   return e == cudaSuccess ? 0 : set_error("scan_bwd launch: %s", cudaGetErrorString(e));
 }
 
-extern "C" int ccb_plain_scan_fwd(const float* decay, const void* update, int64_t update_is_bf16,
-                                  const float* h0, float* states, int64_t B, int64_t T, int64_t D,
-                                  void* stream) {
+// dtype codes: 0 = fp32, 1 = bf16, 2 = fp16.  Accepted (decay, update) pairs: (1,1) (1,2) (2,2) (0,0) (0,1) (0,2).
+static inline bool plain_scan_combo_ok(int64_t dd, int64_t ud) {
+  return (dd == 1 && ud == 1) || (dd == 1 && ud == 2) || (dd == 2 && ud == 2) || (dd == 0 && ud >= 0 && ud <= 2);
+}
+#define CCB_SCAN_DISPATCH(dd, ud, CALL)                                                     \
+  do {                                                                                      \
+    if (dd == 0 && ud == 0) { using DT = float; using UT = float; CALL; }                   \
+    else if (dd == 0 && ud == 1) { using DT = float; using UT = __nv_bfloat16; CALL; }      \
+    else if (dd == 0 && ud == 2) { using DT = float; using UT = __half; CALL; }             \
+    else if (dd == 1 && ud == 1) { using DT = __nv_bfloat16; using UT = __nv_bfloat16; CALL; } \
+    else if (dd == 1 && ud == 2) { using DT = __nv_bfloat16; using UT = __half; CALL; }     \
+    else { using DT = __half; using UT = __half; CALL; }                                    \
+  } while (0)
+
+extern "C" int ccb_plain_scan_fwd(const void* decay, int64_t decay_dtype, const void* update,
+                                  int64_t update_dtype, const float* h0, float* states, int64_t B,
+                                  int64_t T, int64_t D, void* stream) {
   if (B <= 0 || T <= 0 || D <= 0) return 0;
+  if (!plain_scan_combo_ok(decay_dtype, update_dtype))
+    return set_error("ccb_plain_scan_fwd: (decay, update) dtype pair (%lld, %lld) is not supported",
+                     (long long)decay_dtype, (long long)update_dtype);
   dim3 grid((unsigned)((D + SCAN_THREADS - 1) / SCAN_THREADS), (unsigned)B);
-  if (update_is_bf16)
-    plain_scan_fwd_kernel<__nv_bfloat16><<<grid, SCAN_THREADS, 0, (cudaStream_t)stream>>>(
-        decay, (const __nv_bfloat16*)update, h0, states, (int)T, (int)D);
-  else
-    plain_scan_fwd_kernel<float><<<grid, SCAN_THREADS, 0, (cudaStream_t)stream>>>(
-        decay, (const float*)update, h0, states, (int)T, (int)D);
+  CCB_SCAN_DISPATCH(decay_dtype, update_dtype,
+                    (plain_scan_fwd_kernel<DT, UT><<<grid, SCAN_THREADS, 0, (cudaStream_t)stream>>>(
+                        (const DT*)decay, (const UT*)update, h0, states, (int)T, (int)D)));
   count_launch();
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : set_error("plain_scan_fwd launch: %s", cudaGetErrorString(e));
 }
 
-extern "C" int ccb_plain_scan_bwd(const float* decay, const float* states, const float* h0,
-                                  const float* gstates, float* gdecay, float* gupdate, float* gh0,
-                                  int64_t B, int64_t T, int64_t D, void* stream) {
+extern "C" int ccb_plain_scan_bwd(const void* decay, int64_t decay_dtype, const float* states,
+                                  const float* h0, const void* gstates, int64_t update_dtype,
+                                  void* gdecay, void* gupdate, float* gh0, int64_t B, int64_t T,
+                                  int64_t D, void* stream) {
   if (B <= 0 || T <= 0 || D <= 0) return 0;
+  if (!plain_scan_combo_ok(decay_dtype, update_dtype))
+    return set_error("ccb_plain_scan_bwd: (decay, update) dtype pair (%lld, %lld) is not supported",
+                     (long long)decay_dtype, (long long)update_dtype);
   dim3 grid((unsigned)((D + SCAN_THREADS - 1) / SCAN_THREADS), (unsigned)B);
-  plain_scan_bwd_kernel<<<grid, SCAN_THREADS, 0, (cudaStream_t)stream>>>(
-      decay, states, h0, gstates, gdecay, gupdate, gh0, (int)T, (int)D);
+  CCB_SCAN_DISPATCH(decay_dtype, update_dtype,
+                    (plain_scan_bwd_kernel<DT, UT><<<grid, SCAN_THREADS, 0, (cudaStream_t)stream>>>(
+                        (const DT*)decay, states, h0, (const UT*)gstates, (DT*)gdecay, (UT*)gupdate, gh0,
+                        (int)T, (int)D)));
   count_launch();
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : set_error("plain_scan_bwd launch: %s", cudaGetErrorString(e));

@@ -101,6 +101,11 @@ def _linear_ce(x, weight, targets, row_weight=None):
     """Returns (weighted sum of per-row CE, per-row CE)."""
     if LH.kernel_supported(x, weight) and _lib.available():
         return _LinearCeFn.apply(x.contiguous(), weight.contiguous(), targets.reshape(-1), row_weight)
+    if x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16:
+        # the kernels' own dtype with a shape they do not take: refuse, like the reference's dispatcher;
+        # other dtypes (fp32 debugging runs) and CPU tensors are outside the kernels' domain
+        raise TypeError(f"fused linear+CE: no kernel takes x {tuple(x.shape)} with weight {tuple(weight.shape)} "
+                        "(model dim a multiple of 8 and at most 512, vocabulary a multiple of 8)")
     logits = F.linear(x, weight).float()
     rows = F.cross_entropy(logits, targets.reshape(-1).long(), reduction="none")
     total = (rows * row_weight.float()).sum() if row_weight is not None else rows.sum()
@@ -158,5 +163,8 @@ def fused_rms_linear_cross_entropy_with_ce(x, norm_weight, linear_weight, target
 def fused_lm_head_forward_with_ce_entropy(x, weight, target, *, tile_size: int = 8192):
     """Forward only: ``(mean loss, lse, per-token CE, per-token entropy)``."""
     x2 = x.reshape(-1, x.shape[-1]).contiguous()
-    rows, lse, ent = LH.lm_head_lse(x2, None, weight.contiguous(), target.reshape(-1), want_entropy=True)
+    # the entropy by-product exists in the single-kernel head (model dim 256) only; other dims take the
+    # PyTorch statement in bounded row chunks, which this forward-only diagnostic asks for explicitly
+    rows, lse, ent = LH.lm_head_lse(x2, None, weight.contiguous(), target.reshape(-1), want_entropy=True,
+                                    allow_materialized=True)
     return rows.mean(), lse, rows, ent

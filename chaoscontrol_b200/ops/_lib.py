@@ -61,8 +61,8 @@ _SIGS = {
     "ccb_scan_fwd": ([vp, i64, vp, vp, vp, vp, vp, i64, i64, i64, vp], C.c_int),
     "ccb_scan_bwd": ([vp, i64, vp, vp, vp, vp, vp, vp, f32, f32, vp, i64, vp, vp, i64, i64, i64, vp],
                      C.c_int),
-    "ccb_plain_scan_fwd": ([vp, vp, i64, vp, vp, i64, i64, i64, vp], C.c_int),
-    "ccb_plain_scan_bwd": ([vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, vp], C.c_int),
+    "ccb_plain_scan_fwd": ([vp, i64, vp, i64, vp, vp, i64, i64, i64, vp], C.c_int),
+    "ccb_plain_scan_bwd": ([vp, i64, vp, vp, vp, i64, vp, vp, vp, i64, i64, i64, vp], C.c_int),
     "ccb_embed_fwd": ([vp, i64, vp, vp, vp, i64, i64, i64, vp], C.c_int),
     "ccb_embed_bwd_sorted": ([vp, vp, vp, vp, vp, i64, i64, i64, vp], C.c_int),
     "ccb_embed_bwd_slots": ([i64, i64, i64], C.c_int64),

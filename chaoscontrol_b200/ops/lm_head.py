@@ -120,6 +120,17 @@ def lm_head_reference(x, rowss, W_f, targets, *, gscale: float = 1.0, rowweight=
     return loss_rows.detach(), lse.detach(), xf.grad, Wf.grad
 
 
+def _refuse_unless_allowed(x, W_f, allow_materialized: bool, what: str) -> None:
+    """On a CUDA device an operand the kernels do not take is an error, not a quiet drop to a
+    logits-materialising PyTorch path (the reference's dispatcher refuses the same way,
+    src/chaoscontrol/kernels/_lm_head_loss/__init__.py:1041-1145); a caller that wants that path
+    says so with ``allow_materialized=True``.  CPU tensors always take the PyTorch statement."""
+    if x.is_cuda and not allow_materialized:
+        raise TypeError(f"{what}: no LM-head kernel takes x {tuple(x.shape)} {x.dtype} with W {tuple(W_f.shape)} "
+                        f"{W_f.dtype} (bf16, model dim a multiple of 8 and at most 512, vocabulary a multiple of 8); "
+                        "pass allow_materialized=True to run the PyTorch statement, which builds the logits")
+
+
 def _prep(x, rowss, W_f, targets):
     assert x.is_contiguous() and W_f.is_contiguous()
     t = targets.reshape(-1)
@@ -138,22 +149,40 @@ def _few_rows(R: int) -> bool:
     return (R + 127) // 128 < SMALL_R_TILES
 
 
-def lm_head_lse(x, rowss, W_f, targets, *, eps: float = EPS, want_entropy: bool = False):
+def _lse_materialized(x, rowss, W_f, targets, eps, want_entropy, max_logit_bytes: int = 256 << 20):
+    """PyTorch statement in row chunks (logits of one chunk at a time, at most ``max_logit_bytes``)."""
+    R, D = x.shape
+    V = W_f.shape[0]
+    rc = max(1, min(R, max_logit_bytes // (4 * V)))
+    t = targets.reshape(-1)
+    outs = []
+    for r0 in range(0, R, rc):
+        xs = x[r0:r0 + rc].float()
+        if rowss is not None:
+            xs = xs * torch.rsqrt((xs * xs).sum(-1, keepdim=True) / D + eps)
+        logits = xs @ W_f.float().t()
+        lse = torch.logsumexp(logits, -1)
+        rows = lse - logits.gather(1, t[r0:r0 + rc].view(-1, 1).long()).squeeze(1)
+        ent = lse - (torch.softmax(logits, -1) * logits).sum(-1) if want_entropy else None
+        outs.append((rows, lse, ent))
+    rows = torch.cat([o[0] for o in outs])
+    lse = torch.cat([o[1] for o in outs])
+    if want_entropy:
+        return rows, lse, torch.cat([o[2] for o in outs])
+    return rows, lse
+
+
+def lm_head_lse(x, rowss, W_f, targets, *, eps: float = EPS, want_entropy: bool = False,
+                allow_materialized: bool = False):
     """Forward only: ``(loss_rows, lse)`` fp32 ``[R]`` (plus the softmax entropy
-    when asked); no logits in memory."""
+    when asked); no logits in memory.  Operands no kernel takes raise on a CUDA device unless
+    ``allow_materialized`` (then the PyTorch statement runs in bounded row chunks)."""
     R, D = x.shape
     if (not fused_supported(x, W_f) or _few_rows(R)) and general_supported(x, W_f) and not want_entropy:
         return _lse_general(x, rowss, W_f, _prep(x, rowss, W_f, targets), eps)
     if not fused_supported(x, W_f):
-        lr, lse, _, _ = lm_head_reference(x, rowss, W_f, targets, eps=eps, want_grads=False)
-        if want_entropy:
-            xf = x.float()
-            if rowss is not None:
-                xf = xf * torch.rsqrt((xf * xf).sum(-1, keepdim=True) / D + eps)
-            logits = xf @ W_f.float().t()
-            p = torch.softmax(logits, -1)
-            return lr, lse, lse - (p * logits).sum(-1)
-        return lr, lse
+        _refuse_unless_allowed(x, W_f, allow_materialized, "lm_head_lse" + (" (entropy)" if want_entropy else ""))
+        return _lse_materialized(x, rowss, W_f, targets, eps, want_entropy)
     t = _prep(x, rowss, W_f, targets)
     lse = torch.empty(R, dtype=torch.float32, device=x.device)
     loss = torch.empty(R, dtype=torch.float32, device=x.device)
@@ -190,7 +219,7 @@ ONE_SWEEP = True      # module switch: lse + dX in one vocabulary sweep (see lm_
 
 def lm_head_train(x, rowss, W_f, targets, *, gscale: float, rowweight=None, eps: float = EPS,
                   row_chunks: Optional[int] = None, lse: Optional[torch.Tensor] = None,
-                  one_sweep: Optional[bool] = None):
+                  one_sweep: Optional[bool] = None, allow_materialized: bool = False):
     """Loss and both gradients.  Returns ``(loss_rows, lse, dX bf16, dW_f_partials fp32 [C,V,D])``.
 
     ``dX`` is the gradient w.r.t. the un-normalised hidden state (RMSNorm
@@ -210,6 +239,7 @@ def lm_head_train(x, rowss, W_f, targets, *, gscale: float, rowweight=None, eps:
     if (not fused_supported(x, W_f) or (_few_rows(R) and one_sweep is None)) and general_supported(x, W_f):
         return _train_general(x, rowss, W_f, _prep(x, rowss, W_f, targets), gscale, rowweight, eps, lse)
     if not fused_supported(x, W_f):
+        _refuse_unless_allowed(x, W_f, allow_materialized, "lm_head_train")
         lr, lse, dX, dW = lm_head_reference(x, rowss, W_f, targets, gscale=gscale,
                                             rowweight=rowweight, eps=eps)
         return lr, lse, dX.to(x.dtype), dW.unsqueeze(0)

@@ -143,39 +143,42 @@ def scan_fused_bwd(P: torch.Tensor, log_a_f32: torch.Tensor, h0: Optional[torch.
 # ---------------------------------------------------------------------------
 # public ssm_scan(decay, update) with autograd
 # ---------------------------------------------------------------------------
+_DT_CODE = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
+#: (decay, update) dtype pairs the native scan takes as they are -- the reference op's whitelist
+#: (src/chaoscontrol/kernels/_ssm_scan/__init__.py:104-113)
+KERNEL_DTYPE_COMBOS = frozenset({
+    (torch.bfloat16, torch.bfloat16), (torch.bfloat16, torch.float16), (torch.float16, torch.float16),
+    (torch.float32, torch.float32), (torch.float32, torch.bfloat16), (torch.float32, torch.float16),
+})
+
+
 class _SsmScanFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, decay, update, h0):
         B, T, D = update.shape
-        dec = decay.float().contiguous()
-        upd = update.contiguous()
-        if upd.dtype not in (torch.float32, torch.bfloat16):
-            upd = upd.float()
         states = torch.empty(B, T, D, dtype=torch.float32, device=update.device)
         h0c = None if h0 is None else h0.float().contiguous()
-        _lib.check(_lib.lib().ccb_plain_scan_fwd(dec.data_ptr(), upd.data_ptr(),
-                                                 int(upd.dtype == torch.bfloat16), _lib.ptr(h0c),
-                                                 states.data_ptr(), B, T, D, _lib.stream_ptr()),
-                   "plain_scan_fwd")
-        ctx.save_for_backward(dec, states, h0c if h0c is not None else torch.empty(0))
+        _lib.check(_lib.lib().ccb_plain_scan_fwd(decay.data_ptr(), _DT_CODE[decay.dtype], update.data_ptr(),
+                                                 _DT_CODE[update.dtype], _lib.ptr(h0c), states.data_ptr(),
+                                                 B, T, D, _lib.stream_ptr()), "plain_scan_fwd")
+        ctx.save_for_backward(decay, states, h0c if h0c is not None else torch.empty(0))
         ctx.has_h0 = h0 is not None
-        ctx.dtypes = (decay.dtype, update.dtype)
+        ctx.update_dtype = update.dtype
         return states.to(update.dtype)
 
     @staticmethod
     def backward(ctx, g):
-        dec, states, h0c = ctx.saved_tensors
+        decay, states, h0c = ctx.saved_tensors
         B, T, D = states.shape
-        gs = g.float().contiguous()
-        gdec = torch.empty_like(states)
-        gupd = torch.empty_like(states)
+        gs = g.to(ctx.update_dtype).contiguous()
+        gdec = torch.empty_like(decay)                     # decay dtype
+        gupd = torch.empty_like(gs)                        # update dtype
         gh0 = torch.empty(B, D, dtype=torch.float32, device=g.device) if ctx.has_h0 else None
-        _lib.check(_lib.lib().ccb_plain_scan_bwd(dec.data_ptr(), states.data_ptr(),
-                                                 h0c.data_ptr() if ctx.has_h0 else None,
-                                                 gs.data_ptr(), gdec.data_ptr(), gupd.data_ptr(),
-                                                 _lib.ptr(gh0), B, T, D, _lib.stream_ptr()),
-                   "plain_scan_bwd")
-        return gdec.to(ctx.dtypes[0]), gupd.to(ctx.dtypes[1]), gh0
+        _lib.check(_lib.lib().ccb_plain_scan_bwd(decay.data_ptr(), _DT_CODE[decay.dtype], states.data_ptr(),
+                                                 h0c.data_ptr() if ctx.has_h0 else None, gs.data_ptr(),
+                                                 _DT_CODE[ctx.update_dtype], gdec.data_ptr(), gupd.data_ptr(),
+                                                 _lib.ptr(gh0), B, T, D, _lib.stream_ptr()), "plain_scan_bwd")
+        return gdec, gupd, gh0
 
 
 def ssm_scan(decay: torch.Tensor, update: torch.Tensor,
@@ -191,5 +194,8 @@ def ssm_scan(decay: torch.Tensor, update: torch.Tensor,
     if not decay.is_contiguous() or not update.is_contiguous():
         raise ValueError("ssm_scan requires contiguous inputs")
     if update.is_cuda:
+        if (decay.dtype, update.dtype) not in KERNEL_DTYPE_COMBOS:
+            raise TypeError(f"ssm_scan: (decay, update) dtypes ({decay.dtype}, {update.dtype}) are not among the "
+                            f"pairs the native scan takes: {sorted(map(str, KERNEL_DTYPE_COMBOS))}; cast explicitly")
         return _SsmScanFn.apply(decay, update, initial_state)
     return diag_recurrence_chunked(decay, update, h0=initial_state).to(update.dtype)

@@ -7,6 +7,11 @@ and maps every peer's copies (handles travel through the process group's object
 all-gather).  ``all_reduce_`` then launches the pack / reduce kernels on the
 current stream; no NCCL call is involved.
 
+The epoch that tags every collective's flags lives in device memory (slot 15 of the
+counter array) and is advanced by the kernels themselves, so a collective's launch
+arguments never change: a training step that contains collectives can be captured in
+a CUDA graph.
+
 Timeouts: every device-side wait is bounded by ``timeout_ms``; a rank that
 never signals makes the others record ``CCB_ERR_PEER_TIMEOUT`` in the status
 word and return with their gradients unreduced, instead of hanging.  The host
@@ -35,11 +40,11 @@ _lib.register_sig("ccb_comm_free", [vp])
 _lib.register_sig("ccb_ipc_get", [vp, vp])
 _lib.register_sig("ccb_ipc_open", [vp], vp)
 _lib.register_sig("ccb_ipc_close", [vp])
-_lib.register_sig("ccb_allreduce", [vp, i64, C.c_float, vp, vp, vp, i64, i64, i64, vp, i64, i64, vp])
+_lib.register_sig("ccb_allreduce", [vp, i64, C.c_float, vp, vp, vp, i64, i64, vp, i64, i64, vp])
 _lib.register_sig("ccb_comm_wait_probe", [vp, i64, i64, vp, vp])
-_lib.register_sig("ccb_sharded_sync", [i64, vp, vp, i64, C.c_float, vp, i64, vp, vp, vp, i64, i64, i64, vp, i64, vp])
-_lib.register_sig("ccb_allreduce_ranges", [vp, vp, i64, i64, C.c_float, vp, vp, vp, i64, i64, i64, vp, i64, i64, vp])
-_lib.register_sig("ccb_comm_bcast", [vp, i64, i64, vp, vp, vp, i64, i64, i64, vp, i64, vp])
+_lib.register_sig("ccb_sharded_sync", [i64, vp, vp, i64, C.c_float, vp, i64, vp, vp, vp, i64, i64, vp, i64, vp])
+_lib.register_sig("ccb_allreduce_ranges", [vp, vp, i64, i64, C.c_float, vp, vp, vp, i64, i64, vp, i64, i64, vp])
+_lib.register_sig("ccb_comm_bcast", [vp, i64, i64, vp, vp, vp, i64, i64, vp, i64, vp])
 _lib.register_sig("ccb_comm_flag_max", [i64, vp, i64, i64, i64, vp, i64, vp])
 _lib.register_sig("ccb_comm_clear", [vp, i64])
 
@@ -59,7 +64,6 @@ class PeerComm:
         self.rank = 0
         self.ws = 1
         self.numel = 0
-        self.epoch = 0
         self.timeout_ms = 2000
         self._own: list[int] = []
         self._opened: list[int] = []
@@ -163,10 +167,9 @@ class PeerComm:
             return
         if mode is None:
             mode = 0 if n * 2 <= ONE_SHOT_MAX_BYTES else 1
-        self.epoch += 1
         scale = 1.0 / self.ws if average else 1.0
         _lib.check(_lib.lib().ccb_allreduce(flat.data_ptr(), n, scale, self._bufs, self._bufs2,
-                                            self._pads, self.rank, self.ws, self.epoch,
+                                            self._pads, self.rank, self.ws,
                                             self._counters.data_ptr(), mode, self.timeout_ms,
                                             _lib.stream_ptr()), "allreduce")
 
@@ -189,7 +192,6 @@ class PeerComm:
         n = flat_grad.numel()
         if flat_grad.dtype != torch.float32 or n % 8 or n > self.numel:
             raise ValueError("sharded_reduce_ needs an fp32 flat tensor, length % 8 == 0, within the buffer")
-        self.epoch += 1
         self._sharded(0, flat_grad, None, n, 1.0 / self.ws if average else 1.0, ranges)
 
     def sharded_gather_(self, flat_param: torch.Tensor, ranges: torch.Tensor) -> None:
@@ -202,7 +204,7 @@ class PeerComm:
     def _sharded(self, phase, grad, param, n, scale, ranges) -> None:
         _lib.check(_lib.lib().ccb_sharded_sync(
             phase, _lib.ptr(grad), _lib.ptr(param), n, scale, ranges.data_ptr(), ranges.shape[0], self._bufs,
-            self._bufs2, self._pads, self.rank, self.ws, self.epoch, self._counters.data_ptr(), self.timeout_ms,
+            self._bufs2, self._pads, self.rank, self.ws, self._counters.data_ptr(), self.timeout_ms,
             _lib.stream_ptr()), "sharded_sync")
 
     # ------------------------------------------------------------------
@@ -214,10 +216,9 @@ class PeerComm:
         self._alive()
         if flat_grad.dtype != torch.float32 or flat_grad.numel() > self.numel:
             raise ValueError("all_reduce_ranges_ needs an fp32 flat tensor within the symmetric buffer")
-        self.epoch += 1
         _lib.check(_lib.lib().ccb_allreduce_ranges(
             flat_grad.data_ptr(), ranges.data_ptr(), int(r0), int(r1), 1.0 / self.ws if average else 1.0,
-            self._bufs, self._bufs2, self._pads, self.rank, self.ws, self.epoch, self._counters.data_ptr(),
+            self._bufs, self._bufs2, self._pads, self.rank, self.ws, self._counters.data_ptr(),
             int(blocks), self.timeout_ms, _lib.stream_ptr() if stream is None else stream), "allreduce_ranges")
 
     def broadcast_(self, flat: torch.Tensor, src: int = 0) -> None:
@@ -227,9 +228,8 @@ class PeerComm:
         nbytes = flat.numel() * flat.element_size()
         if not flat.is_contiguous() or nbytes % 16 or nbytes > self.numel * 2:
             raise ValueError("broadcast_ needs a contiguous tensor of 16-byte words within the symmetric buffer")
-        self.epoch += 1
         _lib.check(_lib.lib().ccb_comm_bcast(flat.data_ptr(), nbytes, int(src), self._bufs, self._bufs2,
-                                             self._pads, self.rank, self.ws, self.epoch,
+                                             self._pads, self.rank, self.ws,
                                              self._counters.data_ptr(), self.timeout_ms, _lib.stream_ptr()),
                    "bcast")
 
@@ -274,8 +274,7 @@ class PeerComm:
         dist.barrier(group=self.group)
         own_pad = self._pads[self.rank]
         _lib.check(_lib.lib().ccb_comm_clear(own_pad, PAD_ROWS * MAX_RANKS * 4), "comm_clear")
-        self._counters.zero_()
-        self.epoch = 0
+        self._counters.zero_()                    # arrival counters and the device-resident epoch
         self._flag_seq = 0
         _lib.read_status(reset=True)
         torch.cuda.synchronize()

@@ -243,6 +243,103 @@ def train_ssm_step(model: nn.Module, inputs: torch.Tensor, targets: torch.Tensor
     return loss
 
 
+class GraphedTrainStep:
+    """A fixed-shape training step -- forward, backward, the data-parallel gradient exchange and the
+    gradient clip -- captured once in a CUDA graph and replayed per batch.
+
+    ``step(inputs, targets)`` copies the batch into two static device buffers (the copy may come
+    straight from pinned host memory), replays the graph and returns the loss as a device scalar
+    that the next replay overwrites.  The first ``eager_steps`` calls run :func:`train_ssm_step`
+    eagerly (they are real training steps and also finish every lazy set-up a capture must not
+    contain), the next call captures.  The optimizer step stays outside: its AdamW bias corrections
+    are host scalars that change every step.
+
+    Data-parallel steps can be captured because the peer-memory collectives keep their epoch in
+    device memory (no launch argument changes between steps); with the library fallback
+    (NCCL / gloo) the step is not capturable here and ``step`` stays eager.
+
+    The reference rejected whole-step graphs at this model size (2.34 M vs 2.55 M tokens/s eager,
+    experiments/23_fast_path/RESULTS_GRAPH_PROBE.md:15-16); here the step is about 220 launches of
+    10-700 us, and the graph removes the gaps between them.
+    """
+
+    def __init__(self, model: nn.Module, *, chunk_size: int = 64, ddp_active: bool = False, world_size: int = 1,
+                 precision: str = "bf16", lm_head_backward_mode: str = "fused_streaming_cached",
+                 lm_head_tile_size: int = 8192, grad_clip_norm: float = 0.0, eager_steps: int = 2) -> None:
+        self.model = model
+        self.kw = dict(ddp_active=ddp_active, world_size=world_size, precision=precision,
+                       lm_head_backward_mode=lm_head_backward_mode, lm_head_tile_size=lm_head_tile_size)
+        self.chunk_size = int(chunk_size)
+        self.grad_clip_norm = float(grad_clip_norm)
+        self.eager_left = max(1, int(eager_steps))
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self._in: Optional[torch.Tensor] = None
+        self._tg: Optional[torch.Tensor] = None
+        self._loss: Optional[torch.Tensor] = None
+        self.capturable = True
+        self.replays = 0
+        self.launches_per_replay = 0
+
+    def _eager(self, inputs: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        loss = train_ssm_step(self.model, inputs, targets, self.chunk_size, **self.kw)
+        if self.grad_clip_norm > 0.0:
+            arena = get_arena(self.model)
+            if arena is not None and arena.grads_fresh:
+                clip_arena_grad_norm(arena, self.grad_clip_norm)
+            else:
+                clip_grad_norm_fused(self.model.parameters(), self.grad_clip_norm)
+        return loss
+
+    def _can_capture(self) -> bool:
+        if not (torch.cuda.is_available() and next(self.model.parameters()).is_cuda):
+            return False
+        if _engine_for(self.model) is None:
+            return False
+        if self.kw["ddp_active"] and self.kw["world_size"] > 1:
+            from .parallel import symm
+            comm = symm.active_comm(None)
+            return comm is not None and comm.ws == self.kw["world_size"]
+        return True
+
+    def step(self, inputs: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        if self.graph is None:
+            if self.eager_left > 0 or not self.capturable:
+                self.eager_left -= 1
+                return self._eager(inputs.to(next(self.model.parameters()).device, non_blocking=True),
+                                   targets.to(next(self.model.parameters()).device, non_blocking=True))
+            if not self._can_capture():
+                self.capturable = False
+                return self.step(inputs, targets)
+            dev = next(self.model.parameters()).device
+            self._in = torch.empty(inputs.shape, dtype=inputs.dtype, device=dev)
+            self._tg = torch.empty(targets.shape, dtype=targets.dtype, device=dev)
+            self._in.copy_(inputs, non_blocking=True)
+            self._tg.copy_(targets, non_blocking=True)
+            torch.cuda.synchronize(dev)
+            g = torch.cuda.CUDAGraph()
+            from .ops import _lib
+            n0 = _lib.launch_count()
+            with torch.cuda.graph(g, capture_error_mode="thread_local"):
+                self._loss = self._eager(self._in, self._tg)
+            self.launches_per_replay = _lib.launch_count() - n0     # this library's kernels inside the graph
+            self.graph = g
+        else:
+            if inputs.shape != self._in.shape or targets.shape != self._tg.shape:
+                raise ValueError(f"GraphedTrainStep was captured for batches of {tuple(self._in.shape)}; got "
+                                 f"{tuple(inputs.shape)}")
+            self._in.copy_(inputs, non_blocking=True)
+            self._tg.copy_(targets, non_blocking=True)
+        self.graph.replay()
+        self.replays += 1
+        arena = get_arena(self.model)
+        if arena is not None:
+            arena.grads_fresh = True          # host flags a replay does not set
+            arena.grads_reduced = False
+        return self._loss
+
+    __call__ = step
+
+
 def train_ssm_step_with_ce(model: nn.Module, inputs: torch.Tensor, targets: torch.Tensor, *,
                            precision: str = "bf16", lm_head_backward_mode: str = "fused",
                            lm_head_tile_size: int = 1024) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:

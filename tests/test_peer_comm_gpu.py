@@ -169,3 +169,81 @@ def test_peer_allreduce_two_gpus():
         mp.spawn(_worker, args=(2, port, d), nprocs=2, join=True)
         outs = [open(os.path.join(d, f"r{r}.txt")).read() for r in range(2)]
     assert all(o == "OK" for o in outs), outs
+
+
+def _graph_worker(rank, ws, port, outdir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=ws, device_id=torch.device("cuda", rank))
+    ok, msg = True, ""
+    try:
+        from chaoscontrol_b200.models.model import CareStudentLM
+        from chaoscontrol_b200.optim.muon import Muon
+        from chaoscontrol_b200.parallel import symm_comm
+        from chaoscontrol_b200.parallel.distributed import broadcast_params, clip_arena_grad_norm
+        from chaoscontrol_b200.train_ssm import GraphedTrainStep, train_ssm_step
+        from chaoscontrol_b200.utils.arena import ParamArena
+
+        def build():
+            torch.manual_seed(0)
+            m = CareStudentLM(vocab_size=2048, dim=256, num_layers=2, ff_mult=2).cuda().to(torch.bfloat16)
+            arena = ParamArena.install(m)
+            m.train()
+            opt = Muon(m.parameters(), lr=0.02, weight_decay=0.01, adamw_lr=0.02, adamw_weight_decay=0.01, fused=True)
+            opt.bind_arena(arena)
+            return m, arena, opt
+
+        g = torch.Generator().manual_seed(10 + rank)              # every rank trains on its own batches
+        batches = [torch.randint(0, 2048, (16, 257), generator=g).cuda() for _ in range(6)]
+        m1, a1, o1 = build()
+        symm_comm.enable(a1.flat_grad.numel())
+        broadcast_params(m1)
+        for b in batches:                                           # eager: overlapped exchange, then clip
+            train_ssm_step(m1, b[:, :-1], b[:, 1:], 64, ddp_active=True, world_size=ws, precision="bf16",
+                           lm_head_backward_mode="fused_streaming_cached")
+            clip_arena_grad_norm(a1, 1.0)
+            o1.step()
+        m2, a2, o2 = build()
+        broadcast_params(m2)
+        step = GraphedTrainStep(m2, ddp_active=True, world_size=ws, grad_clip_norm=1.0, eager_steps=2)
+        for b in batches:                                           # two eager steps, then graph replays
+            step(b[:, :-1], b[:, 1:])
+            o2.step()
+        torch.cuda.synchronize()
+        if step.graph is None or step.replays != 4:
+            ok, msg = False, f"graph not used (graph {step.graph}, replays {step.replays})"
+        if not torch.equal(a1.flat_param, a2.flat_param):
+            d = (a1.flat_param.float() - a2.flat_param.float()).abs().max().item()
+            ok, msg = False, f"graphed DDP steps differ from eager ones (max {d})"
+        chk = a2.flat_param.float().double().sum().reshape(1)
+        gathered = [torch.zeros_like(chk) for _ in range(ws)]
+        dist.all_gather(gathered, chk)
+        if any(float(t) != float(gathered[0]) for t in gathered):
+            ok, msg = False, "replicas disagree after graphed DDP steps"
+        if _lib.read_status() != 0:
+            ok, msg = False, f"status {_lib.read_status()}"
+        dist.barrier()
+        symm_comm.disable()
+    except Exception as exc:  # pragma: no cover
+        import traceback
+        ok, msg = False, f"{type(exc).__name__}: {exc} {traceback.format_exc()[-600:]}"
+    finally:
+        with open(os.path.join(outdir, f"r{rank}.txt"), "w") as f:
+            f.write("OK" if ok else "FAIL " + msg)
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_graphed_data_parallel_step_two_gpus():
+    """The whole data-parallel step (overlapped peer-memory exchange included) replayed from a CUDA
+    graph gives the same parameter bits as the eager steps, on every rank."""
+    import torch.multiprocessing as mp
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_graph_worker, args=(2, port, d), nprocs=2, join=True)
+        outs = [open(os.path.join(d, f"r{r}.txt")).read() for r in range(2)]
+    assert all(o == "OK" for o in outs), outs

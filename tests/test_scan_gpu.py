@@ -69,3 +69,47 @@ def test_ssm_scan_public_op():
     assert torch.count_nonzero(gd[:, 0]) == 0
     with pytest.raises(ValueError):
         S.ssm_scan(decay.transpose(0, 1), update.transpose(0, 1))
+
+
+_COMBOS = [(torch.bfloat16, torch.bfloat16), (torch.bfloat16, torch.float16), (torch.float16, torch.float16),
+           (torch.float32, torch.float32), (torch.float32, torch.bfloat16), (torch.float32, torch.float16)]
+
+
+@pytest.mark.parametrize("ddt,udt", _COMBOS, ids=lambda d: str(d).replace("torch.", ""))
+@pytest.mark.parametrize("with_h0", [False, True])
+def test_ssm_scan_dtype_matrix(ddt, udt, with_h0):
+    """The six (decay, update) dtype pairs of the reference op run natively (no cast of the operands):
+    values and both gradients against the fp32 serial loop on the same rounded inputs, gradient
+    dtypes follow the operand dtypes."""
+    torch.manual_seed(3)
+    B, T, D = 2, 70, 160
+    decay = (torch.rand(B, T, D, device="cuda") * 0.9 + 0.05).to(ddt).requires_grad_(True)
+    update = torch.randn(B, T, D, device="cuda").to(udt).requires_grad_(True)
+    h0 = torch.randn(B, D, device="cuda").requires_grad_(True) if with_h0 else None
+    out = S.ssm_scan(decay, update, h0)
+    assert out.dtype == udt
+    dref = decay.detach().float().requires_grad_(True)
+    uref = update.detach().float().requires_grad_(True)
+    href = h0.detach().clone().requires_grad_(True) if with_h0 else None
+    ref = S.diag_recurrence_reference(dref, uref, href)
+    lowp = udt != torch.float32
+    tol = dict(rtol=2e-2, atol=2e-2) if lowp else dict(rtol=1e-5, atol=1e-5)
+    assert torch.allclose(out.float(), ref, **tol)
+    g = torch.randn(B, T, D, device="cuda").to(udt)
+    ins = (decay, update) + ((h0,) if with_h0 else ())
+    refs = (dref, uref) + ((href,) if with_h0 else ())
+    got = torch.autograd.grad(out, ins, g)
+    want = torch.autograd.grad(ref, refs, g.float())
+    assert got[0].dtype == ddt and got[1].dtype == udt
+    gt = dict(rtol=5e-2, atol=1e-1) if (lowp or ddt != torch.float32) else dict(rtol=1e-4, atol=1e-4)
+    for a, b in zip(got, want):
+        assert torch.allclose(a.float(), b, **gt), (a.float() - b).abs().max()
+
+
+def test_ssm_scan_rejects_unlisted_dtype_pairs():
+    d = torch.rand(1, 4, 8, device="cuda", dtype=torch.float16)
+    u = torch.randn(1, 4, 8, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(TypeError):
+        S.ssm_scan(d, u)
+    with pytest.raises(TypeError):
+        S.ssm_scan(d.double(), u.double())

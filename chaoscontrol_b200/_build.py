@@ -92,7 +92,7 @@ def build_cuda(verbose: bool = False) -> Path:
 def build_ctrl(verbose: bool = False) -> Path:
     """Compile the CPU control plane (``native/*.cpp``) into ``libccb200_ctrl.so``."""
     cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
-    srcs = sorted(NATIVE.glob("*.cpp"))
+    srcs = sorted(p for p in NATIVE.glob("*.cpp") if p.name != "selftest.cpp")   # the stress driver has a main()
     if not srcs:
         return CTRL_LIB
     headers = sorted(NATIVE.glob("*.h"))
@@ -107,12 +107,61 @@ def build_ctrl(verbose: bool = False) -> Path:
     return CTRL_LIB
 
 
+SANITIZERS = ("thread", "address")
+
+
+def build_and_run_selftest(sanitize: str, timeout: float = 300.0) -> tuple[int, str]:
+    """Compile ``native/selftest.cpp`` with the ring, shared-memory and pad-protocol sources under
+    ``-fsanitize=<thread|address>`` into ``lib/ccb200_ctrl_selftest_<sanitizer>`` and run it.
+    Returns ``(exit code, combined output)``; 0 means every check held and the sanitizer stayed quiet,
+    127 that the compiler has no runtime library for that sanitizer on this machine.  ``sanitize="none"``
+    builds and runs the same driver without instrumentation (the functional half of the check)."""
+    if sanitize not in SANITIZERS + ("none",):
+        raise ValueError(f"sanitize must be one of {SANITIZERS + ('none',)}, got {sanitize!r}")
+    # the sanitizer runtimes ship with the distribution's compiler, which need not be $CXX or the first
+    # g++ on PATH: try each candidate until one links
+    cands = [os.environ.get("CCB_SANITIZE_CXX"), "/usr/bin/g++-13", "/usr/bin/x86_64-linux-gnu-g++-13", "/usr/bin/g++",
+             os.environ.get("CXX"), shutil.which("g++")]
+    cands = [c for i, c in enumerate(cands) if c and Path(c).exists() and c not in cands[:i]] or ["g++"]
+    LIBDIR.mkdir(parents=True, exist_ok=True)
+    exe = LIBDIR / f"ccb200_ctrl_selftest_{sanitize}"
+    srcs = [NATIVE / n for n in ("selftest.cpp", "ring.cpp", "pad_protocol.cpp")]
+    san = [] if sanitize == "none" else [f"-fsanitize={sanitize}"]
+    missing = []
+    for cxx in cands:
+        cmd = [cxx, "-std=c++17", "-O1", "-g", "-fno-omit-frame-pointer", *san, "-pthread",
+               "-I", str(NATIVE), *map(str, srcs), "-o", str(exe), "-lrt"]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode == 0:
+            break
+        if "cannot find -ltsan" in res.stderr or "cannot find -lasan" in res.stderr or "preinit.o" in res.stderr:
+            missing.append(cxx)
+            continue
+        return res.returncode, f"compile failed: {' '.join(cmd)}\n{res.stdout}\n{res.stderr}"
+    else:
+        return 127, f"no sanitizer runtime for -fsanitize={sanitize} with any of {missing}"
+    env = dict(os.environ)
+    env.setdefault("TSAN_OPTIONS", "halt_on_error=1 exitcode=66 second_deadlock_stack=1")
+    env.setdefault("ASAN_OPTIONS", "detect_leaks=1 exitcode=66")
+    run = [str(exe)]
+    if sanitize == "thread" and shutil.which("setarch"):
+        run = ["setarch", "-R", *run]          # ThreadSanitizer's shadow layout wants ASLR off on recent kernels
+    out = subprocess.run(run, capture_output=True, text=True, timeout=timeout, env=env)
+    return out.returncode, out.stdout + out.stderr
+
+
 def build_all(verbose: bool = False) -> dict[str, str]:
     LIBDIR.mkdir(parents=True, exist_ok=True)
     return {"cuda": str(build_cuda(verbose)), "ctrl": str(build_ctrl(verbose))}
 
 
 if __name__ == "__main__":
+    if "--sanitize" in sys.argv:
+        which = sys.argv[sys.argv.index("--sanitize") + 1]
+        rc, text = build_and_run_selftest(which)
+        print(text.strip())
+        print(f"selftest under -fsanitize={which}: exit code {rc}")
+        sys.exit(rc)
     out = build_all(verbose="-v" in sys.argv)
     for k, v in out.items():
         print(f"{k}: {v}")

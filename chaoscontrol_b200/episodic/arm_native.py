@@ -38,6 +38,7 @@ def _L() -> C.CDLL:
         L.ccbc_lmhead_pack.argtypes = [vp, vp, i32, i32]
         L.ccbc_lmhead_free.argtypes = [vp]
         L.ccbc_rms_lmhead_nll.argtypes = [vp, vp, vp, i32, f32, vp]
+        L.ccbc_rms_lmhead_nll_mode.argtypes = [vp, vp, vp, i32, f32, vp, i32]
         L.ccbc_evidence_new.restype = vp
         L.ccbc_evidence_new.argtypes = [u32, u32]
         L.ccbc_evidence_free.argtypes = [vp]
@@ -155,14 +156,19 @@ class PackedLmHead:
             pass
 
 
-def rms_lmhead_nll(head: PackedLmHead, hidden: torch.Tensor, targets: torch.Tensor, eps: float = 1e-6
-                   ) -> tuple[torch.Tensor, bool]:
+def rms_lmhead_nll(head: PackedLmHead, hidden: torch.Tensor, targets: torch.Tensor, eps: float = 1e-6, *,
+                   packed_amx: bool = True) -> tuple[torch.Tensor, bool]:
     """``(per-token NLL [T] fp32, used_amx)`` of ``lm_head(RMSNorm(hidden))`` computed on the host cores from
-    bf16 operands; the vocabulary is streamed in tiles with an online log-sum-exp."""
+    bf16 operands; the vocabulary is streamed in tiles with an online log-sum-exp.
+
+    On CPUs with AMX the default path multiplies straight out of the VNNI tile cache that
+    ``PackedLmHead`` built once and folds each 16 x 16 logits tile into the running (max, sum);
+    ``packed_amx=False`` takes the generic tile-matmul path instead (the oracle for the fused one)."""
     h = _bf16_bits(hidden.reshape(-1, head.D))
     y = np.ascontiguousarray(targets.detach().cpu().numpy().reshape(-1).astype(np.int64))
     out = np.zeros(h.shape[0], np.float32)
-    used = _L().ccbc_rms_lmhead_nll(head._h, h.ctypes.data, y.ctypes.data, int(h.shape[0]), float(eps), out.ctypes.data)
+    used = _L().ccbc_rms_lmhead_nll_mode(head._h, h.ctypes.data, y.ctypes.data, int(h.shape[0]), float(eps),
+                                         out.ctypes.data, 0 if packed_amx else 1)
     return torch.from_numpy(out), bool(used)
 
 

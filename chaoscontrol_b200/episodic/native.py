@@ -120,6 +120,13 @@ def lib() -> C.CDLL:
         L.ccbc_simplex_forward.argtypes = [C.c_int] * 4 + [C.c_float] + [C.c_void_p] * 6
         L.ccbc_simplex_grad.argtypes = ([C.c_int] * 4 + [C.c_float] + [C.c_void_p] * 4 +
                                         [C.c_int, C.c_float, C.c_float, C.c_void_p])
+        L.ccbc_simplex_flat_size_ex.argtypes = [C.c_int] * 7
+        L.ccbc_simplex_flat_size_ex.restype = C.c_int64
+        L.ccbc_simplex_forward_ex.argtypes = [C.c_int] * 8 + [C.c_float] + [C.c_void_p] * 7
+        L.ccbc_simplex_grad_ex.argtypes = ([C.c_int] * 8 + [C.c_float] + [C.c_void_p] * 4 +
+                                           [C.c_int, C.c_float, C.c_float, C.c_void_p])
+        L.ccbc_forward_pretrain_model.argtypes = [C.c_int] * 5 + [C.c_void_p] * 13
+        L.ccbc_learner_init_ex.argtypes = [C.c_void_p] + [C.c_int] * 8 + [C.c_float, C.c_void_p]
         L.ccbc_learner_new.argtypes = [C.c_int, C.c_int, C.c_float, C.c_float, C.c_int, C.c_float,
                                        C.c_int64, C.c_float, C.c_float]
         L.ccbc_learner_free.argtypes = [C.c_void_p]
@@ -282,6 +289,74 @@ class SimplexPolicy:
         if rc:
             raise ValueError(_err())
         return g
+
+
+class SimplexPolicyV3(SimplexPolicy):
+    """The policy with its optional parts: ``K_e`` edge features per vertex pair, ``n_heads`` residual
+    attention heads over the vertices (learned H x H query / key / value projections, per-head
+    edge bias, averaged per-vertex logits scaled by ``lambda_hxh``) and a stored bucket-embedding
+    table (simplex_policy.h:27-53 of the reference).  Flat layout: the base block, then
+    ``[lambda | W_q | W_k | W_v | W_o | W_e]`` when ``n_heads > 0``, then ``bucket_embed``."""
+
+    def __init__(self, N: int = 16, K_v: int = 16, K_e: int = 1, K_s: int = 4, H: int = 32, n_heads: int = 0,
+                 n_buckets: int = 0, embed_dim: int = 0, temperature: float = 1.0, seed: int = 0) -> None:
+        self.N, self.K_v, self.K_e, self.K_s, self.H = N, K_v, K_e, K_s, H
+        self.n_heads, self.n_buckets, self.embed_dim = n_heads, n_buckets, embed_dim
+        self.temperature = float(temperature)
+        n = int(lib().ccbc_simplex_flat_size_ex(K_v, K_e, K_s, H, n_heads, n_buckets, embed_dim))
+        self.flat = (np.random.default_rng(seed).standard_normal(n) * 0.1).astype(np.float32)
+
+    def _dims(self):
+        return (self.N, self.K_v, self.K_e, self.K_s, self.H, self.n_heads, self.n_buckets, self.embed_dim)
+
+    def forward(self, V, E, feats, with_branch: bool = False):
+        V, E, feats = _f32(V), _f32(E), _f32(feats)
+        p, logits, hxh = (np.zeros(self.N, np.float32) for _ in range(3))
+        rc = lib().ccbc_simplex_forward_ex(*self._dims(), self.temperature, self.flat.ctypes.data, V.ctypes.data,
+                                           E.ctypes.data, feats.ctypes.data, p.ctypes.data, logits.ctypes.data,
+                                           hxh.ctypes.data)
+        if rc:
+            raise ValueError(_err())
+        return (p, logits, hxh) if with_branch else (p, logits)
+
+    def grad(self, V, E, feats, chosen: int, advantage: float, entropy_beta: float = 0.0) -> np.ndarray:
+        V, E, feats = _f32(V), _f32(E), _f32(feats)
+        g = np.zeros_like(self.flat)
+        rc = lib().ccbc_simplex_grad_ex(*self._dims(), self.temperature, self.flat.ctypes.data, V.ctypes.data,
+                                        E.ctypes.data, feats.ctypes.data, chosen, advantage, entropy_beta,
+                                        g.ctypes.data)
+        if rc:
+            raise ValueError(_err())
+        return g
+
+
+def forward_pretrain_model(features, weights: dict):
+    """``(logits [B, D_slot], value [B])`` of the offline-pretrained controller trunk from features
+    ``[B, F]`` and a weight dict with the reference's names (``trunk.in_proj.weight`` ... ``value_head.bias``,
+    cpu_ssm_controller.cpp:309-355)."""
+    x = _f32(features)
+    w = {k: _f32(v) for k, v in weights.items()}
+    Dg, F = w["trunk.in_proj.weight"].shape
+    L = w["trunk.decay"].shape[0]
+    Ds = w["policy_head.weight"].shape[0]
+    if x.ndim != 2 or x.shape[1] != F:
+        raise ValueError(f"features must be [B, {F}], got {x.shape}")
+    for name, shape in (("trunk.in_proj.bias", (Dg,)), ("trunk.decay", (L, Dg)), ("trunk.w_in", (L, Dg, Dg)),
+                        ("trunk.w_out", (L, Dg, Dg)), ("trunk.bias", (L, Dg)), ("policy_head.weight", (Ds, Dg)),
+                        ("policy_head.bias", (Ds,)), ("value_head.weight", (1, Dg)), ("value_head.bias", (1,))):
+        if tuple(w[name].shape) != shape:
+            raise ValueError(f"{name} must have shape {shape}, got {tuple(w[name].shape)}")
+    B = x.shape[0]
+    logits = np.zeros((B, Ds), np.float32)
+    value = np.zeros(B, np.float32)
+    rc = lib().ccbc_forward_pretrain_model(
+        B, F, Dg, L, Ds, x.ctypes.data, w["trunk.in_proj.weight"].ctypes.data, w["trunk.in_proj.bias"].ctypes.data,
+        w["trunk.decay"].ctypes.data, w["trunk.w_in"].ctypes.data, w["trunk.w_out"].ctypes.data,
+        w["trunk.bias"].ctypes.data, w["policy_head.weight"].ctypes.data, w["policy_head.bias"].ctypes.data,
+        w["value_head.weight"].ctypes.data, w["value_head.bias"].ctypes.data, logits.ctypes.data, value.ctypes.data)
+    if rc:
+        raise ValueError(_err())
+    return logits, value
 
 
 class SimplexOnlineLearner:

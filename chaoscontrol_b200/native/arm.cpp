@@ -36,6 +36,9 @@ namespace ccb::ctrl {
 void matvec(const float*, const float*, float*, int, int);
 void diag_step(const float*, const float*, float*, int);
 int bf16_matmul(const uint16_t*, const uint16_t*, float*, int, int, int);
+void pack_vnni_wt(const uint16_t* W, int V, int D, std::vector<uint16_t>* out);
+int lse_over_vnni(const uint16_t* xn, int T, int Tpad, int Dpad, const uint16_t* packed, int V,
+                  const int64_t* targets, float* run_m, float* run_s, float* tgt);
 }  // namespace ccb::ctrl
 
 using namespace ccb;
@@ -177,6 +180,7 @@ struct LmHead {
   int D = 0, V = 0;
   std::vector<float> norm_w;
   std::vector<uint16_t> wt_tiles;   // per vocabulary tile: [D, kVocabTile] bf16 (W^T, zero padded)
+  std::vector<uint16_t> vnni;       // the same weight in 16 x 16 x 32 VNNI tiles, packed once (AMX path)
   int tiles() const { return (V + kVocabTile - 1) / kVocabTile; }
 };
 
@@ -188,20 +192,34 @@ void pack_lm_head(const float* norm_w, const uint16_t* W, int V, int D, LmHead* 
     uint16_t* tile = out->wt_tiles.data() + (size_t)(v / kVocabTile) * D * kVocabTile;
     for (int d = 0; d < D; ++d) tile[(size_t)d * kVocabTile + v % kVocabTile] = W[(size_t)v * D + d];
   }
+  pack_vnni_wt(W, V, D, &out->vnni);
 }
 
 // hidden: [T, D] bf16; targets: [T]; nll: [T].  Returns 1 when the AMX path ran.
-int rms_lmhead_nll(const LmHead& h, const uint16_t* hidden, const int64_t* targets, int T, float eps, float* nll) {
+// mode: 0 = the VNNI-packed fused AMX path when the CPU has AMX, else the generic path;
+// 1 = generic matmul path (packs per call when it uses AMX); used to pin the two against each other.
+int rms_lmhead_nll_mode(const LmHead& h, const uint16_t* hidden, const int64_t* targets, int T, float eps, float* nll,
+                        int mode) {
   const int D = h.D;
-  std::vector<uint16_t> xn((size_t)T * D);
+  const int Tpad = (T + 15) / 16 * 16, Dpad = (D + 31) / 32 * 32;
+  std::vector<uint16_t> xn((size_t)Tpad * Dpad, 0);
   for (int t = 0; t < T; ++t) {
     double ss = 0.0;
     for (int d = 0; d < D; ++d) { const float v = bf16_to_f32(hidden[(size_t)t * D + d]); ss += (double)v * v; }
     const float inv = 1.0f / std::sqrt((float)(ss / D) + eps);
     for (int d = 0; d < D; ++d)
-      xn[(size_t)t * D + d] = f32_to_bf16(bf16_to_f32(hidden[(size_t)t * D + d]) * inv * h.norm_w[d]);
+      xn[(size_t)t * Dpad + d] = f32_to_bf16(bf16_to_f32(hidden[(size_t)t * D + d]) * inv * h.norm_w[d]);
   }
-  std::vector<float> logits((size_t)T * kVocabTile), run_m(T, -INFINITY), run_s(T, 0.f), tgt(T, 0.f);
+  std::vector<float> run_m(T, -INFINITY), run_s(T, 0.f), tgt(T, 0.f);
+  if (mode == 0 && !h.vnni.empty() &&
+      lse_over_vnni(xn.data(), T, Tpad, Dpad, h.vnni.data(), h.V, targets, run_m.data(), run_s.data(), tgt.data())) {
+    for (int t = 0; t < T; ++t) nll[t] = run_m[t] + std::log(run_s[t]) - tgt[t];
+    return 1;
+  }
+  if (Dpad != D) {                       // the generic path wants densely packed rows
+    for (int t = 1; t < T; ++t) std::memmove(&xn[(size_t)t * D], &xn[(size_t)t * Dpad], (size_t)D * 2);
+  }
+  std::vector<float> logits((size_t)T * kVocabTile);
   int used_amx = 0;
   for (int tile = 0; tile < h.tiles(); ++tile) {
     used_amx |= bf16_matmul(xn.data(), h.wt_tiles.data() + (size_t)tile * D * kVocabTile, logits.data(), T,
@@ -220,6 +238,9 @@ int rms_lmhead_nll(const LmHead& h, const uint16_t* hidden, const int64_t* targe
   }
   for (int t = 0; t < T; ++t) nll[t] = run_m[t] + std::log(run_s[t]) - tgt[t];
   return used_amx;
+}
+int rms_lmhead_nll(const LmHead& h, const uint16_t* hidden, const int64_t* targets, int T, float eps, float* nll) {
+  return rms_lmhead_nll_mode(h, hidden, targets, T, eps, nll, 0);
 }
 
 // ------------------------------------------------------------------ evidence engine
@@ -467,6 +488,10 @@ void* ccbc_lmhead_pack(const float* norm_w, const uint16_t* W_bf16, int V, int D
   return h;
 }
 void ccbc_lmhead_free(void* h) { delete static_cast<LmHead*>(h); }
+int ccbc_rms_lmhead_nll_mode(void* h, const uint16_t* hidden_bf16, const int64_t* targets, int T, float eps,
+                             float* nll, int mode) {
+  return rms_lmhead_nll_mode(*static_cast<LmHead*>(h), hidden_bf16, targets, T, eps, nll, mode);
+}
 int ccbc_rms_lmhead_nll(void* h, const uint16_t* hidden_bf16, const int64_t* targets, int T, float eps, float* nll) {
   return rms_lmhead_nll(*static_cast<LmHead*>(h), hidden_bf16, targets, T, eps, nll);
 }

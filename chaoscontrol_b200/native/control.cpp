@@ -76,37 +76,65 @@ void softmax_row(float* row, std::size_t n) {
 }
 }  // namespace
 
+void SimplexWeights::resize() {
+  W_vp.assign(static_cast<std::size_t>(K_v) * H, 0.f);
+  b_vp.assign(H, 0.f);
+  W_lh.assign(H, 0.f);
+  W_sb.assign(K_s, 0.f);
+  const std::size_t hh = static_cast<std::size_t>(n_heads) * H * H;
+  W_q.assign(hh, 0.f); W_k.assign(hh, 0.f); W_v.assign(hh, 0.f);
+  W_o.assign(static_cast<std::size_t>(n_heads) * H, 0.f);
+  W_e.assign(static_cast<std::size_t>(n_heads) * K_e, 0.f);
+  bucket_embed.assign(static_cast<std::size_t>(n_buckets) * embed_dim, 0.f);
+}
+namespace {
+inline void put(float*& o, const std::vector<float>& v) { std::memcpy(o, v.data(), v.size() * 4); o += v.size(); }
+inline void get(const float*& i, std::vector<float>& v) { std::memcpy(v.data(), i, v.size() * 4); i += v.size(); }
+}  // namespace
 void SimplexWeights::to_flat(float* out) const {
-  std::size_t o = 0;
-  std::memcpy(out + o, W_vp.data(), W_vp.size() * 4); o += W_vp.size();
-  std::memcpy(out + o, b_vp.data(), b_vp.size() * 4); o += b_vp.size();
-  std::memcpy(out + o, W_lh.data(), W_lh.size() * 4); o += W_lh.size();
-  out[o++] = b_lh;
-  std::memcpy(out + o, W_sb.data(), W_sb.size() * 4); o += W_sb.size();
-  out[o++] = alpha;
+  float* o = out;
+  put(o, W_vp); put(o, b_vp); put(o, W_lh);
+  *o++ = b_lh;
+  put(o, W_sb);
+  *o++ = alpha;
+  if (n_heads) {
+    *o++ = lambda_hxh;
+    put(o, W_q); put(o, W_k); put(o, W_v); put(o, W_o); put(o, W_e);
+  }
+  put(o, bucket_embed);
 }
 void SimplexWeights::from_flat(const float* in) {
-  std::size_t o = 0;
-  std::memcpy(W_vp.data(), in + o, W_vp.size() * 4); o += W_vp.size();
-  std::memcpy(b_vp.data(), in + o, b_vp.size() * 4); o += b_vp.size();
-  std::memcpy(W_lh.data(), in + o, W_lh.size() * 4); o += W_lh.size();
-  b_lh = in[o++];
-  std::memcpy(W_sb.data(), in + o, W_sb.size() * 4); o += W_sb.size();
-  alpha = in[o++];
+  const float* i = in;
+  get(i, W_vp); get(i, b_vp); get(i, W_lh);
+  b_lh = *i++;
+  get(i, W_sb);
+  alpha = *i++;
+  if (n_heads) {
+    lambda_hxh = *i++;
+    get(i, W_q); get(i, W_k); get(i, W_v); get(i, W_o); get(i, W_e);
+  }
+  get(i, bucket_embed);
 }
 std::string SimplexWeights::validate() const {
-  if (N == 0 || K_v == 0 || K_s == 0 || H == 0) return "simplex dims must be positive";
+  if (N == 0 || K_v == 0 || K_s == 0 || H == 0 || K_e == 0) return "simplex dims must be positive";
   if (!(temperature > 0.f)) return "temperature must be positive";
   if (W_vp.size() != static_cast<std::size_t>(K_v) * H) return "W_vp must have K_v*H elements";
   if (b_vp.size() != H) return "b_vp must have H elements";
   if (W_lh.size() != H) return "W_lh must have H elements";
   if (W_sb.size() != K_s) return "W_sb must have K_s elements";
+  const std::size_t hh = static_cast<std::size_t>(n_heads) * H * H;
+  if (n_heads == 0 && lambda_hxh != 0.f) return "n_heads must be positive when lambda_hxh != 0";
+  if (W_q.size() != hh || W_k.size() != hh || W_v.size() != hh) return "W_q / W_k / W_v must have n_heads*H*H elements";
+  if (W_o.size() != static_cast<std::size_t>(n_heads) * H) return "W_o must have n_heads*H elements";
+  if (W_e.size() != static_cast<std::size_t>(n_heads) * K_e) return "W_e must have n_heads*K_e elements";
+  if (bucket_embed.size() != static_cast<std::size_t>(n_buckets) * embed_dim)
+    return "bucket_embed must have n_buckets*embed_dim elements";
   return "";
 }
 
 SimplexForward simplex_forward(const SimplexWeights& w, const float* V, const float* E,
                                const float* feats) {
-  const std::size_t N = w.N, H = w.H, Kv = w.K_v;
+  const std::size_t N = w.N, H = w.H, Kv = w.K_v, Ke = w.K_e;
   SimplexForward f;
   f.pre.assign(N * H, 0.f);
   f.vertex_h.resize(N * H);
@@ -130,7 +158,7 @@ SimplexForward simplex_forward(const SimplexWeights& w, const float* V, const fl
     for (std::size_t j = 0; j < N; ++j) {
       float dot = 0.f;
       for (std::size_t h = 0; h < H; ++h) dot += f.vertex_h[i * H + h] * f.vertex_h[j * H + h];
-      arow[j] = dot * scale + w.alpha * E[i * N + j];
+      arow[j] = dot * scale + w.alpha * E[(i * N + j) * Ke];
     }
     softmax_row(arow, N);
   }
@@ -145,6 +173,52 @@ SimplexForward simplex_forward(const SimplexWeights& w, const float* V, const fl
     for (std::size_t h = 0; h < H; ++h) lg += mrow[h] * w.W_lh[h];
     f.logits[i] = lg;
   }
+  // residual branch: per head, attention over the vertices with learned projections
+  const std::size_t nh = w.n_heads;
+  f.logits_hxh.assign(N, 0.f);
+  if (nh) {
+    f.hq.assign(nh * N * H, 0.f); f.hk.assign(nh * N * H, 0.f); f.hv.assign(nh * N * H, 0.f);
+    f.hmixed.assign(nh * N * H, 0.f);
+    f.hattn.assign(nh * N * N, 0.f);
+    const float inv_heads = 1.f / static_cast<float>(nh);
+    for (std::size_t hd = 0; hd < nh; ++hd) {
+      const float *Wq = w.W_q.data() + hd * H * H, *Wk = w.W_k.data() + hd * H * H, *Wv = w.W_v.data() + hd * H * H;
+      float *q = f.hq.data() + hd * N * H, *k = f.hk.data() + hd * N * H, *v = f.hv.data() + hd * N * H;
+      for (std::size_t i = 0; i < N; ++i)
+        for (std::size_t a = 0; a < H; ++a) {
+          const float x = f.vertex_h[i * H + a];
+          const float *rq = Wq + a * H, *rk = Wk + a * H, *rv = Wv + a * H;
+          for (std::size_t o = 0; o < H; ++o) {
+            q[i * H + o] += x * rq[o];
+            k[i * H + o] += x * rk[o];
+            v[i * H + o] += x * rv[o];
+          }
+        }
+      float* at = f.hattn.data() + hd * N * N;
+      const float* We = w.W_e.data() + hd * Ke;
+      for (std::size_t i = 0; i < N; ++i) {
+        for (std::size_t j = 0; j < N; ++j) {
+          float dot = 0.f, eb = 0.f;
+          for (std::size_t o = 0; o < H; ++o) dot += q[i * H + o] * k[j * H + o];
+          for (std::size_t e = 0; e < Ke; ++e) eb += We[e] * E[(i * N + j) * Ke + e];
+          at[i * N + j] = dot * scale + eb;
+        }
+        softmax_row(at + i * N, N);
+      }
+      float* mx = f.hmixed.data() + hd * N * H;
+      const float* Wo = w.W_o.data() + hd * H;
+      for (std::size_t i = 0; i < N; ++i) {
+        for (std::size_t j = 0; j < N; ++j) {
+          const float a = at[i * N + j];
+          for (std::size_t o = 0; o < H; ++o) mx[i * H + o] += a * v[j * H + o];
+        }
+        float lg = 0.f;
+        for (std::size_t o = 0; o < H; ++o) lg += mx[i * H + o] * Wo[o];
+        f.logits_hxh[i] += lg * inv_heads;
+      }
+    }
+    for (std::size_t i = 0; i < N; ++i) f.logits[i] += w.lambda_hxh * f.logits_hxh[i];
+  }
   float bias = 0.f;
   for (std::size_t k = 0; k < w.K_s; ++k) bias += w.W_sb[k] * feats[k];
   f.simplex_bias = bias;
@@ -153,16 +227,65 @@ SimplexForward simplex_forward(const SimplexWeights& w, const float* V, const fl
   return f;
 }
 
+void forward_pretrain_model(const PretrainModel& m, const float* x, std::size_t B, float* logits_out,
+                            float* value_out) {
+  const std::size_t F = m.F, Dg = m.Dg, L = m.L, Ds = m.Ds;
+  std::vector<float> h(Dg), t(Dg);
+  for (std::size_t b = 0; b < B; ++b) {
+    const float* xr = x + b * F;
+    for (std::size_t o = 0; o < Dg; ++o) {
+      float acc = m.in_b[o];
+      const float* wr = m.in_w + o * F;
+      for (std::size_t k = 0; k < F; ++k) acc += xr[k] * wr[k];
+      h[o] = acc;
+    }
+    for (std::size_t l = 0; l < L; ++l) {
+      const float *dec = m.decay + l * Dg, *wi = m.w_in + l * Dg * Dg, *wo = m.w_out + l * Dg * Dg,
+                  *bs = m.bias + l * Dg;
+      for (std::size_t o = 0; o < Dg; ++o) t[o] = h[o] * dec[o] + bs[o];
+      for (std::size_t k = 0; k < Dg; ++k) {                     // + h @ w_in (w_in is [in, out])
+        const float hk = h[k];
+        const float* wr = wi + k * Dg;
+        for (std::size_t o = 0; o < Dg; ++o) t[o] += hk * wr[o];
+      }
+      for (std::size_t o = 0; o < Dg; ++o) t[o] = gelu(t[o]);
+      std::fill(h.begin(), h.end(), 0.f);
+      for (std::size_t k = 0; k < Dg; ++k) {                     // @ w_out
+        const float tk = t[k];
+        const float* wr = wo + k * Dg;
+        for (std::size_t o = 0; o < Dg; ++o) h[o] += tk * wr[o];
+      }
+    }
+    for (std::size_t s = 0; s < Ds; ++s) {
+      float acc = m.pol_b[s];
+      const float* wr = m.pol_w + s * Dg;
+      for (std::size_t k = 0; k < Dg; ++k) acc += h[k] * wr[k];
+      logits_out[b * Ds + s] = acc;
+    }
+    float v = m.val_b[0];
+    for (std::size_t k = 0; k < Dg; ++k) v += h[k] * m.val_w[k];
+    value_out[b] = v;
+  }
+}
+
 void simplex_backward(const SimplexWeights& w, const SimplexForward& f, const float* V, const float* E,
                       const float* feats, uint32_t chosen, float advantage, float entropy_beta,
                       float* grad) {
-  const std::size_t N = w.N, H = w.H, Kv = w.K_v, Ks = w.K_s;
+  const std::size_t N = w.N, H = w.H, Kv = w.K_v, Ks = w.K_s, Ke = w.K_e, nh = w.n_heads;
   float* gW_vp = grad;
   float* gb_vp = gW_vp + Kv * H;
   float* gW_lh = gb_vp + H;
   float* gb_lh = gW_lh + H;
   float* gW_sb = gb_lh + 1;
   float* galpha = gW_sb + Ks;
+  // residual-branch block of the flat layout (present when n_heads > 0); the bucket embedding that
+  // follows it takes no gradient (the forward does not read it)
+  float* glambda = galpha + 1;
+  float* gW_q = glambda + 1;
+  float* gW_k = gW_q + nh * H * H;
+  float* gW_v = gW_k + nh * H * H;
+  float* gW_o = gW_v + nh * H * H;
+  float* gW_e = gW_o + nh * H;
 
   // loss = -adv * log p[c] - beta * H(p);  z = (logits + bias) / T
   double ent = 0.0;
@@ -201,12 +324,67 @@ void simplex_backward(const SimplexWeights& w, const SimplexForward& f, const fl
     }
     for (std::size_t j = 0; j < N; ++j) {
       ds[j] = f.attn[i * N + j] * (dA[j] - dotA);
-      *galpha += ds[j] * E[i * N + j];
+      *galpha += ds[j] * E[(i * N + j) * Ke];
       const float g = ds[j] * scale;
       for (std::size_t h = 0; h < H; ++h) {
         dvh[i * H + h] += g * f.vertex_h[j * H + h];
         dvh[j * H + h] += g * f.vertex_h[i * H + h];
       }
+    }
+  }
+  if (nh) {
+    // d logits[i] / d logits_hxh[i] = lambda; every head contributes out_i / n_heads
+    const float inv_heads = 1.f / static_cast<float>(nh);
+    for (std::size_t i = 0; i < N; ++i) *glambda += dlogit[i] * f.logits_hxh[i];
+    std::vector<float> dmx(N * H), dq(N * H), dk(N * H), dv(N * H), dat(N);
+    for (std::size_t hd = 0; hd < nh; ++hd) {
+      const float *Wq = w.W_q.data() + hd * H * H, *Wk = w.W_k.data() + hd * H * H, *Wv = w.W_v.data() + hd * H * H;
+      const float *Wo = w.W_o.data() + hd * H;
+      const float *q = f.hq.data() + hd * N * H, *k = f.hk.data() + hd * N * H, *v = f.hv.data() + hd * N * H;
+      const float *mx = f.hmixed.data() + hd * N * H, *at = f.hattn.data() + hd * N * N;
+      std::fill(dq.begin(), dq.end(), 0.f);
+      std::fill(dk.begin(), dk.end(), 0.f);
+      std::fill(dv.begin(), dv.end(), 0.f);
+      for (std::size_t i = 0; i < N; ++i) {
+        const float g = dlogit[i] * w.lambda_hxh * inv_heads;
+        for (std::size_t o = 0; o < H; ++o) {
+          gW_o[hd * H + o] += g * mx[i * H + o];
+          dmx[i * H + o] = g * Wo[o];
+        }
+      }
+      for (std::size_t i = 0; i < N; ++i) {
+        float dot = 0.f;
+        for (std::size_t j = 0; j < N; ++j) {
+          float d = 0.f;
+          for (std::size_t o = 0; o < H; ++o) d += dmx[i * H + o] * v[j * H + o];
+          dat[j] = d;
+          dot += at[i * N + j] * d;
+          const float a = at[i * N + j];
+          for (std::size_t o = 0; o < H; ++o) dv[j * H + o] += a * dmx[i * H + o];
+        }
+        for (std::size_t j = 0; j < N; ++j) {
+          const float dsc = at[i * N + j] * (dat[j] - dot);        // d score[i, j]
+          for (std::size_t e = 0; e < Ke; ++e) gW_e[hd * Ke + e] += dsc * E[(i * N + j) * Ke + e];
+          const float gs = dsc * scale;
+          for (std::size_t o = 0; o < H; ++o) {
+            dq[i * H + o] += gs * k[j * H + o];
+            dk[j * H + o] += gs * q[i * H + o];
+          }
+        }
+      }
+      // q = vh @ W_q (and k, v alike): weight gradients, and the branch's gradient into vertex_h
+      for (std::size_t i = 0; i < N; ++i)
+        for (std::size_t a = 0; a < H; ++a) {
+          const float x = f.vertex_h[i * H + a];
+          float acc = 0.f;
+          for (std::size_t o = 0; o < H; ++o) {
+            gW_q[hd * H * H + a * H + o] += x * dq[i * H + o];
+            gW_k[hd * H * H + a * H + o] += x * dk[i * H + o];
+            gW_v[hd * H * H + a * H + o] += x * dv[i * H + o];
+            acc += dq[i * H + o] * Wq[a * H + o] + dk[i * H + o] * Wk[a * H + o] + dv[i * H + o] * Wv[a * H + o];
+          }
+          dvh[i * H + a] += acc;
+        }
     }
   }
   for (std::size_t i = 0; i < N; ++i) {

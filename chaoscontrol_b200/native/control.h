@@ -78,7 +78,26 @@ struct SimplexWeights {
   std::vector<float> W_sb;   // [K_s]
   float alpha = 0.f;         // edge-vs-content mixing
   float temperature = 1.f;
-  std::size_t flat_size() const { return W_vp.size() + b_vp.size() + W_lh.size() + 1 + W_sb.size() + 1; }
+  // Optional residual branch: n_heads attention heads over the N vertices with learned H x H
+  // query / key / value projections and a per-head edge-feature bias; each head emits one logit
+  // per vertex (W_o), the heads are averaged and lambda_hxh scales the sum into the base logits
+  // (simplex_policy.h:27-53 of the reference).  n_heads == 0 leaves the base policy untouched.
+  uint32_t n_heads = 0;
+  float lambda_hxh = 0.f;
+  std::vector<float> W_q, W_k, W_v;   // [n_heads, H, H] each, row-major (out = in @ W)
+  std::vector<float> W_o;             // [n_heads, H]
+  std::vector<float> W_e;             // [n_heads, K_e]
+  // Write-bucket embedding table: carried by the weight file and the learner state, not read by
+  // the forward pass (as in the reference's current policy).
+  uint32_t n_buckets = 0, embed_dim = 0;
+  std::vector<float> bucket_embed;    // [n_buckets, embed_dim]
+  // flat layout: W_vp | b_vp | W_lh | b_lh | W_sb | alpha | [lambda | W_q | W_k | W_v | W_o | W_e] | bucket_embed
+  std::size_t flat_size() const {
+    return W_vp.size() + b_vp.size() + W_lh.size() + 1 + W_sb.size() + 1 +
+           (n_heads ? 1 + W_q.size() + W_k.size() + W_v.size() + W_o.size() + W_e.size() : 0) +
+           bucket_embed.size();
+  }
+  void resize();                    // allocate every vector from the dims
   void to_flat(float* out) const;
   void from_flat(const float* in);
   std::string validate() const;     // empty when consistent
@@ -88,17 +107,34 @@ struct SimplexForward {
   std::vector<float> vertex_h; // [N, H] gelu(pre)
   std::vector<float> attn;     // [N, N] row softmax
   std::vector<float> mixed_h;  // [N, H] attn @ vertex_h + vertex_h
-  std::vector<float> logits;   // [N]
+  std::vector<float> logits;   // [N] (residual branch included)
   std::vector<float> p;        // [N] softmax((logits + bias) / T)
   float simplex_bias = 0.f;
+  // residual branch, saved for backward
+  std::vector<float> hq, hk, hv, hmixed;   // [n_heads, N, H]
+  std::vector<float> hattn;                // [n_heads, N, N]
+  std::vector<float> logits_hxh;           // [N] before lambda
 };
-// V: [N, K_v]; E: [N, N] edge features; feats: [K_s].
+// V: [N, K_v]; E: [N, N, K_e] edge features (the base mixing reads feature 0); feats: [K_s].
 SimplexForward simplex_forward(const SimplexWeights& w, const float* V, const float* E, const float* feats);
 // Accumulates d(-advantage * log p[chosen] - entropy_beta * H(p)) / d weights into `grad`
 // (same flat layout as SimplexWeights::to_flat).
 void simplex_backward(const SimplexWeights& w, const SimplexForward& f, const float* V, const float* E,
                       const float* feats, uint32_t chosen, float advantage, float entropy_beta,
                       float* grad);
+
+// ---------------------------------------------------- pretrain model ----
+// Forward of the controller's offline-pretrained trunk (cpu_ssm_controller.cpp:309-355 of the
+// reference): h = x W_in^T + b; per layer h = gelu(h * decay_l + h @ w_in_l + bias_l) @ w_out_l;
+// logits = h W_p^T + b_p, value = h w_v + b_v.  x: [B, F]; logits_out: [B, D_slot]; value_out: [B].
+struct PretrainModel {
+  uint32_t F = 0, Dg = 0, L = 0, Ds = 0;
+  const float *in_w = nullptr, *in_b = nullptr;          // [Dg, F], [Dg]
+  const float *decay = nullptr, *w_in = nullptr, *w_out = nullptr, *bias = nullptr;   // [L,Dg] [L,Dg,Dg] [L,Dg,Dg] [L,Dg]
+  const float *pol_w = nullptr, *pol_b = nullptr, *val_w = nullptr, *val_b = nullptr; // [Ds,Dg] [Ds] [Dg] [1]
+};
+void forward_pretrain_model(const PretrainModel& m, const float* x, std::size_t B, float* logits_out,
+                            float* value_out);
 
 // -------------------------------------------------------- online learner ----
 struct ActionRecord {

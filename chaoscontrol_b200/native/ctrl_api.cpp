@@ -151,6 +151,65 @@ int ccbc_simplex_grad(int N, int Kv, int Ks, int H, float temperature, const flo
   return 0;
 }
 
+// Extended policy: K_e edge features per pair, n_heads residual attention heads, a stored bucket
+// embedding.  With n_heads == n_buckets == 0 and K_e == 1 the flat layout equals the base one.
+static SimplexWeights make_weights_ex(int N, int Kv, int Ke, int Ks, int H, int n_heads, int n_buckets,
+                                      int embed_dim, float temperature, const float* flat) {
+  SimplexWeights w;
+  w.N = N; w.K_v = Kv; w.K_e = Ke; w.K_s = Ks; w.H = H; w.temperature = temperature;
+  w.n_heads = n_heads; w.n_buckets = n_buckets; w.embed_dim = embed_dim;
+  w.resize();
+  if (flat) w.from_flat(flat);
+  return w;
+}
+int64_t ccbc_simplex_flat_size_ex(int Kv, int Ke, int Ks, int H, int n_heads, int n_buckets, int embed_dim) {
+  return (int64_t)make_weights_ex(1, Kv, Ke, Ks, H, n_heads, n_buckets, embed_dim, 1.f, nullptr).flat_size();
+}
+int ccbc_simplex_forward_ex(int N, int Kv, int Ke, int Ks, int H, int n_heads, int n_buckets, int embed_dim,
+                            float temperature, const float* flat, const float* V, const float* E,
+                            const float* feats, float* p_out, float* logits_out, float* logits_hxh_out) {
+  SimplexWeights w = make_weights_ex(N, Kv, Ke, Ks, H, n_heads, n_buckets, embed_dim, temperature, flat);
+  std::string e = w.validate();
+  if (!e.empty()) return fail(e);
+  SimplexForward f = simplex_forward(w, V, E, feats);
+  std::memcpy(p_out, f.p.data(), sizeof(float) * N);
+  if (logits_out) std::memcpy(logits_out, f.logits.data(), sizeof(float) * N);
+  if (logits_hxh_out) std::memcpy(logits_hxh_out, f.logits_hxh.data(), sizeof(float) * N);
+  return 0;
+}
+int ccbc_simplex_grad_ex(int N, int Kv, int Ke, int Ks, int H, int n_heads, int n_buckets, int embed_dim,
+                         float temperature, const float* flat, const float* V, const float* E,
+                         const float* feats, int chosen, float advantage, float entropy_beta, float* grad_out) {
+  SimplexWeights w = make_weights_ex(N, Kv, Ke, Ks, H, n_heads, n_buckets, embed_dim, temperature, flat);
+  std::string e = w.validate();
+  if (!e.empty()) return fail(e);
+  SimplexForward f = simplex_forward(w, V, E, feats);
+  std::memset(grad_out, 0, sizeof(float) * w.flat_size());
+  simplex_backward(w, f, V, E, feats, (uint32_t)chosen, advantage, entropy_beta, grad_out);
+  return 0;
+}
+// Offline-pretrained controller trunk: logits [B, Ds] and value [B] from features [B, F].
+int ccbc_forward_pretrain_model(int B, int F, int Dg, int L, int Ds, const float* x, const float* in_w,
+                                const float* in_b, const float* decay, const float* w_in, const float* w_out,
+                                const float* bias, const float* pol_w, const float* pol_b, const float* val_w,
+                                const float* val_b, float* logits_out, float* value_out) {
+  if (B <= 0 || F <= 0 || Dg <= 0 || L < 0 || Ds <= 0) return fail("forward_pretrain_model: bad dims");
+  PretrainModel m;
+  m.F = F; m.Dg = Dg; m.L = L; m.Ds = Ds;
+  m.in_w = in_w; m.in_b = in_b; m.decay = decay; m.w_in = w_in; m.w_out = w_out; m.bias = bias;
+  m.pol_w = pol_w; m.pol_b = pol_b; m.val_w = val_w; m.val_b = val_b;
+  forward_pretrain_model(m, x, (size_t)B, logits_out, value_out);
+  return 0;
+}
+int ccbc_learner_init_ex(void* l, int N, int Kv, int Ke, int Ks, int H, int n_heads, int n_buckets, int embed_dim,
+                         float temperature, const float* flat) {
+  SimplexWeights w = make_weights_ex(N, Kv, Ke, Ks, H, n_heads, n_buckets, embed_dim, temperature, flat);
+  std::string e = w.validate();
+  if (!e.empty()) return fail(e);
+  static_cast<SimplexOnlineLearner*>(l)->initialize(w);
+  return 0;
+}
+
 // ---- online learner ------------------------------------------------------------
 void* ccbc_learner_new(int num_slots, int max_entries, float gamma, float lr, int sgd_interval,
                        float ema_alpha, int64_t ema_interval, float gerber_c, float entropy_beta) {

@@ -144,6 +144,77 @@ __attribute__((target("amx-tile,amx-bf16,avx512f"))) static void bf16_matmul_amx
   _tile_release();
 }
 
+// ---- VNNI-packed weight cache + fused logits / online log-sum-exp on AMX -------------------------
+// (Reference: amx_matmul.cpp:231-251 packs the LM-head weight once, :384-624 fuses RMSNorm -> head ->
+// NLL over it.)  The head weight W [V, D] is the B operand W^T of logits = xn @ W^T.  tdpbf16ps wants
+// B tiles of 16 K-pairs x 16 columns with the two K values of a pair interleaved; packing it per call
+// costs more than the tile multiply, so it is done ONCE per weight:
+//   packed[((nt * kblocks + kb) * 16 + kp) * 32 + 2 * j + t] = W[(16 nt + j) * D + 32 kb + 2 kp + t]
+// (zero past V or D).  A tiles are loaded straight from the normalised activations with their row
+// stride, so the hot loop is two tile loads and one tdpbf16ps per 16 x 16 x 32 block; each finished
+// 16-token x 16-vocabulary tile updates the tokens' running (max, sum) and picks up target logits.
+void pack_vnni_wt(const uint16_t* W, int V, int D, std::vector<uint16_t>* out) {
+  const int ntiles = (V + 15) / 16, kblocks = (D + 31) / 32;
+  out->assign((size_t)ntiles * kblocks * 512, 0);
+  for (int nt = 0; nt < ntiles; ++nt)
+    for (int kb = 0; kb < kblocks; ++kb) {
+      uint16_t* tile = out->data() + ((size_t)nt * kblocks + kb) * 512;
+      for (int kp = 0; kp < 16; ++kp)
+        for (int j = 0; j < 16; ++j)
+          for (int t = 0; t < 2; ++t) {
+            const int v = nt * 16 + j, k = kb * 32 + 2 * kp + t;
+            if (v < V && k < D) tile[kp * 32 + 2 * j + t] = W[(size_t)v * D + k];
+          }
+    }
+}
+
+// xn: [Tpad, Dpad] bf16, Tpad a multiple of 16 and Dpad of 32 (zero padded).  run_m / run_s / tgt: [T].
+__attribute__((target("amx-tile,amx-bf16,avx512f"))) static void lse_over_vnni_amx(
+    const uint16_t* xn, int T, int Tpad, int Dpad, const uint16_t* packed, int V, const int64_t* targets,
+    float* run_m, float* run_s, float* tgt) {
+  TileConfig cfg;
+  cfg.rows[0] = 16; cfg.colsb[0] = 64;
+  cfg.rows[1] = 16; cfg.colsb[1] = 64;
+  cfg.rows[2] = 16; cfg.colsb[2] = 64;
+  _tile_loadconfig(&cfg);
+  const int ntiles = (V + 15) / 16, kblocks = Dpad / 32;
+  alignas(64) float c_tile[16 * 16];
+  for (int m0 = 0; m0 < Tpad; m0 += 16) {
+    for (int nt = 0; nt < ntiles; ++nt) {
+      _tile_zero(0);
+      const uint16_t* bt = packed + (size_t)nt * kblocks * 512;
+      for (int kb = 0; kb < kblocks; ++kb) {
+        _tile_loadd(1, xn + (size_t)m0 * Dpad + kb * 32, Dpad * 2);
+        _tile_loadd(2, bt + (size_t)kb * 512, 64);
+        _tile_dpbf16ps(0, 1, 2);
+      }
+      _tile_stored(0, c_tile, 64);
+      const int v0 = nt * 16, nv = V - v0 < 16 ? V - v0 : 16;
+      for (int i = 0; i < 16 && m0 + i < T; ++i) {
+        const int t = m0 + i;
+        const float* row = c_tile + i * 16;
+        float m = run_m[t];
+        for (int j = 0; j < nv; ++j) m = row[j] > m ? row[j] : m;
+        float sum = run_s[t] * __builtin_expf(run_m[t] - m);
+        for (int j = 0; j < nv; ++j) sum += __builtin_expf(row[j] - m);
+        run_m[t] = m;
+        run_s[t] = sum;
+        const int64_t y = targets[t];
+        if (y >= v0 && y < v0 + nv) tgt[t] = row[y - v0];
+      }
+    }
+  }
+  _tile_release();
+}
+
+// returns 1 when the AMX path ran (and filled the outputs), 0 when the CPU has no usable AMX
+int lse_over_vnni(const uint16_t* xn, int T, int Tpad, int Dpad, const uint16_t* packed, int V,
+                  const int64_t* targets, float* run_m, float* run_s, float* tgt) {
+  if (!cpu_features().amx_enabled) return 0;
+  lse_over_vnni_amx(xn, T, Tpad, Dpad, packed, V, targets, run_m, run_s, tgt);
+  return 1;
+}
+
 // returns 1 when the AMX path ran, 0 for the scalar path
 int bf16_matmul(const uint16_t* A, const uint16_t* B, float* C, int M, int N, int K) {
   if (cpu_features().amx_enabled) {

@@ -52,6 +52,27 @@ def test_fused_cpu_nll_matches_torch():
     head.close()
 
 
+@pytest.mark.parametrize("T,D,V", [(37, 64, 700), (16, 384, 4099), (5, 40, 33)])
+def test_packed_amx_nll_agrees_with_the_generic_path_and_torch(T, D, V):
+    """The VNNI-packed fused path (AMX CPUs) against the generic tile-matmul path and the fp32
+    statement, with token counts / model dims / vocabularies that are not multiples of the tile."""
+    torch.manual_seed(2)
+    hidden = torch.randn(T, D).bfloat16()
+    W = (torch.randn(V, D) * 0.2).bfloat16()
+    nw = torch.rand(D) + 0.5
+    y = torch.randint(0, V, (T,))
+    head = A.PackedLmHead(nw, W)
+    fused, used = A.rms_lmhead_nll(head, hidden, y)
+    generic, _ = A.rms_lmhead_nll(head, hidden, y, packed_amx=False)
+    xn = (F.rms_norm(hidden.float(), (D,), eps=1e-6) * nw).bfloat16().float()
+    ref = F.cross_entropy(xn @ W.float().t(), y, reduction="none")
+    assert torch.allclose(fused, generic, atol=1e-3, rtol=1e-3), (fused - generic).abs().max()
+    assert torch.allclose(fused, ref, atol=3e-3, rtol=3e-3), (fused - ref).abs().max()
+    if A.cpu_has_amx() if hasattr(A, "cpu_has_amx") else False:
+        assert used
+    head.close()
+
+
 def test_evidence_engine():
     torch.manual_seed(1)
     eng = A.CpuEvidenceEngine(lanes=2, d_model=32)

@@ -234,3 +234,94 @@ def test_controller_loop_drains_rings_and_feeds_learner():
         exit_flag.close(unlink=True)
         stats.close(unlink=True)
         L.close()
+
+
+# ---------------------------------------------------------------------------
+# residual attention heads + bucket embedding of the simplex policy, and the pretrain trunk
+# ---------------------------------------------------------------------------
+def _torch_policy_v3(pol, V, E, feats):
+    """Torch twin of the native forward on the same flat weights (differentiable)."""
+    import torch
+    N, Kv, Ke, Ks, H, nh = pol.N, pol.K_v, pol.K_e, pol.K_s, pol.H, pol.n_heads
+    flat = torch.tensor(pol.flat, dtype=torch.float64, requires_grad=True)
+    o = 0
+
+    def take(*shape):
+        nonlocal o
+        n = int(np.prod(shape)) if shape else 1
+        t = flat[o:o + n].reshape(shape) if shape else flat[o]
+        o += n
+        return t
+    W_vp, b_vp, W_lh, b_lh, W_sb, alpha = take(Kv, H), take(H), take(H), take(), take(Ks), take()
+    V, E, feats = (torch.tensor(np.asarray(a), dtype=torch.float64) for a in (V, E, feats))
+    E = E.reshape(N, N, Ke)
+    vh = torch.nn.functional.gelu(V @ W_vp + b_vp)
+    attn = torch.softmax(vh @ vh.T / H ** 0.5 + alpha * E[..., 0], dim=-1)
+    mixed = attn @ vh + vh
+    logits = mixed @ W_lh + b_lh
+    hxh = torch.zeros(N, dtype=torch.float64)
+    if nh:
+        lam = take()
+        Wq, Wk, Wv, Wo, We = take(nh, H, H), take(nh, H, H), take(nh, H, H), take(nh, H), take(nh, Ke)
+        for h in range(nh):
+            q, k, v = vh @ Wq[h], vh @ Wk[h], vh @ Wv[h]
+            a = torch.softmax(q @ k.T / H ** 0.5 + (E * We[h]).sum(-1), dim=-1)
+            hxh = hxh + ((a @ v) @ Wo[h]) / nh
+        logits = logits + lam * hxh
+    p = torch.softmax((logits + feats @ W_sb) / pol.temperature, dim=-1)
+    return flat, p, logits, hxh
+
+
+@pytest.mark.parametrize("n_heads,K_e", [(0, 1), (2, 3), (1, 1)])
+def test_simplex_policy_residual_heads_match_a_torch_twin(n_heads, K_e):
+    import torch
+    from chaoscontrol_b200.episodic.native import SimplexPolicyV3
+    rng = np.random.default_rng(5)
+    pol = SimplexPolicyV3(N=8, K_v=6, K_e=K_e, K_s=3, H=10, n_heads=n_heads, n_buckets=4, embed_dim=5,
+                          temperature=0.7, seed=3)
+    pol.flat *= 4.0
+    V, E, feats = rng.standard_normal((8, 6)), rng.standard_normal((8, 8, K_e)), rng.standard_normal(3)
+    p, logits, hxh = pol.forward(V, E, feats, with_branch=True)
+    flat, tp, tl, th = _torch_policy_v3(pol, V, E, feats)
+    assert np.allclose(p, tp.detach().numpy(), atol=2e-5) and np.allclose(logits, tl.detach().numpy(), atol=2e-4)
+    assert np.allclose(hxh, th.detach().numpy(), atol=2e-4)
+    if n_heads:
+        assert np.abs(hxh).max() > 1e-3                       # the branch is live
+    chosen, adv, beta = 3, 0.8, 0.05
+    loss = -adv * torch.log(tp[chosen]) + beta * (tp * torch.log(tp)).sum()      # -adv log p - beta H(p)
+    loss.backward()
+    g = pol.grad(V, E, feats, chosen, adv, beta)
+    ref = flat.grad.numpy()
+    assert np.allclose(g, ref, atol=3e-4, rtol=2e-3), np.abs(g - ref).max()
+    n_embed = 4 * 5
+    assert np.all(g[-n_embed:] == 0.0)                        # the stored embedding takes no gradient
+    # with no heads, one edge feature and no table the flat layout is the base policy's
+    if n_heads == 0:
+        from chaoscontrol_b200.episodic.native import SimplexPolicy
+        base = SimplexPolicy(N=8, K_v=6, K_s=3, H=10, temperature=0.7, seed=3)
+        assert base.flat.size == pol.flat.size - n_embed
+        base.flat[:] = pol.flat[: base.flat.size]
+        pb, lb = base.forward(V, E[..., 0], feats)
+        assert np.allclose(pb, p, atol=1e-6) and np.allclose(lb, logits, atol=1e-6)
+
+
+def test_forward_pretrain_model_matches_torch():
+    import torch
+    from chaoscontrol_b200.episodic.native import forward_pretrain_model
+    g = torch.Generator().manual_seed(0)
+    B, F, Dg, L, Ds = 5, 7, 12, 3, 4
+    w = {"trunk.in_proj.weight": torch.randn(Dg, F, generator=g) * 0.3, "trunk.in_proj.bias": torch.randn(Dg, generator=g) * 0.1,
+         "trunk.decay": torch.rand(L, Dg, generator=g), "trunk.w_in": torch.randn(L, Dg, Dg, generator=g) * 0.2,
+         "trunk.w_out": torch.randn(L, Dg, Dg, generator=g) * 0.3, "trunk.bias": torch.randn(L, Dg, generator=g) * 0.1,
+         "policy_head.weight": torch.randn(Ds, Dg, generator=g) * 0.3, "policy_head.bias": torch.randn(Ds, generator=g) * 0.1,
+         "value_head.weight": torch.randn(1, Dg, generator=g) * 0.3, "value_head.bias": torch.randn(1, generator=g) * 0.1}
+    x = torch.randn(B, F, generator=g)
+    h = x @ w["trunk.in_proj.weight"].T + w["trunk.in_proj.bias"]
+    for l in range(L):
+        h = torch.nn.functional.gelu(h * w["trunk.decay"][l] + h @ w["trunk.w_in"][l] + w["trunk.bias"][l]) @ w["trunk.w_out"][l]
+    ref_logits = h @ w["policy_head.weight"].T + w["policy_head.bias"]
+    ref_value = (h @ w["value_head.weight"].T + w["value_head.bias"]).squeeze(-1)
+    logits, value = forward_pretrain_model(x.numpy(), {k: v.numpy() for k, v in w.items()})
+    assert np.allclose(logits, ref_logits.numpy(), atol=1e-5) and np.allclose(value, ref_value.numpy(), atol=1e-5)
+    with pytest.raises(ValueError):
+        forward_pretrain_model(x.numpy()[:, :3], {k: v.numpy() for k, v in w.items()})

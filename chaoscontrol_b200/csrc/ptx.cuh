@@ -402,6 +402,24 @@ __device__ __forceinline__ float tanhf_fast(float x) {
 __device__ __forceinline__ float sigmoidf_fast(float x) {
   return fmaf(0.5f, tanhf_fast(0.5f * x), 0.5f);
 }
+// e^x for x <= 0 on the FMA pipe only (no special-function op): round-to-nearest split of x*log2(e)
+// with the 1.5*2^23 trick, a degree-6 polynomial for 2^f on [-0.5, 0.5] (truncation error 1.2e-7
+// relative) and the integer part added into the exponent field.  Inputs below -87 give 0.
+__device__ __forceinline__ float exp_nonpos_fma(float x) {
+  float t = fmaxf(x * 1.4426950408889634f, -126.f);
+  const float magic = 12582912.f;
+  const float r = t + magic;
+  const float f = t - (r - magic);
+  float p = 1.5403530e-4f;
+  p = fmaf(p, f, 1.3333558e-3f);
+  p = fmaf(p, f, 9.6181291e-3f);
+  p = fmaf(p, f, 5.5504109e-2f);
+  p = fmaf(p, f, 2.4022651e-1f);
+  p = fmaf(p, f, 6.9314718e-1f);
+  p = fmaf(p, f, 1.f);
+  const float y = __int_as_float(__float_as_int(p) + (__float_as_int(r) << 23));
+  return x < -87.f ? 0.f : y;
+}
 __device__ __forceinline__ float rcpf_fast(float x) {
   float y;
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

@@ -28,33 +28,39 @@ struct Gates {
   float decay, sel, cand, gate, sp_sig, delta;  // sp_sig = d softplus / d raw (0 when clamped)
 };
 
+// POLY: the two exponentials run on the FMA pipe (exp_nonpos_fma) instead of the special-function
+// unit, which the three tanh and the logarithm of every channel step already keep busy.
+template <bool POLY>
 __device__ __forceinline__ Gates eval_gates(float s_raw, float c_raw, float g_raw, float d_raw,
                                             float a) {
   Gates g;
   g.sel = sigmoidf_fast(s_raw);
   g.cand = tanhf_fast(c_raw);
   g.gate = sigmoidf_fast(g_raw);
-  const float e = __expf(-fabsf(d_raw));
+  const float e = POLY ? exp_nonpos_fma(-fabsf(d_raw)) : __expf(-fabsf(d_raw));
   float sp = fmaxf(d_raw, 0.f) + __logf(1.f + e);
   // d softplus / dx = sigmoid(x)
   const float inv1pe = rcpf_fast(1.f + e);
   const float sig = d_raw >= 0.f ? inv1pe : e * inv1pe;
   g.sp_sig = sp > 1e-4f ? sig : 0.f;
   g.delta = fmaxf(sp, 1e-4f);
-  g.decay = __expf(-g.delta * a);
+  g.decay = POLY ? exp_nonpos_fma(-g.delta * a) : __expf(-g.delta * a);
   return g;
 }
 
 // grid: (ceil(D/256), B); block: 128 threads, 2 channels per thread.
+template <bool POLY>
 __global__ void __launch_bounds__(SCAN_THREADS)
 scan_fwd_kernel(const __nv_bfloat16* __restrict__ P, long long ldp, const float* __restrict__ log_a,
                 const float* __restrict__ h0, __nv_bfloat16* __restrict__ y,
-                __nv_bfloat16* __restrict__ hout, float* __restrict__ hT, int T, int D) {
+                __nv_bfloat16* __restrict__ hout, float* __restrict__ hT, int T, int D,
+                long long la_bstride) {
   const int b = blockIdx.y;
   const int d = (blockIdx.x * SCAN_THREADS + threadIdx.x) * 2;
   if (d >= D) return;
-  const float a0 = sigmoidf_fast(log_a[d]);
-  const float a1 = sigmoidf_fast(log_a[d + 1]);
+  // la_bstride != 0: every batch row has its own decay vector (per-document test-time training)
+  const float a0 = sigmoidf_fast(log_a[b * la_bstride + d]);
+  const float a1 = sigmoidf_fast(log_a[b * la_bstride + d + 1]);
   float s0 = 0.f, s1 = 0.f;
   if (h0 != nullptr) {
     s0 = h0[(long long)b * D + d];
@@ -85,8 +91,8 @@ scan_fwd_kernel(const __nv_bfloat16* __restrict__ P, long long ldp, const float*
         const float2 cr = unpack_bf16x2(raw[u][1]);
         const float2 gr = unpack_bf16x2(raw[u][2]);
         const float2 dr = unpack_bf16x2(raw[u][3]);
-        const Gates g0 = eval_gates(sr.x, cr.x, gr.x, dr.x, a0);
-        const Gates g1 = eval_gates(sr.y, cr.y, gr.y, dr.y, a1);
+        const Gates g0 = eval_gates<POLY>(sr.x, cr.x, gr.x, dr.x, a0);
+        const Gates g1 = eval_gates<POLY>(sr.y, cr.y, gr.y, dr.y, a1);
         s0 = g0.decay * s0 + g0.sel * g0.cand;
         s1 = g1.decay * s1 + g1.sel * g1.cand;
         const long long o = (long long)(t0 + u) * dq;
@@ -106,18 +112,19 @@ scan_fwd_kernel(const __nv_bfloat16* __restrict__ P, long long ldp, const float*
 // gates.  Emits dP (optionally pre-multiplied by the consumer's RMSNorm row
 // scale rs[r] = rsqrt(rowss[r] * inv_dim + eps)), per-batch-row partials of
 // d log_a, and optionally d h0.
+template <bool POLY>
 __global__ void __launch_bounds__(SCAN_THREADS)
 scan_bwd_kernel(const __nv_bfloat16* __restrict__ P, long long ldp, const float* __restrict__ log_a,
                 const float* __restrict__ h0, const __nv_bfloat16* __restrict__ hstates,
                 const __nv_bfloat16* __restrict__ dy, const float* __restrict__ dhT,
                 const float* __restrict__ rowss, float inv_dim, float eps,
                 __nv_bfloat16* __restrict__ dP, long long lddp, float* __restrict__ dloga_part,
-                float* __restrict__ dh0, int T, int D) {
+                float* __restrict__ dh0, int T, int D, long long la_bstride) {
   const int b = blockIdx.y;
   const int d = (blockIdx.x * SCAN_THREADS + threadIdx.x) * 2;
   if (d >= D) return;
-  const float a0 = sigmoidf_fast(log_a[d]);
-  const float a1 = sigmoidf_fast(log_a[d + 1]);
+  const float a0 = sigmoidf_fast(log_a[b * la_bstride + d]);
+  const float a1 = sigmoidf_fast(log_a[b * la_bstride + d + 1]);
   const long long rowbase = (long long)b * T;
   const int dq = D / 2;
   const uint32_t* Pw = reinterpret_cast<const uint32_t*>(P + rowbase * ldp + d);
@@ -171,8 +178,8 @@ scan_bwd_kernel(const __nv_bfloat16* __restrict__ P, long long ldp, const float*
         } else {
           hprev = make_float2(0.f, 0.f);
         }
-        const Gates g0 = eval_gates(sr.x, cr.x, gr.x, dr.x, a0);
-        const Gates g1 = eval_gates(sr.y, cr.y, gr.y, dr.y, a1);
+        const Gates g0 = eval_gates<POLY>(sr.x, cr.x, gr.x, dr.x, a0);
+        const Gates g1 = eval_gates<POLY>(sr.y, cr.y, gr.y, dr.y, a1);
         // y = gate * h
         const float dgate0 = dyv.x * hcur.x, dgate1 = dyv.y * hcur.y;
         const float dh0_ = dyv.x * g0.gate + c0, dh1_ = dyv.y * g1.gate + c1;
@@ -274,15 +281,24 @@ plain_scan_bwd_kernel(const DT* __restrict__ decay, const float* __restrict__ st
 
 using namespace ccb;
 
+// 1: exponentials of the gate evaluation on the FMA pipe; 0: special-function unit.  Returns the old value.
+static int g_scan_poly_exp = 0;
+extern "C" int ccb_scan_poly_exp(int on) {
+  const int old = g_scan_poly_exp;
+  if (on == 0 || on == 1) g_scan_poly_exp = on;
+  return old;
+}
+
 extern "C" int ccb_scan_fwd(const void* P, int64_t ldp, const float* log_a, const float* h0,
                             void* y, void* hout, float* hT, int64_t B, int64_t T, int64_t D,
-                            void* stream) {
+                            int64_t la_bstride, void* stream) {
   if (B <= 0 || T <= 0) return 0;
   if (D % 8 != 0 || ldp % 2 != 0) return set_error("ccb_scan_fwd: D must be a multiple of 8");
   dim3 grid((unsigned)((D / 2 + SCAN_THREADS - 1) / SCAN_THREADS), (unsigned)B);
-  scan_fwd_kernel<<<grid, SCAN_THREADS, 0, (cudaStream_t)stream>>>(
+  auto kern = g_scan_poly_exp ? scan_fwd_kernel<true> : scan_fwd_kernel<false>;
+  kern<<<grid, SCAN_THREADS, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)P, ldp, log_a, h0, (__nv_bfloat16*)y, (__nv_bfloat16*)hout, hT, (int)T,
-      (int)D);
+      (int)D, (long long)la_bstride);
   count_launch();
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : set_error("scan_fwd launch: %s", cudaGetErrorString(e));
@@ -292,14 +308,15 @@ extern "C" int ccb_scan_bwd(const void* P, int64_t ldp, const float* log_a, cons
                             const void* hstates, const void* dy, const float* dhT,
                             const float* rowss, float inv_dim, float eps, void* dP, int64_t lddp,
                             float* dloga_part, float* dh0, int64_t B, int64_t T, int64_t D,
-                            void* stream) {
+                            int64_t la_bstride, void* stream) {
   if (B <= 0 || T <= 0) return 0;
   if (D % 8 != 0) return set_error("ccb_scan_bwd: D must be a multiple of 8");
   dim3 grid((unsigned)((D / 2 + SCAN_THREADS - 1) / SCAN_THREADS), (unsigned)B);
-  scan_bwd_kernel<<<grid, SCAN_THREADS, 0, (cudaStream_t)stream>>>(
+  auto kern = g_scan_poly_exp ? scan_bwd_kernel<true> : scan_bwd_kernel<false>;
+  kern<<<grid, SCAN_THREADS, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)P, ldp, log_a, h0, (const __nv_bfloat16*)hstates,
       (const __nv_bfloat16*)dy, dhT, rowss, inv_dim, eps, (__nv_bfloat16*)dP, lddp, dloga_part, dh0,
-      (int)T, (int)D);
+      (int)T, (int)D, (long long)la_bstride);
   count_launch();
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : set_error("scan_bwd launch: %s", cudaGetErrorString(e));

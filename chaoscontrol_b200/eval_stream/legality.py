@@ -28,8 +28,13 @@ def summed_ce(logits: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
 
 class LegalityController:
     def __init__(self, model: nn.Module, *, loss_fn: Callable = summed_ce, leak_detection: bool = False,
-                 cache=None, fingerprint_window: int = 4) -> None:
+                 cache=None, fingerprint_window: int = 4, last_token_is_target_only: bool = False) -> None:
+        """``last_token_is_target_only``: the caller's chunks overlap by one token (chunk ``k`` ends
+        with the token chunk ``k + 1`` starts with, so that every position of a document is a target
+        exactly once).  The model then reads all but the last token, and the returned final state has
+        seen every token once; without the flag a chunk is self-contained, as in the reference."""
         self.model = model
+        self.last_token_is_target_only = bool(last_token_is_target_only)
         self.loss_fn = loss_fn
         self.leak_detection = leak_detection
         self.cache = cache
@@ -52,9 +57,14 @@ class LegalityController:
 
     def _forward_loss(self, chunk: torch.Tensor, initial_states):
         kw = {"initial_states": initial_states} if initial_states else {}
-        out = self.model(chunk, **kw)
-        logits = out["logits"] if isinstance(out, dict) else out
-        loss = self.loss_fn(logits[:, :-1], chunk[:, 1:])
+        if self.last_token_is_target_only:
+            out = self.model(chunk[:, :-1], **kw)
+            logits = out["logits"] if isinstance(out, dict) else out
+            loss = self.loss_fn(logits, chunk[:, 1:])
+        else:
+            out = self.model(chunk, **kw)
+            logits = out["logits"] if isinstance(out, dict) else out
+            loss = self.loss_fn(logits[:, :-1], chunk[:, 1:])
         finals = list(out["final_states"]) if isinstance(out, dict) and "final_states" in out else []
         return loss, finals
 

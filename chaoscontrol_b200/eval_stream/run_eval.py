@@ -57,8 +57,8 @@ def _sha256(path: Path) -> Optional[str]:
 
 def run(cfg: RunConfig, *, val_cache_dir: Optional[str] = None, jsonl_paths: Optional[Sequence[str]] = None,
         sp_model_path: Optional[str] = None, model: Optional[torch.nn.Module] = None,
-        device: Optional[torch.device] = None, optimizer: str = "sgd", use_graph: Optional[bool] = None
-        ) -> dict[str, Any]:
+        device: Optional[torch.device] = None, optimizer: str = "sgd", use_graph: Optional[bool] = None,
+        batched: Optional[bool] = None) -> dict[str, Any]:
     from ..scoring import run_ttt_eval, run_ttt_eval_graph
     torch.manual_seed(cfg.seed)
     device = device or torch.device("cuda:0" if torch.cuda.is_available() else "cpu")
@@ -84,8 +84,17 @@ def run(cfg: RunConfig, *, val_cache_dir: Optional[str] = None, jsonl_paths: Opt
         use_graph = graph_ok
     if use_graph and not graph_ok:
         raise ValueError("the graph runner covers SGD, one step per chunk, reset persistence on a GPU only")
+    driver = None
     try:
-        if use_graph:
+        from .batched_ttt import SUPPORTED_ADAPT_SETS, BatchedTTT, run_ttt_eval_batched
+        if (use_graph and batched is not False and metrics is None and cfg.adapt_set in SUPPORTED_ADAPT_SETS
+                and BatchedTTT.supported(model)):
+            # many documents per step; per-document metric rows need the one-document-at-a-time drivers
+            out = run_ttt_eval_batched(model, docs, adapt_set=cfg.adapt_set, chunk_size=cfg.chunk_size,
+                                       eval_lr=cfg.eval_lr, max_docs=cfg.max_docs)
+            out.pop("runner", None)
+            driver = "batched"
+        elif use_graph:
             out = run_ttt_eval_graph(model, docs, adapt_set=cfg.adapt_set, chunk_size=cfg.chunk_size,
                                      eval_lr=cfg.eval_lr, max_docs=cfg.max_docs, metrics=metrics)
         else:
@@ -101,7 +110,7 @@ def run(cfg: RunConfig, *, val_cache_dir: Optional[str] = None, jsonl_paths: Opt
     summary = {k: v for k, v in out.items() if k != "per_doc_ce"}
     ck = Path(cfg.checkpoint_path) if cfg.checkpoint_path else None
     summary.update({
-        "driver": "graph" if use_graph else "eager", "config": asdict(cfg),
+        "driver": driver or ("graph" if use_graph else "eager"), "config": asdict(cfg),
         "ckpt_sha256": _sha256(ck) if ck else None,
         "ckpt_cfg_hash": hashlib.sha256(json.dumps(ckpt_cfg, sort_keys=True, default=str).encode()).hexdigest()[:16],
         "gpu_name": torch.cuda.get_device_name(device) if device.type == "cuda" else None,

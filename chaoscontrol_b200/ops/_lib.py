@@ -58,8 +58,9 @@ _SIGS = {
     "ccb_fp8_flush_amax": ([vp, i64, vp, vp, f32, vp], C.c_int),
     "ccb_pack_write_events": ([vp, vp, vp, vp, i64, vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, i64, i64, i64,
                                i64, vp], C.c_int),
-    "ccb_scan_fwd": ([vp, i64, vp, vp, vp, vp, vp, i64, i64, i64, vp], C.c_int),
-    "ccb_scan_bwd": ([vp, i64, vp, vp, vp, vp, vp, vp, f32, f32, vp, i64, vp, vp, i64, i64, i64, vp],
+    "ccb_scan_poly_exp": ([C.c_int], C.c_int),
+    "ccb_scan_fwd": ([vp, i64, vp, vp, vp, vp, vp, i64, i64, i64, i64, vp], C.c_int),
+    "ccb_scan_bwd": ([vp, i64, vp, vp, vp, vp, vp, vp, f32, f32, vp, i64, vp, vp, i64, i64, i64, i64, vp],
                      C.c_int),
     "ccb_plain_scan_fwd": ([vp, i64, vp, i64, vp, vp, i64, i64, i64, vp], C.c_int),
     "ccb_plain_scan_bwd": ([vp, i64, vp, vp, vp, i64, vp, vp, vp, i64, i64, i64, vp], C.c_int),

@@ -62,7 +62,7 @@ def general_row_chunk(R: int) -> int:
     return min(R, 128 * sms)
 
 
-def _train_general(x, rowss, W_f, t, gscale, rowweight, eps, lse):
+def _train_general(x, rowss, W_f, t, gscale, rowweight, eps, lse, want_dw=True):
     """Chunked LM-head backward from GEMM epilogues.  Per row chunk: ``g = (softmax - onehot) *
     scale`` is produced by the logits GEMM's epilogue as a bf16 ``[rows, V]`` tile (bounded by the
     chunk, never the full ``[R, V]``), then ``dX = RMSNorm-backward(g @ W')`` and
@@ -77,7 +77,7 @@ def _train_general(x, rowss, W_f, t, gscale, rowweight, eps, lse):
     nchunks = (R + rc - 1) // rc
     S = G.pick_splits(V, D, rc)
     dX = torch.empty_like(x)
-    part = torch.empty(nchunks * S, V, D, dtype=torch.float32, device=x.device)
+    part = torch.empty(nchunks * S, V, D, dtype=torch.float32, device=x.device) if want_dw else None
     gbuf = torch.empty(rc, V, dtype=torch.bfloat16, device=x.device)
     for i in range(nchunks):
         r0, r1 = i * rc, min(R, (i + 1) * rc)
@@ -91,6 +91,8 @@ def _train_general(x, rowss, W_f, t, gscale, rowweight, eps, lse):
                    out=dX[r0:r1])
         else:
             G.gemm(g, W_f, b_mn=True, out=dX[r0:r1])
+        if not want_dw:
+            continue
         Sc = min(S, G.pick_splits(V, D, r1 - r0))
         if Sc != S:
             part[i * S + Sc:(i + 1) * S].zero_()
@@ -219,8 +221,13 @@ ONE_SWEEP = True      # module switch: lse + dX in one vocabulary sweep (see lm_
 
 def lm_head_train(x, rowss, W_f, targets, *, gscale: float, rowweight=None, eps: float = EPS,
                   row_chunks: Optional[int] = None, lse: Optional[torch.Tensor] = None,
-                  one_sweep: Optional[bool] = None, allow_materialized: bool = False):
+                  one_sweep: Optional[bool] = None, allow_materialized: bool = False,
+                  want_dw: bool = True):
     """Loss and both gradients.  Returns ``(loss_rows, lse, dX bf16, dW_f_partials fp32 [C,V,D])``.
+
+    ``want_dw=False`` skips the weight-gradient kernel and returns ``None`` in its
+    place: test-time training adapts recurrence parameters only and needs ``dX``
+    alone.
 
     ``dX`` is the gradient w.r.t. the un-normalised hidden state (RMSNorm
     backward applied); the partials sum to the gradient w.r.t. ``W_f``.
@@ -237,7 +244,7 @@ def lm_head_train(x, rowss, W_f, targets, *, gscale: float, rowweight=None, eps:
     R, D = x.shape
     V = W_f.shape[0]
     if (not fused_supported(x, W_f) or (_few_rows(R) and one_sweep is None)) and general_supported(x, W_f):
-        return _train_general(x, rowss, W_f, _prep(x, rowss, W_f, targets), gscale, rowweight, eps, lse)
+        return _train_general(x, rowss, W_f, _prep(x, rowss, W_f, targets), gscale, rowweight, eps, lse, want_dw)
     if not fused_supported(x, W_f):
         _refuse_unless_allowed(x, W_f, allow_materialized, "lm_head_train")
         lr, lse, dX, dW = lm_head_reference(x, rowss, W_f, targets, gscale=gscale,
@@ -256,6 +263,8 @@ def lm_head_train(x, rowss, W_f, targets, *, gscale: float, rowweight=None, eps:
                                   1 if lse_given else (2 if (ONE_SWEEP if one_sweep is None else one_sweep) else 0),
                                   loss.data_ptr(), dX.data_ptr(), R, V, D, _lib.stream_ptr()),
                "lmhead_train")
+    if not want_dw:
+        return loss, lse, dX, None
     C = row_chunks or default_row_chunks(R, V)
     part = torch.empty(C, V, D, dtype=torch.float32, device=dev)
     _lib.check(L.ccb_lmhead_dw(x.data_ptr(), W_f.data_ptr(), _lib.ptr(rowss), eps, t.data_ptr(),

@@ -82,7 +82,8 @@ def scan_fused_reference(P: torch.Tensor, log_a: torch.Tensor, h0: Optional[torc
     """
     Pf = P.float().view(B, T, 4 * D)
     s_raw, c_raw, g_raw, d_raw = Pf.split(D, dim=-1)
-    a = torch.sigmoid(log_a.float())[None, None, :]
+    a = torch.sigmoid(log_a.float())
+    a = a[None, None, :] if a.dim() == 1 else a[:, None, :]      # shared, or one decay vector per batch row
     delta = F.softplus(d_raw).clamp_min(1e-4)
     decay = torch.exp(-delta * a)
     update = torch.sigmoid(s_raw) * torch.tanh(c_raw)
@@ -99,18 +100,28 @@ def scan_fused_reference(P: torch.Tensor, log_a: torch.Tensor, h0: Optional[torc
 # ---------------------------------------------------------------------------
 # fused CUDA scan
 # ---------------------------------------------------------------------------
+def _log_a_batch_stride(log_a: torch.Tensor, B: int, D: int) -> int:
+    if log_a.dim() == 1:
+        assert log_a.numel() == D and log_a.is_contiguous()
+        return 0
+    assert log_a.shape == (B, D) and log_a.stride(1) == 1, "per-row log_a must be [B, D]"
+    return int(log_a.stride(0))
+
+
 def scan_fused_fwd(P: torch.Tensor, log_a_f32: torch.Tensor, h0: Optional[torch.Tensor], B: int,
                    T: int, D: int, *, save_h: bool = True, want_hT: bool = True):
     """Launch ``scan_fwd_kernel``.  ``P`` bf16 ``[B*T, >=4D]`` (row stride free),
-    ``log_a_f32`` fp32 ``[D]``, ``h0`` fp32 ``[B, D]`` or None."""
+    ``log_a_f32`` fp32 ``[D]`` (shared) or ``[B, D]`` (one decay vector per batch
+    row), ``h0`` fp32 ``[B, D]`` or None."""
     assert P.dtype == torch.bfloat16 and log_a_f32.dtype == torch.float32
+    la_bs = _log_a_batch_stride(log_a_f32, B, D)
     y = torch.empty(B * T, D, dtype=torch.bfloat16, device=P.device)
     h = torch.empty(B * T, D, dtype=torch.bfloat16, device=P.device) if save_h else None
     hT = torch.empty(B, D, dtype=torch.float32, device=P.device) if want_hT else None
     if h0 is not None:
         assert h0.dtype == torch.float32 and h0.is_contiguous()
     _lib.check(_lib.lib().ccb_scan_fwd(P.data_ptr(), P.stride(0), log_a_f32.data_ptr(), _lib.ptr(h0),
-                                       y.data_ptr(), _lib.ptr(h), _lib.ptr(hT), B, T, D,
+                                       y.data_ptr(), _lib.ptr(h), _lib.ptr(hT), B, T, D, la_bs,
                                        _lib.stream_ptr()), "scan_fwd")
     return y, h, hT
 
@@ -119,11 +130,14 @@ def scan_fused_bwd(P: torch.Tensor, log_a_f32: torch.Tensor, h0: Optional[torch.
                    h: torch.Tensor, dy: torch.Tensor, dhT: Optional[torch.Tensor],
                    rowss: Optional[torch.Tensor], inv_dim: float, eps: float, B: int, T: int, D: int,
                    *, want_dh0: bool = False, dP: Optional[torch.Tensor] = None):
-    """Launch ``scan_bwd_kernel``.  Returns ``(dP bf16 [B*T,4D], dlog_a fp32 [D], dh0)``.
+    """Launch ``scan_bwd_kernel``.  Returns ``(dP bf16 [B*T,4D], dlog_a fp32, dh0)``.
 
     When ``rowss`` is given, ``dP`` comes out pre-multiplied by the producing
-    RMSNorm's row scale so the following GEMMs need no separate pass.
+    RMSNorm's row scale so the following GEMMs need no separate pass.  With a
+    shared ``log_a`` (``[D]``) its gradient is summed over the batch; with one
+    decay vector per batch row (``[B, D]``) the gradient keeps that shape.
     """
+    la_bs = _log_a_batch_stride(log_a_f32, B, D)
     if dP is None:
         dP = torch.empty(B * T, 4 * D, dtype=torch.bfloat16, device=P.device)
     part = torch.empty(B, D, dtype=torch.float32, device=P.device)
@@ -132,7 +146,9 @@ def scan_fused_bwd(P: torch.Tensor, log_a_f32: torch.Tensor, h0: Optional[torch.
     _lib.check(_lib.lib().ccb_scan_bwd(
         P.data_ptr(), P.stride(0), log_a_f32.data_ptr(), _lib.ptr(h0), h.data_ptr(), dy.data_ptr(),
         _lib.ptr(dhT), _lib.ptr(rowss), inv_dim, eps, dP.data_ptr(), dP.stride(0), part.data_ptr(),
-        _lib.ptr(dh0), B, T, D, _lib.stream_ptr()), "scan_bwd")
+        _lib.ptr(dh0), B, T, D, la_bs, _lib.stream_ptr()), "scan_bwd")
+    if log_a_f32.dim() == 2:
+        return dP, part, dh0
     # deterministic second stage of the d log_a reduction
     dloga = torch.empty(D, dtype=torch.float32, device=P.device)
     _lib.check(_lib.lib().ccb_colsum(part.data_ptr(), B, D, dloga.data_ptr(), 0, _lib.stream_ptr()),

@@ -206,7 +206,7 @@ def run_ttt_eval(model: nn.Module, docs, *, adapt_set: str = "log_a+delta_proj",
         opt = torch.optim.SGD(params, lr=eval_lr) if params else None
     keep_weights = persistence_mode in ("carry_weights", "carry_both") or not restore_weights_per_doc
     ctl = LegalityController(model, loss_fn=lambda lg, tg: torch.nn.functional.cross_entropy(
-        lg.reshape(-1, lg.shape[-1]).float(), tg.reshape(-1), reduction="sum"))
+        lg.reshape(-1, lg.shape[-1]).float(), tg.reshape(-1), reduction="sum"), last_token_is_target_only=True)
     sm = StateManager(model, persistence_mode=persistence_mode)
     budget = BudgetTracker(total_budget_seconds=budget_seconds, score_floor_seconds=score_floor_seconds,
                            safety_margin_seconds=safety_margin_seconds)

@@ -8,12 +8,21 @@ from chaoscontrol_b200.ops import scan as S
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(params=[0, 1], ids=["sfu_exp", "fma_exp"])
+def poly(request):
+    """Both ways of evaluating the gate exponentials: special-function unit and FMA-pipe polynomial."""
+    old = _lib.lib().ccb_scan_poly_exp(request.param)
+    yield request.param
+    _lib.lib().ccb_scan_poly_exp(old)
+
+
+@pytest.mark.parametrize("per_row_log_a", [False, True], ids=["shared_log_a", "log_a_per_row"])
 @pytest.mark.parametrize("B,T,D,with_h0", [(4, 64, 256, False), (3, 37, 512, True), (2, 9, 64, True)])
-def test_scan_fused_fwd_bwd(B, T, D, with_h0):
+def test_scan_fused_fwd_bwd(B, T, D, with_h0, per_row_log_a, poly):
     torch.manual_seed(0)
     dev = "cuda"
     P = (torch.randn(B * T, 4 * D, device=dev) * 1.5).bfloat16()
-    log_a = torch.randn(D, device=dev)
+    log_a = torch.randn(B, D, device=dev) if per_row_log_a else torch.randn(D, device=dev)
     h0 = torch.randn(B, D, device=dev) if with_h0 else None
     y, h, hT = S.scan_fused_fwd(P, log_a, h0, B, T, D)
     Pr = P.float().requires_grad_(True)
@@ -33,9 +42,29 @@ def test_scan_fused_fwd_bwd(B, T, D, with_h0):
     scale = Pr.grad.abs().max().item()
     assert (dP.float() - Pr.grad).abs().max().item() <= 0.03 * scale + 1e-3
     ga = la.grad
+    assert dloga.shape == ga.shape
     assert (dloga - ga).abs().max().item() <= 0.03 * ga.abs().max().item() + 1e-2
     if with_h0:
         assert torch.allclose(dh0, h0r.grad, rtol=2e-2, atol=2e-2)
+
+
+def test_scan_fma_exponentials_track_the_sfu_ones():
+    """The two evaluations of exp differ by a few fp32 ulps: outputs agree far inside bf16 rounding."""
+    torch.manual_seed(3)
+    B, T, D = 4, 512, 256
+    P = (torch.randn(B * T, 4 * D, device="cuda") * 2.0).bfloat16()
+    P[:, 3 * D:] -= 4.0                       # small steps: long memory, where a decay error would compound
+    log_a = torch.randn(D, device="cuda")
+    outs = []
+    for mode in (0, 1):
+        old = _lib.lib().ccb_scan_poly_exp(mode)
+        try:
+            outs.append(S.scan_fused_fwd(P, log_a, None, B, T, D))
+        finally:
+            _lib.lib().ccb_scan_poly_exp(old)
+    (y0, h0_, hT0), (y1, h1_, hT1) = outs
+    assert (hT0 - hT1).abs().max().item() <= 2e-4 * hT0.abs().max().item()
+    assert (y0.float() - y1.float()).abs().max().item() <= 2.0 ** -7 * y0.float().abs().max().item()
 
 
 def test_scan_bwd_rowscale():

@@ -48,8 +48,59 @@ __device__ __forceinline__ Gates eval_gates(float s_raw, float c_raw, float g_ra
   return g;
 }
 
+// ---- packed fp32x2 evaluation ------------------------------------------------------------------
+// One thread owns two adjacent channels that go through the same arithmetic, and both kernels are
+// bound by instruction issue, not by bytes: sm_100's two-wide fp32 instructions (fma / mul / add on a
+// register pair) do each step for both channels at once.  Special-function ops stay one per channel.
+__device__ __forceinline__ float2 f2(float a, float b) { return make_float2(a, b); }
+__device__ __forceinline__ float2 f2s(float a) { return make_float2(a, a); }
+__device__ __forceinline__ float ex2f(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float lg2f(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float2 sigmoid2(float2 x) {
+  const float2 h = __fmul2_rn(x, f2s(0.5f));
+  return __ffma2_rn(f2(tanhf_fast(h.x), tanhf_fast(h.y)), f2s(0.5f), f2s(0.5f));
+}
+
+struct Gates2 {
+  float2 decay, sel, cand, gate, sp_sig, delta;
+};
+
+// nal2e = -sigmoid(log_a) * log2(e), per channel: decay = 2^(delta * nal2e)
+template <bool WANT_SIG>
+__device__ __forceinline__ Gates2 eval_gates2(float2 s_raw, float2 c_raw, float2 g_raw, float2 d_raw,
+                                              float2 nal2e) {
+  constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
+  Gates2 g;
+  g.sel = sigmoid2(s_raw);
+  g.cand = f2(tanhf_fast(c_raw.x), tanhf_fast(c_raw.y));
+  g.gate = sigmoid2(g_raw);
+  const float2 t = __fmul2_rn(f2(-fabsf(d_raw.x), -fabsf(d_raw.y)), f2s(LOG2E));
+  const float2 e = f2(ex2f(t.x), ex2f(t.y));
+  const float2 ope = __fadd2_rn(e, f2s(1.f));
+  const float2 sp = __ffma2_rn(f2(lg2f(ope.x), lg2f(ope.y)), f2s(LN2), f2(fmaxf(d_raw.x, 0.f), fmaxf(d_raw.y, 0.f)));
+  if (WANT_SIG) {
+    const float2 inv = f2(rcpf_fast(ope.x), rcpf_fast(ope.y));
+    const float2 einv = __fmul2_rn(e, inv);
+    g.sp_sig = f2(sp.x > 1e-4f ? (d_raw.x >= 0.f ? inv.x : einv.x) : 0.f,
+                  sp.y > 1e-4f ? (d_raw.y >= 0.f ? inv.y : einv.y) : 0.f);
+  }
+  g.delta = f2(fmaxf(sp.x, 1e-4f), fmaxf(sp.y, 1e-4f));
+  const float2 u = __fmul2_rn(g.delta, nal2e);
+  g.decay = f2(ex2f(u.x), ex2f(u.y));
+  return g;
+}
+
 // grid: (ceil(D/256), B); block: 128 threads, 2 channels per thread.
-template <bool POLY>
+// MODE 0: scalar arithmetic; 1: scalar with FMA-pipe exponentials; 2: packed fp32x2 arithmetic.
+template <int MODE>
 __global__ void __launch_bounds__(SCAN_THREADS)
 scan_fwd_kernel(const __nv_bfloat16* __restrict__ P, long long ldp, const float* __restrict__ log_a,
                 const float* __restrict__ h0, __nv_bfloat16* __restrict__ y,
@@ -61,6 +112,7 @@ scan_fwd_kernel(const __nv_bfloat16* __restrict__ P, long long ldp, const float*
   // la_bstride != 0: every batch row has its own decay vector (per-document test-time training)
   const float a0 = sigmoidf_fast(log_a[b * la_bstride + d]);
   const float a1 = sigmoidf_fast(log_a[b * la_bstride + d + 1]);
+  const float2 nal2e = f2(-a0 * 1.4426950408889634f, -a1 * 1.4426950408889634f);
   float s0 = 0.f, s1 = 0.f;
   if (h0 != nullptr) {
     s0 = h0[(long long)b * D + d];
@@ -91,12 +143,21 @@ scan_fwd_kernel(const __nv_bfloat16* __restrict__ P, long long ldp, const float*
         const float2 cr = unpack_bf16x2(raw[u][1]);
         const float2 gr = unpack_bf16x2(raw[u][2]);
         const float2 dr = unpack_bf16x2(raw[u][3]);
-        const Gates g0 = eval_gates<POLY>(sr.x, cr.x, gr.x, dr.x, a0);
-        const Gates g1 = eval_gates<POLY>(sr.y, cr.y, gr.y, dr.y, a1);
-        s0 = g0.decay * s0 + g0.sel * g0.cand;
-        s1 = g1.decay * s1 + g1.sel * g1.cand;
         const long long o = (long long)(t0 + u) * dq;
-        yw[o] = pack_bf16x2(g0.gate * s0, g1.gate * s1);
+        if (MODE == 2) {
+          const Gates2 g = eval_gates2<false>(sr, cr, gr, dr, nal2e);
+          const float2 st = __ffma2_rn(g.decay, f2(s0, s1), __fmul2_rn(g.sel, g.cand));
+          s0 = st.x;
+          s1 = st.y;
+          const float2 yv = __fmul2_rn(g.gate, st);
+          yw[o] = pack_bf16x2(yv.x, yv.y);
+        } else {
+          const Gates g0 = eval_gates<MODE == 1>(sr.x, cr.x, gr.x, dr.x, a0);
+          const Gates g1 = eval_gates<MODE == 1>(sr.y, cr.y, gr.y, dr.y, a1);
+          s0 = g0.decay * s0 + g0.sel * g0.cand;
+          s1 = g1.decay * s1 + g1.sel * g1.cand;
+          yw[o] = pack_bf16x2(g0.gate * s0, g1.gate * s1);
+        }
         if (hw) hw[o] = pack_bf16x2(s0, s1);
       }
     }
@@ -112,7 +173,7 @@ scan_fwd_kernel(const __nv_bfloat16* __restrict__ P, long long ldp, const float*
 // gates.  Emits dP (optionally pre-multiplied by the consumer's RMSNorm row
 // scale rs[r] = rsqrt(rowss[r] * inv_dim + eps)), per-batch-row partials of
 // d log_a, and optionally d h0.
-template <bool POLY>
+template <int MODE>
 __global__ void __launch_bounds__(SCAN_THREADS)
 scan_bwd_kernel(const __nv_bfloat16* __restrict__ P, long long ldp, const float* __restrict__ log_a,
                 const float* __restrict__ h0, const __nv_bfloat16* __restrict__ hstates,
@@ -125,6 +186,7 @@ scan_bwd_kernel(const __nv_bfloat16* __restrict__ P, long long ldp, const float*
   if (d >= D) return;
   const float a0 = sigmoidf_fast(log_a[b * la_bstride + d]);
   const float a1 = sigmoidf_fast(log_a[b * la_bstride + d + 1]);
+  const float2 nal2e = f2(-a0 * 1.4426950408889634f, -a1 * 1.4426950408889634f);
   const long long rowbase = (long long)b * T;
   const int dq = D / 2;
   const uint32_t* Pw = reinterpret_cast<const uint32_t*>(P + rowbase * ldp + d);
@@ -178,32 +240,58 @@ scan_bwd_kernel(const __nv_bfloat16* __restrict__ P, long long ldp, const float*
         } else {
           hprev = make_float2(0.f, 0.f);
         }
-        const Gates g0 = eval_gates<POLY>(sr.x, cr.x, gr.x, dr.x, a0);
-        const Gates g1 = eval_gates<POLY>(sr.y, cr.y, gr.y, dr.y, a1);
-        // y = gate * h
-        const float dgate0 = dyv.x * hcur.x, dgate1 = dyv.y * hcur.y;
-        const float dh0_ = dyv.x * g0.gate + c0, dh1_ = dyv.y * g1.gate + c1;
-        // h = decay * hprev + sel * cand
-        const float ddec0 = dh0_ * hprev.x, ddec1 = dh1_ * hprev.y;
-        c0 = dh0_ * g0.decay;
-        c1 = dh1_ * g1.decay;
-        const float ds0 = dh0_ * g0.cand * g0.sel * (1.f - g0.sel);
-        const float ds1 = dh1_ * g1.cand * g1.sel * (1.f - g1.sel);
-        const float dc0 = dh0_ * g0.sel * (1.f - g0.cand * g0.cand);
-        const float dc1 = dh1_ * g1.sel * (1.f - g1.cand * g1.cand);
-        const float dg0 = dgate0 * g0.gate * (1.f - g0.gate);
-        const float dg1 = dgate1 * g1.gate * (1.f - g1.gate);
-        // decay = exp(-delta * a): d/d delta = -a * decay ; d/d a = -delta * decay
-        const float dd0 = ddec0 * (-a0 * g0.decay) * g0.sp_sig;
-        const float dd1 = ddec1 * (-a1 * g1.decay) * g1.sp_sig;
-        da0 += ddec0 * (-g0.delta * g0.decay);
-        da1 += ddec1 * (-g1.delta * g1.decay);
         const float rs = rsr[u];
         uint32_t* orow = dPw + (long long)t * dprs;
-        orow[0] = pack_bf16x2(ds0 * rs, ds1 * rs);
-        orow[dq] = pack_bf16x2(dc0 * rs, dc1 * rs);
-        orow[2 * dq] = pack_bf16x2(dg0 * rs, dg1 * rs);
-        orow[3 * dq] = pack_bf16x2(dd0 * rs, dd1 * rs);
+        if (MODE == 2) {
+          const Gates2 g = eval_gates2<true>(sr, cr, gr, dr, nal2e);
+          const float2 one = f2s(1.f), neg1 = f2s(-1.f), rs2 = f2s(rs);
+          // y = gate * h;  h = decay * hprev + sel * cand
+          const float2 dgate = __fmul2_rn(dyv, hcur);
+          const float2 dh = __ffma2_rn(dyv, g.gate, f2(c0, c1));
+          const float2 ddec = __fmul2_rn(dh, hprev);
+          const float2 cn = __fmul2_rn(dh, g.decay);
+          c0 = cn.x;
+          c1 = cn.y;
+          const float2 ds = __fmul2_rn(__fmul2_rn(dh, g.cand), __fmul2_rn(g.sel, __ffma2_rn(g.sel, neg1, one)));
+          const float2 dc = __fmul2_rn(__fmul2_rn(dh, g.sel), __ffma2_rn(__fmul2_rn(g.cand, neg1), g.cand, one));
+          const float2 dg = __fmul2_rn(dgate, __fmul2_rn(g.gate, __ffma2_rn(g.gate, neg1, one)));
+          // decay = exp(-delta * a): d/d delta = -a * decay ; d/d a = -delta * decay
+          const float2 dd = __fmul2_rn(__fmul2_rn(ddec, __fmul2_rn(f2(-a0, -a1), g.decay)), g.sp_sig);
+          const float2 dan = __ffma2_rn(__fmul2_rn(ddec, g.delta), __fmul2_rn(g.decay, neg1), f2(da0, da1));
+          da0 = dan.x;
+          da1 = dan.y;
+          const float2 o0 = __fmul2_rn(ds, rs2), o1 = __fmul2_rn(dc, rs2), o2 = __fmul2_rn(dg, rs2),
+                       o3 = __fmul2_rn(dd, rs2);
+          orow[0] = pack_bf16x2(o0.x, o0.y);
+          orow[dq] = pack_bf16x2(o1.x, o1.y);
+          orow[2 * dq] = pack_bf16x2(o2.x, o2.y);
+          orow[3 * dq] = pack_bf16x2(o3.x, o3.y);
+        } else {
+          const Gates g0 = eval_gates<MODE == 1>(sr.x, cr.x, gr.x, dr.x, a0);
+          const Gates g1 = eval_gates<MODE == 1>(sr.y, cr.y, gr.y, dr.y, a1);
+          // y = gate * h
+          const float dgate0 = dyv.x * hcur.x, dgate1 = dyv.y * hcur.y;
+          const float dh0_ = dyv.x * g0.gate + c0, dh1_ = dyv.y * g1.gate + c1;
+          // h = decay * hprev + sel * cand
+          const float ddec0 = dh0_ * hprev.x, ddec1 = dh1_ * hprev.y;
+          c0 = dh0_ * g0.decay;
+          c1 = dh1_ * g1.decay;
+          const float ds0 = dh0_ * g0.cand * g0.sel * (1.f - g0.sel);
+          const float ds1 = dh1_ * g1.cand * g1.sel * (1.f - g1.sel);
+          const float dc0 = dh0_ * g0.sel * (1.f - g0.cand * g0.cand);
+          const float dc1 = dh1_ * g1.sel * (1.f - g1.cand * g1.cand);
+          const float dg0 = dgate0 * g0.gate * (1.f - g0.gate);
+          const float dg1 = dgate1 * g1.gate * (1.f - g1.gate);
+          // decay = exp(-delta * a): d/d delta = -a * decay ; d/d a = -delta * decay
+          const float dd0 = ddec0 * (-a0 * g0.decay) * g0.sp_sig;
+          const float dd1 = ddec1 * (-a1 * g1.decay) * g1.sp_sig;
+          da0 += ddec0 * (-g0.delta * g0.decay);
+          da1 += ddec1 * (-g1.delta * g1.decay);
+          orow[0] = pack_bf16x2(ds0 * rs, ds1 * rs);
+          orow[dq] = pack_bf16x2(dc0 * rs, dc1 * rs);
+          orow[2 * dq] = pack_bf16x2(dg0 * rs, dg1 * rs);
+          orow[3 * dq] = pack_bf16x2(dd0 * rs, dd1 * rs);
+        }
         hcur = hprev;
       }
     }
@@ -281,11 +369,13 @@ plain_scan_bwd_kernel(const DT* __restrict__ decay, const float* __restrict__ st
 
 using namespace ccb;
 
-// 1: exponentials of the gate evaluation on the FMA pipe; 0: special-function unit.  Returns the old value.
-static int g_scan_poly_exp = 0;
-extern "C" int ccb_scan_poly_exp(int on) {
+// Arithmetic of the fused scan kernels: 0 scalar fp32; 1 scalar with the gate exponentials as an FMA-pipe
+// polynomial (measured slower: the kernels are bound by instruction issue, not by the special-function
+// unit); 2 packed fp32x2.  Returns the old value.
+static int g_scan_poly_exp = 2;
+extern "C" int ccb_scan_poly_exp(int mode) {
   const int old = g_scan_poly_exp;
-  if (on == 0 || on == 1) g_scan_poly_exp = on;
+  if (mode >= 0 && mode <= 2) g_scan_poly_exp = mode;
   return old;
 }
 
@@ -295,7 +385,7 @@ extern "C" int ccb_scan_fwd(const void* P, int64_t ldp, const float* log_a, cons
   if (B <= 0 || T <= 0) return 0;
   if (D % 8 != 0 || ldp % 2 != 0) return set_error("ccb_scan_fwd: D must be a multiple of 8");
   dim3 grid((unsigned)((D / 2 + SCAN_THREADS - 1) / SCAN_THREADS), (unsigned)B);
-  auto kern = g_scan_poly_exp ? scan_fwd_kernel<true> : scan_fwd_kernel<false>;
+  auto kern = g_scan_poly_exp == 2 ? scan_fwd_kernel<2> : (g_scan_poly_exp == 1 ? scan_fwd_kernel<1> : scan_fwd_kernel<0>);
   kern<<<grid, SCAN_THREADS, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)P, ldp, log_a, h0, (__nv_bfloat16*)y, (__nv_bfloat16*)hout, hT, (int)T,
       (int)D, (long long)la_bstride);
@@ -312,7 +402,7 @@ extern "C" int ccb_scan_bwd(const void* P, int64_t ldp, const float* log_a, cons
   if (B <= 0 || T <= 0) return 0;
   if (D % 8 != 0) return set_error("ccb_scan_bwd: D must be a multiple of 8");
   dim3 grid((unsigned)((D / 2 + SCAN_THREADS - 1) / SCAN_THREADS), (unsigned)B);
-  auto kern = g_scan_poly_exp ? scan_bwd_kernel<true> : scan_bwd_kernel<false>;
+  auto kern = g_scan_poly_exp == 2 ? scan_bwd_kernel<2> : (g_scan_poly_exp == 1 ? scan_bwd_kernel<1> : scan_bwd_kernel<0>);
   kern<<<grid, SCAN_THREADS, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)P, ldp, log_a, h0, (const __nv_bfloat16*)hstates,
       (const __nv_bfloat16*)dy, dhT, rowss, inv_dim, eps, (__nv_bfloat16*)dP, lddp, dloga_part, dh0,

@@ -8,9 +8,9 @@ from chaoscontrol_b200.ops import scan as S
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(params=[0, 1], ids=["sfu_exp", "fma_exp"])
+@pytest.fixture(params=[0, 1, 2], ids=["scalar", "scalar_fma_exp", "packed_f32x2"])
 def poly(request):
-    """Both ways of evaluating the gate exponentials: special-function unit and FMA-pipe polynomial."""
+    """Every arithmetic mode of the fused scan: scalar fp32, scalar with FMA-pipe exponentials, packed fp32x2."""
     old = _lib.lib().ccb_scan_poly_exp(request.param)
     yield request.param
     _lib.lib().ccb_scan_poly_exp(old)
@@ -48,23 +48,24 @@ def test_scan_fused_fwd_bwd(B, T, D, with_h0, per_row_log_a, poly):
         assert torch.allclose(dh0, h0r.grad, rtol=2e-2, atol=2e-2)
 
 
-def test_scan_fma_exponentials_track_the_sfu_ones():
-    """The two evaluations of exp differ by a few fp32 ulps: outputs agree far inside bf16 rounding."""
+def test_scan_arithmetic_modes_track_each_other():
+    """The modes differ by a few fp32 ulps per step: outputs agree far inside bf16 rounding."""
     torch.manual_seed(3)
     B, T, D = 4, 512, 256
     P = (torch.randn(B * T, 4 * D, device="cuda") * 2.0).bfloat16()
     P[:, 3 * D:] -= 4.0                       # small steps: long memory, where a decay error would compound
     log_a = torch.randn(D, device="cuda")
     outs = []
-    for mode in (0, 1):
+    for mode in (0, 1, 2):
         old = _lib.lib().ccb_scan_poly_exp(mode)
         try:
             outs.append(S.scan_fused_fwd(P, log_a, None, B, T, D))
         finally:
             _lib.lib().ccb_scan_poly_exp(old)
-    (y0, h0_, hT0), (y1, h1_, hT1) = outs
-    assert (hT0 - hT1).abs().max().item() <= 2e-4 * hT0.abs().max().item()
-    assert (y0.float() - y1.float()).abs().max().item() <= 2.0 ** -7 * y0.float().abs().max().item()
+    y0, _, hT0 = outs[0]
+    for y1, _, hT1 in outs[1:]:
+        assert (hT0 - hT1).abs().max().item() <= 2e-4 * hT0.abs().max().item()
+        assert (y0.float() - y1.float()).abs().max().item() <= 2.0 ** -7 * y0.float().abs().max().item()
 
 
 def test_scan_bwd_rowscale():

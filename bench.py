@@ -64,6 +64,7 @@ def _parse():
     ap.add_argument("--seq", type=int, default=SEQ, help=argparse.SUPPRESS)
     ap.add_argument("--no-e2e", action="store_true", help=argparse.SUPPRESS)
     ap.add_argument("--no-graph", action="store_true", help=argparse.SUPPRESS)
+    ap.add_argument("--scan-arith", type=int, default=-1, choices=[-1, 0, 1, 2], help=argparse.SUPPRESS)
     ap.add_argument("--config", default="submission", choices=sorted(CONFIGS), help=argparse.SUPPRESS)
     a = ap.parse_args()
     cfg = CONFIGS[a.config]
@@ -216,6 +217,8 @@ def run_ours(args):
 
     rank, local, ws = _dist_setup(args)
     dev = torch.device("cuda", local)
+    if args.scan_arith >= 0:                  # A/B switch of the scan kernels' arithmetic (same box, same run)
+        _lib.lib().ccb_scan_poly_exp(args.scan_arith)
     torch.manual_seed(0)
     model = CareStudentLM(vocab_size=VOCAB, dim=DIM, num_layers=LAYERS, ff_mult=FF_MULT)
     model = model.to(dev).to(torch.bfloat16)

@@ -65,6 +65,7 @@ def _parse():
     ap.add_argument("--no-e2e", action="store_true", help=argparse.SUPPRESS)
     ap.add_argument("--no-graph", action="store_true", help=argparse.SUPPRESS)
     ap.add_argument("--scan-arith", type=int, default=-1, choices=[-1, 0, 1, 2], help=argparse.SUPPRESS)
+    ap.add_argument("--gemm-pdl", type=int, default=-1, choices=[-1, 0, 1], help=argparse.SUPPRESS)
     ap.add_argument("--config", default="submission", choices=sorted(CONFIGS), help=argparse.SUPPRESS)
     a = ap.parse_args()
     cfg = CONFIGS[a.config]
@@ -219,6 +220,8 @@ def run_ours(args):
     dev = torch.device("cuda", local)
     if args.scan_arith >= 0:                  # A/B switch of the scan kernels' arithmetic (same box, same run)
         _lib.lib().ccb_scan_poly_exp(args.scan_arith)
+    if args.gemm_pdl >= 0:
+        _lib.lib().ccb_gemm_pdl(args.gemm_pdl)
     torch.manual_seed(0)
     model = CareStudentLM(vocab_size=VOCAB, dim=DIM, num_layers=LAYERS, ff_mult=FF_MULT)
     model = model.to(dev).to(torch.bfloat16)
@@ -239,10 +242,13 @@ def run_ours(args):
     if ws > 1 and not args.dist_muon:
         from chaoscontrol_b200.parallel.grad_overlap import reducer_for
         reducer = reducer_for(engine, ws)
-        if reducer is None:
+        if reducer is None and os.environ.get("CCB_GRAD_OVERLAP", "1") == "0":
+            collective = "peer-oneshot over CUDA-IPC symmetric buffers, one exchange after backward (CCB_GRAD_OVERLAP=0)"
+        elif reducer is None:
             raise RuntimeError("overlapped peer-memory gradient exchange unavailable: refusing to bench a fallback")
-        collective = (f"peer-oneshot over CUDA-IPC symmetric buffers, {reducer.n_buckets} buckets overlapped "
-                      "with backward")
+        else:
+            collective = (f"peer-oneshot over CUDA-IPC symmetric buffers, {reducer.n_buckets} buckets overlapped "
+                          "with backward")
     elif ws > 1:
         collective = "peer-memory reduce of owned ranges + parameter gather (distributed Muon)"
     dist_opt = None

@@ -254,6 +254,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   if (CG == 2) cluster_sync_all();     // both CTAs' barriers exist before either touches the peer's
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // Barriers, tensor memory and descriptors are set up: everything above overlaps the tail of the
+  // previous kernel when this one was launched as a programmatic dependent.  Nothing below runs before
+  // that kernel has finished; our own successor may be scheduled onto SMs as our CTAs leave them.
+  pdl_wait();
+  pdl_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -770,6 +775,7 @@ static int g_gemm_dbg = 0;
 // RMSNorm-backward GEMM, whose K = 512 operand stream already fills the L2 path (0.191 -> 0.202 ms);
 // prefetching A helps only the streaming layout (0.206 -> 0.183 ms), which the resident layout beats.
 static int g_gemm_l2pf = -1;
+static int g_gemm_pdl = 0;
 
 template <int BN, int A_MN, int B_MN, int LM = 0, int EPI_T = -1, int CG = 1, int BRES = 0>
 static int launch_gemm(const CcbGemmArgs* a, cudaStream_t stream) {
@@ -916,6 +922,21 @@ static int launch_gemm(const CcbGemmArgs* a, cudaStream_t stream) {
         p.epi == CCB_EPI_ROWSCALE_SILU || p.f8)
       return set_error("ccb_gemm: shape not eligible for the resident-B layout (dispatch error)");
   }
+  if (g_gemm_pdl) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, tmC2, p);
+    count_launch();
+    if (e != cudaSuccess) return set_error("gemm launch (programmatic dependent): %s", cudaGetErrorString(e));
+    return 0;
+  }
   kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, tmC, tmC2, p);
   count_launch();
   cudaError_t e = cudaGetLastError();
@@ -940,6 +961,13 @@ extern "C" int ccb_gemm_debug(int bits) {
 extern "C" int ccb_gemm_l2_prefetch(int bits) {
   const int old = ccb::g_gemm_l2pf;
   if (bits >= -1 && bits <= 3) ccb::g_gemm_l2pf = bits;
+  return old;
+}
+// 1: single-CTA GEMMs are launched as programmatic dependents (their set-up overlaps the tail of the
+// previous kernel in the stream); 0: ordinary stream order.  Returns the old value.
+extern "C" int ccb_gemm_pdl(int on) {
+  const int old = ccb::g_gemm_pdl;
+  if (on == 0 || on == 1) ccb::g_gemm_pdl = on;
   return old;
 }
 // 1: K <= 256 single-output GEMMs keep their weight tile resident in shared memory (see GemmCfg).

@@ -391,6 +391,17 @@ __host__ __device__ constexpr uint32_t make_idesc_f8(int M, int N, int a_fmt, in
 }
 
 // ---------------------------------------------------------------------------
+// Programmatic dependent launch: a kernel launched with the programmatic-stream-serialization
+// attribute may begin while its predecessor in the stream is still running.  `pdl_wait` returns once
+// the predecessor grid has completed and its writes are visible (immediately when the kernel was
+// launched the ordinary way); everything before it must touch no global memory the predecessor
+// writes or reads.  `pdl_launch_dependents` lets the successor's CTAs be scheduled as soon as every
+// CTA of this grid has called it or exited.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
+
+// ---------------------------------------------------------------------------
 // Small math helpers shared by epilogues and elementwise kernels
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ float tanhf_fast(float x) {

@@ -9,6 +9,7 @@ the reference dispatcher that refuses silent fallback
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 from typing import Optional
 
@@ -59,6 +60,7 @@ _SIGS = {
     "ccb_pack_write_events": ([vp, vp, vp, vp, i64, vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, i64, i64, i64,
                                i64, vp], C.c_int),
     "ccb_scan_poly_exp": ([C.c_int], C.c_int),
+    "ccb_gemm_pdl": ([C.c_int], C.c_int),
     "ccb_scan_fwd": ([vp, i64, vp, vp, vp, vp, vp, i64, i64, i64, i64, vp], C.c_int),
     "ccb_scan_bwd": ([vp, i64, vp, vp, vp, vp, vp, vp, f32, f32, vp, i64, vp, vp, i64, i64, i64, i64, vp],
                      C.c_int),
@@ -118,6 +120,11 @@ def lib() -> C.CDLL:
         fn.restype = restype
     _late_sigs(L)
     _lib = L
+    # process-wide kernel switches from the environment (A/B measurements, test runs of a non-default mode)
+    for var, fn in (("CCB_GEMM_PDL", "ccb_gemm_pdl"), ("CCB_SCAN_ARITH", "ccb_scan_poly_exp")):
+        val = os.environ.get(var)
+        if val is not None and hasattr(L, fn):
+            getattr(L, fn)(int(val))
     return L
 
 

@@ -103,7 +103,10 @@ class OverlappedGradReducer:
 def reducer_for(engine, world_size: int, group=None) -> Optional[OverlappedGradReducer]:
     """The engine's cached reducer when the peer-memory communicator of ``group`` is alive and spans
     ``world_size`` ranks, else None (the caller reduces after the step instead)."""
+    import os
     from . import symm
+    if os.environ.get("CCB_GRAD_OVERLAP", "1") == "0":       # one exchange after the step instead (A/B measurements)
+        return None
     comm = symm.active_comm(group)
     if comm is None or comm.ws != world_size or not engine.arena.flat_grad.is_cuda:
         return None

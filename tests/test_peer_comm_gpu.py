@@ -37,12 +37,13 @@ def test_flag_wait_times_out_and_reports():
 
 def _worker(rank, ws, port, outdir):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import traceback
     import torch.distributed as dist
-    torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=ws, device_id=torch.device("cuda", rank))
     ok = True
     msg = ""
     try:
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=ws, device_id=torch.device("cuda", rank))
         from chaoscontrol_b200.parallel.peer import PeerComm
         n = 1 << 20
         comm = PeerComm.create(n)
@@ -150,12 +151,16 @@ def _worker(rank, ws, port, outdir):
             ok, msg = False, f"status {_lib.read_status()} after resync"
         dist.barrier()
         comm.close()
-    except Exception as exc:  # pragma: no cover
-        ok, msg = False, f"{type(exc).__name__}: {exc}"
+    except BaseException as exc:  # pragma: no cover
+        ok, msg = False, f"{type(exc).__name__}: {exc}\n{traceback.format_exc()}"
     finally:
         with open(os.path.join(outdir, f"r{rank}.txt"), "w") as f:
             f.write("OK" if ok else "FAIL " + msg)
-        dist.destroy_process_group()
+        try:
+            if dist.is_initialized():
+                dist.destroy_process_group()
+        except Exception:  # pragma: no cover
+            pass
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")

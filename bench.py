@@ -64,7 +64,7 @@ def _parse():
     ap.add_argument("--seq", type=int, default=SEQ, help=argparse.SUPPRESS)
     ap.add_argument("--no-e2e", action="store_true", help=argparse.SUPPRESS)
     ap.add_argument("--no-graph", action="store_true", help=argparse.SUPPRESS)
-    ap.add_argument("--scan-arith", type=int, default=-1, choices=[-1, 0, 1, 2], help=argparse.SUPPRESS)
+    ap.add_argument("--scan-arith", type=int, default=-1, choices=[-1, 0, 1, 2, 3, 4], help=argparse.SUPPRESS)
     ap.add_argument("--gemm-pdl", type=int, default=-1, choices=[-1, 0, 1], help=argparse.SUPPRESS)
     ap.add_argument("--config", default="submission", choices=sorted(CONFIGS), help=argparse.SUPPRESS)
     a = ap.parse_args()
@@ -242,10 +242,11 @@ def run_ours(args):
     if ws > 1 and not args.dist_muon:
         from chaoscontrol_b200.parallel.grad_overlap import reducer_for
         reducer = reducer_for(engine, ws)
-        if reducer is None and os.environ.get("CCB_GRAD_OVERLAP", "1") == "0":
-            collective = "peer-oneshot over CUDA-IPC symmetric buffers, one exchange after backward (CCB_GRAD_OVERLAP=0)"
-        elif reducer is None:
-            raise RuntimeError("overlapped peer-memory gradient exchange unavailable: refusing to bench a fallback")
+        from chaoscontrol_b200.parallel import symm
+        if symm.active_comm(None) is None:
+            raise RuntimeError("peer-memory gradient exchange unavailable: refusing to bench a fallback")
+        if reducer is None:
+            collective = "peer-oneshot over CUDA-IPC symmetric buffers, one exchange after backward"
         else:
             collective = (f"peer-oneshot over CUDA-IPC symmetric buffers, {reducer.n_buckets} buckets overlapped "
                           "with backward")
@@ -965,10 +966,12 @@ def run_reference(args):
                "api": "chaoscontrol.train_ssm.train_ssm_step + Muon.step"}
 
     toks = ws * args.batch * args.seq / (ms / 1e3)
-    out = {"metric": "train tokens/sec, 4Lx256d V16384 SSM (seq 512, bs 1024/rank, bf16, Muon)",
+    headline = args.config == "submission"
+    out = {"metric": ("train tokens/sec, 4Lx256d V16384 SSM (seq 512, bs 1024/rank, bf16, Muon)" if headline else
+                      f"train tokens/sec, {LAYERS}Lx{DIM}d V16384 SSM (seq {args.seq}, bs {args.batch}/rank, bf16, Muon)"),
            "value": toks, "unit": "tokens/s", "n_gpus": ws, "steps": args.steps, "warmup": args.warmup,
            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-           "vs_baseline": toks / (BASELINE_TOKS_8XH100 * ws / 8.0), "dtype": "bf16",
+           "vs_baseline": toks / (BASELINE_TOKS_8XH100 * ws / 8.0) if headline else None, "dtype": "bf16",
            "data": "synthetic Zipf(1.1) tokens, random-init weights", "impl": "reference",
            "final_loss": final_loss, "clocks": cs.summary(), "e2e": e2e,
            "config": _train_config(args, ws, sum(p.numel() for p in model.parameters()), False),

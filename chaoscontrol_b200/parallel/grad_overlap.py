@@ -100,15 +100,35 @@ class OverlappedGradReducer:
         self.arena.grads_reduced = True         # type: ignore[attr-defined]
 
 
-def reducer_for(engine, world_size: int, group=None) -> Optional[OverlappedGradReducer]:
-    """The engine's cached reducer when the peer-memory communicator of ``group`` is alive and spans
-    ``world_size`` ranks, else None (the caller reduces after the step instead)."""
+#: measured per-direction peer bandwidth of this pool's B200s (bytes / s), for the overlap rule below
+PEER_BYTES_PER_S = 770e9
+#: overlap only when the exchange left exposed at the end of the step would exceed this many seconds
+OVERLAP_MIN_EXPOSED_S = 0.4e-3
+
+
+def overlap_wanted(payload_bytes: int, world_size: int) -> bool:
+    """``CCB_GRAD_OVERLAP=1`` / ``0`` forces the bucketed, overlapped exchange on / off.  Unset: overlap
+    only when one exchange after backward would take longer than ``OVERLAP_MIN_EXPOSED_S`` (bf16 payload
+    read from ``world_size - 1`` peers at the measured peer bandwidth).  Measured on 4 x B200 with the
+    10.8 M-parameter submission model (21.5 MB payload, ~0.1 ms of peer reads): one exchange after
+    backward 33.15-33.19 ms per step, six overlapped buckets 33.54-33.62 ms, one GPU alone 32.61 ms;
+    the side-stream kernels cost the concurrent backward more than the ~0.1 ms they hide."""
     import os
+    env = os.environ.get("CCB_GRAD_OVERLAP")
+    if env is not None:
+        return env != "0"
+    return payload_bytes * max(world_size - 1, 0) / PEER_BYTES_PER_S > OVERLAP_MIN_EXPOSED_S
+
+
+def reducer_for(engine, world_size: int, group=None) -> Optional[OverlappedGradReducer]:
+    """The engine's cached reducer when the overlapped exchange is wanted (:func:`overlap_wanted`) and the
+    peer-memory communicator of ``group`` is alive and spans ``world_size`` ranks, else None (the caller
+    reduces once after the step)."""
     from . import symm
-    if os.environ.get("CCB_GRAD_OVERLAP", "1") == "0":       # one exchange after the step instead (A/B measurements)
+    if not engine.arena.flat_grad.is_cuda or not overlap_wanted(engine.arena.flat_grad.numel() * 2, world_size):
         return None
     comm = symm.active_comm(group)
-    if comm is None or comm.ws != world_size or not engine.arena.flat_grad.is_cuda:
+    if comm is None or comm.ws != world_size:
         return None
     red = getattr(engine, "_reducer", None)
     if red is None or red.comm is not comm:

@@ -26,6 +26,8 @@ succeeded the buffers are released again everywhere and ``create`` returns
 """
 from __future__ import annotations
 
+import os
+
 import ctypes as C
 from typing import Optional
 
@@ -166,7 +168,8 @@ class PeerComm:
             flat.copy_(tmp[:n])
             return
         if mode is None:
-            mode = 0 if n * 2 <= ONE_SHOT_MAX_BYTES else 1
+            forced = os.environ.get("CCB_ALLREDUCE_MODE")          # 0 one-shot, 1 two-shot (A/B measurements)
+            mode = int(forced) if forced in ("0", "1") else (0 if n * 2 <= ONE_SHOT_MAX_BYTES else 1)
         scale = 1.0 / self.ws if average else 1.0
         _lib.check(_lib.lib().ccb_allreduce(flat.data_ptr(), n, scale, self._bufs, self._bufs2,
                                             self._pads, self.rank, self.ws,

@@ -176,13 +176,14 @@ def test_peer_allreduce_two_gpus():
     assert all(o == "OK" for o in outs), outs
 
 
-def _graph_worker(rank, ws, port, outdir):
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+def _graph_worker(rank, ws, port, outdir, overlap):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      CCB_GRAD_OVERLAP="1" if overlap else "0")
     import torch.distributed as dist
-    torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=ws, device_id=torch.device("cuda", rank))
     ok, msg = True, ""
     try:
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=ws, device_id=torch.device("cuda", rank))
         from chaoscontrol_b200.models.model import CareStudentLM
         from chaoscontrol_b200.optim.muon import Muon
         from chaoscontrol_b200.parallel import symm_comm
@@ -204,7 +205,11 @@ def _graph_worker(rank, ws, port, outdir):
         m1, a1, o1 = build()
         symm_comm.enable(a1.flat_grad.numel())
         broadcast_params(m1)
-        for b in batches:                                           # eager: overlapped exchange, then clip
+        from chaoscontrol_b200.parallel.grad_overlap import reducer_for
+        from chaoscontrol_b200.train_ssm import _engine_for
+        if (reducer_for(_engine_for(m1), ws) is not None) != bool(overlap):
+            ok, msg = False, "CCB_GRAD_OVERLAP did not select the exchange"
+        for b in batches:                                           # eager: exchange (overlapped or not), then clip
             train_ssm_step(m1, b[:, :-1], b[:, 1:], 64, ddp_active=True, world_size=ws, precision="bf16",
                            lm_head_backward_mode="fused_streaming_cached")
             clip_arena_grad_norm(a1, 1.0)
@@ -230,25 +235,31 @@ def _graph_worker(rank, ws, port, outdir):
             ok, msg = False, f"status {_lib.read_status()}"
         dist.barrier()
         symm_comm.disable()
-    except Exception as exc:  # pragma: no cover
+    except BaseException as exc:  # pragma: no cover
         import traceback
-        ok, msg = False, f"{type(exc).__name__}: {exc} {traceback.format_exc()[-600:]}"
+        ok, msg = False, f"{type(exc).__name__}: {exc} {traceback.format_exc()[-1200:]}"
     finally:
         with open(os.path.join(outdir, f"r{rank}.txt"), "w") as f:
             f.write("OK" if ok else "FAIL " + msg)
-        dist.destroy_process_group()
+        try:
+            if dist.is_initialized():
+                dist.destroy_process_group()
+        except Exception:  # pragma: no cover
+            pass
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_graphed_data_parallel_step_two_gpus():
-    """The whole data-parallel step (overlapped peer-memory exchange included) replayed from a CUDA
-    graph gives the same parameter bits as the eager steps, on every rank."""
+@pytest.mark.parametrize("overlap", [False, True], ids=["one_exchange", "overlapped_buckets"])
+def test_graphed_data_parallel_step_two_gpus(overlap):
+    """The whole data-parallel step (peer-memory exchange included: one exchange after backward, or the
+    bucketed exchange overlapped with it) replayed from a CUDA graph gives the same parameter bits as
+    the eager steps, on every rank."""
     import torch.multiprocessing as mp
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
     port = s.getsockname()[1]
     s.close()
     with tempfile.TemporaryDirectory() as d:
-        mp.spawn(_graph_worker, args=(2, port, d), nprocs=2, join=True)
+        mp.spawn(_graph_worker, args=(2, port, d, overlap), nprocs=2, join=True)
         outs = [open(os.path.join(d, f"r{r}.txt")).read() for r in range(2)]
     assert all(o == "OK" for o in outs), outs

@@ -64,7 +64,7 @@ def _parse():
     ap.add_argument("--seq", type=int, default=SEQ, help=argparse.SUPPRESS)
     ap.add_argument("--no-e2e", action="store_true", help=argparse.SUPPRESS)
     ap.add_argument("--no-graph", action="store_true", help=argparse.SUPPRESS)
-    ap.add_argument("--scan-arith", type=int, default=-1, choices=[-1, 0, 1, 2, 3, 4], help=argparse.SUPPRESS)
+    ap.add_argument("--scan-arith", type=int, default=-1, choices=[-1, 0, 1, 2], help=argparse.SUPPRESS)
     ap.add_argument("--gemm-pdl", type=int, default=-1, choices=[-1, 0, 1], help=argparse.SUPPRESS)
     ap.add_argument("--config", default="submission", choices=sorted(CONFIGS), help=argparse.SUPPRESS)
     a = ap.parse_args()

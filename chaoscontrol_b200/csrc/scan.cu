@@ -100,7 +100,7 @@ __device__ __forceinline__ Gates2 eval_gates2(float2 s_raw, float2 c_raw, float2
 // grid: (ceil(D/256), B); block: 128 threads, 2 channels per thread.
 // MODE 0: scalar arithmetic; 1: scalar with FMA-pipe exponentials; 2: packed fp32x2 arithmetic.
 // U time steps are loaded ahead of their arithmetic; MINB resident blocks per SM bound the registers.
-template <int MODE, int U = 8, int MINB = 1>
+template <int MODE, int U = 8, int MINB = 4>
 __global__ void __launch_bounds__(SCAN_THREADS, MINB)
 scan_fwd_kernel(const __nv_bfloat16* __restrict__ P, long long ldp, const float* __restrict__ log_a,
                 const float* __restrict__ h0, __nv_bfloat16* __restrict__ y,
@@ -174,7 +174,7 @@ scan_fwd_kernel(const __nv_bfloat16* __restrict__ P, long long ldp, const float*
 // gates.  Emits dP (optionally pre-multiplied by the consumer's RMSNorm row
 // scale rs[r] = rsqrt(rowss[r] * inv_dim + eps)), per-batch-row partials of
 // d log_a, and optionally d h0.
-template <int MODE, int U = 8, int MINB = 1>
+template <int MODE, int U = 8, int MINB = 4>
 __global__ void __launch_bounds__(SCAN_THREADS, MINB)
 scan_bwd_kernel(const __nv_bfloat16* __restrict__ P, long long ldp, const float* __restrict__ log_a,
                 const float* __restrict__ h0, const __nv_bfloat16* __restrict__ hstates,
@@ -373,12 +373,11 @@ using namespace ccb;
 
 // Arithmetic of the fused scan kernels: 0 scalar fp32; 1 scalar with the gate exponentials as an FMA-pipe
 // polynomial (measured slower: the kernels are bound by instruction issue, not by the special-function
-// unit); 2 packed fp32x2; 3 / 4 packed with 4 / 6 steps loaded ahead and six resident blocks per SM (fewer
-// registers, more warps).  Returns the old value.
+// unit); 2 packed fp32x2.  Returns the old value.
 static int g_scan_poly_exp = 2;
 extern "C" int ccb_scan_poly_exp(int mode) {
   const int old = g_scan_poly_exp;
-  if (mode >= 0 && mode <= 4) g_scan_poly_exp = mode;
+  if (mode >= 0 && mode <= 2) g_scan_poly_exp = mode;
   return old;
 }
 
@@ -388,7 +387,9 @@ extern "C" int ccb_scan_fwd(const void* P, int64_t ldp, const float* log_a, cons
   if (B <= 0 || T <= 0) return 0;
   if (D % 8 != 0 || ldp % 2 != 0) return set_error("ccb_scan_fwd: D must be a multiple of 8");
   dim3 grid((unsigned)((D / 2 + SCAN_THREADS - 1) / SCAN_THREADS), (unsigned)B);
-  auto kern = g_scan_poly_exp == 4 ? scan_fwd_kernel<2, 6, 6> : g_scan_poly_exp == 3 ? scan_fwd_kernel<2, 4, 6> : g_scan_poly_exp == 2 ? scan_fwd_kernel<2> : (g_scan_poly_exp == 1 ? scan_fwd_kernel<1> : scan_fwd_kernel<0>);
+  // forward: six steps loaded ahead and six resident blocks per SM (72 registers) measured best: 0.286 ms at
+  // 524 288 rows against 0.311 ms with eight steps ahead and four blocks
+  auto kern = g_scan_poly_exp == 2 ? scan_fwd_kernel<2, 6, 6> : (g_scan_poly_exp == 1 ? scan_fwd_kernel<1> : scan_fwd_kernel<0>);
   kern<<<grid, SCAN_THREADS, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)P, ldp, log_a, h0, (__nv_bfloat16*)y, (__nv_bfloat16*)hout, hT, (int)T,
       (int)D, (long long)la_bstride);
@@ -405,7 +406,9 @@ extern "C" int ccb_scan_bwd(const void* P, int64_t ldp, const float* log_a, cons
   if (B <= 0 || T <= 0) return 0;
   if (D % 8 != 0) return set_error("ccb_scan_bwd: D must be a multiple of 8");
   dim3 grid((unsigned)((D / 2 + SCAN_THREADS - 1) / SCAN_THREADS), (unsigned)B);
-  auto kern = g_scan_poly_exp == 4 ? scan_bwd_kernel<2, 6, 6> : g_scan_poly_exp == 3 ? scan_bwd_kernel<2, 4, 6> : g_scan_poly_exp == 2 ? scan_bwd_kernel<2> : (g_scan_poly_exp == 1 ? scan_bwd_kernel<1> : scan_bwd_kernel<0>);
+  // backward: eight steps ahead, four blocks per SM (116 registers): 0.538 ms; six blocks with six / four steps
+  // ahead measured 0.632 / 0.706 ms (fewer loads in flight cost more than the extra warps bring)
+  auto kern = g_scan_poly_exp == 2 ? scan_bwd_kernel<2> : (g_scan_poly_exp == 1 ? scan_bwd_kernel<1> : scan_bwd_kernel<0>);
   kern<<<grid, SCAN_THREADS, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)P, ldp, log_a, h0, (const __nv_bfloat16*)hstates,
       (const __nv_bfloat16*)dy, dhT, rowss, inv_dim, eps, (__nv_bfloat16*)dP, lddp, dloga_part, dh0,

@@ -140,7 +140,7 @@ def main() -> None:
                          "stages with X in shared memory (-1: library default)")
     ap.add_argument("--gemm-bres", type=int, default=-1, choices=[-1, 0, 1],
                     help="1: K <= 256 GEMMs keep their weight tile resident in shared memory (-1: library default)")
-    ap.add_argument("--scan-poly", type=int, default=-1, choices=[-1, 0, 1, 2, 3, 4],
+    ap.add_argument("--scan-poly", type=int, default=-1, choices=[-1, 0, 1, 2],
                     help="scan kernel arithmetic: 0 scalar, 1 scalar with FMA-pipe exponentials, 2 packed fp32x2")
     ap.add_argument("--gemm-l2pf", type=int, default=-2, choices=[-2, -1, 0, 1, 2, 3],
                     help="(-2: leave the library default) GEMM L2 prefetch bits: 1 = A tiles two tiles ahead, 2 = next tile's epilogue operands")

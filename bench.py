@@ -66,6 +66,7 @@ def _parse():
     ap.add_argument("--no-graph", action="store_true", help=argparse.SUPPRESS)
     ap.add_argument("--scan-arith", type=int, default=-1, choices=[-1, 0, 1, 2], help=argparse.SUPPRESS)
     ap.add_argument("--gemm-pdl", type=int, default=-1, choices=[-1, 0, 1], help=argparse.SUPPRESS)
+    ap.add_argument("--gemm-pres", type=int, default=-1, choices=[-1, 0, 1, 2, 3], help=argparse.SUPPRESS)
     ap.add_argument("--config", default="submission", choices=sorted(CONFIGS), help=argparse.SUPPRESS)
     a = ap.parse_args()
     cfg = CONFIGS[a.config]
@@ -222,6 +223,8 @@ def run_ours(args):
         _lib.lib().ccb_scan_poly_exp(args.scan_arith)
     if args.gemm_pdl >= 0:
         _lib.lib().ccb_gemm_pdl(args.gemm_pdl)
+    if args.gemm_pres >= 0:
+        _lib.lib().ccb_gemm_pair_resident(args.gemm_pres)
     torch.manual_seed(0)
     model = CareStudentLM(vocab_size=VOCAB, dim=DIM, num_layers=LAYERS, ff_mult=FF_MULT)
     model = model.to(dev).to(torch.bfloat16)

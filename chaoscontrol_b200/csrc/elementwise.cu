@@ -256,7 +256,14 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ part, int S, long
       if (n < N) {
         float s = 0.f;
         const float* pp = part + (long long)n * K + k;
-        for (int sp = 0; sp < S; ++sp) s += pp[(long long)sp * split_stride];
+        int sp = 0;
+        // four independent loads in flight, added in index order (the sum keeps its fixed order)
+        for (; sp + 4 <= S; sp += 4) {
+          const float v0 = pp[(long long)sp * split_stride], v1 = pp[(long long)(sp + 1) * split_stride];
+          const float v2 = pp[(long long)(sp + 2) * split_stride], v3 = pp[(long long)(sp + 3) * split_stride];
+          s += v0; s += v1; s += v2; s += v3;
+        }
+        for (; sp < S; ++sp) s += pp[(long long)sp * split_stride];
         const long long o = (long long)n * K + k;
         if (W) cacc += s * __bfloat162float(W[o]);
         const float val = s * cs;

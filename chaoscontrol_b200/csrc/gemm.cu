@@ -83,21 +83,28 @@ constexpr int STG_BYTES = EPI_WARPS * STG_BUFS_PER_WARP * STG_BUF_BYTES;   // 64
 // further tile fits in flight; with B resident a tile needs 64 KiB and a full tile of A is in flight.
 // The staging area shrinks to one buffer per epilogue warp to make room.
 constexpr int BRES_KBLOCKS = 4;
+// On a CTA pair each CTA keeps only its half of the weight tile (BN / 2 rows), so the resident layout has
+// room to spare: BRES = 1 holds K <= 256 (64 KiB) and gives the A ring eight stages (two tiles of A in
+// flight per CTA); BRES = 2 holds K <= 512 (128 KiB) with a four-stage ring, which takes the weight
+// re-reads (256 KiB from L2 per 128-row tile on a single CTA) out of the K = 512 input-gradient GEMMs.
 
 template <int BN, int CG = 1, int BRES = 0>
 struct GemmCfg {
+  static_assert(BRES == 0 || BRES == 1 || (BRES == 2 && CG == 2), "BRES 2 (K <= 512 resident) needs a CTA pair");
   static constexpr int B_ROWS = BN / CG;                  // rows of the B tile this CTA stages
   static constexpr int B_STAGE_BYTES = B_ROWS * BK * 2;
-  static constexpr int STAGES = BRES ? 4 : ((BN == 256 && CG == 1) ? 3 : 4);
+  static constexpr int RES_KBLOCKS = BRES == 2 ? 8 : BRES_KBLOCKS;   // k-blocks of the resident tile
+  static constexpr int STAGES = BRES ? ((CG == 2 && BRES == 1) ? 8 : 4) : ((BN == 256 && CG == 1) ? 3 : 4);
   static constexpr int TMEM_COLS = 2 * BN;   // 512 or 256: powers of two
   static constexpr int STG_BUFS = BRES ? 1 : STG_BUFS_PER_WARP;
-  static constexpr int A_OFF = BRES ? BRES_KBLOCKS * B_STAGE_BYTES : 0;
+  static constexpr int A_OFF = BRES ? RES_KBLOCKS * B_STAGE_BYTES : 0;
   static constexpr int STG_OFF = BRES ? A_OFF + STAGES * A_STAGE_BYTES : STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);
   static constexpr int BAR_OFF = STG_OFF + EPI_WARPS * STG_BUFS * STG_BUF_BYTES;
   static constexpr int XCH_OFF = BAR_OFF + 256;     // per-row partials exchanged between warps
   // the resident layout has no room for alignment slack: its kernel checks that the dynamic
   // shared-memory window starts on a 1 KiB boundary (it does when the kernel has no static shared memory)
   static constexpr int SMEM_BYTES = (BRES ? 0 : 1024) + XCH_OFF + 2 * EPI_PARTS * BM * 4;
+  static_assert(2 * STAGES * 8 + 56 <= 256, "barrier block overflows its 256 bytes");
   static_assert(SMEM_BYTES <= 227 * 1024, "tile configuration exceeds the per-CTA shared memory limit");
 };
 
@@ -187,7 +194,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             const GemmKArgs p) {
   using Cfg = GemmCfg<BN, CG, BRES>;
   static_assert(CG == 1 || (A_MN == 0 && LM == 0), "CTA pairs: K-major A, trunk epilogues");
-  static_assert(BRES == 0 || (CG == 1 && A_MN == 0 && LM == 0), "resident B: single CTA, K-major A, trunk epilogues");
+  static_assert(BRES == 0 || (A_MN == 0 && LM == 0), "resident B: K-major A, trunk epilogues");
   static_assert(BRES == 0 || EPI_T != CCB_EPI_ROWSCALE_SILU, "resident B has one staging buffer per warp: one output");
   constexpr int STG_BUFS = Cfg::STG_BUFS;
   // pair geometry: `cta_rank` 0 is the leader (issues the MMAs, owns the barriers the loads and the
@@ -269,6 +276,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       if (BRES && walker < total_tiles) {
         // the weight tile of this CTA's N coordinate, all k-blocks, once
         const TileCoord t0 = decode_tile(p, walker, BN, BM_TILE);
+        if (CG == 2) {
+          // each CTA loads its half of the tile into its own shared memory; both report to the leader's
+          // barrier, which expects the bytes of the pair
+          if (cta_rank == 0) mbar_arrive_expect_tx(bres_bar, (uint32_t)(2 * p.kblocks * B_STAGE_BYTES));
+          const uint32_t rb = mapa_shared(smem_u32(bres_bar), 0);
+          for (int kb = 0; kb < p.kblocks; ++kb) {
+            uint8_t* b_dst = sB + kb * B_STAGE_BYTES;
+            if (B_MN == 0) {
+              tma_load_3d_cg2(b_dst, &tmB, rb, kb * p.bk, t0.n0 + Cfg::B_ROWS * (int)cta_rank, 0);
+            } else {
+#pragma unroll
+              for (int j = 0; j < Cfg::B_ROWS / 64; ++j)
+                tma_load_3d_cg2(b_dst + j * 8192, &tmB, rb, t0.n0 + Cfg::B_ROWS * (int)cta_rank + 64 * j,
+                                kb * BK, 0);
+            }
+          }
+        } else {
         mbar_arrive_expect_tx(bres_bar, (uint32_t)(p.kblocks * B_STAGE_BYTES));
         for (int kb = 0; kb < p.kblocks; ++kb) {
           uint8_t* b_dst = sB + kb * B_STAGE_BYTES;
@@ -279,6 +303,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             for (int j = 0; j < BN / 64; ++j)
               tma_load_3d(b_dst + j * 8192, &tmB, bres_bar, t0.n0 + 64 * j, kb * BK, 0);
           }
+        }
         }
       }
       for (int tile = walker; tile < total_tiles && ok; tile += n_walkers) {
@@ -297,8 +322,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             }
           }
           if (BRES) {
-            mbar_arrive_expect_tx(&full_bar[stage], A_STAGE_BYTES);
-            tma_load_3d(a_dst, &tmA, &full_bar[stage], kb * p.bk, t.m0, t.b);
+            if (CG == 2) {
+              if (cta_rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * A_STAGE_BYTES);
+              tma_load_3d_cg2(a_dst, &tmA, mapa_shared(smem_u32(&full_bar[stage]), 0), kb * p.bk,
+                              t.m0 + BM * (int)cta_rank, t.b);
+            } else {
+              mbar_arrive_expect_tx(&full_bar[stage], A_STAGE_BYTES);
+              tma_load_3d(a_dst, &tmA, &full_bar[stage], kb * p.bk, t.m0, t.b);
+            }
             if (++stage == STAGES) { stage = 0; phase ^= 1u; }
             continue;
           }
@@ -900,7 +931,14 @@ static int launch_gemm(const CcbGemmArgs* a, cudaStream_t stream) {
   if (total <= 0) return 0;
   if (CG == 2) {
     if (p.pair) return set_error("ccb_gemm: the 512-column RMSNorm-backward tile is not available on CTA pairs");
-    const int pairs = (int)(total < max_pairs[dev & 15] ? total : max_pairs[dev & 15]);
+    int pairs = (int)(total < max_pairs[dev & 15] ? total : max_pairs[dev & 15]);
+    if (BRES) {
+      // every pair keeps one N coordinate: the number of walkers is a multiple of the N-tile count
+      pairs -= pairs % p.tiles_n;
+      if (pairs < p.tiles_n || p.kblocks > Cfg::RES_KBLOCKS || p.splits != 1 || p.batch != 1 ||
+          p.epi == CCB_EPI_ROWSCALE_SILU || p.f8)
+        return set_error("ccb_gemm: shape not eligible for the resident-B pair layout (dispatch error)");
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(2 * pairs));
     cfg.blockDim = dim3(GEMM_THREADS);
@@ -977,6 +1015,14 @@ extern "C" int ccb_gemm_resident_b(int on) {
   if (on == 0 || on == 1) g_gemm_bres = on;
   return old;
 }
+// CTA pairs with the weight tile resident, half in each CTA (bit 1: K <= 256 with an eight-stage A ring,
+// bit 2: K in (256, 512] with a four-stage ring); 0: off.  Returns the old value.
+static int g_gemm_pair_resident = 0;
+extern "C" int ccb_gemm_pair_resident(int bits) {
+  const int old = g_gemm_pair_resident;
+  if (bits >= 0 && bits <= 3) g_gemm_pair_resident = bits;
+  return old;
+}
 static int g_gemm_cta_group = 1;
 extern "C" int ccb_gemm_cta_group(int cg) {
   const int old = g_gemm_cta_group;
@@ -1012,6 +1058,37 @@ extern "C" int ccb_gemm(const CcbGemmArgs* a, void* stream_) {
     // CTA pairs: bf16, K-major A, a whole number of 8-row-aligned rows per 256-row tile is not
     // needed (TMA clips), but tiny problems gain nothing; the 512-column RMSNorm-backward tile and
     // split-K stay on single CTAs
+    {
+      // pair + resident weight tile: K <= 256 with the deep A ring (BRES 1), K <= 512 (BRES 2)
+      const long long tiles_n = (a->N + 255) / 256, tiles_m2 = (a->M + 255) / 256;
+      const int pr = g_gemm_pair_resident;
+      const bool pres_ok = pr != 0 && !a->a_fp8 && a->a_mn == 0 && a->batch == 1 && a->splits <= 1 &&
+                           a->epi != CCB_EPI_ROWSCALE_SILU && !(a->epi == CCB_EPI_RMSBWD && a->N > 256) &&
+                           a->K % 64 == 0 && tiles_m2 * tiles_n >= ccb_num_sms() && tiles_n <= 8;
+      if (pres_ok && a->K <= 256 && (pr & 1)) {
+        if (key == 0) switch ((int)a->epi) {
+          case CCB_EPI_ROWSCALE: return launch_gemm<256, 0, 0, 0, CCB_EPI_ROWSCALE, 2, 1>(a, stream);
+          case CCB_EPI_RESID_SS: return launch_gemm<256, 0, 0, 0, CCB_EPI_RESID_SS, 2, 1>(a, stream);
+          default: return launch_gemm<256, 0, 0, 0, -1, 2, 1>(a, stream);
+        }
+        if (key == 1) switch ((int)a->epi) {
+          case CCB_EPI_DSILU: return launch_gemm<256, 0, 1, 0, CCB_EPI_DSILU, 2, 1>(a, stream);
+          case CCB_EPI_RMSBWD: return launch_gemm<256, 0, 1, 0, CCB_EPI_RMSBWD, 2, 1>(a, stream);
+          default: return launch_gemm<256, 0, 1, 0, -1, 2, 1>(a, stream);
+        }
+      }
+      if (pres_ok && a->K > 256 && a->K <= 512 && (pr & 2)) {
+        if (key == 1) switch ((int)a->epi) {
+          case CCB_EPI_DSILU: return launch_gemm<256, 0, 1, 0, CCB_EPI_DSILU, 2, 2>(a, stream);
+          case CCB_EPI_RMSBWD: return launch_gemm<256, 0, 1, 0, CCB_EPI_RMSBWD, 2, 2>(a, stream);
+          default: return launch_gemm<256, 0, 1, 0, -1, 2, 2>(a, stream);
+        }
+        if (key == 0) switch ((int)a->epi) {
+          case CCB_EPI_RESID_SS: return launch_gemm<256, 0, 0, 0, CCB_EPI_RESID_SS, 2, 2>(a, stream);
+          default: break;
+        }
+      }
+    }
     const bool pair_ok = g_gemm_cta_group == 2 && !a->a_fp8 && a->a_mn == 0 && a->M >= 512 &&
                          a->batch == 1 && a->splits <= 1 && !(a->epi == CCB_EPI_RMSBWD && a->N > 256);
     if (pair_ok && key == 0) {

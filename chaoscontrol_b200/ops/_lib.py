@@ -61,6 +61,7 @@ _SIGS = {
                                i64, vp], C.c_int),
     "ccb_scan_poly_exp": ([C.c_int], C.c_int),
     "ccb_gemm_pdl": ([C.c_int], C.c_int),
+    "ccb_gemm_pair_resident": ([C.c_int], C.c_int),
     "ccb_scan_fwd": ([vp, i64, vp, vp, vp, vp, vp, i64, i64, i64, i64, vp], C.c_int),
     "ccb_scan_bwd": ([vp, i64, vp, vp, vp, vp, vp, vp, f32, f32, vp, i64, vp, vp, i64, i64, i64, i64, vp],
                      C.c_int),
@@ -121,7 +122,8 @@ def lib() -> C.CDLL:
     _late_sigs(L)
     _lib = L
     # process-wide kernel switches from the environment (A/B measurements, test runs of a non-default mode)
-    for var, fn in (("CCB_GEMM_PDL", "ccb_gemm_pdl"), ("CCB_SCAN_ARITH", "ccb_scan_poly_exp")):
+    for var, fn in (("CCB_GEMM_PDL", "ccb_gemm_pdl"), ("CCB_SCAN_ARITH", "ccb_scan_poly_exp"),
+                    ("CCB_GEMM_PAIR_RESIDENT", "ccb_gemm_pair_resident")):
         val = os.environ.get(var)
         if val is not None and hasattr(L, fn):
             getattr(L, fn)(int(val))

@@ -140,6 +140,8 @@ def main() -> None:
                          "stages with X in shared memory (-1: library default)")
     ap.add_argument("--gemm-bres", type=int, default=-1, choices=[-1, 0, 1],
                     help="1: K <= 256 GEMMs keep their weight tile resident in shared memory (-1: library default)")
+    ap.add_argument("--gemm-pres", type=int, default=-1, choices=[-1, 0, 1, 2, 3],
+                    help="GEMM: CTA pairs with the weight tile resident (bit 1: K <= 256, bit 2: K <= 512)")
     ap.add_argument("--scan-poly", type=int, default=-1, choices=[-1, 0, 1, 2],
                     help="scan kernel arithmetic: 0 scalar, 1 scalar with FMA-pipe exponentials, 2 packed fp32x2")
     ap.add_argument("--gemm-l2pf", type=int, default=-2, choices=[-2, -1, 0, 1, 2, 3],
@@ -149,6 +151,8 @@ def main() -> None:
         _lib.lib().ccb_gemm_l2_prefetch(a.gemm_l2pf)
     if a.scan_poly >= 0:
         _lib.lib().ccb_scan_poly_exp(a.scan_poly)
+    if a.gemm_pres >= 0:
+        _lib.lib().ccb_gemm_pair_resident(a.gemm_pres)
     if a.gemm_bres >= 0:
         _lib.lib().ccb_gemm_resident_b(a.gemm_bres)
     if a.lmhead_deep >= 0:
@@ -180,7 +184,7 @@ def main() -> None:
     times.sort()
     ms = times[len(times) // 2]
     pk = peaks()
-    out = {"kernel": a.kernel, "rows": a.rows, "lmhead_parts": a.lmhead_parts or None, "gemm_cg": a.gemm_cg or None, "gemm_debug": a.gemm_debug or None, "gemm_bres": a.gemm_bres if a.gemm_bres >= 0 else None, "gemm_l2pf": a.gemm_l2pf if a.gemm_l2pf >= -1 else None, "lmhead_debug": a.lmhead_debug or None, "lmhead_deep": a.lmhead_deep if a.lmhead_deep >= 0 else None, "scan_poly": a.scan_poly if a.scan_poly >= 0 else None,
+    out = {"kernel": a.kernel, "rows": a.rows, "lmhead_parts": a.lmhead_parts or None, "gemm_cg": a.gemm_cg or None, "gemm_debug": a.gemm_debug or None, "gemm_bres": a.gemm_bres if a.gemm_bres >= 0 else None, "gemm_l2pf": a.gemm_l2pf if a.gemm_l2pf >= -1 else None, "lmhead_debug": a.lmhead_debug or None, "lmhead_deep": a.lmhead_deep if a.lmhead_deep >= 0 else None, "scan_poly": a.scan_poly if a.scan_poly >= 0 else None, "gemm_pres": a.gemm_pres if a.gemm_pres >= 0 else None,
            "ms_median": ms, "ms_min": times[0],
            "GBps": nbytes / ms / 1e6, "frac_hbm": nbytes / ms / 1e6 / pk["hbm_gbs"],
            "TFLOPs": flops / ms / 1e9, "frac_bf16_burst": flops / ms / 1e9 / pk["bf16_tflops"],

@@ -12,13 +12,19 @@ from chaoscontrol_b200.ops import gemm as G
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(params=["pairs", "resident"])
+@pytest.fixture(params=["pairs", "resident", "pair_resident"])
 def pairs(request):
     L = _lib.lib()
     if request.param == "pairs":
         old = L.ccb_gemm_cta_group(2)
         yield
         L.ccb_gemm_cta_group(old)
+    elif request.param == "pair_resident":
+        # CTA pairs with the weight tile resident (half per CTA): K <= 256 and K in (256, 512]; shapes the
+        # layout does not take fall through to the default kernel
+        old = L.ccb_gemm_pair_resident(3)
+        yield
+        L.ccb_gemm_pair_resident(old)
     else:
         old = L.ccb_gemm_resident_b(1)
         yield
@@ -27,12 +33,13 @@ def pairs(request):
 
 def _default_layout(fn):
     L = _lib.lib()
-    cg, rb = L.ccb_gemm_cta_group(1), L.ccb_gemm_resident_b(0)
+    cg, rb, pr = L.ccb_gemm_cta_group(1), L.ccb_gemm_resident_b(0), L.ccb_gemm_pair_resident(0)
     try:
         return fn()
     finally:
         L.ccb_gemm_cta_group(cg)
         L.ccb_gemm_resident_b(rb)
+        L.ccb_gemm_pair_resident(pr)
 
 
 def _rand(*shape, scale=1.0):
@@ -48,7 +55,8 @@ def _close(got, ref, rtol=2e-2, atol=2e-2):
 
 @pytest.mark.parametrize("M,N,K", [(512, 256, 64), (512, 256, 256), (1000, 768, 256), (640, 512, 320),
                                    (4096, 1024, 256), (513, 200, 128), (5000, 256, 1024),
-                                   (40000, 256, 256), (20001, 1024, 192), (19000, 512, 256), (37999, 200, 64)])
+                                   (40000, 256, 256), (20001, 1024, 192), (19000, 512, 256), (37999, 200, 64),
+                                   (40000, 256, 512), (38001, 512, 448)])
 def test_pair_gemm_tn(pairs, M, N, K):
     torch.manual_seed(0)
     a, b = _rand(M, K), _rand(N, K)
@@ -60,7 +68,7 @@ def test_pair_gemm_tn(pairs, M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K", [(512, 256, 256), (1024, 304, 128), (4096, 512, 256), (777, 256, 512),
-                                   (38000, 256, 256), (19001, 512, 128)])
+                                   (38000, 256, 256), (19001, 512, 128), (38000, 256, 512), (40001, 512, 384)])
 def test_pair_gemm_b_mn(pairs, M, N, K):
     torch.manual_seed(1)
     a, b = _rand(M, K), _rand(K, N)
@@ -69,7 +77,7 @@ def test_pair_gemm_b_mn(pairs, M, N, K):
     _close(out, G.gemm_reference(a, b, b_mn=True), atol=0.05 * (K ** 0.5) / 16)
 
 
-@pytest.mark.parametrize("M", [640, 4096, 9000, 40100])
+@pytest.mark.parametrize("M", [640, 4096, 9000, 40100, 76001])
 def test_pair_gemm_epilogues(pairs, M):
     torch.manual_seed(4)
     D, F = 256, 512

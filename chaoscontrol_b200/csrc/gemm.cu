@@ -87,6 +87,11 @@ constexpr int BRES_KBLOCKS = 4;
 // room to spare: BRES = 1 holds K <= 256 (64 KiB) and gives the A ring eight stages (two tiles of A in
 // flight per CTA); BRES = 2 holds K <= 512 (128 KiB) with a four-stage ring, which takes the weight
 // re-reads (256 KiB from L2 per 128-row tile on a single CTA) out of the K = 512 input-gradient GEMMs.
+// Measured at 524 288 rows against the single-CTA kernels (bit-identical outputs): packed projection
+// 0.437 vs 0.331 ms, out_proj + residual 0.197 vs 0.177, dSiLU 0.367 vs 0.320, RMSNorm backward (K = 512)
+// 0.386 vs 0.361, whole step 33.9 vs 33.3 ms.  A pair couples two SMs' load streams to one MMA issuer, so
+// either CTA's late stage stalls both; on these memory-bound shapes that costs more than the saved weight
+// traffic.  Kept behind ccb_gemm_pair_resident (default off), like the plain pair mode.
 
 template <int BN, int CG = 1, int BRES = 0>
 struct GemmCfg {

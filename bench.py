@@ -205,6 +205,51 @@ def _timed(fn_step, n: int, ws: int) -> float:
     return _max_over_ranks(e0.elapsed_time(e1), ws) / n
 
 
+class _E2EFeeder:
+    """The end-to-end loop of either arm: the next batch is copied from pinned host memory on a copy
+    stream while the current step computes (two device buffers), and every step's loss is copied to
+    pinned host memory asynchronously and read by the host one step later, so the host never blocks
+    on the step it has just launched.  ``run_step(block) -> loss tensor`` is the arm's own step."""
+
+    FEEDING = ("batch copied from pinned host memory on a copy stream one step ahead (two device buffers); "
+               "loss copied to pinned host memory every step and read by the host one step later")
+
+    def __init__(self, host_batches, dev, run_step):
+        import torch
+        self.torch, self.host, self.run_step = torch, host_batches, run_step
+        self.copy_stream = torch.cuda.Stream()
+        self.dev_buf = [torch.empty_like(host_batches[0], device=dev) for _ in range(2)]
+        self.filled = [torch.cuda.Event() for _ in range(2)]
+        self.consumed = [torch.cuda.Event() for _ in range(2)]
+        self.host_loss = torch.zeros(2, dtype=torch.float32).pin_memory()
+        self.loss_done = [torch.cuda.Event() for _ in range(2)]
+        self.read: list[float] = []
+        for ev in self.consumed:
+            ev.record()
+        self._prefetch(0)
+        self.k = 0
+
+    def _prefetch(self, i):
+        torch, j = self.torch, i % 2
+        with torch.cuda.stream(self.copy_stream):
+            self.copy_stream.wait_event(self.consumed[j])
+            self.dev_buf[j].copy_(self.host[i % len(self.host)], non_blocking=True)
+            self.filled[j].record(self.copy_stream)
+
+    def step(self, _i=None):
+        torch, k = self.torch, self.k
+        torch.cuda.current_stream().wait_event(self.filled[k % 2])
+        loss = self.run_step(self.dev_buf[k % 2])
+        self.consumed[k % 2].record()
+        self._prefetch(k + 1)
+        if k >= 1:                                   # the previous step's loss has had a whole step to arrive
+            self.loss_done[(k - 1) % 2].synchronize()
+            self.read.append(float(self.host_loss[(k - 1) % 2]))
+        self.host_loss[k % 2: k % 2 + 1].copy_(loss.detach().float().reshape(1), non_blocking=True)
+        self.loss_done[k % 2].record()
+        self.k += 1
+
+
 # ---------------------------------------------------------------------------
 def run_ours(args):
     import torch
@@ -310,31 +355,33 @@ def run_ours(args):
     if not args.no_e2e:
         h2d = host[0].numel() * host[0].element_size()
 
-        def step_e2e(i):
-            blk = host[i % len(host)].to(dev, non_blocking=True)
+        def run_block(blk):
             inputs, targets = blk[:, :-1], blk[:, 1:]
             if gstep is not None:
                 loss = gstep(inputs, targets)
                 opt.step()
+                return loss
+            opt.zero_grad(set_to_none=True)
+            loss = train_ssm_step(model, inputs, targets, 64, ddp_active=ws > 1 and dist_opt is None,
+                                  world_size=ws, precision="bf16",
+                                  lm_head_backward_mode="fused_streaming_cached", lm_head_tile_size=8192)
+            if dist_opt is not None:
+                dist_opt.step()
             else:
-                opt.zero_grad(set_to_none=True)
-                loss = train_ssm_step(model, inputs, targets, 64, ddp_active=ws > 1 and dist_opt is None,
-                                      world_size=ws, precision="bf16",
-                                      lm_head_backward_mode="fused_streaming_cached", lm_head_tile_size=8192)
-                if dist_opt is not None:
-                    dist_opt.step()
-                else:
-                    clip_arena_grad_norm(arena, CLIP)
-                    opt.step()
-            step_e2e.last = float(loss.item())
+                clip_arena_grad_norm(arena, CLIP)
+                opt.step()
+            return loss
 
+        feeder = _E2EFeeder(host, dev, run_block)
+        step_e2e = feeder.step
         for i in range(max(3, args.warmup // 2)):
             step_e2e(i)
         ms_e = _timed(step_e2e, args.steps, ws)
         e2e = {"value": ws * args.batch * args.seq / (ms_e / 1e3), "unit": "tokens/s",
                "ms_per_step": ms_e, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
                "api": ("chaoscontrol_b200.train_ssm.GraphedTrainStep + Muon.step" if gstep is not None else
-                       "chaoscontrol_b200.train_ssm.train_ssm_step + Muon.step")}
+                       "chaoscontrol_b200.train_ssm.train_ssm_step + Muon.step"),
+               "feeding": _E2EFeeder.FEEDING, "losses_read_on_host": len(feeder.read)}
 
     toks = ws * args.batch * args.seq / (ms / 1e3)
     headline = args.config == "submission"
@@ -749,10 +796,8 @@ def run_fp8(args):
     final_loss = float(torch.stack([l.float() for l in losses[-args.steps:]]).mean().item())
     h2d = host[0].numel() * host[0].element_size()
 
-    def step_e2e(i):
-        blk = host[i % len(host)].to(dev, non_blocking=True)
-        step_e2e.last = float(one(blk[:, :-1].to(torch.int32), blk[:, 1:]).item())
-
+    feeder = _E2EFeeder(host, dev, lambda blk: one(blk[:, :-1].to(torch.int32), blk[:, 1:]))
+    step_e2e = feeder.step
     for i in range(3):
         step_e2e(i)
     ms_e = _timed(step_e2e, args.steps, ws)
@@ -957,16 +1002,15 @@ def run_reference(args):
     if not args.no_e2e:
         h2d = host[0].numel() * host[0].element_size()
 
-        def step_e2e(i):
-            blk = host[i % len(host)].to(dev, non_blocking=True)
-            step_e2e.last = float(one(blk[:, :-1].to(torch.int32), blk[:, 1:]).item())
-
+        feeder = _E2EFeeder(host, dev, lambda blk: one(blk[:, :-1].to(torch.int32), blk[:, 1:]))
+        step_e2e = feeder.step
         for i in range(max(3, args.warmup // 2)):
             step_e2e(i)
         ms_e = _timed(step_e2e, args.steps, ws)
         e2e = {"value": ws * args.batch * args.seq / (ms_e / 1e3), "unit": "tokens/s",
                "ms_per_step": ms_e, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
-               "api": "chaoscontrol.train_ssm.train_ssm_step + Muon.step"}
+               "api": "chaoscontrol.train_ssm.train_ssm_step + Muon.step",
+               "feeding": _E2EFeeder.FEEDING, "losses_read_on_host": len(feeder.read)}
 
     toks = ws * args.batch * args.seq / (ms / 1e3)
     headline = args.config == "submission"

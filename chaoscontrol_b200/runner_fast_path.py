@@ -436,7 +436,9 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
                           spectral_reg_lambda_dead: float = 0.0, spectral_reg_lambda_sticky: float = 0.0,
                           spectral_reg_min_a: float = 0.05, spectral_reg_max_a: float = 0.98,
                           predictive_aux_weight: float = 0.0, predictive_aux_horizon: int = 0,
-                          predictive_aux_dim: int = 0,
+                          predictive_aux_dim: int = 0, scopt_split_interval: int = 4,
+                          scopt_baseline_buckets: int = 16, scopt_baseline_decay: float = 0.99,
+                          scopt_pressure_upper_c: Optional[float] = None, scopt_pressure_upper_floor: float = 1.0,
                           time_fn: Callable[[], float] = time.perf_counter, **unused: Any) -> dict[str, Any]:
     """Budgeted hot loop.  Returns the train-result dict (``steps``, ``elapsed_s``,
     ``initial_loss``, ``final_loss``, ``loss_history``, throughput keys,
@@ -450,6 +452,20 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
         raise ValueError("replay_eviction_enabled needs crct_enabled: slot maintenance runs beside the teacher")
     if event_sleep_enabled and not dreamworld_enabled:
         raise ValueError("event_sleep_enabled requires dreamworld_enabled=True")
+    # the scarcity-aware optimizer is fed by its own step (pressure from CE, rare gradients on split steps)
+    from .optim.scopt import FrequencyBucketBaseline, ScarcityAwareOptimizer
+    scopt_on = isinstance(optimizer, ScarcityAwareOptimizer)
+    scopt_freq = scopt_baseline = None
+    if scopt_on:
+        if crct_enabled or episodic is not None or dreamworld_enabled or distributed_muon:
+            raise ValueError("optimizer 'scopt' runs its own training step: not combinable with crct / episodic / "
+                             "dreamworld / distributed_muon")
+        V = int(vocab_size or model.lm_head.weight.shape[0])
+        scopt_freq = torch.bincount(train_tokens[: int(train_num_tokens)].to(torch.int64).clamp_(0, V - 1),
+                                    minlength=V).to(device=device, dtype=torch.float32)
+        scopt_baseline = FrequencyBucketBaseline(scopt_freq, num_buckets=int(scopt_baseline_buckets),
+                                                 decay=float(scopt_baseline_decay), device=device)
+    scopt_stats = {"split_steps": 0, "clipped": 0}
     if dreamworld_enabled and crct_enabled:
         raise ValueError("dreamworld_enabled and crct_enabled cannot be combined in this runner")
     if episodic is not None and (crct_enabled or dreamworld_enabled or criticality is not None):
@@ -692,6 +708,14 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
                     allreduce_grads(model, world_size)
                     if aux_proj is not None:
                         allreduce_grads(aux_proj, world_size)
+            elif scopt_on:
+                from .optim.scopt_step import run_scopt_train_step
+                loss, scopt_pending = run_scopt_train_step(
+                    model=model, optimizer=optimizer, inputs=inputs, targets=targets, step=steps,
+                    split_interval=int(scopt_split_interval), token_frequencies=scopt_freq, ddp_active=ddp,
+                    world_size=world_size, precision=precision, baseline=scopt_baseline,
+                    pressure_upper_c=scopt_pressure_upper_c, pressure_upper_floor=float(scopt_pressure_upper_floor),
+                    lm_head_backward_mode=lm_head_backward_mode, lm_head_tile_size=lm_head_tile_size)
             elif crct_enabled:
                 payload = None
                 if crct is not None:
@@ -725,6 +749,19 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
             zero_embedding_grad_until(model, steps, embed_freeze_steps)
             if dist_opt is not None:
                 dist_opt.step()                     # reduce (sharded) + clip + owned update + gather
+            elif scopt_on:
+                # the rare side is committed only when the step was not clipped
+                from .optim.scopt_step import apply_pending
+                clipped = False
+                if grad_clip_norm > 0:
+                    total = torch.nn.utils.clip_grad_norm_(model.parameters(), grad_clip_norm)
+                    clipped = bool(total > grad_clip_norm)
+                    optimizer.record_clip_event(triggered=clipped)
+                apply_pending(optimizer, scopt_pending, skip=clipped)
+                if scopt_pending is not None:
+                    scopt_stats["split_steps"] += 1
+                    scopt_stats["clipped"] += int(clipped)
+                optimizer.step()
             else:
                 _clip(model, grad_clip_norm, fused_grad_clip)
                 optimizer.step()
@@ -784,6 +821,9 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
                                     "projection_norm": float(aux_proj.weight.detach().float().norm())}
     if spectral_on:
         result["spectral"]["regularized_steps"] = aux_stats["spectral_steps"]
+    if scopt_on:
+        result["scopt"] = {"split_interval": int(scopt_split_interval), "split_steps": scopt_stats["split_steps"],
+                           "clipped_split_steps": scopt_stats["clipped"], "trace": optimizer.scarcity_trace()}
     if criticality is not None:
         result["criticality_distillation"] = criticality.diagnostics()
     if dream_buffer is not None:
@@ -812,7 +852,8 @@ _LOOP_KEYS = ("chunk_size", "grad_clip_norm", "fused_grad_clip", "precision", "s
               "embed_freeze_steps", "distributed_muon", "crct_enabled",
               "replay_eviction_enabled", "spectral_reg_lambda_dead", "spectral_reg_lambda_sticky",
               "spectral_reg_min_a", "spectral_reg_max_a", "predictive_aux_weight", "predictive_aux_horizon",
-              "predictive_aux_dim") + _DREAM_KEYS
+              "predictive_aux_dim", "scopt_split_interval", "scopt_baseline_buckets", "scopt_baseline_decay",
+              "scopt_pressure_upper_c", "scopt_pressure_upper_floor") + _DREAM_KEYS
 
 
 def _loop_kwargs(config: dict[str, Any]) -> dict[str, Any]:

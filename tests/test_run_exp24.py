@@ -116,7 +116,7 @@ _CELLS = [("first_wave", "fastslow_i32_a050", "fast_slow"),
           ("first_wave", "spectral_dead", "spectral"),
           ("first_wave", "predictive_h4", "predictive_aux"),
           ("first_wave", "eventsleep", "dreamworld"),
-          ("scopt_overhead_gate", "scopt_gate_scopt", None),
+          ("scopt_overhead_gate", "scopt_gate_scopt", "scopt"),
           ("semantic_overhead_gate", "semantic_gate_semantic", None),
           ("phase_a_sampling", "shuffled_epoch", None),
           ("cd_first_smoke", "treatment", "criticality_distillation"),
@@ -152,6 +152,11 @@ def test_bundle_cell_runs_through_the_runner(tmp_path, monkeypatch, matrix, arm,
     assert tr["steps"] == 6 and np.isfinite(tr["final_loss"])
     if block:
         assert block in tr, sorted(tr)
+    if block == "scopt":
+        # every fourth step is a split step once the optimizer's warm-up allows writes: rare gradients and
+        # channel pressures reached the optimizer
+        assert 1 <= tr["scopt"]["split_steps"] <= 2 and tr["scopt"]["trace"]["step"] == 6
+        assert "row_pressure" in tr["scopt"]["trace"] and "pressure_stats" in tr["scopt"]["trace"]
     if block == "spectral":
         assert tr["spectral"]["regularized_steps"] == 6
     if block == "predictive_aux":

@@ -4,7 +4,8 @@ The reference keeps one runner script per study (experiments/09_revised_architec
 run_layered.py, 10_scaling_laws/run_scaling.py, 11_sleep_cycle/run_sleep_ablation.py,
 12_polyphasic_sleep/run_polyphasic_ablation.py, 13_constants_validation/
 run_constants_sweep.py, 14_vram_buffer/run_exp14.py, 15_chaospiece/run_exp15.py,
-16_entropy_sparse_attention/run_exp16.py, 17_local_attn_sidecar/run_exp17.py), each
+16_entropy_sparse_attention/run_exp16.py, 17_local_attn_sidecar/run_exp17.py, and
+experiments/baselines/run_mamba2_baseline.py), each
 repeating the launch loop and its own copy of the statistics.  Here a study is a
 :class:`Study` value -- base envelopes, named conditions, seeds, pre-registered
 contrasts and a decision rule -- and one engine does the rest:
@@ -569,8 +570,50 @@ LOCAL_ATTENTION = Study(
     + tuple(Contrast(f"topk_{k}_vs_random", f"topk_random_{k}", f"topk_{k}", "does the selection matter, or only the compute?")
             for k in (8, 16, 32)))
 
+# architecture baseline ablation (experiments/baselines/run_mamba2_baseline.py:57-110): external SSM vs this
+# core vs typed routing vs the full stack, and the routing width sweep at a constant expert parameter budget
+EXPERT_DIM_FOR_K = {16: 0, 32: 32, 64: 16}          # 0 = full-rank experts; k_max * 2 * expert_dim * 128 stays at 262 144
+
+
+def _routed(k: int, **over: Any) -> dict:
+    return _byte_stack(wernicke_enabled=True, wernicke_router="moe", wernicke_k_max=k, typed_storage=True,
+                       wernicke_expert_dim=EXPERT_DIM_FOR_K.get(k, 0), **over)
+
+
+def _routed_mem(k: int) -> dict:
+    return _routed(k, outer_model_type="multislot", outer_model_dim=64, outer_max_slots=64,
+                   consolidation_write="full_sequence", latent_persistence=True)
+
+
+def _decide_architecture(conf: dict) -> str:
+    full, core = conf.get("full_vs_mamba2"), conf.get("core_vs_mamba2")
+    if full is None or core is None:
+        return "no data"
+    beats = lambda r: r["mean_delta"] < 0 and r["significant"]       # noqa: E731
+    if beats(full):
+        return "FULL STACK BEATS MAMBA-2" + (" (CORE ALONE TOO)" if beats(core) else "")
+    return "CORE COMPETITIVE, STACK NOT AHEAD" if not (core["mean_delta"] > 0 and core["significant"]) else "MAMBA-2 AHEAD"
+
+
+ARCHITECTURE_BASELINES = Study(
+    "baselines_mamba2", "how much does each architectural layer contribute, against an external SSM?",
+    {"mamba2": _byte_stack(model_type="mamba2"), "bare_ssm": _byte_stack(),
+     "ssm_wernicke_k16": _routed(16), "full_stack_k16": _routed_mem(16),
+     "ssm_wernicke_k32": _routed(32), "ssm_wernicke_k64": _routed(64),
+     "full_stack_k32": _routed_mem(32), "full_stack_k64": _routed_mem(64)},
+    confirmatory=(Contrast("full_vs_mamba2", "mamba2", "full_stack_k16", "does the full architecture beat Mamba-2?"),
+                  Contrast("core_vs_mamba2", "mamba2", "bare_ssm", "is the SSM core competitive with Mamba-2?")),
+    exploratory=(Contrast("wernicke_contribution", "bare_ssm", "ssm_wernicke_k16"),
+                 Contrast("memory_contribution", "ssm_wernicke_k16", "full_stack_k16"),
+                 Contrast("wernicke_k32", "ssm_wernicke_k16", "ssm_wernicke_k32"),
+                 Contrast("wernicke_k64", "ssm_wernicke_k16", "ssm_wernicke_k64"),
+                 Contrast("full_k32", "full_stack_k16", "full_stack_k32"),
+                 Contrast("full_k64", "full_stack_k16", "full_stack_k64")),
+    decide=_decide_architecture)
+
 STUDIES: dict[str, Study] = {s.key: s for s in (SLEEP_CYCLE, POLYPHASIC, CONSTANTS, BUFFER_RETRIEVAL, BUFFER_ROUTING,
-                                                BUFFER_COMPOSITION, SUBWORD_SHAPES, SPARSE_ATTENTION, LOCAL_ATTENTION)}
+                                                BUFFER_COMPOSITION, SUBWORD_SHAPES, SPARSE_ATTENTION, LOCAL_ATTENTION,
+                                                ARCHITECTURE_BASELINES)}
 
 
 # ---------------------------------------------------------------------------

@@ -57,6 +57,21 @@ def test_flat_study_matrices_carry_the_reference_condition_names():
     assert S.resolve_data_paths("/d", 8192) == ("/d/datasets/fineweb10B_sp8192", "/d/tokenizers/fineweb_8192_bpe.model")
 
 
+def test_architecture_baseline_study(tmp_path):
+    st = S.ARCHITECTURE_BASELINES
+    assert list(st.conditions)[:4] == ["mamba2", "bare_ssm", "ssm_wernicke_k16", "full_stack_k16"] and len(st.conditions) == 8
+    assert st.conditions["ssm_wernicke_k64"]["wernicke_expert_dim"] == 16 and st.conditions["full_stack_k32"]["outer_max_slots"] == 64
+    assert st.conditions["mamba2"]["model_type"] == "mamba2" and "wernicke_enabled" not in st.conditions["bare_ssm"]
+    for i, s in enumerate(S.SEEDS7):
+        j = 0.001 * ((i * 3) % 4)
+        _write(tmp_path, "mamba2", s, 1.80 + j)
+        _write(tmp_path, "bare_ssm", s, 1.80 + j + (0.002 if i % 2 else -0.002))
+        _write(tmp_path, "full_stack_k16", s, 1.70 + j)
+    out = S.analyse(st, tmp_path)
+    assert out["decision"] == "FULL STACK BEATS MAMBA-2"
+    assert {r["name"]: r["significant"] for r in out["confirmatory"]} == {"full_vs_mamba2": True, "core_vs_mamba2": False}
+
+
 def _write(d, cond, seed, bpb):
     d.mkdir(parents=True, exist_ok=True)
     (d / f"{cond}_s{seed}.json").write_text(json.dumps({"eval": {"bpb": bpb}, "train": {"final_loss": 1.0}}))

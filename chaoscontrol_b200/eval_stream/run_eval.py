@@ -138,6 +138,13 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     if a.config:
         import yaml
         fields.update(yaml.safe_load(a.config.read_text()) or {})
+        # matrix builders write a label and the data paths beside the run fields; flags win over them
+        fields.pop("name", None)
+        fields.pop("phase", None)
+        for key in ("val_cache_dir", "jsonl_paths", "sp_model_path"):
+            v = fields.pop(key, None)
+            if getattr(a, key) is None and v:
+                setattr(a, key, v)
     for k, v in vars(a).items():
         if v is not None and k not in ("config", "val_cache_dir", "jsonl_paths", "sp_model_path", "optimizer", "eager"):
             fields[k] = v

@@ -9,8 +9,11 @@
                           (summarize_phase1.py:1-60 rules)
 * ``fit_power_law``       ``bpb = A * params^-alpha + bpb_irr`` (experiments/10_scaling_laws/
                           analyze_scaling.py:120-200), closed-form in log space over a grid of ``bpb_irr``
+* ``curation_gate``       four-arm replay-curation falsifier: rare-bucket deltas, the tie band, the
+                          spread that asks for more seeds, the four verdicts
+                          (experiments/24_training_time_bundle/analyze_episodic_dw_curation_v1.py:52-170)
 * ``render_markdown``     tables for a report
-* CLI: ``python -m chaoscontrol_b200.analysis summarize|compare|scaling ...``
+* CLI: ``python -m chaoscontrol_b200.analysis summarize|compare|scaling|curation ...``
 """
 from __future__ import annotations
 
@@ -21,7 +24,8 @@ from pathlib import Path
 from typing import Any, Iterable, Optional, Sequence
 
 __all__ = ["load_results", "extract_metrics", "summary_table", "paired_ttest", "paired_comparison",
-           "lever_verdict", "fit_power_law", "render_markdown", "main"]
+           "lever_verdict", "fit_power_law", "curation_gate", "load_curation_cells", "render_curation",
+           "render_markdown", "main"]
 
 
 # ---------------------------------------------------------------------------
@@ -250,6 +254,91 @@ def render_markdown(rows: Sequence[dict], columns: Optional[Sequence[str]] = Non
     return "\n".join(lines) + "\n"
 
 
+# ---------------------------------------------------------------------------
+# replay-curation falsifier (uncurated / cosine x utility / pressure only / no replay)
+# ---------------------------------------------------------------------------
+CURATION_ARMS = ("arm_a_uncurated", "arm_b_cosine_utility", "arm_bp_pressure_only", "arm_c_no_dw")
+CURATION_DELTA_MIN = 0.005          # rare-bucket gain (bpb) that counts as a pass
+CURATION_SIGMA_ESCALATE = 0.008     # spread of the curated arm above which three more seeds are due
+CURATION_VERDICTS = {
+    "pass_mechanism_specific": "PASS, mechanism-specific: the curated query beats both uncurated replay and the "
+                               "pressure-only query on the rarest bucket",
+    "pass_mechanism_agnostic": "PASS, mechanism-agnostic: curated beats uncurated but ties the pressure-only query",
+    "mixed_null": "MIXED / NULL: curation did not beat uncurated replay",
+    "regression": "REGRESSION: curation is worse than uncurated replay",
+}
+
+
+def _mean_se(v: Sequence[float]) -> tuple[float, float]:
+    if len(v) < 2:
+        return (float(v[0]) if v else float("nan")), float("nan")
+    return _mean(v), _std(v) / math.sqrt(len(v))
+
+
+def load_curation_cells(results_dir: Path | str) -> dict[str, list[dict[str, float]]]:
+    """``{arm: [{"rare", "overall", "seed"}]}`` from the result files of the curation matrix.  The rare
+    figure is the first entry of the per-bucket validation list (buckets are ordered rarest first), read
+    from the result itself, its ``train`` block, or the summary file it points at."""
+    out: dict[str, list[dict[str, float]]] = {a: [] for a in CURATION_ARMS}
+    files = sorted(Path(results_dir).glob("*episodic_dw_curation_v1_*.json"))
+    if not files:
+        raise FileNotFoundError(f"no curation cells under {results_dir}")
+    for f in files:
+        cell = json.loads(f.read_text())
+        name = str(cell.get("name") or _get(cell, "config.name") or f.stem)
+        arm = next((a for a in CURATION_ARMS if a in name), None)
+        if arm is None:
+            raise ValueError(f"cannot tell the arm of {name!r}")
+        tr = cell.get("train") or {}
+        buckets = (cell.get("val_per_bucket_bpb") or tr.get("val_per_bucket_bpb") or cell.get("per_bucket_val_ce")
+                   or tr.get("per_bucket_val_ce"))
+        if buckets is None and cell.get("val_summary_path"):
+            buckets = json.loads(Path(cell["val_summary_path"]).read_text()).get("val_per_bucket_bpb")
+        if not buckets:
+            raise ValueError(f"{name!r} carries no per-bucket validation figures")
+        overall = cell.get("val_bpb", _get(cell, "eval.bpb"))
+        out[arm].append({"rare": float(buckets[0]), "overall": float("nan") if overall is None else float(overall),
+                         "seed": float(_get(cell, "config.seed", cell.get("seed", -1)))})
+    return out
+
+
+def curation_gate(cells: dict[str, list[dict[str, float]]]) -> dict[str, Any]:
+    rare = {a: [c["rare"] for c in cells.get(a, [])] for a in CURATION_ARMS}
+    a_mean, _ = _mean_se(rare["arm_a_uncurated"])
+    b_mean, b_se = _mean_se(rare["arm_b_cosine_utility"])
+    bp_mean, bp_se = _mean_se(rare["arm_bp_pressure_only"])
+    c_mean, _ = _mean_se(rare["arm_c_no_dw"])
+    nz = lambda x: 0.0 if math.isnan(x) else x                                                # noqa: E731
+    d_a, d_bp = b_mean - a_mean, b_mean - bp_mean                  # negative = the curated arm is better
+    sigma_b = _std(rare["arm_b_cosine_utility"]) if len(rare["arm_b_cosine_utility"]) >= 2 else float("nan")
+    ties_bp = abs(d_bp) < 2.0 * math.hypot(nz(b_se), nz(bp_se))
+    if d_a >= 0:
+        verdict = "regression" if d_a > 2.0 * nz(b_se) else "mixed_null"
+    elif abs(d_a) < CURATION_DELTA_MIN:
+        verdict = "mixed_null"
+    else:
+        verdict = "pass_mechanism_agnostic" if ties_bp else "pass_mechanism_specific"
+    return {"verdict": verdict, "delta_b_vs_a": d_a, "delta_b_vs_bp": d_bp, "sigma_b": sigma_b,
+            "needs_escalation": (not math.isnan(sigma_b)) and sigma_b > CURATION_SIGMA_ESCALATE,
+            "rare_means": {"A": a_mean, "B": b_mean, "Bp": bp_mean, "C": c_mean},
+            "by_arm_count": {a: len(rare[a]) for a in CURATION_ARMS}}
+
+
+def render_curation(cells: dict[str, list[dict[str, float]]], gate: dict[str, Any]) -> str:
+    rows = []
+    for a in CURATION_ARMS:
+        m, se = _mean_se([c["rare"] for c in cells.get(a, [])])
+        om, _ = _mean_se([c["overall"] for c in cells.get(a, [])])
+        rows.append({"arm": a, "n": len(cells.get(a, [])), "rare_mean": m, "rare_stderr": se, "overall_mean": om})
+    tail = [f"rare-bucket delta, curated - uncurated: {gate['delta_b_vs_a']:+.4f} bpb (negative = curated better)",
+            f"rare-bucket delta, curated - pressure-only: {gate['delta_b_vs_bp']:+.4f} bpb",
+            f"spread of the curated arm: {gate['sigma_b']:.4f} bpb"
+            + (f" (> {CURATION_SIGMA_ESCALATE}: run three more seeds of A, B and B' before deciding)"
+               if gate["needs_escalation"] else ""),
+            "verdict: " + CURATION_VERDICTS[gate["verdict"]]]
+    return render_markdown(rows) + "\n" + "\n".join(tail) + "\n"
+
+
 def main(argv: Optional[Sequence[str]] = None) -> int:
     ap = argparse.ArgumentParser(prog="chaoscontrol_b200.analysis")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -266,7 +355,13 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     g = sub.add_parser("scaling")
     g.add_argument("paths", nargs="+")
     g.add_argument("--by", default="arm")
+    q = sub.add_parser("curation")
+    q.add_argument("results_dir")
     a = ap.parse_args(argv)
+    if a.cmd == "curation":
+        cells = load_curation_cells(a.results_dir)
+        print(render_curation(cells, curation_gate(cells)))
+        return 0
     rows = load_results(a.paths)
     if a.cmd == "summarize":
         print(render_markdown(summary_table(rows, a.metric, a.by)))

@@ -176,6 +176,43 @@ def eval_quant(*, ckpt: Path, val_cache_dir: Path, output_json: Path, device: st
 
 
 # ---------------------------------------------------------------------------
+# artifact headroom of a wider trunk
+# ---------------------------------------------------------------------------
+MEASURED_DIM256_COMPRESSED_BYTES = 7_375_816     # int6 + LZMA size of a trained 4 x 256, V 16384 trunk
+ARTIFACT_LIMIT_BYTES = 16_000_000
+DEFAULT_OVERHEAD_BYTES = 500_000
+
+
+def artifact_headroom(*, dim: int = 384, vocab_size: int = 16_384, num_layers: int = 4, ff_mult: int = 2,
+                      overhead_bytes: int = DEFAULT_OVERHEAD_BYTES, measure: bool = False) -> dict:
+    """Will a ``dim``-wide bare-SSM trunk fit the 16 000 000-byte artifact?  The estimate scales the measured
+    compressed size of the 256-wide trunk by the ratio of raw bf16 sizes
+    (experiments/24_crct/validate_dim384_artifact.py:58-100).  ``measure`` additionally quantises a freshly
+    initialised model of that shape to int6 and LZMA-packs it -- an upper bound in practice, since random
+    weights compress worse than trained ones."""
+    from .models.model import CareStudentLM
+
+    def build(d: int):
+        return CareStudentLM(vocab_size=vocab_size, dim=d, num_layers=num_layers, ff_mult=ff_mult, a_mode="diag",
+                             rich_b_mode="none", outer_model_dim=0)
+    model = build(dim)
+    raw, base_raw = int(model.artifact_bytes()), int(build(256).artifact_bytes())
+    compressed = int(round(raw * MEASURED_DIM256_COMPRESSED_BYTES / float(base_raw)))
+    total = compressed + int(overhead_bytes)
+    out = {"dim": int(dim), "vocab_size": int(vocab_size), "num_layers": int(num_layers), "raw_bf16_bytes": raw,
+           "baseline_dim256_raw_bf16_bytes": base_raw, "estimated_compressed_model_bytes": compressed,
+           "overhead_bytes": int(overhead_bytes), "estimated_total_bytes": total,
+           "margin_bytes": ARTIFACT_LIMIT_BYTES - total, "controller_params": 0,
+           "under_budget": total < ARTIFACT_LIMIT_BYTES}
+    if measure:
+        from .artifact import _collect_state, _pack
+        state = _collect_state(model, None, {"dim": dim}, None, None, None)
+        blob, _ = _pack(state, "int6", 6, None)
+        out["measured_random_init_int6_bytes"] = len(blob)
+    return out
+
+
+# ---------------------------------------------------------------------------
 def main(argv: Optional[Sequence[str]] = None) -> int:
     ap = argparse.ArgumentParser(prog="chaoscontrol_b200.cli")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -207,7 +244,24 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     e.add_argument("--calibration-seqs", type=int, default=16)
     e.add_argument("--calibration-seq-len", type=int, default=128)
     e.add_argument("--seed", type=int, default=0)
+    h = sub.add_parser("artifact-headroom")
+    h.add_argument("--dim", type=int, default=384)
+    h.add_argument("--vocab-size", type=int, default=16_384)
+    h.add_argument("--num-layers", type=int, default=4)
+    h.add_argument("--ff-mult", type=int, default=2)
+    h.add_argument("--overhead-bytes", type=int, default=DEFAULT_OVERHEAD_BYTES)
+    h.add_argument("--measure", action="store_true")
+    h.add_argument("--output", type=Path, default=None)
     a = ap.parse_args(argv)
+    if a.cmd == "artifact-headroom":
+        out = artifact_headroom(dim=a.dim, vocab_size=a.vocab_size, num_layers=a.num_layers, ff_mult=a.ff_mult,
+                                overhead_bytes=a.overhead_bytes, measure=a.measure)
+        text = json.dumps(out, indent=2, sort_keys=True)
+        if a.output is not None:
+            a.output.write_text(text + "\n")
+        else:
+            print(text)
+        return 0 if out["under_budget"] else 2
     if a.cmd == "build-shards":
         out = build_shards(jsonl_paths=a.jsonl_path, sp_model_path=a.sp_model_path, out_dir=a.out_dir,
                            val_docs=a.val_docs, shard_tokens=a.shard_tokens, max_docs=a.max_docs)

@@ -57,3 +57,45 @@ def test_power_law_fit_recovers_its_parameters():
     assert abs(fit["alpha"] - alpha) < 0.02 and abs(fit["bpb_irr"] - irr) < 0.02 and fit["r2"] > 0.999
     with pytest.raises(ValueError):
         A.fit_power_law([1, 2], [1.0, 0.9])
+
+
+# ---------------------------------------------------------------------------
+# replay-curation falsifier
+# ---------------------------------------------------------------------------
+def _curation_dir(tmp_path, rare):
+    import json
+    for arm, vals in rare.items():
+        for i, v in enumerate(vals):
+            (tmp_path / f"exp24_phase3_episodic_dw_curation_v1_{arm}_s{i}.json").write_text(json.dumps(
+                {"name": f"exp24_phase3_episodic_dw_curation_v1_{arm}_s{i}", "val_bpb": 1.5,
+                 "train": {"per_bucket_val_ce": [v, 1.0, 0.5]}, "config": {"seed": i}}))
+    return tmp_path
+
+
+@pytest.mark.parametrize("b,bp,want", [
+    ([2.480, 2.481, 2.479], [2.498, 2.500, 2.499], "pass_mechanism_specific"),
+    ([2.480, 2.481, 2.479], [2.480, 2.482, 2.479], "pass_mechanism_agnostic"),
+    ([2.498, 2.497, 2.499], [2.50, 2.50, 2.50], "mixed_null"),          # better, but by less than 0.005
+    ([2.520, 2.521, 2.519], [2.50, 2.50, 2.50], "regression"),
+])
+def test_curation_gate_verdicts(tmp_path, b, bp, want):
+    from chaoscontrol_b200 import analysis as A
+    d = _curation_dir(tmp_path, {"arm_a_uncurated": [2.500, 2.501, 2.499], "arm_b_cosine_utility": b,
+                                 "arm_bp_pressure_only": bp, "arm_c_no_dw": [2.51, 2.51, 2.51]})
+    cells = A.load_curation_cells(d)
+    g = A.curation_gate(cells)
+    assert g["verdict"] == want and g["by_arm_count"]["arm_b_cosine_utility"] == 3
+    assert not g["needs_escalation"]
+    text = A.render_curation(cells, g)
+    assert "verdict:" in text and "arm_bp_pressure_only" in text
+    assert A.main(["curation", str(d)]) == 0
+
+
+def test_curation_gate_escalation_and_errors(tmp_path):
+    from chaoscontrol_b200 import analysis as A
+    d = _curation_dir(tmp_path, {"arm_a_uncurated": [2.5, 2.5, 2.5], "arm_b_cosine_utility": [2.46, 2.48, 2.47],
+                                 "arm_bp_pressure_only": [2.5, 2.5, 2.5], "arm_c_no_dw": [2.5]})
+    g = A.curation_gate(A.load_curation_cells(d))
+    assert g["needs_escalation"] and g["sigma_b"] == pytest.approx(0.01)
+    with pytest.raises(FileNotFoundError):
+        A.load_curation_cells(tmp_path / "nothing")

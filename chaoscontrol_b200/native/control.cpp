@@ -9,6 +9,14 @@
 #include <limits>
 #include <thread>
 
+// The policy forward / backward are short dense loops over runtime sizes; compile them for AVX2+FMA and for
+// AVX-512 as well as for the baseline ISA and let the loader pick by CPU (GNU function multi-versioning).
+#if defined(__x86_64__) && defined(__GNUC__) && !defined(__clang__) && !defined(CCB_NO_CLONES)
+#define CCB_HOT_CLONES __attribute__((target_clones("arch=x86-64-v4", "arch=x86-64-v3", "default")))
+#else
+#define CCB_HOT_CLONES
+#endif
+
 namespace ccb::ctrl {
 
 // ---------------------------------------------------------------- credit ----
@@ -58,13 +66,25 @@ void FastSlowEma::set_alpha(float a) { alpha_ = std::min(std::max(a, 0.f), 1.f);
 
 // -------------------------------------------------------- simplex policy ----
 namespace {
-constexpr double kInvSqrt2 = 0.70710678118654752440;
-constexpr double kInvSqrt2Pi = 0.39894228040143267794;
-inline float gelu(float x) { return 0.5f * x * (1.f + static_cast<float>(std::erf(x * kInvSqrt2))); }
+// single precision throughout: the double erf / exp of the first version were two thirds of a policy forward
+constexpr float kInvSqrt2 = 0.70710678118654752440f;
+constexpr float kInvSqrt2Pi = 0.39894228040143267794f;
+inline float gelu(float x) { return 0.5f * x * (1.f + std::erf(x * kInvSqrt2)); }
 inline float gelu_grad(float x) {
-  const double cdf = 0.5 * (1.0 + std::erf(x * kInvSqrt2));
-  const double pdf = kInvSqrt2Pi * std::exp(-0.5 * static_cast<double>(x) * x);
-  return static_cast<float>(cdf + x * pdf);
+  const float cdf = 0.5f * (1.f + std::erf(x * kInvSqrt2));
+  const float pdf = kInvSqrt2Pi * std::exp(-0.5f * x * x);
+  return cdf + x * pdf;
+}
+// Dot product with eight independent partial sums: a single running sum is one dependent FMA chain
+// (4 cycles per element), which made the 16 x 16 x 32 attention scores the slowest part of a forward.
+inline float dotf(const float* a, const float* b, std::size_t n) {
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  std::size_t i = 0;
+  for (; i + 8 <= n; i += 8)
+    for (int l = 0; l < 8; ++l) acc[l] += a[i + l] * b[i + l];
+  float tail = 0.f;
+  for (; i < n; ++i) tail += a[i] * b[i];
+  return tail + ((acc[0] + acc[4]) + (acc[1] + acc[5])) + ((acc[2] + acc[6]) + (acc[3] + acc[7]));
 }
 void softmax_row(float* row, std::size_t n) {
   float mx = -std::numeric_limits<float>::infinity();
@@ -132,6 +152,7 @@ std::string SimplexWeights::validate() const {
   return "";
 }
 
+CCB_HOT_CLONES
 SimplexForward simplex_forward(const SimplexWeights& w, const float* V, const float* E,
                                const float* feats) {
   const std::size_t N = w.N, H = w.H, Kv = w.K_v, Ke = w.K_e;
@@ -156,8 +177,7 @@ SimplexForward simplex_forward(const SimplexWeights& w, const float* V, const fl
   for (std::size_t i = 0; i < N; ++i) {
     float* arow = f.attn.data() + i * N;
     for (std::size_t j = 0; j < N; ++j) {
-      float dot = 0.f;
-      for (std::size_t h = 0; h < H; ++h) dot += f.vertex_h[i * H + h] * f.vertex_h[j * H + h];
+      const float dot = dotf(f.vertex_h.data() + i * H, f.vertex_h.data() + j * H, H);
       arow[j] = dot * scale + w.alpha * E[(i * N + j) * Ke];
     }
     softmax_row(arow, N);
@@ -169,9 +189,7 @@ SimplexForward simplex_forward(const SimplexWeights& w, const float* V, const fl
       const float a = f.attn[i * N + j];
       for (std::size_t h = 0; h < H; ++h) mrow[h] += a * f.vertex_h[j * H + h];
     }
-    float lg = w.b_lh;
-    for (std::size_t h = 0; h < H; ++h) lg += mrow[h] * w.W_lh[h];
-    f.logits[i] = lg;
+    f.logits[i] = w.b_lh + dotf(mrow, w.W_lh.data(), H);
   }
   // residual branch: per head, attention over the vertices with learned projections
   const std::size_t nh = w.n_heads;
@@ -198,8 +216,8 @@ SimplexForward simplex_forward(const SimplexWeights& w, const float* V, const fl
       const float* We = w.W_e.data() + hd * Ke;
       for (std::size_t i = 0; i < N; ++i) {
         for (std::size_t j = 0; j < N; ++j) {
-          float dot = 0.f, eb = 0.f;
-          for (std::size_t o = 0; o < H; ++o) dot += q[i * H + o] * k[j * H + o];
+          float eb = 0.f;
+          const float dot = dotf(q + i * H, k + j * H, H);
           for (std::size_t e = 0; e < Ke; ++e) eb += We[e] * E[(i * N + j) * Ke + e];
           at[i * N + j] = dot * scale + eb;
         }
@@ -212,9 +230,7 @@ SimplexForward simplex_forward(const SimplexWeights& w, const float* V, const fl
           const float a = at[i * N + j];
           for (std::size_t o = 0; o < H; ++o) mx[i * H + o] += a * v[j * H + o];
         }
-        float lg = 0.f;
-        for (std::size_t o = 0; o < H; ++o) lg += mx[i * H + o] * Wo[o];
-        f.logits_hxh[i] += lg * inv_heads;
+        f.logits_hxh[i] += dotf(mx + i * H, Wo, H) * inv_heads;
       }
     }
     for (std::size_t i = 0; i < N; ++i) f.logits[i] += w.lambda_hxh * f.logits_hxh[i];
@@ -268,6 +284,7 @@ void forward_pretrain_model(const PretrainModel& m, const float* x, std::size_t 
   }
 }
 
+CCB_HOT_CLONES
 void simplex_backward(const SimplexWeights& w, const SimplexForward& f, const float* V, const float* E,
                       const float* feats, uint32_t chosen, float advantage, float entropy_beta,
                       float* grad) {
@@ -315,8 +332,7 @@ void simplex_backward(const SimplexWeights& w, const SimplexForward& f, const fl
   for (std::size_t i = 0; i < N; ++i) {
     float dotA = 0.f;
     for (std::size_t j = 0; j < N; ++j) {
-      float d = 0.f;
-      for (std::size_t h = 0; h < H; ++h) d += dmixed[i * H + h] * f.vertex_h[j * H + h];
+      const float d = dotf(dmixed.data() + i * H, f.vertex_h.data() + j * H, H);
       dA[j] = d;
       dotA += f.attn[i * N + j] * d;
       const float a = f.attn[i * N + j];
@@ -326,10 +342,10 @@ void simplex_backward(const SimplexWeights& w, const SimplexForward& f, const fl
       ds[j] = f.attn[i * N + j] * (dA[j] - dotA);
       *galpha += ds[j] * E[(i * N + j) * Ke];
       const float g = ds[j] * scale;
-      for (std::size_t h = 0; h < H; ++h) {
-        dvh[i * H + h] += g * f.vertex_h[j * H + h];
-        dvh[j * H + h] += g * f.vertex_h[i * H + h];
-      }
+      float *di = dvh.data() + i * H, *dj = dvh.data() + j * H;      // two loops: rows i and j may be the same row
+      const float *vi = f.vertex_h.data() + i * H, *vj = f.vertex_h.data() + j * H;
+      for (std::size_t h = 0; h < H; ++h) di[h] += g * vj[h];
+      for (std::size_t h = 0; h < H; ++h) dj[h] += g * vi[h];
     }
   }
   if (nh) {
@@ -355,8 +371,7 @@ void simplex_backward(const SimplexWeights& w, const SimplexForward& f, const fl
       for (std::size_t i = 0; i < N; ++i) {
         float dot = 0.f;
         for (std::size_t j = 0; j < N; ++j) {
-          float d = 0.f;
-          for (std::size_t o = 0; o < H; ++o) d += dmx[i * H + o] * v[j * H + o];
+          const float d = dotf(dmx.data() + i * H, v + j * H, H);
           dat[j] = d;
           dot += at[i * N + j] * d;
           const float a = at[i * N + j];
@@ -376,22 +391,26 @@ void simplex_backward(const SimplexWeights& w, const SimplexForward& f, const fl
       for (std::size_t i = 0; i < N; ++i)
         for (std::size_t a = 0; a < H; ++a) {
           const float x = f.vertex_h[i * H + a];
-          float acc = 0.f;
           for (std::size_t o = 0; o < H; ++o) {
             gW_q[hd * H * H + a * H + o] += x * dq[i * H + o];
             gW_k[hd * H * H + a * H + o] += x * dk[i * H + o];
             gW_v[hd * H * H + a * H + o] += x * dv[i * H + o];
-            acc += dq[i * H + o] * Wq[a * H + o] + dk[i * H + o] * Wk[a * H + o] + dv[i * H + o] * Wv[a * H + o];
           }
-          dvh[i * H + a] += acc;
+          dvh[i * H + a] += dotf(dq.data() + i * H, Wq + a * H, H) + dotf(dk.data() + i * H, Wk + a * H, H) +
+                            dotf(dv.data() + i * H, Wv + a * H, H);
         }
     }
   }
+  std::vector<float> dpre(H);
   for (std::size_t i = 0; i < N; ++i) {
     for (std::size_t h = 0; h < H; ++h) {
-      const float dp = dvh[i * H + h] * gelu_grad(f.pre[i * H + h]);
-      gb_vp[h] += dp;
-      for (std::size_t k = 0; k < Kv; ++k) gW_vp[k * H + h] += V[i * Kv + k] * dp;
+      dpre[h] = dvh[i * H + h] * gelu_grad(f.pre[i * H + h]);
+      gb_vp[h] += dpre[h];
+    }
+    for (std::size_t k = 0; k < Kv; ++k) {                          // unit stride over h: vectorises
+      const float v = V[i * Kv + k];
+      float* gr = gW_vp + k * H;
+      for (std::size_t h = 0; h < H; ++h) gr[h] += v * dpre[h];
     }
   }
 }

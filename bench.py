@@ -293,8 +293,12 @@ def run_ours(args):
         from chaoscontrol_b200.parallel import symm
         if symm.active_comm(None) is None:
             raise RuntimeError("peer-memory gradient exchange unavailable: refusing to bench a fallback")
+        from chaoscontrol_b200.parallel.peer import ONE_SHOT_MAX_BYTES
+        forced = os.environ.get("CCB_ALLREDUCE_MODE")
+        two = forced == "1" or (forced != "0" and arena.flat_grad.numel() * 2 > ONE_SHOT_MAX_BYTES)
+        kind = "peer-twoshot (reduce-scatter + all-gather)" if two else "peer-oneshot"
         if reducer is None:
-            collective = "peer-oneshot over CUDA-IPC symmetric buffers, one exchange after backward"
+            collective = f"{kind} over CUDA-IPC symmetric buffers, one exchange after backward"
         else:
             collective = (f"peer-oneshot over CUDA-IPC symmetric buffers, {reducer.n_buckets} buckets overlapped "
                           "with backward")

@@ -205,6 +205,7 @@ def test_train_loop_inline_teacher_and_maintenance():
 
 
 def _crct_rank(rank, world, port, mode, out_dir, split=False, cuda=False):
+    torch.set_num_threads(1)      # several ranks share this machine's cores: no intra-op thread pools
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       NCCL_NVLS_ENABLE="0")
     dev = torch.device("cpu")

@@ -47,6 +47,7 @@ def test_one_rank_produces_consumes_and_replays(tmp_path):
 
 
 def _rank(rank, world, port, out_dir, cuda=False):
+    torch.set_num_threads(1)      # several ranks share this machine's cores: no intra-op thread pools
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       NCCL_NVLS_ENABLE="0")
     dev = torch.device("cpu")

@@ -81,6 +81,7 @@ def test_commit_after_clip_contract():
 
 
 def _rank(rank, ws, port, outdir):
+    torch.set_num_threads(1)      # several ranks share this machine's cores: no intra-op thread pools
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     import torch.distributed as dist
     dist.init_process_group("gloo", rank=rank, world_size=ws)

@@ -97,6 +97,7 @@ def test_budget_loop_fake_clock_and_loss_goes_down():
 
 
 def _ddp_worker(rank, ws, port, outdir):
+    torch.set_num_threads(1)      # several ranks share this machine's cores: no intra-op thread pools
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=ws)

@@ -998,21 +998,38 @@ class CrctRuntime:
         if self.topology["split_memory_ranks"] and mode != "async_rank0_memory_mailbox":
             raise ValueError("split memory ranks need the mailbox transport")
         self.mode = mode
+        def first(*names, default):
+            """First key that the config carries: the reference's key names and this package's own."""
+            for n in names:
+                if n in config and config[n] is not None:
+                    return config[n]
+            return default
         self.tau = float(get("crct_lm_weight_tau", 0.10))
         self.strength = float(get("crct_lm_weight_strength", 0.10))
         self.w_max = float(get("crct_lm_weight_w_max", 1.20))
         self.alpha_max = float(get("crct_lm_weight_alpha_max", 0.15))
         self.write_tokens = int(get("crct_memory_write_tokens_per_step", 256))
-        self.score_interval = max(1, int(get("crct_score_interval_steps", 1)))
-        self.param_sync_interval = int(get("crct_teacher_param_sync_interval", 16))
+        self.score_interval = max(1, int(first("crct_teacher_score_interval_steps", "crct_score_interval_steps", default=1)))
+        self.param_sync_interval = int(first("crct_teacher_param_sync_interval_steps", "crct_teacher_param_sync_interval",
+                                             default=16))
+        self.plasticity_strength = float(get("crct_plasticity_budget_strength", 0.25))
+        self.plasticity_applied = self.plasticity_missing = 0
         self.approximate_packets = bool(get("crct_approximate_packets", False))
         self.cache = TransactionalWakeCache()
         self.scarcity = (ScarcityAwareMemoryOptimizer(tau=self.tau,
                                                       target_read_rate=float(get("crct_target_read_rate", 0.25)),
-                                                      target_write_rate=float(get("crct_target_write_rate", 0.10)))
+                                                      target_write_rate=float(get("crct_target_write_rate", 0.10)),
+                                                      dual_lr=float(get("crct_dual_lr", 0.01)),
+                                                      ema_beta=float(get("crct_ema_beta", 0.95)),
+                                                      max_price=float(get("crct_max_price", 0.50)))
                          if bool(get("crct_scarcity_enabled", True)) else None)
-        self.conflict = (CrctGradientConflictMonitor(enabled=True)
-                         if bool(get("crct_gradient_conflict_enabled", False)) else None)
+        self.conflict = None
+        if bool(get("crct_gradient_conflict_enabled", False)):
+            opts = {k: config[f"crct_gradient_conflict_{k}"] for k in
+                    ("ema_beta", "catastrophic_threshold", "soft_gate_strength", "soft_gate_floor", "trace_path",
+                     "trace_stride", "trace_max_rows", "trace_flush_rows")
+                    if config.get(f"crct_gradient_conflict_{k}") is not None}
+            self.conflict = CrctGradientConflictMonitor(enabled=True, **opts)
         topo = self.topology
         split = topo["split_memory_ranks"]
         self.packet_rank, self.maint_rank = topo["packet_rank"], topo["maintenance_rank"]
@@ -1021,9 +1038,15 @@ class CrctRuntime:
         self.replay_loop = None
         if bool(get("replay_eviction_enabled", False)) and (self.is_maintenance_rank or world_size == 1):
             from .replay_eviction import ReplayEvictionLoop
-            self.replay_loop = ReplayEvictionLoop(**{k[len("replay_eviction_"):]: v for k, v in config.items()
-                                                     if k.startswith("replay_eviction_") and
-                                                     k != "replay_eviction_enabled"})
+            kw = {k[len("replay_eviction_"):]: v for k, v in config.items()
+                  if k.startswith("replay_eviction_") and k != "replay_eviction_enabled" and v is not None}
+            # the reference's runner keys for five of the loop's options
+            for ref_key, own in (("mode", "action_mode"), ("threshold", "eviction_threshold"),
+                                 ("ema_beta", "eviction_ema_beta"), ("min_age_steps", "min_slot_age_steps"),
+                                 ("max_seconds", "max_seconds_per_tick")):
+                if ref_key in kw:
+                    kw.setdefault(own, kw.pop(ref_key))
+            self.replay_loop = ReplayEvictionLoop(**kw)
         # process groups: every rank must take part in every new_group call, in the same order
         self.all_group = all_group
         self.train_group = self.teacher_group = self.maint_group = self.peer_group = None
@@ -1043,15 +1066,16 @@ class CrctRuntime:
                        f"/ccb_crct_{os.environ.get('MASTER_PORT', '0')}_{os.getppid()}")
             hidden = int(getattr(model, "dim", 0) or get("model_dim", 0))
             dt = {"fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16}[
-                str(get("crct_async_payload_dtype", "fp32")).lower()]
+                str(first("crct_async_teacher_payload_dtype", "crct_async_payload_dtype", default="fp32")).lower()]
             scope = "packet" if split else "full"
 
             def open_box(box_name: str, role: str, box_scope: str) -> TeacherMailbox:
                 return TeacherMailbox(
                     name=box_name, role=role, batch_size=batch_size, seq_len=seq_len, hidden_dim=hidden,
                     device=device, payload_dtype=dt, capacity=int(get("crct_mailbox_capacity", 8)),
-                    max_local_batches=int(get("crct_max_local_batches", 8)),
-                    max_payload_lag_steps=int(get("crct_max_payload_lag_steps", 8)),
+                    max_local_batches=int(first("crct_async_teacher_pending_batches", "crct_max_local_batches", default=8)),
+                    max_payload_lag_steps=int(first("crct_async_teacher_max_lag_steps", "crct_max_payload_lag_steps",
+                                                    default=8)),
                     score_interval_steps=self.score_interval, weight_bytes=_weight_bytes(model, box_scope),
                     weight_snapshot_scope=box_scope, source_rank=rank)
             # rank 0 creates the regions, the memory side attaches after a barrier on their two-rank group
@@ -1161,6 +1185,26 @@ class CrctRuntime:
         else:
             self.teacher_payloads += 1
         return payload, inputs, targets
+
+    def apply_plasticity_budget(self, optimizer: Any, payload: Optional[dict[str, Any]]) -> bool:
+        """Before the optimizer step: hand the packet's per-channel plasticity budget to an optimizer that
+        takes one (``set_plasticity_budget``, e.g. Muon), so channels whose memory residual tracked utility
+        move faster this step (runner_fast_path.py:1727-1751 of the reference).  Counts what was applied and
+        what arrived without a budget."""
+        setter = getattr(optimizer, "set_plasticity_budget", None)
+        budget = payload.get("plasticity_budget") if isinstance(payload, dict) else None
+        if not callable(setter) or not isinstance(budget, torch.Tensor):
+            if payload is not None:
+                self.plasticity_missing += 1
+            return False
+        conf = payload.get("plasticity_confidence")
+        step = payload.get("step_id_int")
+        if not isinstance(step, int) and isinstance(payload.get("step_id"), torch.Tensor):
+            step = int(payload["step_id"].detach().cpu().item())
+        setter(budget.detach(), confidence=conf.detach() if isinstance(conf, torch.Tensor) else None,
+               strength=self.plasticity_strength, step=step if isinstance(step, int) else None)
+        self.plasticity_applied += 1
+        return True
 
     def after_optimizer_step(self, step: int) -> None:
         """Train side: weight hand-off to the teacher; inline maintenance."""
@@ -1289,7 +1333,9 @@ class CrctRuntime:
             "teacher_fail_open": self.teacher_fail_open, "teacher_bypass_steps": self.teacher_bypass_steps,
             "packets_served": self.packets_served, "param_syncs": self.param_syncs,
             "lm_weight_tau": self.tau, "lm_weight_strength": self.strength, "lm_weight_w_max": self.w_max,
-            "lm_weight_alpha_max": self.alpha_max}
+            "lm_weight_alpha_max": self.alpha_max, "plasticity_budget_strength": self.plasticity_strength,
+            "plasticity_budget_payloads_applied": self.plasticity_applied,
+            "plasticity_budget_payloads_missing": self.plasticity_missing}
         if self.mailbox is not None:
             d["mailbox"] = self.mailbox.metrics.as_dict()
         elif self._mailbox_final is not None:

@@ -120,12 +120,14 @@ def overlap_wanted(payload_bytes: int, world_size: int) -> bool:
     return payload_bytes * max(world_size - 1, 0) / PEER_BYTES_PER_S > OVERLAP_MIN_EXPOSED_S
 
 
-def reducer_for(engine, world_size: int, group=None) -> Optional[OverlappedGradReducer]:
-    """The engine's cached reducer when the overlapped exchange is wanted (:func:`overlap_wanted`) and the
-    peer-memory communicator of ``group`` is alive and spans ``world_size`` ranks, else None (the caller
-    reduces once after the step)."""
+def reducer_for(engine, world_size: int, group=None, *, force: bool = False) -> Optional[OverlappedGradReducer]:
+    """The engine's cached reducer when the overlapped exchange is wanted (:func:`overlap_wanted`, or
+    ``force``: the caller asked for the overlapped mode by name) and the peer-memory communicator of
+    ``group`` is alive and spans ``world_size`` ranks, else None (the caller reduces once after the step)."""
     from . import symm
-    if not engine.arena.flat_grad.is_cuda or not overlap_wanted(engine.arena.flat_grad.numel() * 2, world_size):
+    if not engine.arena.flat_grad.is_cuda:
+        return None
+    if not force and not overlap_wanted(engine.arena.flat_grad.numel() * 2, world_size):
         return None
     comm = symm.active_comm(group)
     if comm is None or comm.ws != world_size:

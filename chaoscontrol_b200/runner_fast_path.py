@@ -439,6 +439,7 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
                           predictive_aux_dim: int = 0, scopt_split_interval: int = 4,
                           scopt_baseline_buckets: int = 16, scopt_baseline_decay: float = 0.99,
                           scopt_pressure_upper_c: Optional[float] = None, scopt_pressure_upper_floor: float = 1.0,
+                          grad_allreduce_mode: str = "bulk",
                           time_fn: Callable[[], float] = time.perf_counter, **unused: Any) -> dict[str, Any]:
     """Budgeted hot loop.  Returns the train-result dict (``steps``, ``elapsed_s``,
     ``initial_loss``, ``final_loss``, ``loss_history``, throughput keys,
@@ -448,6 +449,20 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
     bad = [k for k in UNSUPPORTED_OPTIONS if unused.get(k)]
     if bad:
         raise NotImplementedError(f"options {bad} are not supported by this runner")
+    ar_mode = str(grad_allreduce_mode).strip().lower()
+    if ar_mode not in {"bulk", "async_param"}:
+        raise ValueError(f"grad_allreduce_mode must be 'bulk' or 'async_param', got {grad_allreduce_mode!r}")
+    if ar_mode == "async_param":
+        # per-parameter reductions start inside backward: every gradient of the step must come from that
+        # one backward pass, reduced symmetrically over all ranks
+        clash = [name for name, on in (("crct_enabled", crct_enabled), ("episodic_enabled", episodic is not None),
+                                       ("dreamworld_enabled", dreamworld_enabled),
+                                       ("distributed_muon", distributed_muon),
+                                       ("predictive_aux_weight", float(predictive_aux_weight) > 0.0 and
+                                        int(predictive_aux_horizon) > 0),
+                                       ("criticality_distill_enabled", criticality is not None)) if on]
+        if clash:
+            raise ValueError(f"grad_allreduce_mode='async_param' cannot be combined with {clash}")
     if replay_eviction_enabled and not crct_enabled:
         raise ValueError("replay_eviction_enabled needs crct_enabled: slot maintenance runs beside the teacher")
     if event_sleep_enabled and not dreamworld_enabled:
@@ -460,6 +475,8 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
         if crct_enabled or episodic is not None or dreamworld_enabled or distributed_muon:
             raise ValueError("optimizer 'scopt' runs its own training step: not combinable with crct / episodic / "
                              "dreamworld / distributed_muon")
+        if ar_mode != "bulk":
+            raise ValueError("optimizer 'scopt' requires grad_allreduce_mode='bulk'")
         V = int(vocab_size or model.lm_head.weight.shape[0])
         scopt_freq = torch.bincount(train_tokens[: int(train_num_tokens)].to(torch.int64).clamp_(0, V - 1),
                                     minlength=V).to(device=device, dtype=torch.float32)
@@ -565,6 +582,12 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
         arena = get_arena(model)
         if arena is not None:
             dist_opt = DistributedMuon(optimizer, arena, comm=symm.active_comm(None), grad_clip_norm=grad_clip_norm)
+    # overlapped exchange on the autograd path: hooks launch one all-reduce per parameter during backward
+    # (the kernel engine has its own bucketed exchange for the same mode and takes no hooks)
+    async_reducer = None
+    if ar_mode == "async_param" and ddp and get_arena(model) is None:
+        from .parallel.distributed import AsyncGradAllReducer
+        async_reducer = AsyncGradAllReducer(model, world_size)
     if device.type == "cuda":
         torch.cuda.reset_peak_memory_stats(device)
     losses: list[torch.Tensor] = []
@@ -717,9 +740,10 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
                     pressure_upper_c=scopt_pressure_upper_c, pressure_upper_floor=float(scopt_pressure_upper_floor),
                     lm_head_backward_mode=lm_head_backward_mode, lm_head_tile_size=lm_head_tile_size)
             elif crct_enabled:
-                payload = None
+                payload = crct_payload = None
                 if crct is not None:
                     payload, inputs, targets = crct.begin_step(inputs, targets, steps)
+                    crct_payload = payload
                 loss = crct_train_step(model, inputs, targets, payload, precision=precision,
                                        lm_head_backward_mode=lm_head_backward_mode,
                                        lm_head_tile_size=lm_head_tile_size)
@@ -732,7 +756,10 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
                                       world_size=world_size, precision=precision,
                                       compile_full_path=compile_full_path,
                                       lm_head_backward_mode=lm_head_backward_mode,
-                                      lm_head_tile_size=lm_head_tile_size)
+                                      lm_head_tile_size=lm_head_tile_size,
+                                      grad_allreduce_mode=ar_mode if (async_reducer is not None or
+                                                                      get_arena(model) is not None) else "bulk",
+                                      async_grad_reducer=async_reducer)
                 if predictive_on:
                     aux_backward(inputs)
                     if ddp and dist_opt is None:
@@ -764,6 +791,8 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
                 optimizer.step()
             else:
                 _clip(model, grad_clip_norm, fused_grad_clip)
+                if crct is not None and crct_enabled:
+                    crct.apply_plasticity_budget(optimizer, crct_payload)
                 optimizer.step()
             if aux_opt is not None:
                 if dist_opt is not None and ddp:
@@ -787,6 +816,8 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
             step_times.append(time_fn() - ts)
     finally:
         prefetch.close()
+        if async_reducer is not None:
+            async_reducer.close()
         if crct is not None:
             crct.close()
     if device.type == "cuda":
@@ -801,6 +832,7 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
         "steady_state_step_seconds": FP.steady_state_step_seconds(step_times) if step_times else float("nan"),
         "train_sampling_mode": mode, "lm_head_backward_mode": lm_head_backward_mode,
         "cuda_graph_mode": str(cuda_graph_mode), "distributed_muon": dist_opt is not None,
+        "grad_allreduce_mode": ar_mode,
         "spectral": spectral_summary(model),
     }
     result.update(FP.summarize_train_timing(steps=steps, elapsed_s=elapsed, batch_size=batch_size, seq_len=seq_len,
@@ -849,7 +881,7 @@ _LOOP_KEYS = ("chunk_size", "grad_clip_norm", "fused_grad_clip", "precision", "s
               "stop_margin_seconds", "compile_full_path", "prefetch_batches", "lm_head_backward_mode",
               "lm_head_tile_size", "cuda_graph_mode", "cuda_graph_min_total_speedup",
               "cuda_graph_max_capture_seconds", "cuda_graph_warmup_steps", "train_sampling_mode",
-              "embed_freeze_steps", "distributed_muon", "crct_enabled",
+              "embed_freeze_steps", "distributed_muon", "grad_allreduce_mode", "crct_enabled",
               "replay_eviction_enabled", "spectral_reg_lambda_dead", "spectral_reg_lambda_sticky",
               "spectral_reg_min_a", "spectral_reg_max_a", "predictive_aux_weight", "predictive_aux_horizon",
               "predictive_aux_dim", "scopt_split_interval", "scopt_baseline_buckets", "scopt_baseline_decay",

@@ -196,9 +196,16 @@ def _engine_for(model: nn.Module) -> Optional[TrainEngine]:
 def train_ssm_step(model: nn.Module, inputs: torch.Tensor, targets: torch.Tensor, chunk_size: int, *,
                    ddp_active: bool = False, world_size: int = 1, precision: str = "bf16",
                    compile_full_path: bool = False, lm_head_backward_mode: str = "chunked",
-                   lm_head_tile_size: int = 1024) -> torch.Tensor:
+                   lm_head_tile_size: int = 1024, grad_allreduce_mode: str = "bulk",
+                   async_grad_reducer=None) -> torch.Tensor:
     """One forward + backward.  Gradients are left on the parameters (averaged
     across ranks when ``ddp_active``); returns the detached mean CE.
+
+    ``grad_allreduce_mode``: ``"bulk"`` reduces once after backward; ``"async_param"`` overlaps the
+    exchange with backward (train_ssm.py:1186-1260 of the reference).  On the autograd path that is
+    an :class:`~chaoscontrol_b200.parallel.distributed.AsyncGradAllReducer` whose per-parameter hooks
+    launched the all-reduces during backward (pass it as ``async_grad_reducer``; this function waits
+    for it); on the kernel engine it is the bucketed peer-memory exchange on a side stream.
 
     ``compile_full_path`` is accepted for signature compatibility and ignored:
     there is no tracing compiler in this stack, the encoder is already one
@@ -212,13 +219,21 @@ def train_ssm_step(model: nn.Module, inputs: torch.Tensor, targets: torch.Tensor
                          "'fused_streaming', 'fused_streaming_v2', or 'fused_streaming_cached', or "
                          f"'fused_norm_streaming_v2', got {lm_head_backward_mode!r}")
 
+    ar_mode = str(grad_allreduce_mode).strip().lower()
+    if ar_mode not in ("bulk", "async_param"):
+        raise ValueError(f"grad_allreduce_mode must be 'bulk' or 'async_param', got {grad_allreduce_mode!r}")
+    if ar_mode == "async_param" and mode == "chunked":
+        # the chunked head runs one backward per chunk, so the head's gradients accumulate over several
+        # passes and a per-parameter hook would reduce partial sums
+        raise ValueError("grad_allreduce_mode='async_param' needs a single backward pass: use "
+                         "lm_head_backward_mode 'single' or one of the fused modes, not 'chunked'")
     engine = _engine_for(model) if (fused_mode and precision in ("bf16", "fp8_fused") and
                                     model.training) else None
     if engine is not None:
         reducer = None
         if ddp_active and world_size > 1:
             from .parallel.grad_overlap import reducer_for
-            reducer = reducer_for(engine, world_size)
+            reducer = reducer_for(engine, world_size, force=ar_mode == "async_param")
         loss = engine.step(inputs, targets, reducer=reducer)
         if ddp_active and world_size > 1:
             allreduce_grads(model, world_size)       # no-op when the reducer already did the exchange
@@ -239,7 +254,12 @@ def train_ssm_step(model: nn.Module, inputs: torch.Tensor, targets: torch.Tensor
                                             chunk_size)
             hidden.backward(gradient=hidden_for_ce.grad)
     if ddp_active and world_size > 1:
-        allreduce_grads(model, world_size)
+        if ar_mode == "async_param":
+            if async_grad_reducer is None:
+                raise ValueError("grad_allreduce_mode='async_param' requires an AsyncGradAllReducer instance")
+            async_grad_reducer.wait()
+        else:
+            allreduce_grads(model, world_size)
     return loss
 
 

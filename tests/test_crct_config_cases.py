@@ -1,0 +1,111 @@
+"""CRCT runtime: the reference's config key names are honoured, and the teacher packet's plasticity budget reaches
+an optimizer that takes one (CPU, one rank, inline teacher)."""
+import pytest
+import torch
+
+from chaoscontrol_b200 import crct as C
+from chaoscontrol_b200.models.model import CareStudentLM
+from chaoscontrol_b200.runner_fast_path import _build_optimizer, train_fast_for_budget
+
+
+def _memory_model(seed=0):
+    torch.manual_seed(seed)
+    return CareStudentLM(vocab_size=48, dim=16, num_layers=2, outer_model_dim=8, outer_model_type="multislot",
+                         outer_max_slots=0, buffer_mode="append_only")
+
+
+def _rt(model, **cfg):
+    base = dict(crct_enabled=True, crct_memory_write_tokens_per_step=4, model_dim=16)
+    base.update(cfg)
+    return C.CrctRuntime(model=model, config=base, rank=0, world_size=1, device=torch.device("cpu"), batch_size=3,
+                         seq_len=8, total_steps=8)
+
+
+def _train(model, rt, optimizer="muon", steps=6, **kw):
+    tokens = torch.randint(0, 48, (4000,), dtype=torch.int16, generator=torch.Generator().manual_seed(0))
+    optim = _build_optimizer(dict(optimizer=optimizer, base_lr=1e-3, fused_muon=False), model)
+    res = train_fast_for_budget(model, train_tokens=tokens, train_num_tokens=4000, optimizer=optim, max_steps=steps, crct=rt,
+                                stride=8, seq_len=8, batch_size=3, device=torch.device("cpu"), budget_seconds=600.0,
+                                precision="fp32", stop_check_interval=1, lm_head_backward_mode="fused",
+                                prefetch_batches=False, vocab_size=48, **kw)
+    return res, optim
+
+
+def test_reference_interval_keys_are_read():
+    m = _memory_model()
+    rt = _rt(m, crct_teacher_score_interval_steps=3, crct_teacher_param_sync_interval_steps=5)
+    assert rt.score_interval == 3 and rt.param_sync_interval == 5
+    own = _rt(_memory_model(), crct_score_interval_steps=2, crct_teacher_param_sync_interval=7)
+    assert own.score_interval == 2 and own.param_sync_interval == 7
+    both = _rt(_memory_model(), crct_teacher_score_interval_steps=4, crct_score_interval_steps=9)
+    assert both.score_interval == 4                                    # the reference's name wins when both are given
+    assert _rt(_memory_model()).score_interval == 1 and _rt(_memory_model()).param_sync_interval == 16
+
+
+def test_price_and_conflict_options_reach_their_objects(tmp_path):
+    rt = _rt(_memory_model(), crct_dual_lr=0.2, crct_ema_beta=0.5, crct_max_price=0.9, crct_target_read_rate=0.4,
+             crct_gradient_conflict_enabled=True, crct_gradient_conflict_catastrophic_threshold=-0.3,
+             crct_gradient_conflict_soft_gate_strength=0.7, crct_gradient_conflict_trace_path=str(tmp_path / "c.ndjson"),
+             crct_gradient_conflict_trace_stride=4)
+    s = rt.scarcity
+    assert (s.dual_lr, s.ema_beta, s.max_price, s.target_read_rate) == (0.2, 0.5, 0.9, 0.4)
+    c = rt.conflict
+    assert c.catastrophic_threshold == -0.3 and c.soft_gate_strength == 0.7 and c.trace_stride == 4
+    assert str(c.trace_path) == str(tmp_path / "c.ndjson")
+    assert _rt(_memory_model()).conflict is None and _rt(_memory_model(), crct_scarcity_enabled=False).scarcity is None
+
+
+def test_reference_maintenance_keys_are_mapped_onto_the_loop():
+    rt = _rt(_memory_model(), replay_eviction_enabled=True, replay_eviction_mode="shadow", replay_eviction_threshold=0.07,
+             replay_eviction_ema_beta=0.6, replay_eviction_min_age_steps=11, replay_eviction_max_seconds=0.25,
+             replay_eviction_commit_policy="rule", replay_eviction_action_agreement_count=3,
+             replay_eviction_trace_path=None)
+    loop = rt.replay_loop
+    assert loop.action_mode == "shadow" and loop.commit_policy == "rule" and loop.agreement == 3
+    assert loop._rule_kw["eviction_threshold"] == 0.07 and loop.beta == 0.6 and loop.min_age == 11 and loop.max_seconds == 0.25
+    own = _rt(_memory_model(), replay_eviction_enabled=True, replay_eviction_action_mode="shadow",
+              replay_eviction_min_slot_age_steps=5).replay_loop
+    assert own.action_mode == "shadow" and own.min_age == 5
+    with pytest.raises(ValueError, match="action_mode"):
+        _rt(_memory_model(), replay_eviction_enabled=True, replay_eviction_mode="sometimes")
+
+
+def test_plasticity_budget_of_every_packet_reaches_muon():
+    m = _memory_model()
+    rt = _rt(m, crct_plasticity_budget_strength=0.5)
+    res, optim = _train(m, rt, optimizer="muon")
+    d = res["crct"]
+    assert d["teacher_payloads"] == 6 and d["plasticity_budget_payloads_applied"] == 6
+    assert d["plasticity_budget_payloads_missing"] == 0 and d["plasticity_budget_strength"] == 0.5
+    tr = optim.plasticity_budget_trace()
+    assert tr["updates"] == 6 and tr["dim"] == 16 and tr["strength"] == 0.5 and 1.0 <= tr["lr_multiplier_max"] <= 1.5
+    assert tr["step"] >= 0
+
+
+def test_optimizer_without_a_budget_hook_is_counted_as_missing_and_unscored_steps_are_not():
+    m = _memory_model()
+    rt = _rt(m, crct_teacher_score_interval_steps=2)
+    res, optim = _train(m, rt, optimizer="adamw")
+    d = res["crct"]
+    assert d["teacher_payloads"] == 3 and d["plasticity_budget_payloads_applied"] == 0
+    assert d["plasticity_budget_payloads_missing"] == 3                # three packets arrived, AdamW takes no budget
+
+
+def test_apply_plasticity_budget_contract():
+    rt = _rt(_memory_model())
+
+    class Opt:
+        calls = []
+
+        def set_plasticity_budget(self, budget, *, confidence=None, strength=0.25, step=None):
+            self.calls.append((budget.clone(), confidence, strength, step))
+    o = Opt()
+    assert rt.apply_plasticity_budget(o, None) is False and rt.plasticity_missing == 0      # no packet this step
+    assert rt.apply_plasticity_budget(o, {"utility": torch.zeros(2)}) is False and rt.plasticity_missing == 1
+    pay = {"plasticity_budget": torch.tensor([0.2, 0.4], requires_grad=True), "plasticity_confidence": torch.tensor([1.0, 0.5]),
+           "step_id": torch.tensor(17)}
+    assert rt.apply_plasticity_budget(o, pay) is True and rt.plasticity_applied == 1
+    b, c, strength, step = o.calls[0]
+    assert not b.requires_grad and c.tolist() == [1.0, 0.5] and strength == 0.25 and step == 17
+    rt.apply_plasticity_budget(o, {"plasticity_budget": torch.ones(2), "step_id_int": 4})
+    assert o.calls[1][1] is None and o.calls[1][3] == 4

@@ -373,6 +373,41 @@ def coerce_action_space(value: Any) -> Optional[ConstrainedActionSpace]:
     raise TypeError("action_space must be None, False, a dict, or ConstrainedActionSpace")
 
 
+ACTION_SPACE_HEADS = ("write_admission", "eviction", "replay_timing", "replay_budget", "write_budget", "temperature",
+                      "entropy_beta", "ema_alpha", "consolidation", "selection_rank")
+
+
+def _head_value(config: Mapping[str, Any], head: str, what: str, default: float) -> float:
+    """``episodic_controller_head_<what>: {head: value}`` wins over ``episodic_controller_<head>_<what>``."""
+    table = config.get(f"episodic_controller_head_{what}")
+    if isinstance(table, Mapping) and head in table:
+        return float(table[head])
+    return float(config.get(f"episodic_controller_{head}_{what}", default))
+
+
+def build_action_space_from_config(config: Mapping[str, Any], *, trace_log: Any = None) -> Optional["ConstrainedActionSpace"]:
+    """The bounded action space of the episodic controller as the run config describes it, or None when
+    ``episodic_controller_action_space_enabled`` is off (runner_fast_path.py:6790-6850 of the reference):
+    per-head readiness and maximal deviation, the selection head's pair under its own two keys, an optional
+    cap on tags per query, trace-only mode, the shared event recurrence (on unless switched off) and the
+    online learning rate / reward clip of the heads."""
+    if not bool(config.get("episodic_controller_action_space_enabled", False)):
+        return None
+    ready = {h: _head_value(config, h, "readiness", 0.0) for h in ACTION_SPACE_HEADS}
+    delta = {h: _head_value(config, h, "max_delta", 0.0) for h in ACTION_SPACE_HEADS}
+    ready["selection_rank"] = float(config.get("episodic_controller_selection_readiness", ready["selection_rank"]))
+    delta["selection_rank"] = float(config.get("episodic_controller_selection_max_delta", delta["selection_rank"]))
+    max_tags = config.get("episodic_controller_max_tags_per_query")
+    return ConstrainedActionSpace(
+        trace_only=bool(config.get("episodic_controller_action_space_trace_only", False)),
+        selection_readiness=ready["selection_rank"], selection_max_delta=delta["selection_rank"],
+        max_tags_per_query=None if max_tags is None else int(max_tags), head_readiness=ready, head_max_delta=delta,
+        event_ssm=(make_shared_event_ssm_from_config(config)
+                   if bool(config.get("episodic_controller_shared_event_ssm_enabled", True)) else None),
+        trace_log=trace_log, online_learning_rate=float(config.get("episodic_controller_action_learning_rate", 0.0)),
+        reward_clip=float(config.get("episodic_controller_action_reward_clip", 5.0)))
+
+
 def make_shared_event_ssm_from_config(config: Mapping[str, Any]) -> SharedEventSsm:
     g = config.get
     return SharedEventSsm(hidden_dim=int(g("episodic_controller_ssm_hidden_dim", 16)),

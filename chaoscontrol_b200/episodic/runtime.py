@@ -96,7 +96,20 @@ class EpisodicRuntime:
         if self.consumer:
             self.cache = EpisodicCache(capacity=int(get("episodic_capacity", 4096)), span_length=self.span,
                                        key_rep_dim=self.key_rep_dim,
-                                       grace_steps=int(get("episodic_grace_steps", 200)))
+                                       grace_steps=int(get("episodic_grace_steps", 200)),
+                                       utility_ema_decay=float(get("episodic_utility_ema_decay", 0.99)))
+        # how many write events the consumer takes from one producer's ring per step (0 = all that arrived)
+        self.max_drain = max(0, int(get("episodic_write_ring_max_drain_per_step", 4096)))
+        # the controller's bounded action space (off unless the config enables it) and its trace
+        self.action_space = self.action_trace = None
+        if self.consumer and bool(get("episodic_controller_action_space_enabled", False)):
+            from .learned_action_space import build_action_space_from_config
+            path = str(get("episodic_controller_action_trace_path", "") or "")
+            if path:
+                from .diagnostics import ActionSpaceTraceLogger
+                self.action_trace = ActionSpaceTraceLogger(path)
+            self.action_space = build_action_space_from_config(
+                config, trace_log=self.action_trace if self.action_trace is not None else [])
         # rings: the consumer creates, producers attach after a barrier
         self._write_rings: dict[int, N.Ring] = {}
         self._query_rings: dict[int, N.Ring] = {}
@@ -163,12 +176,13 @@ class EpisodicRuntime:
                 sgd_interval=int(get("episodic_controller_sgd_interval", 16)),
                 ema_alpha=float(get("episodic_controller_ema_alpha", 0.25)),
                 ema_interval=int(get("episodic_controller_ema_interval", 64)),
-                entropy_beta=float(get("episodic_controller_entropy_beta", 0.0)))
+                entropy_beta=float(get("episodic_controller_entropy_beta", 0.0)),
+                gerber_c=float(get("episodic_controller_gerber_c", 0.5)))
             trace = str(get("episodic_controller_simplex_trace_path", "") or "")
             if trace:
                 os.makedirs(os.path.dirname(trace) or ".", exist_ok=True)
                 self.simplex.learner.set_trace_path(trace)
-            self._sel_gen = torch.Generator().manual_seed(int(get("seed", 0)))
+            self._sel_gen = torch.Generator().manual_seed(int(get("episodic_controller_selection_seed", get("seed", 0))))
             self.selection_mode = str(get("episodic_controller_selection_mode",
                                           get("episodic_simplex_selection_mode", "sample")))
             if self.selection_mode not in ("argmax", "sample"):
@@ -267,10 +281,12 @@ class EpisodicRuntime:
         cache = self.cache
         for r in self.producers:
             ring = self._write_rings[r]
-            while True:
+            taken = 0
+            while self.max_drain <= 0 or taken < self.max_drain:
                 rec = ring.pop()
                 if rec is None:
                     break
+                taken += 1
                 cache.append(key_fp=int(rec["key_fp"]), key_rep=_bits_fp16(rec["key_rep"], self.key_rep_dim),
                              value_tok_ids=torch.from_numpy(rec["value_tok_ids"][: self.span].astype(np.int64)),
                              value_anchor_id=int(rec["value_anchor_id"]), current_step=int(rec["gpu_step"]),
@@ -307,7 +323,7 @@ class EpisodicRuntime:
                              simplex_selection_mode=self.selection_mode, simplex_generator=self._sel_gen)
             run_controller_cycle(controller_query_queue=self.query_queue, tagged_replay_queue=self.tagged,
                                  cache=self.cache, k=self.topk, score_mode=self.score_mode, queue_lock=self._lock,
-                                 **extra)
+                                 action_space=self.action_space, **extra)
         else:
             self.query_queue.clear()
         done = 0
@@ -411,6 +427,9 @@ class EpisodicRuntime:
         self._flush()
         if self.logger is not None:
             self.logger.close()
+        if self.action_trace is not None:
+            self.action_trace.close()
+            self.action_trace = None
         if self.simplex is not None and not self._closed_learner:
             self._final_controller = self.simplex.learner.telemetry()
             self._closed_learner = True
@@ -427,6 +446,13 @@ class EpisodicRuntime:
                                "train_online": self.train_online, "selection_mode": self.selection_mode,
                                "temperature": float(self.simplex.policy.temperature),
                                **self.simplex.learner.telemetry()}
+        if self.action_space is not None:
+            sp = self.action_space
+            d["action_space"] = {"trace_only": bool(sp.trace_only), "selection_readiness": float(sp.selection_readiness),
+                                 "selection_max_delta": float(sp.selection_max_delta),
+                                 "max_tags_per_query": sp.max_tags_per_query,
+                                 "shared_event_ssm": sp.event_ssm is not None,
+                                 "online_learning_rate": float(sp.online_learning_rate)}
         if self.cache is not None:
             d["cache_entries"] = len(self.cache)
             d["cache_capacity"] = int(self.cache.capacity)

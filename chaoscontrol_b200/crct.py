@@ -1012,6 +1012,10 @@ class CrctRuntime:
         self.score_interval = max(1, int(first("crct_teacher_score_interval_steps", "crct_score_interval_steps", default=1)))
         self.param_sync_interval = int(first("crct_teacher_param_sync_interval_steps", "crct_teacher_param_sync_interval",
                                              default=16))
+        # per-stage seconds of the scoring pass, summed over the run (off by default: the timers synchronise)
+        self.stage_timing = bool(get("crct_score_stage_timing_enabled", False))
+        self.stage_seconds: dict[str, float] = {}
+        self.stage_samples = 0
         self.plasticity_strength = float(get("crct_plasticity_budget_strength", 0.25))
         self.plasticity_applied = self.plasticity_missing = 0
         self.approximate_packets = bool(get("crct_approximate_packets", False))
@@ -1122,9 +1126,16 @@ class CrctRuntime:
             if self.approximate_packets:
                 return packet_payload_inline(model=self.model, cache=self.cache, inputs=inputs, targets=targets,
                                              step=step, memory_write_tokens=self.write_tokens)
+            stages: Optional[dict[str, float]] = {} if self.stage_timing else None
             with torch.no_grad():
-                return score_payload_inline(inputs=inputs, targets=targets, update_model_memory_after=True,
-                                            **self._score_kw(step))
+                out = score_payload_inline(inputs=inputs, targets=targets, update_model_memory_after=True,
+                                           record_stage_seconds=stages, **self._score_kw(step))
+            if stages:
+                self.stage_samples += 1
+                for k, v in stages.items():
+                    if not k.startswith("_"):                     # underscore keys carry the problem shape
+                        self.stage_seconds[k] = self.stage_seconds.get(k, 0.0) + float(v)
+            return out
         finally:
             self.model.train(was_training)
 
@@ -1336,6 +1347,8 @@ class CrctRuntime:
             "lm_weight_alpha_max": self.alpha_max, "plasticity_budget_strength": self.plasticity_strength,
             "plasticity_budget_payloads_applied": self.plasticity_applied,
             "plasticity_budget_payloads_missing": self.plasticity_missing}
+        if self.stage_timing:
+            d["score_stage_seconds"] = {"samples": self.stage_samples, **{k: float(v) for k, v in self.stage_seconds.items()}}
         if self.mailbox is not None:
             d["mailbox"] = self.mailbox.metrics.as_dict()
         elif self._mailbox_final is not None:

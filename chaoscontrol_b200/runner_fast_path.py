@@ -439,7 +439,8 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
                           predictive_aux_dim: int = 0, scopt_split_interval: int = 4,
                           scopt_baseline_buckets: int = 16, scopt_baseline_decay: float = 0.99,
                           scopt_pressure_upper_c: Optional[float] = None, scopt_pressure_upper_floor: float = 1.0,
-                          grad_allreduce_mode: str = "bulk",
+                          grad_allreduce_mode: str = "bulk", emit_topology_snapshot: bool = False,
+                          scopt_trace_interval_steps: int = 0,
                           time_fn: Callable[[], float] = time.perf_counter, **unused: Any) -> dict[str, Any]:
     """Budgeted hot loop.  Returns the train-result dict (``steps``, ``elapsed_s``,
     ``initial_loss``, ``final_loss``, ``loss_history``, throughput keys,
@@ -483,6 +484,11 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
         scopt_baseline = FrequencyBucketBaseline(scopt_freq, num_buckets=int(scopt_baseline_buckets),
                                                  decay=float(scopt_baseline_decay), device=device)
     scopt_stats = {"split_steps": 0, "clipped": 0}
+    scopt_traces: list[dict[str, Any]] = []
+    topo_snapshot = None
+    if emit_topology_snapshot:
+        from .utils.profiling import topology_snapshot
+        topo_snapshot = topology_snapshot()                      # host / GPU wiring of this run, read-only queries
     if dreamworld_enabled and crct_enabled:
         raise ValueError("dreamworld_enabled and crct_enabled cannot be combined in this runner")
     if episodic is not None and (crct_enabled or dreamworld_enabled or criticality is not None):
@@ -789,6 +795,8 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
                     scopt_stats["split_steps"] += 1
                     scopt_stats["clipped"] += int(clipped)
                 optimizer.step()
+                if int(scopt_trace_interval_steps) > 0 and (steps + 1) % int(scopt_trace_interval_steps) == 0:
+                    scopt_traces.append({"step": steps + 1, **optimizer.scarcity_trace()})
             else:
                 _clip(model, grad_clip_norm, fused_grad_clip)
                 if crct is not None and crct_enabled:
@@ -837,6 +845,8 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
     }
     result.update(FP.summarize_train_timing(steps=steps, elapsed_s=elapsed, batch_size=batch_size, seq_len=seq_len,
                                             world_size=world_size))
+    if topo_snapshot is not None:
+        result["topology_snapshot"] = topo_snapshot
     if fast_slow is not None:
         result["fast_slow"] = fast_slow.diagnostics(model)
     if graph_summary is not None:
@@ -856,6 +866,8 @@ def train_fast_for_budget(model: torch.nn.Module, *, train_tokens: torch.Tensor,
     if scopt_on:
         result["scopt"] = {"split_interval": int(scopt_split_interval), "split_steps": scopt_stats["split_steps"],
                            "clipped_split_steps": scopt_stats["clipped"], "trace": optimizer.scarcity_trace()}
+        if scopt_traces:
+            result["scopt"]["interval_traces"] = scopt_traces
     if criticality is not None:
         result["criticality_distillation"] = criticality.diagnostics()
     if dream_buffer is not None:
@@ -881,7 +893,8 @@ _LOOP_KEYS = ("chunk_size", "grad_clip_norm", "fused_grad_clip", "precision", "s
               "stop_margin_seconds", "compile_full_path", "prefetch_batches", "lm_head_backward_mode",
               "lm_head_tile_size", "cuda_graph_mode", "cuda_graph_min_total_speedup",
               "cuda_graph_max_capture_seconds", "cuda_graph_warmup_steps", "train_sampling_mode",
-              "embed_freeze_steps", "distributed_muon", "grad_allreduce_mode", "crct_enabled",
+              "embed_freeze_steps", "distributed_muon", "grad_allreduce_mode", "emit_topology_snapshot",
+              "scopt_trace_interval_steps", "crct_enabled",
               "replay_eviction_enabled", "spectral_reg_lambda_dead", "spectral_reg_lambda_sticky",
               "spectral_reg_min_a", "spectral_reg_max_a", "predictive_aux_weight", "predictive_aux_horizon",
               "predictive_aux_dim", "scopt_split_interval", "scopt_baseline_buckets", "scopt_baseline_decay",

@@ -109,3 +109,15 @@ def test_apply_plasticity_budget_contract():
     assert not b.requires_grad and c.tolist() == [1.0, 0.5] and strength == 0.25 and step == 17
     rt.apply_plasticity_budget(o, {"plasticity_budget": torch.ones(2), "step_id_int": 4})
     assert o.calls[1][1] is None and o.calls[1][3] == 4
+
+
+def test_score_stage_timing_is_opt_in_and_sums_named_stages():
+    m = _memory_model()
+    rt = _rt(m, crct_score_stage_timing_enabled=True)
+    res, _ = _train(m, rt, optimizer="adamw", steps=3)
+    st = res["crct"]["score_stage_seconds"]
+    assert st["samples"] == 3 and {"encode_off", "nll_off", "nll_mem", "plasticity"} <= set(st)
+    assert all(v >= 0 for v in st.values()) and not any(k.startswith("_") for k in st)
+    m2 = _memory_model()
+    res2, _ = _train(m2, _rt(m2), optimizer="adamw", steps=2)
+    assert "score_stage_seconds" not in res2["crct"]

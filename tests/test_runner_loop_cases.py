@@ -189,3 +189,24 @@ def test_graph_gate_charges_capture_to_the_budget():
 def test_predictive_aux_dim_must_match_the_model():
     with pytest.raises(ValueError, match="predictive_aux_dim"):
         _run(predictive_aux_weight=0.1, predictive_aux_horizon=2, predictive_aux_dim=8)
+
+
+# ---------------------------------------------------------------- optional result blocks
+def test_topology_snapshot_only_when_asked():
+    res, _ = _run(max_steps=1)
+    assert "topology_snapshot" not in res
+    res, _ = _run(max_steps=1, emit_topology_snapshot=True)
+    snap = res["topology_snapshot"]
+    assert isinstance(snap, dict) and all(isinstance(v, str) for v in snap.values())
+    assert "lscpu" in snap or snap == {}                                 # whatever query tools this host has
+
+
+def test_scopt_interval_traces():
+    model = CareStudentLM(vocab_size=64, dim=16, num_layers=1)
+    res, _ = _run(model=model, opt="scopt", max_steps=4, lm_head_backward_mode="fused", scopt_trace_interval_steps=2,
+                  scopt_split_interval=2)
+    tr = res["scopt"]["interval_traces"]
+    assert [t["step"] for t in tr] == [2, 4] and all("scarcity_enabled" in t for t in tr)
+    res2, _ = _run(model=CareStudentLM(vocab_size=64, dim=16, num_layers=1), opt="scopt", max_steps=2,
+                   lm_head_backward_mode="fused")
+    assert "interval_traces" not in res2["scopt"]

@@ -989,7 +989,21 @@ class CrctRuntime:
                                            split_memory_ranks=bool(get("crct_split_memory_ranks", False)))
         self.memory_rank = self.topology["packet_rank"] if world_size > 1 else -1     # the sync teacher
         self.is_memory_rank = world_size > 1 and rank in self.topology["memory_ranks"]
-        mode = str(get("crct_teacher_transport_mode", "async_rank0_memory_mailbox")).strip().lower()
+        mode = get("crct_teacher_transport_mode")
+        if mode is None:
+            # the reference's pair of keys: asynchronous transport on / off, and which carrier
+            if not bool(get("crct_async_teacher_transport", True)):
+                mode = "sync"
+            else:
+                backend = str(get("crct_async_teacher_transport_backend", "mailbox")).strip().lower()
+                if backend in ("mailbox", "file", "file_mailbox"):
+                    mode = "async_rank0_memory_mailbox"
+                elif backend in ("collective", "broadcast", "nccl"):
+                    mode = "sync"                      # lock-step collectives with the memory rank
+                else:
+                    raise ValueError("crct_async_teacher_transport_backend must be one of 'collective' or 'mailbox'; "
+                                     f"got {backend!r}")
+        mode = str(mode).strip().lower()
         if world_size == 1:
             mode = "inline"
         if mode not in ("inline", "sync", "async_rank0_memory_mailbox"):

@@ -97,7 +97,9 @@ class EpisodicRuntime:
             self.cache = EpisodicCache(capacity=int(get("episodic_capacity", 4096)), span_length=self.span,
                                        key_rep_dim=self.key_rep_dim,
                                        grace_steps=int(get("episodic_grace_steps", 200)),
-                                       utility_ema_decay=float(get("episodic_utility_ema_decay", 0.99)))
+                                       utility_ema_decay=float(get("episodic_utility_ema_decay", 0.99)),
+                                       slot_state_dim=int(get("episodic_slot_state_dim", 0)),
+                                       simplex_k_max=int(get("episodic_simplex_k_max", 0)))
         # how many write events the consumer takes from one producer's ring per step (0 = all that arrived)
         self.max_drain = max(0, int(get("episodic_write_ring_max_drain_per_step", 4096)))
         # the controller's bounded action space (off unless the config enables it) and its trace

@@ -121,3 +121,20 @@ def test_score_stage_timing_is_opt_in_and_sums_named_stages():
     m2 = _memory_model()
     res2, _ = _train(m2, _rt(m2), optimizer="adamw", steps=2)
     assert "score_stage_seconds" not in res2["crct"]
+
+
+def test_reference_transport_keys_choose_the_mode():
+    def mode(**cfg):
+        torch.manual_seed(0)
+        m = _memory_model()
+        # world_size 1 always ends inline, so read the decision through a failing multi-rank construction instead
+        base = dict(crct_enabled=True, model_dim=16, **cfg)
+        try:
+            C.CrctRuntime(model=m, config=base, rank=0, world_size=4, device=torch.device("cpu"), batch_size=2, seq_len=4)
+        except Exception as exc:                                        # no process group here: the mode was accepted
+            return "accepted" if "process group" in str(exc).lower() else str(exc)
+    assert "must be one of 'collective' or 'mailbox'" in mode(crct_async_teacher_transport_backend="pigeon")
+    assert mode(crct_async_teacher_transport_backend="mailbox") == "accepted"
+    assert mode(crct_async_teacher_transport=False) == "accepted"
+    assert "crct_teacher_transport_mode must be" in mode(crct_teacher_transport_mode="pigeon")
+    assert _rt(_memory_model(), crct_async_teacher_transport_backend="collective").mode == "inline"

@@ -114,3 +114,11 @@ def test_enabled_action_space_runs_in_the_loop_and_traces(tmp_path):
     rows = [json.loads(x) for x in trace.read_text().splitlines()]
     assert rows and {"gpu_step", "head_name", "bounded_action_json", "accepted", "readiness"} <= set(rows[0])
     assert any(r["head_name"] == "selection_rank" for r in rows)
+
+
+def test_cache_side_tables_take_their_sizes_from_the_config():
+    _, rt = _rt(episodic_slot_state_dim=6, episodic_simplex_k_max=3)
+    try:
+        assert rt.cache.slot_state.shape == (64, 6) and rt.cache.simplex_edge_slot.shape == (64, 3)
+    finally:
+        rt.close()

@@ -267,9 +267,20 @@ def _load_model(checkpoint_path: str, device: torch.device) -> tuple[nn.Module, 
 def run(*, cache_dir: str, checkpoint_path: Optional[str], output_path: Optional[str], chunk_size: int = 512,
         doc_batch_size: int = 1024, max_forward_tokens="auto", doc_packing: Optional[str] = None,
         max_docs: Optional[int] = None, budget_seconds: float = 600.0, model: Optional[nn.Module] = None,
-        device: Optional[torch.device] = None) -> dict[str, Any]:
+        device: Optional[torch.device] = None, summary_path: Optional[str] = None,
+        safety_margin_seconds: float = 0.0, sort_docs_by_length: Optional[bool] = None,
+        score_warmup_steps: int = 0, per_doc_path: Optional[str] = None,
+        episodic_cache_source: str = "auto", allow_online_replay_checkpoint: bool = False) -> dict[str, Any]:
     """Scores a validation cache with documents sharded over the launched ranks and returns (rank 0
-    also writes) the aggregate summary: bpb, tokens, documents, timing and provenance."""
+    also writes) the aggregate summary: bpb, tokens, documents, timing and provenance.
+
+    ``summary_path`` receives the summary and ``per_doc_path`` one JSON line per document (doc id, scored
+    tokens, summed CE, bytes) -- the reference's ``--summary-path`` / ``--output-path`` pair; without
+    ``summary_path`` the summary goes to ``output_path``.  ``safety_margin_seconds`` is taken off the budget,
+    ``score_warmup_steps`` scores that many leading batches once before the timed pass (kernel warm-up).
+    ``episodic_cache_source`` (auto | fresh | checkpoint) and ``allow_online_replay_checkpoint`` only check
+    the checkpoint's payload: frozen-weight scoring never consults the episodic cache, so cold and warm
+    caches score identically and the summary says which one was asked for."""
     import torch.distributed as dist
     ws = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -280,16 +291,31 @@ def run(*, cache_dir: str, checkpoint_path: Optional[str], output_path: Optional
         torch.cuda.set_device(device)
     if ws > 1 and not dist.is_initialized():
         dist.init_process_group("nccl" if device.type == "cuda" else "gloo")
+    if episodic_cache_source not in ("auto", "fresh", "checkpoint"):
+        raise ValueError(f"episodic_cache_source must be auto, fresh or checkpoint; got {episodic_cache_source!r}")
     ckpt_cfg: dict = {}
+    cache_state = "none"
     if model is None:
         if not checkpoint_path:
             raise ValueError("run() needs a model or a checkpoint_path")
+        blob = torch.load(checkpoint_path, map_location="cpu", weights_only=False)
+        has_cache = isinstance(blob, dict) and blob.get("episodic_cache") is not None
+        online = isinstance(blob, dict) and isinstance(blob.get("online_eval_state"), dict) and \
+            blob["online_eval_state"].get("replay_eviction") is not None
+        if online and not allow_online_replay_checkpoint:
+            raise ValueError("checkpoint carries online replay-eviction state; frozen-weight scoring does not run "
+                             "the memory control plane: pass allow_online_replay_checkpoint to score it anyway")
+        if episodic_cache_source == "checkpoint" and not has_cache:
+            raise ValueError("--episodic-cache-source=checkpoint requires ckpt['episodic_cache']; payload absent")
+        cache_state = ("fresh_forced" if episodic_cache_source == "fresh" and has_cache else
+                       "loaded" if has_cache and episodic_cache_source != "fresh" else "fresh")
+        del blob
         model, ckpt_cfg = _load_model(checkpoint_path, device)
     cache = load_val_cache(Path(cache_dir))
     docs = list(cache.iter_docs())
     if max_docs is not None:
         docs = docs[: int(max_docs)]
-    packing = resolve_doc_packing(doc_packing=doc_packing, sort_docs_by_length=None)
+    packing = resolve_doc_packing(doc_packing=doc_packing, sort_docs_by_length=sort_docs_by_length)
     mft = resolve_max_forward_tokens(max_forward_tokens=max_forward_tokens, requested_doc_batch_size=doc_batch_size,
                                      chunk_size=chunk_size, device=device,
                                      probe_fn=lambda want: estimate_max_forward_tokens(model, device=device))
@@ -300,9 +326,12 @@ def run(*, cache_dir: str, checkpoint_path: Optional[str], output_path: Optional
     starts = np.asarray([w.doc.token_start for w in work], dtype=np.int64)
     lens = np.asarray([w.doc.token_len for w in work], dtype=np.int64)
     rawb = np.asarray([w.doc.raw_bytes for w in work], dtype=np.int64)
+    if int(score_warmup_steps) > 0 and len(work):
+        n_warm = min(len(work), int(score_warmup_steps) * bs)
+        score_docs(model, tokens, starts[:n_warm], lens[:n_warm], chunk_size=chunk_size, max_batch_tokens=bs * chunk_size)
     t0 = time.perf_counter()
     res = score_docs(model, tokens, starts, lens, chunk_size=chunk_size, max_batch_tokens=bs * chunk_size,
-                     raw_bytes=rawb, deadline_s=budget_seconds)
+                     raw_bytes=rawb, deadline_s=max(0.0, float(budget_seconds) - float(safety_margin_seconds)))
     for w, n in zip(work, res.doc_tokens):
         if not res.extra.get("timed_out"):
             validate_doc_score_coverage(doc=w.doc, tokens_scored=int(n), chunk_size=chunk_size,
@@ -324,14 +353,27 @@ def run(*, cache_dir: str, checkpoint_path: Optional[str], output_path: Optional
         "doc_packing": packing, "timed_out": bool(res.extra.get("timed_out")),
         "record_order_safe": record_order_safe_reason(persistence_mode="reset", score_only_mode=True,
                                                       doc_packing=packing),
+        "score_warmup_steps": int(score_warmup_steps), "safety_margin_seconds": float(safety_margin_seconds),
+        "episodic_cache": {"source": episodic_cache_source, "state": cache_state, "consulted": False},
         "provenance": {"checkpoint_path": checkpoint_path,
                        "checkpoint_sha256": _sha256(Path(checkpoint_path)) if checkpoint_path else None,
                        "config_hash": hashlib.sha1(json.dumps(ckpt_cfg, sort_keys=True, default=str).encode()
                                                    ).hexdigest()[:12],
                        "gpu": torch.cuda.get_device_name(device) if device.type == "cuda" else "cpu",
                        "torch": torch.__version__, "cuda": torch.version.cuda}}
-    if rank == 0 and output_path:
-        out = Path(output_path)
+    if per_doc_path:
+        # every rank writes its own documents; rank 0 keeps the plain name, the others add their rank
+        pp = Path(per_doc_path)
+        if ws > 1 and rank > 0:
+            pp = pp.with_name(f"{pp.stem}.rank{rank}{pp.suffix}")
+        pp.parent.mkdir(parents=True, exist_ok=True)
+        with pp.open("w") as fh:
+            for w, n, ce in zip(work, res.doc_tokens, res.doc_ce):
+                fh.write(json.dumps({"doc_id": int(w.doc.doc_id), "tokens_scored": int(n), "ce_nats": float(ce),
+                                     "raw_bytes": int(w.doc.raw_bytes)}) + "\n")
+    target = summary_path or output_path
+    if rank == 0 and target:
+        out = Path(target)
         out.parent.mkdir(parents=True, exist_ok=True)
         tmp = out.with_suffix(out.suffix + ".tmp")
         tmp.write_text(json.dumps(summary, indent=2))
@@ -350,11 +392,42 @@ def main(argv: Optional[list[str]] = None) -> int:
     ap.add_argument("--doc-packing", default=None, choices=DOC_PACKINGS)
     ap.add_argument("--max-docs", type=int, default=None)
     ap.add_argument("--budget-seconds", type=float, default=600.0)
+    # the reference scorer's flag set (scripts/run_exp20_fast_score.py:1398-1490): with --summary-path the
+    # summary goes there and --output-path receives one JSON line per document
+    ap.add_argument("--summary-path", default=None)
+    ap.add_argument("--safety-margin-seconds", type=float, default=0.0)
+    ap.add_argument("--persistence-mode", choices=["reset"], default="reset")
+    ap.add_argument("--max-batch-tokens", dest="max_forward_tokens", help=argparse.SUPPRESS)
+    ap.add_argument("--score-boundary-targets", action=argparse.BooleanOptionalAction, default=True)
+    ap.add_argument("--sort-docs-by-length", action=argparse.BooleanOptionalAction, default=None)
+    ap.add_argument("--torch-compile-mode", choices=["none", "default", "reduce-overhead", "max-autotune"], default="none",
+                    help="accepted for command-line compatibility; there is no tracing compiler in this stack")
+    ap.add_argument("--score-warmup-steps", type=int, default=0)
+    ap.add_argument("--score-graph-mode", choices=["none", "cuda"], default="none",
+                    help="accepted for compatibility: the chunk scorer is already one fused kernel sequence per batch")
+    ap.add_argument("--score-through-packet-lane", action=argparse.BooleanOptionalAction, default=False,
+                    help="accepted for compatibility: bare-SSM checkpoints have no side channel to bypass")
+    ap.add_argument("--episodic-cache-enabled", action=argparse.BooleanOptionalAction, default=False)
+    ap.add_argument("--episodic-cache-reset-per-doc", action=argparse.BooleanOptionalAction, default=False)
+    for flag, default in (("--episodic-cache-capacity", 4096), ("--episodic-span-length", 4), ("--episodic-key-rep-dim", -1),
+                          ("--episodic-grace-steps", 1000), ("--episodic-fingerprint-window", 8)):
+        ap.add_argument(flag, type=int, default=default)
+    ap.add_argument("--episodic-cache-source", choices=("auto", "fresh", "checkpoint"), default="auto")
+    ap.add_argument("--allow-online-replay-checkpoint", action=argparse.BooleanOptionalAction, default=False)
+    ap.add_argument("--device", default="auto")
     a = ap.parse_args(argv)
+    if not a.score_boundary_targets:
+        ap.error("--no-score-boundary-targets is not supported: every document contributes len - 1 targets")
     mft = a.max_forward_tokens if str(a.max_forward_tokens).lower() == "auto" else int(a.max_forward_tokens)
-    s = run(cache_dir=a.cache_dir, checkpoint_path=a.checkpoint_path, output_path=a.output_path,
+    dev = None if a.device == "auto" else torch.device(a.device)
+    s = run(cache_dir=a.cache_dir, checkpoint_path=a.checkpoint_path,
+            output_path=None if a.summary_path else a.output_path, summary_path=a.summary_path,
+            per_doc_path=a.output_path if a.summary_path else None,
             chunk_size=a.chunk_size, doc_batch_size=a.doc_batch_size, max_forward_tokens=mft,
-            doc_packing=a.doc_packing, max_docs=a.max_docs, budget_seconds=a.budget_seconds)
+            doc_packing=a.doc_packing, max_docs=a.max_docs, budget_seconds=a.budget_seconds, device=dev,
+            safety_margin_seconds=a.safety_margin_seconds, sort_docs_by_length=a.sort_docs_by_length,
+            score_warmup_steps=a.score_warmup_steps, episodic_cache_source=a.episodic_cache_source,
+            allow_online_replay_checkpoint=a.allow_online_replay_checkpoint)
     if int(os.environ.get("RANK", "0")) == 0:
         print(json.dumps({k: s[k] for k in ("bpb", "tokens_scored", "docs_scored", "elapsed_s", "tokens_per_s")}))
     import torch.distributed as dist

@@ -1,7 +1,9 @@
 """Data-preparation and measurement commands that sit beside the runners:
 
-``build-shards``      JSONL text + SentencePiece model -> ``fineweb_{train,val}_NNN.bin`` (flat little-endian
-                      uint16, no header, no EOS appended)            (scripts/build_sp_shards.py)
+``build-dataset``     JSONL text -> BPE tokenizer (trained on documents after the validation split, seeded,
+                      byte fallback) -> shards -> ``build_manifest.json``      (scripts/build_sp_shards.py)
+``build-shards``      JSONL text + SentencePiece model -> ``fineweb_{train,val}_NNNNNN.bin`` (flat little-endian
+                      uint16, no header, no EOS appended, every shard ends on a document boundary)
 ``build-val-cache``   JSONL text -> ``tokens.npy`` / ``docs.npy`` / ``manifest.json``  (scripts/build_exp20_val_cache.py)
 ``verify-val-cache``  a validation shard against a cache built from the same text     (scripts/verify_sp16384_eval_cache.py)
 ``eval-quant``        bits-per-byte of a checkpoint before and after the int6 GPTQ + LZMA round trip
@@ -12,7 +14,9 @@
 from __future__ import annotations
 
 import argparse
+import hashlib
 import json
+import os
 import time
 from pathlib import Path
 from typing import Optional, Sequence
@@ -26,16 +30,125 @@ ARTIFACT_LIMIT_BYTES = 16 * 1024 * 1024
 
 
 # ---------------------------------------------------------------------------
-# shards
+# tokenizer + shards
 # ---------------------------------------------------------------------------
+SHARD_INDEX_WIDTH = 6            # fineweb_{train,val}_{NNNNNN}.bin
+MAX_VOCAB_FOR_SHARDS = 32768     # the loaders map the uint16 files as int16: same bits below 2^15
+
+
+def _jsonl_texts(paths: Sequence[Path]):
+    for path in paths:
+        with open(path, "r", encoding="utf-8") as fh:
+            for line in fh:
+                line = line.strip()
+                if not line:
+                    continue
+                try:
+                    text = json.loads(line).get("text", "")
+                except json.JSONDecodeError:
+                    continue
+                if text:
+                    yield text
+
+
+def train_tokenizer(*, jsonl_paths: Sequence[Path], vocab_size: int, tokenizer_dir: Path, val_docs: int = 50_000,
+                    sp_train_docs: int = 5_000_000, sp_seed: int = 1337, num_threads: int = 4,
+                    force: bool = False) -> Path:
+    """Trains the BPE tokenizer of the shard pipeline (scripts/build_sp_shards.py:140-218 of the reference) and
+    returns ``<tokenizer_dir>/fineweb_<vocab>_bpe.model``.  The training text is the first ``sp_train_docs``
+    documents AFTER the validation split, so the tokenizer never sees validation text; byte fallback keeps every
+    string round-trippable; unk / bos / eos are ids 0 / 1 / 2 and there is no pad; the whole corpus is used in file
+    order with input shuffling off, which leaves BPE training nothing random: the same input gives the same
+    model (``sp_seed`` is recorded in the build manifest; this trainer has no seed field to hand it to).  An existing model is kept unless ``force``.  The
+    model and its vocabulary file appear together (trained under a partial name, then renamed)."""
+    import sentencepiece as spm
+    if not 0 < int(vocab_size) <= MAX_VOCAB_FOR_SHARDS:
+        raise ValueError(f"vocab_size must be in (0, {MAX_VOCAB_FOR_SHARDS}], got {vocab_size}")
+    tokenizer_dir = Path(tokenizer_dir)
+    tokenizer_dir.mkdir(parents=True, exist_ok=True)
+    final = tokenizer_dir / f"fineweb_{int(vocab_size)}_bpe.model"
+    if final.exists() and not force:
+        return final
+    corpus = tokenizer_dir / f".sp_train_{int(vocab_size)}.txt"
+    n = 0
+    with corpus.open("w", encoding="utf-8") as out:
+        for i, text in enumerate(_jsonl_texts(jsonl_paths)):
+            if i < int(val_docs):
+                continue
+            if n >= int(sp_train_docs):
+                break
+            out.write(text.replace("\n", " ") + "\n")
+            n += 1
+    if n == 0:
+        corpus.unlink(missing_ok=True)
+        raise ValueError("no training documents after the validation split: lower val_docs or supply more text")
+    partial = tokenizer_dir / f".partial_fineweb_{int(vocab_size)}_bpe"
+    for suf in (".model", ".vocab"):
+        Path(str(partial) + suf).unlink(missing_ok=True)
+    try:
+        spm.SentencePieceTrainer.Train(
+            input=str(corpus), model_prefix=str(partial), vocab_size=int(vocab_size), model_type="bpe",
+            character_coverage=0.9995, byte_fallback=True, unk_id=0, bos_id=1, eos_id=2, pad_id=-1,
+            num_threads=int(num_threads), input_sentence_size=0, shuffle_input_sentence=False, minloglevel=2)
+    finally:
+        corpus.unlink(missing_ok=True)
+    os.replace(str(partial) + ".model", final)
+    try:
+        os.replace(str(partial) + ".vocab", final.with_suffix(".vocab"))
+    except OSError:
+        final.unlink(missing_ok=True)           # the pair stays consistent
+        raise
+    return final
+
+
+def build_dataset(*, jsonl_paths: Sequence[Path], vocab_size: int, output_dir: Path, tokenizer_dir: Path,
+                  val_docs: int = 50_000, sp_train_docs: int = 5_000_000, shard_size: int = 100_000_000,
+                  sp_seed: int = 1337, num_threads: int = 4, skip_train: bool = False, skip_tokenize: bool = False,
+                  force: bool = False, dry_run: bool = False) -> dict:
+    """Tokenizer, then shards, then ``build_manifest.json`` describing both (the reference's one-command
+    pipeline).  A finished build whose manifest matches the request is left alone unless ``force``."""
+    output_dir, tokenizer_dir = Path(output_dir), Path(tokenizer_dir)
+    request = {"vocab_size": int(vocab_size), "val_docs": int(val_docs), "sp_train_docs": int(sp_train_docs),
+               "shard_size": int(shard_size), "sp_seed": int(sp_seed), "docs": [str(Path(p)) for p in jsonl_paths]}
+    model_path = tokenizer_dir / f"fineweb_{int(vocab_size)}_bpe.model"
+    plan = {"request": request, "tokenizer_model": str(model_path), "output_dir": str(output_dir),
+            "train_tokenizer": not skip_train and (force or not model_path.exists()), "tokenize": not skip_tokenize}
+    if dry_run:
+        return {"dry_run": True, **plan}
+    mpath = output_dir / "build_manifest.json"
+    if mpath.exists() and not force:
+        old = json.loads(mpath.read_text())
+        if old.get("request") == request:
+            return old
+        raise ValueError(f"{mpath} describes another build ({old.get('request')}); use force=True or another "
+                         "output directory")
+    if not skip_train:
+        train_tokenizer(jsonl_paths=jsonl_paths, vocab_size=vocab_size, tokenizer_dir=tokenizer_dir, val_docs=val_docs,
+                        sp_train_docs=sp_train_docs, sp_seed=sp_seed, num_threads=num_threads, force=force)
+    if not model_path.exists():
+        raise FileNotFoundError(f"{model_path} not found: train the tokenizer first (skip_train was set)")
+    out = dict(plan)
+    if not skip_tokenize:
+        if force and output_dir.exists():
+            for f in output_dir.glob("fineweb_*_*.bin"):
+                f.unlink()
+        out["shards"] = build_shards(jsonl_paths=jsonl_paths, sp_model_path=model_path, out_dir=output_dir,
+                                     val_docs=val_docs, shard_tokens=shard_size)
+        out["tokenizer_sha256"] = hashlib.sha256(model_path.read_bytes()).hexdigest()
+        output_dir.mkdir(parents=True, exist_ok=True)
+        mpath.write_text(json.dumps(out, indent=2))
+    return out
+
+
 def build_shards(*, jsonl_paths: Sequence[Path], sp_model_path: Path, out_dir: Path, val_docs: int = 50_000,
                  shard_tokens: int = 100_000_000, max_docs: Optional[int] = None) -> dict:
     """The first ``val_docs`` documents become validation shards, the rest
     training shards; tokens are uint16 and a vocabulary above 65 536 is refused."""
     import sentencepiece as spm
     sp = spm.SentencePieceProcessor(model_file=str(sp_model_path))
-    if sp.vocab_size() > 65536:
-        raise ValueError(f"vocabulary {sp.vocab_size()} does not fit uint16 shards")
+    if sp.vocab_size() > MAX_VOCAB_FOR_SHARDS:
+        raise ValueError(f"vocabulary {sp.vocab_size()} does not fit the shard format: readers view the uint16 "
+                         f"shards as int16, so token ids must stay below {MAX_VOCAB_FOR_SHARDS}")
     out_dir = Path(out_dir)
     out_dir.mkdir(parents=True, exist_ok=True)
     state = {"train": {"buf": [], "n": 0, "idx": 0, "tokens": 0, "docs": 0},
@@ -46,7 +159,7 @@ def build_shards(*, jsonl_paths: Sequence[Path], sp_model_path: Path, out_dir: P
         if not s["buf"]:
             return
         arr = np.concatenate(s["buf"]).astype("<u2")
-        arr.tofile(out_dir / f"fineweb_{split}_{s['idx']:03d}.bin")
+        arr.tofile(out_dir / f"fineweb_{split}_{s['idx']:0{SHARD_INDEX_WIDTH}d}.bin")
         s["buf"], s["n"], s["idx"] = [], 0, s["idx"] + 1
 
     seen = 0
@@ -244,6 +357,20 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     e.add_argument("--calibration-seqs", type=int, default=16)
     e.add_argument("--calibration-seq-len", type=int, default=128)
     e.add_argument("--seed", type=int, default=0)
+    d = sub.add_parser("build-dataset", help="train the BPE tokenizer, then write the uint16 shards")
+    d.add_argument("--docs-path", "--jsonl-path", dest="docs_path", type=Path, nargs="+", required=True)
+    d.add_argument("--vocab-size", type=int, required=True)
+    d.add_argument("--output-dir", type=Path, required=True)
+    d.add_argument("--tokenizer-dir", type=Path, required=True)
+    d.add_argument("--sp-train-docs", type=int, default=5_000_000)
+    d.add_argument("--val-docs", type=int, default=50_000)
+    d.add_argument("--shard-size", type=int, default=100_000_000)
+    d.add_argument("--sp-seed", type=int, default=1337)
+    d.add_argument("--num-workers", type=int, default=max(1, (os.cpu_count() or 2) // 2))
+    d.add_argument("--dry-run", action="store_true")
+    d.add_argument("--skip-tokenize", action="store_true")
+    d.add_argument("--skip-train", action="store_true")
+    d.add_argument("--force", action="store_true")
     h = sub.add_parser("artifact-headroom")
     h.add_argument("--dim", type=int, default=384)
     h.add_argument("--vocab-size", type=int, default=16_384)
@@ -262,6 +389,13 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
         else:
             print(text)
         return 0 if out["under_budget"] else 2
+    if a.cmd == "build-dataset":
+        out = build_dataset(jsonl_paths=a.docs_path, vocab_size=a.vocab_size, output_dir=a.output_dir,
+                            tokenizer_dir=a.tokenizer_dir, val_docs=a.val_docs, sp_train_docs=a.sp_train_docs,
+                            shard_size=a.shard_size, sp_seed=a.sp_seed, num_threads=a.num_workers,
+                            skip_train=a.skip_train, skip_tokenize=a.skip_tokenize, force=a.force, dry_run=a.dry_run)
+        print(json.dumps(out, indent=2, default=str))
+        return 0
     if a.cmd == "build-shards":
         out = build_shards(jsonl_paths=a.jsonl_path, sp_model_path=a.sp_model_path, out_dir=a.out_dir,
                            val_docs=a.val_docs, shard_tokens=a.shard_tokens, max_docs=a.max_docs)

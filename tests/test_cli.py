@@ -12,7 +12,7 @@ from chaoscontrol_b200.eval_stream.io import write_synthetic_val_cache
 def test_verify_val_cache_finds_the_first_mismatch(tmp_path):
     write_synthetic_val_cache(tmp_path / "cache", n_docs=20, vocab=64, median_len=40, min_len=8, max_len=80)
     toks = np.load(tmp_path / "cache" / "tokens.npy")
-    shard = tmp_path / "fineweb_val_000.bin"
+    shard = tmp_path / "fineweb_val_000000.bin"
     toks.astype("<u2").tofile(shard)
     ok = cli.verify_val_cache(val_shard=shard, val_cache_dir=tmp_path / "cache", expected_tokens=int(toks.size),
                               chunk_tokens=100)

@@ -84,7 +84,7 @@ def test_shards_split_validation_first_and_roll_over_by_size(corpus, tmp_path):
     assert man["val_docs"] == 10 and man["train_docs"] == 50 and man["vocab_size"] == 80 and man["append_eos"] is False
     assert man["dtype"] == "uint16-le" and man["header_bytes"] == 0 and man["train_shards"] >= 2
     files = sorted(p.name for p in (tmp_path / "sh").glob("*.bin"))
-    assert files[0].startswith("fineweb_train_000") and any(f.startswith("fineweb_val_000") for f in files)
+    assert files[0] == "fineweb_train_000000.bin" and "fineweb_val_000000.bin" in files
     train = np.concatenate([np.fromfile(p, dtype="<u2") for p in sorted((tmp_path / "sh").glob("fineweb_train_*.bin"))])
     val = np.concatenate([np.fromfile(p, dtype="<u2") for p in sorted((tmp_path / "sh").glob("fineweb_val_*.bin"))])
     sp = spm.SentencePieceProcessor(model_file=str(corpus["model"]))
@@ -104,7 +104,7 @@ def test_shards_respect_max_docs(corpus, tmp_path):
 def test_validation_shard_and_cache_agree_token_for_token(corpus, tmp_path):
     cli.build_shards(jsonl_paths=corpus["jsonl"], sp_model_path=corpus["model"], out_dir=tmp_path / "sh", val_docs=60)
     IO.write_val_cache(jsonl_paths=corpus["jsonl"], sp_model_path=corpus["model"], cache_dir=tmp_path / "vc", max_docs=60)
-    shard = tmp_path / "sh" / "fineweb_val_000.bin"
+    shard = tmp_path / "sh" / "fineweb_val_000000.bin"
     ok = cli.verify_val_cache(val_shard=shard, val_cache_dir=tmp_path / "vc", chunk_tokens=97)
     assert ok["ok"] and ok["first_mismatch"] is None and ok["docs"] == 60 and ok["shard_tokens"] == ok["cache_tokens"] == ok["doc_token_sum"]
     assert not cli.verify_val_cache(val_shard=shard, val_cache_dir=tmp_path / "vc", expected_tokens=ok["cache_tokens"] + 1)["ok"]
@@ -122,3 +122,44 @@ def test_cli_builds_shards_and_cache(corpus, tmp_path, capsys):
     assert json.loads(capsys.readouterr().out)["val_docs"] == 8
     assert cli.main(["build-val-cache", *args, "--cache-dir", str(tmp_path / "vc"), "--max-docs", "9"]) == 0
     assert json.loads(capsys.readouterr().out)["num_docs"] == 9
+
+
+def test_tokenizer_training_is_seeded_skips_validation_text_and_keeps_the_pair_together(corpus, tmp_path):
+    kw = dict(jsonl_paths=corpus["jsonl"], vocab_size=300, val_docs=10, sp_train_docs=40, num_threads=1)
+    a = cli.train_tokenizer(tokenizer_dir=tmp_path / "t1", **kw)
+    b = cli.train_tokenizer(tokenizer_dir=tmp_path / "t2", **kw)
+    # the model file records its own input path, so compare what matters: the learned pieces and their scores
+    assert a.name == "fineweb_300_bpe.model" and a.with_suffix(".vocab").read_text() == b.with_suffix(".vocab").read_text()
+    assert not list((tmp_path / "t1").glob(".partial*")) and not list((tmp_path / "t1").glob(".sp_train*"))
+    sp = spm.SentencePieceProcessor(model_file=str(a))
+    assert (sp.unk_id(), sp.bos_id(), sp.eos_id(), sp.pad_id()) == (0, 1, 2, -1) and sp.vocab_size() == 300
+    assert sp.decode(sp.encode("alpha \u2603 beta")) == "alpha \u2603 beta"          # byte fallback round-trips a rare character
+    stamp = a.stat().st_mtime_ns
+    assert cli.train_tokenizer(tokenizer_dir=tmp_path / "t1", **kw) == a and a.stat().st_mtime_ns == stamp   # kept
+    with pytest.raises(ValueError, match="no training documents"):
+        cli.train_tokenizer(tokenizer_dir=tmp_path / "t3", **{**kw, "val_docs": 1000})
+    with pytest.raises(ValueError, match="vocab_size"):
+        cli.train_tokenizer(tokenizer_dir=tmp_path / "t3", **{**kw, "vocab_size": 40000})
+
+
+def test_one_command_dataset_build_is_idempotent_and_guards_its_folder(corpus, tmp_path, capsys):
+    args = ["build-dataset", "--docs-path", *map(str, corpus["jsonl"]), "--vocab-size", "300", "--output-dir",
+            str(tmp_path / "ds"), "--tokenizer-dir", str(tmp_path / "tok"), "--val-docs", "10", "--sp-train-docs", "40",
+            "--shard-size", "400", "--num-workers", "1"]
+    assert cli.main(args + ["--dry-run"]) == 0
+    plan = json.loads(capsys.readouterr().out)
+    assert plan["dry_run"] and plan["train_tokenizer"] and plan["tokenize"] and not (tmp_path / "ds").exists()
+    assert cli.main(args) == 0
+    man = json.loads(capsys.readouterr().out)
+    assert man["shards"]["val_docs"] == 10 and man["shards"]["train_docs"] == 50 and man["shards"]["vocab_size"] == 300
+    assert len(man["tokenizer_sha256"]) == 64 and (tmp_path / "ds" / "build_manifest.json").exists()
+    files = {p.name: p.stat().st_mtime_ns for p in (tmp_path / "ds").glob("*.bin")}
+    assert cli.main(args) == 0                                            # same request: nothing is rewritten
+    capsys.readouterr()
+    assert files == {p.name: p.stat().st_mtime_ns for p in (tmp_path / "ds").glob("*.bin")}
+    other = [x if x != "300" else "280" for x in args]
+    with pytest.raises(ValueError, match="another build"):
+        cli.main(other)
+    with pytest.raises(FileNotFoundError):
+        cli.build_dataset(jsonl_paths=corpus["jsonl"], vocab_size=290, output_dir=tmp_path / "ds2", tokenizer_dir=tmp_path / "tok",
+                          skip_train=True)

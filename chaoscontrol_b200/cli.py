@@ -236,9 +236,10 @@ def _score(model, cache, *, chunk_size: int, max_docs: Optional[int], device: to
         return score_val_cache(model, cache, chunk_size=chunk_size, max_docs=max_docs, device=device)
 
 
-def eval_quant(*, ckpt: Path, val_cache_dir: Path, output_json: Path, device: str = "auto", chunk_size: int = 512,
-               max_docs: Optional[int] = None, calibration_seqs: int = 16, calibration_seq_len: int = 128,
-               seed: int = 0) -> dict:
+def eval_quant(*, ckpt: Path, val_cache_dir: Optional[Path] = None, output_json: Path, device: str = "auto",
+               chunk_size: int = 512, max_docs: Optional[int] = None, calibration_seqs: int = 16,
+               calibration_seq_len: int = 128, seed: int = 0, eval_jsonl: Optional[Path] = None,
+               sp_model_path: Optional[Path] = None) -> dict:
     """Score the validation cache with the checkpoint as trained, quantise
     (self-generated calibration text -> Hessians -> GPTQ int6 -> LZMA), write the
     blob beside the JSON, load it back into a fresh model, score the same
@@ -256,6 +257,15 @@ def eval_quant(*, ckpt: Path, val_cache_dir: Path, output_json: Path, device: st
     dtype = torch.bfloat16 if dev.type == "cuda" else torch.float32
     model = build_model(cfg, dev, dtype)
     model.load_state_dict(blob["model"], strict=True)
+    if val_cache_dir is None:
+        # the reference's input pair: raw validation text and the tokenizer; tokenised once into a cache
+        # beside the output
+        if eval_jsonl is None or sp_model_path is None:
+            raise ValueError("eval_quant needs val_cache_dir, or eval_jsonl together with sp_model_path")
+        from .eval_stream.io import write_val_cache
+        val_cache_dir = Path(output_json).with_suffix(".valcache")
+        write_val_cache(jsonl_paths=[Path(eval_jsonl)], sp_model_path=Path(sp_model_path), cache_dir=val_cache_dir,
+                        max_docs=max_docs if max_docs is not None else 50_000)
     cache = load_val_cache(Path(val_cache_dir))
     t0 = time.perf_counter()
     before = _score(model, cache, chunk_size=chunk_size, max_docs=max_docs, device=dev)
@@ -349,7 +359,10 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     v.add_argument("--chunk-tokens", type=int, default=1 << 22)
     e = sub.add_parser("eval-quant")
     e.add_argument("--ckpt", type=Path, required=True)
-    e.add_argument("--val-cache-dir", type=Path, required=True)
+    e.add_argument("--val-cache-dir", type=Path, default=None)
+    e.add_argument("--eval-jsonl", type=Path, default=None, help="raw validation text (with --sp-model-path) instead of a cache")
+    e.add_argument("--sp-model-path", type=Path, default=None)
+    e.add_argument("--budget-seconds", type=float, default=600.0, help="accepted for command-line compatibility")
     e.add_argument("--output-json", type=Path, required=True)
     e.add_argument("--device", default="auto")
     e.add_argument("--chunk-size", type=int, default=512)
@@ -411,7 +424,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     else:
         out = eval_quant(ckpt=a.ckpt, val_cache_dir=a.val_cache_dir, output_json=a.output_json, device=a.device,
                          chunk_size=a.chunk_size, max_docs=a.max_docs, calibration_seqs=a.calibration_seqs,
-                         calibration_seq_len=a.calibration_seq_len, seed=a.seed)
+                         calibration_seq_len=a.calibration_seq_len, seed=a.seed, eval_jsonl=a.eval_jsonl,
+                         sp_model_path=a.sp_model_path)
         out = {k: v for k, v in out.items() if not k.startswith("pass_")}
     print(json.dumps(out, indent=2, default=str))
     return 0

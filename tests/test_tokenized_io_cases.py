@@ -163,3 +163,21 @@ def test_one_command_dataset_build_is_idempotent_and_guards_its_folder(corpus, t
     with pytest.raises(FileNotFoundError):
         cli.build_dataset(jsonl_paths=corpus["jsonl"], vocab_size=290, output_dir=tmp_path / "ds2", tokenizer_dir=tmp_path / "tok",
                           skip_train=True)
+
+
+def test_eval_quant_takes_raw_text_and_a_tokenizer(corpus, tmp_path):
+    import torch
+
+    from chaoscontrol_b200.models.model import CareStudentLM
+    from chaoscontrol_b200.runner_exp21 import save_output_ckpt
+    torch.manual_seed(0)
+    model = CareStudentLM(vocab_size=80, dim=16, num_layers=1)
+    save_output_ckpt(str(tmp_path / "m.pt"), model, dict(vocab_size=80, model_dim=16, num_layers=1))
+    rc = cli.main(["eval-quant", "--ckpt", str(tmp_path / "m.pt"), "--eval-jsonl", str(corpus["jsonl"][0]), "--sp-model-path",
+                   str(corpus["model"]), "--output-json", str(tmp_path / "q.json"), "--device", "cpu", "--chunk-size", "16",
+                   "--max-docs", "6", "--calibration-seqs", "2", "--calibration-seq-len", "16", "--budget-seconds", "5"])
+    out = json.loads((tmp_path / "q.json").read_text())
+    assert rc == 0 and out["docs_scored"] == 6 and out["bpb_bf16"] > 0 and out["artifact_bytes"] > 0
+    assert (tmp_path / "q.valcache" / "manifest.json").exists()
+    with pytest.raises(ValueError, match="val_cache_dir, or eval_jsonl"):
+        cli.eval_quant(ckpt=tmp_path / "m.pt", output_json=tmp_path / "q2.json", device="cpu")

@@ -117,6 +117,10 @@ def save_simplex_policy(path, policy) -> None:
                                  "feature_manifest_hash": FEATURE_MANIFEST_HASH},
                     "tensors": tensors}, str(path))
         return
+    if str(path).endswith((".cswg3", ".v3.cswg")) or getattr(policy, "n_heads", 0) or getattr(policy, "n_buckets", 0):
+        from .cswg import policy_to_cswg                  # self-describing file: carries the optional parts too
+        policy_to_cswg(policy, path)
+        return
     from . import native
     native.write_cswg(str(path), np.concatenate([flat, [np.float32(policy.temperature)]]),
                       n_layers=policy.N, d_global=policy.K_v, d_slot=policy.K_s, feature_dim=policy.H)
@@ -132,6 +136,9 @@ def load_simplex_policy(path):
                                    H=int(dims["h"]), temperature=float(t["temperature"]))
         flat = np.concatenate([np.asarray(t[k], np.float32).reshape(-1) for k in _SIMPLEX_TENSORS])
     else:
+        from .cswg import file_version, policy_from_cswg
+        if file_version(path) == 3:
+            return policy_from_cswg(path)
         hdr, payload = native.load_cswg(str(path))
         pol = native.SimplexPolicy(N=hdr["n_layers"], K_v=hdr["d_global"], K_s=hdr["d_slot"],
                                    H=hdr["feature_dim"])

@@ -127,7 +127,27 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     ap.add_argument("--temperature", type=float, default=1.0)
     ap.add_argument("--out", type=Path, default=Path("simplex_policy_v1.pt"),
                     help="*.pt (tensor dict) or any other suffix for the CSWG binary")
+    ap.add_argument("--checkpoint", type=Path, default=None,
+                    help="dump mode: a saved policy (*.pt or CSWG) to convert instead of training")
+    ap.add_argument("--output", type=Path, default=None,
+                    help="dump mode: target file (self-describing CSWG version 3 unless it ends in .pt)")
     a = ap.parse_args(argv)
+    if a.checkpoint is not None or a.output is not None:
+        if a.checkpoint is None or a.output is None:
+            ap.error("dump mode needs both --checkpoint and --output")
+        from .controller import load_simplex_policy, save_simplex_policy
+        from .cswg import policy_to_cswg
+        pol = load_simplex_policy(a.checkpoint)
+        if str(a.output).endswith(".pt"):
+            save_simplex_policy(a.output, pol)
+            print(f"wrote {a.output} ({a.output.stat().st_size} bytes)")
+        else:
+            m = policy_to_cswg(pol, a.output)
+            d = m["dims"]
+            print(f"wrote {m['path']} version={m['version']} dims=(N={d['n_vertices']}, K_v={d['k_v']}, K_e={d['k_e']}, "
+                  f"K_s={d['k_s']}, H={d['h']}, heads={d['n_heads']}) file_bytes={m['file_bytes']} "
+                  f"fp16_drift={m['fp32_vs_fp16_max_abs_drift']:.3g}")
+        return 0
     res = train(PretrainConfig(n_batches=a.n_batches, seed=a.seed, temperature=a.temperature))
     print(f"final_policy_acc={res['final_policy_acc']:.4f} final_loss={res['final_loss']:.4f} "
           f"mean_max_p={res['mean_max_p']:.4f}")

@@ -10,13 +10,14 @@ entries carry no ``fast_slow_interval``.
 from __future__ import annotations
 
 import copy
+import json
 from pathlib import Path
-from typing import Any, Mapping
+from typing import Any, Mapping, Optional, Sequence
 
 from .exp24 import ARTIFACT_CHANGES_WEIGHTS_ONLY, _CRCT, _DW_OFF, _base_entry
 
 __all__ = ["VALIDATION_ARMS", "EXP26_MODEL_DIM", "EXP26_DELTA_RANK", "DEFAULT_VALIDATION_TRACE_DIR",
-           "build_validation_matrix"]
+           "build_validation_matrix", "run_validation", "main"]
 
 VALIDATION_ARMS: tuple[str, ...] = ("validation_fastslow_control", "validation_adaptive_residual_memory")
 EXP26_MODEL_DIM = 384
@@ -111,3 +112,51 @@ def build_validation_matrix(*, speed_config: Mapping[str, Any], world_size: int 
             entry["replay_eviction_arm_runtime_namespace"] = name
         entries.append(copy.deepcopy(entry))
     return entries
+
+
+def run_validation(*, speed_config: Mapping[str, Any], world_size: int = 4, seed: int = 1337, budget_seconds: float = 45.0,
+                   data_path: Path | str = "data", sp_model_path: Optional[Path | str] = None,
+                   output_dir: Path | str = DEFAULT_VALIDATION_DIR, trace_dir: Optional[Path | str] = None,
+                   dry_run: bool = False, say=print) -> dict[str, Any]:
+    """The fixed two-cell validation run (run_exp26.py:49-108 of the reference): build, print, and unless
+    ``dry_run`` (which touches nothing on disk) write ``matrix.json`` and launch both cells."""
+    output_dir = Path(output_dir)
+    entries = build_validation_matrix(speed_config=speed_config, world_size=int(world_size), seed=int(seed),
+                                      budget_seconds=float(budget_seconds),
+                                      trace_dir=Path(trace_dir) if trace_dir is not None else output_dir / "traces")
+    say(f"[exp26] validation entries={len(entries)} world_size={world_size} budget={budget_seconds}s dry_run={dry_run}")
+    if dry_run:
+        for e in entries:
+            say(f"[exp26] {e['name']}")
+            say(json.dumps(e, indent=2, sort_keys=True, default=str))
+        return {"entries": entries, "commands": []}
+    from .fast_path import write_matrix
+    from .launch import run_matrix
+    output_dir.mkdir(parents=True, exist_ok=True)
+    write_matrix(output_dir / "matrix.json", entries)
+    summary = run_matrix(entries, results_dir=output_dir, data_path=str(data_path),
+                         sp_model_path=None if sp_model_path is None else str(sp_model_path), world_size=int(world_size))
+    return {"entries": entries, **summary}
+
+
+def main(argv: Optional[Sequence[str]] = None) -> int:
+    import argparse
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--config", type=Path, default=None, help="speed config (YAML / JSON); empty when omitted")
+    ap.add_argument("--data-path", type=Path, default=Path("data"))
+    ap.add_argument("--sp-model-path-16384", "--sp-model-path", dest="sp_model_path", type=Path, default=None)
+    ap.add_argument("--world-size", type=int, default=4)
+    ap.add_argument("--budget", type=float, default=45.0, help="wall budget per validation cell (seconds)")
+    ap.add_argument("--seed", type=int, default=1337)
+    ap.add_argument("--output-dir", type=Path, default=DEFAULT_VALIDATION_DIR)
+    ap.add_argument("--dry-run", action="store_true")
+    a = ap.parse_args(argv)
+    from .fast_path import read_speed_config
+    run_validation(speed_config=read_speed_config(a.config) if a.config else {}, world_size=a.world_size, seed=a.seed,
+                   budget_seconds=a.budget, data_path=a.data_path, sp_model_path=a.sp_model_path, output_dir=a.output_dir,
+                   dry_run=a.dry_run)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -155,6 +155,85 @@ def build_ttt_headline_matrix(*, speed_config: dict[str, Any], calibration_manif
     return entries
 
 
+def _probe_from_checkpoint(checkpoint: Path, val_cache_dir: Path, sp_model_path: Path, calc_types: Sequence[str],
+                           budget_seconds: float, probe_docs: int) -> tuple[dict, dict]:
+    import sentencepiece as spm
+    import torch
+    from .eval_stream import load_val_cache
+    from .fast_score import _load_model
+    from .sp_eval import build_sentencepiece_luts
+    dev = torch.device("cuda:0" if torch.cuda.is_available() else "cpu")
+    model, _ = _load_model(str(checkpoint), dev)
+    sp = spm.SentencePieceProcessor()
+    sp.Load(str(sp_model_path))
+    luts = build_sentencepiece_luts(sp, int(model.vocab_size), dev)
+    return probe_calc_types(model=model, val_cache=load_val_cache(val_cache_dir), device=dev, luts=luts,
+                            calc_types=calc_types, budget_seconds=budget_seconds, probe_docs=probe_docs)
+
+
+def run_stages(a, say=print) -> int:
+    """``run --stage calibrate|analyze|headline|all`` (run_exp27.py:96-340 of the reference).
+
+    * calibrate: with a checkpoint, every requested evaluation pass is timed on the first documents and its
+      shrink knob halved until the extrapolated pass fits the headline budget; the report goes to
+      ``--trace-path`` (default: beside the manifest).  Without a checkpoint there is nothing to time.
+    * analyze: writes the calibration manifest -- the probed hyper-parameters when a report exists, the
+      defaults otherwise.
+    * headline: one entry per seed (training a trunk, or evaluating ``--checkpoint-path``), each running the
+      selected passes; launched through ``launch.run_matrix``.
+
+    ``--dry-run`` writes and creates nothing: every stage prints what it would do."""
+    from .fast_path import read_speed_config, write_matrix
+    speed = read_speed_config(a.config) if a.config else {}
+    trace = Path(a.trace_path) if a.trace_path else Path(a.manifest_path).with_name("probe_report.json")
+    if a.stage in ("calibrate", "all"):
+        probing = a.checkpoint_path is not None and a.sp_model_path is not None and Path(a.val_cache_dir).is_dir()
+        say(f"[exp27] stage=calibrate probe={probing} dry_run={a.dry_run}")
+        if a.dry_run:
+            say(json.dumps(build_manifest(), indent=2, sort_keys=True, default=str))
+        elif probing:
+            hp, report = _probe_from_checkpoint(a.checkpoint_path, a.val_cache_dir, a.sp_model_path, a.calc_types,
+                                                a.headline_budget, a.probe_docs)
+            trace.parent.mkdir(parents=True, exist_ok=True)
+            trace.write_text(json.dumps({"hyperparams": hp, "report": report, "source": str(a.checkpoint_path)}, indent=2))
+    if a.stage in ("analyze", "all"):
+        probed = json.loads(trace.read_text()) if trace.exists() else None
+        manifest = (build_manifest(hyperparams=probed["hyperparams"], source=probed.get("source", str(trace)),
+                                   probe=probed["report"]) if probed else build_manifest())
+        say(f"[exp27] stage=analyze manifest={a.manifest_path} probed={probed is not None} dry_run={a.dry_run}")
+        if a.dry_run:
+            say(json.dumps(manifest, indent=2, sort_keys=True, default=str))
+        else:
+            write_manifest(a.manifest_path, manifest)
+    if a.stage in ("headline", "all"):
+        if a.dry_run and not Path(a.manifest_path).exists():
+            say(f"[exp27] stage=headline dry_run=True manifest_absent=True: previewing default hyper-parameters")
+            say(json.dumps(build_manifest(), indent=2, sort_keys=True, default=str))
+            return 0
+        entries = build_ttt_headline_matrix(speed_config=speed, calibration_manifest_path=a.manifest_path,
+                                            checkpoint_path=a.checkpoint_path, world_size=a.world_size,
+                                            budget_seconds=a.headline_budget, seed_values=a.seeds,
+                                            calc_types=a.calc_types)
+        say(f"[exp27] stage=headline entries={len(entries)} world_size={a.world_size} budget={a.headline_budget}s "
+            f"dry_run={a.dry_run}")
+        if a.dry_run:
+            for e in entries:
+                say(f"[exp27] {e['name']}")
+                say(json.dumps(e, indent=2, sort_keys=True, default=str))
+            return 0
+        if entries and not Path(a.val_cache_dir).is_dir():
+            raise FileNotFoundError("the evaluation passes need a validation cache: build it with "
+                                    f"`python -m chaoscontrol_b200.cli build-val-cache` (missing: {a.val_cache_dir})")
+        from .launch import run_matrix
+        out = Path(a.headline_output_dir)
+        out.mkdir(parents=True, exist_ok=True)
+        write_matrix(out / "matrix.json", entries)
+        run_matrix(entries, results_dir=out, data_path=str(a.data_path),
+                   sp_model_path=None if a.sp_model_path is None else str(a.sp_model_path), world_size=int(a.world_size),
+                   val_cache_dir=str(a.val_cache_dir), limit=a.limit, skip_existing=bool(a.skip_existing))
+    return 0
+
+
 def main(argv: Optional[Sequence[str]] = None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -175,7 +254,28 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     m.add_argument("--seeds", type=int, nargs="+", default=list(DEFAULT_HEADLINE_SEEDS))
     m.add_argument("--calc-types", nargs="+", default=None)
     m.add_argument("--out", type=Path, default=None)
+    r = sub.add_parser("run", help="the staged orchestrator: calibrate -> analyze -> headline")
+    r.add_argument("--stage", choices=["calibrate", "analyze", "headline", "all"], default="all")
+    r.add_argument("--config", type=Path, default=None)
+    r.add_argument("--data-path", type=Path, default=Path("data"))
+    r.add_argument("--sp-model-path-16384", "--sp-model-path", dest="sp_model_path", type=Path, default=None)
+    r.add_argument("--val-cache-dir", type=Path, default=Path("val_cache"))
+    r.add_argument("--checkpoint-path", type=Path, default=None,
+                   help="a trained trunk: the headline cells then only evaluate it")
+    r.add_argument("--world-size", type=int, default=4)
+    r.add_argument("--seeds", type=int, nargs="+", default=list(DEFAULT_HEADLINE_SEEDS))
+    r.add_argument("--calc-types", nargs="+", default=list(CALC_TYPES_DEFAULT))
+    r.add_argument("--manifest-path", type=Path, default=Path("calibration/manifest.json"))
+    r.add_argument("--trace-path", type=Path, default=None, help="probe report of an earlier calibrate stage")
+    r.add_argument("--headline-output-dir", type=Path, default=Path("results/exp27"))
+    r.add_argument("--headline-budget", type=float, default=600.0)
+    r.add_argument("--probe-docs", type=int, default=16)
+    r.add_argument("--limit", type=int, default=None)
+    r.add_argument("--skip-existing", action=argparse.BooleanOptionalAction, default=True)
+    r.add_argument("--dry-run", action="store_true")
     a = ap.parse_args(argv)
+    if a.cmd == "run":
+        return run_stages(a)
     if a.cmd == "calibrate":
         if a.checkpoint is None:
             man = write_manifest(a.manifest)

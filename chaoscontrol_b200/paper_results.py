@@ -159,6 +159,8 @@ def main(argv: Optional[list[str]] = None) -> int:
     add.add_argument("--seed", type=int, required=True)
     add.add_argument("--metrics", required=True, help="JSON object")
     add.add_argument("--artifact", action="append", default=[])
+    add.add_argument("--artifacts", nargs="*", default=[], help="artifact paths, as one list")
+    add.add_argument("--extras", default=None, help="JSON object stored with the record")
     a = ap.parse_args(argv)
     try:
         if a.cmd == "verify":
@@ -168,7 +170,8 @@ def main(argv: Optional[list[str]] = None) -> int:
                 print(json.dumps(asdict(r), sort_keys=True))
         else:
             rec = register(experiment=a.experiment, condition=a.condition, seed=a.seed, status=a.status,
-                           metrics=json.loads(a.metrics), config_hash=a.config_hash, artifacts=a.artifact,
+                           metrics=json.loads(a.metrics), config_hash=a.config_hash,
+                           artifacts=[*a.artifact, *a.artifacts], extras=json.loads(a.extras) if a.extras else None,
                            registry_path=a.registry)
             print(json.dumps(asdict(rec), sort_keys=True))
     except ValueError as exc:

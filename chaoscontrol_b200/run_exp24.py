@@ -218,7 +218,7 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     ap.add_argument("--world-size", type=int, default=None)
     ap.add_argument("--budget", type=float, default=None)
     ap.add_argument("--data-path", type=Path, default=Path("data"))
-    ap.add_argument("--sp-model-path", type=Path, default=None)
+    ap.add_argument("--sp-model-path", "--sp-model-path-16384", dest="sp_model_path", type=Path, default=None)
     ap.add_argument("--skip-existing", action=argparse.BooleanOptionalAction, default=True)
     ap.add_argument("--checkpoint-dir", type=Path, default=None)
     ap.add_argument("--full-val-score", action=argparse.BooleanOptionalAction, default=False)

@@ -27,6 +27,7 @@ import hashlib
 import json
 import os
 import random
+import subprocess
 import sys
 import time
 import traceback
@@ -45,7 +46,7 @@ FP8_UNAVAILABLE_PATTERNS = ("fp8 unavailable",)
 __all__ = ["config_hash", "require_config_match", "apply_seed", "write_result_json", "sync_error_flag",
            "warmup_and_restore", "run_one_seed", "run_matrix_worker", "check_output_integrity",
            "validate_matrix_world_size", "base_config", "build_default_matrix", "fp8_is_available",
-           "reject_stale_skip_markers", "filter_matrix_for_fp8", "write_skip_markers", "main"]
+           "reject_stale_skip_markers", "filter_matrix_for_fp8", "write_skip_markers", "launch_main", "main"]
 
 
 # ---------------------------------------------------------------- worker-side helpers
@@ -299,9 +300,83 @@ def write_skip_markers(skipped: list[dict], output_dir: Path) -> None:
                           {"config": e, "error": "skipped: fp8 unavailable on this host"})
 
 
+# ---------------------------------------------------------------- CLI (launcher)
+DEFAULT_LAUNCH_SEEDS = [1337, 2674, 4011, 5348]
+
+
+def launch_main(argv: Optional[list[str]] = None, *, call=subprocess.call) -> int:
+    """``python -m chaoscontrol_b200.runner_persistent_ddp launch ...``: builds (or reads) the matrix, runs
+    the pre-flight checks, starts ONE torchrun job whose ranks walk the whole matrix in a warm process group
+    (this module's worker), then fails closed on any real error among the expected outputs
+    (experiments/19_prereqs/run_persistent_launcher.py:382-540 of the reference)."""
+    ap = argparse.ArgumentParser(prog="runner_persistent_ddp launch", description="warm multi-seed launcher")
+    ap.add_argument("--data-path", required=True)
+    ap.add_argument("--sp-model-path", default=None)
+    ap.add_argument("--output-dir", required=True)
+    ap.add_argument("--budget", type=float, default=600.0)
+    ap.add_argument("--world-size", type=int, default=4)
+    ap.add_argument("--base-lr", type=float, default=0.128)
+    ap.add_argument("--seeds", type=int, nargs="+", default=DEFAULT_LAUNCH_SEEDS)
+    ap.add_argument("--conditions", nargs="+", default=["bf16", "fp8"])
+    ap.add_argument("--matrix-json", default=None, help="a pre-written matrix instead of conditions x seeds")
+    ap.add_argument("--rdzv-port", type=int, default=29500)
+    ap.add_argument("--dry-run", action="store_true")
+    a = ap.parse_args(argv)
+    out = Path(a.output_dir)
+    out.mkdir(parents=True, exist_ok=True)
+    if a.matrix_json:
+        entries = json.loads(Path(a.matrix_json).read_text())
+        if not isinstance(entries, list):
+            raise ValueError(f"--matrix-json file must be a JSON list, got {type(entries).__name__}")
+        print(f"[launcher] using external matrix: {a.matrix_json} ({len(entries)} entries)", flush=True)
+    else:
+        entries = build_default_matrix(a.world_size, a.base_lr, list(a.seeds), list(a.conditions))
+        print(f"[launcher] built matrix: conditions={a.conditions} seeds={a.seeds} ws={a.world_size} lr={a.base_lr} "
+              f"({len(entries)} entries)", flush=True)
+    validate_matrix_world_size(entries, a.world_size)
+    reject_stale_skip_markers(entries, out)
+    runnable, skipped = filter_matrix_for_fp8(entries, out)
+    if skipped:
+        write_skip_markers(skipped, out)
+    if not runnable:
+        print(f"[launcher] FAIL: zero runnable entries of {len(entries)} after the pre-flight checks; an empty run "
+              "is not a successful run", flush=True)
+        return 1
+    matrix_path = out / ".persistent_matrix.json"
+    matrix_path.write_text(json.dumps(runnable, indent=2, default=str))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={int(a.world_size)}",
+           "--master-addr", "127.0.0.1", "--master-port", str(int(a.rdzv_port)), "-m",
+           "chaoscontrol_b200.runner_persistent_ddp", "--config-matrix", str(matrix_path), "--data-path", a.data_path,
+           "--output-dir", str(out), "--budget", str(float(a.budget)), "--world-size", str(int(a.world_size))]
+    if a.sp_model_path:
+        cmd += ["--sp-model-path", a.sp_model_path]
+    if a.dry_run:
+        print("[launcher] dry-run; would execute:\n  " + " ".join(cmd))
+        print("[launcher] first runnable entry:\n  " + json.dumps(runnable[0], indent=2, default=str))
+        print(f"[launcher] matrix left at {matrix_path} for inspection")
+        return 0
+    print(f"[launcher] launching: {' '.join(cmd)}", flush=True)
+    try:
+        ret = call(cmd)
+    finally:
+        matrix_path.unlink(missing_ok=True)
+    if ret != 0:
+        print(f"[launcher] torchrun exited non-zero: {ret}", flush=True)
+        return int(ret)
+    ok, benign, bad = check_output_integrity(out, entries)
+    print(f"[launcher] outputs: success={ok} benign_skip={benign} errors={len(bad)} total_expected={len(entries)}", flush=True)
+    for err in bad:
+        print(f"  - {err}", flush=True)
+    return 1 if bad else 0
+
+
 # ---------------------------------------------------------------- CLI (worker)
 def main(argv: Optional[list[str]] = None) -> int:
-    ap = argparse.ArgumentParser(description="warm multi-run worker")
+    args = list(sys.argv[1:] if argv is None else argv)
+    if args and args[0] == "launch":
+        return launch_main(args[1:])
+    argv = args
+    ap = argparse.ArgumentParser(description="warm multi-run worker (or `launch ...` for the launcher)")
     ap.add_argument("--data-path", required=True)
     ap.add_argument("--sp-model-path", default=None)
     ap.add_argument("--config-matrix", required=True)

@@ -20,6 +20,7 @@ from __future__ import annotations
 import argparse
 import json
 import math
+import re
 from pathlib import Path
 from typing import Any, Iterable, Optional, Sequence
 
@@ -339,6 +340,87 @@ def render_curation(cells: dict[str, list[dict[str, float]]], gate: dict[str, An
     return render_markdown(rows) + "\n" + "\n".join(tail) + "\n"
 
 
+# ---------------------------------------------------------------------------------------------------------
+# Controller arms: throughput, loss, event-path health and learner-trace gradient diagnostics per arm
+# (scripts/analyze_step3_v3_diagnostics.py:31-190, without DuckDB).
+_ARM_NAME = re.compile(r"(arm_[a-z]+(?:_[a-z]+)*)_s(\d+)$")
+
+
+def load_controller_arms(results_dir: Path | str, prefix: str = "") -> dict[str, list[dict[str, Any]]]:
+    """Result files ``<prefix><arm>_s<seed>.json`` grouped by arm (``arm_d_simplex_online`` and the like)."""
+    arms: dict[str, list[dict[str, Any]]] = {}
+    for f in sorted(Path(results_dir).glob(f"{prefix}*.json")):
+        m = _ARM_NAME.search(f.stem[len(prefix):])
+        if not m:
+            continue
+        arms.setdefault(m.group(1), []).append({"seed": int(m.group(2)), "name": f.stem[len(prefix):],
+                                                "data": json.loads(f.read_text())})
+    for cells in arms.values():
+        cells.sort(key=lambda c: c["seed"])
+    return arms
+
+
+def controller_arm_report(results_dir: Path | str, traces_dir: Optional[Path | str] = None, *, prefix: str = "",
+                          trace_prefix: str = "", headline: Optional[tuple[str, str]] = None) -> dict[str, Any]:
+    """Per arm: cells, mean steps, steps per second and final loss (mean, sample std); per cell: how many
+    write / query events were emitted, dropped and ingested and how many SGD steps the learner took; per
+    arm over its learner traces (``<trace_prefix><arm>_s<seed>.ndjson``): the gradient-norm columns and the
+    entropy drift of credited actions; with ``headline=(baseline, sharp)`` the ratio table that says whether
+    the sharper start accumulates more gradient and weight."""
+    from .episodic.bootstrap_bench import compare_traces, headline_ratio, summarize_trace
+    arms = load_controller_arms(results_dir, prefix)
+    summary, health = [], []
+    trace_paths: dict[str, list[Path]] = {}
+    for arm in sorted(arms):
+        trains = [c["data"].get("train") or {} for c in arms[arm]]
+        sps = [t["steps"] / t["elapsed_s"] for t in trains if t.get("steps") and t.get("elapsed_s")]
+        losses = [float(t["final_loss"]) for t in trains if t.get("final_loss") is not None]
+        summary.append({"arm": arm, "n": len(trains), "mean_steps": _mean([float(t.get("steps", 0)) for t in trains]),
+                        "steps_per_s": _mean(sps) if sps else None, "steps_per_s_std": _std(sps) if len(sps) > 1 else None,
+                        "final_loss": _mean(losses) if losses else None,
+                        "final_loss_std": _std(losses) if len(losses) > 1 else None})
+        for c in arms[arm]:
+            tr = c["data"].get("train") or {}
+            ep = tr.get("episodic") or c["data"].get("episodic") or {}
+            aw = _get(c["data"], "train.mechanisms.episodic_async_writes") or {}
+            row = {"cell": c["name"],
+                   "emitted": int(ep.get("write_events_emitted", aw.get("pushed", 0)) or 0),
+                   "dropped": int(ep.get("write_events_dropped", aw.get("publish_drops", 0)) or 0),
+                   "ingested": int(ep.get("write_events_ingested", 0) or 0),
+                   "query_dropped": int(ep.get("query_events_dropped", 0) or 0),
+                   "errors": int(aw.get("drain_errors", 0) or 0), "sgd_steps": None}
+            if traces_dir is not None:
+                t = Path(traces_dir) / f"{trace_prefix}{c['name']}.ndjson"
+                if t.exists():
+                    row["sgd_steps"] = summarize_trace(t)["sgd_steps"]
+                    trace_paths.setdefault(arm, []).append(t)
+            health.append(row)
+    out: dict[str, Any] = {"arms": summary, "health": health}
+    if trace_paths:
+        out["traces"] = compare_traces(trace_paths)
+        if headline is not None and all(h in out["traces"] for h in headline):
+            out["headline"] = headline_ratio(out["traces"], headline[0], headline[1])
+    return out
+
+
+def render_controller_arms(rep: dict[str, Any]) -> str:
+    pm = lambda m, s_: "-" if m is None else (f"{m:.4f}" if s_ is None else f"{m:.4f} +/- {s_:.4f}")          # noqa: E731
+    parts = ["## Per arm", render_markdown([{"arm": r["arm"], "n": r["n"], "steps": int(r["mean_steps"]),
+                                              "steps/s": pm(r["steps_per_s"], r["steps_per_s_std"]),
+                                              "final loss": pm(r["final_loss"], r["final_loss_std"])} for r in rep["arms"]]),
+             "", "## Event path health", render_markdown(rep["health"])]
+    if "traces" in rep:
+        cols = ("credits", "sgd_steps_mean", "entropy_drift_mean", "grad_logits_l2_mean", "grad_w_lh_l2_mean",
+                "grad_w_lh_accum_l2_mean", "w_lh_l2_mean")
+        parts += ["", "## Credited actions (means over each arm's traces)",
+                  render_markdown([{"arm": a, **{c: v.get(c) for c in cols}} for a, v in rep["traces"].items()])]
+    if "headline" in rep:
+        h = rep["headline"]
+        parts += ["", f"## {h['sharp_arm']} over {h['baseline_arm']}: " + ("confirmed" if h["confirmed"] else "not confirmed"),
+                  render_markdown([{"column": c, **h[c]} for c in ("grad_w_lh_accum_l2", "w_lh_l2", "grad_logits_l2")])]
+    return "\n".join(parts)
+
+
 def main(argv: Optional[Sequence[str]] = None) -> int:
     ap = argparse.ArgumentParser(prog="chaoscontrol_b200.analysis")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -357,7 +439,19 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     g.add_argument("--by", default="arm")
     q = sub.add_parser("curation")
     q.add_argument("results_dir")
+    ca = sub.add_parser("controller-arms")
+    ca.add_argument("results_dir")
+    ca.add_argument("--traces-dir", default=None)
+    ca.add_argument("--prefix", default="")
+    ca.add_argument("--trace-prefix", default="")
+    ca.add_argument("--headline", nargs=2, default=None, metavar=("BASELINE_ARM", "SHARP_ARM"))
+    ca.add_argument("--json", action="store_true")
     a = ap.parse_args(argv)
+    if a.cmd == "controller-arms":
+        rep = controller_arm_report(a.results_dir, a.traces_dir, prefix=a.prefix, trace_prefix=a.trace_prefix,
+                                    headline=tuple(a.headline) if a.headline else None)
+        print(json.dumps(rep, indent=2) if a.json else render_controller_arms(rep))
+        return 0
     if a.cmd == "curation":
         cells = load_curation_cells(a.results_dir)
         print(render_curation(cells, curation_gate(cells)))

@@ -25,7 +25,10 @@ import numpy as np
 
 from . import native as N
 
-__all__ = ["run_bootstrap", "summarize_trace", "compare_traces", "main"]
+__all__ = ["run_bootstrap", "summarize_trace", "compare_traces", "headline_ratio", "main"]
+
+# per-credit gradient diagnostics the learner writes on every ``credit`` row
+GRADIENT_COLUMNS = ("grad_logits_l2", "grad_w_lh_l2", "grad_w_lh_accum_l2", "w_lh_l2")
 
 
 def _near_uniform_policy(temperature: float, seed: int):
@@ -41,7 +44,7 @@ def _near_uniform_policy(temperature: float, seed: int):
 def run_bootstrap(*, temperature: float = 1.0, events: int = 4000, seed: int = 0, good_vertex: int = 3,
                   reward_gap: float = 1.0, reward_std: float = 0.5, learning_rate: float = 1e-2,
                   sgd_interval: int = 16, entropy_beta: float = 0.0, num_slots: int = 64,
-                  report_every: int = 500) -> dict[str, Any]:
+                  report_every: int = 500, trace_path: Optional[Path | str] = None) -> dict[str, Any]:
     rng = np.random.default_rng(seed)
     pol = _near_uniform_policy(temperature, seed)
     start = pol.flat.copy()
@@ -49,6 +52,8 @@ def run_bootstrap(*, temperature: float = 1.0, events: int = 4000, seed: int = 0
                                      learning_rate=learning_rate, sgd_interval=sgd_interval, ema_interval=64,
                                      gerber_c=0.0, entropy_beta=entropy_beta)
     learner.initialize(pol)
+    if trace_path is not None:
+        learner.set_trace_path(str(trace_path))
     # one fixed simplex: the policy has to find the paying vertex from rewards alone
     V = rng.standard_normal((pol.N, pol.K_v)).astype(np.float32)
     Vn = V / np.linalg.norm(V, axis=1, keepdims=True)
@@ -105,10 +110,13 @@ def summarize_trace(path: Path | str, *, max_rows: Optional[int] = None) -> dict
             if kind == "skip":
                 reasons[str(row.get("status_reason", ""))] += 1
             for key in ("entropy", "p_chosen", "current_entropy", "advantage_final", "gerber_weight",
-                        "reward_shaped"):
+                        "reward_shaped", *GRADIENT_COLUMNS):
                 if isinstance(row.get(key), (int, float)):
                     sums[f"{kind}.{key}"].append(float(row[key]))
-    stats = {k: {"mean": float(np.mean(v)), "min": float(np.min(v)), "max": float(np.max(v)), "n": len(v)}
+            if kind == "credit" and all(isinstance(row.get(k), (int, float)) for k in ("entropy", "current_entropy")):
+                sums["credit.entropy_drift"].append(float(row["current_entropy"]) - float(row["entropy"]))
+    stats = {k: {"mean": float(np.mean(v)), "std": float(np.std(v, ddof=1)) if len(v) > 1 else 0.0,
+                 "min": float(np.min(v)), "max": float(np.max(v)), "n": len(v)}
              for k, v in sums.items()}
     return {"path": str(path), "rows": dict(counts), "skip_reasons": dict(reasons), "sgd_steps": last_sgd,
             "stats": stats}
@@ -131,9 +139,26 @@ def compare_traces(paths_by_arm: dict[str, Sequence[Path | str]]) -> dict[str, A
                     "decision_entropy_mean": mean_of("decision.entropy"),
                     "decision_entropy_min": mean_of("decision.entropy", "min"),
                     "credit_entropy_mean": mean_of("credit.current_entropy"),
+                    "entropy_drift_mean": mean_of("credit.entropy_drift"),
+                    **{f"{c}_mean": mean_of(f"credit.{c}") for c in GRADIENT_COLUMNS},
                     "abs_advantage_max": max((abs(s["stats"]["credit.advantage_final"][f]) for s in per
                                               if "credit.advantage_final" in s["stats"] for f in ("min", "max")),
                                              default=None)}
+    return out
+
+
+def headline_ratio(comparison: dict[str, Any], baseline_arm: str, sharp_arm: str) -> dict[str, Any]:
+    """The load-bearing comparison of the trace analysis: per credited action, does the arm that starts
+    sharp accumulate a larger gradient and end with larger weights than the arm at the default
+    temperature?  Ratios above one on ``grad_w_lh_accum_l2`` and ``w_lh_l2`` confirm that a uniform
+    start starves the policy gradient."""
+    a, b = comparison[baseline_arm], comparison[sharp_arm]
+    out: dict[str, Any] = {"baseline_arm": baseline_arm, "sharp_arm": sharp_arm}
+    for c in ("grad_w_lh_accum_l2", "w_lh_l2", "grad_logits_l2"):
+        x, y = a.get(f"{c}_mean"), b.get(f"{c}_mean")
+        out[c] = {"baseline": x, "sharp": y, "ratio": (y / x) if x and y is not None else None}
+    r1, r2 = out["grad_w_lh_accum_l2"]["ratio"], out["w_lh_l2"]["ratio"]
+    out["confirmed"] = bool(r1 is not None and r2 is not None and r1 > 1.0 and r2 > 1.0)
     return out
 
 
@@ -143,10 +168,15 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     ap.add_argument("--temperatures", type=float, nargs="+", default=[1.0, 0.2, 0.05])
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--traces", nargs="*", default=None, help="arm=path[,path...] learner traces to compare instead")
+    ap.add_argument("--headline", nargs=2, metavar=("BASELINE_ARM", "SHARP_ARM"), default=None,
+                    help="with --traces: gradient / weight-norm ratios of the second arm over the first")
     a = ap.parse_args(argv)
     if a.traces:
         arms = {spec.split("=", 1)[0]: spec.split("=", 1)[1].split(",") for spec in a.traces}
-        print(json.dumps(compare_traces(arms), indent=2))
+        cmp = compare_traces(arms)
+        if a.headline:
+            cmp = {"arms": cmp, "headline": headline_ratio(cmp, a.headline[0], a.headline[1])}
+        print(json.dumps(cmp, indent=2))
         return 0
     print(f"{'T':>6} {'max_p0':>8} {'entropy':>8} {'p_good':>7} {'drift':>8} {'sgd':>5}")
     for T in a.temperatures:

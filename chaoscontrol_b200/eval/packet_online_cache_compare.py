@@ -54,3 +54,30 @@ def load_and_run_packet_online_cache_compare(*, artifact_path: str | Path, val_c
     model._compare_artifact_path = str(artifact_path)
     return run_packet_online_cache_compare(model=model, val_cache=load_val_cache(Path(val_cache_dir)), device=dev,
                                            compare_config=compare_config, output_json=output_json)
+
+
+def main(argv: Optional[list[str]] = None) -> int:
+    """``python -m chaoscontrol_b200.eval.packet_online_cache_compare --artifact-path A --val-cache-dir D
+    --output-json O`` (scripts/run_packet_online_cache_compare.py:22-47)."""
+    import argparse
+    ap = argparse.ArgumentParser(description="Score one artifact with its trained-in episodic store and with the "
+                                             "store emptied first, and keep the summary.")
+    ap.add_argument("--artifact-path", required=True, type=Path)
+    ap.add_argument("--val-cache-dir", required=True, type=Path)
+    ap.add_argument("--output-json", required=True, type=Path)
+    ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
+    ap.add_argument("--chunk-tokens", type=int, default=256)
+    ap.add_argument("--write-tokens-per-chunk", type=int, default=16)
+    ap.add_argument("--gate-value", type=float, default=1.0)
+    ap.add_argument("--decay", type=float, default=1.0)
+    a = ap.parse_args(argv)
+    res = load_and_run_packet_online_cache_compare(
+        artifact_path=a.artifact_path, val_cache_dir=a.val_cache_dir, device=a.device,
+        compare_config={"chunk_tokens": a.chunk_tokens, "write_tokens_per_chunk": a.write_tokens_per_chunk,
+                        "gate_value": a.gate_value, "decay": a.decay}, output_json=a.output_json)
+    print(json.dumps(res, indent=2, sort_keys=True, default=str))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

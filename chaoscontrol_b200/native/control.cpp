@@ -7,6 +7,7 @@
 #include <cstring>
 #include <fstream>
 #include <limits>
+#include <string>
 #include <thread>
 
 // The policy forward / backward are short dense loops over runtime sizes; compile them for AVX2+FMA and for
@@ -460,6 +461,7 @@ void SimplexOnlineLearner::record_decision(uint64_t slot_id, ActionRecord rec) {
   if (trace_fp_ && init_ && rec.V.size() == static_cast<std::size_t>(fast_.N) * fast_.K_v &&
       rec.E.size() == static_cast<std::size_t>(fast_.N) * fast_.N && rec.feats.size() == fast_.K_s) {
     SimplexForward f = simplex_forward(fast_, rec.V.data(), rec.E.data(), rec.feats.data());
+    rec.entropy = static_cast<float>(entropy_of(f.p));
     std::fprintf(trace_fp_, "{\"row_type\":\"decision\",\"status\":\"ok\",\"gpu_step\":%llu,"
                             "\"slot_id\":%llu,\"chosen_idx\":%u,\"p_chosen\":%g,\"entropy\":%g,"
                             "\"temperature\":%g,\"entropy_beta\":%g,\"sgd_steps\":%llu}\n",
@@ -509,23 +511,47 @@ void SimplexOnlineLearner::on_replay_outcome(const wire::ReplayOutcome& ev) {
     if (gw == 0.f) { ++tel_.gerber_rejected; continue; }
     ++tel_.gerber_accepted;
     const float adv = recency_decay(adv_std, ev.gpu_step, rec.gpu_step, gamma_);
+    // trace-only diagnostics of this one credit: the W_lh block of the gradient accumulator before
+    // the backward pass (its change is this credit's own W_lh gradient)
+    const std::size_t lh_off = static_cast<std::size_t>(fast_.K_v) * fast_.H + fast_.H, lh_n = fast_.H;
+    std::vector<float> lh_before;
+    if (trace_fp_) lh_before.assign(grad_.begin() + lh_off, grad_.begin() + lh_off + lh_n);
     simplex_backward(fast_, f, rec.V.data(), rec.E.data(), rec.feats.data(), rec.chosen, adv,
                      entropy_beta_, grad_.data());
     const double ent = entropy_of(f.p);
     tel_.last_entropy = static_cast<float>(ent);
     ++tel_.credited_actions;
-    if (trace_fp_)
+    if (trace_fp_) {
+      double g_lh = 0.0, g_acc = 0.0, w_lh = 0.0, g_logit = 0.0;
+      for (std::size_t h = 0; h < lh_n; ++h) {
+        const double d = grad_[lh_off + h] - lh_before[h];
+        g_lh += d * d;
+        g_acc += static_cast<double>(grad_[lh_off + h]) * grad_[lh_off + h];
+        w_lh += static_cast<double>(fast_.W_lh[h]) * fast_.W_lh[h];
+      }
+      for (std::size_t i = 0; i < f.p.size(); ++i) {             // d loss / d logits, as the backward forms it
+        const float pi = f.p[i];
+        float dz = -adv * ((i == rec.chosen ? 1.f : 0.f) - pi);
+        if (entropy_beta_ != 0.f && pi > 0.f) dz += entropy_beta_ * pi * (std::log(pi) + static_cast<float>(ent));
+        dz /= fast_.temperature;
+        g_logit += static_cast<double>(dz) * dz;
+      }
       std::fprintf(trace_fp_, "{\"row_type\":\"credit\",\"status\":\"ok\",\"gpu_step\":%llu,"
                               "\"slot_id\":%u,\"selection_step\":%llu,\"chosen_idx\":%u,\"p_chosen\":%g,"
                               "\"p_current_chosen\":%g,\"current_entropy\":%g,\"reward_shaped\":%g,"
                               "\"advantage_raw\":%g,\"advantage_standardized\":%g,\"gerber_weight\":%g,"
                               "\"advantage_final\":%g,\"behavior_logprob_margin\":%g,"
-                              "\"current_logprob_margin\":%g,\"sgd_steps\":%llu,\"ema_blends\":%llu}\n",
+                              "\"current_logprob_margin\":%g,\"entropy\":%s,\"grad_logits_l2\":%g,"
+                              "\"grad_w_lh_l2\":%g,\"grad_w_lh_accum_l2\":%g,\"w_lh_l2\":%g,"
+                              "\"sgd_steps\":%llu,\"ema_blends\":%llu}\n",
                    static_cast<unsigned long long>(ev.gpu_step), ev.slot_id,
                    static_cast<unsigned long long>(rec.gpu_step), rec.chosen, rec.p_chosen,
                    f.p[rec.chosen], ent, reward, adv_raw, adv_std, gw, adv, then, now,
+                   rec.entropy >= 0.f ? std::to_string(rec.entropy).c_str() : "null",
+                   std::sqrt(g_logit), std::sqrt(g_lh), std::sqrt(g_acc), std::sqrt(w_lh),
                    static_cast<unsigned long long>(tel_.sgd_steps),
                    static_cast<unsigned long long>(tel_.ema_blends));
+    }
     ++since_sgd_;
     ema_.tick();
     maybe_sgd();

@@ -142,6 +142,7 @@ struct ActionRecord {
   uint32_t policy_version = 0, chosen = 0;
   float p_chosen = 0.f;
   int32_t bucket = 0;
+  float entropy = -1.f;   // policy entropy at decision time; filled only while a trace is open
   std::vector<float> V, E, feats;
 };
 struct LearnerTelemetry {

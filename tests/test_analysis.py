@@ -99,3 +99,33 @@ def test_curation_gate_escalation_and_errors(tmp_path):
     assert g["needs_escalation"] and g["sigma_b"] == pytest.approx(0.01)
     with pytest.raises(FileNotFoundError):
         A.load_curation_cells(tmp_path / "nothing")
+
+
+def test_controller_arm_report_reads_results_and_learner_traces(tmp_path, capsys):
+    """Per-arm table, event-path health and the sharp-over-default gradient ratios from real learner traces."""
+    import json
+    from chaoscontrol_b200 import analysis as A
+    from chaoscontrol_b200.episodic import bootstrap_bench as B
+    res, tr = tmp_path / "results", tmp_path / "traces"
+    res.mkdir(); tr.mkdir()
+    for arm, T in (("arm_d_simplex_online", 1.0), ("arm_f_simplex_sharp_online", 0.2)):
+        for seed in (1, 2):
+            cell = {"train": {"steps": 100 + seed, "elapsed_s": 10.0, "final_loss": 4.0 + 0.1 * seed,
+                              "episodic": {"write_events_emitted": 50, "write_events_dropped": seed, "write_events_ingested": 49}}}
+            (res / f"exp_{arm}_s{seed}.json").write_text(json.dumps(cell))
+            B.run_bootstrap(temperature=T, events=200, seed=seed, trace_path=tr / f"ctl_{arm}_s{seed}.ndjson")
+    (res / "exp_unrelated.json").write_text("{}")
+    rep = A.controller_arm_report(res, tr, prefix="exp_", trace_prefix="ctl_",
+                                  headline=("arm_d_simplex_online", "arm_f_simplex_sharp_online"))
+    assert [r["arm"] for r in rep["arms"]] == ["arm_d_simplex_online", "arm_f_simplex_sharp_online"]
+    d = rep["arms"][0]
+    assert d["n"] == 2 and abs(d["steps_per_s"] - 10.15) < 1e-9 and abs(d["final_loss"] - 4.15) < 1e-9 and d["final_loss_std"] > 0
+    assert [h["dropped"] for h in rep["health"]] == [1, 2, 1, 2] and all(h["sgd_steps"] > 0 for h in rep["health"])
+    assert rep["traces"]["arm_f_simplex_sharp_online"]["seeds"] == 2 and rep["headline"]["grad_logits_l2"]["ratio"] > 1
+    assert A.main(["controller-arms", str(res), "--traces-dir", str(tr), "--prefix", "exp_", "--trace-prefix", "ctl_",
+                   "--headline", "arm_d_simplex_online", "arm_f_simplex_sharp_online"]) == 0
+    out = capsys.readouterr().out
+    assert "## Per arm" in out and "Event path health" in out and "arm_f_simplex_sharp_online over arm_d_simplex_online" in out
+    # without traces the report still has the two result tables
+    rep2 = A.controller_arm_report(res, None, prefix="exp_")
+    assert "traces" not in rep2 and all(h["sgd_steps"] is None for h in rep2["health"])

@@ -2,6 +2,8 @@
 import json
 import math
 
+import pytest
+
 from chaoscontrol_b200.episodic import bootstrap_bench as B
 
 
@@ -39,3 +41,23 @@ def test_trace_summary_and_arm_comparison(tmp_path, capsys):
     assert cmp["arm_f"]["abs_advantage_max"] == 0.8
     assert B.main(["--traces", f"arm_d={tmp_path / 'd1.ndjson'}"]) == 0
     assert "arm_d" in capsys.readouterr().out
+
+
+def test_credit_rows_carry_gradient_diagnostics_and_the_headline_ratio(tmp_path):
+    """A sharper start accumulates a larger policy gradient per credited action than the default start."""
+    import json
+    paths = {}
+    for arm, T in (("arm_d", 1.0), ("arm_f", 0.2)):
+        paths[arm] = tmp_path / f"{arm}.ndjson"
+        B.run_bootstrap(temperature=T, events=400, seed=0, trace_path=paths[arm])
+    rows = [json.loads(l) for l in paths["arm_f"].read_text().splitlines()]
+    credit = [r for r in rows if r["row_type"] == "credit"]
+    assert credit and all(set(B.GRADIENT_COLUMNS) <= set(r) for r in credit)
+    assert all(r["grad_w_lh_accum_l2"] >= 0 and r["w_lh_l2"] >= 0 and r["entropy"] is not None for r in credit)
+    # the accumulator holds this credit's own gradient right after an SGD apply emptied it
+    first = credit[0]
+    assert first["grad_w_lh_accum_l2"] == pytest.approx(first["grad_w_lh_l2"], rel=1e-4)
+    cmp = B.compare_traces({k: [v] for k, v in paths.items()})
+    assert cmp["arm_f"]["grad_logits_l2_mean"] > 0 and cmp["arm_f"]["entropy_drift_mean"] is not None
+    h = B.headline_ratio(cmp, "arm_d", "arm_f")
+    assert h["grad_logits_l2"]["ratio"] > 1.0 and isinstance(h["confirmed"], bool)

@@ -185,3 +185,21 @@ def test_seeded_versus_empty_store_compare(setup, tmp_path):
     assert out["seeded"]["tokens_scored"] == out["empty"]["tokens_scored"]
     assert out["delta_bpb"] == pytest.approx(out["empty"]["bpb"] - out["seeded"]["bpb"])
     assert (tmp_path / "cmp.json").exists() and out["compare_type"] == "packet_online_cache"
+
+
+def test_seeded_versus_empty_compare_command_line(setup, tmp_path, monkeypatch, capsys):
+    import json
+    from chaoscontrol_b200.eval import packet_online_cache_compare as P
+    _, vc = setup
+    seen = {}
+
+    def fake(**kw):
+        seen.update(kw)
+        return P.run_packet_online_cache_compare(model=_memory_model(), val_cache=vc, device=torch.device("cpu"),
+                                                 compare_config=kw["compare_config"], output_json=kw["output_json"])
+    monkeypatch.setattr(P, "load_and_run_packet_online_cache_compare", fake)
+    assert P.main(["--artifact-path", "a.ccb", "--val-cache-dir", "vc", "--output-json", str(tmp_path / "o.json"),
+                   "--device", "cpu", "--chunk-tokens", "8", "--write-tokens-per-chunk", "1", "--decay", "0.9"]) == 0
+    assert seen["compare_config"] == {"chunk_tokens": 8, "write_tokens_per_chunk": 1, "gate_value": 1.0, "decay": 0.9}
+    printed = json.loads(capsys.readouterr().out)
+    assert printed["compare_type"] == "packet_online_cache" and json.loads((tmp_path / "o.json").read_text())["delta_bpb"] == printed["delta_bpb"]
